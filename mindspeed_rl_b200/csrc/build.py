@@ -22,6 +22,7 @@ PKG = CSRC.parent
 OUT_DIR = PKG / "_C"
 OBJ_DIR = OUT_DIR / "obj"
 LIB_PATH = OUT_DIR / "libmsrl_b200.so"
+HOST_LIB_PATH = OUT_DIR / "libmsrl_host.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -71,15 +72,25 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     srcs = sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as pool:
         objs = list(pool.map(lambda s: _compile_one(s, force, log_dir), srcs))
-    need_link = force or not LIB_PATH.exists() or any(
-        o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs)
-    if need_link:
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
-               "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-Xcompiler", "-fPIC",
+    cu_objs = [o for s, o in zip(srcs, objs) if s.suffix == ".cu"]
+    host_objs = [o for s, o in zip(srcs, objs) if s.suffix == ".cpp"]
+
+    def stale(lib, deps):
+        return force or not lib.exists() or any(o.stat().st_mtime > lib.stat().st_mtime for o in deps)
+
+    if cu_objs and stale(LIB_PATH, cu_objs):
+        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, cu_objs),
+               "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-Xcompiler", "-fPIC",
                "-Xlinker", "-z,noexecstack"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    if host_objs and stale(HOST_LIB_PATH, host_objs):
+        # host-only runtime pieces (block manager, ...) load on machines without CUDA
+        cmd = ["g++", "-shared", "-o", str(HOST_LIB_PATH), *map(str, host_objs), "-pthread"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"host link failed:\n{res.stdout}\n{res.stderr}")
     if verbose:
         for s in srcs:
             log = log_dir / (s.stem + ".log")

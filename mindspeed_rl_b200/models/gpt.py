@@ -1,0 +1,483 @@
+"""Decoder-only transformer (Qwen2 / Qwen3 dense and MoE families) for packed token streams.
+
+Design notes
+------------
+* Activations are always packed ``[T, H]`` ("THD"); sequences are delimited by ``cu_seqlens``.
+* Each transformer layer is **one autograd node** with a hand-written backward.  With
+  ``recompute_granularity == "full"`` only the layer input is kept and the forward is re-run
+  inside the backward; otherwise the intermediates are kept.  Parameter gradients are
+  accumulated in place into ``param.main_grad`` (the contiguous DDP buffer) -- or ``param.grad``
+  when the model is not wrapped -- so autograd never materialises a second copy.
+* Parameter names and layouts follow Megatron-mcore (``decoder.layers.N.self_attention.linear_qkv``
+  with the per-KV-group interleave, ``mlp.linear_fc1`` as ``[gate; up]`` per TP shard, ...), which is
+  what the checkpoint format and the resharding planner expect
+  (reference name map: ``mindspeed_rl/workers/resharding/weight_adaptor.py:54-65``).
+* Tensor/sequence parallel communication goes through ``TPComm`` (NCCL baseline or fused kernels).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..ops import QKVLayout
+from ..parallel.tp_comm import NO_TP, TPComm
+from .transformer_config import TransformerConfig
+
+
+@dataclass
+class PackedMeta:
+    """Per micro-batch sequence metadata (device tensors are int32)."""
+    cu_seqlens: torch.Tensor          # [B+1]
+    max_seqlen: int
+    positions: torch.Tensor           # [T]
+    cp: Any = None                    # context-parallel helper (parallel.context_parallel), optional
+
+    @classmethod
+    def from_lengths(cls, lengths, device, align: int = 1) -> "PackedMeta":
+        lens = torch.as_tensor(lengths, dtype=torch.int32)
+        padded = (lens + (align - 1)) // align * align
+        cu = torch.zeros(lens.numel() + 1, dtype=torch.int32)
+        cu[1:] = torch.cumsum(padded, 0)
+        pos = torch.cat([torch.arange(int(n), dtype=torch.int32) for n in padded.tolist()]) \
+            if lens.numel() else torch.zeros(0, dtype=torch.int32)
+        return cls(cu.to(device), int(padded.max()) if lens.numel() else 0, pos.to(device))
+
+
+# ---------------------------------------------------------------------------------------------------
+# gradient accumulation helpers
+# ---------------------------------------------------------------------------------------------------
+def grad_buffer(p: torch.Tensor) -> torch.Tensor:
+    g = getattr(p, "main_grad", None)
+    if g is None:
+        if p.grad is None:
+            p.grad = torch.zeros_like(p)
+        g = p.grad
+    return g
+
+
+def accum_wgrad(p: torch.Tensor, dy: torch.Tensor, x: torch.Tensor) -> None:
+    """``grad(p) += dy^T x`` for a weight ``p [out, in]``."""
+    if not p.requires_grad:
+        return
+    g = grad_buffer(p)
+    if g.dtype == dy.dtype:
+        g.addmm_(dy.t(), x)
+    else:
+        g.add_(torch.matmul(dy.t(), x).to(g.dtype))
+
+
+def accum_vec(p: torch.Tensor, v: torch.Tensor) -> None:
+    if p.requires_grad:
+        grad_buffer(p).add_(v.to(grad_buffer(p).dtype))
+
+
+class _Holder(nn.Module):
+    """Parameter holder so that state-dict keys read ``<name>.weight`` / ``<name>.bias``."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        super().__init__()
+        self.weight = nn.Parameter(weight)
+        if bias is not None:
+            self.bias = nn.Parameter(bias)
+        else:
+            self.bias = None
+
+
+def _normal(shape, std, dtype, device, gen=None):
+    t = torch.empty(shape, dtype=torch.float32, device=device)
+    t.normal_(0.0, std, generator=gen)
+    return t.to(dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Transformer layer
+# ---------------------------------------------------------------------------------------------------
+class SelfAttention(nn.Module):
+    def __init__(self, cfg: TransformerConfig, device, gen):
+        super().__init__()
+        tp = cfg.tensor_model_parallel_size
+        if cfg.num_attention_heads % tp or cfg.num_query_groups % tp:
+            raise ValueError("attention heads and query groups must be divisible by the TP size")
+        nh, nkv, hd = cfg.num_attention_heads // tp, cfg.num_query_groups // tp, cfg.head_dim
+        self.layout = QKVLayout(nh, nkv, hd, interleaved=True)
+        dt, std = cfg.params_dtype, cfg.init_method_std
+        out_std = std / math.sqrt(2.0 * cfg.num_layers)
+        bias = torch.zeros(self.layout.width, dtype=dt, device=device) if cfg.add_qkv_bias else None
+        self.linear_qkv = _Holder(_normal((self.layout.width, cfg.hidden_size), std, dt, device, gen), bias)
+        self.linear_proj = _Holder(_normal((cfg.hidden_size, nh * hd), out_std, dt, device, gen))
+        if cfg.qk_layernorm:
+            self.q_layernorm = _Holder(torch.ones(hd, dtype=dt, device=device))
+            self.k_layernorm = _Holder(torch.ones(hd, dtype=dt, device=device))
+        else:
+            self.q_layernorm = self.k_layernorm = None
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: TransformerConfig, device, gen, ffn: Optional[int] = None):
+        super().__init__()
+        tp = cfg.tensor_model_parallel_size
+        f = (ffn or cfg.ffn_hidden_size) // tp
+        dt, std = cfg.params_dtype, cfg.init_method_std
+        out_std = std / math.sqrt(2.0 * cfg.num_layers)
+        self.linear_fc1 = _Holder(_normal((2 * f, cfg.hidden_size), std, dt, device, gen))
+        self.linear_fc2 = _Holder(_normal((cfg.hidden_size, f), out_std, dt, device, gen))
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, cfg: TransformerConfig, layer_number: int, device, gen, comm: TPComm):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_number = layer_number
+        self.comm = comm
+        dt = cfg.params_dtype
+        self.input_layernorm = _Holder(torch.ones(cfg.hidden_size, dtype=dt, device=device))
+        self.self_attention = SelfAttention(cfg, device, gen)
+        self.pre_mlp_layernorm = _Holder(torch.ones(cfg.hidden_size, dtype=dt, device=device))
+        if cfg.layer_is_moe(layer_number):
+            from .moe import MoELayer
+
+            self.mlp = MoELayer(cfg, device, gen)
+        else:
+            self.mlp = MLP(cfg, device, gen)
+        self._rope_table = None
+
+    # -- helpers ------------------------------------------------------------------------------------
+    def rope_table(self, device) -> torch.Tensor:
+        if self._rope_table is None or self._rope_table.device != device:
+            c = self.cfg
+            self._rope_table = ops.rope_table(c.max_position_embeddings, c.head_dim, c.rotary_base,
+                                              device, c.rope_scaling)
+        return self._rope_table
+
+    def forward(self, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+        if torch.is_grad_enabled() and (h.requires_grad or any(p.requires_grad for p in self.parameters())):
+            return _LayerFn.apply(h, self, meta)
+        out, _ = layer_forward(self, h, meta, keep=False)
+        return out
+
+
+def _attention_core_fwd(layer: TransformerLayer, qkv: torch.Tensor, meta: PackedMeta):
+    """qk-norm -> rope -> attention.  Returns (attn_out, lse, saved_pre_norm, rstd_q, rstd_k)."""
+    sa = layer.self_attention
+    lay = sa.layout
+    pre = rq = rk = None
+    if sa.q_layernorm is not None:
+        pre = qkv.clone()
+        rq = ops.headnorm_fwd_(qkv, lay, "q", sa.q_layernorm.weight, layer.cfg.norm_epsilon)
+        rk = ops.headnorm_fwd_(qkv, lay, "k", sa.k_layernorm.weight, layer.cfg.norm_epsilon)
+    ops.rope_(qkv, lay, meta.positions, layer.rope_table(qkv.device))
+    if meta.cp is not None:
+        attn, lse = meta.cp.attention_fwd(qkv, lay, meta)
+    else:
+        attn, lse = ops.attn_varlen_fwd(qkv, lay, meta.cu_seqlens, meta.max_seqlen, causal=True)
+    return attn, lse, pre, rq, rk
+
+
+def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, keep: bool
+                  ) -> Tuple[torch.Tensor, Optional[Dict[str, Any]]]:
+    """Forward of one layer; ``keep`` returns the intermediates the backward needs."""
+    cfg, comm, sa = layer.cfg, layer.comm, layer.self_attention
+    eps = cfg.norm_epsilon
+    x1, rstd1, _ = ops.rmsnorm_fwd(h, layer.input_layernorm.weight, eps, want_rstd=keep)
+    x1g = comm.gather_seq(x1)
+    qkv = torch.matmul(x1g, sa.linear_qkv.weight.t())
+    if sa.linear_qkv.bias is not None:
+        qkv += sa.linear_qkv.bias
+    attn, lse, pre, rq, rk = _attention_core_fwd(layer, qkv, meta)
+    proj = comm.reduce_out(torch.matmul(attn, sa.linear_proj.weight.t()))
+    h1 = ops.add(h, proj)
+    x2, rstd2, _ = ops.rmsnorm_fwd(h1, layer.pre_mlp_layernorm.weight, eps, want_rstd=keep)
+    x2g = comm.gather_seq(x2)
+    if isinstance(layer.mlp, MLP):
+        gu = torch.matmul(x2g, layer.mlp.linear_fc1.weight.t())
+        y = ops.swiglu_fwd(gu)
+        mlp_out = comm.reduce_out(torch.matmul(y, layer.mlp.linear_fc2.weight.t()))
+        mlp_ctx = (gu, y) if keep else None
+    else:
+        mlp_out, mlp_ctx = layer.mlp.forward_tokens(x2g, comm, keep)
+    h2 = ops.add(h1, mlp_out)
+    if not keep:
+        return h2, None
+    ctx = dict(h=h, rstd1=rstd1, x1g=x1g, qkv=qkv, attn=attn, lse=lse, pre=pre, rq=rq, rk=rk, h1=h1,
+               rstd2=rstd2, x2g=x2g, mlp_ctx=mlp_ctx)
+    return h2, ctx
+
+
+def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMeta, dh2: torch.Tensor
+                   ) -> torch.Tensor:
+    cfg, comm, sa = layer.cfg, layer.comm, layer.self_attention
+    lay = sa.layout
+    # ---- MLP ----
+    d_out = comm.reduce_out_bwd(dh2)
+    if isinstance(layer.mlp, MLP):
+        gu, y = ctx["mlp_ctx"]
+        fc1, fc2 = layer.mlp.linear_fc1.weight, layer.mlp.linear_fc2.weight
+        dy = torch.matmul(d_out, fc2)
+        accum_wgrad(fc2, d_out, y)
+        dgu = ops.swiglu_bwd(gu, dy)
+        dx2g = torch.matmul(dgu, fc1)
+        accum_wgrad(fc1, dgu, ctx["x2g"])
+    else:
+        dx2g = layer.mlp.backward_tokens(ctx["mlp_ctx"], ctx["x2g"], d_out, comm)
+    dx2 = comm.gather_seq_bwd(dx2g)
+    dh1 = ops.rmsnorm_bwd(dx2, ctx["h1"], layer.pre_mlp_layernorm.weight, ctx["rstd2"],
+                          grad_buffer(layer.pre_mlp_layernorm.weight), dres=dh2)
+    # ---- attention ----
+    d_proj = comm.reduce_out_bwd(dh1)
+    dattn = torch.matmul(d_proj, sa.linear_proj.weight)
+    accum_wgrad(sa.linear_proj.weight, d_proj, ctx["attn"])
+    if meta.cp is not None:
+        dqkv = meta.cp.attention_bwd(dattn, ctx["qkv"], ctx["attn"], ctx["lse"], lay, meta)
+    else:
+        dqkv = ops.attn_varlen_bwd(dattn, ctx["qkv"], ctx["attn"], ctx["lse"], lay, meta.cu_seqlens,
+                                   meta.max_seqlen, causal=True)
+    ops.rope_(dqkv, lay, meta.positions, layer.rope_table(dqkv.device), inverse=True)
+    if sa.q_layernorm is not None:
+        ops.headnorm_bwd_(dqkv, ctx["pre"], lay, "q", sa.q_layernorm.weight, ctx["rq"],
+                          grad_buffer(sa.q_layernorm.weight))
+        ops.headnorm_bwd_(dqkv, ctx["pre"], lay, "k", sa.k_layernorm.weight, ctx["rk"],
+                          grad_buffer(sa.k_layernorm.weight))
+    dx1g = torch.matmul(dqkv, sa.linear_qkv.weight)
+    accum_wgrad(sa.linear_qkv.weight, dqkv, ctx["x1g"])
+    if sa.linear_qkv.bias is not None and sa.linear_qkv.bias.requires_grad:
+        ops.colsum_accumulate(dqkv, grad_buffer(sa.linear_qkv.bias))
+    dx1 = comm.gather_seq_bwd(dx1g)
+    dh = ops.rmsnorm_bwd(dx1, ctx["h"], layer.input_layernorm.weight, ctx["rstd1"],
+                         grad_buffer(layer.input_layernorm.weight), dres=dh1)
+    return dh
+
+
+class _LayerFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h: torch.Tensor, layer: TransformerLayer, meta: PackedMeta):
+        full_recompute = layer.cfg.recompute_granularity == "full"
+        out, saved = layer_forward(layer, h, meta, keep=not full_recompute)
+        ctx.layer, ctx.meta, ctx.full = layer, meta, full_recompute
+        if full_recompute:
+            ctx.save_for_backward(h)
+        else:
+            ctx.saved = saved
+        return out
+
+    @staticmethod
+    def backward(ctx, dh2: torch.Tensor):
+        layer, meta = ctx.layer, ctx.meta
+        if ctx.full:
+            (h,) = ctx.saved_tensors
+            with torch.no_grad():
+                _, saved = layer_forward(layer, h, meta, keep=True)
+        else:
+            saved = ctx.saved
+            ctx.saved = None
+        with torch.no_grad():
+            dh = layer_backward(layer, saved, meta, dh2.contiguous())
+        return dh, None, None
+
+
+# ---------------------------------------------------------------------------------------------------
+# Embedding / output
+# ---------------------------------------------------------------------------------------------------
+class _EmbedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, weight: torch.Tensor, ids: torch.Tensor, comm: TPComm, vocab_start: int):
+        v_local = weight.shape[0]
+        if comm.world_size > 1:
+            local = ids - vocab_start
+            mine = (local >= 0) & (local < v_local)
+            out = weight[local.clamp(0, v_local - 1)]
+            out = out * mine.unsqueeze(-1).to(out.dtype)
+            out = comm.reduce_out(out)
+        else:
+            local, mine = ids, None
+            out = weight[ids]
+        ctx.save_for_backward(local, mine if mine is not None else ids.new_empty(0))
+        ctx.comm, ctx.weight = comm, weight
+        return out
+
+    @staticmethod
+    def backward(ctx, dout: torch.Tensor):
+        local, mine = ctx.saved_tensors
+        comm, weight = ctx.comm, ctx.weight
+        if weight.requires_grad:
+            d = comm.reduce_out_bwd(dout.contiguous())
+            g = grad_buffer(weight)
+            if mine.numel():
+                d = d * mine.unsqueeze(-1).to(d.dtype)
+                local = local.clamp(0, weight.shape[0] - 1)
+            g.index_add_(0, local, d.to(g.dtype))
+        return None, None, None, None
+
+
+class _LogProbHeadFn(torch.autograd.Function):
+    """final RMSNorm -> LM head -> (log p(label), entropy), logits never fully materialised."""
+
+    @staticmethod
+    def forward(ctx, h, model: "GPTModel", labels, inv_temp: float, want_entropy: bool):
+        cfg, comm = model.cfg, model.comm
+        x, rstd, _ = ops.rmsnorm_fwd(h, model.decoder.final_layernorm.weight, cfg.norm_epsilon)
+        xg = comm.gather_seq(x)
+        w = model.output_weight()
+        logp, ent, lse = ops.lmhead_logprob_fwd(xg, w, labels, inv_temp, model.vocab_start, comm.group,
+                                                want_entropy)
+        ctx.model, ctx.inv_temp = model, inv_temp
+        ctx.save_for_backward(h, rstd, labels, lse, ent if ent is not None else lse.new_empty(0))
+        if ent is None:
+            ent = torch.zeros_like(logp)
+            ctx.mark_non_differentiable(ent)
+        return logp, ent
+
+    @staticmethod
+    def backward(ctx, dlogp, dent):
+        model = ctx.model
+        cfg, comm = model.cfg, model.comm
+        h, rstd, labels, lse, ent = ctx.saved_tensors
+        with torch.no_grad():
+            x, _, _ = ops.rmsnorm_fwd(h, model.decoder.final_layernorm.weight, cfg.norm_epsilon,
+                                      want_rstd=False)
+            xg = comm.gather_seq(x)
+            w = model.output_weight()
+            has_ent = ent.numel() > 0 and dent is not None
+            dxg = ops.lmhead_logprob_bwd(xg, w, labels, lse, ent if has_ent else None, dlogp,
+                                         dent if has_ent else None,
+                                         grad_buffer(w) if w.requires_grad else None, ctx.inv_temp,
+                                         model.vocab_start)
+            dx = comm.gather_seq_bwd(dxg)
+            dh = ops.rmsnorm_bwd(dx, h, model.decoder.final_layernorm.weight, rstd,
+                                 grad_buffer(model.decoder.final_layernorm.weight))
+        return dh, None, None, None, None
+
+
+class _Decoder(nn.Module):
+    def __init__(self, cfg, layer_numbers: List[int], device, gen, comm, post_process: bool):
+        super().__init__()
+        self.layers = nn.ModuleList([TransformerLayer(cfg, n, device, gen, comm) for n in layer_numbers])
+        if post_process:
+            self.final_layernorm = _Holder(torch.ones(cfg.hidden_size, dtype=cfg.params_dtype,
+                                                      device=device))
+        else:
+            self.final_layernorm = None
+
+
+class _Embedding(nn.Module):
+    def __init__(self, cfg, device, gen):
+        super().__init__()
+        v = cfg.vocab_size // cfg.tensor_model_parallel_size
+        self.word_embeddings = _Holder(_normal((v, cfg.hidden_size), cfg.init_method_std,
+                                               cfg.params_dtype, device, gen))
+
+
+class GPTModel(nn.Module):
+    """One pipeline stage (or the whole model) of the decoder.
+
+    ``pre_process`` owns the embedding, ``post_process`` the final norm, the LM head and the
+    optional scalar value head (``rm_head`` -- critic / outcome reward model; reference:
+    ``mindspeed_rl/models/orm/orm_model.py:87-184``).
+    """
+
+    def __init__(self, cfg: TransformerConfig, comm: Optional[TPComm] = None, pre_process: bool = True,
+                 post_process: bool = True, layer_numbers: Optional[List[int]] = None, device=None,
+                 seed: int = 1234):
+        super().__init__()
+        self.cfg = cfg
+        self.comm = comm or NO_TP
+        self.pre_process, self.post_process = pre_process, post_process
+        device = torch.device(device if device is not None else "cpu")
+        gen = torch.Generator(device=device).manual_seed(seed + 7919 * self.comm.rank)
+        layer_numbers = list(range(cfg.num_layers)) if layer_numbers is None else layer_numbers
+        self.layer_numbers = layer_numbers
+        if cfg.vocab_size % cfg.tensor_model_parallel_size:
+            raise ValueError("vocab size must be divisible by the TP size")
+        self.vocab_start = self.comm.rank * (cfg.vocab_size // cfg.tensor_model_parallel_size)
+        self.embedding = _Embedding(cfg, device, gen) if pre_process else None
+        self.decoder = _Decoder(cfg, layer_numbers, device, gen, self.comm, post_process)
+        self.output_layer = None
+        self.rm_head = None
+        if post_process:
+            if cfg.untie_embeddings_and_output_weights or not pre_process:
+                v = cfg.vocab_size // cfg.tensor_model_parallel_size
+                self.output_layer = _Holder(_normal((v, cfg.hidden_size), cfg.init_method_std,
+                                                    cfg.params_dtype, device, gen))
+            if cfg.value_head:
+                self.rm_head = nn.Linear(cfg.hidden_size, 1, bias=True, device=device,
+                                         dtype=torch.float32)
+
+    # -----------------------------------------------------------------------------------------------
+    def output_weight(self) -> torch.Tensor:
+        if self.output_layer is not None:
+            return self.output_layer.weight
+        return self.embedding.word_embeddings.weight
+
+    def embed(self, ids: torch.Tensor) -> torch.Tensor:
+        return _EmbedFn.apply(self.embedding.word_embeddings.weight, ids, self.comm, self.vocab_start)
+
+    def run_layers(self, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+        for layer in self.decoder.layers:
+            h = layer(h, meta)
+        return h
+
+    def hidden_states(self, ids_or_h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+        h = self.embed(ids_or_h) if self.pre_process else ids_or_h
+        if torch.is_grad_enabled() and not h.requires_grad and \
+                any(p.requires_grad for p in self.decoder.parameters()):
+            # layer nodes only run their backward when an input requires grad
+            h = h.detach().requires_grad_(True)
+        return self.run_layers(h, meta)
+
+    def forward_logprob(self, ids_or_h: torch.Tensor, labels: torch.Tensor, meta: PackedMeta,
+                        temperature: float = 1.0, want_entropy: bool = False
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Packed ids (or the previous stage's hidden states) -> per-token ``(logp, entropy)``."""
+        h = self.hidden_states(ids_or_h, meta)
+        if not self.post_process:
+            return h, None
+        return _LogProbHeadFn.apply(h, self, labels, 1.0 / temperature, want_entropy)
+
+    def forward_values(self, ids_or_h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+        """Per-token scalar from the value head (fp32), ``[T]``."""
+        h = self.hidden_states(ids_or_h, meta)
+        if not self.post_process:
+            return h
+        x = _NormFn.apply(h, self.decoder.final_layernorm.weight, self.cfg.norm_epsilon)
+        xg = self.comm.gather_seq(x) if not torch.is_grad_enabled() else _GatherSeq.apply(x, self.comm)
+        return self.rm_head(xg.float()).squeeze(-1)
+
+    def forward_logits(self, ids: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+        """Full (local-vocab) logits ``[T, V/tp]`` -- evaluation / tests only."""
+        h = self.hidden_states(ids, meta)
+        x, _, _ = ops.rmsnorm_fwd(h, self.decoder.final_layernorm.weight, self.cfg.norm_epsilon,
+                                  want_rstd=False)
+        return torch.matmul(self.comm.gather_seq(x), self.output_weight().t())
+
+
+class _NormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, w, eps):
+        y, rstd, _ = ops.rmsnorm_fwd(h, w, eps)
+        ctx.save_for_backward(h, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, w, rstd = ctx.saved_tensors
+        dx = ops.rmsnorm_bwd(dy.contiguous(), h, w, rstd, grad_buffer(w))
+        return dx, None, None
+
+
+class _GatherSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        return comm.gather_seq(x)
+
+    @staticmethod
+    def backward(ctx, d):
+        return ctx.comm.gather_seq_bwd(d.contiguous()), None
+
+
+def count_parameters(model: nn.Module) -> int:
+    return sum(p.numel() for p in model.parameters())

@@ -1,0 +1,216 @@
+"""Training / scoring engine shared by the actor, reference, critic and reward roles.
+
+Flow (reference behaviour: ``mindspeed_rl/models/base/base_training_engine.py:125-537``):
+
+``update``:  epochs x mini-batches (``mini_batch_size_per_dp`` rows) -> micro-batches (fixed
+size, or token-budget bins when ``use_dynamic_bsz``) -> packed forward/backward with gradient
+accumulation -> DP gradient reduction -> optimizer step -> LR scheduler step.
+``forward``: the same micro-batching without gradients, results returned in input order.
+
+What differs by design: every micro-batch is a *packed* token stream (remove-padding is not an
+option but the only layout), labels/positions/gather indices are built vectorised on the host
+and shipped once, the LM head never materialises logits, and the loss is a fused
+forward+backward kernel over the response tokens.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..utils.seqlen_balancing import get_reverse_idx, rearrange_micro_batches
+from .gpt import GPTModel, PackedMeta
+from .loss.registry import BaseLossFunc, LossFuncFactory
+
+
+def _unwrap(model):
+    return model.module if hasattr(model, "module") and not isinstance(model, GPTModel) else model
+
+
+class MicroBatch:
+    """Packed view of some rows of a padded batch (host tensors until ``to``)."""
+
+    def __init__(self, data: Dict[str, torch.Tensor], rows: Sequence[int], align: int):
+        rows_t = torch.as_tensor(list(rows), dtype=torch.int64)
+        ids2d = data["input_ids"][rows_t].to(torch.int64)
+        b, s = ids2d.shape
+        p_len = data["prompt_length"][rows_t].reshape(-1).to(torch.int64)
+        r_len = data["response_length"][rows_t].reshape(-1).to(torch.int64)
+        lens = (p_len + r_len).clamp(max=s)
+        padded = (lens + align - 1) // align * align
+        cu = torch.zeros(b + 1, dtype=torch.int64)
+        cu[1:] = torch.cumsum(padded, 0)
+        total = int(cu[-1])
+        col = torch.arange(s).unsqueeze(0)
+        valid = col < lens.unsqueeze(1)
+        dest = (cu[:-1].unsqueeze(1) + col)[valid]
+        ids = torch.zeros(total, dtype=torch.int64)
+        ids[dest] = ids2d[valid]
+        shifted = torch.cat([ids2d[:, 1:], ids2d.new_zeros(b, 1)], dim=1)
+        shifted = shifted.masked_fill(col == (lens - 1).unsqueeze(1), 0)
+        labels = torch.zeros(total, dtype=torch.int64)
+        labels[dest] = shifted[valid]
+        pos = torch.arange(total) - torch.repeat_interleave(cu[:-1], padded)
+        width = data["responses"].shape[1]
+        j = torch.arange(width).unsqueeze(0)
+        self.resp_valid = j < r_len.unsqueeze(1)
+        self.resp_index = (cu[:-1] + p_len - 1).unsqueeze(1) + j
+        self.resp_index = torch.where(self.resp_valid, self.resp_index, torch.zeros_like(self.resp_index))
+        self.last_index = cu[:-1] + lens - 1
+        self.rows = rows_t
+        self.ids, self.labels, self.positions = ids, labels, pos.to(torch.int32)
+        self.cu = cu.to(torch.int32)
+        self.max_seqlen = int(padded.max()) if b else 0
+        self.num_tokens = total
+        self.data = {k: v[rows_t] for k, v in data.items() if torch.is_tensor(v) and v.shape[:1] == data["input_ids"].shape[:1]}
+
+    def to(self, device) -> "MicroBatch":
+        for k in ("ids", "labels", "positions", "cu", "resp_index", "resp_valid", "last_index"):
+            setattr(self, k, getattr(self, k).to(device, non_blocking=True))
+        return self
+
+    def meta(self) -> PackedMeta:
+        return PackedMeta(self.cu, self.max_seqlen, self.positions)
+
+
+class TrainingEngine:
+    def __init__(self, model, optimizer=None, opt_param_scheduler=None, *, stage: str = "ray_grpo",
+                 role: str = "actor", micro_batch_size: int = 1, mini_batch_size_per_dp: int = 1,
+                 epochs: int = 1, shuffle_mini_batch: bool = False, temperature: float = 1.0,
+                 use_dynamic_bsz: bool = False, max_packing_token_size: Optional[int] = None,
+                 forward_max_packing_token_size: Optional[int] = None,
+                 dynamic_max_batch_size: Optional[int] = None, pad_multiple: int = 1, dp_group=None,
+                 dp_size: int = 1, device=None, forward_micro_batch_size: Optional[int] = None,
+                 want_entropy: Optional[bool] = None, forward_backward_func: Optional[Callable] = None,
+                 **loss_options):
+        self.model = model
+        self.core: GPTModel = _unwrap(model)
+        self.optimizer, self.opt_param_scheduler = optimizer, opt_param_scheduler
+        self.stage, self.role = stage, role
+        self.micro_batch_size = micro_batch_size
+        self.forward_micro_batch_size = forward_micro_batch_size or micro_batch_size
+        self.mini_batch_size_per_dp = mini_batch_size_per_dp
+        self.epochs, self.shuffle_mini_batch = epochs, shuffle_mini_batch
+        self.temperature = temperature
+        self.use_dynamic_bsz = use_dynamic_bsz
+        self.max_packing_token_size = max_packing_token_size
+        self.forward_max_packing_token_size = forward_max_packing_token_size or max_packing_token_size
+        self.dynamic_max_batch_size = dynamic_max_batch_size
+        self.pad_multiple = pad_multiple
+        self.dp_group, self.dp_size = dp_group, dp_size
+        self.device = device or next(self.core.parameters()).device
+        self.forward_backward_func = forward_backward_func
+        stage_key = "ray_grpo" if (stage == "ray_dapo" and role != "actor") else stage
+        self.loss_func: BaseLossFunc = LossFuncFactory.get_instance(stage_key, role, **loss_options)
+        c_ent = float(loss_options.get("entropy_coeff", 0.0) or 0.0)
+        self.want_entropy = (role == "actor") if want_entropy is None else want_entropy
+        self.entropy_needs_grad = c_ent != 0.0
+
+    # ------------------------------------------------------------------------------------------
+    def _split(self, data: Dict[str, torch.Tensor], rows: List[int], update: bool) -> List[List[int]]:
+        if not self.use_dynamic_bsz:
+            mbs = self.micro_batch_size if update else self.forward_micro_batch_size
+            return [rows[i:i + mbs] for i in range(0, len(rows), mbs)]
+        lens = (data["prompt_length"].reshape(-1) + data["response_length"].reshape(-1))[rows].tolist()
+        budget = self.max_packing_token_size if update else self.forward_max_packing_token_size
+        parts = rearrange_micro_batches(lens, budget, self.dynamic_max_batch_size, self.dp_group)
+        return [[rows[i] for i in p] for p in parts if p]
+
+    def _run_model(self, mb: MicroBatch, want_entropy: bool):
+        """Returns the role's per-response-token outputs ``[b, R]`` (autograd-connected)."""
+        core = self.core
+        if self.loss_func.output_kind == "value":
+            v = core.forward_values(mb.ids, mb.meta())
+            if self.role == "reward":
+                return v[mb.last_index].unsqueeze(-1), None
+            return v[mb.resp_index] * mb.resp_valid, None
+        logp, ent = core.forward_logprob(mb.ids, mb.labels, mb.meta(), self.temperature, want_entropy)
+        lp = logp[mb.resp_index] * mb.resp_valid
+        en = ent[mb.resp_index] * mb.resp_valid if want_entropy else None
+        return lp, en
+
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, data: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """Forward-only pass; returns ``[B, R]`` fp32 on the host in the order of ``data`` rows."""
+        self.model.eval()
+        n = data["input_ids"].shape[0]
+        width = 1 if self.role == "reward" else data["responses"].shape[1]
+        out = torch.zeros(n, width, dtype=torch.float32)
+        results = []
+        for rows in self._split(data, list(range(n)), update=False):
+            mb = MicroBatch(data, rows, self.pad_multiple).to(self.device)
+            vals, _ = self._run_model(mb, want_entropy=False)
+            results.append((rows, vals.float()))
+        for rows, vals in results:
+            out[torch.as_tensor(rows)] = vals.cpu()
+        return out
+
+    # ------------------------------------------------------------------------------------------
+    def update(self, data: Dict[str, torch.Tensor], kl_ctrl=None) -> Dict[str, List[float]]:
+        """Run ``epochs`` passes of mini-batch updates over ``data``; returns metric lists."""
+        self.model.train()
+        if kl_ctrl is not None:
+            self.loss_func.add_loss_meta_info({"kl_ctrl": getattr(kl_ctrl, "value", kl_ctrl)})
+        n = data["input_ids"].shape[0]
+        metrics: Dict[str, List[Any]] = {}
+        lr_key = "critic/lr" if self.role == "critic" else "actor/lr"
+        gn_key = "critic/grad_norm" if self.role == "critic" else "actor/grad_norm"
+        for _ in range(self.epochs):
+            order = torch.randperm(n).tolist() if self.shuffle_mini_batch else list(range(n))
+            for s in range(0, n, self.mini_batch_size_per_dp):
+                mini = order[s:s + self.mini_batch_size_per_dp]
+                self._zero_grad()
+                stats = self._forward_backward(data, mini)
+                ok, grad_norm, _ = self._optimizer_step()
+                if self.opt_param_scheduler is not None and ok:
+                    self.opt_param_scheduler.step(increment=len(mini) * self.dp_size)
+                for k, v in stats.items():
+                    metrics.setdefault(k, []).append(v)
+                metrics.setdefault(gn_key, []).append(grad_norm)
+                if self.optimizer is not None:
+                    metrics.setdefault(lr_key, []).append(self.optimizer.param_groups[0]["lr"])
+        return {k: [float(x) for x in v] for k, v in metrics.items()}
+
+    def _zero_grad(self) -> None:
+        if hasattr(self.model, "zero_grad_buffer"):
+            self.model.zero_grad_buffer()
+        else:
+            for p in self.core.parameters():
+                p.grad = None
+        if self.optimizer is not None and not hasattr(self.model, "zero_grad_buffer"):
+            self.optimizer.zero_grad()
+
+    def _forward_backward(self, data, mini: List[int]) -> Dict[str, torch.Tensor]:
+        parts = self._split(data, mini, update=True)
+        n_micro = len(parts)
+        sums: Dict[str, torch.Tensor] = {}
+        for rows in parts:
+            mb = MicroBatch(data, rows, self.pad_multiple).to(self.device)
+            scale = 1.0 / n_micro
+            if self.use_dynamic_bsz:   # re-weight bins by their share of the mini-batch rows
+                scale = len(rows) / len(mini)
+            out, ent = self._run_model(mb, want_entropy=self.want_entropy)
+            batch_dev = {k: v.to(self.device, non_blocking=True) for k, v in mb.data.items()
+                         if k not in ("input_ids",)}
+            if not self.entropy_needs_grad and ent is not None:
+                ent = ent.detach()
+            grad, dent, stats = self.loss_func.compute(batch_dev, out.detach(), ent.detach() if ent is not None else None, scale)
+            outs, grads = [out], [grad]
+            if dent is not None and ent is not None and ent.requires_grad:
+                outs.append(ent)
+                grads.append(dent)
+            torch.autograd.backward(outs, grads)
+            for k, v in stats.items():
+                v = v.detach() * scale
+                sums[k] = v if k not in sums else sums[k] + v
+        return sums
+
+    def _optimizer_step(self):
+        if hasattr(self.model, "finish_grad_sync"):
+            self.model.finish_grad_sync(to_shards=True)
+        if self.optimizer is None:
+            return True, 0.0, 0
+        return self.optimizer.step()

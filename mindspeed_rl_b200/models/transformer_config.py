@@ -1,0 +1,113 @@
+"""Architecture description consumed by the training model and the rollout model runner."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+
+@dataclass
+class TransformerConfig:
+    num_layers: int
+    hidden_size: int
+    ffn_hidden_size: int
+    num_attention_heads: int
+    num_query_groups: int
+    vocab_size: int
+    kv_channels: Optional[int] = None
+    norm_epsilon: float = 1e-6
+    rotary_base: float = 1_000_000.0
+    max_position_embeddings: int = 32768
+    add_qkv_bias: bool = False
+    qk_layernorm: bool = False
+    untie_embeddings_and_output_weights: bool = True
+    init_method_std: float = 0.02
+    # MoE
+    num_experts: Optional[int] = None
+    moe_router_topk: int = 2
+    moe_ffn_hidden_size: Optional[int] = None
+    n_shared_experts: Optional[int] = None
+    norm_topk_prob: bool = False
+    moe_router_score_function: str = "softmax"
+    moe_aux_loss_coeff: float = 0.0
+    first_k_dense_replace: int = 0
+    moe_router_topk_scaling_factor: Optional[float] = None
+    moe_router_enable_expert_bias: bool = False
+    moe_router_num_groups: Optional[int] = None
+    moe_router_group_topk: Optional[int] = None
+    # rope scaling (YaRN); None = plain RoPE
+    rope_scaling: Optional[dict] = None
+    # numerics / memory
+    params_dtype: torch.dtype = torch.bfloat16
+    recompute_granularity: Optional[str] = "full"   # "full" -> keep only layer inputs
+    # parallel sizes seen by the model code
+    tensor_model_parallel_size: int = 1
+    sequence_parallel: bool = False
+    expert_model_parallel_size: int = 1
+    # value/reward head
+    value_head: bool = False
+    # LoRA
+    lora_r: int = 0
+    lora_alpha: int = 16
+    lora_target_modules: tuple = ()
+
+    def __post_init__(self):
+        if self.kv_channels is None:
+            self.kv_channels = self.hidden_size // self.num_attention_heads
+        if self.num_query_groups is None:
+            self.num_query_groups = self.num_attention_heads
+
+    @property
+    def head_dim(self) -> int:
+        return self.kv_channels
+
+    @property
+    def is_moe(self) -> bool:
+        return bool(self.num_experts)
+
+    def layer_is_moe(self, layer_idx: int) -> bool:
+        return self.is_moe and layer_idx >= (self.first_k_dense_replace or 0)
+
+    @classmethod
+    def from_megatron(cls, cfg, **overrides) -> "TransformerConfig":
+        """Build from a :class:`~mindspeed_rl_b200.config.MegatronConfig`."""
+        nqg = cfg.num_query_groups if cfg.group_query_attention else cfg.num_attention_heads
+        vocab = cfg.padded_vocab_size
+        rope_scaling = None
+        if getattr(cfg, "rope_scaling_type", None) == "yarn":
+            rope_scaling = dict(
+                factor=cfg.rope_scaling_factor,
+                original_max_position_embeddings=(cfg.rope_scaling_original_max_position_embeddings
+                                                  or cfg.original_max_position_embeddings or 4096),
+                beta_fast=cfg.beta_fast, beta_slow=cfg.beta_slow, mscale=cfg.rope_scaling_mscale,
+                mscale_all_dim=cfg.rope_scaling_mscale_all_dim)
+        kw = dict(
+            num_layers=cfg.num_layers, hidden_size=cfg.hidden_size,
+            ffn_hidden_size=cfg.ffn_hidden_size, num_attention_heads=cfg.num_attention_heads,
+            num_query_groups=nqg, vocab_size=vocab, kv_channels=cfg.kv_channels,
+            norm_epsilon=cfg.norm_epsilon, rotary_base=float(cfg.rotary_base),
+            max_position_embeddings=cfg.max_position_embeddings or 32768,
+            add_qkv_bias=bool(cfg.add_qkv_bias), qk_layernorm=bool(cfg.qk_layernorm),
+            untie_embeddings_and_output_weights=bool(cfg.untie_embeddings_and_output_weights),
+            init_method_std=cfg.init_method_std, num_experts=cfg.num_experts,
+            moe_router_topk=cfg.moe_router_topk, moe_ffn_hidden_size=cfg.moe_ffn_hidden_size,
+            n_shared_experts=cfg.n_shared_experts, norm_topk_prob=bool(cfg.norm_topk_prob),
+            moe_router_score_function=cfg.moe_router_score_function,
+            moe_aux_loss_coeff=cfg.moe_aux_loss_coeff or 0.0,
+            first_k_dense_replace=cfg.first_k_dense_replace or 0,
+            moe_router_topk_scaling_factor=cfg.moe_router_topk_scaling_factor,
+            moe_router_enable_expert_bias=bool(cfg.moe_router_enable_expert_bias),
+            moe_router_num_groups=cfg.moe_router_num_groups,
+            moe_router_group_topk=cfg.moe_router_group_topk,
+            rope_scaling=rope_scaling,
+            params_dtype=torch.bfloat16 if cfg.bf16 else torch.float32,
+            recompute_granularity=cfg.recompute_granularity,
+            tensor_model_parallel_size=cfg.tensor_model_parallel_size,
+            sequence_parallel=bool(cfg.sequence_parallel) and cfg.tensor_model_parallel_size > 1,
+            expert_model_parallel_size=cfg.expert_model_parallel_size,
+            lora_r=cfg.lora_r if cfg.lora_target_modules else 0, lora_alpha=cfg.lora_alpha,
+            lora_target_modules=tuple(cfg.lora_target_modules or ()),
+        )
+        kw.update(overrides)
+        return cls(**kw)

@@ -1,0 +1,125 @@
+"""Variable-length causal attention over packed token streams (training / prefill).
+
+``attn_varlen_fwd(qkv, layout, cu_seqlens, max_seqlen)`` reads q/k/v heads straight out of
+the fused QKV projection output (``QKVLayout``) and returns ``[T, nh*hd]`` plus the
+log-sum-exp needed by ``attn_varlen_bwd``, which writes dq/dk/dv straight into a ``dqkv``
+tensor of the same layout.  CUDA path: ``csrc/attention.cu``; CPU path: per-sequence fp32
+softmax attention (also the test oracle).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import c_int, c_ll, check, ptr, stream
+from .elementwise import _workspace
+from .layouts import QKVLayout
+
+
+def _layout_array(*specs) -> ctypes.Array:
+    vals = []
+    for _, (st, gs, hpg, hs) in specs:
+        vals += [st, gs, hpg, hs]
+    return (ctypes.c_longlong * len(vals))(*vals)
+
+
+def _ref_attention(q, k, v, cu_q, cu_k, causal):
+    """fp32 reference; q [Tq, nh, hd], k/v [Tk, nkv, hd]; returns out [Tq, nh, hd], lse [nh, Tq]."""
+    tq, nh, hd = q.shape
+    nkv = k.shape[1]
+    rep = nh // nkv
+    out = torch.zeros(tq, nh, hd, dtype=torch.float32, device=q.device)
+    lse = torch.zeros(nh, tq, dtype=torch.float32, device=q.device)
+    scale = 1.0 / math.sqrt(hd)
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    for b in range(len(cq) - 1):
+        qs, qe, ks, ke = cq[b], cq[b + 1], ck[b], ck[b + 1]
+        if qe == qs:
+            continue
+        qi = q[qs:qe].float().transpose(0, 1)                       # [nh, Lq, hd]
+        ki = k[ks:ke].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        vi = v[ks:ke].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        s = torch.matmul(qi, ki.transpose(1, 2)) * scale            # [nh, Lq, Lk]
+        if causal:
+            lq, lk = qe - qs, ke - ks
+            i = torch.arange(lq, device=q.device).unsqueeze(1)
+            j = torch.arange(lk, device=q.device).unsqueeze(0)
+            s = s.masked_fill(j > i + (lk - lq), float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l.unsqueeze(-1))
+        out[qs:qe] = torch.matmul(p, vi).transpose(0, 1)
+        lse[:, qs:qe] = l
+    return out, lse
+
+
+def attn_varlen_fwd(qkv: torch.Tensor, layout: QKVLayout, cu_seqlens: torch.Tensor, max_seqlen: int,
+                    causal: bool = True, kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                    cu_seqlens_k: Optional[torch.Tensor] = None
+                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(out [T, nh*hd], lse [nh, T] fp32)``.
+
+    ``kv=(k, v)`` with contiguous ``[Tk, nkv, hd]`` tensors and ``cu_seqlens_k`` selects the
+    prefix-attention form (queries from ``qkv``, keys/values from ``kv``; the causal mask is
+    bottom-right aligned).
+    """
+    t = qkv.shape[0]
+    nh, nkv, hd = layout.num_heads, layout.num_kv_heads, layout.head_dim
+    batch = cu_seqlens.numel() - 1
+    cu_k = cu_seqlens if cu_seqlens_k is None else cu_seqlens_k
+    if _lib.use_kernels(qkv, cu_seqlens):
+        flat = qkv.view(-1)
+        qs = layout.q()
+        if kv is None:
+            ks, vs = layout.k(), layout.v()
+            kb, vb = flat[ks[0]:], flat[vs[0]:]
+        else:
+            ks = vs = (0, (nkv * hd, 0, nkv, hd))
+            kb, vb = kv[0].contiguous().view(-1), kv[1].contiguous().view(-1)
+        lay = _layout_array(qs, ks, vs)
+        out = torch.empty(t, nh * hd, device=qkv.device, dtype=qkv.dtype)
+        lse = torch.empty(nh, t, device=qkv.device, dtype=torch.float32)
+        check(_lib.load().msrl_flash_attn_varlen_fwd(
+            ptr(flat[qs[0]:]), ptr(kb), ptr(vb), lay, ptr(out), c_ll(nh * hd), ptr(lse),
+            ptr(cu_seqlens), ptr(cu_k), c_int(batch), c_int(int(max_seqlen)), c_int(nh), c_int(nkv),
+            c_ll(t), c_int(hd), c_int(1 if causal else 0), stream()), "flash_attn_varlen_fwd")
+        return out, lse
+    q, k, v = layout.split(qkv)
+    if kv is not None:
+        k, v = kv
+    o, lse = _ref_attention(q, k, v, cu_seqlens, cu_k, causal)
+    return o.reshape(t, nh * hd).to(qkv.dtype), lse
+
+
+def attn_varlen_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
+                    layout: QKVLayout, cu_seqlens: torch.Tensor, max_seqlen: int,
+                    causal: bool = True) -> torch.Tensor:
+    """Returns ``dqkv`` with the layout of ``qkv`` (self-attention form only)."""
+    t = qkv.shape[0]
+    nh, nkv, hd = layout.num_heads, layout.num_kv_heads, layout.head_dim
+    batch = cu_seqlens.numel() - 1
+    if _lib.use_kernels(qkv, dout, out):
+        flat = qkv.view(-1)
+        dqkv = torch.empty_like(qkv)
+        dflat = dqkv.view(-1)
+        qs, ks, vs = layout.q(), layout.k(), layout.v()
+        lay = _layout_array(qs, ks, vs)
+        delta = _workspace("attn_delta", nh * t, qkv.device)
+        do = dout.contiguous()
+        check(_lib.load().msrl_flash_attn_varlen_bwd(
+            ptr(flat[qs[0]:]), ptr(flat[ks[0]:]), ptr(flat[vs[0]:]), lay, ptr(out), ptr(do),
+            c_ll(nh * hd), ptr(lse), ptr(delta), ptr(dflat[qs[0]:]), ptr(dflat[ks[0]:]),
+            ptr(dflat[vs[0]:]), ptr(cu_seqlens), ptr(cu_seqlens), c_int(batch),
+            c_int(int(max_seqlen)), c_int(int(max_seqlen)), c_int(nh), c_int(nkv), c_ll(t), c_int(hd),
+            c_int(1 if causal else 0), stream()), "flash_attn_varlen_bwd")
+        return dqkv
+    # reference: autograd through the fp32 formulation
+    with torch.enable_grad():
+        x = qkv.detach().float().requires_grad_(True)
+        q, k, v = layout.split(x)
+        o, _ = _ref_attention(q, k, v, cu_seqlens, cu_seqlens, causal)
+        (gx,) = torch.autograd.grad(o.reshape(t, nh * hd), x, dout.float())
+    return gx.to(qkv.dtype)

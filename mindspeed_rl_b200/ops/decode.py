@@ -1,0 +1,201 @@
+"""Rollout-engine ops: paged KV-cache write / gather, paged decode attention, token sampler.
+
+Cache tensors are ``[num_blocks, block_size, n_kv_heads, head_dim]``.  CUDA path:
+``csrc/decode.cu``.  The CPU path keeps the same semantics in plain PyTorch so the engine and
+its scheduler can be exercised without a GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import c_float, c_int, c_ll, c_ull, check, ptr, stream
+from .elementwise import _workspace
+from .layouts import QKVLayout
+
+
+def _lay(*specs):
+    vals = []
+    for _, (st, gs, hpg, hs) in specs:
+        vals += [st, gs, hpg, hs]
+    return (ctypes.c_longlong * len(vals))(*vals)
+
+
+def kv_cache_write(qkv: torch.Tensor, layout: QKVLayout, slots: torch.Tensor,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    """Store the k / v heads of each row of ``qkv`` at ``slots[t]`` (int64; < 0 skips the row)."""
+    t = qkv.shape[0]
+    nkv, hd = layout.num_kv_heads, layout.head_dim
+    if _lib.use_kernels(qkv, slots, k_cache):
+        flat = qkv.view(-1)
+        ks, vs = layout.k(), layout.v()
+        check(_lib.load().msrl_kv_cache_write(ptr(flat[ks[0]:]), ptr(flat[vs[0]:]), _lay(ks, vs),
+                                              ptr(slots), ptr(k_cache), ptr(v_cache), c_ll(t),
+                                              c_int(nkv), c_int(hd), stream()), "kv_cache_write")
+        return
+    _, k, v = layout.split(qkv)
+    ok = slots >= 0
+    kc = k_cache.view(-1, nkv, hd)
+    vc = v_cache.view(-1, nkv, hd)
+    kc[slots[ok]] = k[ok].to(kc.dtype)
+    vc[slots[ok]] = v[ok].to(vc.dtype)
+
+
+def kv_cache_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                    token_seq: torch.Tensor, token_pos: torch.Tensor
+                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Contiguous ``[T, nkv, hd]`` K / V for tokens given as (block-table row, position)."""
+    nb, bs, nkv, hd = k_cache.shape
+    t = token_seq.numel()
+    if _lib.use_kernels(k_cache, block_tables, token_seq):
+        k = torch.empty(t, nkv, hd, device=k_cache.device, dtype=k_cache.dtype)
+        v = torch.empty_like(k)
+        check(_lib.load().msrl_kv_cache_gather(ptr(k_cache), ptr(v_cache), ptr(block_tables),
+                                               c_int(block_tables.shape[1]), ptr(token_seq),
+                                               ptr(token_pos), ptr(k), ptr(v), c_ll(t), c_int(nkv),
+                                               c_int(hd), c_int(bs), stream()), "kv_cache_gather")
+        return k, v
+    blk = block_tables[token_seq.long(), (token_pos // bs).long()].long()
+    slot = blk * bs + (token_pos % bs).long()
+    return k_cache.view(-1, nkv, hd)[slot], v_cache.view(-1, nkv, hd)[slot]
+
+
+def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, block_tables: torch.Tensor,
+                           context_lens: torch.Tensor, max_context: int,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query token per sequence against its paged KV (which already holds that token)."""
+    b = qkv.shape[0]
+    nh, nkv, hd = layout.num_heads, layout.num_kv_heads, layout.head_dim
+    bs = k_cache.shape[1]
+    if out is None:
+        out = torch.empty(b, nh * hd, device=qkv.device, dtype=qkv.dtype)
+    if _lib.use_kernels(qkv, k_cache, block_tables, context_lens):
+        L = _lib.load()
+        nsplit = L.msrl_paged_decode_nsplit(c_int(b), c_int(nkv), c_int(int(max_context)))
+        part_o = _workspace("decode_part_o", b * nh * nsplit * hd, qkv.device)
+        part_ml = _workspace("decode_part_ml", b * nh * nsplit * 2, qkv.device)
+        qs = layout.q()
+        check(L.msrl_paged_decode(ptr(qkv.view(-1)[qs[0]:]), _lay(qs), ptr(k_cache), ptr(v_cache),
+                                  ptr(block_tables), c_int(block_tables.shape[1]), ptr(context_lens),
+                                  ptr(out), c_ll(nh * hd), ptr(part_o), ptr(part_ml), c_int(b),
+                                  c_int(nh), c_int(nkv), c_int(hd), c_int(bs), c_int(nsplit),
+                                  stream()), "paged_decode")
+        return out
+    q, _, _ = layout.split(qkv)
+    rep = nh // nkv
+    scale = 1.0 / math.sqrt(hd)
+    kc, vc = k_cache.view(-1, nkv, hd), v_cache.view(-1, nkv, hd)
+    for i in range(b):
+        n = int(context_lens[i])
+        pos = torch.arange(n, device=qkv.device)
+        slot = block_tables[i, (pos // bs).long()].long() * bs + pos % bs
+        k = kc[slot].float().repeat_interleave(rep, dim=1)      # [n, nh, hd]
+        v = vc[slot].float().repeat_interleave(rep, dim=1)
+        s = torch.einsum("hd,nhd->hn", q[i].float(), k) * scale
+        p = torch.softmax(s, dim=-1)
+        out[i] = torch.einsum("hn,nhd->hd", p, v).reshape(nh * hd).to(out.dtype)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Sampler
+# ------------------------------------------------------------------------------------------------
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], min_p: Optional[torch.Tensor], row_keys: torch.Tensor,
+           seed: int, eos_prob: Optional[torch.Tensor] = None, eos_id: int = -1,
+           vocab_offset: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Draw one token per row from ``softmax(logits / T)`` after top-k / top-p / min-p filtering.
+
+    ``temperature[b] <= 0`` means greedy.  ``row_keys`` (uint64 as int64) individualise the random
+    stream per request and step; together with ``seed`` the draw is reproducible.  ``eos_prob``
+    (>= 0) forces the probability of ``eos_id`` (benchmark length control).
+    Returns ``(tokens int64 [B], logprobs fp32 [B])`` under the temperature-scaled distribution.
+    """
+    b, v = logits.shape
+    inv_t = torch.where(temperature > 0, 1.0 / temperature.clamp(min=1e-6),
+                        torch.zeros_like(temperature)).float()
+    need_filter = any(x is not None for x in (top_k, top_p, min_p))
+    if _lib.use_kernels(logits, temperature, row_keys):
+        L = _lib.load()
+        is_bf16 = 1 if logits.dtype == torch.bfloat16 else 0
+        if not is_bf16 and logits.dtype != torch.float32:
+            logits = logits.float()
+        logits = logits if logits.stride(-1) == 1 else logits.contiguous()
+        dev = logits.device
+        thresh = None
+        if need_filter:
+            tk = top_k.to(torch.int32) if top_k is not None else torch.zeros(b, dtype=torch.int32, device=dev)
+            tp = top_p.float() if top_p is not None else torch.ones(b, device=dev)
+            mp = min_p.float() if min_p is not None else torch.zeros(b, device=dev)
+            thresh = torch.empty(b, device=dev, dtype=torch.float32)
+            check(L.msrl_sample_filter(ptr(logits), c_int(is_bf16), c_ll(logits.stride(0)), c_int(b),
+                                       c_int(v), ptr(inv_t), ptr(tk), ptr(tp), ptr(mp), ptr(thresh),
+                                       stream()), "sample_filter")
+        rec = torch.empty(b * L.msrl_sample_rec_bytes(), device=dev, dtype=torch.uint8)
+        ep = eos_prob.float() if eos_prob is not None else None
+        check(L.msrl_sample(ptr(logits), c_int(is_bf16), c_ll(logits.stride(0)), c_int(b), c_int(v),
+                            c_int(vocab_offset), ptr(inv_t), ptr(thresh), ptr(ep), c_int(eos_id),
+                            ptr(row_keys), c_ull(seed & (2 ** 64 - 1)), ptr(rec), stream()), "sample")
+        tokens = torch.empty(b, device=dev, dtype=torch.int64)
+        logprobs = torch.empty(b, device=dev, dtype=torch.float32)
+        check(L.msrl_sample_combine(ptr(rec), c_int(1), c_int(b), ptr(ep), c_int(eos_id), ptr(row_keys),
+                                    c_ull(seed & (2 ** 64 - 1)), ptr(tokens), ptr(logprobs), stream()),
+              "sample_combine")
+        return tokens, logprobs
+    return _sample_reference(logits, inv_t, top_k, top_p, min_p, row_keys, seed, eos_prob, eos_id)
+
+
+def _sample_reference(logits, inv_t, top_k, top_p, min_p, row_keys, seed, eos_prob, eos_id):
+    b, v = logits.shape
+    z = logits.float() * torch.where(inv_t > 0, inv_t, torch.ones_like(inv_t)).unsqueeze(1)
+    keep = torch.ones_like(z, dtype=torch.bool)
+    if top_k is not None:
+        for i in range(b):
+            k = int(top_k[i])
+            if 0 < k < v:
+                kth = torch.topk(z[i], k).values[-1]
+                keep[i] &= z[i] >= kth
+    if min_p is not None:
+        mx = z.max(dim=1, keepdim=True).values
+        thr = mx + torch.log(min_p.float().clamp(min=1e-30)).unsqueeze(1)
+        keep &= torch.where(min_p.unsqueeze(1) > 0, z >= thr, torch.ones_like(keep))
+    if top_p is not None:
+        for i in range(b):
+            p = float(top_p[i])
+            if 0 < p < 1:
+                zi = z[i].masked_fill(~keep[i], float("-inf"))
+                srt, idx = torch.sort(zi, descending=True)
+                pr = torch.softmax(srt, dim=0)
+                cum = torch.cumsum(pr, dim=0)
+                cut = int((cum < p).sum().item()) + 1
+                m = torch.zeros(v, dtype=torch.bool)
+                m[idx[:cut]] = True
+                keep[i] &= m
+    zf = z.masked_fill(~keep, float("-inf"))
+    if eos_prob is not None and eos_id >= 0:
+        forced = eos_prob >= 0
+        zf[forced, eos_id] = float("-inf")
+    lse = torch.logsumexp(zf, dim=1)
+    tokens = torch.empty(b, dtype=torch.int64)
+    logprobs = torch.empty(b, dtype=torch.float32)
+    for i in range(b):
+        g = torch.Generator().manual_seed((int(seed) * 1000003 + int(row_keys[i])) % (2 ** 63))
+        if inv_t[i] <= 0:
+            tok = int(zf[i].argmax())
+        else:
+            u = torch.rand(v, generator=g).clamp(min=1e-12)
+            tok = int((zf[i] - torch.log(-torch.log(u))).argmax())
+        lp = float(zf[i, tok] - lse[i])
+        if eos_prob is not None and eos_id >= 0 and float(eos_prob[i]) >= 0:
+            pe = float(eos_prob[i])
+            if float(torch.rand(1, generator=g)) < pe:
+                tok, lp = eos_id, math.log(max(pe, 1e-30))
+            else:
+                lp += math.log(max(1 - pe, 1e-30))
+        tokens[i], logprobs[i] = tok, lp
+    return tokens.to(logits.device), logprobs.to(logits.device)

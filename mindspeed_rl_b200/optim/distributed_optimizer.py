@@ -1,0 +1,244 @@
+"""AdamW over the flat parameter buffers, sharded across the data-parallel group (ZeRO-1), with
+optional optimizer state in pinned host memory ("swap optimizer").
+
+``step()`` = reduce-scatter-ed gradients -> global L2 norm (one tiny all-reduce) -> clip
+coefficient computed on the device -> fused AdamW on this rank's shard (fp32 master + moments,
+bf16 working copy written in the same pass) -> parameter all-gather.  It returns
+``(update_successful, grad_norm, num_zeros_in_grad)`` like the Megatron optimizers the reference
+drives (``mindspeed_rl/models/base/base_training_engine.py:523-531``).
+
+Host mode keeps ``master / exp_avg / exp_avg_sq`` in pinned memory and streams them through two
+device staging buffers in ``swap_optimizer_times`` chunks, overlapping H2D, the Adam kernel and
+D2H on separate streams (reference feature: ``docs/zh/features/swap_optimizer.md:17-33``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..parallel.ddp import ParamAndGradBuffer
+
+
+class OptimizerParamScheduler:
+    """Learning-rate schedule: linear warm-up then constant / linear / cosine decay."""
+
+    def __init__(self, optimizer, max_lr: float, min_lr: float = 0.0, lr_warmup_steps: int = 0,
+                 lr_decay_steps: int = 1, lr_decay_style: str = "constant"):
+        self.optimizer = optimizer
+        self.max_lr, self.min_lr = float(max_lr), float(min_lr)
+        self.lr_warmup_steps, self.lr_decay_steps = lr_warmup_steps, max(lr_decay_steps, 1)
+        self.lr_decay_style = lr_decay_style
+        self.num_steps = 0
+        self.step(0)
+
+    def get_lr(self) -> float:
+        n = self.num_steps
+        if self.lr_warmup_steps > 0 and n <= self.lr_warmup_steps:
+            return self.max_lr * n / self.lr_warmup_steps
+        if self.lr_decay_style == "constant":
+            return self.max_lr
+        if n > self.lr_decay_steps:
+            return self.min_lr
+        ratio = (n - self.lr_warmup_steps) / max(self.lr_decay_steps - self.lr_warmup_steps, 1)
+        delta = self.max_lr - self.min_lr
+        if self.lr_decay_style == "linear":
+            coeff = 1.0 - ratio
+        elif self.lr_decay_style == "cosine":
+            coeff = 0.5 * (math.cos(math.pi * ratio) + 1.0)
+        else:
+            raise ValueError(f"unknown lr_decay_style {self.lr_decay_style}")
+        return self.min_lr + coeff * delta
+
+    def step(self, increment: int = 1) -> None:
+        self.num_steps += increment
+        lr = self.get_lr()
+        for g in self.optimizer.param_groups:
+            g["lr"] = lr
+
+    def state_dict(self):
+        return dict(max_lr=self.max_lr, min_lr=self.min_lr, lr_warmup_steps=self.lr_warmup_steps,
+                    lr_decay_steps=self.lr_decay_steps, lr_decay_style=self.lr_decay_style,
+                    num_steps=self.num_steps)
+
+    def load_state_dict(self, sd):
+        self.num_steps = 0
+        self.step(sd.get("num_steps", 0))
+
+
+class DistributedOptimizer:
+    def __init__(self, buffers: List[ParamAndGradBuffer], lr: float = 1e-6, betas=(0.9, 0.999),
+                 eps: float = 1e-8, weight_decay: float = 0.01, clip_grad: float = 1.0,
+                 dp_group=None, dp_rank: int = 0, model_parallel_group=None,
+                 offload_to_host: bool = False, swap_chunks: int = 16,
+                 norm_duplicate_filter=None):
+        self.buffers = buffers
+        self.param_groups = [dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)]
+        self.clip_grad = clip_grad
+        self.dp_group, self.dp_rank = dp_group, dp_rank
+        self.mp_group = model_parallel_group
+        self.offload_to_host = offload_to_host
+        self.swap_chunks = max(1, swap_chunks)
+        self.step_count = 0
+        self.state: List[Dict[str, torch.Tensor]] = []
+        self.norm_duplicate_filter = norm_duplicate_filter
+        for buf in buffers:
+            s, e = buf.shard_range(dp_rank)
+            shard = buf.param_data[s:e]
+            if offload_to_host:
+                pin = shard.is_cuda
+                master = torch.empty(e - s, dtype=torch.float32, pin_memory=pin)
+                master.copy_(shard.float())
+                st = dict(master=master,
+                          exp_avg=torch.zeros(e - s, dtype=torch.float32, pin_memory=pin),
+                          exp_avg_sq=torch.zeros(e - s, dtype=torch.float32, pin_memory=pin))
+            else:
+                st = dict(master=shard.float().clone(), exp_avg=torch.zeros(e - s, dtype=torch.float32,
+                                                                            device=shard.device),
+                          exp_avg_sq=torch.zeros(e - s, dtype=torch.float32, device=shard.device))
+            self.state.append(st)
+        dev = buffers[0].device
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._streams = None
+
+    # ------------------------------------------------------------------------------------------
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for b in self.buffers:
+            b.zero_grad()
+
+    def _grad_shard(self, buf: ParamAndGradBuffer) -> torch.Tensor:
+        s, e = buf.shard_range(self.dp_rank)
+        return buf.grad_data[s:e]
+
+    def compute_grad_norm(self) -> torch.Tensor:
+        """Global L2 norm of the (already reduced) gradients; stays on the device."""
+        self._sumsq.zero_()
+        for buf in self.buffers:
+            ops.sumsq_accumulate(self._grad_shard(buf), self._sumsq)
+        if dist.is_available() and dist.is_initialized():
+            if self.dp_group is not None and buffers_dp(self.buffers) > 1:
+                dist.all_reduce(self._sumsq, group=self.dp_group)
+            if self.mp_group is not None and dist.get_world_size(self.mp_group) > 1:
+                dist.all_reduce(self._sumsq, group=self.mp_group)
+        return self._sumsq
+
+    @torch.no_grad()
+    def step(self) -> Tuple[bool, torch.Tensor, int]:
+        self.step_count += 1
+        g = self.param_groups[0]
+        self.compute_grad_norm()
+        ops.clip_coefficient(self._sumsq, float(self.clip_grad or 0.0), 1.0, self._coef, self._norm)
+        for buf, st in zip(self.buffers, self.state):
+            s, e = buf.shard_range(self.dp_rank)
+            grad = buf.grad_data[s:e]
+            p16 = buf.param_data[s:e] if buf.param_dtype != torch.float32 else None
+            if self.offload_to_host and grad.is_cuda:
+                self._step_host(st, grad, p16 if p16 is not None else buf.param_data[s:e], g,
+                                p16 is None)
+            else:
+                ops.adamw_step(st["master"], st["exp_avg"], st["exp_avg_sq"], grad, p16, g["lr"],
+                               g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"],
+                               self.step_count, self._coef)
+                if p16 is None:
+                    buf.param_data[s:e].copy_(st["master"])
+            buf.gather_params(self.dp_group)
+        return True, self._norm.clone(), 0
+
+    def _step_host(self, st, grad, p_out, g, fp32_params: bool) -> None:
+        """Chunked H2D -> AdamW -> D2H with double buffering."""
+        n = grad.numel()
+        chunk = (n + self.swap_chunks - 1) // self.swap_chunks
+        chunk = (chunk + 63) // 64 * 64
+        dev = grad.device
+        if self._streams is None:
+            self._streams = (torch.cuda.Stream(), torch.cuda.Stream())
+            self._stage = [
+                {k: torch.empty(chunk, dtype=torch.float32, device=dev) for k in ("master", "exp_avg", "exp_avg_sq")}
+                for _ in range(2)]
+            self._stage_events = [torch.cuda.Event(), torch.cuda.Event()]
+        if self._stage[0]["master"].numel() < chunk:
+            self._stage = [
+                {k: torch.empty(chunk, dtype=torch.float32, device=dev) for k in ("master", "exp_avg", "exp_avg_sq")}
+                for _ in range(2)]
+        h2d, d2h = self._streams
+        main = torch.cuda.current_stream()
+        h2d.wait_stream(main)
+        d2h.wait_stream(main)
+        done_events = [None, None]
+        for i, s in enumerate(range(0, n, chunk)):
+            e = min(n, s + chunk)
+            k = i & 1
+            stage = self._stage[k]
+            if done_events[k] is not None:
+                h2d.wait_event(done_events[k])     # staging buffer free again
+            with torch.cuda.stream(h2d):
+                for key in ("master", "exp_avg", "exp_avg_sq"):
+                    stage[key][:e - s].copy_(st[key][s:e], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(h2d)
+            main.wait_event(ready)
+            ops.adamw_step(stage["master"][:e - s], stage["exp_avg"][:e - s], stage["exp_avg_sq"][:e - s],
+                           grad[s:e], None if fp32_params else p_out[s:e], g["lr"], g["betas"][0],
+                           g["betas"][1], g["eps"], g["weight_decay"], self.step_count, self._coef)
+            if fp32_params:
+                p_out[s:e].copy_(stage["master"][:e - s])
+            computed = torch.cuda.Event()
+            computed.record(main)
+            d2h.wait_event(computed)
+            with torch.cuda.stream(d2h):
+                for key in ("master", "exp_avg", "exp_avg_sq"):
+                    st[key][s:e].copy_(stage[key][:e - s], non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(d2h)
+            done_events[k] = done
+        main.wait_stream(d2h)
+
+    # ---- master <-> working copy ------------------------------------------------------------------
+    def reload_model_params(self) -> None:
+        """Refresh the fp32 master weights from the (externally modified) model parameters."""
+        for buf, st in zip(self.buffers, self.state):
+            s, e = buf.shard_range(self.dp_rank)
+            st["master"].copy_(buf.param_data[s:e].float())
+
+    # ---- checkpoint ---------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        return dict(step=self.step_count, param_groups=self.param_groups,
+                    shards=[{k: v.detach().cpu() for k, v in st.items()} for st in self.state])
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = sd.get("step", 0)
+        for st, src in zip(self.state, sd["shards"]):
+            for k in st:
+                st[k].copy_(src[k])
+
+    # ---- memory choreography (offload between phases) --------------------------------------------
+    def offload_state(self) -> None:
+        """Move device-resident optimizer state to pinned host memory (rollout phase)."""
+        if self.offload_to_host:
+            return
+        for st in self.state:
+            for k, v in list(st.items()):
+                if v.is_cuda:
+                    host = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
+                    host.copy_(v, non_blocking=True)
+                    st[k] = host
+        torch.cuda.synchronize()
+        self._state_offloaded = True
+
+    def onload_state(self) -> None:
+        if not getattr(self, "_state_offloaded", False):
+            return
+        dev = self.buffers[0].device
+        for st in self.state:
+            for k, v in list(st.items()):
+                st[k] = v.to(dev, non_blocking=True)
+        self._state_offloaded = False
+
+
+def buffers_dp(buffers: List[ParamAndGradBuffer]) -> int:
+    return buffers[0].dp_size if buffers else 1

@@ -1,0 +1,151 @@
+"""Contiguous parameter / gradient buffers and data-parallel gradient reduction.
+
+Every trainable parameter of a model chunk becomes a view into one flat ``param_data`` buffer
+and gets a ``main_grad`` view into a matching ``grad_data`` buffer (bf16, or fp32 with
+``accumulate_allreduce_grads_in_fp32``).  The layer backward accumulates straight into
+``main_grad``.  The flat layout is what makes whole-model operations single kernels or single
+collectives: gradient reduce-scatter / all-reduce over DP, the Adam update, the parameter
+all-gather of the distributed optimizer, offload to pinned host memory and the train->rollout
+resharding plan.
+
+Role in the reference: Megatron's ``DistributedDataParallel`` with ``use_distributed_optimizer``
+(``mindspeed_rl/workers/resharding/megatron_off_loader.py:138-224`` walks the same buffers).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+def _align(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+@dataclass
+class ParamSlot:
+    name: str
+    start: int
+    numel: int
+    shape: torch.Size
+
+
+class ParamAndGradBuffer:
+    """Flat storage of the trainable parameters of one model chunk."""
+
+    ALIGN = 64  # elements; keeps every parameter 128-byte aligned in bf16
+
+    def __init__(self, named_params: Iterable[Tuple[str, nn.Parameter]], dp_size: int = 1,
+                 grad_dtype: Optional[torch.dtype] = None, bucket_numel: Optional[int] = None):
+        params = [(n, p) for n, p in named_params if p.requires_grad]
+        if not params:
+            raise ValueError("no trainable parameters")
+        self.param_dtype = params[0][1].dtype
+        self.device = params[0][1].device
+        if any(p.dtype != self.param_dtype for _, p in params):
+            raise ValueError("all buffered parameters must share one dtype")
+        self.grad_dtype = grad_dtype or self.param_dtype
+        self.dp_size = dp_size
+        self.slots: List[ParamSlot] = []
+        off = 0
+        for n, p in params:
+            self.slots.append(ParamSlot(n, off, p.numel(), p.shape))
+            off = _align(off + p.numel(), self.ALIGN)
+        self.numel = _align(off, self.ALIGN * max(dp_size, 1))
+        self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=self.device)
+        self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
+        self.params: List[nn.Parameter] = []
+        for (n, p), slot in zip(params, self.slots):
+            view = self.param_data[slot.start:slot.start + slot.numel].view(slot.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.main_grad = self.grad_data[slot.start:slot.start + slot.numel].view(slot.shape)
+            p.grad = None
+            self.params.append(p)
+        self.by_name: Dict[str, ParamSlot] = {s.name: s for s in self.slots}
+        # bucket boundaries (multiples of ALIGN*dp) used by the overlapped reduce / gather
+        self.buckets: List[Tuple[int, int]] = []
+        step = _align(bucket_numel or self.numel, self.ALIGN * max(dp_size, 1))
+        for s in range(0, self.numel, step):
+            self.buckets.append((s, min(self.numel, s + step)))
+
+    # ------------------------------------------------------------------------------------------
+    def zero_grad(self) -> None:
+        self.grad_data.zero_()
+
+    def shard_range(self, dp_rank: int) -> Tuple[int, int]:
+        per = self.numel // self.dp_size
+        return dp_rank * per, (dp_rank + 1) * per
+
+    def rebind(self) -> None:
+        """Re-point parameters at the buffers (after the storage was released and re-created)."""
+        for p, slot in zip(self.params, self.slots):
+            p.data = self.param_data[slot.start:slot.start + slot.numel].view(slot.shape)
+            p.main_grad = self.grad_data[slot.start:slot.start + slot.numel].view(slot.shape) \
+                if self.grad_data is not None and self.grad_data.numel() else None
+
+    # ---- gradient reduction over the data-parallel group --------------------------------------------
+    def reduce_grads(self, group=None, average: bool = True, to_shards: bool = False) -> None:
+        """Sum (or average) gradients over DP.  ``to_shards=True`` leaves each rank with the
+        reduced values of its own shard only (reduce-scatter, distributed optimizer)."""
+        if self.dp_size == 1 or group is None:
+            return
+        if average:
+            self.grad_data.div_(self.dp_size)
+        if to_shards:
+            per = self.numel // self.dp_size
+            r = dist.get_rank(group)
+            out = self.grad_data[r * per:(r + 1) * per]
+            dist.reduce_scatter_tensor(out, self.grad_data, group=group)
+        else:
+            dist.all_reduce(self.grad_data, group=group)
+
+    def gather_params(self, group=None) -> None:
+        """All-gather the parameter shards updated by the distributed optimizer."""
+        if self.dp_size == 1 or group is None:
+            return
+        per = self.numel // self.dp_size
+        r = dist.get_rank(group)
+        dist.all_gather_into_tensor(self.param_data, self.param_data[r * per:(r + 1) * per].clone(),
+                                    group=group)
+
+
+class DistributedDataParallel(nn.Module):
+    """Wraps a model chunk, owns its :class:`ParamAndGradBuffer` and the DP group."""
+
+    def __init__(self, module: nn.Module, dp_group=None, dp_size: int = 1,
+                 grad_in_fp32: bool = False, bucket_numel: Optional[int] = None):
+        super().__init__()
+        self.module = module
+        self.dp_group, self.dp_size = dp_group, dp_size
+        fp32_params = [(n, p) for n, p in module.named_parameters()
+                       if p.requires_grad and p.dtype == torch.float32 and
+                       next(module.parameters()).dtype != torch.float32]
+        main = [(n, p) for n, p in module.named_parameters()
+                if p.requires_grad and not any(p is q for _, q in fp32_params)]
+        self.buffers: List[ParamAndGradBuffer] = []
+        if main:
+            self.buffers.append(ParamAndGradBuffer(main, dp_size, torch.float32 if grad_in_fp32 else None,
+                                                   bucket_numel))
+        if fp32_params:  # e.g. the fp32 value head
+            self.buffers.append(ParamAndGradBuffer(fp32_params, dp_size, torch.float32, bucket_numel))
+
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    def __getattr__(self, name):
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(self.module, name)
+
+    def zero_grad_buffer(self) -> None:
+        for b in self.buffers:
+            b.zero_grad()
+
+    def finish_grad_sync(self, to_shards: bool = False) -> None:
+        for b in self.buffers:
+            b.reduce_grads(self.dp_group, average=True, to_shards=to_shards)

@@ -1,0 +1,71 @@
+"""Tensor-parallel communication around the column / row linears of a transformer layer.
+
+``TPComm`` hides which collective pattern a layer uses:
+
+* plain TP: activations are replicated; row-parallel outputs are all-reduced;
+* TP + sequence parallel: activations between layers are sharded over tokens; the
+  column-parallel input is all-gathered and the row-parallel output reduce-scattered.
+
+The NCCL implementation here is the baseline ("reference-equivalent") path; the fused
+all-gather->GEMM and GEMM->reduce-scatter kernels plug in through ``fused_ag_gemm`` /
+``fused_gemm_rs`` hooks when a symmetric-memory team is attached.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class TPComm:
+    def __init__(self, group=None, sequence_parallel: bool = False, world_size: Optional[int] = None,
+                 rank: Optional[int] = None):
+        self.group = group
+        inited = dist.is_available() and dist.is_initialized()
+        if world_size is None:
+            world_size = dist.get_world_size(group) if (inited and group is not None) else 1
+        if rank is None:
+            rank = dist.get_rank(group) if (inited and group is not None) else 0
+        self.world_size = world_size
+        self.rank = rank
+        self.sequence_parallel = sequence_parallel and world_size > 1
+        self.fused = None  # optional object with ag_gemm / gemm_rs (parallel.fused_tp)
+
+    # forward direction ---------------------------------------------------------------------------
+    def gather_seq(self, x: torch.Tensor) -> torch.Tensor:
+        """Before a column-parallel linear: all-gather tokens when sequence parallel."""
+        if not self.sequence_parallel:
+            return x
+        out = torch.empty(x.shape[0] * self.world_size, *x.shape[1:], device=x.device, dtype=x.dtype)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out
+
+    def reduce_out(self, y: torch.Tensor) -> torch.Tensor:
+        """After a row-parallel linear: reduce-scatter (SP) or all-reduce partial sums."""
+        if self.world_size == 1:
+            return y
+        if self.sequence_parallel:
+            out = torch.empty(y.shape[0] // self.world_size, *y.shape[1:], device=y.device,
+                              dtype=y.dtype)
+            dist.reduce_scatter_tensor(out, y.contiguous(), group=self.group)
+            return out
+        dist.all_reduce(y, group=self.group)
+        return y
+
+    # backward direction (transposes of the above) -----------------------------------------------------
+    def gather_seq_bwd(self, dx_full: torch.Tensor) -> torch.Tensor:
+        """Gradient of :meth:`gather_seq`: reduce-scatter (SP) / all-reduce (input was replicated)."""
+        return self.reduce_out(dx_full)
+
+    def reduce_out_bwd(self, dy: torch.Tensor) -> torch.Tensor:
+        """Gradient of :meth:`reduce_out`: all-gather (SP) / identity."""
+        return self.gather_seq(dy)
+
+    def all_reduce(self, t: torch.Tensor, op=None) -> torch.Tensor:
+        if self.world_size > 1:
+            dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=self.group)
+        return t
+
+
+NO_TP = TPComm()

@@ -1,0 +1,41 @@
+"""Zero-copy binding of training parameters as rollout weights.
+
+When the rollout layout equals the training layout (same TP, PP = 1, no EP change) nothing has
+to move: the rollout model runner can read the Megatron-layout tensors directly, because its
+kernels address q/k/v heads through ``QKVLayout`` (interleaved or not) and ``linear_fc1`` is
+already ``[gate; up]``.  This is the degenerate -- and fastest -- case of resharding; the
+general case (TP shrink/grow, PP gather, EP re-homing) is handled by ``reshard.planner`` +
+the reshard kernel.
+"""
+from __future__ import annotations
+
+from ..models.gpt import GPTModel, MLP
+from ..rollout.model_runner import LayerWeights, RolloutWeights
+
+
+def alias_rollout_weights(model: GPTModel) -> RolloutWeights:
+    layers = []
+    for layer in model.decoder.layers:
+        sa = layer.self_attention
+        kw = dict(
+            input_norm=layer.input_layernorm.weight.data,
+            qkv_w=sa.linear_qkv.weight.data,
+            qkv_b=sa.linear_qkv.bias.data if sa.linear_qkv.bias is not None else None,
+            o_w=sa.linear_proj.weight.data,
+            post_norm=layer.pre_mlp_layernorm.weight.data,
+            q_norm=sa.q_layernorm.weight.data if sa.q_layernorm is not None else None,
+            k_norm=sa.k_layernorm.weight.data if sa.k_layernorm is not None else None,
+        )
+        if isinstance(layer.mlp, MLP):
+            kw.update(gate_up_w=layer.mlp.linear_fc1.weight.data, down_w=layer.mlp.linear_fc2.weight.data)
+        else:
+            kw.update(moe=layer.mlp.rollout_view())
+        layers.append(LayerWeights(**kw))
+    return RolloutWeights(
+        embed=model.embedding.word_embeddings.weight.data,
+        layers=layers,
+        final_norm=model.decoder.final_layernorm.weight.data,
+        lm_head=model.output_weight().data,
+        qkv_layout=model.decoder.layers[0].self_attention.layout,
+        vocab_start=model.vocab_start,
+    )

@@ -1,0 +1,181 @@
+"""Memory / weight choreography between the three phases of a co-located actor.
+
+Modes (reference state machine: ``mindspeed_rl/workers/resharding/megatron_sharding_manager.py:113-218``):
+
+* **infer**   -- rollout weights are produced from the training weights (zero-copy alias when
+  the layouts coincide, otherwise the reshard plan executed by the reshard kernel), optional
+  offload of optimizer state / gradient buffers / training weights to pinned host memory,
+  weights bound into the rollout engine, KV cache allocated;
+* **forward** -- training weights resident (log-prob passes);
+* **train**   -- weights + gradient buffers + optimizer state resident.
+
+Every transition reports its wall time so the trainer can log ``timing/resharding_to_infer``
+(enter + exit infer) and ``timing/resharding_to_train``.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, List, Optional
+
+import torch
+
+from ..parallel.ddp import DistributedDataParallel
+from .alias import alias_rollout_weights
+
+
+class GradBufferOffloader:
+    """Release / re-create the flat gradient buffers (they hold no state between steps)."""
+
+    def __init__(self, ddp: Optional[DistributedDataParallel]):
+        self.ddp = ddp
+        self.released = False
+
+    def release(self) -> None:
+        if self.ddp is None or self.released:
+            return
+        for b in self.ddp.buffers:
+            b.grad_data = torch.empty(0, dtype=b.grad_dtype, device=b.device)
+            for p in b.params:
+                p.main_grad = None
+        self.released = True
+
+    def restore(self) -> None:
+        if self.ddp is None or not self.released:
+            return
+        for b in self.ddp.buffers:
+            b.grad_data = torch.zeros(b.numel, dtype=b.grad_dtype, device=b.device)
+            b.rebind()
+        self.released = False
+
+
+class ParamOffloader:
+    """Swap a flat parameter buffer between the device and a pinned host twin."""
+
+    def __init__(self, ddp: Optional[DistributedDataParallel]):
+        self.ddp = ddp
+        self.host: List[Optional[torch.Tensor]] = []
+        self.offloaded = False
+
+    def offload(self) -> None:
+        if self.ddp is None or self.offloaded:
+            return
+        if not self.host:
+            self.host = [torch.empty(b.numel, dtype=b.param_dtype, pin_memory=b.device.type == "cuda")
+                         for b in self.ddp.buffers]
+        for b, h in zip(self.ddp.buffers, self.host):
+            h.copy_(b.param_data, non_blocking=True)
+        if self.ddp.buffers[0].device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        for b in self.ddp.buffers:
+            b.param_data = torch.empty(0, dtype=b.param_dtype, device=b.device)
+            for p in b.params:
+                p.data = b.param_data
+        self.offloaded = True
+
+    def onload(self) -> None:
+        if self.ddp is None or not self.offloaded:
+            return
+        for b, h in zip(self.ddp.buffers, self.host):
+            b.param_data = torch.empty(b.numel, dtype=b.param_dtype, device=b.device)
+            b.param_data.copy_(h, non_blocking=True)
+            grads = b.grad_data
+            b.rebind()
+            b.grad_data = grads
+        self.offloaded = False
+
+
+class ShardingManager:
+    def __init__(self, train_model, rollout_engine, optimizer=None, *,
+                 offload_train_optimizer: bool = False, offload_train_grad: bool = False,
+                 offload_train_param: bool = False, num_kv_blocks: Optional[int] = None,
+                 gpu_memory_utilization: float = 0.5, resharder=None,
+                 build_weights: Optional[Callable] = None):
+        self.train_model = train_model
+        self.core = train_model.module if hasattr(train_model, "module") else train_model
+        self.engine = rollout_engine
+        self.optimizer = optimizer
+        self.offload_train_optimizer = offload_train_optimizer
+        self.offload_train_grad = offload_train_grad
+        self.offload_train_param = offload_train_param
+        self.num_kv_blocks = num_kv_blocks
+        self.gpu_memory_utilization = gpu_memory_utilization
+        self.resharder = resharder           # reshard.planner.Resharder when layouts differ
+        self.build_weights = build_weights
+        ddp = train_model if isinstance(train_model, DistributedDataParallel) else None
+        self.grad_offloader = GradBufferOffloader(ddp)
+        self.param_offloader = ParamOffloader(ddp)
+        self.mode = "train"
+        self.last_timing = {}
+
+    # ------------------------------------------------------------------------------------------
+    def _kv_blocks(self) -> int:
+        if self.num_kv_blocks:
+            return self.num_kv_blocks
+        dev = self.engine.device
+        if dev.type != "cuda":
+            return 256
+        free, total = torch.cuda.mem_get_info(dev)
+        budget = min(free - (2 << 30), int(total * self.gpu_memory_utilization))
+        return max(int(budget // self.engine.kv_bytes_per_block()), 16)
+
+    def enter_infer_mode(self) -> float:
+        t0 = time.time()
+        if self.offload_train_grad:
+            self.grad_offloader.release()
+        if self.offload_train_optimizer and self.optimizer is not None:
+            self.optimizer.offload_state()
+        if self.resharder is not None:
+            weights = self.resharder.reshard(self.core)
+            if self.offload_train_param:
+                self.param_offloader.offload()
+        elif self.build_weights is not None:
+            weights = self.build_weights(self.core)
+        else:
+            weights = alias_rollout_weights(self.core)
+        self.engine.runner.bind_weights(weights)
+        self.engine.init_cache(self._kv_blocks())
+        self._sync()
+        self.mode = "infer"
+        dt = time.time() - t0
+        self.last_timing["enter_infer"] = dt
+        return dt
+
+    def exit_infer_mode(self) -> float:
+        t0 = time.time()
+        self.engine.free_cache()
+        if self.resharder is not None:
+            self.engine.runner.bind_weights(None)
+            self.resharder.release()
+        self._sync()
+        if self.engine.device.type == "cuda":
+            torch.cuda.empty_cache()
+        self.mode = "idle"
+        dt = time.time() - t0
+        self.last_timing["exit_infer"] = dt
+        return dt
+
+    def enter_forward_mode(self) -> None:
+        self.param_offloader.onload()
+        self.mode = "forward"
+
+    def exit_forward_mode(self) -> None:
+        self.mode = "idle"
+
+    def enter_train_mode(self) -> float:
+        t0 = time.time()
+        self.param_offloader.onload()
+        self.grad_offloader.restore()
+        if self.optimizer is not None:
+            self.optimizer.onload_state()
+        self._sync()
+        self.mode = "train"
+        dt = time.time() - t0
+        self.last_timing["enter_train"] = dt
+        return dt
+
+    def exit_train_mode(self) -> None:
+        self.mode = "idle"
+
+    def _sync(self) -> None:
+        if self.engine.device.type == "cuda":
+            torch.cuda.synchronize(self.engine.device)

@@ -1,0 +1,278 @@
+"""The rollout engine: request API, step loop and the training-framework facing wrapper.
+
+``LLMEngine`` offers the request-level API the workers use for synchronous generation,
+asynchronous streaming, partial rollout (abort + resume) and the multi-turn tool loop:
+``add_request / step / abort_request / has_unfinished_requests`` (reference contract:
+``mindspeed_rl/models/rollout/vllm_engine.py:506-555``,
+``workers/actor_hybrid_worker.py:685-733``).
+
+``RolloutEngine`` implements the inference-engine interface of the framework
+(``init_cache_engine / free_cache_engine / sync_model_weights / offload_model_weights /
+generate_sequences / async_generate_sequences``; reference:
+``mindspeed_rl/models/base/base_inference_engine.py:6-125``).
+"""
+from __future__ import annotations
+
+import uuid
+import zlib
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterator, List, Optional, Sequence as Seq_, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.transformer_config import TransformerConfig
+from ..parallel.tp_comm import NO_TP, TPComm
+from .block_manager import BlockManager
+from .model_runner import KVCache, ModelRunner, RolloutWeights
+from .scheduler import (PrefillItem, RequestGroup, SamplingParams, Scheduler, SchedulerOutput, SeqStatus,
+                        Sequence)
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    token_ids: List[int]
+    logprobs: List[float]
+    finish_reason: str
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: List[int]
+    outputs: List[CompletionOutput]
+    finished: bool = True
+
+
+def length_hazard(step: int, lo: int, hi: int) -> float:
+    """P(stop at response length ``step``) so that lengths are uniform on ``[lo, hi]``."""
+    if step < lo:
+        return 0.0
+    if step >= hi:
+        return 1.0
+    return 1.0 / (hi - step + 1)
+
+
+class LLMEngine:
+    def __init__(self, cfg: TransformerConfig, device, *, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 16,
+                 enable_prefix_caching: bool = False, enforce_eager: bool = True,
+                 graph_batch_sizes: Seq_[int] = (), eos_token_id: int = -1, pad_token_id: int = 0,
+                 comm: Optional[TPComm] = None, seed: int = 0):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.comm = comm or NO_TP
+        self.max_num_seqs, self.max_num_batched_tokens = max_num_seqs, max_num_batched_tokens
+        self.max_model_len, self.block_size = max_model_len, block_size
+        self.enable_prefix_caching = enable_prefix_caching
+        self.eos_token_id, self.pad_token_id = eos_token_id, pad_token_id
+        self.seed = seed
+        self.runner = ModelRunner(cfg, device, self.comm, max_model_len, enforce_eager,
+                                  tuple(b for b in graph_batch_sizes if b <= max_num_seqs))
+        self.bm: Optional[BlockManager] = None
+        self.scheduler: Optional[Scheduler] = None
+        self._step_counter = 0
+        self.stats = dict(prefill_tokens=0, decode_tokens=0, steps=0, preemptions=0)
+
+    # ---- cache lifecycle -----------------------------------------------------------------------
+    def kv_bytes_per_block(self) -> int:
+        c = self.cfg
+        nkv = c.num_query_groups // self.comm.world_size
+        return KVCache.bytes_per_block(c.num_layers, self.block_size, nkv, c.head_dim, c.params_dtype)
+
+    def init_cache(self, num_blocks: int) -> None:
+        c = self.cfg
+        nkv = c.num_query_groups // self.comm.world_size
+        cache = KVCache(c.num_layers, num_blocks, self.block_size, nkv, c.head_dim, c.params_dtype,
+                        self.device)
+        self.runner.bind_cache(cache)
+        self.bm = BlockManager(num_blocks, self.block_size, self.enable_prefix_caching)
+        self.scheduler = Scheduler(self.bm, self.max_num_seqs, self.max_num_batched_tokens,
+                                   self.max_model_len)
+
+    def free_cache(self) -> None:
+        self.runner.bind_cache(None)
+        self.bm = None
+        self.scheduler = None
+
+    # ---- request API ---------------------------------------------------------------------------
+    def add_request(self, request_id: Optional[str], prompt_token_ids: Seq_[int],
+                    params: SamplingParams) -> str:
+        rid = request_id or uuid.uuid4().hex[:12]
+        if rid in self.scheduler.groups:
+            raise ValueError(f"request id {rid} is already in flight")
+        lead = Sequence(rid, list(int(t) for t in prompt_token_ids), params, sample_index=0)
+        self.scheduler.add_group(RequestGroup(rid, params, [lead]))
+        return rid
+
+    def abort_request(self, request_id: str) -> Optional[RequestOutput]:
+        group = self.scheduler.groups.get(request_id)
+        if group is None:
+            return None
+        self.scheduler.abort(request_id)
+        self.scheduler.groups.pop(request_id, None)
+        return self._to_output(group)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler is not None and self.scheduler.has_unfinished()
+
+    def get_num_unfinished_requests(self) -> int:
+        return len(self.scheduler.groups)
+
+    # ---- one engine step -----------------------------------------------------------------------
+    def step(self) -> List[RequestOutput]:
+        sched = self.scheduler.schedule()
+        self.stats["steps"] += 1
+        self.stats["preemptions"] += len(sched.preempted)
+        if sched.prefill:
+            self._run_prefill(sched.prefill)
+        elif sched.decode:
+            self._run_decode(sched.decode)
+        self._step_counter += 1
+        return [self._to_output(g) for g in self.scheduler.pop_finished_groups()]
+
+    # ---- internals -----------------------------------------------------------------------------
+    def _sampling_tensors(self, seqs: List[Sequence]):
+        dev = self.device
+        temp = torch.tensor([s.params.temperature for s in seqs], dtype=torch.float32, device=dev)
+        need_filter = any(s.params.top_k > 0 or s.params.top_p < 1.0 or s.params.min_p > 0.0 for s in seqs)
+        top_k = top_p = min_p = None
+        if need_filter:
+            top_k = torch.tensor([max(s.params.top_k, 0) for s in seqs], dtype=torch.int32, device=dev)
+            top_p = torch.tensor([s.params.top_p for s in seqs], dtype=torch.float32, device=dev)
+            min_p = torch.tensor([s.params.min_p for s in seqs], dtype=torch.float32, device=dev)
+        keys = []
+        for s in seqs:
+            base = s.params.seed if s.params.seed is not None else (zlib.crc32(s.request_id.encode()) & 0x7FFFFFFF)
+            keys.append(((base * 1000003 + s.sample_index) * 1000003 + len(s.output_ids)) & (2 ** 62 - 1))
+        row_keys = torch.tensor(keys, dtype=torch.int64, device=dev)
+        eos_prob = None
+        if any(s.params.eos_hazard is not None for s in seqs):
+            eos_prob = torch.tensor(
+                [length_hazard(len(s.output_ids) + 1, *s.params.eos_hazard)
+                 if s.params.eos_hazard is not None else -1.0 for s in seqs],
+                dtype=torch.float32, device=dev)
+        return temp, top_k, top_p, min_p, row_keys, eos_prob
+
+    def _sample(self, logits: torch.Tensor, seqs: List[Sequence]) -> Tuple[List[int], List[float]]:
+        temp, top_k, top_p, min_p, keys, eos_prob = self._sampling_tensors(seqs)
+        if self.comm.world_size > 1:  # vocabulary-sharded head: gather the logits of the few rows
+            parts = [torch.empty_like(logits) for _ in range(self.comm.world_size)]
+            torch.distributed.all_gather(parts, logits.contiguous(), group=self.comm.group)
+            logits = torch.cat(parts, dim=-1)
+        tokens, logprobs = ops.sample(logits, temp, top_k, top_p, min_p, keys, self.seed, eos_prob,
+                                      self.eos_token_id)
+        return tokens.tolist(), logprobs.tolist()
+
+    def _append_token(self, seq: Sequence, token: int, logprob: float) -> None:
+        seq.output_ids.append(int(token))
+        seq.output_logprobs.append(float(logprob))
+        p = seq.params
+        if not p.ignore_eos and (token == self.eos_token_id or token in p.stop_token_ids):
+            self.scheduler.finish(seq, SeqStatus.FINISHED_STOPPED)
+        elif len(seq.output_ids) >= p.max_tokens or seq.total_len >= self.max_model_len:
+            self.scheduler.finish(seq, SeqStatus.FINISHED_LENGTH)
+
+    def _run_prefill(self, items: List[PrefillItem]) -> None:
+        dev = self.device
+        ids, pos, slots, cu, last_rows, finishing = [], [], [], [0], [], []
+        need_prefix = any(it.start > 0 for it in items)
+        tok_seq, tok_pos, cu_k = [], [], [0]
+        for row, it in enumerate(items):
+            s = it.seq
+            all_ids = s.all_ids
+            ids.extend(all_ids[it.start:it.start + it.length])
+            pos.extend(range(it.start, it.start + it.length))
+            slots.append(self.bm.slots(s.seq_id, it.start, it.length))
+            cu.append(cu[-1] + it.length)
+            if it.completes_prompt:
+                last_rows.append(cu[-1] - 1)
+                finishing.append(s)
+            if need_prefix:
+                end = it.start + it.length
+                tok_seq.extend([row] * end)
+                tok_pos.extend(range(end))
+                cu_k.append(cu_k[-1] + end)
+        t_ids = torch.tensor(ids, dtype=torch.int64, device=dev)
+        t_pos = torch.tensor(pos, dtype=torch.int32, device=dev)
+        t_slots = torch.from_numpy(np.concatenate(slots)).to(dev)
+        t_cu = torch.tensor(cu, dtype=torch.int32, device=dev)
+        t_last = torch.tensor(last_rows, dtype=torch.int64, device=dev)
+        prefix = None
+        if need_prefix:
+            max_blocks = max(len(self.bm.block_table(it.seq.seq_id)) for it in items)
+            bt = self.bm.block_tables([it.seq.seq_id for it in items], max_blocks)
+            prefix = dict(block_tables=torch.from_numpy(bt).to(dev),
+                          token_seq=torch.tensor(tok_seq, dtype=torch.int32, device=dev),
+                          token_pos=torch.tensor(tok_pos, dtype=torch.int32, device=dev),
+                          cu_k=torch.tensor(cu_k, dtype=torch.int32, device=dev))
+        logits = self.runner.prefill(t_ids, t_pos, t_slots, t_cu, max(it.length for it in items), t_last,
+                                     prefix)
+        self.stats["prefill_tokens"] += len(ids)
+        for it in items:
+            it.seq.num_computed = it.start + it.length
+            self.bm.commit(it.seq.seq_id, it.seq.all_ids, it.seq.num_computed)
+        if not finishing:
+            return
+        # fork n-sample groups, then sample one token per resulting sequence
+        rows, seqs = [], []
+        for r, lead in enumerate(finishing):
+            rows.append(r)
+            seqs.append(lead)
+            group = self.scheduler.groups.get(lead.request_id)
+            if group is not None and not group.forked:
+                for child, (src, dst) in self.scheduler.fork_group(lead):
+                    if src >= 0:
+                        self.runner.cache.copy_block(src, dst)
+                    rows.append(r)
+                    seqs.append(child)
+        sel = logits[torch.tensor(rows, dtype=torch.int64, device=dev)] if len(rows) != logits.shape[0] \
+            or rows != list(range(len(rows))) else logits
+        tokens, lps = self._sample(sel, seqs)
+        for s, tok, lp in zip(seqs, tokens, lps):
+            self._append_token(s, tok, lp)
+
+    def _run_decode(self, seqs: List[Sequence]) -> None:
+        dev = self.device
+        b = len(seqs)
+        ids = torch.tensor([s.output_ids[-1] if s.output_ids else s.prompt_ids[-1] for s in seqs],
+                           dtype=torch.int64, device=dev)
+        lens = [s.total_len for s in seqs]
+        pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=dev)
+        slots = torch.from_numpy(np.concatenate(
+            [self.bm.slots(s.seq_id, n - 1, 1) for s, n in zip(seqs, lens)])).to(dev)
+        max_ctx = max(lens)
+        max_blocks = (max_ctx + self.block_size - 1) // self.block_size
+        bt = torch.from_numpy(self.bm.block_tables([s.seq_id for s in seqs], max_blocks)).to(dev)
+        ctx = torch.tensor(lens, dtype=torch.int32, device=dev)
+        logits = self.runner.decode(ids, pos, slots, bt, ctx, max_ctx)
+        self.stats["decode_tokens"] += b
+        for s, n in zip(seqs, lens):
+            s.num_computed = n
+        tokens, lps = self._sample(logits, seqs)
+        for s, tok, lp in zip(seqs, tokens, lps):
+            self._append_token(s, tok, lp)
+
+    def _to_output(self, group: RequestGroup) -> RequestOutput:
+        reasons = {SeqStatus.FINISHED_STOPPED: "stop", SeqStatus.FINISHED_LENGTH: "length",
+                   SeqStatus.FINISHED_ABORTED: "abort"}
+        outs = [CompletionOutput(s.sample_index, list(s.output_ids), list(s.output_logprobs),
+                                 reasons.get(s.status, "abort"))
+                for s in sorted(group.seqs, key=lambda x: x.sample_index)]
+        return RequestOutput(group.request_id, list(group.seqs[0].prompt_ids), outs, True)
+
+    # ---- convenience -----------------------------------------------------------------------------
+    def generate(self, prompts: Seq_[Seq_[int]], params: SamplingParams,
+                 request_ids: Optional[Seq_[str]] = None) -> List[RequestOutput]:
+        """Blocking generation; results come back in the order of ``prompts``."""
+        rids = [self.add_request(None if request_ids is None else request_ids[i], p, params)
+                for i, p in enumerate(prompts)]
+        done: Dict[str, RequestOutput] = {}
+        while self.has_unfinished_requests():
+            for out in self.step():
+                done[out.request_id] = out
+        for g in self.scheduler.pop_finished_groups():
+            done[g.request_id] = self._to_output(g)
+        return [done[r] for r in rids]

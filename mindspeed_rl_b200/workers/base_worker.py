@@ -1,0 +1,110 @@
+"""Per-GPU worker base: data-plane access shared by every role.
+
+Each model-parallel replica has one *leader* (tp 0, cp 0, pp 0) that talks to the experience
+store; what it pulls is fanned out to the other ranks of the replica in **one** host-side
+object broadcast (header + payload together), and results are written back only by the last
+pipeline stage's tp-0 rank.  This replaces the per-column broadcast cascades of the reference
+(``mindspeed_rl/workers/base_worker.py:367-516,685-822``) while keeping its semantics: ragged
+rows from the store arrive as padded 2-D tensors, padded to a multiple of ``tp*cp`` (``2*tp*cp``
+for ring context parallel).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.state import ParallelState, get_parallel_state
+from ..utils.pad_process import (pad_rows, padding_dict_to_tensor_dict,
+                                 remove_padding_tensor_dict_to_dict, truncate_rows)
+
+_TOKEN_COLUMNS = ("prompts", "responses", "input_ids", "labels")
+
+
+def pad_batch(ragged: Dict[str, List[torch.Tensor]], pad_id: int, multiple: int = 1) -> Dict[str, torch.Tensor]:
+    """Ragged rows -> ``[n, W]`` tensors; 1-element columns become ``[n]``."""
+    out = {}
+    for k, rows in ragged.items():
+        rows = list(rows)
+        if k in _TOKEN_COLUMNS:
+            out[k] = pad_rows(rows, pad_id, multiple).long()
+        elif all(r.numel() == 1 for r in rows):
+            out[k] = torch.stack([r.reshape(()) for r in rows])
+        else:
+            out[k] = pad_rows(rows, 0)
+    return out
+
+
+class BaseWorker:
+    def __init__(self, td=None, pad_token_id: int = 0, state: Optional[ParallelState] = None):
+        self.td = td
+        self.pad_token_id = pad_token_id
+        self._state = state
+
+    # ---- parallel coordinates ------------------------------------------------------------------
+    @property
+    def parallel_state(self) -> ParallelState:
+        return self._state or get_parallel_state()
+
+    def is_replica_leader(self, tp_rank=None, cp_rank=None, pp_rank=None) -> bool:
+        ps = self.parallel_state
+        return ps.rank_in("tp") == 0 and ps.rank_in("cp") == 0 and ps.rank_in("pp") == 0
+
+    def is_writer(self) -> bool:
+        ps = self.parallel_state
+        return ps.rank_in("tp") == 0 and ps.rank_in("cp") == 0 and ps.is_pipeline_last_stage()
+
+    def _replica_group(self):
+        ps = self.parallel_state
+        return ps.group("mp_cp"), ps.global_ranks("mp_cp")[0], ps.size("mp_cp")
+
+    # ---- data plane ------------------------------------------------------------------------------
+    def dispatch_transfer_dock_data(self, consumer: str, columns: Sequence[str], experience_count: int,
+                                    pad_multiple: int = 1, indexes: Optional[List[int]] = None,
+                                    get_n_samples: bool = True, use_batch_seqlen_balance: bool = False,
+                                    dp_size: int = 1
+                                    ) -> Tuple[Optional[Dict[str, torch.Tensor]], Optional[List[int]], bool]:
+        """Returns ``(batch, indexes, finished)``.  ``finished`` is True when the consumer has
+        nothing left to process in this iteration (then ``batch`` is ``None``)."""
+        group, src, size = self._replica_group()
+        payload = None
+        if self.is_replica_leader():
+            if self.td.all_consumed(consumer):
+                payload = (None, None, True)
+            else:
+                batch, idx = self.td.get_experience(consumer, list(columns), experience_count,
+                                                    dp_size=dp_size, indexes=indexes,
+                                                    get_n_samples=get_n_samples,
+                                                    use_batch_seqlen_balance=use_batch_seqlen_balance)
+                payload = (batch, idx, False)
+        if size > 1 and dist.is_initialized():
+            box = [payload]
+            dist.broadcast_object_list(box, src=src, group=group)
+            payload = box[0]
+        batch, idx, finished = payload
+        if finished or not batch or not idx:
+            return None, None, finished
+        ragged = remove_padding_tensor_dict_to_dict(batch)
+        return pad_batch(ragged, self.pad_token_id, pad_multiple), idx, False
+
+    def collect_transfer_dock_data(self, output: Dict[str, torch.Tensor], indexes: List[int],
+                                   lengths: Optional[torch.Tensor] = None) -> None:
+        """Write result columns back (ragged when ``lengths`` is given). Only one rank per replica
+        writes."""
+        if not self.is_writer():
+            return
+        out = {}
+        for k, v in output.items():
+            if isinstance(v, list):
+                out[k] = [t.detach().cpu() for t in v]
+            elif lengths is not None and v.dim() == 2 and v.shape[1] > 1:
+                out[k] = truncate_rows(v.detach().cpu(), lengths)
+            else:
+                out[k] = [row.reshape(-1) for row in v.detach().cpu()]
+        self.td.put_experience(padding_dict_to_tensor_dict(out), indexes)
+
+    def update_metrics(self, key, value, cumulate=True) -> None:
+        if self.is_writer():
+            self.td.update_metrics(key, value=value, cumulate=cumulate)

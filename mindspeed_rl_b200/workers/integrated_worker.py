@@ -1,0 +1,254 @@
+"""Co-located actor worker: training model + frozen reference + rollout engine on one GPU.
+
+Stages (each loops "pull from the experience store -> compute -> write back" until the store
+says the stage has consumed everything; reference: ``workers/actor_hybrid_worker.py:114-869``,
+``workers/integrated_worker.py:27-287``):
+
+* ``generate_sequences``      -- enter infer mode (reshard), rollout, exit infer mode
+* ``compute_ref_log_prob``    -- frozen reference forward
+* ``compute_log_prob``        -- actor forward (old log-probs)
+* ``update``                  -- policy update
+* ``save_checkpoint`` / ``get_iteration`` / ``get_consumed_train_samples``
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.gpt import GPTModel
+from ..models.training_engine import TrainingEngine
+from ..models.transformer_config import TransformerConfig
+from ..optim.distributed_optimizer import DistributedOptimizer, OptimizerParamScheduler
+from ..parallel.ddp import DistributedDataParallel
+from ..parallel.state import get_parallel_state
+from ..parallel.tp_comm import TPComm
+from ..reshard.sharding_manager import ShardingManager
+from ..rollout.engine import LLMEngine
+from ..rollout.scheduler import SamplingParams
+from .base_worker import BaseWorker
+
+
+def _now() -> float:
+    return time.time()
+
+
+class IntegratedWorker(BaseWorker):
+    def __init__(self, actor_config, rl_config, generate_config, td=None, *, eos_token_id: int = -1,
+                 pad_token_id: int = 0, device=None, ref_config=None, with_reference: bool = True,
+                 sampling_overrides: Optional[dict] = None, seed: Optional[int] = None):
+        super().__init__(td, pad_token_id)
+        self.actor_config, self.rl_config, self.generate_config = actor_config, rl_config, generate_config
+        self.ref_config = ref_config or actor_config
+        self.with_reference = with_reference
+        self.eos_token_id = eos_token_id
+        self.device = torch.device(device if device is not None
+                                   else ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.sampling_overrides = sampling_overrides or {}
+        self.seed = actor_config.seed if seed is None else seed
+        self.iteration = 0
+        self.consumed_train_samples = 0
+        self.initialized = False
+
+    # ------------------------------------------------------------------------------------------
+    def initialize(self) -> None:
+        ac, rl, gc = self.actor_config, self.rl_config, self.generate_config
+        ps = self.parallel_state
+        tp = ps.size("tp")
+        self.comm = TPComm(ps.group("tp"), ac.sequence_parallel, world_size=tp, rank=ps.rank_in("tp"))
+        dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        tcfg = TransformerConfig.from_megatron(ac, params_dtype=dtype)
+        self.tcfg = tcfg
+        core = GPTModel(tcfg, self.comm, device=self.device, seed=self.seed)
+        dp = ps.size("dp_cp")
+        self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
+                                             grad_in_fp32=bool(ac.accumulate_allreduce_grads_in_fp32))
+        self.optimizer = DistributedOptimizer(
+            self.model.buffers, lr=ac.lr or 1e-6, betas=(ac.adam_beta1, ac.adam_beta2),
+            weight_decay=ac.weight_decay, clip_grad=ac.clip_grad, dp_group=ps.group("dp_cp"),
+            dp_rank=ps.rank_in("dp_cp"), model_parallel_group=ps.group("mp"),
+            offload_to_host=bool(ac.swap_optimizer))
+        iters = ac.train_iters or 1
+        n_updates = iters * max(1, (ac.global_batch_size * rl.n_samples_per_prompt) // max(rl.mini_batch_size, 1))
+        samples = n_updates * rl.mini_batch_size
+        warm = int((ac.lr_warmup_fraction or 0.0) * samples)
+        self.scheduler = OptimizerParamScheduler(self.optimizer, ac.lr or 1e-6, ac.min_lr or 0.0, warm,
+                                                 samples, ac.lr_decay_style or "constant")
+        loss_opts = dict(clip_ratio=rl.clip_ratio, kl_penalty=rl.kl_penalty, entropy_coeff=rl.entropy_coeff,
+                         token_level_loss=rl.token_level_loss, clip_higher_enable=rl.clip_higher_enable,
+                         clip_ratio_low=rl.clip_ratio_low, clip_ratio_high=rl.clip_ratio_high,
+                         kl_ctrl=rl.init_kl_coef)
+        pad_mult = tp * ps.size("cp") * (2 if (ps.size("cp") > 1 and ac.context_parallel_algo == "megatron_cp_algo") else 1)
+        self.pad_multiple = pad_mult
+        temperature = gc.sampling_config.get("temperature", 1.0) or 1.0
+        common = dict(stage=ac.stage or "ray_grpo", temperature=temperature,
+                      use_dynamic_bsz=rl.use_dynamic_bsz, pad_multiple=pad_mult,
+                      dp_group=ps.group("dp_cp"), dp_size=dp, device=self.device,
+                      dynamic_max_batch_size=rl.actor_dynamic_max_batch_size)
+        self.actor = TrainingEngine(
+            self.model, self.optimizer, self.scheduler, role="actor",
+            micro_batch_size=ac.micro_batch_size or 1,
+            forward_micro_batch_size=rl.actor_forward_micro_batch_size or ac.micro_batch_size or 1,
+            mini_batch_size_per_dp=max(rl.mini_batch_size // dp, 1), epochs=rl.epochs,
+            shuffle_mini_batch=rl.shuffle_mini_batch,
+            max_packing_token_size=rl.update_max_packing_token_size,
+            forward_max_packing_token_size=rl.actor_max_packing_token_size, **common, **loss_opts)
+        self.ref_model = None
+        self.reference = None
+        if self.with_reference:
+            rcfg = TransformerConfig.from_megatron(self.ref_config, params_dtype=dtype)
+            self.ref_model = GPTModel(rcfg, self.comm, device=self.device, seed=self.seed)
+            self.ref_model.load_state_dict(core.state_dict())
+            for p in self.ref_model.parameters():
+                p.requires_grad_(False)
+            self.reference = TrainingEngine(
+                self.ref_model, role="reference",
+                micro_batch_size=rl.ref_forward_micro_batch_size or self.ref_config.micro_batch_size or 1,
+                max_packing_token_size=rl.ref_max_packing_token_size, **common)
+        # rollout engine (infer TP == train TP here; other layouts go through reshard.planner)
+        self.engine = LLMEngine(
+            tcfg, self.device, max_num_seqs=gc.max_num_seqs, max_num_batched_tokens=gc.max_num_batched_tokens,
+            max_model_len=gc.max_model_len, block_size=gc.kv_block_size,
+            enable_prefix_caching=gc.enable_prefix_caching, enforce_eager=gc.enforce_eager,
+            graph_batch_sizes=tuple(gc.graph_batch_sizes), eos_token_id=self.eos_token_id,
+            pad_token_id=self.pad_token_id, comm=self.comm if tp > 1 else None, seed=self.seed)
+        resharder = None
+        if gc.infer_tensor_parallel_size != tp or ps.size("pp") > 1:
+            from ..reshard.planner import Resharder
+
+            resharder = Resharder.for_worker(self, gc)
+            self.engine = resharder.engine
+        self.sharding_manager = ShardingManager(
+            self.model, self.engine, self.optimizer, offload_train_optimizer=gc.offload_train_optimizer,
+            offload_train_grad=gc.offload_train_grad, offload_train_param=gc.offload_train_param,
+            gpu_memory_utilization=gc.gpu_memory_utilization, resharder=resharder)
+        self.sampling_params = SamplingParams.from_config(gc.sampling_config, n=rl.n_samples_per_prompt,
+                                                          **self.sampling_overrides)
+        self.initialized = True
+
+    def init_transfer_dock(self, td) -> None:
+        self.td = td
+
+    def get_iteration(self) -> int:
+        return self.iteration
+
+    def get_consumed_train_samples(self) -> int:
+        return self.consumed_train_samples
+
+    # ---- rollout -----------------------------------------------------------------------------------
+    def generate_sequences(self) -> None:
+        rl = self.rl_config
+        start_reshard = _now()
+        t_enter = self.sharding_manager.enter_infer_mode()
+        self.update_metrics("timing/resharding_enter_infer", [t_enter])
+        start = _now()
+        n = rl.n_samples_per_prompt
+        while True:
+            batch, idx, finished = self.dispatch_transfer_dock_data(
+                "actor_rollout", ["prompts", "prompt_length"], rl.actor_rollout_dispatch_size,
+                get_n_samples=True)
+            if finished:
+                break
+            if batch is None:
+                time.sleep(0.002)
+                continue
+            self._generate_batch(batch, idx, n)
+        end = _now()
+        t_exit = self.sharding_manager.exit_infer_mode()
+        self.update_metrics("timing/rollout", [round(end, 4), round(start, 4)])
+        self.update_metrics("timing/resharding_exit_infer", [t_exit])
+        self.update_metrics("timing/resharding_to_infer", [t_enter + t_exit])
+
+    def _generate_batch(self, batch: Dict[str, torch.Tensor], idx: List[int], n: int) -> None:
+        prompts, plen = batch["prompts"], batch["prompt_length"].reshape(-1)
+        uniq = list(range(0, len(idx), n))                   # the store holds n copies per prompt
+        prompt_lists = [prompts[i, :int(plen[i])].tolist() for i in uniq]
+        outs = self.engine.generate(prompt_lists, self.sampling_params)
+        vocab = self.tcfg.vocab_size
+        responses, input_ids, lengths = [], [], []
+        for p, o in zip(prompt_lists, outs):
+            for c in o.outputs:
+                ids = [t if t < vocab else 0 for t in c.token_ids]
+                responses.append(torch.tensor(ids, dtype=torch.int64))
+                input_ids.append(torch.tensor(p + ids, dtype=torch.int64))
+                lengths.append(torch.tensor([len(ids)], dtype=torch.int32))
+        self.collect_transfer_dock_data(
+            {"responses": responses, "input_ids": input_ids, "response_length": lengths}, idx)
+
+    # ---- forward-only stages ---------------------------------------------------------------------------
+    def _logprob_stage(self, consumer: str, engine: TrainingEngine, out_column: str, dispatch_size: int,
+                       timing_key: str) -> None:
+        columns = ["input_ids", "responses", "response_length", "prompt_length"]
+        start = _now()
+        while True:
+            batch, idx, finished = self.dispatch_transfer_dock_data(
+                consumer, columns, dispatch_size, pad_multiple=1, get_n_samples=False,
+                use_batch_seqlen_balance=self.rl_config.use_dp_batch_balance)
+            if finished:
+                break
+            if batch is None:
+                time.sleep(0.002)
+                continue
+            lp = engine.forward(batch)
+            self.collect_transfer_dock_data({out_column: lp}, idx, lengths=batch["response_length"])
+        self.update_metrics(timing_key, [round(_now(), 4), round(start, 4)])
+
+    def compute_ref_log_prob(self) -> None:
+        if self.reference is None:
+            raise RuntimeError("this worker was built without a reference model")
+        self.sharding_manager.enter_forward_mode()
+        self._logprob_stage("ref_log_prob", self.reference, "ref_log_prob",
+                            self.rl_config.ref_dispatch_size, "timing/reference_model")
+        self.update_metrics("end_time/reference", [round(_now(), 4)])
+        self.sharding_manager.exit_forward_mode()
+
+    def compute_log_prob(self) -> None:
+        self.sharding_manager.enter_forward_mode()
+        self._logprob_stage("actor_log_prob", self.actor, "old_log_prob",
+                            self.rl_config.actor_logprob_dispatch_size, "timing/old_log_p")
+        self.update_metrics("end_time/old_log_p", [round(_now(), 4)])
+        self.sharding_manager.exit_forward_mode()
+
+    # ---- update ----------------------------------------------------------------------------------------
+    def update(self, kl_ctrl=None, skip_actor_log_prob: bool = False) -> None:
+        rl = self.rl_config
+        t_reshard = self.sharding_manager.enter_train_mode()
+        self.update_metrics("timing/resharding_to_train", [t_reshard])
+        columns = ["responses", "advantages", "input_ids", "response_length", "prompt_length"]
+        if not skip_actor_log_prob:
+            columns.append("old_log_prob")
+        if self.with_reference and (self.actor_config.stage or "ray_grpo") != "ray_dapo":
+            columns.append("ref_log_prob")
+        if rl.multi_turn_enable:
+            columns.append("response_mask")
+        start = _now()
+        while True:
+            batch, idx, finished = self.dispatch_transfer_dock_data(
+                "actor_train", columns, rl.actor_update_dispatch_size, get_n_samples=False,
+                use_batch_seqlen_balance=rl.use_dp_batch_balance)
+            if finished:
+                break
+            if batch is None:
+                time.sleep(0.002)
+                continue
+            metrics = self.actor.update(batch, kl_ctrl)
+            self.consumed_train_samples += len(idx) * self.parallel_state.size("dp_cp")
+            if self.is_writer():
+                self.td.update_metrics("", value=metrics, cumulate=True)
+        self.update_metrics("timing/update", [round(_now(), 4), round(start, 4)])
+        self.iteration += 1
+        self.sharding_manager.exit_train_mode()
+
+    # ---- checkpoint ---------------------------------------------------------------------------------------
+    def save_checkpoint(self, iteration: int) -> None:
+        from ..checkpoint.mcore import save_checkpoint
+
+        if not self.actor_config.save:
+            return
+        self.sharding_manager.enter_train_mode()
+        save_checkpoint(self.actor_config.save, iteration, self.model.module, self.optimizer,
+                        self.scheduler, self.parallel_state, self.actor_config,
+                        consumed_train_samples=self.consumed_train_samples)
+        self.sharding_manager.exit_train_mode()
