@@ -100,6 +100,15 @@ def compose(config_name: str, config_dir: Optional[str] = None,
     return apply_overrides(out, overrides)
 
 
+def load_model_catalogue(names: Sequence[str], config_dir: Optional[str] = None) -> Dict[str, Any]:
+    """``{name: architecture dict}`` read from ``<config dir>/model/<name>.yaml``."""
+    dirs = ([os.path.abspath(config_dir)] if config_dir else []) + [DEFAULT_CONFIG_DIR]
+    out: Dict[str, Any] = {}
+    for name in names:
+        _deep_merge(out, _read_yaml(_find(name, dirs, sub="model")))
+    return out
+
+
 def parse_cli(argv: Optional[Sequence[str]] = None, default_name: Optional[str] = None):
     """Parse ``--config-name/--config-dir`` plus free ``key=value`` overrides."""
     ap = argparse.ArgumentParser(add_help=True)

@@ -20,6 +20,7 @@ from typing import Any, Callable, Dict, List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
+from ..obs.io_counter import to_device, to_host
 from ..utils.seqlen_balancing import get_reverse_idx, rearrange_micro_batches
 from .gpt import GPTModel, PackedMeta
 from .loss.registry import BaseLossFunc, LossFuncFactory
@@ -68,7 +69,8 @@ class MicroBatch:
 
     def to(self, device) -> "MicroBatch":
         for k in ("ids", "labels", "positions", "cu", "resp_index", "resp_valid", "last_index"):
-            setattr(self, k, getattr(self, k).to(device, non_blocking=True))
+            t = getattr(self, k)
+            setattr(self, k, to_device(t, t.dtype, device))
         return self
 
     def meta(self) -> PackedMeta:
@@ -145,7 +147,7 @@ class TrainingEngine:
             vals, _ = self._run_model(mb, want_entropy=False)
             results.append((rows, vals.float()))
         for rows, vals in results:
-            out[torch.as_tensor(rows)] = vals.cpu()
+            out[torch.as_tensor(rows)] = to_host(vals)
         return out
 
     # ------------------------------------------------------------------------------------------
@@ -193,8 +195,8 @@ class TrainingEngine:
             if self.use_dynamic_bsz:   # re-weight bins by their share of the mini-batch rows
                 scale = len(rows) / len(mini)
             out, ent = self._run_model(mb, want_entropy=self.want_entropy)
-            batch_dev = {k: v.to(self.device, non_blocking=True) for k, v in mb.data.items()
-                         if k not in ("input_ids",)}
+            batch_dev = {k: to_device(v, v.dtype, self.device) for k, v in mb.data.items()
+                         if k not in ("input_ids", "prompts", "responses")}
             if not self.entropy_needs_grad and ent is not None:
                 ent = ent.detach()
             grad, dent, stats = self.loss_func.compute(batch_dev, out.detach(), ent.detach() if ent is not None else None, scale)

@@ -23,6 +23,7 @@ import torch
 
 from .. import ops
 from ..models.transformer_config import TransformerConfig
+from ..obs.io_counter import to_device, to_host
 from ..parallel.tp_comm import NO_TP, TPComm
 from .block_manager import BlockManager
 from .model_runner import KVCache, ModelRunner, RolloutWeights
@@ -134,37 +135,52 @@ class LLMEngine:
         return [self._to_output(g) for g in self.scheduler.pop_finished_groups()]
 
     # ---- internals -----------------------------------------------------------------------------
-    def _sampling_tensors(self, seqs: List[Sequence]):
+    def _ship(self, ints: List[List[int]], floats: Optional[List[List[float]]] = None):
+        """Send several equally long integer (and float) rows in ONE pinned copy each."""
         dev = self.device
-        temp = torch.tensor([s.params.temperature for s in seqs], dtype=torch.float32, device=dev)
-        need_filter = any(s.params.top_k > 0 or s.params.top_p < 1.0 or s.params.min_p > 0.0 for s in seqs)
-        top_k = top_p = min_p = None
-        if need_filter:
-            top_k = torch.tensor([max(s.params.top_k, 0) for s in seqs], dtype=torch.int32, device=dev)
-            top_p = torch.tensor([s.params.top_p for s in seqs], dtype=torch.float32, device=dev)
-            min_p = torch.tensor([s.params.min_p for s in seqs], dtype=torch.float32, device=dev)
-        keys = []
-        for s in seqs:
-            base = s.params.seed if s.params.seed is not None else (zlib.crc32(s.request_id.encode()) & 0x7FFFFFFF)
-            keys.append(((base * 1000003 + s.sample_index) * 1000003 + len(s.output_ids)) & (2 ** 62 - 1))
-        row_keys = torch.tensor(keys, dtype=torch.int64, device=dev)
-        eos_prob = None
-        if any(s.params.eos_hazard is not None for s in seqs):
-            eos_prob = torch.tensor(
-                [length_hazard(len(s.output_ids) + 1, *s.params.eos_hazard)
-                 if s.params.eos_hazard is not None else -1.0 for s in seqs],
-                dtype=torch.float32, device=dev)
-        return temp, top_k, top_p, min_p, row_keys, eos_prob
+        it = to_device(np.asarray(ints, dtype=np.int64), torch.int64, dev)
+        ft = to_device(np.asarray(floats, dtype=np.float32), torch.float32, dev) if floats else None
+        return it, ft
 
-    def _sample(self, logits: torch.Tensor, seqs: List[Sequence]) -> Tuple[List[int], List[float]]:
-        temp, top_k, top_p, min_p, keys, eos_prob = self._sampling_tensors(seqs)
+    def _sampling_rows(self, seqs: List[Sequence]):
+        """Host-side sampling parameters: (row_keys, float rows, flags)."""
+        keys, temp = [], []
+        need_filter = need_eos = False
+        for s in seqs:
+            p = s.params
+            base = p.seed if p.seed is not None else (zlib.crc32(s.request_id.encode()) & 0x7FFFFFFF)
+            keys.append(((base * 1000003 + s.sample_index) * 1000003 + len(s.output_ids)) & (2 ** 62 - 1))
+            temp.append(p.temperature)
+            need_filter |= p.top_k > 0 or p.top_p < 1.0 or p.min_p > 0.0
+            need_eos |= p.eos_hazard is not None
+        floats = [temp]
+        if need_filter:
+            floats += [[float(max(s.params.top_k, 0)) for s in seqs], [s.params.top_p for s in seqs],
+                       [s.params.min_p for s in seqs]]
+        if need_eos:
+            floats.append([length_hazard(len(s.output_ids) + 1, *s.params.eos_hazard)
+                           if s.params.eos_hazard is not None else -1.0 for s in seqs])
+        return keys, floats, need_filter, need_eos
+
+    def _sample(self, logits: torch.Tensor, seqs: List[Sequence], keys: torch.Tensor,
+                ft: torch.Tensor, need_filter: bool, need_eos: bool) -> Tuple[List[int], List[float]]:
+        temp = ft[0]
+        top_k = top_p = min_p = eos_prob = None
+        row = 1
+        if need_filter:
+            top_k, top_p, min_p = ft[1].to(torch.int32), ft[2], ft[3]
+            row = 4
+        if need_eos:
+            eos_prob = ft[row]
         if self.comm.world_size > 1:  # vocabulary-sharded head: gather the logits of the few rows
             parts = [torch.empty_like(logits) for _ in range(self.comm.world_size)]
             torch.distributed.all_gather(parts, logits.contiguous(), group=self.comm.group)
             logits = torch.cat(parts, dim=-1)
         tokens, logprobs = ops.sample(logits, temp, top_k, top_p, min_p, keys, self.seed, eos_prob,
                                       self.eos_token_id)
-        return tokens.tolist(), logprobs.tolist()
+        # one device->host read per step: tokens and their log-probs together
+        both = to_host(torch.stack([tokens.double(), logprobs.double()]))
+        return both[0].long().tolist(), both[1].tolist()
 
     def _append_token(self, seq: Sequence, token: int, logprob: float) -> None:
         seq.output_ids.append(int(token))
@@ -195,19 +211,17 @@ class LLMEngine:
                 tok_seq.extend([row] * end)
                 tok_pos.extend(range(end))
                 cu_k.append(cu_k[-1] + end)
-        t_ids = torch.tensor(ids, dtype=torch.int64, device=dev)
-        t_pos = torch.tensor(pos, dtype=torch.int32, device=dev)
-        t_slots = torch.from_numpy(np.concatenate(slots)).to(dev)
-        t_cu = torch.tensor(cu, dtype=torch.int32, device=dev)
-        t_last = torch.tensor(last_rows, dtype=torch.int64, device=dev)
+        tok, _ = self._ship([ids, pos, np.concatenate(slots).tolist()])
+        t_ids, t_pos, t_slots = tok[0], tok[1].to(torch.int32), tok[2]
+        t_cu = to_device(cu, torch.int32, dev)
+        t_last = to_device(last_rows, torch.int64, dev)
         prefix = None
         if need_prefix:
             max_blocks = max(len(self.bm.block_table(it.seq.seq_id)) for it in items)
             bt = self.bm.block_tables([it.seq.seq_id for it in items], max_blocks)
-            prefix = dict(block_tables=torch.from_numpy(bt).to(dev),
-                          token_seq=torch.tensor(tok_seq, dtype=torch.int32, device=dev),
-                          token_pos=torch.tensor(tok_pos, dtype=torch.int32, device=dev),
-                          cu_k=torch.tensor(cu_k, dtype=torch.int32, device=dev))
+            pt, _ = self._ship([tok_seq, tok_pos])
+            prefix = dict(block_tables=to_device(bt, torch.int32, dev), token_seq=pt[0].to(torch.int32),
+                          token_pos=pt[1].to(torch.int32), cu_k=to_device(cu_k, torch.int32, dev))
         logits = self.runner.prefill(t_ids, t_pos, t_slots, t_cu, max(it.length for it in items), t_last,
                                      prefix)
         self.stats["prefill_tokens"] += len(ids)
@@ -228,30 +242,30 @@ class LLMEngine:
                         self.runner.cache.copy_block(src, dst)
                     rows.append(r)
                     seqs.append(child)
-        sel = logits[torch.tensor(rows, dtype=torch.int64, device=dev)] if len(rows) != logits.shape[0] \
-            or rows != list(range(len(rows))) else logits
-        tokens, lps = self._sample(sel, seqs)
-        for s, tok, lp in zip(seqs, tokens, lps):
-            self._append_token(s, tok, lp)
+        keys, floats, need_filter, need_eos = self._sampling_rows(seqs)
+        it_, ft = self._ship([keys, rows], floats)
+        sel = logits if rows == list(range(logits.shape[0])) else logits[it_[1]]
+        tokens, lps = self._sample(sel, seqs, it_[0], ft, need_filter, need_eos)
+        for s, tok_, lp in zip(seqs, tokens, lps):
+            self._append_token(s, tok_, lp)
 
     def _run_decode(self, seqs: List[Sequence]) -> None:
         dev = self.device
         b = len(seqs)
-        ids = torch.tensor([s.output_ids[-1] if s.output_ids else s.prompt_ids[-1] for s in seqs],
-                           dtype=torch.int64, device=dev)
+        last = [s.output_ids[-1] if s.output_ids else s.prompt_ids[-1] for s in seqs]
         lens = [s.total_len for s in seqs]
-        pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=dev)
-        slots = torch.from_numpy(np.concatenate(
-            [self.bm.slots(s.seq_id, n - 1, 1) for s, n in zip(seqs, lens)])).to(dev)
+        slots = [int(self.bm.slots(s.seq_id, n - 1, 1)[0]) for s, n in zip(seqs, lens)]
+        keys, floats, need_filter, need_eos = self._sampling_rows(seqs)
+        it_, ft = self._ship([last, [n - 1 for n in lens], slots, lens, keys], floats)
         max_ctx = max(lens)
         max_blocks = (max_ctx + self.block_size - 1) // self.block_size
-        bt = torch.from_numpy(self.bm.block_tables([s.seq_id for s in seqs], max_blocks)).to(dev)
-        ctx = torch.tensor(lens, dtype=torch.int32, device=dev)
-        logits = self.runner.decode(ids, pos, slots, bt, ctx, max_ctx)
+        bt = to_device(self.bm.block_tables([s.seq_id for s in seqs], max_blocks), torch.int32, dev)
+        logits = self.runner.decode(it_[0], it_[1].to(torch.int32), it_[2], bt, it_[3].to(torch.int32),
+                                    max_ctx)
         self.stats["decode_tokens"] += b
         for s, n in zip(seqs, lens):
             s.num_computed = n
-        tokens, lps = self._sample(logits, seqs)
+        tokens, lps = self._sample(logits, seqs, it_[4], ft, need_filter, need_eos)
         for s, tok, lp in zip(seqs, tokens, lps):
             self._append_token(s, tok, lp)
 

@@ -1,0 +1,271 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 formulation of the same op.
+
+Each test runs the op on CUDA tensors (kernel path) and on CPU copies (reference path inside the
+same front-end) and compares within bf16 tolerances."""
+import math
+
+import pytest
+import torch
+
+from mindspeed_rl_b200 import ops
+from mindspeed_rl_b200.ops import QKVLayout
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def close(a, b, atol, rtol, what=""):
+    a, b = a.detach().float().cpu(), b.detach().float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"{what}: max err {err.max().item():.4g} (ref max {b.abs().max().item():.4g})"
+
+
+@pytest.mark.parametrize("rows,h", [(37, 3584), (5, 4096), (300, 256), (9, 5120)])
+def test_rmsnorm_fwd_bwd(rows, h):
+    torch.manual_seed(0)
+    x = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(h, device=DEV)).bfloat16()
+    y, rstd, s = ops.rmsnorm_fwd(x, w, 1e-6, residual=res)
+    yr, rstdr, sr = ops.rmsnorm_fwd(x.cpu(), w.cpu(), 1e-6, residual=res.cpu())
+    close(s, sr, 1e-2, 1e-2, "sum")
+    close(y, yr, 2e-2, 2e-2, "y")
+    close(rstd, rstdr, 1e-3, 1e-2, "rstd")
+    dy = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16)
+    dres = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16)
+    dw = torch.zeros(h, device=DEV, dtype=torch.float32)
+    dx = ops.rmsnorm_bwd(dy, s, w, rstd, dw, dres=dres)
+    dwr = torch.zeros(h, dtype=torch.float32)
+    dxr = ops.rmsnorm_bwd(dy.cpu(), s.cpu(), w.cpu(), rstd.cpu(), dwr, dres=dres.cpu())
+    close(dx, dxr, 3e-2, 3e-2, "dx")
+    close(dw, dwr, 5e-2 * math.sqrt(rows), 2e-2, "dw")
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_headnorm_and_rope(interleaved):
+    torch.manual_seed(1)
+    lay = QKVLayout(8, 2, 128, interleaved)
+    t = 53
+    qkv = torch.randn(t, lay.width, device=DEV, dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(128, device=DEV)).bfloat16()
+    pos = torch.randint(0, 4000, (t,), device=DEV, dtype=torch.int32)
+    tab = ops.rope_table(4096, 128, 1e6, DEV)
+    a, b = qkv.clone(), qkv.cpu().clone()
+    for which in ("q", "k"):
+        r1 = ops.headnorm_fwd_(a, lay, which, w, 1e-6)
+        r2 = ops.headnorm_fwd_(b, lay, which, w.cpu(), 1e-6)
+        close(r1, r2, 1e-3, 1e-2, "rstd " + which)
+    close(a, b, 3e-2, 2e-2, "headnorm")
+    ops.rope_(a, lay, pos, tab)
+    ops.rope_(b, lay, pos.cpu(), tab.cpu())
+    close(a, b, 4e-2, 2e-2, "rope")
+    # inverse rotation restores the input up to bf16 rounding
+    c = a.clone()
+    ops.rope_(c, lay, pos, tab, inverse=True)
+    ref = qkv.clone()
+    for which in ("q", "k"):
+        ops.headnorm_fwd_(ref, lay, which, w, 1e-6)
+    close(c, ref, 6e-2, 3e-2, "rope inverse")
+    # head-norm backward
+    dq = torch.randn(t, lay.width, device=DEV, dtype=torch.bfloat16)
+    dqc = dq.cpu().clone()
+    rs = ops.headnorm_fwd_(qkv.clone(), lay, "q", w, 1e-6)
+    dw = torch.zeros(128, device=DEV)
+    dwr = torch.zeros(128)
+    ops.headnorm_bwd_(dq, qkv, lay, "q", w, rs, dw)
+    ops.headnorm_bwd_(dqc, qkv.cpu(), lay, "q", w.cpu(), rs.cpu(), dwr)
+    close(dq, dqc, 3e-2, 3e-2, "headnorm dx")
+    close(dw, dwr, 0.3, 3e-2, "headnorm dw")
+
+
+def test_swiglu_and_colsum():
+    torch.manual_seed(2)
+    x = torch.randn(77, 2 * 1536, device=DEV, dtype=torch.bfloat16)
+    y = ops.swiglu_fwd(x)
+    close(y, ops.swiglu_fwd(x.cpu()), 2e-2, 2e-2, "swiglu")
+    dy = torch.randn(77, 1536, device=DEV, dtype=torch.bfloat16)
+    close(ops.swiglu_bwd(x, dy), ops.swiglu_bwd(x.cpu(), dy.cpu()), 3e-2, 2e-2, "swiglu bwd")
+    out = torch.zeros(3072, device=DEV)
+    ops.colsum_accumulate(x, out)
+    close(out, x.float().sum(0), 1e-2, 1e-3, "colsum")
+    a, b = torch.randn(4096, device=DEV).bfloat16(), torch.randn(4096, device=DEV).bfloat16()
+    close(ops.add(a, b), a.float() + b.float(), 2e-2, 1e-2, "add")
+
+
+@pytest.mark.parametrize("hd,nh,nkv,interleaved", [(128, 4, 2, True), (64, 4, 4, False), (128, 7, 1, True)])
+def test_flash_attention_varlen(hd, nh, nkv, interleaved):
+    torch.manual_seed(3)
+    lay = QKVLayout(nh, nkv, hd, interleaved)
+    lens = [1, 70, 130, 64, 257]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    t = int(cu[-1])
+    qkv = (0.5 * torch.randn(t, lay.width, device=DEV)).bfloat16()
+    out, lse = ops.attn_varlen_fwd(qkv, lay, cu.to(DEV), max(lens))
+    outr, lser = ops.attn_varlen_fwd(qkv.cpu(), lay, cu, max(lens))
+    close(out, outr, 2e-2, 2e-2, "attn out")
+    close(lse, lser, 2e-2, 1e-2, "lse")
+    dout = (0.5 * torch.randn(t, nh * hd, device=DEV)).bfloat16()
+    dqkv = ops.attn_varlen_bwd(dout, qkv, out, lse, lay, cu.to(DEV), max(lens))
+    dqkvr = ops.attn_varlen_bwd(dout.cpu(), qkv.cpu(), outr, lser, lay, cu, max(lens))
+    close(dqkv, dqkvr, 3e-2, 5e-2, "dqkv")
+
+
+def test_flash_attention_prefix():
+    torch.manual_seed(4)
+    lay = QKVLayout(4, 2, 128, False)
+    qlens, klens = [5, 64, 1], [40, 200, 65]
+    cu_q = torch.tensor([0, 5, 69, 70], dtype=torch.int32)
+    cu_k = torch.tensor([0, 40, 240, 305], dtype=torch.int32)
+    qkv = (0.5 * torch.randn(70, lay.width, device=DEV)).bfloat16()
+    k = (0.5 * torch.randn(305, 2, 128, device=DEV)).bfloat16()
+    v = (0.5 * torch.randn(305, 2, 128, device=DEV)).bfloat16()
+    out, _ = ops.attn_varlen_fwd(qkv, lay, cu_q.to(DEV), 64, kv=(k, v), cu_seqlens_k=cu_k.to(DEV))
+    outr, _ = ops.attn_varlen_fwd(qkv.cpu(), lay, cu_q, 64, kv=(k.cpu(), v.cpu()), cu_seqlens_k=cu_k)
+    close(out, outr, 2e-2, 2e-2, "prefix attention")
+
+
+@pytest.mark.parametrize("nh,nkv,hd,bs", [(28, 4, 128, 16), (8, 8, 64, 8), (16, 1, 128, 16)])
+def test_paged_decode_and_cache(nh, nkv, hd, bs):
+    torch.manual_seed(5)
+    lay = QKVLayout(nh, nkv, hd, True)
+    lens = [1, 17, 300, 1025, 64]
+    b = len(lens)
+    nblocks = sum((n + bs - 1) // bs for n in lens) + 3
+    kc = torch.zeros(nblocks, bs, nkv, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    perm = torch.randperm(nblocks).tolist()
+    maxb = max((n + bs - 1) // bs for n in lens)
+    bt = torch.zeros(b, maxb, dtype=torch.int32)
+    cur = 0
+    for i, n in enumerate(lens):
+        nb = (n + bs - 1) // bs
+        bt[i, :nb] = torch.tensor(perm[cur:cur + nb], dtype=torch.int32)
+        cur += nb
+    # fill the cache through the write kernel, sequence by sequence
+    for i, n in enumerate(lens):
+        x = (0.5 * torch.randn(n, lay.width, device=DEV)).bfloat16()
+        pos = torch.arange(n)
+        slots = (bt[i, (pos // bs)].long() * bs + pos % bs).to(DEV)
+        ops.kv_cache_write(x, lay, slots, kc, vc)
+    kcr, vcr = kc.cpu(), vc.cpu()
+    q = (0.5 * torch.randn(b, lay.width, device=DEV)).bfloat16()
+    ctx = torch.tensor(lens, dtype=torch.int32)
+    out = ops.paged_decode_attention(q, lay, kc, vc, bt.to(DEV), ctx.to(DEV), max(lens))
+    outr = ops.paged_decode_attention(q.cpu(), lay, kcr, vcr, bt, ctx, max(lens))
+    close(out, outr, 2e-2, 2e-2, "paged decode")
+    # gather
+    tok_seq = torch.tensor([2] * 300 + [4] * 64, dtype=torch.int32)
+    tok_pos = torch.tensor(list(range(300)) + list(range(64)), dtype=torch.int32)
+    kg, vg = ops.kv_cache_gather(kc, vc, bt.to(DEV), tok_seq.to(DEV), tok_pos.to(DEV))
+    kgr, vgr = ops.kv_cache_gather(kcr, vcr, bt, tok_seq, tok_pos)
+    assert torch.equal(kg.cpu(), kgr) and torch.equal(vg.cpu(), vgr)
+
+
+def test_lmhead_logprob_fwd_bwd():
+    torch.manual_seed(6)
+    t, h, v = 300, 256, 5000
+    x = (torch.randn(t, h, device=DEV)).bfloat16()
+    w = (0.05 * torch.randn(v, h, device=DEV)).bfloat16()
+    y = torch.randint(0, v, (t,), device=DEV)
+    logp, ent, lse = ops.lmhead_logprob_fwd(x, w, y, 1 / 0.7, chunk=128)
+    z = (x.float() @ w.float().t()) / 0.7
+    ls = torch.log_softmax(z, -1)
+    close(logp, ls.gather(-1, y[:, None])[:, 0], 3e-2, 1e-2, "logp")
+    close(ent, -(ls.exp() * ls).sum(-1), 3e-2, 1e-2, "entropy")
+    dlogp = torch.randn(t, device=DEV)
+    dent = 0.1 * torch.randn(t, device=DEV)
+    dw = torch.zeros_like(w)
+    dx = ops.lmhead_logprob_bwd(x, w, y, lse, ent, dlogp, dent, dw, 1 / 0.7, chunk=128)
+    xr = x.float().requires_grad_(True)
+    wr = w.float().requires_grad_(True)
+    zr = (xr @ wr.t()) / 0.7
+    lsr = torch.log_softmax(zr, -1)
+    ((lsr.gather(-1, y[:, None])[:, 0] * dlogp).sum() + (-(lsr.exp() * lsr).sum(-1) * dent).sum()).backward()
+    close(dx, xr.grad, 2e-2, 5e-2, "dx")
+    close(dw, wr.grad, 5e-2, 5e-2, "dw")
+
+
+def test_policy_value_loss_gae():
+    torch.manual_seed(7)
+    b, l = 64, 200
+    lp = -torch.rand(b, l, device=DEV) * 3
+    old = lp + 0.3 * torch.randn(b, l, device=DEV)
+    ref = lp + 0.3 * torch.randn(b, l, device=DEV)
+    adv = torch.randn(b, l, device=DEV)
+    mask = (torch.rand(b, l, device=DEV) > 0.3).float()
+    for kl in ("low_var_kl", "kl", "abs", "mse"):
+        for token_level in (True, False):
+            d, st = ops.policy_loss_fwd_bwd(lp, old, ref, adv, mask, 0.2, 0.28, 0.01, kl, token_level, 0.5)
+            dr, sr = ops.policy_loss_fwd_bwd(lp.cpu(), old.cpu(), ref.cpu(), adv.cpu(), mask.cpu(), 0.2, 0.28,
+                                             0.01, kl, token_level, 0.5)
+            close(d, dr, 1e-6, 1e-3, f"dlogp {kl}")
+            for k in ("pg_loss", "pg_clipfrac", "ppo_kl", "kl_loss"):
+                close(st[k], sr[k], 1e-4, 1e-3, f"{k} {kl} {token_level}")
+    v, vo, ret = torch.randn(b, l, device=DEV), torch.randn(b, l, device=DEV), torch.randn(b, l, device=DEV)
+    dv, st = ops.value_loss_fwd_bwd(v, vo, ret, mask, 0.5)
+    dvr, sr = ops.value_loss_fwd_bwd(v.cpu(), vo.cpu(), ret.cpu(), mask.cpu(), 0.5)
+    close(dv, dvr, 1e-6, 1e-3, "dv")
+    close(st["vf_loss"], sr["vf_loss"], 1e-4, 1e-3, "vf_loss")
+    r = torch.randn(b, l, device=DEV)
+    a1, r1 = ops.gae(r, v, mask, 0.99, 0.95)
+    a2, r2 = ops.gae(r.cpu(), v.cpu(), mask.cpu(), 0.99, 0.95)
+    close(a1, a2, 1e-3, 1e-3, "gae adv")
+    close(r1, r2, 1e-3, 1e-3, "gae ret")
+    sc = torch.randint(0, 2, (b,), device=DEV).float()
+    close(ops.group_norm_advantage(sc, mask, 8), ops.group_norm_advantage(sc.cpu(), mask.cpu(), 8),
+          1e-4, 1e-4, "group norm")
+
+
+def test_adam_and_norm():
+    torch.manual_seed(8)
+    n = 100_003
+    p = torch.randn(n, device=DEV)
+    g = (0.1 * torch.randn(n, device=DEV)).bfloat16()
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    p16 = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    pc, mc, vc = p.cpu().clone(), m.cpu().clone(), v.cpu().clone()
+    ss = torch.zeros(1, device=DEV)
+    ops.sumsq_accumulate(g, ss)
+    close(ss, g.float().pow(2).sum().reshape(1), 1e-2, 1e-3, "sumsq")
+    coef, norm = torch.ones(1, device=DEV), torch.zeros(1, device=DEV)
+    ops.clip_coefficient(ss, 1.0, 1.0, coef, norm)
+    close(norm, ss.sqrt(), 1e-3, 1e-4, "norm")
+    for step in (1, 2, 3):
+        ops.adamw_step(p, m, v, g, p16, 1e-3, 0.9, 0.95, 1e-8, 0.01, step, coef)
+        ops.adamw_step(pc, mc, vc, g.cpu(), None, 1e-3, 0.9, 0.95, 1e-8, 0.01, step, coef.cpu())
+    close(p, pc, 1e-5, 1e-4, "adam p")
+    close(p16, pc, 1e-2, 1e-2, "adam p16")
+
+
+def test_sampler_distribution_and_greedy():
+    torch.manual_seed(9)
+    b, v = 64, 2000
+    logits = 2 * torch.randn(b, v, device=DEV)
+    keys = torch.arange(b, device=DEV, dtype=torch.int64)
+    temp0 = torch.zeros(b, device=DEV)
+    tok, lp = ops.sample(logits, temp0, None, None, None, keys, 0)
+    assert torch.equal(tok, logits.argmax(-1))
+    close(lp, torch.log_softmax(logits, -1).gather(-1, tok[:, None])[:, 0], 1e-3, 1e-3, "greedy logprob")
+    # empirical distribution of one row under temperature 1
+    row = torch.tensor([2.0, 1.0, 0.0, -1.0] + [-30.0] * (v - 4), device=DEV)
+    n = 4000
+    tok, _ = ops.sample(row.expand(n, v).contiguous(), torch.ones(n, device=DEV), None, None, None,
+                        torch.arange(n, device=DEV, dtype=torch.int64), 123)
+    freq = torch.bincount(tok, minlength=v)[:4].float() / n
+    want = torch.softmax(row[:4], 0)
+    assert (freq.cpu() - want.cpu()).abs().max() < 0.03, (freq, want)
+    # top-k = 2 keeps only the two best tokens, top-p small keeps the best
+    tok, _ = ops.sample(row.expand(n, v).contiguous(), torch.ones(n, device=DEV),
+                        torch.full((n,), 2, device=DEV, dtype=torch.int32), None, None,
+                        torch.arange(n, device=DEV, dtype=torch.int64), 5)
+    assert int(tok.max()) <= 1
+    tok, _ = ops.sample(row.expand(n, v).contiguous(), torch.ones(n, device=DEV), None,
+                        torch.full((n,), 0.5, device=DEV), None,
+                        torch.arange(n, device=DEV, dtype=torch.int64), 5)
+    assert int(tok.max()) == 0
+    # forced EOS probability
+    tok, _ = ops.sample(row.expand(n, v).contiguous(), torch.ones(n, device=DEV), None, None, None,
+                        torch.arange(n, device=DEV, dtype=torch.int64), 7,
+                        eos_prob=torch.full((n,), 0.25, device=DEV), eos_id=1999)
+    assert abs(float((tok == 1999).float().mean()) - 0.25) < 0.03
