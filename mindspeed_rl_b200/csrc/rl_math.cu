@@ -32,15 +32,16 @@ __device__ __forceinline__ void kl_value_grad(int kind, float lp, float ref, flo
   }
 }
 
-// stats[0]=sum w_loss*pg  [1]=sum w_stat*clipped  [2]=sum w_stat*(old-lp)  [3]=sum w_loss*kl
-// dlogp = w_loss * (d pg/d lp + kl_coef * d kl/d lp)
+// stats[0]=sum w_loss*pg  [1]=sum w_stat*clipped  [2]=sum w_stat*(old-lp)  [3]=sum w_stat*kl
+// dlogp = w_loss * d pg/d lp + w_stat * kl_scale * kl_coef * d kl/d lp   (the KL term is always a
+// token mean; kl_scale carries the gradient-accumulation scale that w_loss already contains)
 // w_loss / w_stat already contain mask / normaliser (token-mean or seq-mean-token-mean).
 __global__ void policy_loss_kernel(const float* __restrict__ logp, const float* __restrict__ old_logp,
                                    const float* __restrict__ ref_logp, const float* __restrict__ adv,
                                    const float* __restrict__ w_loss, const float* __restrict__ w_stat,
                                    float* __restrict__ dlogp, float* __restrict__ stats,
                                    long long n, float ratio_lo, float ratio_hi, float kl_coef,
-                                   int kl_kind) {
+                                   float kl_scale, int kl_kind) {
   __shared__ float red[32];
   float s_pg = 0.f, s_clip = 0.f, s_kl_old = 0.f, s_kl = 0.f;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -69,8 +70,8 @@ __global__ void policy_loss_kernel(const float* __restrict__ logp, const float* 
       if (kl_kind != KL_NONE && ref_logp != nullptr) {
         float kv, kg;
         kl_value_grad(kl_kind, lp, ref_logp[i], kv, kg);
-        s_kl += wl * kv;
-        grad += wl * kl_coef * kg;
+        s_kl += ws * kv;
+        grad += ws * kl_scale * kl_coef * kg;
       }
     }
     dlogp[i] = grad;
@@ -170,14 +171,15 @@ using namespace msrl;
 MSRL_API int msrl_policy_loss(const float* logp, const float* old_logp, const float* ref_logp,
                               const float* adv, const float* w_loss, const float* w_stat,
                               float* dlogp, float* stats4, long long n, float ratio_lo,
-                              float ratio_hi, float kl_coef, int kl_kind, cudaStream_t st) {
+                              float ratio_hi, float kl_coef, float kl_scale, int kl_kind,
+                              cudaStream_t st) {
   cudaMemsetAsync(stats4, 0, 4 * sizeof(float), st);
   if (n == 0) return 0;
   long long blocks = ceil_div(n, 256);
   if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
   policy_loss_kernel<<<(unsigned)blocks, 256, 0, st>>>(logp, old_logp, ref_logp, adv, w_loss, w_stat,
                                                        dlogp, stats4, n, ratio_lo, ratio_hi,
-                                                       kl_coef, kl_kind);
+                                                       kl_coef, kl_scale, kl_kind);
   MSRL_LAUNCH_CHECK();
 }
 

@@ -84,12 +84,12 @@ def policy_loss_fwd_bwd(logp: torch.Tensor, old_logp: Optional[torch.Tensor],
                                            ptr(w_loss), ptr(w_stat), ptr(dlogp), ptr(st),
                                            c_ll(lp.numel()), c_float(1.0 - clip_low),
                                            c_float(1.0 + clip_high), c_float(kl_coef if use_kl else 0.0),
+                                           c_float(loss_scale),
                                            c_int(KL_KINDS[kl_penalty] if use_kl else 0), stream()),
               "policy_loss")
         pg = st[0] / loss_scale if loss_scale != 1.0 else st[0]
-        kl = st[3] / loss_scale if loss_scale != 1.0 else st[3]
-        stats = {"pg_loss": pg, "pg_clipfrac": st[1], "ppo_kl": st[2], "kl_loss": kl,
-                 "loss": st[0] + kl_coef * st[3]}
+        stats = {"pg_loss": pg, "pg_clipfrac": st[1], "ppo_kl": st[2], "kl_loss": st[3],
+                 "loss": st[0] + kl_coef * loss_scale * st[3]}
         return dlogp, stats
     with torch.enable_grad():
         x = logp.detach().float().requires_grad_(True)
