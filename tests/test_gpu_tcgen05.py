@@ -1,0 +1,44 @@
+"""tcgen05 / TMA GEMM and the fused LM-head statistics epilogue against PyTorch references."""
+import pytest
+import torch
+
+from mindspeed_rl_b200.ops import gemm as G
+from mindspeed_rl_b200.ops import _lib
+from mindspeed_rl_b200.ops._lib import c_int, c_ll, ptr, stream
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 520, 192), (1024, 3584, 3584), (77, 1000, 4096)])
+def test_gemm_bf16_tn(m, n, k):
+    torch.manual_seed(0)
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    b = (torch.randn(n, k, device=DEV) * 0.5).bfloat16()
+    c = G.gemm_bf16_tn(a, b)
+    G.check_status(DEV)
+    ref = a.float() @ b.float().t()
+    err = (c.float() - ref).abs()
+    tol = 2e-2 * ref.abs() + 0.25
+    assert bool((err <= tol).all()), f"max err {err.max().item()} ref max {ref.abs().max().item()}"
+
+
+@pytest.mark.parametrize("t,v,h", [(200, 1000, 256), (513, 5000, 896)])
+def test_lmhead_stats_fused(t, v, h):
+    torch.manual_seed(1)
+    x = torch.randn(t, h, device=DEV).bfloat16()
+    w = (0.05 * torch.randn(v, h, device=DEV)).bfloat16()
+    y = torch.randint(0, v, (t,), device=DEV)
+    stats, tiles = G.lmhead_stats(x, w, y, 1 / 0.7)
+    G.check_status(DEV)
+    logp = torch.empty(t, device=DEV)
+    ent = torch.empty(t, device=DEV)
+    lse = torch.empty(t, device=DEV)
+    L = _lib.load()
+    assert L.msrl_logprob_finish(ptr(stats), c_int(tiles), c_ll(t), ptr(logp), ptr(ent), ptr(lse), stream()) == 0
+    z = (x.float() @ w.float().t()).bfloat16().float() / 0.7
+    ls = torch.log_softmax(z, -1)
+    ref_lp = ls.gather(-1, y[:, None])[:, 0]
+    ref_ent = -(ls.exp() * ls).sum(-1)
+    assert (logp - ref_lp).abs().max() < 3e-2, (logp - ref_lp).abs().max()
+    assert (ent - ref_ent).abs().max() < 3e-2, (ent - ref_ent).abs().max()
