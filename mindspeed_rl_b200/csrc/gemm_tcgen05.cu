@@ -28,7 +28,7 @@ constexpr int G_BM = 128, G_BN = 256, G_BK = 64, G_STAGES = 4;
 constexpr uint32_t G_SMEM_A = G_BM * G_BK * 2;   // 16 KiB
 constexpr uint32_t G_SMEM_B = G_BN * G_BK * 2;   // 32 KiB
 constexpr uint32_t G_STAGE_BYTES = G_SMEM_A + G_SMEM_B;
-constexpr uint32_t G_TMEM_COLS = 256;
+constexpr uint32_t G_TMEM_COLS = 512;           // two 128x256 fp32 accumulators
 constexpr long long G_WAIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
 
 enum GemmError { GEMM_OK = 0, GEMM_TIMEOUT_FULL = 1, GEMM_TIMEOUT_EMPTY = 2, GEMM_TIMEOUT_ACC = 3 };
@@ -44,6 +44,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -152,14 +155,18 @@ template <int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
+  // Persistent: each CTA walks tiles blockIdx.x, +gridDim.x, ... (M-tiles fastest so that CTAs
+  // running together share B tiles through L2).  The TMEM allocation holds two 128x256 fp32
+  // accumulators; the epilogue of tile i overlaps the main loop of tile i+1.
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t full_bar[G_STAGES], empty_bar[G_STAGES], acc_bar;
+  __shared__ uint64_t full_bar[G_STAGES], empty_bar[G_STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * G_BM, n0 = blockIdx.y * G_BN;
+  const int m_tiles = (p.M + G_BM - 1) / G_BM, n_tiles = (p.N + G_BN - 1) / G_BN;
+  const int total_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + G_BK - 1) / G_BK;
 
   if (threadIdx.x == 0) {
@@ -167,7 +174,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);   // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 5) {
@@ -184,45 +194,68 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 4) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % G_STAGES;
-        const uint32_t use = kb / G_STAGES;
-        if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, p.error, GEMM_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(&full_bar[s], G_STAGE_BYTES);
-        unsigned char* sa = smem + (size_t)s * G_STAGE_BYTES;
-        tma_load_2d(sa, &map_a, &full_bar[s], kb * G_BK, m0);
-        tma_load_2d(sa + G_SMEM_A, &map_b, &full_bar[s], kb * G_BK, n0);
+      uint32_t it = 0;  // k-blocks issued so far (ring position)
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * G_BM, n0 = (tile / m_tiles) * G_BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % G_STAGES;
+          const uint32_t use = it / G_STAGES;
+          if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, p.error, GEMM_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], G_STAGE_BYTES);
+          unsigned char* sa = smem + (size_t)s * G_STAGE_BYTES;
+          tma_load_2d(sa, &map_a, &full_bar[s], kb * G_BK, m0);
+          tma_load_2d(sa + G_SMEM_A, &map_b, &full_bar[s], kb * G_BK, n0);
+        }
       }
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(G_BM, G_BN);
+      uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % G_STAGES;
-        ok = mbar_wait(&full_bar[s], (kb / G_STAGES) & 1, p.error, GEMM_TIMEOUT_FULL);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t a_addr = smem_u32(smem + (size_t)s * G_STAGE_BYTES);
-        const uint32_t b_addr = a_addr + G_SMEM_A;
-#pragma unroll
-        for (int k = 0; k < G_BK / 16; ++k) {
-          umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
-                    (kb > 0 || k > 0) ? 1u : 0u);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t buf = local & 1;
+        if (local >= 2) {  // the epilogue must have drained this accumulator
+          ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, p.error, GEMM_TIMEOUT_ACC);
+          if (!ok) break;
+          tcgen05_fence_after();
         }
-        tcgen05_commit(&empty_bar[s]);  // slot reusable once these MMAs have read it
+        const uint32_t tmem_acc = tmem_base + buf * G_BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % G_STAGES;
+          ok = mbar_wait(&full_bar[s], (it / G_STAGES) & 1, p.error, GEMM_TIMEOUT_FULL);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * G_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + G_SMEM_A;
+#pragma unroll
+          for (int k = 0; k < G_BK / 16; ++k) {
+            umma_bf16(tmem_acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&empty_bar[s]);  // slot reusable once these MMAs have read it
+        }
+        tcgen05_commit(&acc_full[buf]);   // accumulator complete (or abandoned)
       }
-      tcgen05_commit(&acc_bar);         // accumulator complete (or abandoned)
     }
   } else {
     // ---------------- epilogue: warp w owns TMEM lanes / rows 32w .. 32w+31 ----------------
-    const bool ok = mbar_wait(&acc_bar, 0, p.error, GEMM_TIMEOUT_ACC) &&
-                    (*reinterpret_cast<volatile int*>(p.error) == 0);
-    tcgen05_fence_after();
-    const int row = m0 + warp * 32 + lane;
-    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
-    if (ok) {
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      const uint32_t buf = local & 1;
+      const int m0 = (tile % m_tiles) * G_BM, n0 = (tile / m_tiles) * G_BN;
+      ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, GEMM_TIMEOUT_ACC) &&
+           (*reinterpret_cast<volatile int*>(p.error) == 0);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = m0 + warp * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * G_BN;
       if (EPI == EPI_STORE) {
 #pragma unroll 1
         for (int c = 0; c < G_BN / 32; ++c) {
@@ -278,9 +311,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         if (row < p.M) {
           RowStat4 o{mx, s, zy, spz};
-          p.stats[(long long)blockIdx.y * p.M + row] = o;
+          p.stats[(long long)(tile / m_tiles) * p.M + row] = o;
         }
       }
+      // hand the accumulator back to the MMA warp
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   tcgen05_fence_before();
@@ -329,7 +366,8 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((p.M + G_BM - 1) / G_BM, (p.N + G_BN - 1) / G_BN);
+  const int tiles = ((p.M + G_BM - 1) / G_BM) * ((p.N + G_BN - 1) / G_BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_tcgen05_kernel<EPI><<<grid, 192, smem, st>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }

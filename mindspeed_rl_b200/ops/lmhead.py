@@ -16,10 +16,15 @@ from typing import Optional, Tuple
 import torch
 import torch.distributed as dist
 
+import os
+
 from . import _lib
+from . import gemm as _gemm
 from ._lib import c_float, c_int, c_ll, check, ptr, stream
 
 DEFAULT_CHUNK = 4096
+# MSRL_LMHEAD_TCGEN05=0 selects the chunked cuBLAS + row-kernel formulation (the baseline path)
+USE_TCGEN05 = os.environ.get("MSRL_LMHEAD_TCGEN05", "1") != "0"
 
 
 def _world(group) -> int:
@@ -52,6 +57,20 @@ def lmhead_logprob_fwd(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, i
     labels = labels.to(torch.int64).contiguous()
     if _lib.use_kernels(h, w, labels) and h.dtype == torch.bfloat16:
         L = _lib.load()
+        if USE_TCGEN05 and _gemm.tcgen05_usable(h, w):
+            # fused path: tcgen05 GEMM whose epilogue reduces each 256-column tile to a 16-byte
+            # record per row; the [T, V] logits are never written
+            stats, tiles = _gemm.lmhead_stats(h, w, labels, inv_temp, vocab_offset)
+            if _world(group) > 1:
+                m = stats[..., 0].max(dim=0).values
+                c = torch.exp(stats[..., 0] - m)
+                local = torch.stack([m, (stats[..., 1] * c).sum(0), stats[..., 2].sum(0),
+                                     (stats[..., 3] * c).sum(0)], dim=-1).contiguous()
+                stats, tiles = _combine_stats(local, group)
+            check(L.msrl_logprob_finish(ptr(stats), c_int(tiles), c_ll(t), ptr(logp),
+                                        ptr(ent) if ent is not None else None, ptr(lse), stream()),
+                  "logprob_finish")
+            return logp, ent, lse
         for s in range(0, t, chunk):
             e = min(t, s + chunk)
             z = torch.matmul(h[s:e], w.t())                      # [c, V] bf16

@@ -1,0 +1,185 @@
+"""Kernel micro-benchmarks: CUDA-event timings and roofline fractions of the hand-written kernels.
+
+    python -m mindspeed_rl_b200.ops.microbench [--only NAME[,NAME..]] [--small] [--iters N]
+
+Each case reports the time per call (median of ``iters`` after warm-up; the L2 is flushed between
+timed calls by writing a 256 MiB buffer), the achieved bandwidth or FLOP rate, and the fraction of
+the measured machine peaks (``MEASURED_PEAKS.json`` at the repository root when present, else the
+documented fallback of 6.65 TB/s and 1.59 PFLOP/s).  ``--small`` shrinks every case to a few
+launches on a few hundred MB -- the size meant for profiler captures.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+from typing import Callable, Dict
+
+import torch
+
+from . import QKVLayout
+from . import (adamw_step, attn_varlen_bwd, attn_varlen_fwd, lmhead_logprob_fwd, paged_decode_attention,
+               rmsnorm_bwd, rmsnorm_fwd, sample, swiglu_fwd)
+from . import gemm as G
+from . import lmhead as LM
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), "..", ".."))
+
+
+def peaks() -> Dict[str, float]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+
+
+_flush = None
+
+
+def timeit(fn: Callable[[], None], iters: int, warmup: int = 3) -> float:
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        _flush.zero_()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def report(name: str, ms: float, bytes_: float = 0.0, flops: float = 0.0, note: str = "") -> dict:
+    pk = peaks()
+    out = {"case": name, "ms": round(ms, 4)}
+    if bytes_:
+        gbs = bytes_ / ms / 1e6
+        out.update(gbs=round(gbs, 1), frac_hbm=round(gbs / pk["hbm_gbs"], 3))
+    if flops:
+        tf = flops / ms / 1e9
+        out.update(tflops=round(tf, 1), frac_tensor=round(tf / pk["tflops"], 3))
+    out["of"] = pk["source"]
+    if note:
+        out["note"] = note
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def case_gemm(small: bool, iters: int):
+    shapes = [(4096, 4608, 3584), (4096, 37888, 3584), (4096, 3584, 18944)] if not small else [(1024, 2048, 1024)]
+    for m, n, k in shapes:
+        a = torch.randn(m, k, device="cuda").bfloat16()
+        b = torch.randn(n, k, device="cuda").bfloat16()
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: G.gemm_bf16_tn(a, b, out), iters)
+        report(f"gemm_tcgen05 {m}x{n}x{k}", ms, flops=2.0 * m * n * k)
+        ms = timeit(lambda: torch.matmul(a, b.t(), out=out), iters)
+        report(f"gemm_cublas  {m}x{n}x{k}", ms, flops=2.0 * m * n * k, note="library baseline")
+    G.check_status("cuda")
+
+
+def case_lmhead(small: bool, iters: int):
+    t, h, v = (8192, 3584, 152064) if not small else (1024, 1024, 16384)
+    x = torch.randn(t, h, device="cuda").bfloat16()
+    w = (0.02 * torch.randn(v, h, device="cuda")).bfloat16()
+    y = torch.randint(0, v, (t,), device="cuda")
+    fl = 2.0 * t * h * v
+    LM.USE_TCGEN05 = True
+    ms = timeit(lambda: lmhead_logprob_fwd(x, w, y, 1.0), iters)
+    report(f"lmhead_logprob fused tcgen05 T={t} V={v}", ms, flops=fl)
+    LM.USE_TCGEN05 = False
+    ms = timeit(lambda: lmhead_logprob_fwd(x, w, y, 1.0), iters)
+    report(f"lmhead_logprob chunked cublas T={t} V={v}", ms, flops=fl, note="baseline (logits via HBM)")
+    LM.USE_TCGEN05 = True
+    G.check_status("cuda")
+
+
+def case_attention(small: bool, iters: int):
+    nh, nkv, hd = 28, 4, 128
+    lay = QKVLayout(nh, nkv, hd, True)
+    lens = [2048] * (8 if not small else 2)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    t = sum(lens)
+    qkv = (0.5 * torch.randn(t, lay.width, device="cuda")).bfloat16()
+    fl = sum(4.0 * l * l * nh * hd / 2 for l in lens)
+    out, lse = attn_varlen_fwd(qkv, lay, cu, max(lens))
+    ms = timeit(lambda: attn_varlen_fwd(qkv, lay, cu, max(lens)), iters)
+    report(f"flash_attn_varlen fwd T={t}", ms, flops=fl)
+    do = torch.randn_like(out)
+    ms = timeit(lambda: attn_varlen_bwd(do, qkv, out, lse, lay, cu, max(lens)), iters)
+    report(f"flash_attn_varlen bwd T={t}", ms, flops=2.5 * fl)
+
+
+def case_decode(small: bool, iters: int):
+    nh, nkv, hd, bs = 28, 4, 128, 16
+    lay = QKVLayout(nh, nkv, hd, True)
+    b, ctx = (256, 2048) if not small else (32, 1024)
+    nblk = b * ctx // bs
+    kc = torch.randn(nblk, bs, nkv, hd, device="cuda").bfloat16()
+    vc = torch.randn(nblk, bs, nkv, hd, device="cuda").bfloat16()
+    bt = torch.randperm(nblk, device="cuda").to(torch.int32).view(b, ctx // bs)
+    cl = torch.full((b,), ctx, dtype=torch.int32, device="cuda")
+    q = torch.randn(b, lay.width, device="cuda").bfloat16()
+    ms = timeit(lambda: paged_decode_attention(q, lay, kc, vc, bt, cl, ctx), iters)
+    report(f"paged_decode B={b} ctx={ctx}", ms, bytes_=2.0 * b * ctx * nkv * hd * 2)
+
+
+def case_elementwise(small: bool, iters: int):
+    rows, h, f = (16384, 3584, 18944) if not small else (4096, 3584, 4096)
+    x = torch.randn(rows, h, device="cuda").bfloat16()
+    w = torch.ones(h, device="cuda").bfloat16()
+    ms = timeit(lambda: rmsnorm_fwd(x, w, 1e-6), iters)
+    report(f"rmsnorm fwd {rows}x{h}", ms, bytes_=2.0 * rows * h * 2)
+    y, rstd, _ = rmsnorm_fwd(x, w, 1e-6)
+    dw = torch.zeros(h, device="cuda")
+    ms = timeit(lambda: rmsnorm_bwd(x, x, w, rstd, dw), iters)
+    report(f"rmsnorm bwd {rows}x{h}", ms, bytes_=3.0 * rows * h * 2)
+    gu = torch.randn(rows, 2 * f, device="cuda").bfloat16()
+    ms = timeit(lambda: swiglu_fwd(gu), iters)
+    report(f"swiglu fwd {rows}x{f}", ms, bytes_=3.0 * rows * f * 2)
+
+
+def case_adam(small: bool, iters: int):
+    n = (1 << 30) // 4 if not small else (1 << 26)
+    p = torch.randn(n, device="cuda")
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    g = torch.randn(n, device="cuda").bfloat16()
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: adamw_step(p, m, v, g, p16, 1e-6, 0.9, 0.95, 1e-8, 0.01, 1), iters)
+    report(f"adamw n={n}", ms, bytes_=n * (3 * 4 * 2 + 2 + 2))
+
+
+def case_sampler(small: bool, iters: int):
+    b, v = (256, 152064) if not small else (64, 32768)
+    logits = torch.randn(b, v, device="cuda").bfloat16()
+    t = torch.ones(b, device="cuda")
+    keys = torch.arange(b, device="cuda", dtype=torch.int64)
+    ms = timeit(lambda: sample(logits, t, None, None, None, keys, 0), iters)
+    report(f"sampler B={b} V={v}", ms, bytes_=2.0 * b * v * 2, note="two passes over the logits")
+
+
+CASES = {"gemm": case_gemm, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
+         "elementwise": case_elementwise, "adam": case_adam, "sampler": case_sampler}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    names = [n for n in args.only.split(",") if n] or list(CASES)
+    for n in names:
+        CASES[n](args.small, args.iters)
+
+
+if __name__ == "__main__":
+    main()
