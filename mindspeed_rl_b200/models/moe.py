@@ -1,0 +1,302 @@
+"""Mixture-of-experts MLP block (Qwen3-MoE / DeepSeek style) with expert parallelism.
+
+``tokens -> router (softmax | sigmoid, top-k, optional group-limited routing, renormalisation)
+-> dispatch (permute by expert; all-to-all over the EP group) -> grouped expert GEMMs
+(w1 -> SwiGLU -> w2) -> combine (weighted un-permute; all-to-all back) [+ shared experts]``
+
+Parameter layout follows Megatron's ``GroupedMLP``: ``experts.weight1 [H, E_local * 2 * F]`` (per
+expert ``[gate | up]`` columns), ``experts.weight2 [E_local * F, H]``, ``router.weight [E, H]``.
+The experts' forward/backward is written by hand (like the dense layer); only the tiny router
+graph ``[T, E]`` goes through autograd so that the load-balancing auxiliary loss and the
+probability gradients need no hand derivation.
+
+Reference behaviour: flags ``moe_grouped_gemm``, ``moe_token_dispatcher_type: alltoall_seq``,
+``moe_router_topk``, ``norm_topk_prob``, ``moe_aux_loss_coeff`` (``configs/model/qwen3_30b_a3b.yaml``)
+and the rollout-side routing in ``models/rollout/vllm_adapter/fused_moe.py:230-503``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..parallel.state import get_parallel_state
+
+
+def _normal(shape, std, dtype, device, gen):
+    t = torch.empty(shape, dtype=torch.float32, device=device)
+    t.normal_(0.0, std, generator=gen)
+    return t.to(dtype)
+
+
+class _W(nn.Module):
+    def __init__(self, weight: torch.Tensor):
+        super().__init__()
+        self.weight = nn.Parameter(weight)
+
+
+class _Experts(nn.Module):
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor):
+        super().__init__()
+        self.weight1 = nn.Parameter(w1)
+        self.weight2 = nn.Parameter(w2)
+
+
+def route(logits: torch.Tensor, cfg) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Router logits ``[T, E]`` (fp32) -> ``(top-k probabilities [T, k], expert ids [T, k], full
+    score matrix [T, E])``; differentiable w.r.t. ``logits``."""
+    k = cfg.moe_router_topk
+    if cfg.moe_router_score_function == "sigmoid":
+        scores = torch.sigmoid(logits)
+    else:
+        scores = torch.softmax(logits, dim=-1)
+    pick = scores
+    if cfg.moe_router_num_groups and cfg.moe_router_group_topk:
+        t, e = scores.shape
+        g = cfg.moe_router_num_groups
+        grouped = scores.view(t, g, e // g)
+        group_score = grouped.topk(min(2, e // g), dim=-1).values.sum(-1)
+        keep = group_score.topk(cfg.moe_router_group_topk, dim=-1).indices
+        mask = torch.zeros(t, g, dtype=torch.bool, device=scores.device).scatter_(1, keep, True)
+        pick = scores.masked_fill(~mask.unsqueeze(-1).expand(t, g, e // g).reshape(t, e), float("-inf"))
+    top_idx = pick.topk(k, dim=-1).indices
+    top_p = scores.gather(-1, top_idx)
+    if cfg.norm_topk_prob:
+        top_p = top_p / (top_p.sum(-1, keepdim=True) + 1e-20)
+    if cfg.moe_router_topk_scaling_factor:
+        top_p = top_p * cfg.moe_router_topk_scaling_factor
+    return top_p, top_idx, scores
+
+
+def aux_loss(scores: torch.Tensor, top_idx: torch.Tensor, num_experts: int, topk: int, coeff: float) -> torch.Tensor:
+    """Switch-style load balancing: ``coeff * E * sum_e f_e * P_e``."""
+    t = scores.shape[0]
+    counts = torch.zeros(num_experts, device=scores.device, dtype=scores.dtype)
+    counts.scatter_add_(0, top_idx.reshape(-1), torch.ones(top_idx.numel(), device=scores.device, dtype=scores.dtype))
+    f = counts / max(t * topk, 1)
+    p = scores.mean(dim=0)
+    return coeff * num_experts * (f * p).sum()
+
+
+class MoELayer(nn.Module):
+    def __init__(self, cfg, device, gen):
+        super().__init__()
+        self.cfg = cfg
+        ps = get_parallel_state()
+        self.ep_group = ps.group("ep")
+        self.ep_size = ps.size("ep")
+        self.ep_rank = ps.rank_in("ep")
+        e, h, f = cfg.num_experts, cfg.hidden_size, cfg.moe_ffn_hidden_size
+        if e % self.ep_size:
+            raise ValueError("num_experts must be divisible by the expert-parallel size")
+        self.num_local = e // self.ep_size
+        dt, std = cfg.params_dtype, cfg.init_method_std
+        out_std = std / math.sqrt(2.0 * cfg.num_layers)
+        self.router = _W(_normal((e, h), std, torch.float32, device, gen))
+        self.experts = _Experts(_normal((h, self.num_local * 2 * f), std, dt, device, gen),
+                                _normal((self.num_local * f, h), out_std, dt, device, gen))
+        self.shared_experts = None
+        if cfg.n_shared_experts:
+            from .gpt import MLP
+
+            self.shared_experts = MLP(cfg, device, gen, ffn=f * cfg.n_shared_experts)
+        self.last_aux_loss: Optional[torch.Tensor] = None
+        self.token_counts: Optional[torch.Tensor] = None   # per-expert routed tokens (EPLB statistics)
+
+    # ------------------------------------------------------------------------------------------
+    def _w1(self) -> torch.Tensor:
+        c = self.cfg
+        return self.experts.weight1.view(c.hidden_size, self.num_local, 2 * c.moe_ffn_hidden_size)
+
+    def _w2(self) -> torch.Tensor:
+        c = self.cfg
+        return self.experts.weight2.view(self.num_local, c.moe_ffn_hidden_size, c.hidden_size)
+
+    def _exchange(self, x: torch.Tensor, send_counts: List[int], recv_counts: List[int]) -> torch.Tensor:
+        out = torch.empty(sum(recv_counts), *x.shape[1:], device=x.device, dtype=x.dtype)
+        dist.all_to_all_single(out, x.contiguous(), recv_counts, send_counts, group=self.ep_group)
+        return out
+
+    def _dispatch(self, x: torch.Tensor, top_idx: torch.Tensor):
+        """Permute ``x`` rows into expert order (global experts), exchange over EP.
+
+        Returns ``(xp_local, plan)`` where ``xp_local`` rows are grouped by local expert."""
+        t, k = top_idx.shape
+        e = self.cfg.num_experts
+        flat = top_idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)                 # slots sorted by global expert
+        token_of = order // k
+        xp = x[token_of]
+        counts = torch.bincount(flat, minlength=e)
+        plan: Dict[str, Any] = dict(order=order, token_of=token_of, t=t, k=k)
+        if self.ep_size == 1:
+            plan["local_counts"] = counts.tolist()
+            return xp, plan
+        # counts exchange: row r of `recv` = tokens rank r sends to each of my local experts
+        send = counts.view(self.ep_size, self.num_local)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send.contiguous(), group=self.ep_group)
+        send_rows, recv_rows = send.sum(1).tolist(), recv.sum(1).tolist()
+        got = self._exchange(xp, send_rows, recv_rows)          # grouped by (source rank, local expert)
+        # regroup to (local expert, source rank)
+        recv_l = recv.tolist()
+        seg_starts, s = [], 0
+        for r in range(self.ep_size):
+            row = []
+            for j in range(self.num_local):
+                row.append(s)
+                s += recv_l[r][j]
+            seg_starts.append(row)
+        idx = []
+        for j in range(self.num_local):
+            for r in range(self.ep_size):
+                n = recv_l[r][j]
+                if n:
+                    idx.append(torch.arange(seg_starts[r][j], seg_starts[r][j] + n, device=x.device))
+        perm = torch.cat(idx) if idx else torch.zeros(0, dtype=torch.long, device=x.device)
+        plan.update(send_rows=send_rows, recv_rows=recv_rows, perm=perm,
+                    local_counts=[sum(recv_l[r][j] for r in range(self.ep_size)) for j in range(self.num_local)])
+        return got[perm], plan
+
+    def _undispatch(self, y_local: torch.Tensor, plan) -> torch.Tensor:
+        """Inverse of :meth:`_dispatch` for expert outputs (rows back in sorted-slot order)."""
+        if self.ep_size == 1:
+            return y_local
+        back = torch.empty_like(y_local)
+        back[plan["perm"]] = y_local
+        return self._exchange(back, plan["recv_rows"], plan["send_rows"])
+
+    def _redispatch(self, d_sorted: torch.Tensor, plan) -> torch.Tensor:
+        """Send gradients w.r.t. expert outputs along the dispatch route."""
+        if self.ep_size == 1:
+            return d_sorted
+        got = self._exchange(d_sorted, plan["send_rows"], plan["recv_rows"])
+        return got[plan["perm"]]
+
+    # ------------------------------------------------------------------------------------------
+    def _experts_fwd(self, xp: torch.Tensor, counts: List[int], keep: bool):
+        w1, w2 = self._w1(), self._w2()
+        y = torch.empty(xp.shape[0], self.cfg.hidden_size, device=xp.device, dtype=xp.dtype)
+        gus, acts = [], []
+        s = 0
+        for j, n in enumerate(counts):
+            if n == 0:
+                gus.append(None)
+                acts.append(None)
+                continue
+            gu = torch.matmul(xp[s:s + n], w1[:, j])
+            act = ops.swiglu_fwd(gu)
+            torch.matmul(act, w2[j], out=y[s:s + n])
+            gus.append(gu if keep else None)
+            acts.append(act if keep else None)
+            s += n
+        return y, gus, acts
+
+    def _experts_bwd(self, xp, counts, gus, acts, dy) -> torch.Tensor:
+        from .gpt import grad_buffer
+
+        w1, w2 = self._w1(), self._w2()
+        c = self.cfg
+        train = self.experts.weight1.requires_grad
+        g1 = grad_buffer(self.experts.weight1).view(c.hidden_size, self.num_local, 2 * c.moe_ffn_hidden_size) \
+            if train else None
+        g2 = grad_buffer(self.experts.weight2).view(self.num_local, c.moe_ffn_hidden_size, c.hidden_size) \
+            if train else None
+        dxp = torch.zeros_like(xp)
+        s = 0
+        for j, n in enumerate(counts):
+            if n == 0:
+                continue
+            d = dy[s:s + n]
+            dact = torch.matmul(d, w2[j].t())
+            dgu = ops.swiglu_bwd(gus[j], dact)
+            torch.matmul(dgu, w1[:, j].t(), out=dxp[s:s + n])
+            if train:
+                g2[j].add_(torch.matmul(acts[j].t(), d).to(g2.dtype))
+                g1[:, j].add_(torch.matmul(xp[s:s + n].t(), dgu).to(g1.dtype))
+            s += n
+        return dxp
+
+    # ------------------------------------------------------------------------------------------
+    def forward_tokens(self, x: torch.Tensor, comm, keep: bool):
+        """``x [T, H]`` (full sequence on this rank) -> ``(out [T, H], ctx)``."""
+        cfg = self.cfg
+        t = x.shape[0]
+        with torch.enable_grad():
+            xr = x.detach().float().requires_grad_(keep)
+            logits = torch.matmul(xr, self.router.weight.t())
+            top_p, top_idx, scores = route(logits, cfg)
+            aux = aux_loss(scores, top_idx, cfg.num_experts, cfg.moe_router_topk, cfg.moe_aux_loss_coeff) \
+                if (keep and cfg.moe_aux_loss_coeff) else None
+        self.last_aux_loss = aux.detach() if aux is not None else None
+        self.token_counts = torch.bincount(top_idx.reshape(-1), minlength=cfg.num_experts)
+        xp, plan = self._dispatch(x, top_idx)
+        y_local, gus, acts = self._experts_fwd(xp, plan["local_counts"], keep)
+        y_sorted = self._undispatch(y_local, plan)
+        # combine: slot (token, k) weighted by its probability
+        k = cfg.moe_router_topk
+        w_sorted = top_p.detach().reshape(-1)[plan["order"]].to(x.dtype)
+        out = torch.zeros(t, cfg.hidden_size, device=x.device, dtype=torch.float32)
+        out.index_add_(0, plan["token_of"], (y_sorted * w_sorted.unsqueeze(-1)).float())
+        out = out.to(x.dtype)
+        shared_ctx = None
+        if self.shared_experts is not None:
+            gu = torch.matmul(x, self.shared_experts.linear_fc1.weight.t())
+            act = ops.swiglu_fwd(gu)
+            out = out + comm.reduce_out(torch.matmul(act, self.shared_experts.linear_fc2.weight.t()))
+            shared_ctx = (gu, act) if keep else None
+        if not keep:
+            return out, None
+        ctx = dict(xr=xr, top_p=top_p, aux=aux, plan=plan, xp=xp, gus=gus, acts=acts, y_sorted=y_sorted,
+                   w_sorted=w_sorted, shared=shared_ctx)
+        return out, ctx
+
+    def backward_tokens(self, ctx, x: torch.Tensor, dout: torch.Tensor, comm) -> torch.Tensor:
+        from .gpt import accum_wgrad, grad_buffer
+
+        plan = ctx["plan"]
+        d_tok = dout[plan["token_of"]]                                    # [T*k, H] in sorted-slot order
+        dy_sorted = d_tok * ctx["w_sorted"].unsqueeze(-1)
+        dw_sorted = (d_tok.float() * ctx["y_sorted"].float()).sum(-1)      # d loss / d prob per slot
+        dy_local = self._redispatch(dy_sorted, plan)
+        dxp_local = self._experts_bwd(ctx["xp"], plan["local_counts"], ctx["gus"], ctx["acts"], dy_local)
+        dxp_sorted = self._undispatch(dxp_local, plan)
+        dx = torch.zeros_like(x, dtype=torch.float32)
+        dx.index_add_(0, plan["token_of"], dxp_sorted.float())
+        # router: probabilities (+ auxiliary loss) back to logits, x and the router weight
+        dprob = torch.zeros(plan["t"] * plan["k"], device=x.device, dtype=torch.float32)
+        dprob[plan["order"]] = dw_sorted
+        outs, grads = [ctx["top_p"]], [dprob.view(plan["t"], plan["k"])]
+        if ctx["aux"] is not None:
+            outs.append(ctx["aux"])
+            grads.append(torch.ones_like(ctx["aux"]))
+        wants = [ctx["xr"]] + ([self.router.weight] if self.router.weight.requires_grad else [])
+        got = torch.autograd.grad(outs, wants, grads, allow_unused=True)
+        if got[0] is not None:
+            dx += got[0]
+        if len(got) > 1 and got[1] is not None:
+            grad_buffer(self.router.weight).add_(got[1].to(grad_buffer(self.router.weight).dtype))
+        if self.shared_experts is not None:
+            gu, act = ctx["shared"]
+            fc1, fc2 = self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight
+            d_sh = comm.reduce_out_bwd(dout)
+            dact = torch.matmul(d_sh, fc2)
+            accum_wgrad(fc2, d_sh, act)
+            dgu = ops.swiglu_bwd(gu, dact)
+            dx += torch.matmul(dgu, fc1).float()
+            accum_wgrad(fc1, dgu, x)
+        return dx.to(x.dtype)
+
+    # ------------------------------------------------------------------------------------------
+    def rollout_view(self):
+        """Weights as the rollout model runner consumes them (zero-copy)."""
+        from ..rollout.moe import MoEWeights
+
+        return MoEWeights(self.cfg, self.router.weight.data, self._w1().data, self._w2().data,
+                          self.ep_group, self.ep_size, self.ep_rank,
+                          shared=(self.shared_experts.linear_fc1.weight.data,
+                                  self.shared_experts.linear_fc2.weight.data) if self.shared_experts else None)

@@ -127,6 +127,8 @@ def metrics_sort(metrics: Dict[str, Any], time_all: float) -> Dict[str, Any]:
     if not has_old:
         old_end = ref_end
         head.remove("timing/old_log_p")
+    if ref_start is None:
+        ref_start = 0
     m_ref = max(ref_end - max(old_end, ref_start), 0) if has_ref else 0
     if not has_old and not has_ref:
         m_adv = m.get("timing/adv", 0)

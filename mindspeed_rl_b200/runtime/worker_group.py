@@ -44,7 +44,7 @@ class SPMDWorkerGroup:
         return self
 
     def sync_init_transfer_dock(self, td, mm_td=None, sampling_transfer_dock=None) -> None:
-        self.worker.init_transfer_dock(td)
+        self.worker.init_transfer_dock(td, mm_td, sampling_transfer_dock)
 
     def barrier(self) -> None:
         if self.world_size > 1:

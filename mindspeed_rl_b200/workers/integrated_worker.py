@@ -128,8 +128,9 @@ class IntegratedWorker(BaseWorker):
                                                           **self.sampling_overrides)
         self.initialized = True
 
-    def init_transfer_dock(self, td) -> None:
+    def init_transfer_dock(self, td, mm_td=None, sampling_transfer_dock=None) -> None:
         self.td = td
+        self.sampling_td = sampling_transfer_dock
 
     def get_iteration(self) -> int:
         return self.iteration
@@ -138,28 +139,50 @@ class IntegratedWorker(BaseWorker):
         return self.consumed_train_samples
 
     # ---- rollout -----------------------------------------------------------------------------------
+    def enter_infer_mode(self) -> None:
+        """Reshard into the rollout engine and keep it resident (DAPO re-sampling rounds)."""
+        if self.sharding_manager.mode != "infer":
+            self._t_enter = self.sharding_manager.enter_infer_mode()
+            self.update_metrics("timing/resharding_enter_infer", [self._t_enter])
+            self._held_infer = True
+
+    def exit_infer_mode(self) -> None:
+        if self.sharding_manager.mode == "infer":
+            t_exit = self.sharding_manager.exit_infer_mode()
+            self.update_metrics("timing/resharding_exit_infer", [t_exit])
+            self.update_metrics("timing/resharding_to_infer", [getattr(self, "_t_enter", 0.0) + t_exit])
+            self._held_infer = False
+
     def generate_sequences(self) -> None:
         rl = self.rl_config
-        start_reshard = _now()
-        t_enter = self.sharding_manager.enter_infer_mode()
-        self.update_metrics("timing/resharding_enter_infer", [t_enter])
+        held = getattr(self, "_held_infer", False)
+        if not held:
+            self._t_enter = self.sharding_manager.enter_infer_mode()
+            self.update_metrics("timing/resharding_enter_infer", [self._t_enter])
+        main_td = self.td
+        if getattr(self, "sampling_td", None) is not None:
+            self.td = self.sampling_td          # rollouts of DAPO go to the sampling dock
         start = _now()
         n = rl.n_samples_per_prompt
-        while True:
-            batch, idx, finished = self.dispatch_transfer_dock_data(
-                "actor_rollout", ["prompts", "prompt_length"], rl.actor_rollout_dispatch_size,
-                get_n_samples=True)
-            if finished:
-                break
-            if batch is None:
-                time.sleep(0.002)
-                continue
-            self._generate_batch(batch, idx, n)
-        end = _now()
-        t_exit = self.sharding_manager.exit_infer_mode()
-        self.update_metrics("timing/rollout", [round(end, 4), round(start, 4)])
-        self.update_metrics("timing/resharding_exit_infer", [t_exit])
-        self.update_metrics("timing/resharding_to_infer", [t_enter + t_exit])
+        try:
+            while True:
+                batch, idx, finished = self.dispatch_transfer_dock_data(
+                    "actor_rollout", ["prompts", "prompt_length"], rl.actor_rollout_dispatch_size,
+                    get_n_samples=True)
+                if finished:
+                    break
+                if batch is None:
+                    time.sleep(0.002)
+                    continue
+                self._generate_batch(batch, idx, n)
+            end = _now()
+            self.update_metrics("timing/rollout", [round(end, 4), round(start, 4)])
+        finally:
+            self.td = main_td
+        if not held:
+            t_exit = self.sharding_manager.exit_infer_mode()
+            self.update_metrics("timing/resharding_exit_infer", [t_exit])
+            self.update_metrics("timing/resharding_to_infer", [self._t_enter + t_exit])
 
     def _generate_batch(self, batch: Dict[str, torch.Tensor], idx: List[int], n: int) -> None:
         prompts, plen = batch["prompts"], batch["prompt_length"].reshape(-1)
