@@ -1,0 +1,207 @@
+"""Multi-rank behaviour on CPU (gloo): parallel-state rank maths, tensor/sequence-parallel model
+equivalence with the single-rank model, distributed optimizer vs single-rank Adam, expert
+parallel MoE, and the experience store served over RPC."""
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_distributed
+from mindspeed_rl_b200.parallel.state import RankLayout
+
+
+def test_rank_layout_groups():
+    lay = RankLayout(16, tp=2, pp=2, cp=2)
+    assert lay.dp == 2
+    assert lay.groups("tp")[0] == [0, 1] and lay.groups("cp")[0] == [0, 2]
+    assert lay.groups("dp")[0] == [0, 4] and lay.groups("pp")[0] == [0, 8]
+    assert lay.coords(13) == {"tp": 1, "cp": 0, "dp": 1, "pp": 1}
+    assert lay.rank_of(tp=1, cp=0, dp=1, pp=1) == 13
+    moe = RankLayout(8, tp=2, ep=2, moe_tp_extend_ep=True)
+    assert moe.ep_total == 4 and moe.expert_tp == 1 and moe.expert_dp == 2
+    assert moe.expert_groups("ep")[0] == [0, 1, 2, 3]
+
+
+def _shard_state(full, cfg, tp, r):
+    from mindspeed_rl_b200.checkpoint import convert as C
+    nkv = cfg.num_query_groups
+    out = {}
+    for k, v in full.items():
+        if k.endswith("linear_qkv.weight") or k.endswith("linear_qkv.bias"):
+            out[k] = C.shard_qkv(v, nkv, tp, r)
+        elif k.endswith("linear_fc1.weight"):
+            g, u = v.chunk(2, 0)
+            out[k] = C.shard_fc1(g, u, tp, r)
+        elif k.endswith("linear_proj.weight") or k.endswith("linear_fc2.weight"):
+            out[k] = C.shard_cols(v, tp, r)
+        elif k.endswith("word_embeddings.weight") or k.endswith("output_layer.weight"):
+            out[k] = C.shard_rows(v, tp, r)
+        else:
+            out[k] = v.clone()
+    return out
+
+
+def _tp_worker(rank, world, sp):
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+    ps = initialize_model_parallel(tensor_model_parallel_size=world)
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, add_qkv_bias=True, params_dtype=torch.float32, max_position_embeddings=128)
+    torch.manual_seed(0)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=5)
+    cfg = TransformerConfig(tensor_model_parallel_size=world, sequence_parallel=sp, **kw)
+    comm = TPComm(ps.group("tp"), sp, world_size=world, rank=rank)
+    model = GPTModel(cfg, comm, device="cpu")
+    model.load_state_dict(_shard_state(full.state_dict(), cfg, world, rank))
+    lens = [6, 10]
+    meta = PackedMeta.from_lengths(lens, "cpu", align=world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator().manual_seed(1)
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    ref_lp, ref_ent = full.forward_logprob(ids, labels, meta, 0.9, True)
+    (ref_lp * w + 0.1 * ref_ent).sum().backward()
+    if sp:   # activations between layers are sharded over tokens
+        model.embed = lambda x, _m=model: _seq_shard(_orig_embed(_m, x), world, rank)
+    lp, ent = model.forward_logprob(ids, labels, meta, 0.9, True)
+    (lp * w + 0.1 * ent).sum().backward()
+    assert torch.allclose(lp, ref_lp, atol=1e-4), (lp - ref_lp).abs().max()
+    assert torch.allclose(ent, ref_ent, atol=1e-4)
+    want = _shard_state({n: p.grad for n, p in full.named_parameters()}, cfg, world, rank)
+    for n, p in model.named_parameters():
+        g_ = p.grad
+        if sp and p.dim() == 1 and "linear_qkv" not in n:   # norm weights see only the local tokens
+            dist.all_reduce(g_)
+        assert torch.allclose(g_, want[n], atol=2e-4, rtol=1e-3), (n, (g_ - want[n]).abs().max())
+
+
+def _orig_embed(m, ids):
+    from mindspeed_rl_b200.models.gpt import _EmbedFn
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+    plain = TPComm(m.comm.group, False, world_size=m.comm.world_size, rank=m.comm.rank)
+    return _EmbedFn.apply(m.embedding.word_embeddings.weight, ids, plain, m.vocab_start)
+
+
+class _Shard(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, world, rank):
+        ctx.world, ctx.rank = world, rank
+        return x.chunk(world, 0)[rank].contiguous()
+
+    @staticmethod
+    def backward(ctx, d):
+        parts = [torch.zeros_like(d) for _ in range(ctx.world)]
+        dist.all_gather(parts, d.contiguous())
+        return torch.cat(parts, 0), None, None
+
+
+def _seq_shard(x, world, rank):
+    return _Shard.apply(x, world, rank)
+
+
+def test_tensor_parallel_matches_single_rank():
+    run_distributed(_tp_worker, 2, False)
+
+
+def test_sequence_parallel_matches_single_rank():
+    run_distributed(_tp_worker, 2, True)
+
+
+def _zero1_worker(rank, world):
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    ps = initialize_model_parallel()
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(16, 24), torch.nn.Linear(24, 8))
+    ref = torch.nn.Sequential(torch.nn.Linear(16, 24), torch.nn.Linear(24, 8))
+    ref.load_state_dict(net.state_dict())
+    ddp = DistributedDataParallel(net, ps.group("dp_cp"), world)
+    opt = DistributedOptimizer(ddp.buffers, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, clip_grad=0.5,
+                               dp_group=ps.group("dp_cp"), dp_rank=rank)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01)
+    for step in range(3):
+        xs = [torch.randn(4, 16, generator=torch.Generator().manual_seed(10 * step + r)) for r in range(world)]
+        ddp.zero_grad_buffer()
+        out = net(xs[rank]).pow(2).mean()
+        out.backward()
+        for p in net.parameters():          # plain autograd grads -> flat buffer
+            p.main_grad.copy_(p.grad)
+            p.grad = None
+        ddp.finish_grad_sync(to_shards=True)
+        opt.step()
+        ropt.zero_grad()
+        (sum(ref(x).pow(2).mean() for x in xs) / world).backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        ropt.step()
+    for a, b in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(a, b, atol=1e-5), (a - b).abs().max()
+
+
+def test_distributed_optimizer_matches_adamw():
+    run_distributed(_zero1_worker, 2)
+
+
+def _ep_worker(rank, world):
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel, set_parallel_state
+    kw = dict(num_layers=1, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, params_dtype=torch.float32, max_position_embeddings=64, num_experts=4,
+              moe_router_topk=2, moe_ffn_hidden_size=16, norm_topk_prob=True, moe_aux_loss_coeff=0.0)
+    set_parallel_state(None)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=3)       # all experts on one rank
+    initialize_model_parallel(expert_model_parallel_size=world)
+    model = GPTModel(TransformerConfig(expert_model_parallel_size=world, **kw), device="cpu", seed=3)
+    sd = full.state_dict()
+    per = 4 // world
+    for k in list(sd):
+        if k.endswith("experts.weight1"):
+            sd[k] = sd[k].view(32, 4, 32)[:, rank * per:(rank + 1) * per].reshape(32, -1).contiguous()
+        if k.endswith("experts.weight2"):
+            sd[k] = sd[k].view(4, 16, 32)[rank * per:(rank + 1) * per].reshape(-1, 32).contiguous()
+    model.load_state_dict(sd)
+    # every rank feeds different tokens (data parallel over the EP group)
+    g = torch.Generator().manual_seed(100 + rank)
+    meta = PackedMeta.from_lengths([9], "cpu")
+    ids, labels = torch.randint(0, 64, (9,), generator=g), torch.randint(0, 64, (9,), generator=g)
+    ref, _ = full.forward_logprob(ids, labels, meta)
+    ref.sum().backward()
+    lp, _ = model.forward_logprob(ids, labels, meta)
+    lp.sum().backward()
+    assert torch.allclose(lp, ref, atol=1e-4), (lp - ref).abs().max()
+    # expert grads: sum over the ranks' tokens equals the sum of single-rank grads over both inputs
+    gw = model.decoder.layers[0].mlp.experts.weight2.grad
+    fw = full.decoder.layers[0].mlp.experts.weight2.grad.view(4, 16, 32).clone()
+    dist.all_reduce(fw)
+    assert torch.allclose(gw.view(per, 16, 32), fw[rank * per:(rank + 1) * per], atol=2e-4)
+
+
+def test_expert_parallel_matches_single_rank():
+    run_distributed(_ep_worker, 2)
+
+
+def _dock_worker(rank, world):
+    from mindspeed_rl_b200.data.transfer_dock import GRPOTransferDock
+    from mindspeed_rl_b200.runtime import rpc
+    box = [None]
+    if rank == 0:
+        dock = GRPOTransferDock(4, 2)
+        server = rpc.serve(dock)
+        box[0] = server.address
+    dist.broadcast_object_list(box, src=0)
+    td = dock if rank == 0 else rpc.connect(box[0])
+    if rank == 1:
+        td.put_experience({"prompts": [torch.arange(3 + i) for i in range(8)],
+                           "prompt_length": [torch.tensor([3 + i]) for i in range(8)]}, list(range(8)))
+    dist.barrier()
+    batch, idx = td.get_experience("actor_rollout", ["prompts", "prompt_length"], 4, get_n_samples=True)
+    assert len(idx) == 4 and idx[0] % 2 == 0 and batch["prompts"].shape[0] == 4
+    dist.barrier()
+    assert td.all_consumed("actor_rollout")
+    got = [None] * world
+    dist.all_gather_object(got, sorted(idx))
+    assert sorted(got[0] + got[1]) == list(range(8))      # no row handed out twice
+
+
+def test_transfer_dock_over_rpc():
+    run_distributed(_dock_worker, 2)
