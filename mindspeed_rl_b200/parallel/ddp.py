@@ -55,8 +55,23 @@ class ParamAndGradBuffer:
             self.slots.append(ParamSlot(n, off, p.numel(), p.shape))
             off = _align(off + p.numel(), self.ALIGN)
         self.numel = _align(off, self.ALIGN * max(dp_size, 1))
-        self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=self.device)
-        self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
+        # With a symmetric arena the flat buffers are peer-mapped: gradient reduce-scatter,
+        # parameter all-gather and rollout resharding then run as direct NVLink pull kernels.
+        self.arena = None
+        if self.device.type == "cuda":
+            from .symm import get_arena
+
+            arena = get_arena()
+            need = self.numel * (torch.empty(0, dtype=self.param_dtype).element_size()
+                                 + torch.empty(0, dtype=self.grad_dtype).element_size()) + 1024
+            if arena is not None and arena.free_bytes() >= need:
+                self.arena = arena
+        if self.arena is not None:
+            self.param_data = self.arena.alloc(self.numel, self.param_dtype).zero_()
+            self.grad_data = self.arena.alloc(self.numel, self.grad_dtype).zero_()
+        else:
+            self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=self.device)
+            self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
         self.params: List[nn.Parameter] = []
         for (n, p), slot in zip(params, self.slots):
             view = self.param_data[slot.start:slot.start + slot.numel].view(slot.shape)
@@ -93,6 +108,14 @@ class ParamAndGradBuffer:
         reduced values of its own shard only (reduce-scatter, distributed optimizer)."""
         if self.dp_size == 1 or group is None:
             return
+        if self.arena is not None and to_shards:
+            # one pull kernel: sum the peers' copies of my shard, scale, write my slice in place
+            per = self.numel // self.dp_size
+            r = dist.get_rank(group)
+            self.arena.reduce_scatter(self.grad_data, self.grad_data[r * per:(r + 1) * per],
+                                      scale=1.0 / self.dp_size if average else 1.0,
+                                      ranks=self.arena.team_ranks(group))
+            return
         if average:
             self.grad_data.div_(self.dp_size)
         if to_shards:
@@ -109,6 +132,9 @@ class ParamAndGradBuffer:
             return
         per = self.numel // self.dp_size
         r = dist.get_rank(group)
+        if self.arena is not None:
+            self.arena.all_gather_inplace(self.param_data, ranks=self.arena.team_ranks(group))
+            return
         dist.all_gather_into_tensor(self.param_data, self.param_data[r * per:(r + 1) * per].clone(),
                                     group=group)
 

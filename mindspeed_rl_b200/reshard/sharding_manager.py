@@ -34,6 +34,8 @@ class GradBufferOffloader:
         if self.ddp is None or self.released:
             return
         for b in self.ddp.buffers:
+            if b.arena is not None:      # peer-mapped buffers stay resident for the life of the job
+                continue
             b.grad_data = torch.empty(0, dtype=b.grad_dtype, device=b.device)
             for p in b.params:
                 p.main_grad = None
@@ -43,6 +45,8 @@ class GradBufferOffloader:
         if self.ddp is None or not self.released:
             return
         for b in self.ddp.buffers:
+            if b.arena is not None:
+                continue
             b.grad_data = torch.zeros(b.numel, dtype=b.grad_dtype, device=b.device)
             b.rebind()
         self.released = False
@@ -59,6 +63,8 @@ class ParamOffloader:
     def offload(self) -> None:
         if self.ddp is None or self.offloaded:
             return
+        if any(b.arena is not None for b in self.ddp.buffers):
+            return                       # peer-mapped parameter buffers are never swapped out
         if not self.host:
             self.host = [torch.empty(b.numel, dtype=b.param_dtype, pin_memory=b.device.type == "cuda")
                          for b in self.ddp.buffers]

@@ -53,6 +53,22 @@ class IntegratedWorker(BaseWorker):
         self.initialized = False
 
     # ------------------------------------------------------------------------------------------
+    def _maybe_init_arena(self, core, grads_fp32: bool) -> None:
+        """Single-node multi-GPU jobs keep the flat parameter / gradient buffers in peer-mapped
+        memory (``MSRL_SYMM=0`` falls back to NCCL collectives and gathered resharding)."""
+        import os
+
+        import torch.distributed as dist
+
+        from ..parallel.symm import get_arena, init_arena
+
+        if (self.device.type != "cuda" or not dist.is_initialized() or dist.get_world_size() == 1
+                or dist.get_world_size() > torch.cuda.device_count() or get_arena() is not None
+                or os.environ.get("MSRL_SYMM", "1") != "1"):
+            return
+        n = sum(p.numel() for p in core.parameters())
+        init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20), device=self.device)
+
     def initialize(self) -> None:
         ac, rl, gc = self.actor_config, self.rl_config, self.generate_config
         ps = self.parallel_state
@@ -63,6 +79,7 @@ class IntegratedWorker(BaseWorker):
         self.tcfg = tcfg
         core = GPTModel(tcfg, self.comm, device=self.device, seed=self.seed)
         dp = ps.size("dp_cp")
+        self._maybe_init_arena(core, bool(ac.accumulate_allreduce_grads_in_fp32))
         self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
                                              grad_in_fp32=bool(ac.accumulate_allreduce_grads_in_fp32))
         self.optimizer = DistributedOptimizer(
@@ -164,6 +181,10 @@ class IntegratedWorker(BaseWorker):
             self.td = self.sampling_td          # rollouts of DAPO go to the sampling dock
         start = _now()
         n = rl.n_samples_per_prompt
+        train_state = self._state
+        if self.sharding_manager.resharder is not None:
+            # rollout replicas are (infer-TP)-sized: dispatch / write-back follow the rollout layout
+            self._state = self.sharding_manager.resharder.infer_state
         try:
             while True:
                 batch, idx, finished = self.dispatch_transfer_dock_data(
@@ -179,6 +200,7 @@ class IntegratedWorker(BaseWorker):
             self.update_metrics("timing/rollout", [round(end, 4), round(start, 4)])
         finally:
             self.td = main_td
+            self._state = train_state
         if not held:
             t_exit = self.sharding_manager.exit_infer_mode()
             self.update_metrics("timing/resharding_exit_infer", [t_exit])

@@ -205,3 +205,27 @@ def _dock_worker(rank, world):
 
 def test_transfer_dock_over_rpc():
     run_distributed(_dock_worker, 2)
+
+
+def _launch_worker(rank, world, train_tp, infer_tp):
+    import os
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"actor_config.tensor_model_parallel_size={train_tp}",
+        f"generate_config.infer_tensor_parallel_size={infer_tp}",
+        f"rl_config.actor_resource.num_gpus={world}"])
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == 2
+        assert all(m["timing/rollout"] > 0 and "actor/pg_loss" in m for m in hist)
+
+
+def test_launch_grpo_tp2_rollout_tp1_reshard():
+    """Full ``run_rl`` on 2 gloo ranks: training TP=2, rollout TP=1 (two rollout replicas) through
+    the resharding plan's gathered fallback."""
+    run_distributed(_launch_worker, 2, 2, 1)
+
+
+def test_launch_grpo_dp2():
+    run_distributed(_launch_worker, 2, 1, 1)

@@ -1,0 +1,45 @@
+"""Multi-GPU tests (skipped on boxes with a single GPU): peer-memory collectives, the reshard
+copy-plan kernel and a GRPO iteration with train TP != rollout TP, each run as one process per
+GPU under ``torch.distributed.run``."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _n_gpus() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _run(case: str, nproc: int, timeout: int = 600) -> str:
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29617",
+           os.path.join(ROOT, "tests", "multi_gpu_cases.py"), case]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0 and f"CASE {case} OK" in out, out[-4000:]
+    return out
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_symmetric_collectives():
+    out = _run("collectives", min(_n_gpus(), 8))
+    print([l for l in out.splitlines() if l.startswith("TIMING")])
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_reshard_copy_plan_kernel():
+    _run("reshard", 2)
+    if _n_gpus() >= 4:
+        _run("reshard", 4)
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_grpo_train_tp2_rollout_tp1():
+    _run("grpo_reshard", 2)
