@@ -184,21 +184,20 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
     cfg, comm, sa = layer.cfg, layer.comm, layer.self_attention
     eps = cfg.norm_epsilon
     x1, rstd1, _ = ops.rmsnorm_fwd(h, layer.input_layernorm.weight, eps, want_rstd=keep)
-    x1g = comm.gather_seq(x1)
-    qkv = torch.matmul(x1g, sa.linear_qkv.weight.t())
-    if sa.linear_qkv.bias is not None:
-        qkv += sa.linear_qkv.bias
+    # column linears = (all-gather tokens ->) GEMM, row linears = GEMM (-> reduce-scatter tokens);
+    # ``comm`` runs each pair as one fused kernel when it can
+    qkv, x1g = comm.column_linear(x1, sa.linear_qkv.weight, sa.linear_qkv.bias)
     attn, lse, pre, rq, rk = _attention_core_fwd(layer, qkv, meta)
-    proj = comm.reduce_out(torch.matmul(attn, sa.linear_proj.weight.t()))
+    proj = comm.row_linear(attn, sa.linear_proj.weight)
     h1 = ops.add(h, proj)
     x2, rstd2, _ = ops.rmsnorm_fwd(h1, layer.pre_mlp_layernorm.weight, eps, want_rstd=keep)
-    x2g = comm.gather_seq(x2)
     if isinstance(layer.mlp, MLP):
-        gu = torch.matmul(x2g, layer.mlp.linear_fc1.weight.t())
+        gu, x2g = comm.column_linear(x2, layer.mlp.linear_fc1.weight)
         y = ops.swiglu_fwd(gu)
-        mlp_out = comm.reduce_out(torch.matmul(y, layer.mlp.linear_fc2.weight.t()))
+        mlp_out = comm.row_linear(y, layer.mlp.linear_fc2.weight)
         mlp_ctx = (gu, y) if keep else None
     else:
+        x2g = comm.gather_seq(x2)
         mlp_out, mlp_ctx = layer.mlp.forward_tokens(x2g, comm, keep)
     h2 = ops.add(h1, mlp_out)
     if not keep:
@@ -213,23 +212,21 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
     cfg, comm, sa = layer.cfg, layer.comm, layer.self_attention
     lay = sa.layout
     # ---- MLP ----
-    d_out = comm.reduce_out_bwd(dh2)
     if isinstance(layer.mlp, MLP):
         gu, y = ctx["mlp_ctx"]
         fc1, fc2 = layer.mlp.linear_fc1.weight, layer.mlp.linear_fc2.weight
-        dy = torch.matmul(d_out, fc2)
+        dy, d_out = comm.row_linear_bwd(dh2, fc2)
         accum_wgrad(fc2, d_out, y)
         dgu = ops.swiglu_bwd(gu, dy)
-        dx2g = torch.matmul(dgu, fc1)
         accum_wgrad(fc1, dgu, ctx["x2g"])
+        dx2 = comm.column_linear_bwd(dgu, fc1)
     else:
-        dx2g = layer.mlp.backward_tokens(ctx["mlp_ctx"], ctx["x2g"], d_out, comm)
-    dx2 = comm.gather_seq_bwd(dx2g)
+        d_out = comm.reduce_out_bwd(dh2)
+        dx2 = comm.gather_seq_bwd(layer.mlp.backward_tokens(ctx["mlp_ctx"], ctx["x2g"], d_out, comm))
     dh1 = ops.rmsnorm_bwd(dx2, ctx["h1"], layer.pre_mlp_layernorm.weight, ctx["rstd2"],
                           grad_buffer(layer.pre_mlp_layernorm.weight), dres=dh2)
     # ---- attention ----
-    d_proj = comm.reduce_out_bwd(dh1)
-    dattn = torch.matmul(d_proj, sa.linear_proj.weight)
+    dattn, d_proj = comm.row_linear_bwd(dh1, sa.linear_proj.weight)
     accum_wgrad(sa.linear_proj.weight, d_proj, ctx["attn"])
     if meta.cp is not None:
         dqkv = meta.cp.attention_bwd(dattn, ctx["qkv"], ctx["attn"], ctx["lse"], lay, meta)
@@ -242,11 +239,10 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
                           grad_buffer(sa.q_layernorm.weight))
         ops.headnorm_bwd_(dqkv, ctx["pre"], lay, "k", sa.k_layernorm.weight, ctx["rk"],
                           grad_buffer(sa.k_layernorm.weight))
-    dx1g = torch.matmul(dqkv, sa.linear_qkv.weight)
     accum_wgrad(sa.linear_qkv.weight, dqkv, ctx["x1g"])
     if sa.linear_qkv.bias is not None and sa.linear_qkv.bias.requires_grad:
         ops.colsum_accumulate(dqkv, grad_buffer(sa.linear_qkv.bias))
-    dx1 = comm.gather_seq_bwd(dx1g)
+    dx1 = comm.column_linear_bwd(dqkv, sa.linear_qkv.weight)
     dh = ops.rmsnorm_bwd(dx1, ctx["h"], layer.input_layernorm.weight, ctx["rstd1"],
                          grad_buffer(layer.input_layernorm.weight), dres=dh1)
     return dh

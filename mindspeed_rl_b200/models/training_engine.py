@@ -33,7 +33,10 @@ def _unwrap(model):
 class MicroBatch:
     """Packed view of some rows of a padded batch (host tensors until ``to``)."""
 
-    def __init__(self, data: Dict[str, torch.Tensor], rows: Sequence[int], align: int):
+    def __init__(self, data: Dict[str, torch.Tensor], rows: Sequence[int], align: int, total_align: int = 1):
+        """``align``: every sequence is padded to a multiple of it (TP x CP token sharding);
+        ``total_align``: the last sequence takes extra padding so that the whole stream is a
+        multiple of it (128 x TP lets the communication-fused GEMMs tile the token shards)."""
         rows_t = torch.as_tensor(list(rows), dtype=torch.int64)
         ids2d = data["input_ids"][rows_t].to(torch.int64)
         b, s = ids2d.shape
@@ -41,6 +44,8 @@ class MicroBatch:
         r_len = data["response_length"][rows_t].reshape(-1).to(torch.int64)
         lens = (p_len + r_len).clamp(max=s)
         padded = (lens + align - 1) // align * align
+        if total_align > 1 and b:
+            padded[-1] += (-int(padded.sum())) % total_align
         cu = torch.zeros(b + 1, dtype=torch.int64)
         cu[1:] = torch.cumsum(padded, 0)
         total = int(cu[-1])
@@ -111,6 +116,14 @@ class TrainingEngine:
         self.entropy_needs_grad = c_ent != 0.0
 
     # ------------------------------------------------------------------------------------------
+    def _total_align(self) -> int:
+        """Token-count multiple of a packed stream: 128 per TP rank when the communication-fused
+        linears are attached (they tile each rank's token shard in 128-row tiles)."""
+        comm = self.core.comm
+        if getattr(comm, "fused", None) is not None and comm.sequence_parallel:
+            return 128 * comm.world_size
+        return 1
+
     def _split(self, data: Dict[str, torch.Tensor], rows: List[int], update: bool) -> List[List[int]]:
         if not self.use_dynamic_bsz:
             mbs = self.micro_batch_size if update else self.forward_micro_batch_size
@@ -143,7 +156,7 @@ class TrainingEngine:
         out = torch.zeros(n, width, dtype=torch.float32)
         results = []
         for rows in self._split(data, list(range(n)), update=False):
-            mb = MicroBatch(data, rows, self.pad_multiple).to(self.device)
+            mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
             vals, _ = self._run_model(mb, want_entropy=False)
             results.append((rows, vals.float()))
         for rows, vals in results:
@@ -190,7 +203,7 @@ class TrainingEngine:
         n_micro = len(parts)
         sums: Dict[str, torch.Tensor] = {}
         for rows in parts:
-            mb = MicroBatch(data, rows, self.pad_multiple).to(self.device)
+            mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
             scale = 1.0 / n_micro
             if self.use_dynamic_bsz:   # re-weight bins by their share of the mini-batch rows
                 scale = len(rows) / len(mini)
@@ -215,4 +228,8 @@ class TrainingEngine:
             self.model.finish_grad_sync(to_shards=True)
         if self.optimizer is None:
             return True, 0.0, 0
-        return self.optimizer.step()
+        result = self.optimizer.step()
+        fused = getattr(self.core.comm, "fused", None)
+        if fused is not None:
+            fused.invalidate_weights()       # cached transposed weights are stale now
+        return result

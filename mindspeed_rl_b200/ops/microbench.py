@@ -86,6 +86,26 @@ def case_gemm(small: bool, iters: int):
     G.check_status("cuda")
 
 
+def case_fused_single(small: bool, iters: int):
+    """Communication-fused GEMM variants with a team of one rank: the comm warps copy / reduce
+    through local memory only, which isolates their cost from the NVLink transfer."""
+    from ..parallel.fused_tp import FusedTP
+    from ..parallel.symm import SymmetricArena
+
+    m, n, k = (1024, 1024, 1024) if small else (4096, 4608, 3584)
+    arena = SymmetricArena(8 * m * max(n, k) * 2 + (8 << 20))
+    f = FusedTP(arena, [0], m, k, n)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    report(f"gemm_tcgen05 plain      {m}x{n}x{k}", timeit(lambda: G.gemm_bf16_tn(a, b, out), iters), flops=2.0 * m * n * k)
+    report(f"ag_gemm (1 rank, total) {m}x{n}x{k}", timeit(lambda: f.ag_gemm(a, b), iters), flops=2.0 * m * n * k,
+           note="slot copy + barrier + memset + kernel")
+    report(f"gemm_rs (1 rank)        {m}x{n}x{k}", timeit(lambda: f.gemm_rs(a, b), iters), flops=2.0 * m * n * k)
+    G.check_status(a.device)
+    arena.close()
+
+
 def case_lmhead(small: bool, iters: int):
     t, h, v = (8192, 3584, 152064) if not small else (1024, 1024, 16384)
     x = torch.randn(t, h, device="cuda").bfloat16()
@@ -167,7 +187,8 @@ def case_sampler(small: bool, iters: int):
 
 
 CASES = {"gemm": case_gemm, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
-         "elementwise": case_elementwise, "adam": case_adam, "sampler": case_sampler}
+         "elementwise": case_elementwise, "adam": case_adam, "sampler": case_sampler,
+         "fused_single": case_fused_single}
 
 
 def main():

@@ -67,5 +67,46 @@ class TPComm:
             dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=self.group)
         return t
 
+    # linear + collective pairs ------------------------------------------------------------------------
+    # With a symmetric-memory team attached (``self.fused``) and sequence parallelism on, each pair
+    # runs as one communication-fused tcgen05 kernel; otherwise as collective + matmul.
+    def _fused_ok(self, t: torch.Tensor) -> bool:
+        return self.fused is not None and self.sequence_parallel and t.is_cuda
+
+    def column_linear(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        """``(gather_seq(x) @ w.T + bias, gather_seq(x))``."""
+        if self._fused_ok(x) and self.fused.fits_ag(x, w):
+            y, xg = self.fused.ag_gemm(x, w)
+        else:
+            xg = self.gather_seq(x)
+            y = torch.matmul(xg, w.t())
+        if bias is not None:
+            y += bias
+        return y, xg
+
+    def row_linear(self, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``reduce_out(a @ w.T)``."""
+        if self._fused_ok(a) and self.fused.fits_rs(a, w):
+            return self.fused.gemm_rs(a, w)
+        return self.reduce_out(torch.matmul(a, w.t()))
+
+    def column_linear_bwd(self, dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Input gradient of :meth:`column_linear`: ``gather_seq_bwd(dy @ w)``."""
+        if self._fused_ok(dy):
+            wt = self.fused.transposed(w)
+            if self.fused.fits_rs(dy, wt):
+                return self.fused.gemm_rs(dy, wt)
+        return self.gather_seq_bwd(torch.matmul(dy, w))
+
+    def row_linear_bwd(self, dout: torch.Tensor, w: torch.Tensor):
+        """Input gradient of :meth:`row_linear`: ``(reduce_out_bwd(dout) @ w, reduce_out_bwd(dout))``
+        (the gathered output gradient is what the weight gradient needs)."""
+        if self._fused_ok(dout):
+            wt = self.fused.transposed(w)
+            if self.fused.fits_ag(dout, wt):
+                return self.fused.ag_gemm(dout, wt)
+        d_full = self.reduce_out_bwd(dout)
+        return torch.matmul(d_full, w), d_full
+
 
 NO_TP = TPComm()

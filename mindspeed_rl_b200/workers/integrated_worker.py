@@ -67,7 +67,44 @@ class IntegratedWorker(BaseWorker):
                 or os.environ.get("MSRL_SYMM", "1") != "1"):
             return
         n = sum(p.numel() for p in core.parameters())
-        init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20), device=self.device)
+        extra = 0
+        m_local = self._fused_tp_rows()
+        if m_local:
+            tp = self.parallel_state.size("tp")
+            extra = 2 * m_local * self.tcfg.hidden_size * 2 * (1 + tp) + (1 << 20)
+        init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20) + extra, device=self.device)
+
+    def _fused_tp_rows(self) -> int:
+        """Largest token shard (rows per TP rank, multiple of 128) a packed micro-batch can have,
+        or 0 when the communication-fused TP linears do not apply (no TP / no sequence parallel /
+        ``MSRL_FUSED_TP=0``)."""
+        import os
+
+        ac, rl = self.actor_config, self.rl_config
+        tp = self.parallel_state.size("tp")
+        if tp == 1 or not ac.sequence_parallel or os.environ.get("MSRL_FUSED_TP", "1") != "1":
+            return 0
+        mbs = max(ac.micro_batch_size or 1, rl.actor_forward_micro_batch_size or 1,
+                  rl.ref_forward_micro_batch_size or 1)
+        tokens = max(rl.update_max_packing_token_size or 0, rl.actor_max_packing_token_size or 0,
+                     rl.ref_max_packing_token_size or 0, mbs * (ac.seq_length or 0))
+        tokens += 128 * tp + mbs * tp * 2
+        return (tokens // tp + 127) // 128 * 128
+
+    def _maybe_attach_fused_tp(self) -> None:
+        from ..parallel.symm import get_arena
+
+        arena, m_local = get_arena(), self._fused_tp_rows()
+        if arena is None or not m_local or self.device.type != "cuda":
+            return
+        from ..parallel.fused_tp import FusedTP
+
+        ps = self.parallel_state
+        need = 2 * m_local * self.tcfg.hidden_size * 2 * (1 + ps.size("tp")) + (1 << 19)
+        if arena.free_bytes() < need:
+            return
+        self.comm.fused = FusedTP(arena, arena.team_ranks(ps.group("tp")), m_local, self.tcfg.hidden_size,
+                                  self.tcfg.hidden_size)
 
     def initialize(self) -> None:
         ac, rl, gc = self.actor_config, self.rl_config, self.generate_config
@@ -82,6 +119,7 @@ class IntegratedWorker(BaseWorker):
         self._maybe_init_arena(core, bool(ac.accumulate_allreduce_grads_in_fp32))
         self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
                                              grad_in_fp32=bool(ac.accumulate_allreduce_grads_in_fp32))
+        self._maybe_attach_fused_tp()
         self.optimizer = DistributedOptimizer(
             self.model.buffers, lr=ac.lr or 1e-6, betas=(ac.adam_beta1, ac.adam_beta2),
             weight_decay=ac.weight_decay, clip_grad=ac.clip_grad, dp_group=ps.group("dp_cp"),

@@ -139,6 +139,126 @@ def case_reshard(rank, world):
         assert w.layers[0].o_w.shape == (cfg.hidden_size, cfg.num_attention_heads * 32 // infer_tp)
 
 
+def case_fused_tp(rank, world):
+    """all-gather->GEMM and GEMM->reduce-scatter tcgen05 kernels against NCCL + matmul."""
+    from mindspeed_rl_b200.ops.gemm import check_status
+    from mindspeed_rl_b200.parallel.fused_tp import FusedTP
+    from mindspeed_rl_b200.parallel.symm import SymmetricArena
+
+    small = os.environ.get("MSRL_TEST_SMALL", "0") == "1"
+    ml, hidden, n_col, k_row = (256, 512, 768, 256) if small else (2048, 3584, 4608 // world * 2, 18944 // world // 8 * 8)
+    arena = SymmetricArena((6 * ml * max(hidden, n_col) * 2 * (world + 1)) + (64 << 20))
+    f = FusedTP(arena, list(range(world)), ml, hidden, hidden)
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    rnd = lambda *s: (torch.randn(*s, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    for it in range(3):                                       # several calls: parity buffers, counter re-arming
+        x, w = rnd(ml, hidden), rnd(n_col, hidden)
+        y, xg = f.ag_gemm(x, w)
+        want_x = torch.empty(world * ml, hidden, dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(want_x, x)
+        check_status(torch.device("cuda", torch.cuda.current_device()),"ag_gemm")
+        assert torch.equal(xg, want_x), f"gathered activations differ (call {it})"
+        ref = torch.matmul(want_x.float(), w.float().t())
+        err = (y.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 1e-3, f"ag_gemm error {err} (call {it})"
+        a, w2 = rnd(world * ml, k_row), rnd(hidden, k_row)
+        out = f.gemm_rs(a, w2)
+        part = torch.matmul(a, w2.t())
+        want = torch.empty(ml, hidden, dtype=torch.bfloat16, device="cuda")
+        dist.reduce_scatter_tensor(want, part)
+        check_status(torch.device("cuda", torch.cuda.current_device()),"gemm_rs")
+        ref = want.float()
+        err = (out.float() - ref).abs().max().item()
+        assert err <= 3e-2 * ref.abs().max().item() + 1e-3, f"gemm_rs error {err} (call {it})"
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_.record()
+        for _ in range(iters):
+            fn()
+        b_.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a_.elapsed_time(b_) / iters], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    x, w = rnd(ml, hidden), rnd(n_col, hidden)
+    a, w2 = rnd(world * ml, k_row), rnd(hidden, k_row)
+    xg = torch.empty(world * ml, hidden, dtype=torch.bfloat16, device="cuda")
+    o = torch.empty(ml, hidden, dtype=torch.bfloat16, device="cuda")
+
+    def base_ag():
+        dist.all_gather_into_tensor(xg, x)
+        return torch.matmul(xg, w.t())
+
+    def base_rs():
+        dist.reduce_scatter_tensor(o, torch.matmul(a, w2.t()))
+
+    t = dict(ag_fused=timed(lambda: f.ag_gemm(x, w)), ag_nccl=timed(base_ag),
+             rs_fused=timed(lambda: f.gemm_rs(a, w2)), rs_nccl=timed(base_rs))
+    check_status(torch.device("cuda", torch.cuda.current_device()),"fused timing loop")
+    arena.check()
+    if rank == 0:
+        fl_ag = 2.0 * world * ml * hidden * n_col
+        fl_rs = 2.0 * world * ml * k_row * hidden
+        print(f"TIMING fused_tp world={world} m_local={ml} ag_gemm[N={n_col},K={hidden}] fused={t['ag_fused']:.3f}ms "
+              f"({fl_ag / t['ag_fused'] / 1e9:.0f} TFLOP/s) nccl+cublas={t['ag_nccl']:.3f}ms | "
+              f"gemm_rs[N={hidden},K={k_row}] fused={t['rs_fused']:.3f}ms ({fl_rs / t['rs_fused'] / 1e9:.0f} TFLOP/s) "
+              f"cublas+nccl={t['rs_nccl']:.3f}ms", flush=True)
+    arena.close()
+
+
+def case_tp_model(rank, world):
+    """Sequence-parallel TP model: forward + backward with the fused linears attached equals the
+    NCCL + matmul path on the same weights (bf16 tolerances)."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.ops.gemm import check_status
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.fused_tp import FusedTP
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    from mindspeed_rl_b200.parallel.symm import init_arena
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+
+    ps = initialize_model_parallel(world)
+    cfg = TransformerConfig(num_layers=2, hidden_size=512, ffn_hidden_size=1024, num_attention_heads=8,
+                            num_query_groups=4, vocab_size=2048, kv_channels=64, add_qkv_bias=True,
+                            tensor_model_parallel_size=world, sequence_parallel=True)
+    comm = TPComm(ps.group("tp"), True, world_size=world, rank=rank)
+    arena = init_arena(256 << 20)
+    model = DistributedDataParallel(GPTModel(cfg, comm, device="cuda", seed=11), None, 1)
+    core = model.module
+    lens = [128 * world, 128 * world]
+    meta = PackedMeta.from_lengths(lens, "cuda", align=world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator(device="cuda").manual_seed(1)
+    ids = torch.randint(0, 2048, (t,), device="cuda", generator=g)
+    labels = torch.randint(0, 2048, (t,), device="cuda", generator=g)
+    wts = torch.randn(t, device="cuda", generator=g)
+
+    def run():
+        model.zero_grad_buffer()
+        lp, _ = core.forward_logprob(ids, labels, meta, 1.0, False)
+        (lp * wts).sum().backward()
+        return lp.detach().clone(), [b.grad_data.float().clone() for b in model.buffers]
+
+    lp_ref, g_ref = run()
+    comm.fused = FusedTP(arena, list(range(world)), t // world, cfg.hidden_size, cfg.hidden_size)
+    calls = comm.fused._ag_calls
+    lp, g_f = run()
+    check_status(torch.device("cuda", torch.cuda.current_device()), "fused tp model")
+    arena.check()
+    assert comm.fused._ag_calls > calls and comm.fused._rs_calls > 0, "the fused kernels were not used"
+    assert (lp - lp_ref).abs().max().item() < 5e-2, (lp - lp_ref).abs().max().item()
+    for a, b in zip(g_f, g_ref):
+        denom = b.abs().max().item() + 1e-6
+        assert (a - b).abs().max().item() / denom < 5e-2, ((a - b).abs().max().item(), denom)
+
+
 def case_grpo_reshard(rank, world):
     """One GRPO iteration with train TP=2 and rollout TP=1 (resharding through peer memory)."""
     from mindspeed_rl_b200.config import compose, parse_training_config  # noqa: F401
@@ -152,7 +272,8 @@ def case_grpo_reshard(rank, world):
         assert len(hist) == 2, hist
 
 
-CASES = {"collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard}
+CASES = {"collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+         "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":
     name = sys.argv[1]

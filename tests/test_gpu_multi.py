@@ -43,3 +43,9 @@ def test_reshard_copy_plan_kernel():
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_grpo_train_tp2_rollout_tp1():
     _run("grpo_reshard", 2)
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_fused_tp_kernels():
+    out = _run("fused_tp", 2)
+    print([l for l in out.splitlines() if l.startswith("TIMING")])

@@ -42,3 +42,31 @@ def test_lmhead_stats_fused(t, v, h):
     ref_ent = -(ls.exp() * ls).sum(-1)
     assert (logp - ref_lp).abs().max() < 3e-2, (logp - ref_lp).abs().max()
     assert (ent - ref_ent).abs().max() < 3e-2, (ent - ref_ent).abs().max()
+
+
+@pytest.mark.parametrize("ml,k,n", [(128, 256, 256), (384, 512, 776), (1024, 1024, 1536)])
+def test_fused_comm_gemm_single_rank(ml, k, n):
+    """World size 1 exercises the comm warps, counters and tile order of both fused variants
+    (self-gather, push to the own staging area) without a second GPU."""
+    from mindspeed_rl_b200.parallel.fused_tp import FusedTP
+    from mindspeed_rl_b200.parallel.symm import SymmetricArena
+
+    torch.manual_seed(3)
+    arena = SymmetricArena(8 * ml * max(k, n) * 2 + (8 << 20))
+    try:
+        f = FusedTP(arena, [0], ml, k, n)
+        for call in range(3):
+            x = (torch.randn(ml, k, device=DEV) * 0.5).bfloat16()
+            w = (torch.randn(n, k, device=DEV) * 0.5).bfloat16()
+            assert f.fits_ag(x, w) and f.fits_rs(x, w)
+            y, xg = f.ag_gemm(x, w)
+            G.check_status(x.device)
+            assert torch.equal(xg, x)
+            ref = x.float() @ w.float().t()
+            assert bool(((y.float() - ref).abs() <= 2e-2 * ref.abs() + 0.25).all()), call
+            out = f.gemm_rs(x, w)
+            G.check_status(x.device)
+            assert bool(((out.float() - ref).abs() <= 2e-2 * ref.abs() + 0.25).all()), call
+        arena.check()
+    finally:
+        arena.close()
