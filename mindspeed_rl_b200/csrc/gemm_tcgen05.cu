@@ -480,15 +480,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int n_pieces = m_tiles * G_AG_PIECES;
     for (int piece = blockIdx.x; piece < n_pieces; piece += gridDim.x) {
       const int q = piece / G_AG_PIECES, sub = piece % G_AG_PIECES;
-      const int src_rank = (p.rank + q / mt_local) % p.world;
+      // peers first (in the order their tiles are consumed), this rank's own shard last: nobody
+      // waits for the self-copy, it only completes the gathered buffer for the weight gradient
+      const int src_rank = (p.rank + 1 + q / mt_local) % p.world;
       const int mt = src_rank * mt_local + q % mt_local;
       const int r0 = (q % mt_local) * G_BM + sub * (G_BM / G_AG_PIECES);   // first row inside the shard
       const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.peer[src_rank]);
       __nv_bfloat16* dst = p.gathered + ((long long)src_rank * p.m_local + r0) * p.K;
-#pragma unroll 4
-      for (int v = ct; v < piece_vecs; v += G_COMM_THREADS) {
-        const int rr = v / row_vecs, cc = v % row_vecs;
-        st8(dst + (long long)rr * p.K + cc * 8, ld8(src + (long long)(r0 + rr) * p.ld_peer + cc * 8));
+      // batches of 8 independent 16-byte loads per thread before any store: the loads must all be
+      // in flight together to cover the NVLink round trip
+      for (int v0 = ct; v0 < piece_vecs; v0 += G_COMM_THREADS * 8) {
+        bf16x8 buf[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int v = v0 + u * G_COMM_THREADS;
+          if (v < piece_vecs) buf[u] = ld8(src + (long long)(r0 + v / row_vecs) * p.ld_peer + (v % row_vecs) * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int v = v0 + u * G_COMM_THREADS;
+          if (v < piece_vecs) st8(dst + (long long)(v / row_vecs) * p.K + (v % row_vecs) * 8, buf[u]);
+        }
       }
       __threadfence();
       asm volatile("bar.sync 1, %0;\n" ::"n"(G_COMM_THREADS) : "memory");

@@ -104,6 +104,8 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
                               ref_config=cfg["ref_config"], with_reference=with_ref)
     world = dist.get_world_size() if dist.is_initialized() else 1
     actor_group = SPMDWorkerGroup(worker, world).initialize()
+    if rl_config.multi_turn_enable:
+        worker.attach_tools(tokenizer)
     if actor_config.load:
         from ..checkpoint.mcore import load_checkpoint
 

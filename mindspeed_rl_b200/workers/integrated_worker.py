@@ -233,7 +233,10 @@ class IntegratedWorker(BaseWorker):
                 if batch is None:
                     time.sleep(0.002)
                     continue
-                self._generate_batch(batch, idx, n)
+                if getattr(self, "multi_turn", None) is not None:
+                    self._generate_batch_multi_turn(batch, idx, n)
+                else:
+                    self._generate_batch(batch, idx, n)
             end = _now()
             self.update_metrics("timing/rollout", [round(end, 4), round(start, 4)])
         finally:
@@ -259,6 +262,45 @@ class IntegratedWorker(BaseWorker):
                 lengths.append(torch.tensor([len(ids)], dtype=torch.int32))
         self.collect_transfer_dock_data(
             {"responses": responses, "input_ids": input_ids, "response_length": lengths}, idx)
+
+    # ---- multi-turn tool use ----------------------------------------------------------------------------
+    def attach_tools(self, tokenizer, tool_map=None) -> None:
+        """Enable the multi-turn tool loop for rollouts (``rl_config.multi_turn_enable``)."""
+        from ..tools.base import load_tool_map
+        from ..tools.multi_turn import MultiTurnRollout
+
+        rl = self.rl_config
+        if tool_map is None:
+            tool_map = load_tool_map(rl.tool_config_path) if rl.tool_config_path else {}
+        comm = self.engine.comm
+
+        def share(ids: List[int]) -> List[int]:
+            # the rollout TP ranks run the engine in lock-step: rank 0's tool turn is the one all use
+            if comm.world_size == 1:
+                return ids
+            import torch.distributed as dist
+
+            box = [ids if comm.rank == 0 else None]
+            dist.broadcast_object_list(box, src=dist.get_process_group_ranks(comm.group)[0], group=comm.group)
+            return box[0]
+
+        self.multi_turn = MultiTurnRollout(
+            self.engine, tokenizer, tool_map, rl.tool_parser_format or "hermes", vocab_size=self.tcfg.vocab_size,
+            max_total_response_length=rl.max_total_response_length or self.generate_config.max_model_len,
+            max_tool_calls=rl.max_tool_calls or 1, max_parallel_calls=rl.max_parallel_calls or 1,
+            max_tool_response_length=rl.max_tool_response_length or 256,
+            tool_response_truncate_side=rl.tool_response_truncate_side or "middle", share_result=share)
+
+    def _generate_batch_multi_turn(self, batch: Dict[str, torch.Tensor], idx: List[int], n: int) -> None:
+        prompts, plen = batch["prompts"], batch["prompt_length"].reshape(-1)
+        prompt_lists = [prompts[i, :int(plen[i])].tolist() for i in range(len(idx))]   # one request per sample
+        res = self.multi_turn.generate(prompt_lists, self.sampling_params)
+        t = lambda v, dt=torch.int64: torch.tensor(v, dtype=dt)
+        self.collect_transfer_dock_data({
+            "responses": [t(r["responses"]) for r in res], "input_ids": [t(r["input_ids"]) for r in res],
+            "response_length": [t([r["response_length"]], torch.int32) for r in res],
+            "response_mask": [t(r["response_mask"]) for r in res],
+            "tool_call_num": [t([r["tool_call_num"]], torch.int32) for r in res]}, idx)
 
     # ---- forward-only stages ---------------------------------------------------------------------------
     def _logprob_stage(self, consumer: str, engine: TrainingEngine, out_column: str, dispatch_size: int,
