@@ -74,18 +74,34 @@ class RayBaseTrainer:
         self._td_server = None
 
     # ---- experience store plumbing ----------------------------------------------------------------
+    def _new_dock(self, *args, **kwargs):
+        """Driver side: build the experience store the run's ``data_strategy`` names
+        (``td``: one in-process dock, ``tq``: metadata manager + tensor shards)."""
+        from ..data.transfer_queue import DataStrategy
+
+        rl = getattr(self.actor_worker, "rl_config", None)
+        strategy = DataStrategy(getattr(rl, "data_strategy", "td") or "td",
+                                getattr(rl, "transfer_queue_data_shard_num", 1) or 1)
+        self._strategies = getattr(self, "_strategies", []) + [strategy]
+        dock, self._dock_descriptor = strategy.create(*args, **kwargs)
+        return dock
+
     def _share_dock(self, dock, name: str = "td"):
         """Make the driver's dock reachable from every rank; returns this rank's handle."""
+        from ..data.transfer_queue import DataStrategy
+
         world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
+        descriptor = getattr(self, "_dock_descriptor", None) if self.is_driver else None
+        self._dock_descriptor = None
         if world == 1:
-            return dock
-        box = [None]
+            return DataStrategy.attach(dock, descriptor)
+        box = [None, None]
         if self.is_driver:
             server = rpc.serve(dock, "tcp://127.0.0.1:0", num_threads=max(8, world * 2))
             self._servers = getattr(self, "_servers", []) + [server]
-            box[0] = server.address
+            box = [server.address, descriptor]
         dist.broadcast_object_list(box, src=0)
-        return dock if self.is_driver else rpc.connect(box[0])
+        return DataStrategy.attach(dock if self.is_driver else rpc.connect(box[0]), box[1])
 
     def _driver_section_done(self) -> None:
         """Host barrier after a driver-only stage."""

@@ -33,10 +33,9 @@ class RayGRPOTrainer(RayBaseTrainer):
     def transfer_dock_init(self) -> None:
         dock = None
         if self.is_driver:
-            dock = GRPOTransferDock(self.td_max_len, self.n_samples_per_prompt, self.metrics,
-                                    max_age=self.partial_rollout_max_split,
-                                    GBS_train=self.global_batch_size,
-                                    addition_columns=self.dataset_additional_keys)
+            dock = self._new_dock(self.td_max_len, self.n_samples_per_prompt, self.metrics,
+                                  max_age=self.partial_rollout_max_split, GBS_train=self.global_batch_size,
+                                  addition_columns=self.dataset_additional_keys)
         self.transfer_dock = self._share_dock(dock)
         self.actor_worker.sync_init_transfer_dock(self.transfer_dock)
         if self.ref_worker is not self.actor_worker:
