@@ -102,6 +102,15 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
     with_ref = algorithm != "dapo"
     worker = IntegratedWorker(actor_config, rl_config, generate_config, eos_token_id=eos, pad_token_id=pad,
                               ref_config=cfg["ref_config"], with_reference=with_ref)
+    from ..obs.profiler import TensorDump, enable_range_markers, seed_all
+
+    prof_cfg = (cfg.get("profiler_config") or {}).get("integrated")
+    worker.profiler_config = prof_cfg
+    enable_range_markers(bool(getattr(prof_cfg, "mstx", False)))
+    if cfg.get("msprobe_config") is not None and getattr(cfg["msprobe_config"], "msprobe", False):
+        worker.tensor_dump = TensorDump(cfg["msprobe_config"])
+        worker.tensor_dump.save_configs({"actor": actor_config, "rl": rl_config, "generate": generate_config})
+    seed_all(actor_config.seed or 1234, deterministic=bool(getattr(actor_config, "use_deter_comp", False)))
     world = dist.get_world_size() if dist.is_initialized() else 1
     actor_group = SPMDWorkerGroup(worker, world).initialize()
     if rl_config.multi_turn_enable:

@@ -16,6 +16,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
+from ..obs.profiler import nvtx_range, profiler_start, profiler_stop
 from ..parallel.state import ParallelState, get_parallel_state
 from ..utils.pad_process import (pad_rows, padding_dict_to_tensor_dict,
                                  remove_padding_tensor_dict_to_dict, truncate_rows)
@@ -35,6 +36,29 @@ def pad_batch(ragged: Dict[str, List[torch.Tensor]], pad_id: int, multiple: int 
         else:
             out[k] = pad_rows(rows, 0)
     return out
+
+
+def profiled_stage(role: str):
+    """Wrap a worker stage with an NVTX range and, when the run's profiler config selects this
+    rank / stage / iteration, a ``torch.profiler`` session (reference hook sites:
+    ``workers/actor_hybrid_worker.py:309-313,428-429,819-823``)."""
+    def deco(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapped(self, *a, **kw):
+            prof = profiler_start(getattr(self, "profiler_config", None), role,
+                                  getattr(self, "iteration", None))
+            dump = getattr(self, "tensor_dump", None)
+            try:
+                with nvtx_range(role):
+                    return fn(self, *a, **kw)
+            finally:
+                profiler_stop(prof)
+                if dump is not None and role in ("actor_update", "critic_update"):
+                    dump.step()
+        return wrapped
+    return deco
 
 
 class BaseWorker:

@@ -28,7 +28,7 @@ from ..parallel.tp_comm import TPComm
 from ..reshard.sharding_manager import ShardingManager
 from ..rollout.engine import LLMEngine
 from ..rollout.scheduler import SamplingParams
-from .base_worker import BaseWorker
+from .base_worker import BaseWorker, profiled_stage
 
 
 def _now() -> float:
@@ -208,6 +208,7 @@ class IntegratedWorker(BaseWorker):
             self.update_metrics("timing/resharding_to_infer", [getattr(self, "_t_enter", 0.0) + t_exit])
             self._held_infer = False
 
+    @profiled_stage("actor_generate")
     def generate_sequences(self) -> None:
         rl = self.rl_config
         held = getattr(self, "_held_infer", False)
@@ -320,6 +321,7 @@ class IntegratedWorker(BaseWorker):
             self.collect_transfer_dock_data({out_column: lp}, idx, lengths=batch["response_length"])
         self.update_metrics(timing_key, [round(_now(), 4), round(start, 4)])
 
+    @profiled_stage("reference_compute_log_prob")
     def compute_ref_log_prob(self) -> None:
         if self.reference is None:
             raise RuntimeError("this worker was built without a reference model")
@@ -329,6 +331,7 @@ class IntegratedWorker(BaseWorker):
         self.update_metrics("end_time/reference", [round(_now(), 4)])
         self.sharding_manager.exit_forward_mode()
 
+    @profiled_stage("actor_compute_log_prob")
     def compute_log_prob(self) -> None:
         self.sharding_manager.enter_forward_mode()
         self._logprob_stage("actor_log_prob", self.actor, "old_log_prob",
@@ -337,6 +340,7 @@ class IntegratedWorker(BaseWorker):
         self.sharding_manager.exit_forward_mode()
 
     # ---- update ----------------------------------------------------------------------------------------
+    @profiled_stage("actor_update")
     def update(self, kl_ctrl=None, skip_actor_log_prob: bool = False) -> None:
         rl = self.rl_config
         t_reshard = self.sharding_manager.enter_train_mode()

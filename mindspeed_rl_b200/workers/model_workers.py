@@ -19,7 +19,7 @@ from ..optim.distributed_optimizer import DistributedOptimizer, OptimizerParamSc
 from ..parallel.ddp import DistributedDataParallel
 from ..parallel.tp_comm import TPComm
 from ..reshard.sharding_manager import GradBufferOffloader, ParamOffloader
-from .base_worker import BaseWorker
+from .base_worker import BaseWorker, profiled_stage
 
 
 class _ModelWorker(BaseWorker):
@@ -157,6 +157,7 @@ class ReferenceWorker(_ModelWorker):
     """Frozen policy copy -> ``ref_log_prob``."""
     role = "reference"
 
+    @profiled_stage("reference_compute_log_prob")
     def compute_ref_log_prob(self) -> None:
         self._forward_stage("ref_log_prob", "ref_log_prob", self.rl_config.ref_dispatch_size,
                             "timing/reference_model")
@@ -179,10 +180,12 @@ class CriticWorker(_ModelWorker):
     trainable = True
     value_head = True
 
+    @profiled_stage("critic_compute_values")
     def compute_values(self) -> None:
         self._forward_stage("critic_compute_values", "values", self.rl_config.critic_value_dispatch_size,
                             "timing/critic_model")
 
+    @profiled_stage("critic_update")
     def update_critic(self) -> None:
         rl = self.rl_config
         columns = ["responses", "advantages", "values", "returns", "input_ids", "response_length", "prompt_length"]
