@@ -74,8 +74,10 @@ class DistributedOptimizer:
                  eps: float = 1e-8, weight_decay: float = 0.01, clip_grad: float = 1.0,
                  dp_group=None, dp_rank: int = 0, model_parallel_group=None,
                  offload_to_host: bool = False, swap_chunks: int = 16,
-                 norm_duplicate_filter=None):
+                 norm_duplicate_filter=None, tp_rank: int = 0):
         self.buffers = buffers
+        self.tp_rank = tp_rank
+        self._rep_ranges = None
         self.param_groups = [dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)]
         self.clip_grad = clip_grad
         self.dp_group, self.dp_rank = dp_group, dp_rank
@@ -111,6 +113,23 @@ class DistributedOptimizer:
         for b in self.buffers:
             b.zero_grad()
 
+    _REPLICATED_SUFFIXES = ("layernorm.weight", "router.weight", "rm_head.weight", "rm_head.bias")
+
+    def _replicated_ranges(self):
+        """``(buffer index, lo, hi)`` element ranges of TP-replicated parameters inside this DP
+        rank's shard (cached; the layout never changes)."""
+        if self._rep_ranges is None:
+            out = []
+            for bi, buf in enumerate(self.buffers):
+                s, e = buf.shard_range(self.dp_rank)
+                for p, slot in zip(buf.params, buf.slots):
+                    if slot.name.endswith(self._REPLICATED_SUFFIXES) or getattr(p, "tp_replicated", False):
+                        lo, hi = max(slot.start, s), min(slot.start + slot.numel, e)
+                        if lo < hi:
+                            out.append((bi, lo, hi))
+            self._rep_ranges = out
+        return self._rep_ranges
+
     def _grad_shard(self, buf: ParamAndGradBuffer) -> torch.Tensor:
         s, e = buf.shard_range(self.dp_rank)
         return buf.grad_data[s:e]
@@ -120,6 +139,12 @@ class DistributedOptimizer:
         self._sumsq.zero_()
         for buf in self.buffers:
             ops.sumsq_accumulate(self._grad_shard(buf), self._sumsq)
+        if self.tp_rank > 0:
+            # parameters replicated over TP must count once: the other TP ranks drop their copies
+            dup = torch.zeros_like(self._sumsq)
+            for bi, lo, hi in self._replicated_ranges():
+                ops.sumsq_accumulate(self.buffers[bi].grad_data[lo:hi], dup)
+            self._sumsq -= dup
         if dist.is_available() and dist.is_initialized():
             if self.dp_group is not None and buffers_dp(self.buffers) > 1:
                 dist.all_reduce(self._sumsq, group=self.dp_group)

@@ -172,6 +172,36 @@ class DistributedDataParallel(nn.Module):
         for b in self.buffers:
             b.zero_grad()
 
+    # names of replicated parameters whose gradient is a partial sum over the TP ranks
+    _TP_PARTIAL_ALWAYS = ("q_layernorm.weight", "k_layernorm.weight")          # each rank sees its own heads
+    # norms run on the local token shard (routers and the value head run on gathered tokens)
+    _TP_PARTIAL_WITH_SP = ("input_layernorm.weight", "pre_mlp_layernorm.weight", "final_layernorm.weight")
+
+    def attach_tensor_parallel(self, tp_group, tp_size: int, sequence_parallel: bool) -> None:
+        """Register the TP group so that ``finish_grad_sync`` can sum the gradients of replicated
+        parameters that every TP rank computed from only its own heads / tokens (Megatron does
+        the same for layer-norm gradients under sequence parallelism)."""
+        self.tp_group, self.tp_size, self.tp_sequence_parallel = tp_group, tp_size, sequence_parallel
+
+    def _tp_partial_grads(self) -> List[torch.Tensor]:
+        pats = self._TP_PARTIAL_ALWAYS + (self._TP_PARTIAL_WITH_SP if getattr(self, "tp_sequence_parallel", False)
+                                          else ())
+        out = []
+        for b in self.buffers:
+            for p, slot in zip(b.params, b.slots):
+                if getattr(p, "tp_reduce_grad", False) or slot.name.endswith(pats):
+                    out.append(p.main_grad)
+        return out
+
     def finish_grad_sync(self, to_shards: bool = False) -> None:
+        if getattr(self, "tp_size", 1) > 1 and self.tp_group is not None:
+            grads = self._tp_partial_grads()
+            if grads:
+                flat = torch.cat([g.reshape(-1).float() for g in grads])
+                dist.all_reduce(flat, group=self.tp_group)
+                off = 0
+                for g in grads:
+                    g.copy_(flat[off:off + g.numel()].view_as(g))
+                    off += g.numel()
         for b in self.buffers:
             b.reduce_grads(self.dp_group, average=True, to_shards=to_shards)

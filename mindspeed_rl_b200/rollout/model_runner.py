@@ -50,8 +50,12 @@ class KVCache:
     def __init__(self, num_layers: int, num_blocks: int, block_size: int, nkv: int, hd: int,
                  dtype, device):
         shape = (num_layers, num_blocks, block_size, nkv, hd)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        # uninitialised on the GPU: a slot is always written before any attention reads it, and
+        # zero-filling tens of GB costs ~10 ms per rollout phase.  (The CPU reference path
+        # gathers whole blocks, so it keeps the zero fill.)
+        alloc = torch.empty if torch.device(device).type == "cuda" else torch.zeros
+        self.k = alloc(shape, dtype=dtype, device=device)
+        self.v = alloc(shape, dtype=dtype, device=device)
         self.num_blocks, self.block_size = num_blocks, block_size
 
     @staticmethod

@@ -66,11 +66,12 @@ class _ModelWorker(BaseWorker):
         if self.trainable:
             self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
                                                  grad_in_fp32=bool(mc.accumulate_allreduce_grads_in_fp32))
+            self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(mc.sequence_parallel))
             self.optimizer = DistributedOptimizer(
                 self.model.buffers, lr=mc.lr or 1e-6, betas=(mc.adam_beta1, mc.adam_beta2),
                 weight_decay=mc.weight_decay, clip_grad=mc.clip_grad, dp_group=ps.group("dp_cp"),
                 dp_rank=ps.rank_in("dp_cp"), model_parallel_group=ps.group("mp"),
-                offload_to_host=bool(mc.swap_optimizer))
+                offload_to_host=bool(mc.swap_optimizer), tp_rank=ps.rank_in("tp"))
             self.scheduler = OptimizerParamScheduler(self.optimizer, mc.lr or 1e-6, mc.min_lr or 0.0, 0,
                                                      max(mc.train_iters or 1, 1), mc.lr_decay_style or "constant")
             self.engine = TrainingEngine(self.model, self.optimizer, self.scheduler, role=self.role,

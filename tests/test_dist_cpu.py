@@ -229,3 +229,44 @@ def test_launch_grpo_tp2_rollout_tp1_reshard():
 
 def test_launch_grpo_dp2():
     run_distributed(_launch_worker, 2, 1, 1)
+
+
+def _tp_grad_sync_worker(rank, world):
+    """SP + QK-norm: replicated parameters' gradients are summed over TP by ``finish_grad_sync`` and
+    the optimizer's global gradient norm counts them once."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+    ps = initialize_model_parallel(tensor_model_parallel_size=world)
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, add_qkv_bias=True, qk_layernorm=True, params_dtype=torch.float32,
+              max_position_embeddings=128)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=5)
+    cfg = TransformerConfig(tensor_model_parallel_size=world, sequence_parallel=True, **kw)
+    comm = TPComm(ps.group("tp"), True, world_size=world, rank=rank)
+    core = GPTModel(cfg, comm, device="cpu")
+    core.load_state_dict(_shard_state(full.state_dict(), cfg, world, rank))
+    model = DistributedDataParallel(core, None, 1)
+    model.attach_tensor_parallel(ps.group("tp"), world, True)
+    opt = DistributedOptimizer(model.buffers, lr=0.0, clip_grad=1e9, model_parallel_group=ps.group("tp"),
+                               tp_rank=rank)
+    meta = PackedMeta.from_lengths([6, 10], "cpu", align=world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator().manual_seed(1)
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    (full.forward_logprob(ids, labels, meta, 1.0, False)[0] * w).sum().backward()
+    (core.forward_logprob(ids, labels, meta, 1.0, False)[0] * w).sum().backward()
+    model.finish_grad_sync()
+    want = _shard_state({n: p.grad for n, p in full.named_parameters()}, cfg, world, rank)
+    for n, p in core.named_parameters():
+        assert torch.allclose(p.main_grad, want[n], atol=2e-4, rtol=1e-3), (n, (p.main_grad - want[n]).abs().max())
+    full_norm = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in full.parameters()))
+    norm = torch.sqrt(opt.compute_grad_norm())
+    assert torch.allclose(norm.reshape(()), full_norm, rtol=1e-4), (float(norm), float(full_norm))
+
+
+def test_tp_replicated_grad_sync_and_norm():
+    run_distributed(_tp_grad_sync_worker, 2)
