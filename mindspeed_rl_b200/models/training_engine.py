@@ -91,8 +91,9 @@ class TrainingEngine:
                  dynamic_max_batch_size: Optional[int] = None, pad_multiple: int = 1, dp_group=None,
                  dp_size: int = 1, device=None, forward_micro_batch_size: Optional[int] = None,
                  want_entropy: Optional[bool] = None, forward_backward_func: Optional[Callable] = None,
-                 **loss_options):
+                 pipeline=None, **loss_options):
         self.model = model
+        self.pipeline = pipeline             # parallel.pipeline.PipelineSchedule when PP > 1
         self.core: GPTModel = _unwrap(model)
         self.optimizer, self.opt_param_scheduler = optimizer, opt_param_scheduler
         self.stage, self.role = stage, role
@@ -133,18 +134,26 @@ class TrainingEngine:
         parts = rearrange_micro_batches(lens, budget, self.dynamic_max_batch_size, self.dp_group)
         return [[rows[i] for i in p] for p in parts if p]
 
-    def _run_model(self, mb: MicroBatch, want_entropy: bool):
-        """Returns the role's per-response-token outputs ``[b, R]`` (autograd-connected)."""
+    def _run_model(self, mb: MicroBatch, want_entropy: bool, h_in: Optional[torch.Tensor] = None):
+        """Returns the role's per-response-token outputs ``[b, R]`` (autograd-connected).
+        ``h_in``: hidden states received from the previous pipeline stage (``None`` on the first)."""
         core = self.core
+        x = mb.ids if h_in is None else h_in
         if self.loss_func.output_kind == "value":
-            v = core.forward_values(mb.ids, mb.meta())
+            v = core.forward_values(x, mb.meta())
             if self.role == "reward":
                 return v[mb.last_index].unsqueeze(-1), None
             return v[mb.resp_index] * mb.resp_valid, None
-        logp, ent = core.forward_logprob(mb.ids, mb.labels, mb.meta(), self.temperature, want_entropy)
+        logp, ent = core.forward_logprob(x, mb.labels, mb.meta(), self.temperature, want_entropy)
         lp = logp[mb.resp_index] * mb.resp_valid
         en = ent[mb.resp_index] * mb.resp_valid if want_entropy else None
         return lp, en
+
+    def _stage_forward(self, mb: MicroBatch, h_in: Optional[torch.Tensor], want_entropy: bool):
+        """One pipeline stage: hidden states for inner stages, role outputs on the last stage."""
+        if not self.core.post_process:
+            return self.core.hidden_states(mb.ids if h_in is None else h_in, mb.meta())
+        return self._run_model(mb, want_entropy, h_in)
 
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -155,10 +164,17 @@ class TrainingEngine:
         width = 1 if self.role == "reward" else data["responses"].shape[1]
         out = torch.zeros(n, width, dtype=torch.float32)
         results = []
-        for rows in self._split(data, list(range(n)), update=False):
-            mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
-            vals, _ = self._run_model(mb, want_entropy=False)
-            results.append((rows, vals.float()))
+        if self.pipeline is not None:
+            mbs = [MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
+                   for rows in self._split(data, list(range(n)), update=False)]
+            outs = self.pipeline.forward_only(mbs, lambda m: m.num_tokens,
+                                              lambda m, h: self._stage_forward(m, h, False))
+            results = [(m.rows.tolist(), o[0].float()) for m, o in zip(mbs, outs)]
+        else:
+            for rows in self._split(data, list(range(n)), update=False):
+                mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
+                vals, _ = self._run_model(mb, want_entropy=False)
+                results.append((rows, vals.float()))
         for rows, vals in results:
             out[torch.as_tensor(rows)] = to_host(vals)
         return out
@@ -202,12 +218,12 @@ class TrainingEngine:
         parts = self._split(data, mini, update=True)
         n_micro = len(parts)
         sums: Dict[str, torch.Tensor] = {}
-        for rows in parts:
-            mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
+
+        def loss_backward(mb: MicroBatch, outputs) -> None:
+            out, ent = outputs
             scale = 1.0 / n_micro
             if self.use_dynamic_bsz:   # re-weight bins by their share of the mini-batch rows
-                scale = len(rows) / len(mini)
-            out, ent = self._run_model(mb, want_entropy=self.want_entropy)
+                scale = len(mb.rows) / len(mini)
             batch_dev = {k: to_device(v, v.dtype, self.device) for k, v in mb.data.items()
                          if k not in ("input_ids", "prompts", "responses")}
             if not self.entropy_needs_grad and ent is not None:
@@ -221,6 +237,15 @@ class TrainingEngine:
             for k, v in stats.items():
                 v = v.detach() * scale
                 sums[k] = v if k not in sums else sums[k] + v
+
+        if self.pipeline is not None:
+            mbs = [MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device) for rows in parts]
+            self.pipeline.forward_backward(mbs, lambda m: m.num_tokens,
+                                           lambda m, h: self._stage_forward(m, h, self.want_entropy), loss_backward)
+            return sums
+        for rows in parts:
+            mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
+            loss_backward(mb, self._run_model(mb, want_entropy=self.want_entropy))
         return sums
 
     def _optimizer_step(self):

@@ -114,7 +114,20 @@ class IntegratedWorker(BaseWorker):
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         tcfg = TransformerConfig.from_megatron(ac, params_dtype=dtype)
         self.tcfg = tcfg
-        core = GPTModel(tcfg, self.comm, device=self.device, seed=self.seed)
+        # pipeline stage of this rank: embedding on the first, head on the last, a slice of layers each
+        from ..parallel.pipeline import PipelineSchedule
+        from ..reshard.planner import stage_layers
+
+        pp, pp_rank = ps.size("pp"), ps.rank_in("pp")
+        stage_kw = dict(pre_process=pp_rank == 0, post_process=pp_rank == pp - 1,
+                        layer_numbers=stage_layers(tcfg.num_layers, pp, getattr(ac, "num_layer_list", None))[pp_rank])
+        self.pipeline = None
+        if pp > 1:
+            self.pipeline = PipelineSchedule(
+                ps.group("pp"), pp_rank, pp, ps.get_pipeline_model_parallel_prev_rank(),
+                ps.get_pipeline_model_parallel_next_rank(), tcfg.hidden_size, dtype, self.device,
+                seq_shard=tp if (ac.sequence_parallel and tp > 1) else 1)
+        core = GPTModel(tcfg, self.comm, device=self.device, seed=self.seed, **stage_kw)
         dp = ps.size("dp_cp")
         self._maybe_init_arena(core, bool(ac.accumulate_allreduce_grads_in_fp32))
         self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
@@ -142,7 +155,7 @@ class IntegratedWorker(BaseWorker):
         common = dict(stage=ac.stage or "ray_grpo", temperature=temperature,
                       use_dynamic_bsz=rl.use_dynamic_bsz, pad_multiple=pad_mult,
                       dp_group=ps.group("dp_cp"), dp_size=dp, device=self.device,
-                      dynamic_max_batch_size=rl.actor_dynamic_max_batch_size)
+                      dynamic_max_batch_size=rl.actor_dynamic_max_batch_size, pipeline=self.pipeline)
         self.actor = TrainingEngine(
             self.model, self.optimizer, self.scheduler, role="actor",
             micro_batch_size=ac.micro_batch_size or 1,
@@ -155,7 +168,7 @@ class IntegratedWorker(BaseWorker):
         self.reference = None
         if self.with_reference:
             rcfg = TransformerConfig.from_megatron(self.ref_config, params_dtype=dtype)
-            self.ref_model = GPTModel(rcfg, self.comm, device=self.device, seed=self.seed)
+            self.ref_model = GPTModel(rcfg, self.comm, device=self.device, seed=self.seed, **stage_kw)
             self.ref_model.load_state_dict(core.state_dict())
             for p in self.ref_model.parameters():
                 p.requires_grad_(False)
