@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (development only)")
     ap.add_argument("--pack-tokens", type=int, default=16384, help="token budget of one training micro-batch")
     ap.add_argument("--eager", action="store_true", help="disable CUDA-graph decode")
+    ap.add_argument("--keep-layers", type=int, default=0,
+                    help="layers whose activations stay resident (the others are fully recomputed in the backward)")
     return ap.parse_args()
 
 
@@ -143,7 +145,10 @@ def main():
         model=args.model, global_batch_size=gbs, micro_batch_size=8, seq_length=max_len, lr=1e-6,
         lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, adam_beta1=0.9, adam_beta2=0.95,
         stage="ray_grpo", train_iters=10 ** 6, seed=1234, bf16=True, use_distributed_optimizer=True,
-        recompute_granularity="full", reset_attention_mask=True, sequence_parallel=False), catalogue)
+        recompute_granularity="full", recompute_method="block" if args.keep_layers else None,
+        recompute_num_layers=(args.layers or catalogue[args.model]["num_layers"]) - args.keep_layers
+        if args.keep_layers else None, recompute_activation_function=True,
+        reset_attention_mask=True, sequence_parallel=False), catalogue)
     rl = RLConfig(dict(
         n_samples_per_prompt=n, mini_batch_size=gbs, epochs=1, clip_ratio=0.2, init_kl_coef=0.001,
         kl_penalty="low_var_kl", adv_estimator="group_norm", verifier_function=["contains_token_7"],
@@ -212,7 +217,8 @@ def main():
                        "global_batch": gbs, "n_samples_per_prompt": n, "seq_len": max_len,
                        "prompt_len": args.prompt_len, "response_len": f"uniform {args.min_response}-{args.max_response}",
                        "mean_response_len": mean_resp, "parallelism": f"dp{world}",
-                       "tokens_per_sec_per_gpu": value / world,
+                       "tokens_per_sec_per_gpu": value / world, "layers_not_recomputed": args.keep_layers,
+                       "peak_device_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
                        "l2": "working set >> L2: every pass streams >= 15 GB of weights",
                        "reshard_ms_per_step": sum(m.get("timing/resharding_to_infer", 0) for m in history)
                        / max(len(history), 1) * 1e3,

@@ -195,7 +195,8 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
         gu, x2g = comm.column_linear(x2, layer.mlp.linear_fc1.weight)
         y = ops.swiglu_fwd(gu)
         mlp_out = comm.row_linear(y, layer.mlp.linear_fc2.weight)
-        mlp_ctx = (gu, y) if keep else None
+        # activation-function recompute: drop silu(g)*u and rebuild it from gu in the backward
+        mlp_ctx = (gu, None if cfg.recompute_activation_function else y) if keep else None
     else:
         x2g = comm.gather_seq(x2)
         mlp_out, mlp_ctx = layer.mlp.forward_tokens(x2g, comm, keep)
@@ -214,6 +215,8 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
     # ---- MLP ----
     if isinstance(layer.mlp, MLP):
         gu, y = ctx["mlp_ctx"]
+        if y is None:
+            y = ops.swiglu_fwd(gu)
         fc1, fc2 = layer.mlp.linear_fc1.weight, layer.mlp.linear_fc2.weight
         dy, d_out = comm.row_linear_bwd(dh2, fc2)
         accum_wgrad(fc2, d_out, y)
@@ -251,7 +254,10 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
 class _LayerFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h: torch.Tensor, layer: TransformerLayer, meta: PackedMeta):
-        full_recompute = layer.cfg.recompute_granularity == "full"
+        # "full" keeps only the layer input and re-runs the forward in the backward; with
+        # recompute_method "block" that applies to the first recompute_num_layers layers of the
+        # stage only, the others keep their intermediates
+        full_recompute = layer.cfg.recompute_granularity == "full" and getattr(layer, "recompute_full", True)
         out, saved = layer_forward(layer, h, meta, keep=not full_recompute)
         ctx.layer, ctx.meta, ctx.full = layer, meta, full_recompute
         if full_recompute:
@@ -352,6 +358,9 @@ class _Decoder(nn.Module):
     def __init__(self, cfg, layer_numbers: List[int], device, gen, comm, post_process: bool):
         super().__init__()
         self.layers = nn.ModuleList([TransformerLayer(cfg, n, device, gen, comm) for n in layer_numbers])
+        block = cfg.recompute_method == "block" and cfg.recompute_num_layers is not None
+        for i, layer in enumerate(self.layers):
+            layer.recompute_full = (i < cfg.recompute_num_layers) if block else True
         if post_process:
             self.final_layernorm = _Holder(torch.ones(cfg.hidden_size, dtype=cfg.params_dtype,
                                                       device=device))

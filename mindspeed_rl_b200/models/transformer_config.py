@@ -41,6 +41,9 @@ class TransformerConfig:
     # numerics / memory
     params_dtype: torch.dtype = torch.bfloat16
     recompute_granularity: Optional[str] = "full"   # "full" -> keep only layer inputs
+    recompute_method: Optional[str] = None          # "block": only the first recompute_num_layers layers
+    recompute_num_layers: Optional[int] = None
+    recompute_activation_function: bool = False     # rebuild silu(g)*u in the backward instead of storing it
     # parallel sizes seen by the model code
     tensor_model_parallel_size: int = 1
     sequence_parallel: bool = False
@@ -102,7 +105,9 @@ class TransformerConfig:
             moe_router_group_topk=cfg.moe_router_group_topk,
             rope_scaling=rope_scaling,
             params_dtype=torch.bfloat16 if cfg.bf16 else torch.float32,
-            recompute_granularity=cfg.recompute_granularity,
+            recompute_granularity=cfg.recompute_granularity, recompute_method=cfg.recompute_method,
+            recompute_num_layers=cfg.recompute_num_layers,
+            recompute_activation_function=bool(cfg.recompute_activation_function),
             tensor_model_parallel_size=cfg.tensor_model_parallel_size,
             sequence_parallel=bool(cfg.sequence_parallel) and cfg.tensor_model_parallel_size > 1,
             expert_model_parallel_size=cfg.expert_model_parallel_size,
