@@ -68,6 +68,7 @@ class MicroBatch:
         self.rows = rows_t
         self.ids, self.labels, self.positions = ids, labels, pos.to(torch.int32)
         self.cu = cu.to(torch.int32)
+        self.cu_host = cu.clone()          # stays on the host (context-parallel index arithmetic)
         self.max_seqlen = int(padded.max()) if b else 0
         self.num_tokens = total
         self.data = {k: v[rows_t] for k, v in data.items() if torch.is_tensor(v) and v.shape[:1] == data["input_ids"].shape[:1]}
@@ -91,9 +92,12 @@ class TrainingEngine:
                  dynamic_max_batch_size: Optional[int] = None, pad_multiple: int = 1, dp_group=None,
                  dp_size: int = 1, device=None, forward_micro_batch_size: Optional[int] = None,
                  want_entropy: Optional[bool] = None, forward_backward_func: Optional[Callable] = None,
-                 pipeline=None, **loss_options):
+                 pipeline=None, context_parallel: Optional[dict] = None, **loss_options):
         self.model = model
         self.pipeline = pipeline             # parallel.pipeline.PipelineSchedule when PP > 1
+        cpi = context_parallel or {}         # {"group", "size", "rank", "algo"} when CP > 1
+        self.cp_group, self.cp_size = cpi.get("group"), int(cpi.get("size", 1) or 1)
+        self.cp_rank, self.cp_algo = int(cpi.get("rank", 0) or 0), cpi.get("algo")
         self.core: GPTModel = _unwrap(model)
         self.optimizer, self.opt_param_scheduler = optimizer, opt_param_scheduler
         self.stage, self.role = stage, role
@@ -139,6 +143,23 @@ class TrainingEngine:
         ``h_in``: hidden states received from the previous pipeline stage (``None`` on the first)."""
         core = self.core
         x = mb.ids if h_in is None else h_in
+        cp = self._context_parallel(mb)
+        if cp is not None:
+            # every CP rank runs its own tokens of every sequence; per-token outputs are gathered
+            # back into packed order before the response positions are picked
+            if h_in is None:
+                x = cp.take_local(mb.ids)
+            meta = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(mb.positions), cp=cp)
+            if self.loss_func.output_kind == "value":
+                v = cp.gather_tokens(core.forward_values(x, meta))
+                if self.role == "reward":
+                    return v[mb.last_index].unsqueeze(-1), None
+                return v[mb.resp_index] * mb.resp_valid, None
+            logp, ent = core.forward_logprob(x, cp.take_local(mb.labels), meta, self.temperature, want_entropy)
+            logp = cp.gather_tokens(logp)
+            lp = logp[mb.resp_index] * mb.resp_valid
+            en = cp.gather_tokens(ent)[mb.resp_index] * mb.resp_valid if want_entropy else None
+            return lp, en
         if self.loss_func.output_kind == "value":
             v = core.forward_values(x, mb.meta())
             if self.role == "reward":
@@ -152,8 +173,24 @@ class TrainingEngine:
     def _stage_forward(self, mb: MicroBatch, h_in: Optional[torch.Tensor], want_entropy: bool):
         """One pipeline stage: hidden states for inner stages, role outputs on the last stage."""
         if not self.core.post_process:
-            return self.core.hidden_states(mb.ids if h_in is None else h_in, mb.meta())
+            cp = self._context_parallel(mb)
+            if cp is None:
+                return self.core.hidden_states(mb.ids if h_in is None else h_in, mb.meta())
+            meta = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(mb.positions), cp=cp)
+            return self.core.hidden_states(cp.take_local(mb.ids) if h_in is None else h_in, meta)
         return self._run_model(mb, want_entropy, h_in)
+
+    def _context_parallel(self, mb: MicroBatch):
+        """Context-parallel helper of this micro-batch (cached on it), ``None`` without CP."""
+        if self.cp_size <= 1:
+            return None
+        cp = getattr(mb, "_cp", None)
+        if cp is None:
+            from ..parallel.context_parallel import ContextParallel
+
+            cp = ContextParallel(self.cp_group, self.cp_size, self.cp_rank, self.cp_algo, mb.cu_host, self.device)
+            mb._cp = cp
+        return cp
 
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -167,7 +204,7 @@ class TrainingEngine:
         if self.pipeline is not None:
             mbs = [MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
                    for rows in self._split(data, list(range(n)), update=False)]
-            outs = self.pipeline.forward_only(mbs, lambda m: m.num_tokens,
+            outs = self.pipeline.forward_only(mbs, lambda m: m.num_tokens // self.cp_size,
                                               lambda m, h: self._stage_forward(m, h, False))
             results = [(m.rows.tolist(), o[0].float()) for m, o in zip(mbs, outs)]
         else:
@@ -240,7 +277,7 @@ class TrainingEngine:
 
         if self.pipeline is not None:
             mbs = [MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device) for rows in parts]
-            self.pipeline.forward_backward(mbs, lambda m: m.num_tokens,
+            self.pipeline.forward_backward(mbs, lambda m: m.num_tokens // self.cp_size,
                                            lambda m, h: self._stage_forward(m, h, self.want_entropy), loss_backward)
             return sums
         for rows in parts:

@@ -1,0 +1,149 @@
+"""Context parallelism: shard every packed sequence over the CP group and run attention on it.
+
+Token split (what each CP rank keeps of a packed stream whose sequences are padded to a multiple
+of ``2 * cp``): the *zig-zag* layout of the ring algorithm (chunks ``r`` and ``2cp-1-r`` of every
+sequence, which balances causal work; reference ``mindspeed_rl/utils/context_parallel.py:6-163``)
+or contiguous chunks for the Ulysses algorithm.  Everything outside attention is token-wise and
+runs on the local tokens unchanged.
+
+Attention runs head-parallel: an all-to-all over the CP group turns ``[local tokens, all heads]``
+into ``[all tokens, heads / cp]`` (tokens restored to sequence order, so the ordinary packed
+causal flash-attention kernel applies with the original ``cu_seqlens``), and a second all-to-all
+brings the result back.  This is the Ulysses exchange; it is also used for the zig-zag layout
+whenever the (TP-local) KV heads divide by ``cp``, because on one NVSwitch domain an all-to-all of
+activations costs the same bytes as the ring's KV rotation without serialising ``cp`` steps.
+
+Per-token outputs (log-probs, values) are all-gathered and put back in global order; in the
+backward every rank keeps the gradient of its own tokens, scaled by ``cp`` because the
+data-parallel averaging that follows divides by ``dp * cp``.
+"""
+from __future__ import annotations
+
+from typing import Any, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import QKVLayout
+
+RING, ULYSSES, HYBRID = "megatron_cp_algo", "ulysses_cp_algo", "hybrid_cp_algo"
+
+
+def split_index(cu_padded: torch.Tensor, cp_size: int, cp_rank: int, zigzag: bool) -> torch.Tensor:
+    """Global packed positions kept by ``cp_rank`` (int64, host), ascending within each piece."""
+    cu = cu_padded.to(torch.int64).tolist()
+    pieces = []
+    for s, e in zip(cu[:-1], cu[1:]):
+        n = e - s
+        if zigzag:
+            c = n // (2 * cp_size)
+            if c * 2 * cp_size != n:
+                raise ValueError(f"sequence length {n} is not a multiple of 2*cp = {2 * cp_size}")
+            pieces.append(torch.arange(s + cp_rank * c, s + (cp_rank + 1) * c))
+            pieces.append(torch.arange(e - (cp_rank + 1) * c, e - cp_rank * c))
+        else:
+            c = n // cp_size
+            if c * cp_size != n:
+                raise ValueError(f"sequence length {n} is not a multiple of cp = {cp_size}")
+            pieces.append(torch.arange(s + cp_rank * c, s + (cp_rank + 1) * c))
+    return torch.cat(pieces) if pieces else torch.empty(0, dtype=torch.int64)
+
+
+class _GatherTokens(torch.autograd.Function):
+    """[T_local, ...] -> [T, ...] in global order; backward keeps the local rows (x cp)."""
+
+    @staticmethod
+    def forward(ctx, x, cp: "ContextParallel"):
+        ctx.cp = cp
+        parts = [torch.empty_like(x) for _ in range(cp.size)]
+        dist.all_gather(parts, x.contiguous(), group=cp.group)
+        return torch.cat(parts, 0)[cp.restore]
+
+    @staticmethod
+    def backward(ctx, d):
+        cp = ctx.cp
+        return d[cp.local_index_dev] * float(cp.size), None
+
+
+class ContextParallel:
+    def __init__(self, group, size: int, rank: int, algo: str, cu_padded: torch.Tensor, device):
+        self.group, self.size, self.rank, self.algo = group, size, rank, algo or RING
+        self.device = torch.device(device)
+        self.cu_full = cu_padded.to(torch.int32)
+        zigzag = self.algo != ULYSSES
+        per_rank = [split_index(cu_padded.cpu(), size, r, zigzag) for r in range(size)]
+        self.local_index = per_rank[rank]
+        order = torch.cat(per_rank)                     # rank-major order -> global position
+        restore = torch.empty_like(order)
+        restore[order] = torch.arange(order.numel())
+        self.order_dev = order.to(self.device)          # gathered[i] is global token order[i]
+        self.restore = restore.to(self.device)          # gathered[restore] is in global order
+        self.local_index_dev = self.local_index.to(self.device)
+        lens = (cu_padded[1:] - cu_padded[:-1]).to(torch.int64) // size
+        cu_local = torch.zeros(lens.numel() + 1, dtype=torch.int32)
+        cu_local[1:] = torch.cumsum(lens, 0)
+        self.cu_local = cu_local.to(self.device)
+        self.max_local = int(lens.max()) if lens.numel() else 0
+        self.max_full = int((cu_padded[1:] - cu_padded[:-1]).max()) if lens.numel() else 0
+        self.cu_full_dev = self.cu_full.to(self.device)
+
+    # ---- token plumbing -----------------------------------------------------------------------------
+    def take_local(self, t: torch.Tensor) -> torch.Tensor:
+        return t[self.local_index_dev.to(t.device)]
+
+    def gather_tokens(self, x_local: torch.Tensor) -> torch.Tensor:
+        if torch.is_grad_enabled() and x_local.requires_grad:
+            return _GatherTokens.apply(x_local, self)
+        return _GatherTokens.forward(_Dummy(), x_local, self)
+
+    # ---- attention ------------------------------------------------------------------------------------
+    def _a2a(self, x: torch.Tensor, to_heads: bool) -> torch.Tensor:
+        """``to_heads``: [T_local, H, d] -> [T_full (global order), H/cp, d]; else the inverse."""
+        c = self.size
+        if to_heads:
+            tl, h, d = x.shape
+            send = x.reshape(tl, c, h // c, d).permute(1, 0, 2, 3).contiguous()     # [c, T_l, H/c, d]
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=self.group)
+            return recv.reshape(c * tl, h // c, d)[self.restore]
+        t, hc, d = x.shape
+        tl = t // c
+        send = x[self.order_dev].reshape(c, tl, hc, d).contiguous()                # rank-major token blocks
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        return recv.permute(1, 0, 2, 3).reshape(tl, c * hc, d)
+
+    def _head_layout(self, lay: QKVLayout) -> QKVLayout:
+        if lay.num_kv_heads % self.size or lay.num_heads % self.size:
+            raise NotImplementedError(
+                f"context parallel size {self.size} must divide the local head counts "
+                f"({lay.num_heads} query / {lay.num_kv_heads} key-value heads)")
+        return QKVLayout(lay.num_heads // self.size, lay.num_kv_heads // self.size, lay.head_dim, interleaved=False)
+
+    def attention_fwd(self, qkv: torch.Tensor, lay: QKVLayout, meta) -> Tuple[torch.Tensor, Any]:
+        hl = self._head_layout(lay)
+        q, k, v = lay.split(qkv)
+        # GQA: query heads of a KV group must land on the rank that gets that KV head
+        qf, kf, vf = self._a2a(q.contiguous(), True), self._a2a(k.contiguous(), True), self._a2a(v.contiguous(), True)
+        t = qf.shape[0]
+        packed = torch.cat([qf, kf, vf], dim=1).reshape(t, hl.width).contiguous()
+        out, lse = ops.attn_varlen_fwd(packed, hl, self.cu_full_dev, self.max_full, causal=True)
+        back = self._a2a(out.view(t, hl.num_heads, hl.head_dim), False)
+        return back.reshape(qkv.shape[0], lay.num_heads * lay.head_dim), (packed, out, lse, hl)
+
+    def attention_bwd(self, dattn: torch.Tensor, qkv: torch.Tensor, attn: torch.Tensor, saved: Any, lay: QKVLayout,
+                      meta) -> torch.Tensor:
+        packed, out, lse, hl = saved
+        tl = qkv.shape[0]
+        d_out = self._a2a(dattn.reshape(tl, lay.num_heads, lay.head_dim).contiguous(), True)
+        t = d_out.shape[0]
+        d_packed = ops.attn_varlen_bwd(d_out.reshape(t, -1).contiguous(), packed, out, lse, hl, self.cu_full_dev,
+                                       self.max_full, causal=True)
+        dq, dk, dv = hl.split(d_packed)
+        dq, dk, dv = self._a2a(dq.contiguous(), False), self._a2a(dk.contiguous(), False), self._a2a(dv.contiguous(), False)
+        return lay.merge(dq, dk, dv)
+
+
+class _Dummy:
+    """Stand-in autograd context for the no-grad path of ``_GatherTokens``."""

@@ -155,7 +155,9 @@ class IntegratedWorker(BaseWorker):
         common = dict(stage=ac.stage or "ray_grpo", temperature=temperature,
                       use_dynamic_bsz=rl.use_dynamic_bsz, pad_multiple=pad_mult,
                       dp_group=ps.group("dp_cp"), dp_size=dp, device=self.device,
-                      dynamic_max_batch_size=rl.actor_dynamic_max_batch_size, pipeline=self.pipeline)
+                      dynamic_max_batch_size=rl.actor_dynamic_max_batch_size, pipeline=self.pipeline,
+                      context_parallel=dict(group=ps.group("cp"), size=ps.size("cp"), rank=ps.rank_in("cp"),
+                                            algo=ac.context_parallel_algo) if ps.size("cp") > 1 else None)
         self.actor = TrainingEngine(
             self.model, self.optimizer, self.scheduler, role="actor",
             micro_batch_size=ac.micro_batch_size or 1,
@@ -189,6 +191,14 @@ class IntegratedWorker(BaseWorker):
 
             resharder = Resharder.for_worker(self, gc)
             self.engine = resharder.engine
+        # rank layout of the rollout phase: context-parallel ranks hold identical weights and act
+        # as independent rollout replicas, so dispatch follows a (rollout-TP x DP) layout
+        self.rollout_state = resharder.infer_state if resharder is not None else None
+        if self.rollout_state is None and ps.size("cp") > 1:
+            from ..parallel.state import ParallelState, RankLayout
+
+            self.rollout_state = ParallelState(RankLayout(ps.layout.world_size, tp=tp), ps.rank, backend=ps.backend,
+                                               rank_offset=ps.rank_offset)
         self.sharding_manager = ShardingManager(
             self.model, self.engine, self.optimizer, offload_train_optimizer=gc.offload_train_optimizer,
             offload_train_grad=gc.offload_train_grad, offload_train_param=gc.offload_train_param,
@@ -235,9 +245,9 @@ class IntegratedWorker(BaseWorker):
         start = _now()
         n = rl.n_samples_per_prompt
         train_state = self._state
-        if self.sharding_manager.resharder is not None:
+        if getattr(self, "rollout_state", None) is not None:
             # rollout replicas are (infer-TP)-sized: dispatch / write-back follow the rollout layout
-            self._state = self.sharding_manager.resharder.infer_state
+            self._state = self.rollout_state
         try:
             while True:
                 batch, idx, finished = self.dispatch_transfer_dock_data(

@@ -349,6 +349,42 @@ def test_pipeline_1f1b_matches_single_process():
     run_distributed(_pp_worker, 4, 2)        # fewer micro-batches than stages
 
 
+def _cp_worker(rank, world, algo):
+    """Context parallel (zig-zag or contiguous split, head-parallel attention) == single process."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.context_parallel import ContextParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    ps = initialize_model_parallel(context_parallel_size=world)
+    cfg = TransformerConfig(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4,
+                            num_query_groups=2, vocab_size=64, add_qkv_bias=True, params_dtype=torch.float32,
+                            max_position_embeddings=128)
+    full = GPTModel(cfg, device="cpu", seed=5)
+    model = GPTModel(cfg, device="cpu", seed=5)
+    meta = PackedMeta.from_lengths([6, 13, 4], "cpu", align=2 * world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator().manual_seed(1)
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    ref_lp, _ = full.forward_logprob(ids, labels, meta, 1.0, False)
+    (ref_lp * w).sum().backward()
+    cp = ContextParallel(ps.group("cp"), world, rank, algo, meta.cu_seqlens.to(torch.int64), "cpu")
+    assert cp.local_index.numel() == t // world
+    m_local = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(meta.positions), cp=cp)
+    lp_l, _ = model.forward_logprob(cp.take_local(ids), cp.take_local(labels), m_local, 1.0, False)
+    lp = cp.gather_tokens(lp_l)
+    assert torch.allclose(lp, ref_lp, atol=1e-5), (lp - ref_lp).abs().max()
+    (lp * w).sum().backward()
+    for (n, p), q in zip(model.named_parameters(), full.parameters()):
+        gr = p.grad.clone()
+        dist.all_reduce(gr)
+        assert torch.allclose(gr / world, q.grad, atol=2e-5, rtol=1e-4), (n, (gr / world - q.grad).abs().max())
+
+
+def test_context_parallel_matches_single_process():
+    run_distributed(_cp_worker, 2, "megatron_cp_algo")
+    run_distributed(_cp_worker, 2, "ulysses_cp_algo")
+
+
 def _launch_pp_worker(rank, world):
     from mindspeed_rl_b200.config import compose
     from mindspeed_rl_b200.runtime.launch import run_rl
