@@ -81,7 +81,17 @@ struct DecodeParams {
   float* part_ml;           // scratch [B, nh, nsplit, 2]  (m in exp2 domain, l)
   int max_blocks, block_size, nh, nkv, nsplit;
   float scale_log2;
+  // shared-prefix (grouped) decode: sequences that share their first key_start[b] keys with the
+  // other members of their group skip those keys here; the group kernel covers them once.
+  const int* key_start;     // [B] or nullptr
+  int slot_base;            // first partial slot this kernel writes
+  int slot_total;           // partial slots per (b, head); 1 = write `out` directly
+  const int* group_rows;    // [n_groups, kGroupMax] batch rows (-1 = empty)
+  const int* group_prefix;  // [n_groups] shared keys of the group
+  int npre;                 // prefix splits (slots 0 .. npre-1)
 };
+
+constexpr int kGroupMax = 8;
 
 template <int D>
 __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeParams p) {
@@ -97,9 +107,10 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeParams p)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int frow = lane >> 2, fcol = (lane & 3) * 2;
 
-  int per_split = (ctx + p.nsplit - 1) / p.nsplit;
+  const int k0 = (p.key_start != nullptr) ? min(p.key_start[b], ctx) : 0;
+  int per_split = (ctx - k0 + p.nsplit - 1) / p.nsplit;
   per_split = ((per_split + CH - 1) / CH) * CH;
-  const int kbeg = sp * per_split;
+  const int kbeg = k0 + sp * per_split;
   const int kend = min(ctx, kbeg + per_split);
   const int n_chunks = (kend > kbeg) ? (kend - kbeg + CH - 1) / CH : 0;
 
@@ -248,11 +259,11 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeParams p)
       o += sO[(w * 16 + r) * D + d] * c;
     }
     const int h = hk * rep + r;
-    if (p.nsplit == 1) {
+    if (p.slot_total == 1) {
       p.out[(long long)b * p.out_stride + (long long)h * D + d] =
           __float2bfloat16(l > 0.f ? o / l : 0.f);
     } else {
-      const long long pi = ((long long)b * p.nh + h) * p.nsplit + sp;
+      const long long pi = ((long long)b * p.nh + h) * p.slot_total + p.slot_base + sp;
       p.part_o[pi * D + d] = o;
       if (d == 0) {
         p.part_ml[pi * 2] = m;
@@ -262,23 +273,199 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeParams p)
   }
 }
 
+// Shared-prefix pass of grouped decode.  The n samples of one prompt share the prompt's KV
+// blocks; instead of streaming them once per sample, one CTA handles a whole group for one KV
+// head: the query rows of all members (members x heads-per-KV-head <= 64 rows, 16 per warp) run
+// against each 64-key chunk of the shared prefix, which is therefore read from HBM once per group.
+// Grid (group, kv head, prefix split); partial results go to slots [0, npre) of every member and
+// are merged with the members' own suffix partials by the merge kernel.
+template <int D>
+__global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodeParams p) {
+  constexpr int CH = 64, LD = D + 8, THREADS = 128, ROWS = 64;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // 64 x LD
+  __nv_bfloat16* sK = sQ + ROWS * LD;                               // 2 x CH x LD
+  __nv_bfloat16* sV = sK + 2 * CH * LD;                             // 2 x CH x LD
+
+  const int g = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
+  const int rep = p.nh / p.nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int frow = lane >> 2, fcol = (lane & 3) * 2;
+  const int* rows = p.group_rows + (long long)g * kGroupMax;
+  const int prefix = p.group_prefix[g];
+  const int lead = rows[0];
+  if (lead < 0) return;   // unused group slot (uniform for the whole CTA)
+
+  int per_split = (prefix + p.npre - 1) / p.npre;
+  per_split = ((per_split + CH - 1) / CH) * CH;
+  const int kbeg = sp * per_split;
+  const int kend = min(prefix, kbeg + per_split);
+  const int n_chunks = (kend > kbeg) ? (kend - kbeg + CH - 1) / CH : 0;
+
+  // query rows: row = member * rep + head-in-group
+  for (int i = threadIdx.x; i < ROWS * (D / 8); i += THREADS) {
+    const int r = i / (D / 8), c = i % (D / 8);
+    const int mem = r / rep;
+    const int b = (mem < kGroupMax) ? rows[mem] : -1;
+    const bool ok = b >= 0;
+    const __nv_bfloat16* src = p.q + head_offset(p.Lq, ok ? b : lead, hk * rep + r % rep) + c * 8;
+    cp_async16(sQ + r * LD + c * 8, src, ok);
+  }
+  const int* bt = p.block_tables + (long long)lead * p.max_blocks;
+  auto issue = [&](int chunk, int stage) {
+    const int base = kbeg + chunk * CH;
+    for (int i = threadIdx.x; i < CH * (D / 8); i += THREADS) {
+      const int r = i / (D / 8), c = i % (D / 8);
+      const int key = base + r;
+      const bool ok = key < kend;
+      const int kk = ok ? key : kbeg;
+      const int blk = bt[kk / p.block_size];
+      const long long src = (((long long)blk * p.block_size + kk % p.block_size) * p.nkv + hk) * D + c * 8;
+      cp_async16(sK + (stage * CH + r) * LD + c * 8, p.k_cache + src, ok);
+      cp_async16(sV + (stage * CH + r) * LD + c * 8, p.v_cache + src, ok);
+    }
+  };
+  if (n_chunks > 0) issue(0, 0);
+  cp_async_commit();
+
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const __nv_bfloat16* tQ = sQ + warp * 16 * LD;   // this warp's 16 query rows
+
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int st = ch & 1;
+    if (ch + 1 < n_chunks) {
+      issue(ch + 1, st ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float s[CH / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < CH / 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[nt][j] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, smem_u32(tQ + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+      for (int kt = 0; kt < CH / 16; ++kt) {
+        uint32_t bfr[4];
+        const __nv_bfloat16* tK = sK + (st * CH + kt * 16) * LD;
+        ldmatrix_x4(bfr, smem_u32(tK + ((lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8));
+        mma_16816(s[2 * kt], a, bfr[0], bfr[1]);
+        mma_16816(s[2 * kt + 1], a, bfr[2], bfr[3]);
+      }
+    }
+    const int key0 = kbeg + ch * CH;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < CH / 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = key0 + nt * 8 + fcol + (j & 1);
+        const float v = (key < kend) ? s[nt][j] * p.scale_log2 : -INFINITY;
+        s[nt][j] = v;
+        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+      }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+      corr[r] = exp2f(m_run[r] - m_use[r]);
+      m_run[r] = m_new;
+    }
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < CH / 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float e = exp2f(s[nt][j] - m_use[j >> 1]);
+        s[nt][j] = e;
+        rs[j >> 1] += e;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + rs[r];
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      o_acc[dt][0] *= corr[0];
+      o_acc[dt][1] *= corr[0];
+      o_acc[dt][2] *= corr[1];
+      o_acc[dt][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kt = 0; kt < CH / 16; ++kt) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+      a[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+      a[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+      a[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+      const __nv_bfloat16* tV = sV + (st * CH + kt * 16) * LD;
+#pragma unroll
+      for (int dp = 0; dp < D / 16; ++dp) {
+        uint32_t bfr[4];
+        ldmatrix_x4_trans(bfr, smem_u32(tV + (lane & 15) * LD + dp * 16 + (lane >> 4) * 8));
+        mma_16816(o_acc[2 * dp], a, bfr[0], bfr[1]);
+        mma_16816(o_acc[2 * dp + 1], a, bfr[2], bfr[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  // every warp owns its rows outright: write the partials of the members it covers
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + frow + r * 8;
+    const int mem = row / rep;
+    const int b = (mem < kGroupMax) ? rows[mem] : -1;
+    if (b < 0) continue;
+    const int h = hk * rep + row % rep;
+    const long long pi = ((long long)b * p.nh + h) * p.slot_total + sp;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      p.part_o[pi * D + dt * 8 + fcol] = o_acc[dt][2 * r];
+      p.part_o[pi * D + dt * 8 + fcol + 1] = o_acc[dt][2 * r + 1];
+    }
+    if ((lane & 3) == 0) {
+      p.part_ml[pi * 2] = m_run[r];
+      p.part_ml[pi * 2 + 1] = l_run[r];
+    }
+  }
+}
+
 template <int D>
 __global__ void paged_decode_merge_kernel(const DecodeParams p, int B) {
   const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (gw >= (long long)B * p.nh) return;
-  const float* ml = p.part_ml + gw * p.nsplit * 2;
+  const int ns = p.slot_total;
+  const float* ml = p.part_ml + gw * ns * 2;
   float m = -INFINITY;
-  for (int s = 0; s < p.nsplit; ++s) m = fmaxf(m, ml[2 * s]);
+  for (int s = 0; s < ns; ++s) m = fmaxf(m, ml[2 * s]);
   const float mu = (m == -INFINITY) ? 0.f : m;
   float l = 0.f;
-  for (int s = 0; s < p.nsplit; ++s) l += ml[2 * s + 1] * exp2f(ml[2 * s] - mu);
+  for (int s = 0; s < ns; ++s) l += ml[2 * s + 1] * exp2f(ml[2 * s] - mu);
   const long long b = gw / p.nh;
   const int h = (int)(gw % p.nh);
   for (int d = lane; d < D; d += 32) {
     float o = 0.f;
-    for (int s = 0; s < p.nsplit; ++s)
-      o += p.part_o[(gw * p.nsplit + s) * D + d] * exp2f(ml[2 * s] - mu);
+    for (int s = 0; s < ns; ++s)
+      o += p.part_o[(gw * ns + s) * D + d] * exp2f(ml[2 * s] - mu);
     p.out[b * p.out_stride + (long long)h * D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
   }
 }
@@ -587,21 +774,38 @@ MSRL_API int msrl_kv_cache_gather(const void* k_cache, const void* v_cache, cons
 
 // Scratch requirement (floats) for a given problem: part_o = B*nh*nsplit*D, part_ml = B*nh*nsplit*2.
 MSRL_API int msrl_paged_decode_nsplit(int B, int nkv, int max_ctx) {
-  const int target = 2 * sm_count();
+  // Three CTAs of this kernel are resident per SM (shared memory); pick the smallest split count
+  // that fills the machine and wastes under ~10% of the last wave, keeping >= 256 keys per split.
+  const double slots = 3.0 * sm_count();
   int ns = 1;
-  while (ns < 32 && B * nkv * ns < target && (max_ctx + ns - 1) / ns > 512) ns *= 2;
+  while (ns < 32 && (max_ctx + 2 * ns - 1) / (2 * ns) >= 256) {
+    const double waves = B * (double)nkv * ns / slots;
+    const double eff = waves / ceil(waves);
+    if (waves >= 1.0 && eff >= 0.9) break;
+    ns *= 2;
+  }
   return ns;
 }
 
-MSRL_API int msrl_paged_decode(const void* q, const long long* q_layout4, const void* k_cache,
+static int launch_paged_decode(const void* q, const long long* q_layout4, const void* k_cache,
                                const void* v_cache, const int* block_tables, int max_blocks,
                                const int* context_lens, void* out, long long out_stride,
                                float* part_o, float* part_ml, int B, int nh, int nkv, int D,
-                               int block_size, int nsplit, cudaStream_t st) {
+                               int block_size, int nsplit, const int* key_start, const int* group_rows,
+                               const int* group_prefix, int n_groups, int npre, cudaStream_t st) {
   if (B == 0) return 0;
   if (nh % nkv != 0 || nh / nkv > 16 || (D != 64 && D != 128) || nsplit < 1)
     return (int)cudaErrorInvalidValue;
+  const bool grouped = n_groups > 0;
+  if (grouped && (npre < 1 || key_start == nullptr || group_rows == nullptr || group_prefix == nullptr))
+    return (int)cudaErrorInvalidValue;
   DecodeParams p{};
+  p.key_start = grouped ? key_start : nullptr;
+  p.group_rows = group_rows;
+  p.group_prefix = group_prefix;
+  p.npre = grouped ? npre : 0;
+  p.slot_base = p.npre;
+  p.slot_total = p.npre + nsplit;
   p.q = (const __nv_bfloat16*)q;
   p.Lq = HeadLayout{q_layout4[0], (int)q_layout4[1], (int)q_layout4[2], (int)q_layout4[3]};
   p.k_cache = (const __nv_bfloat16*)k_cache;
@@ -624,6 +828,21 @@ MSRL_API int msrl_paged_decode(const void* q, const long long* q_layout4, const 
   if (merge_smem > smem) smem = merge_smem;
   dim3 grid(B, nkv, nsplit);
   cudaError_t e;
+  if (grouped) {
+    const size_t psmem = (size_t)(64 + 4 * 64) * LD * sizeof(__nv_bfloat16);
+    dim3 pgrid(n_groups, nkv, npre);
+    if (D == 128) {
+      e = cudaFuncSetAttribute(paged_decode_prefix_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
+      if (e != cudaSuccess) return (int)e;
+      paged_decode_prefix_kernel<128><<<pgrid, 128, psmem, st>>>(p);
+    } else {
+      e = cudaFuncSetAttribute(paged_decode_prefix_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
+      if (e != cudaSuccess) return (int)e;
+      paged_decode_prefix_kernel<64><<<pgrid, 128, psmem, st>>>(p);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
   if (D == 128) {
     e = cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -635,13 +854,46 @@ MSRL_API int msrl_paged_decode(const void* q, const long long* q_layout4, const 
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  if (nsplit > 1) {
+  if (p.slot_total > 1) {
     const long long warps = (long long)B * nh;
     const unsigned blocks = (unsigned)ceil_div(warps * 32, 128);
     if (D == 128) paged_decode_merge_kernel<128><<<blocks, 128, 0, st>>>(p, B);
     else paged_decode_merge_kernel<64><<<blocks, 128, 0, st>>>(p, B);
   }
   MSRL_LAUNCH_CHECK();
+}
+
+MSRL_API int msrl_paged_decode(const void* q, const long long* q_layout4, const void* k_cache,
+                               const void* v_cache, const int* block_tables, int max_blocks,
+                               const int* context_lens, void* out, long long out_stride,
+                               float* part_o, float* part_ml, int B, int nh, int nkv, int D,
+                               int block_size, int nsplit, cudaStream_t st) {
+  return launch_paged_decode(q, q_layout4, k_cache, v_cache, block_tables, max_blocks, context_lens, out,
+                             out_stride, part_o, part_ml, B, nh, nkv, D, block_size, nsplit, nullptr, nullptr,
+                             nullptr, 0, 0, st);
+}
+
+MSRL_API int msrl_paged_decode_group_max(int nh, int nkv) {
+  const int cap = 64 / (nh / nkv);
+  return cap < kGroupMax ? cap : kGroupMax;
+}
+
+// Grouped decode: every batch row belongs to exactly one group (singletons allowed, prefix 0).
+// group_rows [n_groups, 8] lists the members' batch rows (-1 padded, at most
+// msrl_paged_decode_group_max members); the members of a group share their first group_prefix[g]
+// keys (same tokens, hence the same K/V, read through the first member's block table);
+// key_start[b] = prefix of b's group.  Scratch: part_o B*nh*(npre+nsplit)*D floats, part_ml
+// B*nh*(npre+nsplit)*2 floats.
+MSRL_API int msrl_paged_decode_grouped(const void* q, const long long* q_layout4, const void* k_cache,
+                                       const void* v_cache, const int* block_tables, int max_blocks,
+                                       const int* context_lens, const int* key_start, const int* group_rows,
+                                       const int* group_prefix, int n_groups, void* out, long long out_stride,
+                                       float* part_o, float* part_ml, int B, int nh, int nkv, int D,
+                                       int block_size, int nsplit, int npre, cudaStream_t st) {
+  if (n_groups < 1) return (int)cudaErrorInvalidValue;
+  return launch_paged_decode(q, q_layout4, k_cache, v_cache, block_tables, max_blocks, context_lens, out,
+                             out_stride, part_o, part_ml, B, nh, nkv, D, block_size, nsplit, key_start, group_rows,
+                             group_prefix, n_groups, npre, st);
 }
 
 MSRL_API int msrl_sample_rec_bytes() { return (int)sizeof(SampleRec); }

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -64,11 +64,56 @@ def kv_cache_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: 
     return k_cache.view(-1, nkv, hd)[slot], v_cache.view(-1, nkv, hd)[slot]
 
 
+def decode_group_max(num_heads: int, num_kv_heads: int) -> int:
+    """Largest group the shared-prefix decode kernel serves with one CTA (members x query heads
+    per KV head must fit 64 rows)."""
+    return max(1, min(8, 64 // max(num_heads // num_kv_heads, 1)))
+
+
+def build_decode_groups(group_ids: Sequence, prefix_lens: Sequence[int], group_max: int):
+    """Host-side grouping for the shared-prefix decode path.
+
+    ``group_ids[i]`` identifies the prompt of batch row ``i`` and ``prefix_lens[i]`` the number of
+    leading tokens it shares with the other rows of that prompt.  Returns
+    ``(key_start [B], group_rows [B][8], group_prefix [B], any_shared)`` as python lists padded to
+    ``B`` groups (unused groups have first member -1), so the arrays have a fixed shape per batch
+    size (CUDA-graph friendly).
+    """
+    b = len(group_ids)
+    by_id = {}
+    for i, gid in enumerate(group_ids):
+        by_id.setdefault(gid, []).append(i)
+    key_start = [0] * b
+    rows_out, prefix_out = [], []
+    shared = False
+    for members in by_id.values():
+        for s in range(0, len(members), group_max):
+            chunk = members[s:s + group_max]
+            prefix = min(prefix_lens[i] for i in chunk) if len(chunk) > 1 else 0
+            shared = shared or prefix > 0
+            for i in chunk:
+                key_start[i] = prefix
+            rows_out.append(chunk + [-1] * (8 - len(chunk)))
+            prefix_out.append(prefix)
+    while len(rows_out) < b:
+        rows_out.append([-1] * 8)
+        prefix_out.append(0)
+    return key_start, rows_out, prefix_out, shared
+
+
 def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.Tensor,
                            v_cache: torch.Tensor, block_tables: torch.Tensor,
                            context_lens: torch.Tensor, max_context: int,
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One query token per sequence against its paged KV (which already holds that token)."""
+                           out: Optional[torch.Tensor] = None,
+                           groups: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+                           prefix_splits: int = 4) -> torch.Tensor:
+    """One query token per sequence against its paged KV (which already holds that token).
+
+    ``groups = (key_start [B], group_rows [G, 8], group_prefix [G])`` (int32, device) enables the
+    shared-prefix path: the members of a group (the n samples of one prompt) have identical
+    first ``group_prefix`` tokens, whose K/V is then read once per group instead of once per
+    member.  Every row must belong to exactly one group; the result is the same either way.
+    """
     b = qkv.shape[0]
     nh, nkv, hd = layout.num_heads, layout.num_kv_heads, layout.head_dim
     bs = k_cache.shape[1]
@@ -77,6 +122,19 @@ def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.
     if _lib.use_kernels(qkv, k_cache, block_tables, context_lens):
         L = _lib.load()
         nsplit = L.msrl_paged_decode_nsplit(c_int(b), c_int(nkv), c_int(int(max_context)))
+        if groups is not None:
+            key_start, group_rows, group_prefix = groups
+            slots = nsplit + prefix_splits
+            part_o = _workspace("decode_part_o", b * nh * slots * hd, qkv.device)
+            part_ml = _workspace("decode_part_ml", b * nh * slots * 2, qkv.device)
+            qs = layout.q()
+            check(L.msrl_paged_decode_grouped(
+                ptr(qkv.view(-1)[qs[0]:]), _lay(qs), ptr(k_cache), ptr(v_cache), ptr(block_tables),
+                c_int(block_tables.shape[1]), ptr(context_lens), ptr(key_start), ptr(group_rows),
+                ptr(group_prefix), c_int(group_rows.shape[0]), ptr(out), c_ll(nh * hd), ptr(part_o), ptr(part_ml),
+                c_int(b), c_int(nh), c_int(nkv), c_int(hd), c_int(bs), c_int(nsplit), c_int(prefix_splits),
+                stream()), "paged_decode_grouped")
+            return out
         part_o = _workspace("decode_part_o", b * nh * nsplit * hd, qkv.device)
         part_ml = _workspace("decode_part_ml", b * nh * nsplit * 2, qkv.device)
         qs = layout.q()

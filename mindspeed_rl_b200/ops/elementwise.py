@@ -17,12 +17,15 @@ from ._lib import c_float, c_int, c_ll, check, ptr, stream
 from .layouts import QKVLayout
 
 _scratch = {}
+_retired = []     # outgrown scratch buffers stay allocated: captured CUDA graphs may still point at them
 
 
 def _workspace(key: str, numel: int, device, dtype=torch.float32) -> torch.Tensor:
     """Grow-only scratch buffers (kernels never allocate)."""
     buf = _scratch.get((key, device, dtype))
     if buf is None or buf.numel() < numel:
+        if buf is not None and buf.is_cuda:
+            _retired.append(buf)
         buf = torch.empty(max(numel, 1), device=device, dtype=dtype)
         _scratch[(key, device, dtype)] = buf
     return buf

@@ -13,6 +13,7 @@ generate_sequences / async_generate_sequences``; reference:
 """
 from __future__ import annotations
 
+import os
 import uuid
 import zlib
 from dataclasses import dataclass, field
@@ -75,6 +76,9 @@ class LLMEngine:
         self.bm: Optional[BlockManager] = None
         self.scheduler: Optional[Scheduler] = None
         self._step_counter = 0
+        nkv_local = max(cfg.num_query_groups // self.comm.world_size, 1)
+        self._group_max = ops.decode_group_max(cfg.num_attention_heads // self.comm.world_size, nkv_local)
+        self.shared_prefix_decode = os.environ.get("MSRL_SHARED_PREFIX_DECODE", "1") == "1"
         self.stats = dict(prefill_tokens=0, decode_tokens=0, steps=0, preemptions=0)
 
     # ---- cache lifecycle -----------------------------------------------------------------------
@@ -256,12 +260,23 @@ class LLMEngine:
         lens = [s.total_len for s in seqs]
         slots = [int(self.bm.slots(s.seq_id, n - 1, 1)[0]) for s, n in zip(seqs, lens)]
         keys, floats, need_filter, need_eos = self._sampling_rows(seqs)
-        it_, ft = self._ship([last, [n - 1 for n in lens], slots, lens, keys], floats)
+        rows = [last, [n - 1 for n in lens], slots, lens, keys]
+        grouped = False
+        if self.shared_prefix_decode and dev.type == "cuda":
+            # samples of one prompt share the prompt's K/V: read it once per group
+            ks, grows, gpre, grouped = ops.build_decode_groups(
+                [s.request_id for s in seqs], [len(s.prompt_ids) for s in seqs], self._group_max)
+            if grouped:
+                rows += [ks, gpre] + [list(col) for col in zip(*grows)]
+        it_, ft = self._ship(rows, floats)
         max_ctx = max(lens)
         max_blocks = (max_ctx + self.block_size - 1) // self.block_size
         bt = to_device(self.bm.block_tables([s.seq_id for s in seqs], max_blocks), torch.int32, dev)
+        groups = None
+        if grouped:
+            groups = (it_[5].to(torch.int32), it_[7:15].t().contiguous().to(torch.int32), it_[6].to(torch.int32))
         logits = self.runner.decode(it_[0], it_[1].to(torch.int32), it_[2], bt, it_[3].to(torch.int32),
-                                    max_ctx)
+                                    max_ctx, groups)
         self.stats["decode_tokens"] += b
         for s, n in zip(seqs, lens):
             s.num_computed = n

@@ -183,13 +183,13 @@ class ModelRunner:
         return self._logits(x[last_index])
 
     # ------------------------------------------------------------------------------------------
-    def _decode_eager(self, ids, positions, slots, block_tables, context_lens, max_context):
+    def _decode_eager(self, ids, positions, slots, block_tables, context_lens, max_context, groups=None):
         cache = self.cache
 
         def attend(li, qkv, lay):
             ops.kv_cache_write(qkv, lay, slots, cache.k[li], cache.v[li])
             return ops.paged_decode_attention(qkv, lay, cache.k[li], cache.v[li], block_tables,
-                                              context_lens, max_context)
+                                              context_lens, max_context, groups=groups)
 
         return self._logits(self._forward(ids, positions, attend))
 
@@ -202,20 +202,24 @@ class ModelRunner:
                       positions=torch.zeros(cap, dtype=torch.int32, device=dev),
                       slots=torch.full((cap,), -1, dtype=torch.int64, device=dev),
                       block_tables=torch.zeros(cap, max_blocks, dtype=torch.int32, device=dev),
-                      context_lens=torch.zeros(cap, dtype=torch.int32, device=dev))
+                      context_lens=torch.zeros(cap, dtype=torch.int32, device=dev),
+                      key_start=torch.zeros(cap, dtype=torch.int32, device=dev),
+                      group_rows=torch.full((cap, 8), -1, dtype=torch.int32, device=dev),
+                      group_prefix=torch.zeros(cap, dtype=torch.int32, device=dev))
             self._static = st
             self._graphs.clear()
         return st
 
     @torch.no_grad()
     def decode(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
-               block_tables: torch.Tensor, context_lens: torch.Tensor, max_context: int
-               ) -> torch.Tensor:
-        """One token per sequence -> logits ``[B, V_local]``."""
+               block_tables: torch.Tensor, context_lens: torch.Tensor, max_context: int,
+               groups=None) -> torch.Tensor:
+        """One token per sequence -> logits ``[B, V_local]``.  ``groups`` (see
+        ``ops.paged_decode_attention``) turns on shared-prefix attention for n-sample groups."""
         b = ids.shape[0]
         bucket = next((s for s in self.graph_batch_sizes if s >= b), None)
         if self.enforce_eager or bucket is None:
-            return self._decode_eager(ids, positions, slots, block_tables, context_lens, max_context)
+            return self._decode_eager(ids, positions, slots, block_tables, context_lens, max_context, groups)
         max_blocks = (self.max_model_len + self.cache.block_size - 1) // self.cache.block_size
         st = self._ensure_static(max_blocks)
         st["ids"][:b].copy_(ids)
@@ -225,15 +229,23 @@ class ModelRunner:
         st["context_lens"][:b].copy_(context_lens)
         st["context_lens"][b:bucket].zero_()
         st["block_tables"][:b, :block_tables.shape[1]].copy_(block_tables)
-        g = self._graphs.get(bucket)
+        grouped = groups is not None
+        if grouped:
+            st["key_start"][:b].copy_(groups[0])
+            st["key_start"][b:bucket].zero_()
+            st["group_rows"][:b].copy_(groups[1])
+            st["group_rows"][b:bucket].fill_(-1)
+            st["group_prefix"][:b].copy_(groups[2])
+        g = self._graphs.get((bucket, grouped))
         if g is None:
-            g = self._capture(bucket, st)
+            g = self._capture(bucket, st, grouped)
         g["graph"].replay()
         return g["logits"][:b]
 
-    def _capture(self, bucket: int, st: dict) -> dict:
+    def _capture(self, bucket: int, st: dict, grouped: bool = False) -> dict:
+        groups = (st["key_start"][:bucket], st["group_rows"][:bucket], st["group_prefix"][:bucket]) if grouped else None
         args = (st["ids"][:bucket], st["positions"][:bucket], st["slots"][:bucket],
-                st["block_tables"][:bucket], st["context_lens"][:bucket], self.max_model_len)
+                st["block_tables"][:bucket], st["context_lens"][:bucket], self.max_model_len, groups)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):       # warm-up: sizes scratch buffers outside the capture
@@ -243,5 +255,5 @@ class ModelRunner:
         with torch.cuda.graph(graph):
             logits = self._decode_eager(*args)
         rec = dict(graph=graph, logits=logits)
-        self._graphs[bucket] = rec
+        self._graphs[(bucket, grouped)] = rec
         return rec

@@ -162,6 +162,57 @@ def test_paged_decode_and_cache(nh, nkv, hd, bs):
     assert torch.equal(kg.cpu(), kgr) and torch.equal(vg.cpu(), vgr)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,bs,n_samples,prompt", [(28, 4, 128, 16, 8, 200), (8, 2, 64, 16, 5, 70),
+                                                           (16, 16, 128, 32, 8, 33)])
+def test_paged_decode_shared_prefix(nh, nkv, hd, bs, n_samples, prompt):
+    """Groups of samples share their prompt blocks; the grouped kernels (prefix read once per
+    group + per-sample suffix + merge) must equal the plain per-sequence path."""
+    torch.manual_seed(11)
+    lay = QKVLayout(nh, nkv, hd, True)
+    n_prompts = 3
+    shared_blocks = prompt // bs                       # full prompt blocks are physically shared
+    gen = [[1 + 37 * j + 11 * g for j in range(n_samples)] for g in range(n_prompts)]   # generated so far
+    lens = [prompt + gen[g][j] for g in range(n_prompts) for j in range(n_samples)] + [90]   # + a singleton
+    b = len(lens)
+    maxb = max((n + bs - 1) // bs for n in lens)
+    nblocks = b * maxb + 8
+    kc = torch.zeros(nblocks, bs, nkv, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    free = torch.randperm(nblocks).tolist()
+    bt = torch.zeros(b, maxb, dtype=torch.int32)
+    row = 0
+    for g in range(n_prompts):
+        prompt_kv = (0.5 * torch.randn(prompt, lay.width, device=DEV)).bfloat16()
+        shared = [free.pop() for _ in range(shared_blocks)]
+        for j in range(n_samples):
+            n = lens[row]
+            nb = (n + bs - 1) // bs
+            blocks = shared + [free.pop() for _ in range(nb - shared_blocks)]
+            bt[row, :nb] = torch.tensor(blocks, dtype=torch.int32)
+            x = torch.cat([prompt_kv, (0.5 * torch.randn(n - prompt, lay.width, device=DEV)).bfloat16()])
+            pos = torch.arange(n)
+            ops.kv_cache_write(x, lay, (bt[row, pos // bs].long() * bs + pos % bs).to(DEV), kc, vc)
+            row += 1
+    n = lens[row]
+    nb = (n + bs - 1) // bs
+    bt[row, :nb] = torch.tensor([free.pop() for _ in range(nb)], dtype=torch.int32)
+    pos = torch.arange(n)
+    ops.kv_cache_write((0.5 * torch.randn(n, lay.width, device=DEV)).bfloat16(), lay,
+                       (bt[row, pos // bs].long() * bs + pos % bs).to(DEV), kc, vc)
+    q = (0.5 * torch.randn(b, lay.width, device=DEV)).bfloat16()
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    btd = bt.to(DEV)
+    plain = ops.paged_decode_attention(q, lay, kc, vc, btd, ctx, max(lens))
+    ids = [g for g in range(n_prompts) for _ in range(n_samples)] + ["solo"]
+    ks, rows, pre, shared_any = ops.build_decode_groups(ids, [prompt] * (b - 1) + [90], ops.decode_group_max(nh, nkv))
+    assert shared_any and sorted(r for grp in rows for r in grp if r >= 0) == list(range(b))
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    grouped = ops.paged_decode_attention(q, lay, kc, vc, btd, ctx, max(lens), groups=(i32(ks), i32(rows), i32(pre)))
+    close(grouped, plain, 1e-2, 1e-2, "shared-prefix decode")
+    ref = ops.paged_decode_attention(q.cpu(), lay, kc.cpu(), vc.cpu(), bt, ctx.cpu(), max(lens))
+    close(grouped, ref, 2e-2, 2e-2, "shared-prefix decode vs reference")
+
+
 def test_lmhead_logprob_fwd_bwd():
     torch.manual_seed(6)
     t, h, v = 300, 256, 5000
