@@ -518,13 +518,17 @@ __device__ __forceinline__ float ld_logit<__nv_bfloat16>(const __nv_bfloat16* p,
   return __bfloat162float(p[i]);
 }
 
+// Grid (row, vocabulary split): every CTA makes ONE pass over its slice of the row (16-byte
+// loads), tracking the soft-max statistics and the Gumbel arg-max together; one Philox call
+// serves four consecutive vocabulary ids.  The per-split records are merged by the combine kernel
+// exactly like records of vocabulary shards on different ranks.
 template <typename T>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 sample_kernel(const T* __restrict__ logits, long long row_stride, int V, int vocab_offset,
               const float* __restrict__ inv_temp, const float* __restrict__ thresh,
               const float* __restrict__ eos_prob, int eos_id,
               const unsigned long long* __restrict__ row_keys, unsigned long long seed,
-              SampleRec* __restrict__ rec) {
+              SampleRec* __restrict__ rec, int B) {
   __shared__ float red[32];
   __shared__ int redi[32];
   const int b = blockIdx.x;
@@ -535,45 +539,68 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, int voc
   const float th = (thresh != nullptr) ? thresh[b] : -INFINITY;
   const float pe = (eos_prob != nullptr) ? eos_prob[b] : -1.f;
   const int eos_local = (pe >= 0.f) ? eos_id - vocab_offset : -1;
+  // this CTA's slice [lo, hi) of the row, in multiples of 8 elements
+  const int per = ((V + (int)gridDim.y - 1) / (int)gridDim.y + 7) & ~7;
+  const int lo = min(V, (int)blockIdx.y * per), hi = min(V, lo + per);
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
 
-  // pass 1: max and sum-exp over the kept tokens (EOS excluded when forced)
+  const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+  const unsigned long long rk = row_keys[b];
   float m = -INFINITY, s = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    if (i == eos_local) continue;
-    const float z = ld_logit<T>(row, i) * sc;
-    if (z < th) continue;
+  float best = -INFINITY, best_z = 0.f;
+  int best_i = -1;
+  uint4 rnd = make_uint4(0u, 0u, 0u, 0u);
+  uint32_t rnd_group = 0xffffffffu;
+  auto visit = [&](int i, float raw) {
+    if (i == eos_local) return;
+    const float z = raw * sc;
+    if (z < th) return;
     if (z > m) {
       s = s * __expf(m - z) + 1.f;
       m = z;
     } else {
       s += __expf(z - m);
     }
-  }
-  const float bm = block_max(m, red);
-  s = (m == -INFINITY) ? 0.f : s * __expf(m - bm);
-  const float bs = block_sum(s, red);
-
-  // pass 2: Gumbel-max
-  const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
-  const unsigned long long rk = row_keys[b];
-  float best = -INFINITY, best_z = 0.f;
-  int best_i = -1;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    if (i == eos_local) continue;
-    const float z = ld_logit<T>(row, i) * sc;
-    if (z < th) continue;
     float val = z;
     if (!greedy) {
       const uint32_t gi = (uint32_t)(i + vocab_offset);
-      const uint4 r = philox4x32_10(make_uint4(gi, 0u, (uint32_t)rk, (uint32_t)(rk >> 32)), key);
-      val = z + gumbel_from_bits(r.x);
+      if ((gi >> 2) != rnd_group) {
+        rnd_group = gi >> 2;
+        rnd = philox4x32_10(make_uint4(rnd_group, 0u, (uint32_t)rk, (uint32_t)(rk >> 32)), key);
+      }
+      const uint32_t c = gi & 3u;
+      val = z + gumbel_from_bits(c == 0 ? rnd.x : (c == 1 ? rnd.y : (c == 2 ? rnd.z : rnd.w)));
     }
     if (val > best || (val == best && i < best_i)) {
       best = val;
       best_z = z;
       best_i = i;
     }
+  };
+  if (vec_ok) {
+    for (int i0 = lo + threadIdx.x * 8; i0 < hi; i0 += blockDim.x * 8) {
+      float f[8];
+      if (i0 + 8 > hi) {                       // ragged tail of the row: never read past its end
+        for (int j = 0; i0 + j < hi; ++j) visit(i0 + j, ld_logit<T>(row, i0 + j));
+        continue;
+      }
+      if (sizeof(T) == 2) {
+        unpack8(ld8(reinterpret_cast<const __nv_bfloat16*>(row) + i0), f);
+      } else {
+        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + i0);
+        const float4 c = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + i0 + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = c.x; f[5] = c.y; f[6] = c.z; f[7] = c.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (i0 + j < hi) visit(i0 + j, f[j]);
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) visit(i, ld_logit<T>(row, i));
   }
+  const float bm = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - bm);
+  const float bs = block_sum(s, red);
   // block arg-max
   float wbest = best;
   int wi = best_i;
@@ -604,7 +631,7 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, int voc
     r.m = bm; r.s = bs; r.best_val = fb; r.best_z = fz;
     r.best_idx = (fi >= 0) ? fi + vocab_offset : -1;
     r.pad = 0;
-    rec[b] = r;
+    rec[(long long)blockIdx.y * B + b] = r;
   }
 }
 
@@ -914,17 +941,29 @@ MSRL_API int msrl_sample_filter(const void* logits, int is_bf16, long long row_s
 MSRL_API int msrl_sample(const void* logits, int is_bf16, long long row_stride, int B, int V,
                          int vocab_offset, const float* inv_temp, const float* thresh,
                          const float* eos_prob, int eos_id, const unsigned long long* row_keys,
-                         unsigned long long seed, void* rec, cudaStream_t st) {
+                         unsigned long long seed, void* rec, int nsplit, cudaStream_t st) {
+  // rec: nsplit * B records laid out [split][row]; merge them with msrl_sample_combine(nshard = nsplit)
   if (B == 0) return 0;
+  if (nsplit < 1) return (int)cudaErrorInvalidValue;
+  dim3 grid(B, nsplit);
   if (is_bf16)
-    sample_kernel<__nv_bfloat16><<<B, 1024, 0, st>>>((const __nv_bfloat16*)logits, row_stride, V,
-                                                     vocab_offset, inv_temp, thresh, eos_prob, eos_id,
-                                                     row_keys, seed, (SampleRec*)rec);
+    sample_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)logits, row_stride, V,
+                                                       vocab_offset, inv_temp, thresh, eos_prob, eos_id,
+                                                       row_keys, seed, (SampleRec*)rec, B);
   else
-    sample_kernel<float><<<B, 1024, 0, st>>>((const float*)logits, row_stride, V, vocab_offset,
-                                             inv_temp, thresh, eos_prob, eos_id, row_keys, seed,
-                                             (SampleRec*)rec);
+    sample_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, row_stride, V, vocab_offset,
+                                               inv_temp, thresh, eos_prob, eos_id, row_keys, seed,
+                                               (SampleRec*)rec, B);
   MSRL_LAUNCH_CHECK();
+}
+
+// Vocabulary splits per row that fill the machine (about four CTAs per SM, >= 4096 ids per CTA).
+MSRL_API int msrl_sample_nsplit(int B, int V) {
+  int ns = (4 * sm_count() + B - 1) / (B > 0 ? B : 1);
+  const int cap = (V + 4095) / 4096;
+  if (ns > cap) ns = cap;
+  if (ns > 32) ns = 32;
+  return ns < 1 ? 1 : ns;
 }
 
 MSRL_API int msrl_sample_combine(const void* rec, int nshard, int B, const float* eos_prob,

@@ -194,14 +194,16 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torc
             check(L.msrl_sample_filter(ptr(logits), c_int(is_bf16), c_ll(logits.stride(0)), c_int(b),
                                        c_int(v), ptr(inv_t), ptr(tk), ptr(tp), ptr(mp), ptr(thresh),
                                        stream()), "sample_filter")
-        rec = torch.empty(b * L.msrl_sample_rec_bytes(), device=dev, dtype=torch.uint8)
+        nsplit = int(L.msrl_sample_nsplit(c_int(b), c_int(v)))      # vocabulary splits per row (one CTA each)
+        rec = torch.empty(b * nsplit * L.msrl_sample_rec_bytes(), device=dev, dtype=torch.uint8)
         ep = eos_prob.float() if eos_prob is not None else None
         check(L.msrl_sample(ptr(logits), c_int(is_bf16), c_ll(logits.stride(0)), c_int(b), c_int(v),
                             c_int(vocab_offset), ptr(inv_t), ptr(thresh), ptr(ep), c_int(eos_id),
-                            ptr(row_keys), c_ull(seed & (2 ** 64 - 1)), ptr(rec), stream()), "sample")
+                            ptr(row_keys), c_ull(seed & (2 ** 64 - 1)), ptr(rec), c_int(nsplit), stream()),
+              "sample")
         tokens = torch.empty(b, device=dev, dtype=torch.int64)
         logprobs = torch.empty(b, device=dev, dtype=torch.float32)
-        check(L.msrl_sample_combine(ptr(rec), c_int(1), c_int(b), ptr(ep), c_int(eos_id), ptr(row_keys),
+        check(L.msrl_sample_combine(ptr(rec), c_int(nsplit), c_int(b), ptr(ep), c_int(eos_id), ptr(row_keys),
                                     c_ull(seed & (2 ** 64 - 1)), ptr(tokens), ptr(logprobs), stream()),
               "sample_combine")
         return tokens, logprobs

@@ -13,7 +13,9 @@ generate_sequences / async_generate_sequences``; reference:
 """
 from __future__ import annotations
 
+import collections
 import os
+import time
 import uuid
 import zlib
 from dataclasses import dataclass, field
@@ -76,6 +78,7 @@ class LLMEngine:
         self.bm: Optional[BlockManager] = None
         self.scheduler: Optional[Scheduler] = None
         self._step_counter = 0
+        self.host_time = collections.defaultdict(float)   # wall-clock seconds per host-side section
         nkv_local = max(cfg.num_query_groups // self.comm.world_size, 1)
         self._group_max = ops.decode_group_max(cfg.num_attention_heads // self.comm.world_size, nkv_local)
         self.shared_prefix_decode = os.environ.get("MSRL_SHARED_PREFIX_DECODE", "1") == "1"
@@ -98,6 +101,10 @@ class LLMEngine:
                                    self.max_model_len)
 
     def free_cache(self) -> None:
+        if os.environ.get("MSRL_ENGINE_PROFILE", "0") == "1" and self.host_time:
+            print("[engine] steps=%d host seconds: %s" % (
+                self.stats["steps"], {k: round(v, 3) for k, v in sorted(self.host_time.items())}), flush=True)
+            self.host_time.clear()
         self.runner.bind_cache(None)
         self.bm = None
         self.scheduler = None
@@ -128,15 +135,23 @@ class LLMEngine:
 
     # ---- one engine step -----------------------------------------------------------------------
     def step(self) -> List[RequestOutput]:
+        t0 = time.perf_counter()
         sched = self.scheduler.schedule()
+        t1 = time.perf_counter()
         self.stats["steps"] += 1
         self.stats["preemptions"] += len(sched.preempted)
         if sched.prefill:
             self._run_prefill(sched.prefill)
+            self.host_time["prefill_step"] += time.perf_counter() - t1
         elif sched.decode:
             self._run_decode(sched.decode)
+            self.host_time["decode_step"] += time.perf_counter() - t1
         self._step_counter += 1
-        return [self._to_output(g) for g in self.scheduler.pop_finished_groups()]
+        t2 = time.perf_counter()
+        out = [self._to_output(g) for g in self.scheduler.pop_finished_groups()]
+        self.host_time["schedule"] += t1 - t0
+        self.host_time["collect"] += time.perf_counter() - t2
+        return out
 
     # ---- internals -----------------------------------------------------------------------------
     def _ship(self, ints: List[List[int]], floats: Optional[List[List[float]]] = None):
@@ -256,6 +271,7 @@ class LLMEngine:
     def _run_decode(self, seqs: List[Sequence]) -> None:
         dev = self.device
         b = len(seqs)
+        t0 = time.perf_counter()
         last = [s.output_ids[-1] if s.output_ids else s.prompt_ids[-1] for s in seqs]
         lens = [s.total_len for s in seqs]
         slots = [int(self.bm.slots(s.seq_id, n - 1, 1)[0]) for s, n in zip(seqs, lens)]
@@ -268,6 +284,7 @@ class LLMEngine:
                 [s.request_id for s in seqs], [len(s.prompt_ids) for s in seqs], self._group_max)
             if grouped:
                 rows += [ks, gpre] + [list(col) for col in zip(*grows)]
+        t1 = time.perf_counter()
         it_, ft = self._ship(rows, floats)
         max_ctx = max(lens)
         max_blocks = (max_ctx + self.block_size - 1) // self.block_size
@@ -275,14 +292,23 @@ class LLMEngine:
         groups = None
         if grouped:
             groups = (it_[5].to(torch.int32), it_[7:15].t().contiguous().to(torch.int32), it_[6].to(torch.int32))
+        t2 = time.perf_counter()
         logits = self.runner.decode(it_[0], it_[1].to(torch.int32), it_[2], bt, it_[3].to(torch.int32),
                                     max_ctx, groups)
         self.stats["decode_tokens"] += b
         for s, n in zip(seqs, lens):
             s.num_computed = n
+        t3 = time.perf_counter()
         tokens, lps = self._sample(logits, seqs, it_[4], ft, need_filter, need_eos)
+        t4 = time.perf_counter()
         for s, tok, lp in zip(seqs, tokens, lps):
             self._append_token(s, tok, lp)
+        ht = self.host_time
+        ht["decode_prep"] += t1 - t0
+        ht["decode_h2d"] += t2 - t1
+        ht["decode_launch"] += t3 - t2
+        ht["decode_sample_sync"] += t4 - t3        # includes waiting for the GPU to finish the step
+        ht["decode_append"] += time.perf_counter() - t4
 
     def _to_output(self, group: RequestGroup) -> RequestOutput:
         reasons = {SeqStatus.FINISHED_STOPPED: "stop", SeqStatus.FINISHED_LENGTH: "length",
