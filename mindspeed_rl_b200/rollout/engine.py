@@ -321,8 +321,11 @@ class LLMEngine:
     # ---- convenience -----------------------------------------------------------------------------
     def generate(self, prompts: Seq_[Seq_[int]], params: SamplingParams,
                  request_ids: Optional[Seq_[str]] = None) -> List[RequestOutput]:
-        """Blocking generation; results come back in the order of ``prompts``."""
-        rids = [self.add_request(None if request_ids is None else request_ids[i], p, params)
+        """Blocking generation; results come back in the order of ``prompts``.  ``params`` may be
+        one ``SamplingParams`` or a list with one entry per prompt."""
+        per_prompt = isinstance(params, (list, tuple))
+        rids = [self.add_request(None if request_ids is None else request_ids[i], p,
+                                 params[i] if per_prompt else params)
                 for i, p in enumerate(prompts)]
         done: Dict[str, RequestOutput] = {}
         while self.has_unfinished_requests():

@@ -248,17 +248,20 @@ class IntegratedWorker(BaseWorker):
         if getattr(self, "rollout_state", None) is not None:
             # rollout replicas are (infer-TP)-sized: dispatch / write-back follow the rollout layout
             self._state = self.rollout_state
+        partial = (rl.partial_rollout_max_split or 1) > 1
+        columns = ["prompts", "prompt_length"] + (["responses", "response_length", "age"] if partial else [])
         try:
             while True:
                 batch, idx, finished = self.dispatch_transfer_dock_data(
-                    "actor_rollout", ["prompts", "prompt_length"], rl.actor_rollout_dispatch_size,
-                    get_n_samples=True)
+                    "actor_rollout", columns, rl.actor_rollout_dispatch_size, get_n_samples=not partial)
                 if finished:
                     break
                 if batch is None:
                     time.sleep(0.002)
                     continue
-                if getattr(self, "multi_turn", None) is not None:
+                if partial:
+                    self._generate_batch_partial(batch, idx)
+                elif getattr(self, "multi_turn", None) is not None:
                     self._generate_batch_multi_turn(batch, idx, n)
                 else:
                     self._generate_batch(batch, idx, n)
@@ -287,6 +290,49 @@ class IntegratedWorker(BaseWorker):
                 lengths.append(torch.tensor([len(ids)], dtype=torch.int32))
         self.collect_transfer_dock_data(
             {"responses": responses, "input_ids": input_ids, "response_length": lengths}, idx)
+
+    # ---- partial rollout --------------------------------------------------------------------------------------
+    def _generate_batch_partial(self, batch: Dict[str, torch.Tensor], idx: List[int]) -> None:
+        """One round of partial rollout (reference: ``workers/actor_hybrid_worker.py:484-573``): every
+        row continues from ``prompt + partial response`` for at most ``max_tokens / max_split`` new
+        tokens; a row is complete on EOS, at ``max_tokens`` response tokens or at the context limit.
+        Unfinished rows stay in the store (one round older) and are continued in a later iteration."""
+        import dataclasses
+        import math
+
+        rl, base = self.rl_config, self.sampling_params
+        max_tokens = base.max_tokens
+        per_round = max(1, math.ceil(max_tokens / rl.partial_rollout_max_split))
+        limit = self.engine.max_model_len
+        rows = [i for i, ix in enumerate(idx) if ix >= 0]       # filler rows (index -2) are skipped
+        prompts, plen = batch["prompts"], batch["prompt_length"].reshape(-1)
+        resp, rlen = batch["responses"], batch["response_length"].reshape(-1)
+        age = batch["age"].reshape(-1) if "age" in batch else torch.zeros(len(idx))
+        ctxs, partials, params, rids = [], [], [], []
+        for i in rows:
+            p = prompts[i, :int(plen[i])].tolist()
+            r = resp[i, :int(rlen[i])].tolist() if int(rlen[i]) > 0 else []
+            budget = min(per_round, max_tokens - len(r), limit - len(p) - len(r))
+            ctxs.append(p + r)
+            partials.append((p, r))
+            params.append(dataclasses.replace(base, n=1, max_tokens=max(int(budget), 1)))
+            rids.append(f"pr_{idx[i]}_{int(age[i])}_{self.iteration}")
+        outs = self.engine.generate(ctxs, params, request_ids=rids) if ctxs else []
+        vocab = self.tcfg.vocab_size
+        t = lambda v, dt=torch.int64: torch.tensor(v, dtype=dt)
+        responses, input_ids, lengths, completed = [], [], [], []
+        for (p, r), o in zip(partials, outs):
+            c = o.outputs[0]
+            new = [x if x < vocab else 0 for x in c.token_ids]
+            full = r + new
+            done = c.finish_reason == "stop" or len(full) >= max_tokens or len(p) + len(full) >= limit
+            responses.append(t(full))
+            input_ids.append(t(p + full))
+            lengths.append(t([len(full)], torch.int32))
+            completed.append(t([1 if done else 0], torch.int32))
+        self.collect_transfer_dock_data(
+            {"responses": responses, "input_ids": input_ids, "response_length": lengths,
+             "rollout_completed": completed}, [idx[i] for i in rows])
 
     # ---- multi-turn tool use ----------------------------------------------------------------------------
     def attach_tools(self, tokenizer, tool_map=None) -> None:

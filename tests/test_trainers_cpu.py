@@ -79,3 +79,32 @@ def test_ppo_with_critic_cpu():
                   "critic/returns/mean", "timing/update_critic", "timing/critic_model", "timing/kl"):
             assert k in m, k
     assert not torch.equal(before, critic_group.worker.model.module.rm_head.weight)
+
+
+def test_grpo_partial_rollout_cpu():
+    """Partial rollout: each round generates at most max_tokens / max_split new tokens; unfinished
+    responses are continued (prompt + partial response) in a later round or iteration."""
+    from test_e2e_grpo_cpu import build
+    from mindspeed_rl_b200.trainer.grpo_trainer import RayGRPOTrainer
+
+    torch.manual_seed(0)
+    actor, rl, gen = build(n_prompts=4, n_samples=2, max_tokens=24, iters=2)
+    rl.partial_rollout_max_split = 2
+    worker = IntegratedWorker(actor, rl, gen, eos_token_id=1023, pad_token_id=0, device="cpu")
+    group = SPMDWorkerGroup(worker, num_gpus=1).initialize()
+    rounds = []
+    inner = worker._generate_batch_partial
+
+    def spy(batch, idx):
+        rounds.append((batch["response_length"].reshape(-1).tolist(), batch["age"].reshape(-1).tolist()))
+        return inner(batch, idx)
+
+    worker._generate_batch_partial = spy
+    trainer = RayGRPOTrainer(group, reward_list=[RuleReward(rl, None, actor)], train_iters=2, save_interval=0,
+                             adv_estimator="group_norm", kl_penalty="low_var_kl", init_kl_coef=0.001,
+                             global_batch_size=4, n_samples_per_prompt=2, pad_token_id=0,
+                             partial_rollout_max_split=2)
+    hist = trainer.fit(iter(SyntheticPromptLoader(4, 32, 1024, seed=0)))
+    assert len(hist) == 2 and all(m["response_length/max"] <= 24 for m in hist)
+    assert any(max(lens) == 0 for lens, _ in rounds), "no fresh prompts were generated"
+    assert any(min(lens) == 12 for lens, _ in rounds), "no half-finished response was continued"
