@@ -26,6 +26,7 @@ import torch.nn as nn
 from .. import ops
 from ..ops import QKVLayout
 from ..parallel.tp_comm import NO_TP, TPComm
+from . import lora
 from .transformer_config import TransformerConfig
 
 
@@ -97,6 +98,15 @@ def _normal(shape, std, dtype, device, gen=None):
 # ---------------------------------------------------------------------------------------------------
 # Transformer layer
 # ---------------------------------------------------------------------------------------------------
+def _attach_lora(module: nn.Module, names, cfg: TransformerConfig, device, gen) -> None:
+    """Adapters on the listed linears when the config asks for them (``models/lora.py``)."""
+    if cfg.lora_r <= 0:
+        return
+    for name in names:
+        if name in cfg.lora_target_modules:
+            lora.attach(getattr(module, name), name, cfg, device, gen, cfg.sequence_parallel)
+
+
 class SelfAttention(nn.Module):
     def __init__(self, cfg: TransformerConfig, device, gen):
         super().__init__()
@@ -115,6 +125,7 @@ class SelfAttention(nn.Module):
             self.k_layernorm = _Holder(torch.ones(hd, dtype=dt, device=device))
         else:
             self.q_layernorm = self.k_layernorm = None
+        _attach_lora(self, ("linear_qkv", "linear_proj"), cfg, device, gen)
 
 
 class MLP(nn.Module):
@@ -126,6 +137,7 @@ class MLP(nn.Module):
         out_std = std / math.sqrt(2.0 * cfg.num_layers)
         self.linear_fc1 = _Holder(_normal((2 * f, cfg.hidden_size), std, dt, device, gen))
         self.linear_fc2 = _Holder(_normal((cfg.hidden_size, f), out_std, dt, device, gen))
+        _attach_lora(self, ("linear_fc1", "linear_fc2"), cfg, device, gen)
 
 
 class TransformerLayer(nn.Module):
@@ -187,14 +199,23 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
     # column linears = (all-gather tokens ->) GEMM, row linears = GEMM (-> reduce-scatter tokens);
     # ``comm`` runs each pair as one fused kernel when it can
     qkv, x1g = comm.column_linear(x1, sa.linear_qkv.weight, sa.linear_qkv.bias)
+    lo: Dict[str, torch.Tensor] = {}      # adapter intermediates (only for adapted linears)
+    if lora.active(sa.linear_qkv):
+        lo["qkv"] = lora.column_fwd(sa.linear_qkv, x1g, qkv)
     attn, lse, pre, rq, rk = _attention_core_fwd(layer, qkv, meta)
     proj = comm.row_linear(attn, sa.linear_proj.weight)
+    if lora.active(sa.linear_proj):
+        lo["proj"] = lora.row_fwd(sa.linear_proj, attn, proj, comm)[1]
     h1 = ops.add(h, proj)
     x2, rstd2, _ = ops.rmsnorm_fwd(h1, layer.pre_mlp_layernorm.weight, eps, want_rstd=keep)
     if isinstance(layer.mlp, MLP):
         gu, x2g = comm.column_linear(x2, layer.mlp.linear_fc1.weight)
+        if lora.active(layer.mlp.linear_fc1):
+            lo["fc1"] = lora.column_fwd(layer.mlp.linear_fc1, x2g, gu)
         y = ops.swiglu_fwd(gu)
         mlp_out = comm.row_linear(y, layer.mlp.linear_fc2.weight)
+        if lora.active(layer.mlp.linear_fc2):
+            lo["fc2"] = lora.row_fwd(layer.mlp.linear_fc2, y, mlp_out, comm)[1]
         # activation-function recompute: drop silu(g)*u and rebuild it from gu in the backward
         mlp_ctx = (gu, None if cfg.recompute_activation_function else y) if keep else None
     else:
@@ -204,7 +225,7 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
     if not keep:
         return h2, None
     ctx = dict(h=h, rstd1=rstd1, x1g=x1g, qkv=qkv, attn=attn, lse=lse, pre=pre, rq=rq, rk=rk, h1=h1,
-               rstd2=rstd2, x2g=x2g, mlp_ctx=mlp_ctx)
+               rstd2=rstd2, x2g=x2g, mlp_ctx=mlp_ctx, lora=lo)
     return h2, ctx
 
 
@@ -218,18 +239,26 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
         if y is None:
             y = ops.swiglu_fwd(gu)
         fc1, fc2 = layer.mlp.linear_fc1.weight, layer.mlp.linear_fc2.weight
+        lo = ctx.get("lora") or {}
         dy, d_out = comm.row_linear_bwd(dh2, fc2)
+        if "fc2" in lo:
+            dy += lora.row_bwd(layer.mlp.linear_fc2, y, lo["fc2"], dh2, comm)
         accum_wgrad(fc2, d_out, y)
         dgu = ops.swiglu_bwd(gu, dy)
         accum_wgrad(fc1, dgu, ctx["x2g"])
         dx2 = comm.column_linear_bwd(dgu, fc1)
+        if "fc1" in lo:
+            dx2 = dx2 + lora.column_bwd(layer.mlp.linear_fc1, ctx["x2g"], lo["fc1"], dgu, comm)
     else:
         d_out = comm.reduce_out_bwd(dh2)
         dx2 = comm.gather_seq_bwd(layer.mlp.backward_tokens(ctx["mlp_ctx"], ctx["x2g"], d_out, comm))
     dh1 = ops.rmsnorm_bwd(dx2, ctx["h1"], layer.pre_mlp_layernorm.weight, ctx["rstd2"],
                           grad_buffer(layer.pre_mlp_layernorm.weight), dres=dh2)
     # ---- attention ----
+    lo = ctx.get("lora") or {}
     dattn, d_proj = comm.row_linear_bwd(dh1, sa.linear_proj.weight)
+    if "proj" in lo:
+        dattn += lora.row_bwd(sa.linear_proj, ctx["attn"], lo["proj"], dh1, comm)
     accum_wgrad(sa.linear_proj.weight, d_proj, ctx["attn"])
     if meta.cp is not None:
         dqkv = meta.cp.attention_bwd(dattn, ctx["qkv"], ctx["attn"], ctx["lse"], lay, meta)
@@ -246,6 +275,8 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
     if sa.linear_qkv.bias is not None and sa.linear_qkv.bias.requires_grad:
         ops.colsum_accumulate(dqkv, grad_buffer(sa.linear_qkv.bias))
     dx1 = comm.column_linear_bwd(dqkv, sa.linear_qkv.weight)
+    if "qkv" in lo:
+        dx1 = dx1 + lora.column_bwd(sa.linear_qkv, ctx["x1g"], lo["qkv"], dqkv, comm)
     dh = ops.rmsnorm_bwd(dx1, ctx["h"], layer.input_layernorm.weight, ctx["rstd1"],
                          grad_buffer(layer.input_layernorm.weight), dres=dh1)
     return dh
@@ -410,6 +441,8 @@ class GPTModel(nn.Module):
             if cfg.value_head:
                 self.rm_head = nn.Linear(cfg.hidden_size, 1, bias=True, device=device,
                                          dtype=torch.float32)
+        if cfg.lora_r > 0:
+            lora.freeze_base(self)          # only the adapters (and nothing else) are trained
 
     # -----------------------------------------------------------------------------------------------
     def output_weight(self) -> torch.Tensor:

@@ -92,8 +92,10 @@ class TrainingEngine:
                  dynamic_max_batch_size: Optional[int] = None, pad_multiple: int = 1, dp_group=None,
                  dp_size: int = 1, device=None, forward_micro_batch_size: Optional[int] = None,
                  want_entropy: Optional[bool] = None, forward_backward_func: Optional[Callable] = None,
-                 pipeline=None, context_parallel: Optional[dict] = None, **loss_options):
+                 pipeline=None, context_parallel: Optional[dict] = None, disable_adapter: bool = False,
+                 **loss_options):
         self.model = model
+        self.disable_adapter = disable_adapter   # LoRA: run the backbone without adapters (reference policy)
         self.pipeline = pipeline             # parallel.pipeline.PipelineSchedule when PP > 1
         cpi = context_parallel or {}         # {"group", "size", "rank", "algo"} when CP > 1
         self.cp_group, self.cp_size = cpi.get("group"), int(cpi.get("size", 1) or 1)
@@ -196,6 +198,15 @@ class TrainingEngine:
     @torch.no_grad()
     def forward(self, data: Dict[str, torch.Tensor]) -> torch.Tensor:
         """Forward-only pass; returns ``[B, R]`` fp32 on the host in the order of ``data`` rows."""
+        if self.disable_adapter:
+            from .lora import adapter_disabled
+
+            self.disable_adapter = False
+            try:
+                with adapter_disabled(self.core):
+                    return self.forward(data)
+            finally:
+                self.disable_adapter = True
         self.model.eval()
         n = data["input_ids"].shape[0]
         width = 1 if self.role == "reward" else data["responses"].shape[1]

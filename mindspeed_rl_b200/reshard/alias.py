@@ -9,6 +9,7 @@ the reshard kernel.
 """
 from __future__ import annotations
 
+from ..models import lora
 from ..models.gpt import GPTModel, MLP
 from ..rollout.model_runner import LayerWeights, RolloutWeights
 
@@ -19,15 +20,16 @@ def alias_rollout_weights(model: GPTModel) -> RolloutWeights:
         sa = layer.self_attention
         kw = dict(
             input_norm=layer.input_layernorm.weight.data,
-            qkv_w=sa.linear_qkv.weight.data,
+            qkv_w=lora.merged_weight(sa.linear_qkv),       # W + (alpha/r) B A when adapted
             qkv_b=sa.linear_qkv.bias.data if sa.linear_qkv.bias is not None else None,
-            o_w=sa.linear_proj.weight.data,
+            o_w=lora.merged_weight(sa.linear_proj),
             post_norm=layer.pre_mlp_layernorm.weight.data,
             q_norm=sa.q_layernorm.weight.data if sa.q_layernorm is not None else None,
             k_norm=sa.k_layernorm.weight.data if sa.k_layernorm is not None else None,
         )
         if isinstance(layer.mlp, MLP):
-            kw.update(gate_up_w=layer.mlp.linear_fc1.weight.data, down_w=layer.mlp.linear_fc2.weight.data)
+            kw.update(gate_up_w=lora.merged_weight(layer.mlp.linear_fc1),
+                      down_w=lora.merged_weight(layer.mlp.linear_fc2))
         else:
             kw.update(moe=layer.mlp.rollout_view())
         layers.append(LayerWeights(**kw))

@@ -168,7 +168,13 @@ class IntegratedWorker(BaseWorker):
             forward_max_packing_token_size=rl.actor_max_packing_token_size, **common, **loss_opts)
         self.ref_model = None
         self.reference = None
-        if self.with_reference:
+        if self.with_reference and tcfg.lora_r > 0:
+            # LoRA: the frozen backbone without adapters *is* the reference policy (no second copy)
+            self.reference = TrainingEngine(
+                self.model, role="reference", disable_adapter=True,
+                micro_batch_size=rl.ref_forward_micro_batch_size or self.ref_config.micro_batch_size or 1,
+                max_packing_token_size=rl.ref_max_packing_token_size, **common)
+        elif self.with_reference:
             rcfg = TransformerConfig.from_megatron(self.ref_config, params_dtype=dtype)
             self.ref_model = GPTModel(rcfg, self.comm, device=self.device, seed=self.seed, **stage_kw)
             self.ref_model.load_state_dict(core.state_dict())

@@ -385,6 +385,69 @@ def test_context_parallel_matches_single_process():
     run_distributed(_cp_worker, 2, "ulysses_cp_algo")
 
 
+def _lora_tp_worker(rank, world, sp):
+    """LoRA under TP (+SP): adapters sharded like their base weights reproduce the single-process
+    outputs and adapter gradients."""
+    from mindspeed_rl_b200.checkpoint import convert as C
+    from mindspeed_rl_b200.models import lora
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+    ps = initialize_model_parallel(tensor_model_parallel_size=world)
+    targets = ("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2")
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, add_qkv_bias=True, params_dtype=torch.float32, max_position_embeddings=128,
+              lora_r=4, lora_alpha=8, lora_target_modules=targets)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=5)
+    g = torch.Generator().manual_seed(3)
+    for h in lora.holders(full):
+        h.lora_B.data.normal_(0, 0.1, generator=g)
+    cfg = TransformerConfig(tensor_model_parallel_size=world, sequence_parallel=sp, **kw)
+    comm = TPComm(ps.group("tp"), sp, world_size=world, rank=rank)
+    core = GPTModel(cfg, comm, device="cpu")
+
+    def shard(state):
+        out = _shard_state({k: v for k, v in state.items() if "lora_" not in k}, cfg, world, rank)
+        for k, v in state.items():
+            if k.endswith("linear_qkv.lora_B"):
+                out[k] = C.shard_qkv(v, cfg.num_query_groups, world, rank)
+            elif k.endswith("linear_fc1.lora_B"):
+                gate, up = v.chunk(2, 0)
+                out[k] = C.shard_fc1(gate, up, world, rank)
+            elif k.endswith(("linear_proj.lora_A", "linear_fc2.lora_A")):
+                out[k] = C.shard_cols(v, world, rank)
+            elif "lora_" in k:
+                out[k] = v.clone()
+        return out
+
+    core.load_state_dict(shard(full.state_dict()))
+    model = DistributedDataParallel(core, None, 1)
+    model.attach_tensor_parallel(ps.group("tp"), world, sp)
+    meta = PackedMeta.from_lengths([6, 10], "cpu", align=world)
+    t = int(meta.cu_seqlens[-1])
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    ref_lp, _ = full.forward_logprob(ids, labels, meta, 1.0, False)
+    (ref_lp * w).sum().backward()
+    lp, _ = core.forward_logprob(ids, labels, meta, 1.0, False)
+    (lp * w).sum().backward()
+    model.finish_grad_sync()
+    assert torch.allclose(lp, ref_lp, atol=1e-4), (lp - ref_lp).abs().max()
+    want = shard({n: p.grad for n, p in full.named_parameters() if p.grad is not None})
+    checked = 0
+    for n, p in core.named_parameters():
+        if p.requires_grad:
+            assert torch.allclose(p.main_grad, want[n], atol=2e-4, rtol=1e-3), (n, (p.main_grad - want[n]).abs().max())
+            checked += 1
+    assert checked == 2 * 4 * 2
+
+
+def test_lora_tensor_parallel_matches_single_rank():
+    run_distributed(_lora_tp_worker, 2, False)
+    run_distributed(_lora_tp_worker, 2, True)
+
+
 def _launch_pp_worker(rank, world):
     from mindspeed_rl_b200.config import compose
     from mindspeed_rl_b200.runtime.launch import run_rl

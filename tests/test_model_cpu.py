@@ -29,3 +29,46 @@ def test_recompute_modes_agree():
         assert torch.allclose(lp, lp0, atol=1e-6)
         for n in g0:
             assert torch.allclose(g[n], g0[n], atol=1e-6), n
+
+
+def test_lora_matches_merged_weights():
+    """LoRA forward == forward with W + (alpha/r) B A; adapter gradients == chain rule through the
+    merged-weight gradients; only adapters are trainable; adapters can be switched off."""
+    from mindspeed_rl_b200.models import lora
+
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, add_qkv_bias=True, params_dtype=torch.float32)
+    targets = ("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2")
+    m = GPTModel(TransformerConfig(lora_r=4, lora_alpha=8, lora_target_modules=targets, **kw), device="cpu", seed=2)
+    trainable = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert trainable and all(n.endswith(("lora_A", "lora_B")) for n in trainable)
+    g = torch.Generator().manual_seed(7)
+    for h in lora.holders(m):
+        h.lora_B.data.normal_(0, 0.1, generator=g)
+    plain = GPTModel(TransformerConfig(**kw), device="cpu", seed=2)
+    sd = {k: v for k, v in m.state_dict().items() if "lora_" not in k}
+    for name, h in [(n, mod) for n, mod in m.named_modules() if getattr(mod, "lora_A", None) is not None]:
+        sd[name + ".weight"] = lora.merged_weight(h)
+    plain.load_state_dict(sd)
+    meta = PackedMeta.from_lengths([7, 12], "cpu")
+    t = int(meta.cu_seqlens[-1])
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    lp, _ = m.forward_logprob(ids, labels, meta, 1.0, False)
+    lp_ref, _ = plain.forward_logprob(ids, labels, meta, 1.0, False)
+    assert torch.allclose(lp, lp_ref, atol=1e-5)
+    (lp * w).sum().backward()
+    (lp_ref * w).sum().backward()
+    ref_mods = dict(plain.named_modules())
+    for name, h in [(n, mod) for n, mod in m.named_modules() if getattr(mod, "lora_A", None) is not None]:
+        dw = ref_mods[name].weight.grad
+        s = h.lora_scale
+        assert torch.allclose(h.lora_A.grad, s * h.lora_B.data.t() @ dw, atol=1e-5), name
+        assert torch.allclose(h.lora_B.grad, s * dw @ h.lora_A.data.t(), atol=1e-5), name
+        assert h.weight.grad is None
+    with lora.adapter_disabled(m), torch.no_grad():
+        off, _ = m.forward_logprob(ids, labels, meta, 1.0, False)
+    base = GPTModel(TransformerConfig(**kw), device="cpu", seed=2)
+    base.load_state_dict({k: v for k, v in m.state_dict().items() if "lora_" not in k})
+    with torch.no_grad():
+        want, _ = base.forward_logprob(ids, labels, meta, 1.0, False)
+    assert torch.allclose(off, want, atol=1e-6) and not torch.allclose(off, lp.detach(), atol=1e-4)

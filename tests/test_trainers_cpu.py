@@ -81,6 +81,34 @@ def test_ppo_with_critic_cpu():
     assert not torch.equal(before, critic_group.worker.model.module.rm_head.weight)
 
 
+def test_grpo_lora_cpu():
+    """LoRA GRPO: only adapters move, the backbone without adapters serves as the reference (no
+    second model), the rollout engine runs on merged weights."""
+    from test_e2e_grpo_cpu import build
+    from mindspeed_rl_b200.trainer.grpo_trainer import RayGRPOTrainer
+
+    torch.manual_seed(0)
+    actor, rl, gen = build(n_prompts=4, n_samples=4, max_tokens=16, iters=2)
+    actor.lora_r, actor.lora_alpha = 4, 8
+    actor.lora_target_modules = ["linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"]
+    actor.lr = 1e-2
+    worker = IntegratedWorker(actor, rl, gen, eos_token_id=1023, pad_token_id=0, device="cpu")
+    group = SPMDWorkerGroup(worker, num_gpus=1).initialize()
+    assert worker.ref_model is None and worker.reference is not None and worker.reference.disable_adapter
+    core = worker.model.module
+    before = {k: v.clone() for k, v in core.state_dict().items()}
+    trainer = RayGRPOTrainer(group, reward_list=[RuleReward(rl, None, actor)], train_iters=2, save_interval=0,
+                             adv_estimator="group_norm", kl_penalty="low_var_kl", init_kl_coef=0.001,
+                             global_batch_size=4, n_samples_per_prompt=4, pad_token_id=0)
+    hist = trainer.fit(iter(SyntheticPromptLoader(4, 32, 1024, seed=0)))
+    assert len(hist) == 2 and "actor/kl_loss" in hist[0]
+    after = core.state_dict()
+    moved = [k for k in before if not torch.equal(before[k], after[k])]
+    assert moved and all("lora_" in k for k in moved), moved
+    assert sum(p.numel() for b in worker.model.buffers for p in b.params) == \
+        sum(p.numel() for n, p in core.named_parameters() if "lora_" in n)
+
+
 def test_grpo_partial_rollout_cpu():
     """Partial rollout: each round generates at most max_tokens / max_split new tokens; unfinished
     responses are continued (prompt + partial response) in a later round or iteration."""
