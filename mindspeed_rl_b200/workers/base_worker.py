@@ -84,6 +84,20 @@ class BaseWorker:
         ps = self.parallel_state
         return ps.group("mp_cp"), ps.global_ranks("mp_cp")[0], ps.size("mp_cp")
 
+    def _side_channel(self, group, src: int, size: int):
+        """ZeroMQ broadcast channel of this replica (``rl_config.zmq_communication``), created on
+        first use by all members together; ``None`` when the option is off."""
+        rl = getattr(self, "rl_config", None)
+        if rl is None or not getattr(rl, "zmq_communication", False):
+            return None
+        cache = self.__dict__.setdefault("_side_channels", {})
+        key = id(group)
+        if key not in cache:
+            from ..runtime.zmq_broadcast import setup_replica_broadcast
+
+            cache[key] = setup_replica_broadcast(group, src, size, self.is_replica_leader())
+        return cache[key]
+
     # ---- data plane ------------------------------------------------------------------------------
     def dispatch_transfer_dock_data(self, consumer: str, columns: Sequence[str], experience_count: int,
                                     pad_multiple: int = 1, indexes: Optional[List[int]] = None,
@@ -104,9 +118,13 @@ class BaseWorker:
                                                     use_batch_seqlen_balance=use_batch_seqlen_balance)
                 payload = (batch, idx, False)
         if size > 1 and dist.is_initialized():
-            box = [payload]
-            dist.broadcast_object_list(box, src=src, group=group)
-            payload = box[0]
+            channel = self._side_channel(group, src, size)
+            if channel is not None:          # host-side ZeroMQ fan-out, no collective on the device stream
+                payload = channel.broadcast(payload)
+            else:
+                box = [payload]
+                dist.broadcast_object_list(box, src=src, group=group)
+                payload = box[0]
         batch, idx, finished = payload
         if finished or not batch or not idx:
             return None, None, finished

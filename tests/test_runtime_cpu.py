@@ -1,0 +1,73 @@
+"""Host runtime pieces: ZeroMQ replica broadcast (ordering, re-send after a dropped message,
+time-out when a follower never acknowledges)."""
+import threading
+
+import pytest
+
+from mindspeed_rl_b200.runtime.zmq_broadcast import ZmqClient, ZmqServer
+
+
+def _follow(address, n_msgs, out, cls=ZmqClient):
+    c = cls(address)
+    out.append([c.receive(timeout=20) for _ in range(n_msgs)])
+    c.close()
+
+
+def test_broadcast_in_order_to_all_followers():
+    server = ZmqServer(num_clients=3, resend_interval=0.2)
+    got = []
+    threads = [threading.Thread(target=_follow, args=(server.address, 5, got)) for _ in range(3)]
+    for t in threads:
+        t.start()
+    server.wait_for_clients(timeout=20)
+    msgs = [{"step": i, "payload": list(range(i))} for i in range(5)]
+    for m in msgs:
+        server.broadcast(m)
+    for t in threads:
+        t.join(20)
+    assert len(got) == 3 and all(g == msgs for g in got)
+    server.close()
+
+
+class _LossyClient(ZmqClient):
+    """Loses the first copy of message 2 (neither delivers nor acknowledges it)."""
+    dropped = False
+
+    def receive(self, timeout=120.0):
+        import pickle
+        import time
+        deadline = time.time() + timeout
+        while time.time() < deadline:
+            if not self.sub.poll(200):
+                continue
+            seq_b, payload = self.sub.recv_multipart()
+            seq = int(seq_b)
+            if seq == 2 and not self.dropped:
+                self.dropped = True            # the message is lost on the wire
+                continue
+            self.push.send_multipart([self.id.encode(), seq_b])
+            if seq == self.next_seq:
+                self.next_seq += 1
+                return pickle.loads(payload)
+        raise TimeoutError
+
+
+def test_dropped_message_is_resent():
+    server = ZmqServer(num_clients=1, resend_interval=0.1)
+    got = []
+    t = threading.Thread(target=_follow, args=(server.address, 3, got, _LossyClient))
+    t.start()
+    server.wait_for_clients(timeout=20)
+    for i in range(3):
+        server.broadcast(i)
+    t.join(20)
+    assert got == [[0, 1, 2]]
+    server.close()
+
+
+def test_missing_acknowledgement_times_out():
+    server = ZmqServer(num_clients=1, resend_interval=0.02, max_resends=3)
+    server.clients.add("ghost")                # registered but never answers
+    with pytest.raises(TimeoutError):
+        server.broadcast("hello")
+    server.close()
