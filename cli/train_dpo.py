@@ -64,7 +64,7 @@ def main(argv=None):
     per_rank = max(mc.global_batch_size // ps.size("dp_cp"), 1)
     loader = InfiniteLoader(PromptDataLoader(train, per_rank, 0, mc.seed + ps.rank_in("dp_cp"), no_shuffle=mc.no_shuffle,
                                              is_pairwise_dataset=True, tokenizer=getattr(tokenizer, "tokenizer", None)))
-    trainer = DPOTrainer(model, ref, opt, sch, beta=0.1, loss_type=mc.dpo_loss_type, train_iters=iters, device=device,
+    trainer = DPOTrainer(model, ref, opt, sch, beta=mc.dpo_beta, loss_type=mc.dpo_loss_type, train_iters=iters, device=device,
                          pad_multiple=ps.size("tp") * ps.size("cp"), log_interval=mc.log_interval or 1,
                          save_fn=(lambda it: save_checkpoint(mc.save, it, core, opt, sch, ps, mc)) if mc.save else None,
                          save_interval=mc.save_interval or 0)

@@ -121,7 +121,7 @@ CKPT = dict(
 ADAPT = dict(
     lora_ckpt_filter=False, lora_r=8, lora_alpha=16, lora_fusion=False,
     lora_target_modules=None,
-    dpo_loss_type="sigmoid", ref_model="", refer_model_iter=1,
+    dpo_loss_type="sigmoid", dpo_beta=0.1, dpo_label_smoothing=0.0, ref_model="", refer_model_iter=1,
 )
 
 

@@ -1,0 +1,55 @@
+"""Every shipped recipe parses, passes cross-config validation and derives its dispatch sizes;
+unknown keys are rejected; the catalogue of model architectures loads."""
+import glob
+import os
+
+import pytest
+
+from mindspeed_rl_b200.config import MegatronConfig, RLConfig, compose, parse_training_config
+from mindspeed_rl_b200.config.loader import load_model_catalogue
+
+ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs")
+RECIPES = sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(ROOT, "*.yaml")))
+
+
+@pytest.mark.parametrize("name", [r for r in RECIPES if not r.startswith("dpo_")])
+def test_recipe_validates(name):
+    cfg = compose(name)
+    out = parse_training_config(cfg, with_critic=name.startswith("ppo_"))
+    actor, rl, gen = out["actor_config"], out["rl_config"], out["generate_config"]
+    gpus = rl.actor_resource["num_npus"]
+    mp = actor.tensor_model_parallel_size * actor.pipeline_model_parallel_size * (actor.context_parallel_size or 1)
+    assert gpus % mp == 0 and gpus % gen.infer_tensor_parallel_size == 0
+    assert rl.actor_rollout_dispatch_size and rl.actor_rollout_dispatch_size > 0
+    assert rl.mini_batch_size % rl.n_samples_per_prompt == 0          # scaled by n during validation
+    assert actor.pad_to_multiple_of == actor.tensor_model_parallel_size * (actor.context_parallel_size or 1)
+    if name.startswith("ppo_"):
+        assert out["critic_config"] is not None and rl.critic_resource is not None
+
+
+def test_dpo_recipe_and_model_catalogue():
+    cfg = compose("dpo_qwen3_30b_a3b_b200")
+    mt = MegatronConfig(cfg["megatron_training"], cfg["model"])
+    assert mt.stage == "dpo" and mt.is_pairwise_dataset and mt.num_experts == 128
+    cat = load_model_catalogue(["qwen25_7b", "qwen3_8b", "deepseekv3_671b"])
+    assert cat["qwen25_7b"]["num_layers"] == 28 and cat["qwen3_8b"]["qk_layernorm"]
+    assert cat["deepseekv3_671b"]["multi_latent_attention"]
+
+
+def test_unknown_keys_are_rejected():
+    with pytest.raises(ValueError):
+        RLConfig({"no_such_option": 1})
+    with pytest.raises(ValueError):
+        MegatronConfig({"model": "tiny_qwen2", "definitely_not_a_knob": True}, compose("grpo_tiny_cpu")["model"])
+
+
+def test_dataset_and_tool_configs_load():
+    import yaml
+
+    from mindspeed_rl_b200.tools.base import build_tool_map
+    for p in glob.glob(os.path.join(ROOT, "datasets", "*.yaml")):
+        d = yaml.safe_load(open(p))
+        assert {"input", "output_prefix", "handler_name", "tokenizer_name_or_path"} <= set(d)
+    for p in glob.glob(os.path.join(ROOT, "tools", "*.yaml")):
+        tools = build_tool_map(yaml.safe_load(open(p))["tools"])
+        assert len(tools) == 1
