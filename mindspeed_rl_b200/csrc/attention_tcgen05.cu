@@ -1,0 +1,475 @@
+// Flash attention forward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head dim 128.
+//
+// One CTA = 128 query rows of one (sequence, head).  Per 128-key tile:
+//   S = Q K^T        tcgen05.mma 128x128x16 (both operands K-major, TMA-staged with 128-byte swizzle)
+//                    into one of two TMEM score buffers, so the next tile's scores are computed
+//                    while this tile's soft-max runs;
+//   soft-max         four warps, one query row per thread: tcgen05.ld the row, mask, running max /
+//                    sum in the exp2 domain, P (bf16) written to shared memory in the UMMA K-major
+//                    swizzled layout, O rescaled in TMEM (tcgen05.ld / tcgen05.st) only when a row
+//                    maximum moved;
+//   O += P V         tcgen05.mma with V as an MN-major operand straight from its [keys, d] tile.
+// Warp roles (192 threads): warps 0-3 soft-max / epilogue (TMEM lane quarter = warp id), warp 4 TMA
+// producer, warp 5 TMEM allocation + MMA issue.  Causal masking is bottom-right aligned when the
+// key sequence is longer than the query sequence, as in the mma.sync kernel of attention.cu,
+// which stays the fallback (other head sizes, backward).
+//
+// Every mbarrier wait is bounded; on expiry the kernel records a code in the status word, skips the
+// rest, frees TMEM and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "mma_utils.cuh"
+
+namespace msrl {
+namespace fa5 {
+
+constexpr int BM = 128, BN = 128, D = 128;
+constexpr uint32_t TILE_HALF = 128 * 64 * 2;          // one [128 rows x 64 cols] bf16 swizzled half tile
+constexpr uint32_t TILE_BYTES = 2 * TILE_HALF;         // 32 KiB
+constexpr uint32_t SMEM_Q = 0, SMEM_K = TILE_BYTES, SMEM_V = 3 * TILE_BYTES, SMEM_P = 5 * TILE_BYTES;
+constexpr uint32_t SMEM_TOTAL = 6 * TILE_BYTES;        // 192 KiB
+constexpr uint32_t TMEM_COLS = 512;                    // S0 [0,128) S1 [128,256) O [256,384)
+constexpr long long WAIT_CYCLES = 4000000000LL;
+constexpr int OUT_PITCH = 144;
+
+enum { ERR_Q = 11, ERR_K = 12, ERR_V = 13, ERR_S = 14, ERR_P = 15, ERR_PV = 16, ERR_EMPTY = 17 };
+
+struct Params {
+  __nv_bfloat16* o;
+  long long o_stride_t;
+  float* lse;
+  const int* cu_q;
+  const int* cu_k;
+  int nh, nkv;
+  long long Tq;
+  float scale_log2;
+  int causal;
+  int q_col0, q_group_stride, q_hpg, q_head_stride;    // column of head h inside a row of the Q tensor map
+  int k_col0, k_group_stride, k_hpg, k_head_stride;
+  int v_col0, v_group_stride, v_hpg, v_head_stride;
+  int* error;
+};
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 255u) == 0) {
+      if (*reinterpret_cast<volatile int*>(err) != 0) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        atomicCAS(err, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle.  K-major operands: rows 128 B apart, 8-row
+// groups 1024 B apart (LBO unused).  MN-major operands ([k rows, 64 contiguous mn elements] per
+// 128-byte row): LBO = distance between 64-element blocks along MN, SBO = distance between 8-row
+// groups along K.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+__device__ __forceinline__ void umma(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+               ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+constexpr uint32_t idesc_bf16(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+        "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ int head_col(int col0, int gs, int hpg, int hs, int h) {
+  return col0 + (h / hpg) * gs + (h % hpg) * hs;
+}
+
+__global__ void __launch_bounds__(192, 1)
+fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_free[2], p_ready, pv_done;
+  __shared__ uint32_t tmem_slot;
+
+  const int b = blockIdx.z, h = blockIdx.y, mt = blockIdx.x;
+  const int q0 = p.cu_q[b], qlen = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], klen = p.cu_k[b + 1] - k0;
+  const int m0 = mt * BM;
+  if (m0 >= qlen) return;                         // uniform for the CTA, before any allocation
+  const int hk = h / (p.nh / p.nkv);
+  const int off = klen - qlen;
+  int kmax = klen;
+  if (p.causal) kmax = min(klen, m0 + BM + off);
+  const int n_tiles = kmax > 0 ? (kmax + BN - 1) / BN : 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
+    }
+    mbar_init(&p_ready, 4);
+    mbar_init(&pv_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tmem_o = tmem + 256;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int qc = head_col(p.q_col0, p.q_group_stride, p.q_hpg, p.q_head_stride, h);
+      const int kc = head_col(p.k_col0, p.k_group_stride, p.k_hpg, p.k_head_stride, hk);
+      const int vc = head_col(p.v_col0, p.v_group_stride, p.v_hpg, p.v_head_stride, hk);
+      mbar_expect_tx(&q_full, TILE_BYTES);
+      tma_load_2d(smem + SMEM_Q, &map_q, &q_full, qc, q0 + m0);
+      tma_load_2d(smem + SMEM_Q + TILE_HALF, &map_q, &q_full, qc + 64, q0 + m0);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t use = j >> 1;
+        if (use > 0) ok = mbar_wait(&k_empty[st], (use - 1) & 1, p.error, ERR_EMPTY);
+        if (!ok) break;
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        unsigned char* sk = smem + SMEM_K + st * TILE_BYTES;
+        tma_load_2d(sk, &map_k, &k_full[st], kc, k0 + j * BN);
+        tma_load_2d(sk + TILE_HALF, &map_k, &k_full[st], kc + 64, k0 + j * BN);
+        if (use > 0) ok = mbar_wait(&v_empty[st], (use - 1) & 1, p.error, ERR_EMPTY);
+        if (!ok) break;
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        unsigned char* sv = smem + SMEM_V + st * TILE_BYTES;
+        tma_load_2d(sv, &map_v, &v_full[st], vc, k0 + j * BN);
+        tma_load_2d(sv + TILE_HALF, &map_v, &v_full[st], vc + 64, k0 + j * BN);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t id_s = idesc_bf16(BM, BN, false);
+      constexpr uint32_t id_o = idesc_bf16(BM, D, true);
+      const uint32_t q_addr = smem_u32(smem + SMEM_Q), p_addr = smem_u32(smem + SMEM_P);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(&k_full[st], (j >> 1) & 1, p.error, ERR_K)) return false;
+        if (j >= 2 && !mbar_wait(&s_free[st], ((j >> 1) - 1) & 1, p.error, ERR_S)) return false;
+        fence_after();
+        const uint32_t k_addr = smem_u32(smem + SMEM_K + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t o2 = (kk >> 2) * TILE_HALF + (kk & 3) * 32;
+          umma(tmem + st * BN, desc_sw128(q_addr + o2, 16, 1024), desc_sw128(k_addr + o2, 16, 1024), id_s,
+               kk > 0 ? 1u : 0u);
+        }
+        commit(&s_full[st]);
+        commit(&k_empty[st]);
+        return true;
+      };
+      bool ok = n_tiles > 0 && mbar_wait(&q_full, 0, p.error, ERR_Q);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);            // next tile's scores run during this soft-max
+        if (!ok) break;
+        ok = mbar_wait(&p_ready, j & 1, p.error, ERR_P) && mbar_wait(&v_full[st], (j >> 1) & 1, p.error, ERR_V);
+        if (!ok) break;
+        fence_after();
+        const uint32_t v_addr = smem_u32(smem + SMEM_V + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint32_t pa = p_addr + (kk >> 2) * TILE_HALF + (kk & 3) * 32;
+          umma(tmem_o, desc_sw128(pa, 16, 1024), desc_sw128(v_addr + kk * 2048, TILE_HALF, 1024), id_o,
+               (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        commit(&pv_done);
+        commit(&v_empty[st]);
+      }
+    }
+  } else {
+    // ---------------- soft-max + epilogue: thread = query row (TMEM lane) ----------------
+    const int row = warp * 32 + lane;                       // row inside the tile
+    const int grow = m0 + row;                              // row inside the sequence
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    unsigned char* sp = smem + SMEM_P;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int sb = j & 1;
+      ok = mbar_wait(&s_full[sb], (j >> 1) & 1, p.error, ERR_S);
+      if (!ok) break;
+      fence_after();
+      float s[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        tmem_ld32(tmem + lane_base + sb * BN + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c * 32 + i] = v[i];
+      }
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[sb]);              // the score buffer may be overwritten
+      const int kbase = j * BN;
+      const bool need_mask = (kbase + BN > klen) || (p.causal && (kbase + BN - 1 > m0 + off));
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BN; ++i) {
+        float v = s[i] * p.scale_log2;
+        if (need_mask) {
+          const int key = kbase + i;
+          v = ((key < klen) && (!p.causal || key <= grow + off)) ? v : -INFINITY;
+        }
+        s[i] = v;
+        mx = fmaxf(mx, v);
+      }
+      // The running maximum follows the row maximum lazily: it moves only when the row maximum
+      // passed it by more than 8 (a factor 256, harmless in fp32 sums and bf16 P), so that O is
+      // rescaled in TMEM on few tiles only.
+      float m_new = fmaxf(m_run, mx);
+      if (m_run != -INFINITY && m_new - m_run <= 8.f) m_new = m_run;
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = exp2f(m_run - m_use);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < BN; ++i) {
+        s[i] = exp2f(s[i] - m_use);
+        sum += s[i];
+      }
+      l_run = l_run * corr + sum;
+      m_run = m_new;
+      if (j > 0) {
+        // the previous P V product must be finished before P is overwritten or O is rescaled
+        ok = mbar_wait(&pv_done, (j - 1) & 1, p.error, ERR_PV);
+        if (!ok) break;
+        fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            float v[32];
+            tmem_ld32(tmem_o + lane_base + c * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= corr;
+            tmem_st32(tmem_o + lane_base + c * 32, v);
+          }
+        }
+      }
+      // P row -> shared memory, K-major, 128-byte swizzle: 16-byte chunk index XOR (row % 8)
+#pragma unroll
+      for (int c8 = 0; c8 < BN / 8; ++c8) {
+        const int half = c8 >> 3, chunk = c8 & 7;
+        unsigned char* dst = sp + half * TILE_HALF + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+        *reinterpret_cast<bf16x8*>(dst) = pack8(&s[c8 * 8]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic smem writes -> UMMA reads
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready);
+    }
+    if (ok && n_tiles > 0) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, p.error, ERR_PV);
+    if (ok) {
+      fence_after();
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      // O: 32 rows x 64 columns at a time through this warp's patch (P is no longer needed)
+      unsigned char* patch = sp + warp * (32 * OUT_PITCH);
+#pragma unroll 1
+      for (int c = 0; c < D / 64; ++c) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          float v[32];
+          if (n_tiles > 0) {
+            tmem_ld32(tmem_o + lane_base + c * 64 + hh * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= inv_l;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<bf16x8*>(patch + lane * OUT_PITCH + hh * 64 + q * 16) = pack8(v + q * 8);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + (lane >> 3);
+          const int gr = m0 + warp * 32 + r;
+          if (gr < qlen)
+            st8(p.o + (long long)(q0 + gr) * p.o_stride_t + (long long)h * D + c * 64 + (lane & 7) * 8,
+                *reinterpret_cast<const bf16x8*>(patch + r * OUT_PITCH + (lane & 7) * 16));
+        }
+        __syncwarp();
+      }
+      if (grow < qlen) p.lse[(long long)h * p.Tq + q0 + grow] = (m_run + log2f(l_run)) * 0.6931471805599453f;
+    }
+  }
+  fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
+  }
+}
+
+}  // namespace fa5
+}  // namespace msrl
+
+using namespace msrl;
+
+static PFN_cuTensorMapEncodeTiled_v12000 fa5_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+// [rows, width] bf16 view with a row pitch of `stride_t` elements; box = 64 columns x 128 rows.
+static bool fa5_make_map(CUtensorMap* map, const void* base, long long rows, long long width, long long stride_t) {
+  auto fn = fa5_encode_fn();
+  if (fn == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (stride_t * 2) % 16 != 0 || width % 8 != 0) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(stride_t * 2)};
+  cuuint32_t box[2] = {64u, 128u};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static long long fa5_width(int heads, long long gs, long long hpg, long long hs) {
+  long long w = 0;
+  for (int h = 0; h < heads; ++h) {
+    const long long c = (h / hpg) * gs + (h % hpg) * hs + fa5::D;
+    w = c > w ? c : w;
+  }
+  return w;
+}
+
+// Same contract as msrl_flash_attn_varlen_fwd (attention.cu) for head dim 128, plus the number of
+// key rows `Tk` and a device status word (0 = ok; 11..17 = a bounded wait ran out).  Layout
+// arrays: {stride_t, group_stride, heads_per_group, head_stride} for q, k, v (12 values).
+// Returns cudaErrorNotSupported for shapes this kernel does not cover: the caller falls back.
+MSRL_API int msrl_flash_attn_varlen_fwd_tcgen05(const void* q, const void* k, const void* v,
+                                                const long long* lay, void* o, long long o_stride_t,
+                                                float* lse, const int* cu_q, const int* cu_k, int batch,
+                                                int max_q, int nh, int nkv, long long Tq, long long Tk,
+                                                int D, int causal, int* error, cudaStream_t st) {
+  if (batch == 0 || Tq == 0) return 0;
+  if (D != fa5::D || nh % nkv != 0 || (o_stride_t % 8) != 0 || (reinterpret_cast<uintptr_t>(o) & 15) != 0)
+    return (int)cudaErrorNotSupported;
+  for (int i = 0; i < 3; ++i) {
+    const long long* l = lay + 4 * i;
+    if (l[0] % 8 != 0 || l[1] % 8 != 0 || l[3] % 8 != 0 || l[2] <= 0) return (int)cudaErrorNotSupported;
+  }
+  CUtensorMap mq, mk, mv;
+  if (!fa5_make_map(&mq, q, Tq, fa5_width(nh, lay[1], lay[2], lay[3]), lay[0]) ||
+      !fa5_make_map(&mk, k, Tk, fa5_width(nkv, lay[5], lay[6], lay[7]), lay[4]) ||
+      !fa5_make_map(&mv, v, Tk, fa5_width(nkv, lay[9], lay[10], lay[11]), lay[8]))
+    return (int)cudaErrorNotSupported;
+  fa5::Params p{};
+  p.o = (__nv_bfloat16*)o;
+  p.o_stride_t = o_stride_t;
+  p.lse = lse;
+  p.cu_q = cu_q;
+  p.cu_k = cu_k;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.Tq = Tq;
+  p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+  p.causal = causal;
+  p.q_col0 = 0; p.q_group_stride = (int)lay[1]; p.q_hpg = (int)lay[2]; p.q_head_stride = (int)lay[3];
+  p.k_col0 = 0; p.k_group_stride = (int)lay[5]; p.k_hpg = (int)lay[6]; p.k_head_stride = (int)lay[7];
+  p.v_col0 = 0; p.v_group_stride = (int)lay[9]; p.v_hpg = (int)lay[10]; p.v_head_stride = (int)lay[11];
+  p.error = error;
+  static bool attr_set = false;
+  const int smem = (int)fa5::SMEM_TOTAL + 1024;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(fa5::fa_fwd_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((max_q + fa5::BM - 1) / fa5::BM, nh, batch);
+  fa5::fa_fwd_tcgen05_kernel<<<grid, 192, smem, st>>>(mq, mk, mv, p);
+  return (int)cudaGetLastError();
+}

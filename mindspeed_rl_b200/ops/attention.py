@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -56,6 +57,15 @@ def _ref_attention(q, k, v, cu_q, cu_k, causal):
     return out, lse
 
 
+def use_tcgen05_attention() -> bool:
+    """The tcgen05 forward kernel (``csrc/attention_tcgen05.cu``) serves head size 128 unless
+    ``MSRL_ATTN_TCGEN05=0``; everything else runs the mma.sync kernel of ``csrc/attention.cu``."""
+    return os.environ.get("MSRL_ATTN_TCGEN05", "1") != "0"
+
+
+_NOT_SUPPORTED = 801   # cudaErrorNotSupported: the shape is outside the tcgen05 kernel's cover
+
+
 def attn_varlen_fwd(qkv: torch.Tensor, layout: QKVLayout, cu_seqlens: torch.Tensor, max_seqlen: int,
                     causal: bool = True, kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                     cu_seqlens_k: Optional[torch.Tensor] = None
@@ -82,6 +92,17 @@ def attn_varlen_fwd(qkv: torch.Tensor, layout: QKVLayout, cu_seqlens: torch.Tens
         lay = _layout_array(qs, ks, vs)
         out = torch.empty(t, nh * hd, device=qkv.device, dtype=qkv.dtype)
         lse = torch.empty(nh, t, device=qkv.device, dtype=torch.float32)
+        if hd == 128 and use_tcgen05_attention():
+            from .gemm import _status_word
+            tk = t if kv is None else kv[0].shape[0]
+            rc = _lib.load().msrl_flash_attn_varlen_fwd_tcgen05(
+                ptr(flat[qs[0]:]), ptr(kb), ptr(vb), lay, ptr(out), c_ll(nh * hd), ptr(lse),
+                ptr(cu_seqlens), ptr(cu_k), c_int(batch), c_int(int(max_seqlen)), c_int(nh), c_int(nkv),
+                c_ll(t), c_ll(tk), c_int(hd), c_int(1 if causal else 0),
+                ptr(_status_word(qkv.device)), stream())
+            if rc != _NOT_SUPPORTED:
+                check(rc, "flash_attn_varlen_fwd_tcgen05")
+                return out, lse
         check(_lib.load().msrl_flash_attn_varlen_fwd(
             ptr(flat[qs[0]:]), ptr(kb), ptr(vb), lay, ptr(out), c_ll(nh * hd), ptr(lse),
             ptr(cu_seqlens), ptr(cu_k), c_int(batch), c_int(int(max_seqlen)), c_int(nh), c_int(nkv),

@@ -130,9 +130,13 @@ def case_attention(small: bool, iters: int):
     t = sum(lens)
     qkv = (0.5 * torch.randn(t, lay.width, device="cuda")).bfloat16()
     fl = sum(4.0 * l * l * nh * hd / 2 for l in lens)
-    out, lse = attn_varlen_fwd(qkv, lay, cu, max(lens))
-    ms = timeit(lambda: attn_varlen_fwd(qkv, lay, cu, max(lens)), iters)
-    report(f"flash_attn_varlen fwd T={t}", ms, flops=fl)
+    import os
+    for flag, name in (("0", "mma.sync"), ("1", "tcgen05")):
+        os.environ["MSRL_ATTN_TCGEN05"] = flag
+        out, lse = attn_varlen_fwd(qkv, lay, cu, max(lens))
+        ms = timeit(lambda: attn_varlen_fwd(qkv, lay, cu, max(lens)), iters)
+        report(f"flash_attn_varlen fwd {name} T={t}", ms, flops=fl)
+    G.check_status("cuda", "tcgen05 attention")
     do = torch.randn_like(out)
     ms = timeit(lambda: attn_varlen_bwd(do, qkv, out, lse, lay, cu, max(lens)), iters)
     report(f"flash_attn_varlen bwd T={t}", ms, flops=2.5 * fl)
