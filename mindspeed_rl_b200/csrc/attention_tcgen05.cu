@@ -4,13 +4,13 @@
 //   S = Q K^T        tcgen05.mma 128x128x16 (both operands K-major, TMA-staged with 128-byte swizzle)
 //                    into one of two TMEM score buffers, so the next tile's scores are computed
 //                    while this tile's soft-max runs;
-//   soft-max         four warps, one query row per thread: tcgen05.ld the row, mask, running max /
-//                    sum in the exp2 domain, P (bf16) written to shared memory in the UMMA K-major
-//                    swizzled layout, O rescaled in TMEM (tcgen05.ld / tcgen05.st) only when a row
-//                    maximum moved;
+//   soft-max         eight warps, two threads per query row (64 key columns each): tcgen05.ld the
+//                    row, mask, running max / sum in the exp2 domain, P (bf16) written to shared
+//                    memory in the UMMA K-major swizzled layout, O rescaled in TMEM (tcgen05.ld /
+//                    tcgen05.st) only when a row maximum moved by more than 2^8;
 //   O += P V         tcgen05.mma with V as an MN-major operand straight from its [keys, d] tile.
-// Warp roles (192 threads): warps 0-3 soft-max / epilogue (TMEM lane quarter = warp id), warp 4 TMA
-// producer, warp 5 TMEM allocation + MMA issue.  Causal masking is bottom-right aligned when the
+// Warp roles (320 threads): warps 0-7 soft-max / epilogue (TMEM lane quarter = warp id % 4), warp 8
+// TMA producer, warp 9 TMEM allocation + MMA issue.  Causal masking is bottom-right aligned when the
 // key sequence is longer than the query sequence, as in the mma.sync kernel of attention.cu,
 // which stays the fallback (other head sizes, backward).
 //
@@ -32,6 +32,7 @@ constexpr uint32_t SMEM_TOTAL = 6 * TILE_BYTES;        // 192 KiB
 constexpr uint32_t TMEM_COLS = 512;                    // S0 [0,128) S1 [128,256) O [256,384)
 constexpr long long WAIT_CYCLES = 4000000000LL;
 constexpr int OUT_PITCH = 144;
+constexpr int SOFTMAX_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, THREADS = 320;
 
 enum { ERR_Q = 11, ERR_K = 12, ERR_V = 13, ERR_S = 14, ERR_P = 15, ERR_PV = 16, ERR_EMPTY = 17 };
 
@@ -147,7 +148,7 @@ __device__ __forceinline__ int head_col(int col0, int gs, int hpg, int hs, int h
   return col0 + (h / hpg) * gs + (h % hpg) * hs;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params p) {
   extern __shared__ unsigned char smem_raw[];
@@ -155,6 +156,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_free[2], p_ready, pv_done;
   __shared__ uint32_t tmem_slot;
+  __shared__ float l_part[2][BM];
 
   const int b = blockIdx.z, h = blockIdx.y, mt = blockIdx.x;
   const int q0 = p.cu_q[b], qlen = p.cu_q[b + 1] - q0;
@@ -176,13 +178,13 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 4);
+      mbar_init(&s_free[i], SOFTMAX_WARPS);
     }
-    mbar_init(&p_ready, 4);
+    mbar_init(&p_ready, SOFTMAX_WARPS);
     mbar_init(&pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_slot)),
                  "r"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
@@ -193,7 +195,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const uint32_t tmem = tmem_slot;
   const uint32_t tmem_o = tmem + 256;
 
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int qc = head_col(p.q_col0, p.q_group_stride, p.q_hpg, p.q_head_stride, h);
@@ -220,7 +222,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tma_load_2d(sv + TILE_HALF, &map_v, &v_full[st], vc + 64, k0 + j * BN);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t id_s = idesc_bf16(BM, BN, false);
@@ -263,42 +265,69 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
     }
   } else {
-    // ---------------- soft-max + epilogue: thread = query row (TMEM lane) ----------------
-    const int row = warp * 32 + lane;                       // row inside the tile
+    // ---------------- soft-max + epilogue ----------------
+    // Two threads per query row: warps 0-3 own key columns [0, 64) of the tile, warps 4-7 columns
+    // [64, 128) (a warp reaches the TMEM lanes of its quarter, warp % 4).  Both read the whole
+    // score row for its maximum, so they agree on the running maximum without talking; each keeps
+    // the partial sum of its own columns, rescales its half of the O columns and writes its half
+    // of P.
+    const int wg = warp >> 2, quarter = warp & 3;
+    const int row = quarter * 32 + lane;                    // row inside the tile
     const int grow = m0 + row;                              // row inside the sequence
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f;
-    unsigned char* sp = smem + SMEM_P;
+    unsigned char* sp = smem + SMEM_P + wg * TILE_HALF;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
       ok = mbar_wait(&s_full[sb], (j >> 1) & 1, p.error, ERR_S);
       if (!ok) break;
       fence_after();
-      float s[BN];
+      const int kbase = j * BN;
+      const bool need_mask = (kbase + BN > klen) || (p.causal && (kbase + BN - 1 > m0 + off));
+      const int limit = min(klen, p.causal ? grow + off + 1 : klen) - kbase;   // valid columns of this row
+      float s[64], t[32];
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      // the other half: maximum only
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld32(tmem + lane_base + sb * BN + c * 32, v);
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = (wg ^ 1) * 64 + c * 32;
+        tmem_ld32(tmem + lane_base + sb * BN + col0, t);
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = v[i];
+          for (int i = 0; i < 32; ++i) t[i] = (col0 + i < limit) ? t[i] : -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, t[i]);
+          mx1 = fmaxf(mx1, t[i + 1]);
+          mx2 = fmaxf(mx2, t[i + 2]);
+          mx3 = fmaxf(mx3, t[i + 3]);
+        }
+      }
+      // this thread's half
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = wg * 64 + c * 32;
+        tmem_ld32(tmem + lane_base + sb * BN + col0, t);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = t[i];
+          if (need_mask) v = (col0 + i < limit) ? v : -INFINITY;
+          s[c * 32 + i] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, s[c * 32 + i]);
+          mx1 = fmaxf(mx1, s[c * 32 + i + 1]);
+          mx2 = fmaxf(mx2, s[c * 32 + i + 2]);
+          mx3 = fmaxf(mx3, s[c * 32 + i + 3]);
+        }
       }
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[sb]);              // the score buffer may be overwritten
-      const int kbase = j * BN;
-      const bool need_mask = (kbase + BN > klen) || (p.causal && (kbase + BN - 1 > m0 + off));
-      float mx = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < BN; ++i) {
-        float v = s[i] * p.scale_log2;
-        if (need_mask) {
-          const int key = kbase + i;
-          v = ((key < klen) && (!p.causal || key <= grow + off)) ? v : -INFINITY;
-        }
-        s[i] = v;
-        mx = fmaxf(mx, v);
-      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;   // scale > 0
       // The running maximum follows the row maximum lazily: it moves only when the row maximum
       // passed it by more than 8 (a factor 256, harmless in fp32 sums and bf16 P), so that O is
       // rescaled in TMEM on few tiles only.
@@ -306,13 +335,19 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (m_run != -INFINITY && m_new - m_run <= 8.f) m_new = m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = exp2f(m_run - m_use);
-      float sum = 0.f;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < BN; ++i) {
-        s[i] = exp2f(s[i] - m_use);
-        sum += s[i];
+      for (int i = 0; i < 64; i += 4) {
+        s[i] = exp2f(fmaf(s[i], p.scale_log2, -m_use));
+        s[i + 1] = exp2f(fmaf(s[i + 1], p.scale_log2, -m_use));
+        s[i + 2] = exp2f(fmaf(s[i + 2], p.scale_log2, -m_use));
+        s[i + 3] = exp2f(fmaf(s[i + 3], p.scale_log2, -m_use));
+        sum0 += s[i];
+        sum1 += s[i + 1];
+        sum2 += s[i + 2];
+        sum3 += s[i + 3];
       }
-      l_run = l_run * corr + sum;
+      l_run = l_run * corr + ((sum0 + sum1) + (sum2 + sum3));
       m_run = m_new;
       if (j > 0) {
         // the previous P V product must be finished before P is overwritten or O is rescaled
@@ -321,21 +356,19 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         fence_after();
         if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            float v[32];
-            tmem_ld32(tmem_o + lane_base + c * 32, v);
+          for (int c = 0; c < 2; ++c) {
+            tmem_ld32(tmem_o + lane_base + wg * 64 + c * 32, t);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= corr;
-            tmem_st32(tmem_o + lane_base + c * 32, v);
+            for (int i = 0; i < 32; ++i) t[i] *= corr;
+            tmem_st32(tmem_o + lane_base + wg * 64 + c * 32, t);
           }
         }
       }
-      // P row -> shared memory, K-major, 128-byte swizzle: 16-byte chunk index XOR (row % 8)
+      // P half row -> shared memory, K-major, 128-byte swizzle: 16-byte chunk index XOR (row % 8)
 #pragma unroll
-      for (int c8 = 0; c8 < BN / 8; ++c8) {
-        const int half = c8 >> 3, chunk = c8 & 7;
-        unsigned char* dst = sp + half * TILE_HALF + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
-        *reinterpret_cast<bf16x8*>(dst) = pack8(&s[c8 * 8]);
+      for (int chunk = 0; chunk < 8; ++chunk) {
+        unsigned char* dst = sp + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+        *reinterpret_cast<bf16x8*>(dst) = pack8(&s[chunk * 8]);
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic smem writes -> UMMA reads
       fence_before();
@@ -343,45 +376,45 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (lane == 0) mbar_arrive(&p_ready);
     }
     if (ok && n_tiles > 0) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, p.error, ERR_PV);
+    // the two partial sums of a row meet in shared memory
+    l_part[wg][row] = l_run;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");        // every soft-max thread reaches this once
     if (ok) {
       fence_after();
-      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      // O: 32 rows x 64 columns at a time through this warp's patch (P is no longer needed)
-      unsigned char* patch = sp + warp * (32 * OUT_PITCH);
-#pragma unroll 1
-      for (int c = 0; c < D / 64; ++c) {
+      const float l_row = l_part[0][row] + l_part[1][row];
+      const float inv_l = l_row > 0.f ? 1.f / l_row : 0.f;
+      // O: 32 rows x 64 columns through this warp's patch (all tiles are consumed: any stage is free)
+      unsigned char* patch = smem + warp * (32 * OUT_PITCH);
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          float v[32];
-          if (n_tiles > 0) {
-            tmem_ld32(tmem_o + lane_base + c * 64 + hh * 32, v);
+      for (int hh = 0; hh < 2; ++hh) {
+        float v[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem_o + lane_base + wg * 64 + hh * 32, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= inv_l;
-          } else {
+          for (int i = 0; i < 32; ++i) v[i] *= inv_l;
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          }
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<bf16x8*>(patch + lane * OUT_PITCH + hh * 64 + q * 16) = pack8(v + q * 8);
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
         }
-        __syncwarp();
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int r = it * 4 + (lane >> 3);
-          const int gr = m0 + warp * 32 + r;
-          if (gr < qlen)
-            st8(p.o + (long long)(q0 + gr) * p.o_stride_t + (long long)h * D + c * 64 + (lane & 7) * 8,
-                *reinterpret_cast<const bf16x8*>(patch + r * OUT_PITCH + (lane & 7) * 16));
-        }
-        __syncwarp();
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<bf16x8*>(patch + lane * OUT_PITCH + hh * 64 + q * 16) = pack8(v + q * 8);
       }
-      if (grow < qlen) p.lse[(long long)h * p.Tq + q0 + grow] = (m_run + log2f(l_run)) * 0.6931471805599453f;
+      __syncwarp();
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        const int gr = m0 + quarter * 32 + r;
+        if (gr < qlen)
+          st8(p.o + (long long)(q0 + gr) * p.o_stride_t + (long long)h * D + wg * 64 + (lane & 7) * 8,
+              *reinterpret_cast<const bf16x8*>(patch + r * OUT_PITCH + (lane & 7) * 16));
+      }
+      if (wg == 0 && grow < qlen) p.lse[(long long)h * p.Tq + q0 + grow] = (m_run + log2f(l_row)) * 0.6931471805599453f;
     }
   }
   fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
   }
 }
@@ -470,6 +503,6 @@ MSRL_API int msrl_flash_attn_varlen_fwd_tcgen05(const void* q, const void* k, co
     attr_set = true;
   }
   dim3 grid((max_q + fa5::BM - 1) / fa5::BM, nh, batch);
-  fa5::fa_fwd_tcgen05_kernel<<<grid, 192, smem, st>>>(mq, mk, mv, p);
+  fa5::fa_fwd_tcgen05_kernel<<<grid, fa5::THREADS, smem, st>>>(mq, mk, mv, p);
   return (int)cudaGetLastError();
 }
