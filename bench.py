@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (development only)")
     ap.add_argument("--pack-tokens", type=int, default=16384, help="token budget of one training micro-batch")
     ap.add_argument("--eager", action="store_true", help="disable CUDA-graph decode")
-    ap.add_argument("--keep-layers", type=int, default=0,
+    ap.add_argument("--keep-layers", type=int, default=14,
                     help="layers whose activations stay resident (the others are fully recomputed in the backward)")
     return ap.parse_args()
 

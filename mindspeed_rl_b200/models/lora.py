@@ -8,8 +8,8 @@ reshards for rollout, ``workers/resharding/vllm_weight_container.py:336-420``).
 Under tensor parallelism the adapter follows the base weight's split:
 
 * column-parallel (``linear_qkv``, ``linear_fc1``): ``A`` replicated, ``B`` split over ``out``.  Each
-  rank back-propagates only its output slice into ``A``, so ``A``'s gradient is a partial sum
-  (``tp_reduce_grad``).
+  rank back-propagates only its output slice, so the tiny ``dy B`` ([tokens, r]) is all-reduced
+  over TP inside ``column_bwd`` before ``A``'s gradient is formed.
 * row-parallel (``linear_proj``, ``linear_fc2``): ``A`` split over ``in``, ``B`` replicated.  The tiny
   ``x A^T`` ([tokens, r]) is all-reduced over TP, after which every rank adds
   ``s * (xA^T)[its tokens] B^T`` to its (reduce-scattered or all-reduced) output; the big
