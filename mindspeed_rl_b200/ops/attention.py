@@ -130,6 +130,17 @@ def attn_varlen_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, ls
         lay = _layout_array(qs, ks, vs)
         delta = _workspace("attn_delta", nh * t, qkv.device)
         do = dout.contiguous()
+        if hd == 128 and use_tcgen05_attention():
+            from .gemm import _status_word
+            rc = _lib.load().msrl_flash_attn_varlen_bwd_tcgen05(
+                ptr(flat[qs[0]:]), ptr(flat[ks[0]:]), ptr(flat[vs[0]:]), lay, ptr(out), ptr(do),
+                c_ll(nh * hd), ptr(lse), ptr(delta), ptr(dflat[qs[0]:]), ptr(dflat[ks[0]:]),
+                ptr(dflat[vs[0]:]), ptr(cu_seqlens), ptr(cu_seqlens), c_int(batch),
+                c_int(int(max_seqlen)), c_int(int(max_seqlen)), c_int(nh), c_int(nkv), c_ll(t), c_ll(t),
+                c_int(hd), c_int(1 if causal else 0), ptr(_status_word(qkv.device)), stream())
+            if rc != _NOT_SUPPORTED:
+                check(rc, "flash_attn_varlen_bwd_tcgen05")
+                return dqkv
         check(_lib.load().msrl_flash_attn_varlen_bwd(
             ptr(flat[qs[0]:]), ptr(flat[ks[0]:]), ptr(flat[vs[0]:]), lay, ptr(out), ptr(do),
             c_ll(nh * hd), ptr(lse), ptr(delta), ptr(dflat[qs[0]:]), ptr(dflat[ks[0]:]),

@@ -138,8 +138,11 @@ def case_attention(small: bool, iters: int):
         report(f"flash_attn_varlen fwd {name} T={t}", ms, flops=fl)
     G.check_status("cuda", "tcgen05 attention")
     do = torch.randn_like(out)
-    ms = timeit(lambda: attn_varlen_bwd(do, qkv, out, lse, lay, cu, max(lens)), iters)
-    report(f"flash_attn_varlen bwd T={t}", ms, flops=2.5 * fl)
+    for flag, name in (("0", "mma.sync"), ("1", "tcgen05")):
+        os.environ["MSRL_ATTN_TCGEN05"] = flag
+        ms = timeit(lambda: attn_varlen_bwd(do, qkv, out, lse, lay, cu, max(lens)), iters)
+        report(f"flash_attn_varlen bwd {name} T={t}", ms, flops=2.5 * fl)
+    G.check_status("cuda", "tcgen05 attention")
 
 
 def case_decode(small: bool, iters: int):

@@ -95,3 +95,29 @@ def test_flash_attention_fwd_tcgen05(nh, nkv, interleaved, causal, monkeypatch):
     torch.testing.assert_close(lse.cpu(), lse_r, rtol=1e-2, atol=2e-2)
     torch.testing.assert_close(out.float(), out_m.float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(lse, lse_m, rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("nh,nkv,interleaved", [(4, 2, True), (7, 1, False)])
+def test_flash_attention_bwd_tcgen05(nh, nkv, interleaved, causal, monkeypatch):
+    """tcgen05 backward (dQ kernel, dK/dV kernel, delta) against autograd through the fp32
+    formulation and against the mma.sync kernels."""
+    from mindspeed_rl_b200 import ops
+    from mindspeed_rl_b200.ops.layouts import QKVLayout
+    torch.manual_seed(12)
+    lay = QKVLayout(nh, nkv, 128, interleaved)
+    lens = [1, 129, 640, 77, 1000, 256]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    t = int(cu[-1])
+    qkv = (0.7 * torch.randn(t, lay.width, device="cuda")).bfloat16()
+    dout = (0.5 * torch.randn(t, nh * 128, device="cuda")).bfloat16()
+    monkeypatch.setenv("MSRL_ATTN_TCGEN05", "1")
+    out, lse = ops.attn_varlen_fwd(qkv, lay, cu.cuda(), max(lens), causal=causal)
+    dqkv = ops.attn_varlen_bwd(dout, qkv, out, lse, lay, cu.cuda(), max(lens), causal=causal)
+    G.check_status(torch.device("cuda", torch.cuda.current_device()), "tcgen05 attention")
+    monkeypatch.setenv("MSRL_ATTN_TCGEN05", "0")
+    dqkv_m = ops.attn_varlen_bwd(dout, qkv, out, lse, lay, cu.cuda(), max(lens), causal=causal)
+    out_r, lse_r = ops.attn_varlen_fwd(qkv.cpu(), lay, cu, max(lens), causal=causal)
+    dqkv_r = ops.attn_varlen_bwd(dout.cpu(), qkv.cpu(), out_r, lse_r, lay, cu, max(lens), causal=causal)
+    torch.testing.assert_close(dqkv.float().cpu(), dqkv_r.float(), rtol=3e-2, atol=5e-2)
+    torch.testing.assert_close(dqkv.float(), dqkv_m.float(), rtol=3e-2, atol=5e-2)
