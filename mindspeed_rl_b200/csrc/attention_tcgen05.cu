@@ -19,22 +19,24 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
+
 #include "mma_utils.cuh"
 
 namespace msrl {
 namespace fa5 {
 
-constexpr int BM = 128, BN = 128, D = 128;
+constexpr int BM = 128, D = 128;
 constexpr uint32_t TILE_HALF = 128 * 64 * 2;          // one [128 rows x 64 cols] bf16 swizzled half tile
 constexpr uint32_t TILE_BYTES = 2 * TILE_HALF;         // 32 KiB
-constexpr uint32_t SMEM_Q = 0, SMEM_K = TILE_BYTES, SMEM_V = 3 * TILE_BYTES, SMEM_P = 5 * TILE_BYTES;
-constexpr uint32_t SMEM_TOTAL = 6 * TILE_BYTES;        // 192 KiB
-constexpr uint32_t TMEM_COLS = 512;                    // S0 [0,128) S1 [128,256) O [256,384)
+constexpr uint32_t SMEM_Q = 0;
+constexpr uint32_t TMEM_COLS = 512;                    // backward kernels
+constexpr uint32_t fwd_smem_bytes(int bn) { return TILE_BYTES + 4u * (2u * bn * 64 * 2) + 128u * bn * 2; }
 constexpr long long WAIT_CYCLES = 4000000000LL;
 constexpr int OUT_PITCH = 144;
 constexpr int SOFTMAX_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, THREADS = 320;
 
-enum { ERR_Q = 11, ERR_K = 12, ERR_V = 13, ERR_S = 14, ERR_P = 15, ERR_PV = 16, ERR_EMPTY = 17 };
+enum { ERR_SMEM = 10, ERR_Q = 11, ERR_K = 12, ERR_V = 13, ERR_S = 14, ERR_P = 15, ERR_PV = 16, ERR_EMPTY = 17 };
 
 struct Params {
   __nv_bfloat16* o;
@@ -148,7 +150,11 @@ __device__ __forceinline__ int head_col(int col0, int gs, int hpg, int hs, int h
   return col0 + (h / hpg) * gs + (h % hpg) * hs;
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+// BN = keys per tile.  128: one CTA per SM (192 KiB of shared memory, 512 TMEM columns).  64: two
+// CTAs per SM (112 KiB, 256 columns each), so that one CTA's soft-max, prologue and epilogue overlap
+// the other's tensor work.
+template <int BN>
+__global__ void __launch_bounds__(THREADS, BN == 128 ? 1 : 2)
 fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params p) {
   extern __shared__ unsigned char smem_raw[];
@@ -156,7 +162,10 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_free[2], p_ready, pv_done;
   __shared__ uint32_t tmem_slot;
-  __shared__ float l_part[2][BM];
+  constexpr uint32_t KV_HALF = BN * 64 * 2, KV_BYTES = 2 * KV_HALF;
+  constexpr uint32_t SMEM_K = TILE_BYTES, SMEM_V = SMEM_K + 2 * KV_BYTES, SMEM_P = SMEM_V + 2 * KV_BYTES;
+  constexpr uint32_t TMEM_COLS = BN == 128 ? 512 : 256;      // S0 [0,BN) S1 [BN,2BN) O [2BN, 2BN+128)
+  constexpr int HALF = BN / 2, NCH = HALF / 32;              // key columns per soft-max thread
 
   const int b = blockIdx.z, h = blockIdx.y, mt = blockIdx.x;
   const int q0 = p.cu_q[b], qlen = p.cu_q[b + 1] - q0;
@@ -169,6 +178,17 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (p.causal) kmax = min(klen, m0 + BM + off);
   const int n_tiles = kmax > 0 ? (kmax + BN - 1) / BN : 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    // the tiles must fit behind the 1024-byte alignment of the dynamic segment (the launch leaves
+    // less than a full KiB of slack when two CTAs share an SM)
+    uint32_t dyn;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;\n" : "=r"(dyn));
+    if ((uint32_t)(smem - smem_raw) + fwd_smem_bytes(BN) > dyn) {
+      if (threadIdx.x == 0) atomicCAS(p.error, 0, ERR_SMEM);
+      return;
+    }
+  }
+  float (*l_part)[BM] = reinterpret_cast<float (*)[BM]>(smem + SMEM_P);   // used after the last P V product
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -193,7 +213,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tmem_o = tmem + 256;
+  const uint32_t tmem_o = tmem + 2 * BN;
 
   if (warp == TMA_WARP) {
     // ---------------- TMA producer ----------------
@@ -210,16 +230,16 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t use = j >> 1;
         if (use > 0) ok = mbar_wait(&k_empty[st], (use - 1) & 1, p.error, ERR_EMPTY);
         if (!ok) break;
-        mbar_expect_tx(&k_full[st], TILE_BYTES);
-        unsigned char* sk = smem + SMEM_K + st * TILE_BYTES;
+        mbar_expect_tx(&k_full[st], KV_BYTES);
+        unsigned char* sk = smem + SMEM_K + st * KV_BYTES;
         tma_load_2d(sk, &map_k, &k_full[st], kc, k0 + j * BN);
-        tma_load_2d(sk + TILE_HALF, &map_k, &k_full[st], kc + 64, k0 + j * BN);
+        tma_load_2d(sk + KV_HALF, &map_k, &k_full[st], kc + 64, k0 + j * BN);
         if (use > 0) ok = mbar_wait(&v_empty[st], (use - 1) & 1, p.error, ERR_EMPTY);
         if (!ok) break;
-        mbar_expect_tx(&v_full[st], TILE_BYTES);
-        unsigned char* sv = smem + SMEM_V + st * TILE_BYTES;
+        mbar_expect_tx(&v_full[st], KV_BYTES);
+        unsigned char* sv = smem + SMEM_V + st * KV_BYTES;
         tma_load_2d(sv, &map_v, &v_full[st], vc, k0 + j * BN);
-        tma_load_2d(sv + TILE_HALF, &map_v, &v_full[st], vc + 64, k0 + j * BN);
+        tma_load_2d(sv + KV_HALF, &map_v, &v_full[st], vc + 64, k0 + j * BN);
       }
     }
   } else if (warp == MMA_WARP) {
@@ -233,11 +253,11 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (!mbar_wait(&k_full[st], (j >> 1) & 1, p.error, ERR_K)) return false;
         if (j >= 2 && !mbar_wait(&s_free[st], ((j >> 1) - 1) & 1, p.error, ERR_S)) return false;
         fence_after();
-        const uint32_t k_addr = smem_u32(smem + SMEM_K + st * TILE_BYTES);
+        const uint32_t k_addr = smem_u32(smem + SMEM_K + st * KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t o2 = (kk >> 2) * TILE_HALF + (kk & 3) * 32;
-          umma(tmem + st * BN, desc_sw128(q_addr + o2, 16, 1024), desc_sw128(k_addr + o2, 16, 1024), id_s,
+          umma(tmem + st * BN, desc_sw128(q_addr + (kk >> 2) * TILE_HALF + (kk & 3) * 32, 16, 1024),
+               desc_sw128(k_addr + (kk >> 2) * KV_HALF + (kk & 3) * 32, 16, 1024), id_s,
                kk > 0 ? 1u : 0u);
         }
         commit(&s_full[st]);
@@ -253,11 +273,11 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ok = mbar_wait(&p_ready, j & 1, p.error, ERR_P) && mbar_wait(&v_full[st], (j >> 1) & 1, p.error, ERR_V);
         if (!ok) break;
         fence_after();
-        const uint32_t v_addr = smem_u32(smem + SMEM_V + st * TILE_BYTES);
+        const uint32_t v_addr = smem_u32(smem + SMEM_V + st * KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint32_t pa = p_addr + (kk >> 2) * TILE_HALF + (kk & 3) * 32;
-          umma(tmem_o, desc_sw128(pa, 16, 1024), desc_sw128(v_addr + kk * 2048, TILE_HALF, 1024), id_o,
+          umma(tmem_o, desc_sw128(pa, 16, 1024), desc_sw128(v_addr + kk * 2048, KV_HALF, 1024), id_o,
                (j > 0 || kk > 0) ? 1u : 0u);
         }
         commit(&pv_done);
@@ -276,7 +296,9 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int grow = m0 + row;                              // row inside the sequence
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f;
-    unsigned char* sp = smem + SMEM_P + wg * TILE_HALF;
+    unsigned char* sp = smem + SMEM_P + ((wg * HALF) >> 6) * TILE_HALF;   // the 64-column half tile of P
+    constexpr int NCHUNK = HALF / 8;
+    const int chunk0 = ((wg * HALF) & 63) >> 3;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
@@ -286,12 +308,12 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const int kbase = j * BN;
       const bool need_mask = (kbase + BN > klen) || (p.causal && (kbase + BN - 1 > m0 + off));
       const int limit = min(klen, p.causal ? grow + off + 1 : klen) - kbase;   // valid columns of this row
-      float s[64], t[32];
+      float s[HALF], t[32];
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
       // the other half: maximum only
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = (wg ^ 1) * 64 + c * 32;
+      for (int c = 0; c < NCH; ++c) {
+        const int col0 = (wg ^ 1) * HALF + c * 32;
         tmem_ld32(tmem + lane_base + sb * BN + col0, t);
         if (need_mask) {
 #pragma unroll
@@ -307,8 +329,8 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
       // this thread's half
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = wg * 64 + c * 32;
+      for (int c = 0; c < NCH; ++c) {
+        const int col0 = wg * HALF + c * 32;
         tmem_ld32(tmem + lane_base + sb * BN + col0, t);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -337,7 +359,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const float corr = exp2f(m_run - m_use);
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {
+      for (int i = 0; i < HALF; i += 4) {
         s[i] = exp2f(fmaf(s[i], p.scale_log2, -m_use));
         s[i + 1] = exp2f(fmaf(s[i + 1], p.scale_log2, -m_use));
         s[i + 2] = exp2f(fmaf(s[i + 2], p.scale_log2, -m_use));
@@ -366,8 +388,8 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
       // P half row -> shared memory, K-major, 128-byte swizzle: 16-byte chunk index XOR (row % 8)
 #pragma unroll
-      for (int chunk = 0; chunk < 8; ++chunk) {
-        unsigned char* dst = sp + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+      for (int chunk = 0; chunk < NCHUNK; ++chunk) {
+        unsigned char* dst = sp + (row >> 3) * 1024 + (row & 7) * 128 + (((chunk0 + chunk) ^ (row & 7)) << 4);
         *reinterpret_cast<bf16x8*>(dst) = pack8(&s[chunk * 8]);
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic smem writes -> UMMA reads
@@ -702,7 +724,7 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int b = blockIdx.z, hk = blockIdx.y, nt = blockIdx.x;
   const int q0 = p.cu_q[b], qlen = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], klen = p.cu_k[b + 1] - k0;
-  const int kb = nt * BN;                                  // first key of this CTA
+  const int kb = nt * BM;                                  // first key of this CTA
   if (kb >= klen) return;
   const int rep = p.nh / p.nkv;
   const int off = klen - qlen;
@@ -764,8 +786,8 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     }
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
-      constexpr uint32_t id_s = idesc_bf16(BN, 64, false);
-      constexpr uint32_t id_o = idesc_bf16(BN, D, true);
+      constexpr uint32_t id_s = idesc_bf16(BM, 64, false);
+      constexpr uint32_t id_o = idesc_bf16(BM, D, true);
       const uint32_t k_addr = smem_u32(smem + KV_SMEM_K), v_addr = smem_u32(smem + KV_SMEM_V);
       const uint32_t p_addr = smem_u32(smem + KV_SMEM_P), ds_addr = smem_u32(smem + KV_SMEM_DS);
       auto issue_s = [&](int it) -> bool {
@@ -931,10 +953,15 @@ MSRL_API int msrl_flash_attn_varlen_fwd_tcgen05(const void* q, const void* k, co
     const long long* l = lay + 4 * i;
     if (l[0] % 8 != 0 || l[1] % 8 != 0 || l[3] % 8 != 0 || l[2] <= 0) return (int)cudaErrorNotSupported;
   }
+  static int bn = 0;
+  if (bn == 0) {
+    const char* e = getenv("MSRL_ATTN_KEY_TILE");
+    bn = (e != nullptr && atoi(e) == 128) ? 128 : 64;
+  }
   CUtensorMap mq, mk, mv;
   if (!fa5_make_map(&mq, q, Tq, fa5_width(nh, lay[1], lay[2], lay[3]), lay[0]) ||
-      !fa5_make_map(&mk, k, Tk, fa5_width(nkv, lay[5], lay[6], lay[7]), lay[4]) ||
-      !fa5_make_map(&mv, v, Tk, fa5_width(nkv, lay[9], lay[10], lay[11]), lay[8]))
+      !fa5_make_map(&mk, k, Tk, fa5_width(nkv, lay[5], lay[6], lay[7]), lay[4], bn) ||
+      !fa5_make_map(&mv, v, Tk, fa5_width(nkv, lay[9], lay[10], lay[11]), lay[8], bn))
     return (int)cudaErrorNotSupported;
   fa5::Params p{};
   p.o = (__nv_bfloat16*)o;
@@ -952,14 +979,19 @@ MSRL_API int msrl_flash_attn_varlen_fwd_tcgen05(const void* q, const void* k, co
   p.v_col0 = 0; p.v_group_stride = (int)lay[9]; p.v_hpg = (int)lay[10]; p.v_head_stride = (int)lay[11];
   p.error = error;
   static bool attr_set = false;
-  const int smem = (int)fa5::SMEM_TOTAL + 1024;
+  const int smem = (int)fa5::fwd_smem_bytes(bn) + (bn == 128 ? 1024 : 896);   // 64: two CTAs in 228 KiB
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(fa5::fa_fwd_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = bn == 128
+        ? cudaFuncSetAttribute(fa5::fa_fwd_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+        : cudaFuncSetAttribute(fa5::fa_fwd_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   dim3 grid((max_q + fa5::BM - 1) / fa5::BM, nh, batch);
-  fa5::fa_fwd_tcgen05_kernel<<<grid, fa5::THREADS, smem, st>>>(mq, mk, mv, p);
+  if (bn == 128)
+    fa5::fa_fwd_tcgen05_kernel<128><<<grid, fa5::THREADS, smem, st>>>(mq, mk, mv, p);
+  else
+    fa5::fa_fwd_tcgen05_kernel<64><<<grid, fa5::THREADS, smem, st>>>(mq, mk, mv, p);
   return (int)cudaGetLastError();
 }
 
@@ -1024,7 +1056,7 @@ MSRL_API int msrl_flash_attn_varlen_bwd_tcgen05(const void* q, const void* k, co
   }
   const long long warps = Tq * nh;
   fa5::fa_delta128_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(p);
-  dim3 grid_kv((max_k + fa5::BN - 1) / fa5::BN, nkv, batch);
+  dim3 grid_kv((max_k + fa5::BM - 1) / fa5::BM, nkv, batch);
   fa5::fa_bwd_dkdv_tcgen05_kernel<<<grid_kv, fa5::THREADS, smem_kv, st>>>(q64, do64, k128, v128, p);
   dim3 grid_q((max_q + fa5::BM - 1) / fa5::BM, nh, batch);
   fa5::fa_bwd_dq_tcgen05_kernel<<<grid_q, fa5::THREADS, smem_dq, st>>>(q128, do128, k64, v64, p);
