@@ -1,0 +1,73 @@
+"""MoE kernels (plan, permute, combine, slot-dot, grouped tcgen05 GEMM) against the PyTorch
+formulation of the same ops."""
+import pytest
+import torch
+
+from mindspeed_rl_b200.ops import gemm as G
+from mindspeed_rl_b200.ops import moe as M
+
+pytestmark = pytest.mark.gpu
+
+
+def _cpu_plan(plan):
+    return M.MoePlan(plan.counts.cpu(), plan.offsets.cpu(), plan.pos.cpu(), plan.tile_expert.cpu(), plan.max_rows,
+                     plan.tokens, plan.k, plan.num_experts)
+
+
+@pytest.mark.parametrize("t,k,e", [(1000, 8, 128), (37, 2, 4), (5000, 8, 16)])
+def test_plan_matches_reference(t, k, e):
+    torch.manual_seed(0)
+    idx = torch.randint(0, e, (t, k), device="cuda")
+    plan = M.moe_plan(idx, e)
+    ref = M.moe_plan(idx.cpu(), e)
+    assert plan.counts.cpu().tolist() == ref.counts.tolist()
+    assert plan.offsets.cpu().tolist() == ref.offsets.tolist()
+    assert plan.pos.cpu().tolist() == ref.pos.tolist()
+    assert plan.tile_expert.cpu().tolist() == ref.tile_expert.tolist()
+
+
+@pytest.mark.parametrize("t,k,e,h,f", [(777, 8, 16, 2048, 768), (130, 2, 4, 256, 128)])
+def test_moe_layer_kernels(t, k, e, h, f):
+    torch.manual_seed(1)
+    dev = "cuda"
+    x = torch.randn(t, h, device=dev).bfloat16()
+    idx = torch.stack([torch.randperm(e, device=dev)[:k] for _ in range(t)])
+    p = torch.rand(t, k, device=dev)
+    w1 = (torch.randn(h, e, 2 * f, device=dev) * 0.05).bfloat16()
+    w2 = (torch.randn(e, f, h, device=dev) * 0.05).bfloat16()
+    plan = M.moe_plan(idx, e)
+    cplan = _cpu_plan(plan)
+    xp = M.moe_permute(x, plan)
+    xp_r = M.moe_permute(x.cpu(), cplan)
+    used = int(plan.offsets[-1])
+    assert torch.equal(xp[:used].cpu(), xp_r[:used])
+    # forward: MN-major operands
+    gu = M.grouped_gemm(xp, plan, w1.view(h, e * 2 * f), True, 2 * f, 0, 2 * f)
+    gu_r = M.grouped_gemm(xp_r.float(), cplan, w1.cpu().float().view(h, e * 2 * f), True, 2 * f, 0, 2 * f)
+    torch.testing.assert_close(gu[:used].float().cpu(), gu_r[:used], rtol=2e-2, atol=2e-2)
+    act = (torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).bfloat16()
+    act[used:] = 0
+    y = M.grouped_gemm(act, plan, w2.view(e * f, h), True, 0, f, h)
+    y_r = M.grouped_gemm(act.cpu().float(), cplan, w2.cpu().float().view(e * f, h), True, 0, f, h)
+    torch.testing.assert_close(y[:used].float().cpu(), y_r[:used], rtol=2e-2, atol=2e-2)
+    out = M.moe_combine(y, plan, p)
+    out_r = M.moe_combine(y.cpu().float(), cplan, p.cpu())
+    torch.testing.assert_close(out.float().cpu(), out_r, rtol=2e-2, atol=2e-2)
+    # backward: scaled scatter, K-major operands, slot dot
+    dout = torch.randn(t, h, device=dev).bfloat16()
+    dy = M.moe_permute(dout, plan, p)
+    dy_r = M.moe_permute(dout.cpu().float(), cplan, p.cpu())
+    torch.testing.assert_close(dy[:used].float().cpu(), dy_r[:used], rtol=1e-2, atol=1e-2)
+    dact = M.grouped_gemm(dy, plan, w2.view(e * f, h), False, 0, f, f)
+    dact_r = M.grouped_gemm(dy.cpu().float(), cplan, w2.cpu().float().view(e * f, h), False, 0, f, f)
+    torch.testing.assert_close(dact[:used].float().cpu(), dact_r[:used], rtol=2e-2, atol=2e-2)
+    real = torch.zeros(plan.max_rows, 1, device=dev)
+    real[plan.pos.long()] = 1                       # pad rows stay zero, as after a real backward
+    dgu = (torch.randn(plan.max_rows, 2 * f, device=dev) * real).bfloat16()
+    dxp = M.grouped_gemm(dgu, plan, w1.view(h, e * 2 * f), False, 2 * f, 0, h)
+    dxp_r = M.grouped_gemm(dgu.cpu().float(), cplan, w1.cpu().float().view(h, e * 2 * f), False, 2 * f, 0, h)
+    torch.testing.assert_close(dxp[:used].float().cpu(), dxp_r[:used], rtol=2e-2, atol=3e-2)
+    dw = M.moe_slot_dot(dout, y, plan)
+    dw_r = M.moe_slot_dot(dout.cpu().float(), y.cpu().float(), cplan)
+    torch.testing.assert_close(dw.cpu(), dw_r, rtol=2e-2, atol=2e-2)
+    G.check_status(torch.device("cuda", torch.cuda.current_device()), "grouped gemm")
