@@ -234,6 +234,8 @@ class MoELayer(nn.Module):
                 if (keep and cfg.moe_aux_loss_coeff) else None
         self.last_aux_loss = aux.detach() if aux is not None else None
         self.token_counts = torch.bincount(top_idx.reshape(-1), minlength=cfg.num_experts)
+        if self.ep_size == 1:
+            return self._forward_local(x, xr, top_p, top_idx, aux, comm, keep)
         xp, plan = self._dispatch(x, top_idx)
         y_local, gus, acts = self._experts_fwd(xp, plan["local_counts"], keep)
         y_sorted = self._undispatch(y_local, plan)
@@ -255,9 +257,91 @@ class MoELayer(nn.Module):
                    w_sorted=w_sorted, shared=shared_ctx)
         return out, ctx
 
+    # ---- all experts on this rank: dispatch plan + grouped GEMMs, no host round trip in the forward ----
+    def _shared_fwd(self, x, comm, keep):
+        gu = torch.matmul(x, self.shared_experts.linear_fc1.weight.t())
+        act = ops.swiglu_fwd(gu)
+        y = comm.reduce_out(torch.matmul(act, self.shared_experts.linear_fc2.weight.t()))
+        return y, ((gu, act) if keep else None)
+
+    def _forward_local(self, x, xr, top_p, top_idx, aux, comm, keep):
+        from ..ops import moe as K
+
+        c = self.cfg
+        e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
+        w1, w2 = self._w1().reshape(h, e * 2 * f), self._w2().reshape(e * f, h)
+        plan = K.moe_plan(top_idx, e)
+        xp = K.moe_permute(x, plan)
+        gu = K.grouped_gemm(xp, plan, w1, True, 2 * f, 0, 2 * f)
+        act = ops.swiglu_fwd(gu)
+        y = K.grouped_gemm(act, plan, w2, True, 0, f, h)
+        out = K.moe_combine(y, plan, top_p.detach())
+        shared_ctx = None
+        if self.shared_experts is not None:
+            sh, shared_ctx = self._shared_fwd(x, comm, keep)
+            out = out + sh
+        if not keep:
+            return out, None
+        return out, dict(local=True, xr=xr, top_p=top_p, aux=aux, plan=plan, xp=xp, gu=gu, act=act, y=y,
+                         shared=shared_ctx)
+
+    def _backward_local(self, ctx, x, dout, comm) -> torch.Tensor:
+        from ..ops import moe as K
+        from .gpt import grad_buffer
+
+        c = self.cfg
+        e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
+        w1, w2 = self._w1().reshape(h, e * 2 * f), self._w2().reshape(e * f, h)
+        plan, top_p = ctx["plan"], ctx["top_p"]
+        dy = K.moe_permute(dout, plan, top_p.detach())                    # rows scaled by their combine weight
+        dprob = K.moe_slot_dot(dout, ctx["y"], plan)                      # [T, k] fp32
+        dact = K.grouped_gemm(dy, plan, w2, False, 0, f, f)
+        dgu = ops.swiglu_bwd(ctx["gu"], dact)
+        dxp = K.grouped_gemm(dgu, plan, w1, False, 2 * f, 0, h)
+        if self.experts.weight1.requires_grad:
+            g1 = grad_buffer(self.experts.weight1).view(h, e, 2 * f)
+            g2 = grad_buffer(self.experts.weight2).view(e, f, h)
+            counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
+            xp, act = ctx["xp"], ctx["act"]
+            for j, n in enumerate(counts):
+                if n == 0:
+                    continue
+                r = slice(offsets[j], offsets[j] + n)
+                g2[j].add_(torch.matmul(act[r].t(), dy[r]).to(g2.dtype))
+                g1[:, j].add_(torch.matmul(xp[r].t(), dgu[r]).to(g1.dtype))
+        dx = K.moe_combine(dxp, plan).float()
+        return self._router_and_shared_bwd(ctx, x, dout, comm, dx, dprob)
+
+    def _router_and_shared_bwd(self, ctx, x, dout, comm, dx, dprob) -> torch.Tensor:
+        """Probabilities (+ auxiliary loss) back to logits, x and the router weight; shared experts."""
+        from .gpt import accum_wgrad, grad_buffer
+
+        outs, grads = [ctx["top_p"]], [dprob]
+        if ctx["aux"] is not None:
+            outs.append(ctx["aux"])
+            grads.append(torch.ones_like(ctx["aux"]))
+        wants = [ctx["xr"]] + ([self.router.weight] if self.router.weight.requires_grad else [])
+        got = torch.autograd.grad(outs, wants, grads, allow_unused=True)
+        if got[0] is not None:
+            dx += got[0]
+        if len(got) > 1 and got[1] is not None:
+            grad_buffer(self.router.weight).add_(got[1].to(grad_buffer(self.router.weight).dtype))
+        if self.shared_experts is not None:
+            gu, act = ctx["shared"]
+            fc1, fc2 = self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight
+            d_sh = comm.reduce_out_bwd(dout)
+            dact = torch.matmul(d_sh, fc2)
+            accum_wgrad(fc2, d_sh, act)
+            dgu = ops.swiglu_bwd(gu, dact)
+            dx += torch.matmul(dgu, fc1).float()
+            accum_wgrad(fc1, dgu, x)
+        return dx.to(x.dtype)
+
     def backward_tokens(self, ctx, x: torch.Tensor, dout: torch.Tensor, comm) -> torch.Tensor:
         from .gpt import accum_wgrad, grad_buffer
 
+        if ctx.get("local"):
+            return self._backward_local(ctx, x, dout, comm)
         plan = ctx["plan"]
         d_tok = dout[plan["token_of"]]                                    # [T*k, H] in sorted-slot order
         dy_sorted = d_tok * ctx["w_sorted"].unsqueeze(-1)

@@ -211,7 +211,48 @@ def case_sampler(small: bool, iters: int):
     report(f"sampler B={b} V={v}", ms, bytes_=2.0 * b * v * 2, note="two passes over the logits")
 
 
-CASES = {"gemm": case_gemm, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
+def case_moe(small: bool, iters: int):
+    """Qwen3-30B-A3B expert shapes on one expert-parallel rank: 16 local experts, hidden 2048,
+    expert FFN 768, top-8 routing."""
+    from . import moe as K
+    from . import swiglu_fwd
+    e, h, f, k = 16, 2048, 768, 8
+    t = 2048 if small else 16384
+    x = torch.randn(t, h, device="cuda").bfloat16()
+    idx = torch.stack([torch.randperm(e, device="cuda")[:k] for _ in range(256)]).repeat(t // 256, 1)
+    p = torch.rand(t, k, device="cuda")
+    w1 = (torch.randn(h, e, 2 * f, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(e, f, h, device="cuda") * 0.02).bfloat16()
+    w1_2d, w2_2d = w1.view(h, e * 2 * f), w2.view(e * f, h)
+    plan = K.moe_plan(idx, e)
+    ms = timeit(lambda: K.moe_plan(idx, e), iters)
+    report(f"moe_plan slots={t * k} E={e}", ms, bytes_=t * k * 12.0)
+    xp = K.moe_permute(x, plan)
+    ms = timeit(lambda: K.moe_permute(x, plan), iters)
+    report(f"moe_permute T={t} k={k} H={h}", ms, bytes_=(t + t * k) * h * 2.0)
+    rows = t * k
+    gu = K.grouped_gemm(xp, plan, w1_2d, True, 2 * f, 0, 2 * f)
+    ms = timeit(lambda: K.grouped_gemm(xp, plan, w1_2d, True, 2 * f, 0, 2 * f), iters)
+    report(f"grouped_gemm w1 (MN-major B) rows={rows}", ms, flops=2.0 * rows * h * 2 * f)
+    act = swiglu_fwd(gu)
+    y = K.grouped_gemm(act, plan, w2_2d, True, 0, f, h)
+    ms = timeit(lambda: K.grouped_gemm(act, plan, w2_2d, True, 0, f, h), iters)
+    report(f"grouped_gemm w2 (MN-major B) rows={rows}", ms, flops=2.0 * rows * f * h)
+    ms = timeit(lambda: K.grouped_gemm(y, plan, w2_2d, False, 0, f, f), iters)
+    report(f"grouped_gemm dact (K-major B) rows={rows}", ms, flops=2.0 * rows * f * h)
+    counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
+
+    def loop():
+        for j, n in enumerate(counts):
+            torch.matmul(xp[offsets[j]:offsets[j] + n], w1[:, j], out=gu[offsets[j]:offsets[j] + n])
+    ms = timeit(loop, iters)
+    report(f"per-expert cuBLAS loop w1 rows={rows}", ms, flops=2.0 * rows * h * 2 * f, note="baseline")
+    ms = timeit(lambda: K.moe_combine(y, plan, p), iters)
+    report(f"moe_combine T={t} k={k} H={h}", ms, bytes_=(t + t * k) * h * 2.0)
+    G.check_status("cuda", "grouped gemm")
+
+
+CASES = {"moe": case_moe, "gemm": case_gemm, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
          "elementwise": case_elementwise, "adam": case_adam, "sampler": case_sampler,
          "fused_single": case_fused_single}
 

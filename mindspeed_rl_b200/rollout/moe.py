@@ -52,6 +52,15 @@ class MoEWeights:
             self.counts += torch.bincount(top_idx.reshape(-1).cpu(), minlength=cfg.num_experts)
         phys = self._physical(top_idx)
         n_phys = self.num_local * self.ep_size
+        if self.ep_size == 1:
+            # all experts here: plan + permute + grouped GEMMs + combine, no host round trip
+            from ..ops import moe as K
+            h, f = x.shape[1], self.w2.shape[1]
+            plan = K.moe_plan(phys, n_phys)
+            gu = K.grouped_gemm(K.moe_permute(x, plan), plan, self.w1.reshape(h, n_phys * 2 * f), True, 2 * f, 0, 2 * f)
+            y = K.grouped_gemm(ops.swiglu_fwd(gu), plan, self.w2.reshape(n_phys * f, h), True, 0, f, h)
+            out = K.moe_combine(y, plan, top_p)
+            return self._add_shared(out, x, comm)
         flat = phys.reshape(-1)
         order = torch.argsort(flat, stable=True)
         token_of = order // k
@@ -85,7 +94,9 @@ class MoEWeights:
         w = top_p.reshape(-1)[order].to(x.dtype)
         out = torch.zeros(t, x.shape[1], device=x.device, dtype=torch.float32)
         out.index_add_(0, token_of, (y * w.unsqueeze(-1)).float())
-        out = out.to(x.dtype)
+        return self._add_shared(out.to(x.dtype), x, comm)
+
+    def _add_shared(self, out: torch.Tensor, x: torch.Tensor, comm) -> torch.Tensor:
         if self.shared is not None:
             fc1, fc2 = self.shared
             sh = torch.matmul(ops.swiglu_fwd(torch.matmul(x, fc1.t())), fc2.t())
