@@ -41,6 +41,12 @@ def to_device(data: Any, dtype: torch.dtype, device) -> torch.Tensor:
     return host.pin_memory().to(device, non_blocking=True)
 
 
+def count_d2h(nbytes: int) -> None:
+    """Account for a device->host copy issued by the caller itself (an asynchronous pinned read)."""
+    global _d2h
+    _d2h += int(nbytes)
+
+
 def to_host(t: torch.Tensor) -> torch.Tensor:
     global _d2h
     if t.is_cuda:

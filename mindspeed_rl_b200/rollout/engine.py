@@ -26,7 +26,7 @@ import torch
 
 from .. import ops
 from ..models.transformer_config import TransformerConfig
-from ..obs.io_counter import to_device, to_host
+from ..obs.io_counter import count_d2h, to_device, to_host
 from ..parallel.tp_comm import NO_TP, TPComm
 from .block_manager import BlockManager
 from .model_runner import KVCache, ModelRunner, RolloutWeights
@@ -82,6 +82,7 @@ class LLMEngine:
         nkv_local = max(cfg.num_query_groups // self.comm.world_size, 1)
         self._group_max = ops.decode_group_max(cfg.num_attention_heads // self.comm.world_size, nkv_local)
         self.shared_prefix_decode = os.environ.get("MSRL_SHARED_PREFIX_DECODE", "1") == "1"
+        self.lookahead_decode = os.environ.get("MSRL_LOOKAHEAD_DECODE", "1") == "1"
         self.stats = dict(prefill_tokens=0, decode_tokens=0, steps=0, preemptions=0)
 
     # ---- cache lifecycle -----------------------------------------------------------------------
@@ -161,14 +162,15 @@ class LLMEngine:
         ft = to_device(np.asarray(floats, dtype=np.float32), torch.float32, dev) if floats else None
         return it, ft
 
-    def _sampling_rows(self, seqs: List[Sequence]):
-        """Host-side sampling parameters: (row_keys, float rows, flags)."""
+    def _sampling_rows(self, seqs: List[Sequence], pend: int = 0):
+        """Host-side sampling parameters: (row_keys, float rows, flags).  ``pend``: tokens sampled
+        but not yet appended on the host."""
         keys, temp = [], []
         need_filter = need_eos = False
         for s in seqs:
             p = s.params
             base = p.seed if p.seed is not None else (zlib.crc32(s.request_id.encode()) & 0x7FFFFFFF)
-            keys.append(((base * 1000003 + s.sample_index) * 1000003 + len(s.output_ids)) & (2 ** 62 - 1))
+            keys.append(((base * 1000003 + s.sample_index) * 1000003 + len(s.output_ids) + pend) & (2 ** 62 - 1))
             temp.append(p.temperature)
             need_filter |= p.top_k > 0 or p.top_p < 1.0 or p.min_p > 0.0
             need_eos |= p.eos_hazard is not None
@@ -177,12 +179,19 @@ class LLMEngine:
             floats += [[float(max(s.params.top_k, 0)) for s in seqs], [s.params.top_p for s in seqs],
                        [s.params.min_p for s in seqs]]
         if need_eos:
-            floats.append([length_hazard(len(s.output_ids) + 1, *s.params.eos_hazard)
+            floats.append([length_hazard(len(s.output_ids) + 1 + pend, *s.params.eos_hazard)
                            if s.params.eos_hazard is not None else -1.0 for s in seqs])
         return keys, floats, need_filter, need_eos
 
     def _sample(self, logits: torch.Tensor, seqs: List[Sequence], keys: torch.Tensor,
                 ft: torch.Tensor, need_filter: bool, need_eos: bool) -> Tuple[List[int], List[float]]:
+        tokens, logprobs = self._sample_device(logits, keys, ft, need_filter, need_eos)
+        # one device->host read per step: tokens and their log-probs together
+        both = to_host(torch.stack([tokens.double(), logprobs.double()]))
+        return both[0].long().tolist(), both[1].tolist()
+
+    def _sample_device(self, logits: torch.Tensor, keys: torch.Tensor, ft: torch.Tensor, need_filter: bool,
+                       need_eos: bool) -> Tuple[torch.Tensor, torch.Tensor]:
         temp = ft[0]
         top_k = top_p = min_p = eos_prob = None
         row = 1
@@ -195,11 +204,7 @@ class LLMEngine:
             parts = [torch.empty_like(logits) for _ in range(self.comm.world_size)]
             torch.distributed.all_gather(parts, logits.contiguous(), group=self.comm.group)
             logits = torch.cat(parts, dim=-1)
-        tokens, logprobs = ops.sample(logits, temp, top_k, top_p, min_p, keys, self.seed, eos_prob,
-                                      self.eos_token_id)
-        # one device->host read per step: tokens and their log-probs together
-        both = to_host(torch.stack([tokens.double(), logprobs.double()]))
-        return both[0].long().tolist(), both[1].tolist()
+        return ops.sample(logits, temp, top_k, top_p, min_p, keys, self.seed, eos_prob, self.eos_token_id)
 
     def _append_token(self, seq: Sequence, token: int, logprob: float) -> None:
         seq.output_ids.append(int(token))
@@ -268,14 +273,23 @@ class LLMEngine:
         for s, tok_, lp in zip(seqs, tokens, lps):
             self._append_token(s, tok_, lp)
 
-    def _run_decode(self, seqs: List[Sequence]) -> None:
+    def _launch_decode(self, seqs: List[Sequence], prev: Optional[dict] = None) -> dict:
+        """Launch one decode step and its sampling; nothing is read back.
+
+        ``prev``: the step still in flight whose sampled tokens (on the device) are this step's
+        input ids; host-side lengths then count that pending token."""
         dev = self.device
         b = len(seqs)
         t0 = time.perf_counter()
-        last = [s.output_ids[-1] if s.output_ids else s.prompt_ids[-1] for s in seqs]
-        lens = [s.total_len for s in seqs]
+        pend = 0 if prev is None else 1
+        lens = [s.total_len + pend for s in seqs]
         slots = [int(self.bm.slots(s.seq_id, n - 1, 1)[0]) for s, n in zip(seqs, lens)]
-        keys, floats, need_filter, need_eos = self._sampling_rows(seqs)
+        keys, floats, need_filter, need_eos = self._sampling_rows(seqs, pend)
+        if prev is None:
+            last = [s.output_ids[-1] if s.output_ids else s.prompt_ids[-1] for s in seqs]
+        else:
+            row_of = {id(s): i for i, s in enumerate(prev["seqs"])}
+            last = [row_of[id(s)] for s in seqs]          # rows of the pending step's token tensor
         rows = [last, [n - 1 for n in lens], slots, lens, keys]
         grouped = False
         if self.shared_prefix_decode and dev.type == "cuda":
@@ -292,23 +306,82 @@ class LLMEngine:
         groups = None
         if grouped:
             groups = (it_[5].to(torch.int32), it_[7:15].t().contiguous().to(torch.int32), it_[6].to(torch.int32))
+        ids = it_[0]
+        if prev is not None:
+            ids = prev["tokens"] if last == list(range(len(prev["seqs"]))) else prev["tokens"][it_[0]]
         t2 = time.perf_counter()
-        logits = self.runner.decode(it_[0], it_[1].to(torch.int32), it_[2], bt, it_[3].to(torch.int32),
-                                    max_ctx, groups)
+        logits = self.runner.decode(ids, it_[1].to(torch.int32), it_[2], bt, it_[3].to(torch.int32), max_ctx, groups)
         self.stats["decode_tokens"] += b
-        for s, n in zip(seqs, lens):
-            s.num_computed = n
-        t3 = time.perf_counter()
-        tokens, lps = self._sample(logits, seqs, it_[4], ft, need_filter, need_eos)
-        t4 = time.perf_counter()
-        for s, tok, lp in zip(seqs, tokens, lps):
-            self._append_token(s, tok, lp)
+        tokens, logprobs = self._sample_device(logits, it_[4], ft, need_filter, need_eos)
+        tokens = tokens.long()
+        both = torch.stack([tokens.double(), logprobs.double()])
+        event = None
+        if both.is_cuda:
+            host = torch.empty(both.shape, dtype=both.dtype, pin_memory=True)
+            host.copy_(both, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            count_d2h(both.numel() * both.element_size())
+        else:
+            host = both
         ht = self.host_time
         ht["decode_prep"] += t1 - t0
         ht["decode_h2d"] += t2 - t1
-        ht["decode_launch"] += t3 - t2
-        ht["decode_sample_sync"] += t4 - t3        # includes waiting for the GPU to finish the step
-        ht["decode_append"] += time.perf_counter() - t4
+        ht["decode_launch"] += time.perf_counter() - t2
+        return dict(seqs=seqs, lens=lens, tokens=tokens, host=host, event=event)
+
+    def _finish_decode(self, h: dict) -> None:
+        """Read a launched step's tokens and append them; sequences that finished while the step
+        was in flight (end of sequence found in the step before) drop their extra token."""
+        t0 = time.perf_counter()
+        if h["event"] is not None:
+            h["event"].synchronize()
+        tokens, lps = h["host"][0].long().tolist(), h["host"][1].tolist()
+        t1 = time.perf_counter()
+        for s, n, tok, lp in zip(h["seqs"], h["lens"], tokens, lps):
+            if s.finished:
+                continue
+            s.num_computed = n
+            self._append_token(s, tok, lp)
+        self.host_time["decode_sample_sync"] += t1 - t0      # includes waiting for the GPU to finish the step
+        self.host_time["decode_append"] += time.perf_counter() - t1
+
+    def _may_look_ahead(self, seqs: List[Sequence]) -> List[Sequence]:
+        """Sequences whose next decode step can be launched before this step's tokens are known:
+        nothing waits for a prefill, the batch is the whole running set, every sequence outlives
+        the pending token by length, and the block pool covers their next slots."""
+        sch = self.scheduler
+        if not self.lookahead_decode or sch.waiting or len(seqs) != len(sch.running):
+            return []
+        cont = [s for s in seqs
+                if len(s.output_ids) + 1 < s.params.max_tokens and s.total_len + 1 < self.max_model_len]
+        if len(cont) != len(seqs):
+            return []          # a sequence ends by length: let the scheduler regroup first
+        need = sum(self.bm.blocks_needed(s.seq_id, s.total_len + 1) for s in cont)
+        if need > self.bm.num_free_blocks:
+            return []
+        return cont
+
+    def _run_decode(self, seqs: List[Sequence]) -> None:
+        """One scheduled decode step, then further steps launched one ahead of the host: step i+1
+        takes its input ids from step i's token tensor on the device, so the host prepares and
+        launches it while step i still runs and reads step i's tokens afterwards.  A sequence that
+        turns out to have ended in step i has one surplus token computed; it is dropped."""
+        h = self._launch_decode(seqs)
+        while True:
+            cont = self._may_look_ahead(h["seqs"])
+            if not cont:
+                break
+            for s in cont:
+                self.bm.append(s.seq_id, 1)       # slot of the pending token
+            nxt = self._launch_decode(cont, h)
+            self._finish_decode(h)
+            self.stats["steps"] += 1
+            self._step_counter += 1
+            h = nxt
+            if any(s.finished for s in cont):
+                break                              # regroup without the finished sequences
+        self._finish_decode(h)
 
     def _to_output(self, group: RequestGroup) -> RequestOutput:
         reasons = {SeqStatus.FINISHED_STOPPED: "stop", SeqStatus.FINISHED_LENGTH: "length",
