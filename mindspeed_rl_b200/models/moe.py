@@ -179,46 +179,45 @@ class MoELayer(nn.Module):
 
     # ------------------------------------------------------------------------------------------
     def _experts_fwd(self, xp: torch.Tensor, counts: List[int], keep: bool):
-        w1, w2 = self._w1(), self._w2()
-        y = torch.empty(xp.shape[0], self.cfg.hidden_size, device=xp.device, dtype=xp.dtype)
-        gus, acts = [], []
-        s = 0
-        for j, n in enumerate(counts):
-            if n == 0:
-                gus.append(None)
-                acts.append(None)
-                continue
-            gu = torch.matmul(xp[s:s + n], w1[:, j])
-            act = ops.swiglu_fwd(gu)
-            torch.matmul(act, w2[j], out=y[s:s + n])
-            gus.append(gu if keep else None)
-            acts.append(act if keep else None)
-            s += n
-        return y, gus, acts
+        """Rows of ``xp`` are grouped by local expert (``counts`` rows each, known on the host after
+        the count exchange).  They are re-laid into 128-row padded segments and run through the
+        grouped GEMM kernels; the result comes back in the order of ``xp``."""
+        from ..ops import moe as K
 
-    def _experts_bwd(self, xp, counts, gus, acts, dy) -> torch.Tensor:
+        c = self.cfg
+        e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
+        w1, w2 = self._w1().reshape(h, e * 2 * f), self._w2().reshape(e * f, h)
+        ids = torch.repeat_interleave(torch.arange(e, device=xp.device),
+                                      torch.tensor(counts, device=xp.device), output_size=xp.shape[0])
+        plan = K.moe_plan(ids.view(-1, 1), e)
+        xpp = K.moe_permute(xp, plan)
+        gu = K.grouped_gemm(xpp, plan, w1, True, 2 * f, 0, 2 * f)
+        act = ops.swiglu_fwd(gu)
+        y = K.moe_combine(K.grouped_gemm(act, plan, w2, True, 0, f, h), plan)
+        return y, ((plan, xpp, gu, act) if keep else None)
+
+    def _experts_bwd(self, counts: List[int], ectx, dy: torch.Tensor) -> torch.Tensor:
+        from ..ops import moe as K
         from .gpt import grad_buffer
 
-        w1, w2 = self._w1(), self._w2()
         c = self.cfg
-        train = self.experts.weight1.requires_grad
-        g1 = grad_buffer(self.experts.weight1).view(c.hidden_size, self.num_local, 2 * c.moe_ffn_hidden_size) \
-            if train else None
-        g2 = grad_buffer(self.experts.weight2).view(self.num_local, c.moe_ffn_hidden_size, c.hidden_size) \
-            if train else None
-        dxp = torch.zeros_like(xp)
-        s = 0
-        for j, n in enumerate(counts):
-            if n == 0:
-                continue
-            d = dy[s:s + n]
-            dact = torch.matmul(d, w2[j].t())
-            dgu = ops.swiglu_bwd(gus[j], dact)
-            torch.matmul(dgu, w1[:, j].t(), out=dxp[s:s + n])
-            if train:
-                g2[j].add_(torch.matmul(acts[j].t(), d).to(g2.dtype))
-                g1[:, j].add_(torch.matmul(xp[s:s + n].t(), dgu).to(g1.dtype))
-            s += n
+        e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
+        w1, w2 = self._w1().reshape(h, e * 2 * f), self._w2().reshape(e * f, h)
+        plan, xpp, gu, act = ectx
+        dyp = K.moe_permute(dy, plan)
+        dact = K.grouped_gemm(dyp, plan, w2, False, 0, f, f)
+        dgu = ops.swiglu_bwd(gu, dact)
+        dxp = K.moe_combine(K.grouped_gemm(dgu, plan, w1, False, 2 * f, 0, h), plan)
+        if self.experts.weight1.requires_grad:
+            g1 = grad_buffer(self.experts.weight1).view(h, e, 2 * f)
+            g2 = grad_buffer(self.experts.weight2).view(e, f, h)
+            start = 0                                   # padded segment starts follow from the host counts
+            for j, n in enumerate(counts):
+                if n:
+                    r = slice(start, start + n)
+                    g2[j].add_(torch.matmul(act[r].t(), dyp[r]).to(g2.dtype))
+                    g1[:, j].add_(torch.matmul(xpp[r].t(), dgu[r]).to(g1.dtype))
+                start += (n + K.PAD - 1) // K.PAD * K.PAD
         return dxp
 
     # ------------------------------------------------------------------------------------------
@@ -237,7 +236,7 @@ class MoELayer(nn.Module):
         if self.ep_size == 1:
             return self._forward_local(x, xr, top_p, top_idx, aux, comm, keep)
         xp, plan = self._dispatch(x, top_idx)
-        y_local, gus, acts = self._experts_fwd(xp, plan["local_counts"], keep)
+        y_local, ectx = self._experts_fwd(xp, plan["local_counts"], keep)
         y_sorted = self._undispatch(y_local, plan)
         # combine: slot (token, k) weighted by its probability
         k = cfg.moe_router_topk
@@ -253,7 +252,7 @@ class MoELayer(nn.Module):
             shared_ctx = (gu, act) if keep else None
         if not keep:
             return out, None
-        ctx = dict(xr=xr, top_p=top_p, aux=aux, plan=plan, xp=xp, gus=gus, acts=acts, y_sorted=y_sorted,
+        ctx = dict(xr=xr, top_p=top_p, aux=aux, plan=plan, ectx=ectx, y_sorted=y_sorted,
                    w_sorted=w_sorted, shared=shared_ctx)
         return out, ctx
 
@@ -347,7 +346,7 @@ class MoELayer(nn.Module):
         dy_sorted = d_tok * ctx["w_sorted"].unsqueeze(-1)
         dw_sorted = (d_tok.float() * ctx["y_sorted"].float()).sum(-1)      # d loss / d prob per slot
         dy_local = self._redispatch(dy_sorted, plan)
-        dxp_local = self._experts_bwd(ctx["xp"], plan["local_counts"], ctx["gus"], ctx["acts"], dy_local)
+        dxp_local = self._experts_bwd(plan["local_counts"], ctx["ectx"], dy_local)
         dxp_sorted = self._undispatch(dxp_local, plan)
         dx = torch.zeros_like(x, dtype=torch.float32)
         dx.index_add_(0, plan["token_of"], dxp_sorted.float())
