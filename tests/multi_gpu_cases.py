@@ -272,7 +272,49 @@ def case_grpo_reshard(rank, world):
         assert len(hist) == 2, hist
 
 
-CASES = {"collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+def case_moe_ep(rank, world):
+    """Expert parallelism on GPUs (token exchange over NCCL, local experts on the plan + grouped tcgen05
+    GEMM kernels) against the same model with all experts on one rank."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.ops.gemm import check_status
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel, set_parallel_state
+    e, h, f = 8, 256, 128
+    kw = dict(num_layers=1, hidden_size=h, ffn_hidden_size=512, num_attention_heads=4, num_query_groups=2,
+              vocab_size=512, kv_channels=64, max_position_embeddings=1024, num_experts=e, moe_router_topk=2,
+              moe_ffn_hidden_size=f, norm_topk_prob=True, moe_aux_loss_coeff=0.0)
+    set_parallel_state(None)
+    full = GPTModel(TransformerConfig(**kw), device="cuda", seed=3)
+    initialize_model_parallel(expert_model_parallel_size=world)
+    model = GPTModel(TransformerConfig(expert_model_parallel_size=world, **kw), device="cuda", seed=3)
+    sd = full.state_dict()
+    per = e // world
+    for k in list(sd):
+        if k.endswith("experts.weight1"):
+            sd[k] = sd[k].view(h, e, 2 * f)[:, rank * per:(rank + 1) * per].reshape(h, -1).contiguous()
+        if k.endswith("experts.weight2"):
+            sd[k] = sd[k].view(e, f, h)[rank * per:(rank + 1) * per].reshape(-1, h).contiguous()
+    model.load_state_dict(sd)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    lens = [300, 212]
+    meta = PackedMeta.from_lengths(lens, "cuda")
+    t = sum(lens)
+    ids = torch.randint(0, 512, (t,), device="cuda", generator=g)
+    labels = torch.randint(0, 512, (t,), device="cuda", generator=g)
+    ref, _ = full.forward_logprob(ids, labels, meta)
+    ref.sum().backward()
+    lp, _ = model.forward_logprob(ids, labels, meta)
+    lp.sum().backward()
+    check_status(torch.device("cuda", torch.cuda.current_device()), "moe ep")
+    assert (lp - ref).abs().max().item() < 5e-2, (lp - ref).abs().max().item()
+    gw = model.decoder.layers[0].mlp.experts.weight2.grad.float().view(per, f, h)
+    fw = full.decoder.layers[0].mlp.experts.weight2.grad.float().view(e, f, h).clone()
+    dist.all_reduce(fw)
+    ref_g = fw[rank * per:(rank + 1) * per]
+    assert (gw - ref_g).abs().max().item() / (ref_g.abs().max().item() + 1e-6) < 5e-2
+
+
+CASES = {"moe_ep": case_moe_ep, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

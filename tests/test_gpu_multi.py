@@ -49,3 +49,8 @@ def test_grpo_train_tp2_rollout_tp1():
 def test_fused_tp_kernels():
     out = _run("fused_tp", 2)
     print([l for l in out.splitlines() if l.startswith("TIMING")])
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_moe_expert_parallel():
+    _run("moe_ep", 2)
