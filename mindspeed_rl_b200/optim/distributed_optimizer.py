@@ -74,8 +74,13 @@ class DistributedOptimizer:
                  eps: float = 1e-8, weight_decay: float = 0.01, clip_grad: float = 1.0,
                  dp_group=None, dp_rank: int = 0, model_parallel_group=None,
                  offload_to_host: bool = False, swap_chunks: int = 16,
-                 norm_duplicate_filter=None, tp_rank: int = 0):
+                 norm_duplicate_filter=None, tp_rank: int = 0, reuse_fp32_param: bool = False):
         self.buffers = buffers
+        # bf16 parameters double as the upper half of the fp32 master weights: only a 16-bit residual
+        # is kept per element (2 bytes instead of 4; reference flag ``reuse_fp32_param``,
+        # docs/zh/features/reuse_fp32_param.md in MindSpeed)
+        self.reuse_fp32_param = bool(reuse_fp32_param) and not offload_to_host and \
+            all(b.param_dtype == torch.bfloat16 for b in buffers)
         self.tp_rank = tp_rank
         self._rep_ranges = None
         self.param_groups = [dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)]
@@ -97,6 +102,10 @@ class DistributedOptimizer:
                 st = dict(master=master,
                           exp_avg=torch.zeros(e - s, dtype=torch.float32, pin_memory=pin),
                           exp_avg_sq=torch.zeros(e - s, dtype=torch.float32, pin_memory=pin))
+            elif self.reuse_fp32_param:
+                st = dict(master_lo=torch.zeros(e - s, dtype=torch.int16, device=shard.device),
+                          exp_avg=torch.zeros(e - s, dtype=torch.float32, device=shard.device),
+                          exp_avg_sq=torch.zeros(e - s, dtype=torch.float32, device=shard.device))
             else:
                 st = dict(master=shard.float().clone(), exp_avg=torch.zeros(e - s, dtype=torch.float32,
                                                                             device=shard.device),
@@ -165,6 +174,8 @@ class DistributedOptimizer:
             if self.offload_to_host and grad.is_cuda:
                 self._step_host(st, grad, p16 if p16 is not None else buf.param_data[s:e], g,
                                 p16 is None)
+            elif self.reuse_fp32_param:
+                self._step_reuse(st, grad, p16, g)
             else:
                 ops.adamw_step(st["master"], st["exp_avg"], st["exp_avg_sq"], grad, p16, g["lr"],
                                g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"],
@@ -173,6 +184,31 @@ class DistributedOptimizer:
                     buf.param_data[s:e].copy_(st["master"])
             buf.gather_params(self.dp_group)
         return True, self._norm.clone(), 0
+
+    # ---- fp32 master = (bf16 parameter, int16 residual) ------------------------------------------
+    @staticmethod
+    def compose_master(p16: torch.Tensor, lo: torch.Tensor) -> torch.Tensor:
+        """fp32 bits = (bf16 bits << 16) + residual (signed)."""
+        bits = (p16.view(torch.int16).to(torch.int32) << 16) + lo.to(torch.int32)
+        return bits.view(torch.float32)
+
+    @staticmethod
+    def split_master(master: torch.Tensor, p16_out: torch.Tensor, lo_out: torch.Tensor) -> None:
+        """bf16 = fp32 rounded half-up on the bit pattern, residual = fp32 bits - (bf16 bits << 16),
+        which always fits 16 signed bits, so ``compose_master`` is exact."""
+        bits = master.view(torch.int32)
+        hi = (bits + 0x8000) >> 16
+        p16_out.view(torch.int16).copy_(hi.to(torch.int16))
+        lo_out.copy_((bits - (hi << 16)).to(torch.int16))
+
+    def _step_reuse(self, st, grad, p16, g, chunk: int = 1 << 25) -> None:
+        n = grad.numel()
+        for s in range(0, n, chunk):
+            e = min(n, s + chunk)
+            master = self.compose_master(p16[s:e], st["master_lo"][s:e])
+            ops.adamw_step(master, st["exp_avg"][s:e], st["exp_avg_sq"][s:e], grad[s:e], None, g["lr"],
+                           g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"], self.step_count, self._coef)
+            self.split_master(master, p16[s:e], st["master_lo"][s:e])
 
     def _step_host(self, st, grad, p_out, g, fp32_params: bool) -> None:
         """Chunked H2D -> AdamW -> D2H with double buffering."""
@@ -228,18 +264,31 @@ class DistributedOptimizer:
         """Refresh the fp32 master weights from the (externally modified) model parameters."""
         for buf, st in zip(self.buffers, self.state):
             s, e = buf.shard_range(self.dp_rank)
-            st["master"].copy_(buf.param_data[s:e].float())
+            if "master_lo" in st:
+                st["master_lo"].zero_()
+            else:
+                st["master"].copy_(buf.param_data[s:e].float())
 
     # ---- checkpoint ---------------------------------------------------------------------------------
     def state_dict(self) -> dict:
-        return dict(step=self.step_count, param_groups=self.param_groups,
-                    shards=[{k: v.detach().cpu() for k, v in st.items()} for st in self.state])
+        shards = []
+        for buf, st in zip(self.buffers, self.state):
+            d = {k: v.detach().cpu() for k, v in st.items() if k != "master_lo"}
+            if "master_lo" in st:        # checkpoints always carry full fp32 master weights
+                s, e = buf.shard_range(self.dp_rank)
+                d["master"] = self.compose_master(buf.param_data[s:e], st["master_lo"]).cpu()
+            shards.append(d)
+        return dict(step=self.step_count, param_groups=self.param_groups, shards=shards)
 
     def load_state_dict(self, sd: dict) -> None:
         self.step_count = sd.get("step", 0)
-        for st, src in zip(self.state, sd["shards"]):
+        for buf, st, src in zip(self.buffers, self.state, sd["shards"]):
             for k in st:
-                st[k].copy_(src[k])
+                if k == "master_lo":
+                    s, e = buf.shard_range(self.dp_rank)
+                    self.split_master(src["master"].to(st[k].device), buf.param_data[s:e], st[k])
+                else:
+                    st[k].copy_(src[k])
 
     # ---- memory choreography (offload between phases) --------------------------------------------
     def offload_state(self) -> None:

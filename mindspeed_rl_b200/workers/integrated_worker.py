@@ -138,7 +138,8 @@ class IntegratedWorker(BaseWorker):
             self.model.buffers, lr=ac.lr or 1e-6, betas=(ac.adam_beta1, ac.adam_beta2),
             weight_decay=ac.weight_decay, clip_grad=ac.clip_grad, dp_group=ps.group("dp_cp"),
             dp_rank=ps.rank_in("dp_cp"), model_parallel_group=ps.group("mp"),
-            offload_to_host=bool(ac.swap_optimizer), tp_rank=ps.rank_in("tp"))
+            offload_to_host=bool(ac.swap_optimizer), tp_rank=ps.rank_in("tp"),
+            reuse_fp32_param=bool(getattr(ac, "reuse_fp32_param", False)))
         iters = ac.train_iters or 1
         n_updates = iters * max(1, (ac.global_batch_size * rl.n_samples_per_prompt) // max(rl.mini_batch_size, 1))
         samples = n_updates * rl.mini_batch_size

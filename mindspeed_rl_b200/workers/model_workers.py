@@ -71,7 +71,8 @@ class _ModelWorker(BaseWorker):
                 self.model.buffers, lr=mc.lr or 1e-6, betas=(mc.adam_beta1, mc.adam_beta2),
                 weight_decay=mc.weight_decay, clip_grad=mc.clip_grad, dp_group=ps.group("dp_cp"),
                 dp_rank=ps.rank_in("dp_cp"), model_parallel_group=ps.group("mp"),
-                offload_to_host=bool(mc.swap_optimizer), tp_rank=ps.rank_in("tp"))
+                offload_to_host=bool(mc.swap_optimizer), tp_rank=ps.rank_in("tp"),
+            reuse_fp32_param=bool(getattr(mc, "reuse_fp32_param", False)))
             self.scheduler = OptimizerParamScheduler(self.optimizer, mc.lr or 1e-6, mc.min_lr or 0.0, 0,
                                                      max(mc.train_iters or 1, 1), mc.lr_decay_style or "constant")
             self.engine = TrainingEngine(self.model, self.optimizer, self.scheduler, role=self.role,

@@ -219,3 +219,37 @@ def test_eplb_invariants():
     for layer in m["layer_list"]:
         hosted = [e for d in layer["device_list"] for e in d["device_expert"]]
         assert set(hosted) == set(range(16)) and all(len(set(d["device_expert"])) == 3 for d in layer["device_list"])
+
+
+def test_reuse_fp32_param_split_is_exact_and_tracks_fp32_master():
+    """bf16 parameter + int16 residual reproduce every fp32 bit pattern; an optimizer that keeps
+    only the residual follows the one with fp32 master weights."""
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    torch.manual_seed(0)
+    x = torch.randn(100000) * torch.logspace(-6, 3, 100000)
+    x[:4] = torch.tensor([0.0, -0.0, 1.00390625, -3.0])          # includes an exact tie (1 + 2^-8)
+    p16 = torch.empty(100000, dtype=torch.bfloat16)
+    lo = torch.empty(100000, dtype=torch.int16)
+    DistributedOptimizer.split_master(x, p16, lo)
+    assert torch.equal(DistributedOptimizer.compose_master(p16, lo), x)
+    assert (p16.float() - x).abs().max() <= (x.abs() * 2 ** -8).max()
+
+    def make(reuse):
+        torch.manual_seed(1)
+        lin = torch.nn.Linear(64, 64, bias=False).bfloat16()
+        m = DistributedDataParallel(lin)
+        return m, DistributedOptimizer(m.buffers, lr=1e-2, weight_decay=0.1, clip_grad=0.0, reuse_fp32_param=reuse)
+
+    (ma, oa), (mb, ob) = make(False), make(True)
+    assert ob.reuse_fp32_param and "master_lo" in ob.state[0]
+    for step in range(5):
+        g = torch.Generator().manual_seed(step)
+        for m in (ma, mb):
+            m.buffers[0].grad_data.copy_(torch.randn(m.buffers[0].grad_data.shape, generator=g.manual_seed(step)))
+        oa.step()
+        ob.step()
+    wa, wb = ma.buffers[0].param_data.float(), mb.buffers[0].param_data.float()
+    assert (wa - wb).abs().max() <= 2 ** -7 * wa.abs().max()      # at most one bf16 ulp apart (tie rounding)
+    full = ob.state_dict()["shards"][0]["master"]
+    torch.testing.assert_close(full, oa.state[0]["master"], rtol=1e-6, atol=1e-7)
