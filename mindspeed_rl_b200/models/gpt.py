@@ -291,8 +291,14 @@ class _LayerFn(torch.autograd.Function):
         full_recompute = layer.cfg.recompute_granularity == "full" and getattr(layer, "recompute_full", True)
         out, saved = layer_forward(layer, h, meta, keep=not full_recompute)
         ctx.layer, ctx.meta, ctx.full = layer, meta, full_recompute
+        ctx.swapped = False
         if full_recompute:
             ctx.save_for_backward(h)
+        elif getattr(layer.cfg, "swap_attention", False):
+            # kept activations wait for their backward in pinned host memory
+            from .activation_swap import swapper_for
+            ctx.saved = swapper_for(h.device).offload(saved)
+            ctx.swapped = True
         else:
             ctx.saved = saved
         return out
@@ -307,6 +313,9 @@ class _LayerFn(torch.autograd.Function):
         else:
             saved = ctx.saved
             ctx.saved = None
+            if ctx.swapped:
+                from .activation_swap import swapper_for
+                saved = swapper_for(dh2.device).restore(saved)
         with torch.no_grad():
             dh = layer_backward(layer, saved, meta, dh2.contiguous())
         return dh, None, None

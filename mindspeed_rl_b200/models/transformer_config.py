@@ -44,6 +44,7 @@ class TransformerConfig:
     recompute_method: Optional[str] = None          # "block": only the first recompute_num_layers layers
     recompute_num_layers: Optional[int] = None
     recompute_activation_function: bool = False     # rebuild silu(g)*u in the backward instead of storing it
+    swap_attention: bool = False                    # kept activations wait for the backward in pinned host memory
     # parallel sizes seen by the model code
     tensor_model_parallel_size: int = 1
     sequence_parallel: bool = False
@@ -108,6 +109,7 @@ class TransformerConfig:
             recompute_granularity=cfg.recompute_granularity, recompute_method=cfg.recompute_method,
             recompute_num_layers=cfg.recompute_num_layers,
             recompute_activation_function=bool(cfg.recompute_activation_function),
+            swap_attention=bool(getattr(cfg, "swap_attention", False)),
             tensor_model_parallel_size=cfg.tensor_model_parallel_size,
             sequence_parallel=bool(cfg.sequence_parallel) and cfg.tensor_model_parallel_size > 1,
             expert_model_parallel_size=cfg.expert_model_parallel_size,

@@ -320,3 +320,53 @@ def test_sampler_distribution_and_greedy():
                         torch.arange(n, device=DEV, dtype=torch.int64), 7,
                         eos_prob=torch.full((n,), 0.25, device=DEV), eos_id=1999)
     assert abs(float((tok == 1999).float().mean()) - 0.25) < 0.03
+
+
+def test_swap_attention_and_reuse_fp32_param_on_gpu():
+    """Activation offload through pinned memory and a side stream leaves the gradients unchanged;
+    the residual-only optimizer follows the fp32-master one on the device kernels."""
+    from mindspeed_rl_b200.models import activation_swap
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    kw = dict(num_layers=4, hidden_size=256, ffn_hidden_size=512, num_attention_heads=4, num_query_groups=2,
+              vocab_size=512, kv_channels=64, max_position_embeddings=2048, recompute_granularity="full",
+              recompute_method="block", recompute_num_layers=1)
+    lens = [700, 523]
+    meta = PackedMeta.from_lengths(lens, DEV)
+    t = sum(lens)
+    g = torch.Generator(device=DEV).manual_seed(2)
+    ids = torch.randint(0, 512, (t,), device=DEV, generator=g)
+    labels = torch.randint(0, 512, (t,), device=DEV, generator=g)
+    grads = []
+    for swap in (False, True):
+        m = DistributedDataParallel(GPTModel(TransformerConfig(swap_attention=swap, **kw), device=DEV, seed=4))
+        sw = activation_swap.swapper_for(DEV)
+        sw.min_bytes, sw.bytes_out, sw.bytes_in = 64 << 10, 0, 0
+        lp, _ = m.module.forward_logprob(ids, labels, meta)
+        lp.sum().backward()
+        torch.cuda.synchronize()
+        grads.append([b.grad_data.float().clone() for b in m.buffers])
+        assert (sw.bytes_out > 0) == swap and sw.bytes_in == sw.bytes_out
+    for a, b in zip(*grads):
+        # weight-gradient reductions use atomics, so two runs differ in the last bits; a lost or
+        # early-reused activation would be off by far more
+        assert (a - b).abs().max().item() <= 1e-2 * a.abs().max().item(), (a - b).abs().max().item()
+    # optimizer: bf16 parameter + int16 residual against fp32 master weights
+    outs = []
+    for reuse in (False, True):
+        m = DistributedDataParallel(GPTModel(TransformerConfig(**kw), device=DEV, seed=4))
+        opt = DistributedOptimizer(m.buffers, lr=1e-3, weight_decay=0.1, clip_grad=1.0, reuse_fp32_param=reuse)
+        for step in range(3):
+            for b, gsrc in zip(m.buffers, grads[0]):
+                b.grad_data.copy_(gsrc * (1 + step))
+            opt.step()
+        outs.append([b.param_data.float().clone() for b in m.buffers])
+        full = opt.state_dict()["shards"][0]["master"]
+        if reuse:
+            torch.testing.assert_close(full, ref_master, rtol=1e-5, atol=1e-7)
+        else:
+            ref_master = full
+    for a, b in zip(*outs):
+        assert (a - b).abs().max() <= 2 ** -7 * a.abs().max()

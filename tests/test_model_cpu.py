@@ -72,3 +72,32 @@ def test_lora_matches_merged_weights():
     with torch.no_grad():
         want, _ = base.forward_logprob(ids, labels, meta, 1.0, False)
     assert torch.allclose(off, want, atol=1e-6) and not torch.allclose(off, lp.detach(), atol=1e-4)
+
+
+def test_swap_attention_gives_identical_gradients():
+    """Activation offload between forward and backward changes nothing numerically; with block
+    recompute it only touches the layers that keep their intermediates."""
+    from mindspeed_rl_b200.models import activation_swap
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    kw = dict(num_layers=3, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
+              vocab_size=96, params_dtype=torch.float32, max_position_embeddings=128,
+              recompute_granularity="full", recompute_method="block", recompute_num_layers=1)
+    lens = [40, 23]
+    meta = PackedMeta.from_lengths(lens, "cpu")
+    t = sum(lens)
+    ids, labels = torch.randint(0, 96, (t,)), torch.randint(0, 96, (t,))
+    grads = []
+    for swap in (False, True):
+        m = GPTModel(TransformerConfig(swap_attention=swap, **kw), device="cpu", seed=4)
+        sw = activation_swap.swapper_for("cpu")
+        sw.min_bytes, sw.bytes_out, sw.bytes_in = 1024, 0, 0
+        lp, _ = m.forward_logprob(ids, labels, meta)
+        lp.sum().backward()
+        grads.append({n: p.grad.clone() for n, p in m.named_parameters()})
+        if swap:
+            assert sw.bytes_out > 0 and sw.bytes_in == sw.bytes_out and sw.last is None
+        else:
+            assert sw.bytes_out == 0
+    for n in grads[0]:
+        assert torch.equal(grads[0][n], grads[1][n]), n
