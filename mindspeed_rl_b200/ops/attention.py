@@ -155,3 +155,98 @@ def attn_varlen_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, ls
         o, _ = _ref_attention(q, k, v, cu_seqlens, cu_seqlens, causal)
         (gx,) = torch.autograd.grad(o.reshape(t, nh * hd), x, dout.float())
     return gx.to(qkv.dtype)
+
+
+def attn_kv_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q: torch.Tensor, cu_k: torch.Tensor,
+                max_q: int, causal: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Attention of contiguous ``q [Tq, nh, hd]`` over separate ``k, v [Tk, nkv, hd]`` (packed
+    sequences, ``cu_q`` / ``cu_k``); returns ``(out [Tq, nh*hd], lse [nh, Tq])``.  The block of the
+    ring algorithm of context parallelism."""
+    tq, nh, hd = q.shape
+    tk, nkv, _ = k.shape
+    batch = cu_q.numel() - 1
+    if _lib.use_kernels(q, k, v):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out = torch.empty(tq, nh * hd, device=q.device, dtype=q.dtype)
+        lse = torch.empty(nh, tq, device=q.device, dtype=torch.float32)
+        lay = (ctypes.c_longlong * 12)(nh * hd, 0, nh, hd, nkv * hd, 0, nkv, hd, nkv * hd, 0, nkv, hd)
+        if hd == 128 and use_tcgen05_attention():
+            from .gemm import _status_word
+            rc = _lib.load().msrl_flash_attn_varlen_fwd_tcgen05(
+                ptr(q), ptr(k), ptr(v), lay, ptr(out), c_ll(nh * hd), ptr(lse), ptr(cu_q), ptr(cu_k), c_int(batch),
+                c_int(int(max_q)), c_int(nh), c_int(nkv), c_ll(tq), c_ll(tk), c_int(hd), c_int(1 if causal else 0),
+                ptr(_status_word(q.device)), stream())
+            if rc != _NOT_SUPPORTED:
+                check(rc, "flash_attn_varlen_fwd_tcgen05")
+                return out, lse
+        check(_lib.load().msrl_flash_attn_varlen_fwd(
+            ptr(q), ptr(k), ptr(v), lay, ptr(out), c_ll(nh * hd), ptr(lse), ptr(cu_q), ptr(cu_k), c_int(batch),
+            c_int(int(max_q)), c_int(nh), c_int(nkv), c_ll(tq), c_int(hd), c_int(1 if causal else 0), stream()),
+            "flash_attn_varlen_fwd")
+        return out, lse
+    o, lse = _ref_attention(q, k, v, cu_q, cu_k, causal)
+    return o.reshape(tq, nh * hd).to(q.dtype), lse
+
+
+def attn_kv_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                lse: torch.Tensor, cu_q: torch.Tensor, cu_k: torch.Tensor, max_q: int, max_k: int, causal: bool
+                ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of one (q block, kv block) pair given the output and log-sum-exp of the WHOLE
+    attention row (``out``, ``lse``: what the forward produced after merging all blocks), which is
+    what makes the per-block gradients add up.  Contiguous ``q [Tq, nh, hd]``, ``k, v [Tk, nkv, hd]``;
+    returns ``(dq, dk, dv)`` of the same shapes."""
+    tq, nh, hd = q.shape
+    tk, nkv, _ = k.shape
+    batch = cu_q.numel() - 1
+    if _lib.use_kernels(q, k, v, dout):
+        q, k, v, do = q.contiguous(), k.contiguous(), v.contiguous(), dout.contiguous()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = _workspace("attn_delta", nh * tq, q.device)
+        # contiguous [T, heads, hd]: head h starts at column h * hd
+        lay = (ctypes.c_longlong * 12)(nh * hd, 0, nh, hd, nkv * hd, 0, nkv, hd, nkv * hd, 0, nkv, hd)
+        if hd == 128 and use_tcgen05_attention():
+            from .gemm import _status_word
+            rc = _lib.load().msrl_flash_attn_varlen_bwd_tcgen05(
+                ptr(q), ptr(k), ptr(v), lay, ptr(out), ptr(do), c_ll(nh * hd), ptr(lse), ptr(delta), ptr(dq),
+                ptr(dk), ptr(dv), ptr(cu_q), ptr(cu_k), c_int(batch), c_int(int(max_q)), c_int(int(max_k)),
+                c_int(nh), c_int(nkv), c_ll(tq), c_ll(tk), c_int(hd), c_int(1 if causal else 0),
+                ptr(_status_word(q.device)), stream())
+            if rc != _NOT_SUPPORTED:
+                check(rc, "flash_attn_varlen_bwd_tcgen05")
+                return dq, dk, dv
+        check(_lib.load().msrl_flash_attn_varlen_bwd(
+            ptr(q), ptr(k), ptr(v), lay, ptr(out), ptr(do), c_ll(nh * hd), ptr(lse), ptr(delta), ptr(dq), ptr(dk),
+            ptr(dv), ptr(cu_q), ptr(cu_k), c_int(batch), c_int(int(max_q)), c_int(int(max_k)), c_int(nh),
+            c_int(nkv), c_ll(tq), c_int(hd), c_int(1 if causal else 0), stream()), "flash_attn_varlen_bwd")
+        return dq, dk, dv
+    # reference: P from the given lse, then the usual formulas (fp32)
+    rep = nh // nkv
+    scale = 1.0 / math.sqrt(hd)
+    dq, dk, dv = torch.zeros_like(q, dtype=torch.float32), torch.zeros_like(k, dtype=torch.float32), \
+        torch.zeros_like(v, dtype=torch.float32)
+    of, dof = out.float().view(tq, nh, hd), dout.float().view(tq, nh, hd)
+    delta = (of * dof).sum(-1)                                              # [Tq, nh]
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    for b in range(batch):
+        qs, qe, ks, ke = cq[b], cq[b + 1], ck[b], ck[b + 1]
+        if qe == qs or ke == ks:
+            continue
+        qi = q[qs:qe].float().transpose(0, 1)                                # [nh, Lq, hd]
+        ki = k[ks:ke].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        vi = v[ks:ke].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        s = torch.matmul(qi, ki.transpose(1, 2)) * scale
+        if causal:
+            lq, lk = qe - qs, ke - ks
+            i = torch.arange(lq).unsqueeze(1)
+            j = torch.arange(lk).unsqueeze(0)
+            s = s.masked_fill(j > i + (lk - lq), float("-inf"))
+        p = torch.exp(s - lse[:, qs:qe].unsqueeze(-1))
+        doi = dof[qs:qe].transpose(0, 1)
+        dvi = torch.matmul(p.transpose(1, 2), doi)
+        dp = torch.matmul(doi, vi.transpose(1, 2))
+        ds = p * (dp - delta[qs:qe].t().unsqueeze(-1)) * scale
+        dq[qs:qe] = torch.matmul(ds, ki).transpose(0, 1)
+        dki = torch.matmul(ds.transpose(1, 2), qi)
+        dk[ks:ke] = dki.view(nkv, rep, ke - ks, hd).sum(1).transpose(0, 1)
+        dv[ks:ke] = dvi.view(nkv, rep, ke - ks, hd).sum(1).transpose(0, 1)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)

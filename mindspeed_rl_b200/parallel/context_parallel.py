@@ -13,12 +13,24 @@ brings the result back.  This is the Ulysses exchange; it is also used for the z
 whenever the (TP-local) KV heads divide by ``cp``, because on one NVSwitch domain an all-to-all of
 activations costs the same bytes as the ring's KV rotation without serialising ``cp`` steps.
 
+The ring algorithm proper (``megatron_cp_algo`` when the head counts do not divide by ``cp``, or
+``MSRL_CP_RING=1``) keeps all heads local and rotates K/V around the CP group instead: step 0 is
+causal attention on the local zig-zag pair of chunks; at step s the K/V of rank ``j = r - s``
+arrive (the transfer of step s+1 is posted before the math of step s) and, because of the zig-zag
+order, the block is never masked: all local queries against the first chunk of ``j`` when
+``j < r``, the queries of the second local chunk against both chunks of ``j`` otherwise.  Block
+results are merged with their log-sum-exp.  The backward runs the same rotation, recomputes each
+block's probabilities from the merged log-sum-exp, adds dQ locally and returns every block's
+dK/dV to the rank that owns those keys (reference: ring attention of
+``docs/zh/features/context_parallel.md:52-86``).
+
 Per-token outputs (log-probs, values) are all-gathered and put back in global order; in the
 backward every rank keeps the gradient of its own tokens, scaled by ``cp`` because the
 data-parallel averaging that follows divides by ``dp * cp``.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, List, Optional, Tuple
 
 import torch
@@ -87,6 +99,119 @@ class ContextParallel:
         self.max_local = int(lens.max()) if lens.numel() else 0
         self.max_full = int((cu_padded[1:] - cu_padded[:-1]).max()) if lens.numel() else 0
         self.cu_full_dev = self.cu_full.to(self.device)
+        self._ring_ready = False
+
+    # ---- ring attention --------------------------------------------------------------------------------
+    def use_ring(self, lay: QKVLayout) -> bool:
+        if self.algo != RING:
+            return False
+        return bool(lay.num_kv_heads % self.size or lay.num_heads % self.size) or \
+            os.environ.get("MSRL_CP_RING", "0") == "1"
+
+    def _ring_setup(self) -> None:
+        if self._ring_ready:
+            return
+        cu = self.cu_local.cpu().to(torch.int64)
+        lens = cu[1:] - cu[:-1]
+        half = lens // 2
+        first = [torch.arange(int(s), int(s + h)) for s, h in zip(cu[:-1], half)]
+        second = [torch.arange(int(s + h), int(e)) for s, h, e in zip(cu[:-1], half, cu[1:])]
+        empty = torch.empty(0, dtype=torch.int64)
+        self.first_idx = (torch.cat(first) if first else empty).to(self.device)
+        self.second_idx = (torch.cat(second) if second else empty).to(self.device)
+        cu_half = torch.zeros(lens.numel() + 1, dtype=torch.int32)
+        cu_half[1:] = torch.cumsum(half, 0)
+        self.cu_half = cu_half.to(self.device)
+        self.max_half = int(half.max()) if half.numel() else 0
+        self._ring_ready = True
+
+    def _post(self, sends, recvs):
+        """``sends`` / ``recvs``: lists of ``(tensor, cp rank)``; returns the requests."""
+        ranks = dist.get_process_group_ranks(self.group)
+        ops_ = [dist.P2POp(dist.isend, t, ranks[r % self.size], self.group) for t, r in sends] + \
+               [dist.P2POp(dist.irecv, t, ranks[r % self.size], self.group) for t, r in recvs]
+        return dist.batch_isend_irecv(ops_) if ops_ else []
+
+    @staticmethod
+    def _wait(reqs) -> None:
+        for q_ in reqs:
+            q_.wait()
+
+    def _ring_fwd(self, q, k, v):
+        self._ring_setup()
+        n, r = self.size, self.rank
+        tl, nh, hd = q.shape
+        cur = torch.stack([k, v]).contiguous()
+        nxt = torch.empty_like(cur) if n > 1 else None
+        reqs = self._post([(cur, r + 1)], [(nxt, r - 1)]) if n > 1 else []     # K/V for step 1 travel during step 0
+        o, lse = ops.attn_kv_fwd(q, k, v, self.cu_local, self.cu_local, self.max_local, True)
+        acc_o, acc_l = o.float().view(tl, nh, hd), lse.clone()                 # [Tl, nh, hd], [nh, Tl]
+        for s in range(1, n):
+            self._wait(reqs)
+            cur = nxt                                      # K/V of rank j
+            j = (r - s) % n
+            if s + 1 < n:
+                nxt = torch.empty_like(cur)
+                reqs = self._post([(cur, r + 1)], [(nxt, r - 1)])
+            if j < r:
+                kj, vj = cur[0][self.first_idx], cur[1][self.first_idx]
+                o, l = ops.attn_kv_fwd(q, kj, vj, self.cu_local, self.cu_half, self.max_local, False)
+                lt = torch.logaddexp(acc_l, l)
+                acc_o = acc_o * torch.exp(acc_l - lt).t().unsqueeze(-1) + \
+                    o.float().view(tl, nh, hd) * torch.exp(l - lt).t().unsqueeze(-1)
+                acc_l = lt
+            else:
+                idx = self.second_idx
+                o, l = ops.attn_kv_fwd(q[idx], cur[0], cur[1], self.cu_half, self.cu_local, self.max_half, False)
+                al = acc_l[:, idx]
+                lt = torch.logaddexp(al, l)
+                acc_o[idx] = acc_o[idx] * torch.exp(al - lt).t().unsqueeze(-1) + \
+                    o.float().view(-1, nh, hd) * torch.exp(l - lt).t().unsqueeze(-1)
+                acc_l[:, idx] = lt
+        return acc_o.reshape(tl, nh * hd).to(q.dtype), acc_l
+
+    def _ring_bwd(self, dout, q, k, v, out, lse):
+        n, r = self.size, self.rank
+        tl, nh, hd = q.shape
+        dq = torch.zeros(tl, nh, hd, dtype=torch.float32, device=q.device)
+        dkv = torch.zeros(2, *k.shape, dtype=torch.float32, device=q.device)
+        cur = torch.stack([k, v]).contiguous()
+        nxt = torch.empty_like(cur) if n > 1 else None
+        reqs = self._post([(cur, r + 1)], [(nxt, r - 1)]) if n > 1 else []
+        g = ops.attn_kv_bwd(dout, q, k, v, out, lse, self.cu_local, self.cu_local, self.max_local, self.max_local, True)
+        dq += g[0].float()
+        dkv[0] += g[1].float()
+        dkv[1] += g[2].float()
+        home = []                                          # (requests, receive buffer) of dK/dV blocks on their way
+        for s in range(1, n):
+            self._wait(reqs)
+            cur = nxt
+            j = (r - s) % n
+            if s + 1 < n:
+                nxt = torch.empty_like(cur)
+                reqs = self._post([(cur, r + 1)], [(nxt, r - 1)])
+            part = torch.zeros(2, *k.shape, dtype=k.dtype, device=q.device)
+            if j < r:
+                idx = self.first_idx
+                g = ops.attn_kv_bwd(dout, q, cur[0][idx], cur[1][idx], out, lse, self.cu_local, self.cu_half,
+                                    self.max_local, self.max_half, False)
+                dq += g[0].float()
+                part[0][idx] = g[1]
+                part[1][idx] = g[2]
+            else:
+                idx = self.second_idx
+                g = ops.attn_kv_bwd(dout[idx], q[idx], cur[0], cur[1], out[idx], lse[:, idx].contiguous(), self.cu_half,
+                                    self.cu_local, self.max_half, self.max_local, False)
+                dq[idx] += g[0].float()
+                part[0] = g[1]
+                part[1] = g[2]
+            # this block's dK/dV goes to the rank that owns the keys; mine comes from rank r + s
+            back = torch.empty_like(part)
+            home.append((self._post([(part, r - s)], [(back, r + s)]), back, part))
+        for rq, back, _ in home:
+            self._wait(rq)
+            dkv += back.float()
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype)
 
     # ---- token plumbing -----------------------------------------------------------------------------
     def take_local(self, t: torch.Tensor) -> torch.Tensor:
@@ -122,6 +247,10 @@ class ContextParallel:
         return QKVLayout(lay.num_heads // self.size, lay.num_kv_heads // self.size, lay.head_dim, interleaved=False)
 
     def attention_fwd(self, qkv: torch.Tensor, lay: QKVLayout, meta) -> Tuple[torch.Tensor, Any]:
+        if self.use_ring(lay):
+            q, k, v = (t.contiguous() for t in lay.split(qkv))
+            out, lse = self._ring_fwd(q, k, v)
+            return out, ("ring", q, k, v, lse)
         hl = self._head_layout(lay)
         q, k, v = lay.split(qkv)
         # GQA: query heads of a KV group must land on the rank that gets that KV head
@@ -134,6 +263,10 @@ class ContextParallel:
 
     def attention_bwd(self, dattn: torch.Tensor, qkv: torch.Tensor, attn: torch.Tensor, saved: Any, lay: QKVLayout,
                       meta) -> torch.Tensor:
+        if saved[0] == "ring":
+            _, q, k, v, lse = saved
+            dq, dk, dv = self._ring_bwd(dattn.contiguous(), q, k, v, attn, lse)
+            return lay.merge(dq, dk, dv)
         packed, out, lse, hl = saved
         tl = qkv.shape[0]
         d_out = self._a2a(dattn.reshape(tl, lay.num_heads, lay.head_dim).contiguous(), True)

@@ -314,7 +314,46 @@ def case_moe_ep(rank, world):
     assert (gw - ref_g).abs().max().item() / (ref_g.abs().max().item() + 1e-6) < 5e-2
 
 
-CASES = {"moe_ep": case_moe_ep, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+def case_cp_ring(rank, world):
+    """Ring attention over the context-parallel group (K/V rotation over NCCL p2p, tcgen05 block
+    kernels with separate q / kv) against the same model on one GPU."""
+    os.environ["MSRL_CP_RING"] = "1"
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.ops.gemm import check_status
+    from mindspeed_rl_b200.parallel.context_parallel import ContextParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    ps = initialize_model_parallel(context_parallel_size=world)
+    cfg = TransformerConfig(num_layers=2, hidden_size=512, ffn_hidden_size=1024, num_attention_heads=4,
+                            num_query_groups=2, vocab_size=1024, kv_channels=128, add_qkv_bias=True,
+                            max_position_embeddings=4096)
+    full = GPTModel(cfg, device="cuda", seed=5)
+    model = GPTModel(cfg, device="cuda", seed=5)
+    meta = PackedMeta.from_lengths([600, 1300, 404], "cuda", align=2 * world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator(device="cuda").manual_seed(1)
+    ids = torch.randint(0, 1024, (t,), device="cuda", generator=g)
+    labels = torch.randint(0, 1024, (t,), device="cuda", generator=g)
+    w = torch.randn(t, device="cuda", generator=g)
+    ref_lp, _ = full.forward_logprob(ids, labels, meta, 1.0, False)
+    (ref_lp * w).sum().backward()
+    cp = ContextParallel(ps.group("cp"), world, rank, "megatron_cp_algo", meta.cu_seqlens.to(torch.int64).cpu(), "cuda")
+    assert cp.use_ring(model.decoder.layers[0].self_attention.layout)
+    m_local = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(meta.positions), cp=cp)
+    lp_l, _ = model.forward_logprob(cp.take_local(ids), cp.take_local(labels), m_local, 1.0, False)
+    lp = cp.gather_tokens(lp_l)
+    assert (lp - ref_lp).abs().max().item() < 5e-2, (lp - ref_lp).abs().max().item()
+    (lp * w).sum().backward()
+    check_status(torch.device("cuda", torch.cuda.current_device()), "cp ring")
+    for (n, p), q in zip(model.named_parameters(), full.parameters()):
+        gr = p.grad.float().clone()
+        dist.all_reduce(gr)
+        ref = q.grad.float()
+        assert (gr / world - ref).abs().max().item() <= 5e-2 * ref.abs().max().item() + 1e-3, \
+            (n, (gr / world - ref).abs().max().item(), ref.abs().max().item())
+
+
+CASES = {"cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

@@ -349,8 +349,10 @@ def test_pipeline_1f1b_matches_single_process():
     run_distributed(_pp_worker, 4, 2)        # fewer micro-batches than stages
 
 
-def _cp_worker(rank, world, algo):
-    """Context parallel (zig-zag or contiguous split, head-parallel attention) == single process."""
+def _cp_worker(rank, world, algo, ring=False):
+    """Context parallel (zig-zag or contiguous split, head-parallel or ring attention) == single process."""
+    import os
+    os.environ["MSRL_CP_RING"] = "1" if ring else "0"
     from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
     from mindspeed_rl_b200.models.transformer_config import TransformerConfig
     from mindspeed_rl_b200.parallel.context_parallel import ContextParallel
@@ -369,6 +371,7 @@ def _cp_worker(rank, world, algo):
     (ref_lp * w).sum().backward()
     cp = ContextParallel(ps.group("cp"), world, rank, algo, meta.cu_seqlens.to(torch.int64), "cpu")
     assert cp.local_index.numel() == t // world
+    assert cp.use_ring(model.decoder.layers[0].self_attention.layout) == (ring or world == 3)
     m_local = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(meta.positions), cp=cp)
     lp_l, _ = model.forward_logprob(cp.take_local(ids), cp.take_local(labels), m_local, 1.0, False)
     lp = cp.gather_tokens(lp_l)
@@ -383,6 +386,11 @@ def _cp_worker(rank, world, algo):
 def test_context_parallel_matches_single_process():
     run_distributed(_cp_worker, 2, "megatron_cp_algo")
     run_distributed(_cp_worker, 2, "ulysses_cp_algo")
+
+
+def test_ring_attention_matches_single_process():
+    run_distributed(_cp_worker, 2, "megatron_cp_algo", True)
+    run_distributed(_cp_worker, 3, "megatron_cp_algo")       # 4 / 2 heads do not divide by 3: ring
 
 
 def _lora_tp_worker(rank, world, sp):
