@@ -235,6 +235,9 @@ class MoELayer(nn.Module):
         self.token_counts = torch.bincount(top_idx.reshape(-1), minlength=cfg.num_experts)
         if self.ep_size == 1:
             return self._forward_local(x, xr, top_p, top_idx, aux, comm, keep)
+        disp = self._p2p_dispatcher(x)
+        if disp is not None:
+            return self._forward_p2p(disp, x, xr, top_p, top_idx, aux, comm, keep)
         xp, plan = self._dispatch(x, top_idx)
         y_local, ectx = self._experts_fwd(xp, plan["local_counts"], keep)
         y_sorted = self._undispatch(y_local, plan)
@@ -283,6 +286,68 @@ class MoELayer(nn.Module):
             return out, None
         return out, dict(local=True, xr=xr, top_p=top_p, aux=aux, plan=plan, xp=xp, gu=gu, act=act, y=y,
                          shared=shared_ctx)
+
+    # ---- expert parallel over peer-mapped memory: tokens are written into the destination ranks' slabs ----
+    def _p2p_dispatcher(self, x: torch.Tensor):
+        rows = int(getattr(self.cfg, "moe_p2p_dispatch_rows", 0) or 0)
+        if rows <= 0 or not x.is_cuda:
+            return None
+        from ..parallel.moe_dispatch import dispatcher_for
+        from ..parallel.symm import get_arena
+        return dispatcher_for(get_arena(), self.ep_group, self.num_local, self.cfg.hidden_size, rows, x.dtype)
+
+    def _forward_p2p(self, disp, x, xr, top_p, top_idx, aux, comm, keep):
+        from ..ops import moe as K
+
+        c = self.cfg
+        e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
+        w1, w2 = self._w1().reshape(h, e * 2 * f), self._w2().reshape(e * f, h)
+        route = disp.dispatch(x, top_idx)
+        gu = K.grouped_gemm(disp.slab, route.plan, w1, True, 2 * f, 0, 2 * f)
+        act = ops.swiglu_fwd(gu)
+        K.grouped_gemm(act, route.plan, w2, True, 0, f, h, out=disp.out_slab)
+        xp = disp.slab.clone() if keep else None                  # the slab is reused by the next layer
+        out, rows = disp.combine(route, top_p.detach(), keep_rows=keep)
+        shared_ctx = None
+        if self.shared_experts is not None:
+            sh, shared_ctx = self._shared_fwd(x, comm, keep)
+            out = out + sh
+        if not keep:
+            return out, None
+        return out, dict(p2p=disp, xr=xr, top_p=top_p, top_idx=top_idx, aux=aux, route=route, xp=xp, gu=gu, act=act,
+                         rows=rows, shared=shared_ctx)
+
+    def _backward_p2p(self, ctx, x, dout, comm) -> torch.Tensor:
+        from ..ops import moe as K
+        from .gpt import grad_buffer
+
+        c = self.cfg
+        disp = ctx["p2p"]
+        e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
+        w1, w2 = self._w1().reshape(h, e * 2 * f), self._w2().reshape(e * f, h)
+        top_p, top_idx = ctx["top_p"], ctx["top_idx"]
+        t, k = top_idx.shape
+        ident = K.MoePlan(None, None, torch.arange(t * k, dtype=torch.int32, device=x.device), None, t * k, t, k, 0)
+        dprob = K.moe_slot_dot(dout, ctx["rows"], ident)                      # [T, k] fp32
+        route = disp.dispatch(dout, top_idx, scale=top_p.detach())            # rows arrive scaled by their weight
+        plan = route.plan
+        dy = disp.slab
+        dact = K.grouped_gemm(dy, plan, w2, False, 0, f, f)
+        dgu = ops.swiglu_bwd(ctx["gu"], dact)
+        if self.experts.weight1.requires_grad:
+            g1 = grad_buffer(self.experts.weight1).view(h, e, 2 * f)
+            g2 = grad_buffer(self.experts.weight2).view(e, f, h)
+            counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
+            xp, act = ctx["xp"], ctx["act"]
+            for j, n in enumerate(counts):
+                if n == 0:
+                    continue
+                r = slice(offsets[j], offsets[j] + n)
+                g2[j].add_(torch.matmul(act[r].t(), dy[r]).to(g2.dtype))
+                g1[:, j].add_(torch.matmul(xp[r].t(), dgu[r]).to(g1.dtype))
+        K.grouped_gemm(dgu, plan, w1, False, 2 * f, 0, h, out=disp.out_slab)
+        dx, _ = disp.combine(route, None)
+        return self._router_and_shared_bwd(ctx, x, dout, comm, dx.float(), dprob)
 
     def _backward_local(self, ctx, x, dout, comm) -> torch.Tensor:
         from ..ops import moe as K
@@ -341,6 +406,8 @@ class MoELayer(nn.Module):
 
         if ctx.get("local"):
             return self._backward_local(ctx, x, dout, comm)
+        if ctx.get("p2p") is not None:
+            return self._backward_p2p(ctx, x, dout, comm)
         plan = ctx["plan"]
         d_tok = dout[plan["token_of"]]                                    # [T*k, H] in sorted-slot order
         dy_sorted = d_tok * ctx["w_sorted"].unsqueeze(-1)

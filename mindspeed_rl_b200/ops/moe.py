@@ -127,7 +127,7 @@ def _sm_count(device) -> int:
 
 
 def grouped_gemm(a: torch.Tensor, plan: MoePlan, b2d: torch.Tensor, b_mn_major: bool, ex: int, ey: int,
-                 n: int) -> torch.Tensor:
+                 n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``c[r] = a[r] @ B_e`` for the rows of expert e.  ``b2d`` is a 2-D contiguous view of all
     experts' weights; expert e's operand starts at ``b2d[e*ey, e*ex]`` and is ``[K, n]`` when
     ``b_mn_major`` else ``[n, K]`` (used transposed).  Rows of ``c`` outside used tiles are
@@ -136,7 +136,8 @@ def grouped_gemm(a: torch.Tensor, plan: MoePlan, b2d: torch.Tensor, b_mn_major: 
     if _lib.use_kernels(a, b2d):
         from .gemm import _status_word
         assert a.is_contiguous() and b2d.is_contiguous() and rows == plan.max_rows
-        c = torch.empty(rows, n, dtype=a.dtype, device=a.device)
+        c = torch.empty(rows, n, dtype=a.dtype, device=a.device) if out is None else out
+        assert c.shape == (rows, n) and c.is_contiguous()
         rc = _lib.load().msrl_moe_grouped_gemm(
             ptr(a), c_ll(k), ptr(b2d), c_ll(b2d.shape[0]), c_ll(b2d.shape[1]), c_ll(b2d.shape[1]),
             c_int(1 if b_mn_major else 0), c_int(ex), c_int(ey), ptr(c), c_ll(n), ptr(plan.tile_expert),
@@ -144,7 +145,7 @@ def grouped_gemm(a: torch.Tensor, plan: MoePlan, b2d: torch.Tensor, b_mn_major: 
         if rc != _NOT_SUPPORTED:
             check(rc, "moe_grouped_gemm")
             return c
-    c = torch.zeros(rows, n, dtype=a.dtype, device=a.device)
+    c = torch.zeros(rows, n, dtype=a.dtype, device=a.device) if out is None else out.zero_()
     counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
     for e, cnt in enumerate(counts):
         if cnt == 0:

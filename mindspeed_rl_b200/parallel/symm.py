@@ -163,6 +163,9 @@ class SymmetricArena:
         code = int(self.status.item())
         if code != 0:
             self.status.zero_()
+            if code >= 300:
+                raise RuntimeError(f"rank {self.rank}: the expert slab of EP member {code - 300} would overflow "
+                                   f"(raise moe_p2p_dispatch_rows)")
             raise SymmetricTimeout(f"rank {self.rank}: barrier timed out waiting for peer {code - 100}")
 
     # ---- collectives -------------------------------------------------------------------------------------

@@ -272,7 +272,13 @@ def case_grpo_reshard(rank, world):
         assert len(hist) == 2, hist
 
 
-def case_moe_ep(rank, world):
+def case_moe_ep_p2p(rank, world):
+    """Expert parallelism with tokens written straight into the destination ranks' expert slabs
+    (peer-mapped memory) and outputs pulled back by the source ranks."""
+    case_moe_ep(rank, world, p2p_rows=4096)
+
+
+def case_moe_ep(rank, world, p2p_rows=0):
     """Expert parallelism on GPUs (token exchange over NCCL, local experts on the plan + grouped tcgen05
     GEMM kernels) against the same model with all experts on one rank."""
     from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
@@ -286,7 +292,12 @@ def case_moe_ep(rank, world):
     set_parallel_state(None)
     full = GPTModel(TransformerConfig(**kw), device="cuda", seed=3)
     initialize_model_parallel(expert_model_parallel_size=world)
-    model = GPTModel(TransformerConfig(expert_model_parallel_size=world, **kw), device="cuda", seed=3)
+    arena = None
+    if p2p_rows:
+        from mindspeed_rl_b200.parallel.symm import init_arena
+        arena = init_arena(64 << 20)
+    model = GPTModel(TransformerConfig(expert_model_parallel_size=world, moe_p2p_dispatch_rows=p2p_rows, **kw),
+                     device="cuda", seed=3)
     sd = full.state_dict()
     per = e // world
     for k in list(sd):
@@ -306,6 +317,11 @@ def case_moe_ep(rank, world):
     lp, _ = model.forward_logprob(ids, labels, meta)
     lp.sum().backward()
     check_status(torch.device("cuda", torch.cuda.current_device()), "moe ep")
+    if p2p_rows:
+        from mindspeed_rl_b200.parallel import moe_dispatch
+        arena.check()
+        used = [d for d in moe_dispatch._dispatchers.values() if d is not None]
+        assert used and used[0].calls >= 2, "the peer-memory dispatcher was not used"
     assert (lp - ref).abs().max().item() < 5e-2, (lp - ref).abs().max().item()
     gw = model.decoder.layers[0].mlp.experts.weight2.grad.float().view(per, f, h)
     fw = full.decoder.layers[0].mlp.experts.weight2.grad.float().view(e, f, h).clone()
@@ -353,7 +369,7 @@ def case_cp_ring(rank, world):
             (n, (gr / world - ref).abs().max().item(), ref.abs().max().item())
 
 
-CASES = {"cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+CASES = {"cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

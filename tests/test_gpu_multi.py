@@ -54,6 +54,7 @@ def test_fused_tp_kernels():
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_moe_expert_parallel():
     _run("moe_ep", 2)
+    _run("moe_ep_p2p", 2)
 
 
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
