@@ -10,6 +10,14 @@ The experts' forward/backward is written by hand (like the dense layer); only th
 graph ``[T, E]`` goes through autograd so that the load-balancing auxiliary loss and the
 probability gradients need no hand derivation.
 
+Three execution paths share the expert math (dispatch plan, permute / combine and the grouped
+tcgen05 GEMM of ``ops/moe.py``, which read the stacked expert weights in place):
+all experts on this rank (no host round trip in the forward); expert parallel with
+``all_to_all_single`` over the EP group (counts on the host, any backend, also gloo);
+expert parallel over peer-mapped memory (``parallel/moe_dispatch.py``: tokens are written straight
+into the destination ranks' expert slabs and outputs are pulled back, chosen when
+``moe_p2p_dispatch_rows`` > 0 and a symmetric arena exists).
+
 Reference behaviour: flags ``moe_grouped_gemm``, ``moe_token_dispatcher_type: alltoall_seq``,
 ``moe_router_topk``, ``norm_topk_prob``, ``moe_aux_loss_coeff`` (``configs/model/qwen3_30b_a3b.yaml``)
 and the rollout-side routing in ``models/rollout/vllm_adapter/fused_moe.py:230-503``.

@@ -45,18 +45,19 @@ class RayDAPOTrainer(RayBaseTrainer):
     def transfer_dock_init(self) -> None:
         cols = self.dataset_additional_keys + ["metric_for_dapo", "response_mask", "tool_call_num"]
         cons = ["dynamic_sampling", "dapo_metrics"]
+        # each store is shared right after it is built (the descriptor of the newest one travels)
         main = sampling = None
         if self.is_driver:
-            main = GRPOTransferDock(self.max_num_prompt_in_batch * (2 if self.enable_partial_rollout else 1),
-                                    self.n_samples_per_prompt, self.metrics,
-                                    max_age=self.partial_rollout_max_split,
-                                    GBS_train=self.max_num_prompt_in_batch, addition_columns=cols,
-                                    addition_consumers=cons)
-            if self.should_filter:
-                sampling = GRPOTransferDock(self.global_batch_size, self.n_samples_per_prompt,
-                                            self.sampling_metrics, addition_columns=cols,
-                                            addition_consumers=cons)
+            main = self._new_dock(self.max_num_prompt_in_batch * (2 if self.enable_partial_rollout else 1),
+                                  self.n_samples_per_prompt, self.metrics,
+                                  max_age=self.partial_rollout_max_split,
+                                  GBS_train=self.max_num_prompt_in_batch, addition_columns=cols,
+                                  addition_consumers=cons)
         self.transfer_dock = self._share_dock(main)
+        if self.should_filter and self.is_driver:
+            sampling = self._new_dock(self.global_batch_size, self.n_samples_per_prompt,
+                                      self.sampling_metrics, addition_columns=cols,
+                                      addition_consumers=cons)
         self.sampling_transfer_dock = self._share_dock(sampling) if self.should_filter else None
         self.actor_worker.sync_init_transfer_dock(self.transfer_dock, None, self.sampling_transfer_dock)
         for r in self.reward_list:

@@ -30,7 +30,7 @@ class RayPPOTrainer(RayBaseTrainer):
     def transfer_dock_init(self) -> None:
         dock = None
         if self.is_driver:
-            dock = GRPOTransferDock(
+            dock = self._new_dock(
                 self.global_batch_size, self.n_samples_per_prompt, self.metrics,
                 addition_columns=self.dataset_additional_keys + ["values"],
                 addition_consumers=["compute_kl", "critic_train", "critic_compute_values", "ppo_metrics"])
