@@ -83,7 +83,7 @@ class LLMEngine:
         self._group_max = ops.decode_group_max(cfg.num_attention_heads // self.comm.world_size, nkv_local)
         self.shared_prefix_decode = os.environ.get("MSRL_SHARED_PREFIX_DECODE", "1") == "1"
         self.lookahead_decode = os.environ.get("MSRL_LOOKAHEAD_DECODE", "1") == "1"
-        self.stats = dict(prefill_tokens=0, decode_tokens=0, steps=0, preemptions=0)
+        self.stats = dict(prefill_tokens=0, decode_tokens=0, steps=0, preemptions=0, lookahead_steps=0)
 
     # ---- cache lifecycle -----------------------------------------------------------------------
     def kv_bytes_per_block(self) -> int:
@@ -103,8 +103,9 @@ class LLMEngine:
 
     def free_cache(self) -> None:
         if os.environ.get("MSRL_ENGINE_PROFILE", "0") == "1" and self.host_time:
-            print("[engine] steps=%d host seconds: %s" % (
-                self.stats["steps"], {k: round(v, 3) for k, v in sorted(self.host_time.items())}), flush=True)
+            print("[engine] steps=%d (launched ahead: %d) host seconds: %s" % (
+                self.stats["steps"], self.stats.get("lookahead_steps", 0),
+                {k: round(v, 3) for k, v in sorted(self.host_time.items())}), flush=True)
             self.host_time.clear()
         self.runner.bind_cache(None)
         self.bm = None
@@ -377,6 +378,7 @@ class LLMEngine:
             nxt = self._launch_decode(cont, h)
             self._finish_decode(h)
             self.stats["steps"] += 1
+            self.stats["lookahead_steps"] += 1
             self._step_counter += 1
             h = nxt
             if any(s.finished for s in cont):
