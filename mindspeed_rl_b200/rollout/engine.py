@@ -64,8 +64,13 @@ class LLMEngine:
                  max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 16,
                  enable_prefix_caching: bool = False, enforce_eager: bool = True,
                  graph_batch_sizes: Seq_[int] = (), eos_token_id: int = -1, pad_token_id: int = 0,
-                 comm: Optional[TPComm] = None, seed: int = 0):
+                 comm: Optional[TPComm] = None, seed: int = 0, lockstep_group=None):
+        """``lockstep_group``: process group whose members must run the same number of model
+        forwards (the expert-parallel group of an MoE model: every forward contains all-to-all
+        exchanges with the other members).  Such engines step together: a member without work
+        joins the others' exchanges with zero tokens until all of them are done."""
         self.cfg = cfg
+        self.lockstep_group = lockstep_group
         self.device = torch.device(device)
         self.comm = comm or NO_TP
         self.max_num_seqs, self.max_num_batched_tokens = max_num_seqs, max_num_batched_tokens
@@ -82,7 +87,7 @@ class LLMEngine:
         nkv_local = max(cfg.num_query_groups // self.comm.world_size, 1)
         self._group_max = ops.decode_group_max(cfg.num_attention_heads // self.comm.world_size, nkv_local)
         self.shared_prefix_decode = os.environ.get("MSRL_SHARED_PREFIX_DECODE", "1") == "1"
-        self.lookahead_decode = os.environ.get("MSRL_LOOKAHEAD_DECODE", "1") == "1"
+        self.lookahead_decode = os.environ.get("MSRL_LOOKAHEAD_DECODE", "1") == "1" and lockstep_group is None
         self.stats = dict(prefill_tokens=0, decode_tokens=0, steps=0, preemptions=0, lookahead_steps=0)
 
     # ---- cache lifecycle -----------------------------------------------------------------------
@@ -132,6 +137,16 @@ class LLMEngine:
     def has_unfinished_requests(self) -> bool:
         return self.scheduler is not None and self.scheduler.has_unfinished()
 
+    def any_unfinished_requests(self) -> bool:
+        """Collective over the lock-step group (every member must call it once per step): true
+        while any member still has requests."""
+        mine = self.has_unfinished_requests()
+        if self.lockstep_group is None:
+            return mine
+        flag = torch.tensor([1 if mine else 0], dtype=torch.int32, device=self.device)
+        torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX, group=self.lockstep_group)
+        return bool(flag.item())
+
     def get_num_unfinished_requests(self) -> int:
         return len(self.scheduler.groups)
 
@@ -148,6 +163,9 @@ class LLMEngine:
         elif sched.decode:
             self._run_decode(sched.decode)
             self.host_time["decode_step"] += time.perf_counter() - t1
+        elif self.lockstep_group is not None:
+            self.runner.idle_forward()            # keep the other members' exchanges paired
+            self.stats["idle_steps"] = self.stats.get("idle_steps", 0) + 1
         self._step_counter += 1
         t2 = time.perf_counter()
         out = [self._to_output(g) for g in self.scheduler.pop_finished_groups()]
@@ -403,7 +421,7 @@ class LLMEngine:
                                  params[i] if per_prompt else params)
                 for i, p in enumerate(prompts)]
         done: Dict[str, RequestOutput] = {}
-        while self.has_unfinished_requests():
+        while self.any_unfinished_requests():
             for out in self.step():
                 done[out.request_id] = out
         for g in self.scheduler.pop_finished_groups():

@@ -142,6 +142,16 @@ class ModelRunner:
             delta = self.comm.all_reduce(torch.matmul(y, lw.down_w.t()))
         return resid, delta
 
+    @torch.no_grad()
+    def idle_forward(self) -> None:
+        """The collective part of a forward for a rank that has no tokens this step: every expert
+        layer joins its group's token exchange with zero tokens (and serves the other ranks' tokens
+        that are routed to its experts)."""
+        empty = torch.zeros(0, self.cfg.hidden_size, dtype=self.cfg.params_dtype, device=self.device)
+        for lw in self.weights.layers:
+            if lw.moe is not None:
+                lw.moe.forward(empty, self.comm)
+
     def _forward(self, ids, positions, attend) -> torch.Tensor:
         """Returns the final hidden states ``[T, H]`` (after the last norm)."""
         w = self.weights

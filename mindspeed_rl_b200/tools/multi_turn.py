@@ -124,7 +124,7 @@ class MultiTurnRollout:
             s = MultiTurnSample(list(p), list(p))
             samples[rid] = s
             self.engine.add_request(rid, s.context, self._params(sampling_params, 0, len(s.context)))
-        while self.engine.has_unfinished_requests():
+        while self.engine.any_unfinished_requests():
             for out in self.engine.step():
                 if not out.finished:
                     continue

@@ -191,7 +191,9 @@ class IntegratedWorker(BaseWorker):
             max_model_len=gc.max_model_len, block_size=gc.kv_block_size,
             enable_prefix_caching=gc.enable_prefix_caching, enforce_eager=gc.enforce_eager,
             graph_batch_sizes=tuple(gc.graph_batch_sizes), eos_token_id=self.eos_token_id,
-            pad_token_id=self.pad_token_id, comm=self.comm if tp > 1 else None, seed=self.seed)
+            pad_token_id=self.pad_token_id, comm=self.comm if tp > 1 else None, seed=self.seed,
+            # expert-parallel replicas exchange tokens in every forward: their engines step together
+            lockstep_group=ps.group("ep") if (tcfg.is_moe and ps.size("ep") > 1) else None)
         resharder = None
         if gc.infer_tensor_parallel_size != tp or ps.size("pp") > 1:
             from ..reshard.planner import Resharder
@@ -324,7 +326,8 @@ class IntegratedWorker(BaseWorker):
             partials.append((p, r))
             params.append(dataclasses.replace(base, n=1, max_tokens=max(int(budget), 1)))
             rids.append(f"pr_{idx[i]}_{int(age[i])}_{self.iteration}")
-        outs = self.engine.generate(ctxs, params, request_ids=rids) if ctxs else []
+        outs = self.engine.generate(ctxs, params, request_ids=rids) \
+            if (ctxs or self.engine.lockstep_group is not None) else []
         vocab = self.tcfg.vocab_size
         t = lambda v, dt=torch.int64: torch.tensor(v, dtype=dt)
         responses, input_ids, lengths, completed = [], [], [], []

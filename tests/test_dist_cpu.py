@@ -180,6 +180,54 @@ def test_expert_parallel_matches_single_rank():
     run_distributed(_ep_worker, 2)
 
 
+def _ep_rollout_worker(rank, world):
+    """Expert-parallel rollout engines step together: a rank with fewer (or no) requests keeps
+    joining the token exchanges, and every rank's greedy tokens equal the single-rank model's."""
+    from mindspeed_rl_b200.models.gpt import GPTModel
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel, set_parallel_state
+    from mindspeed_rl_b200.reshard.alias import alias_rollout_weights
+    from mindspeed_rl_b200.rollout.engine import LLMEngine
+    from mindspeed_rl_b200.rollout.scheduler import SamplingParams
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, params_dtype=torch.float32, max_position_embeddings=64, num_experts=4,
+              moe_router_topk=2, moe_ffn_hidden_size=16, norm_topk_prob=True, moe_aux_loss_coeff=0.0)
+    set_parallel_state(None)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=3)
+    for p in full.parameters():
+        p.data.mul_(3.0)
+    ps = initialize_model_parallel(expert_model_parallel_size=world)
+    model = GPTModel(TransformerConfig(expert_model_parallel_size=world, **kw), device="cpu", seed=3)
+    sd = full.state_dict()
+    per = 4 // world
+    for k in list(sd):
+        if k.endswith("experts.weight1"):
+            sd[k] = sd[k].view(32, 4, 32)[:, rank * per:(rank + 1) * per].reshape(32, -1).contiguous()
+        if k.endswith("experts.weight2"):
+            sd[k] = sd[k].view(4, 16, 32)[rank * per:(rank + 1) * per].reshape(-1, 32).contiguous()
+    model.load_state_dict(sd)
+
+    def engine(m, group):
+        e = LLMEngine(m.cfg, "cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=32, block_size=4,
+                      lockstep_group=group)
+        e.runner.bind_weights(alias_rollout_weights(m))
+        e.init_cache(32)
+        return e
+    prompts = [[3, 9, 27, 5], [1, 2, 3, 4, 5, 6], [11, 12]] if rank == 0 else []      # rank 1 has nothing to do
+    params = SamplingParams(n=1, temperature=0.0, max_tokens=6)
+    ep = engine(model, ps.group("ep"))
+    got = [o.outputs[0].token_ids for o in ep.generate(prompts, params)]
+    set_parallel_state(None)
+    ref = [o.outputs[0].token_ids for o in engine(full, None).generate(prompts, params)]
+    assert got == ref, (got, ref)
+    if rank == 1:
+        assert ep.stats.get("idle_steps", 0) > 0
+
+
+def test_expert_parallel_rollout_steps_together():
+    run_distributed(_ep_rollout_worker, 2)
+
+
 def _dock_worker(rank, world):
     from mindspeed_rl_b200.data.transfer_dock import GRPOTransferDock
     from mindspeed_rl_b200.runtime import rpc
