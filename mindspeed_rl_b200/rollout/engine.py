@@ -28,6 +28,7 @@ from .. import ops
 from ..models.transformer_config import TransformerConfig
 from ..obs.io_counter import count_d2h, to_device, to_host
 from ..parallel.tp_comm import NO_TP, TPComm
+from .base_engine import BaseInferEngine
 from .block_manager import BlockManager
 from .model_runner import KVCache, ModelRunner, RolloutWeights
 from .scheduler import (PrefillItem, RequestGroup, SamplingParams, Scheduler, SchedulerOutput, SeqStatus,
@@ -59,7 +60,7 @@ def length_hazard(step: int, lo: int, hi: int) -> float:
     return 1.0 / (hi - step + 1)
 
 
-class LLMEngine:
+class LLMEngine(BaseInferEngine):
     def __init__(self, cfg: TransformerConfig, device, *, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 16,
                  enable_prefix_caching: bool = False, enforce_eager: bool = True,
@@ -69,6 +70,8 @@ class LLMEngine:
         forwards (the expert-parallel group of an MoE model: every forward contains all-to-all
         exchanges with the other members).  Such engines step together: a member without work
         joins the others' exchanges with zero tokens until all of them are done."""
+        BaseInferEngine.__init__(self, max_num_seqs=max_num_seqs, max_model_len=max_model_len,
+                                 infer_tensor_parallel_size=(comm.world_size if comm is not None else 1))
         self.cfg = cfg
         self.lockstep_group = lockstep_group
         self.device = torch.device(device)
@@ -115,6 +118,23 @@ class LLMEngine:
         self.runner.bind_cache(None)
         self.bm = None
         self.scheduler = None
+
+    # ---- the worker-facing contract (BaseInferEngine) ---------------------------------------------
+    def init_cache_engine(self, num_blocks: Optional[int] = None) -> None:
+        self.init_cache(num_blocks if num_blocks is not None else getattr(self, "default_num_blocks", 0))
+
+    def free_cache_engine(self) -> None:
+        self.free_cache()
+
+    def offload_model_weights(self) -> None:
+        self.runner.bind_weights(None)
+
+    def sync_model_weights(self, params, load_format: str = "megatron") -> None:
+        """``params``: a ``RolloutWeights`` view of the training tensors (aliased or resharded)."""
+        self.runner.bind_weights(params)
+
+    def generate_sequences(self, idx_list, sampling_params=None, **kwargs):
+        return self.generate(idx_list, sampling_params or SamplingParams(**kwargs))
 
     # ---- request API ---------------------------------------------------------------------------
     def add_request(self, request_id: Optional[str], prompt_token_ids: Seq_[int],
