@@ -51,7 +51,7 @@ MOE = dict(
     num_experts=None, moe_router_topk=2, moe_ffn_hidden_size=None, n_shared_experts=None,
     moe_grouped_gemm=False, moe_permutation_async_comm=False, moe_tp_extend_ep=False,
     moe_alltoall_overlap_comm=False, use_fused_moe_token_permute_and_unpermute=False,
-    moe_token_dispatcher_type=None, seq_aux=False, first_k_dense_replace=None,
+    moe_token_dispatcher_type=None, moe_p2p_capacity_factor=0.0, seq_aux=False, first_k_dense_replace=None,
     moe_layer_freq=None, moe_router_load_balancing_type="aux_loss",
     moe_router_num_groups=None, moe_router_group_topk=None,
     moe_router_topk_scaling_factor=None, norm_topk_prob=False,

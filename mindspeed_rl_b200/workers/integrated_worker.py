@@ -72,7 +72,30 @@ class IntegratedWorker(BaseWorker):
         if m_local:
             tp = self.parallel_state.size("tp")
             extra = 2 * m_local * self.tcfg.hidden_size * 2 * (1 + tp) + (1 << 20)
+        extra += self._moe_p2p_bytes()
         init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20) + extra, device=self.device)
+
+    def _moe_p2p_bytes(self) -> int:
+        """Expert-parallel MoE models can move tokens between ranks through peer-mapped slabs
+        (``moe_token_dispatcher_type: p2p`` or ``moe_p2p_capacity_factor`` > 0): size the slabs for
+        ``factor`` times the average load of a rank (its own tokens x top-k) and reserve the arena
+        bytes.  Sets ``tcfg.moe_p2p_dispatch_rows``; 0 keeps the all-to-all collectives."""
+        ac, rl, c = self.actor_config, self.rl_config, self.tcfg
+        ep = self.parallel_state.size("ep")
+        factor = float(getattr(ac, "moe_p2p_capacity_factor", 0.0) or 0.0)
+        if getattr(ac, "moe_token_dispatcher_type", None) == "p2p" and factor <= 0:
+            factor = 2.0
+        if not c.is_moe or ep <= 1 or factor <= 0:
+            return 0
+        from ..parallel.moe_dispatch import P2PDispatcher
+        mbs = max(ac.micro_batch_size or 1, rl.actor_forward_micro_batch_size or 1,
+                  rl.ref_forward_micro_batch_size or 1)
+        tokens = max(rl.update_max_packing_token_size or 0, rl.actor_max_packing_token_size or 0,
+                     rl.ref_max_packing_token_size or 0, mbs * (ac.seq_length or 0), 1)
+        e_local = c.num_experts // ep
+        rows = (int(factor * tokens * c.moe_router_topk) + e_local * 128 + 127) // 128 * 128
+        c.moe_p2p_dispatch_rows = rows
+        return P2PDispatcher.bytes_needed(ep, e_local, c.hidden_size, rows) + (1 << 20)
 
     def _fused_tp_rows(self) -> int:
         """Largest token shard (rows per TP rank, multiple of 128) a packed micro-batch can have,
