@@ -369,7 +369,65 @@ def case_cp_ring(rank, world):
             (n, (gr / world - ref).abs().max().item(), ref.abs().max().item())
 
 
-CASES = {"cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+def case_moe_dispatch_timing(rank, world):
+    """Device time (max over ranks) of one MoE token round trip between expert-parallel ranks:
+    peer-memory dispatch + combine against count exchange + two all-to-all collectives."""
+    from mindspeed_rl_b200.ops import moe as K
+    from mindspeed_rl_b200.parallel.moe_dispatch import P2PDispatcher
+    from mindspeed_rl_b200.parallel.symm import init_arena
+    t, k, h, e_local = 8192, 8, 2048, 16
+    e = e_local * world
+    rows = 2 * t * k + e_local * 128
+    arena = init_arena(P2PDispatcher.bytes_needed(world, e_local, h, rows) + (8 << 20))
+    disp = P2PDispatcher(arena, list(range(world)), e_local, h, rows)
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    x = torch.randn(t, h, device="cuda", generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(e, device="cuda", generator=g)[:k] for _ in range(256)]).repeat(t // 256, 1)
+    w = torch.rand(t, k, device="cuda", generator=g)
+
+    def p2p():
+        route = disp.dispatch(x, idx)
+        disp.out_slab.copy_(disp.slab)                      # stand-in for the expert MLP
+        return disp.combine(route, w)[0]
+
+    def a2a():
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        xp = x[order // k]
+        send = torch.bincount(flat, minlength=e).view(world, e_local)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        send_rows, recv_rows = send.sum(1).tolist(), recv.sum(1).tolist()
+        got = torch.empty(sum(recv_rows), h, device="cuda", dtype=x.dtype)
+        dist.all_to_all_single(got, xp, recv_rows, send_rows)
+        back = torch.empty_like(xp)
+        dist.all_to_all_single(back, got, send_rows, recv_rows)
+        out = torch.zeros(t, h, device="cuda", dtype=torch.float32)
+        out.index_add_(0, order // k, (back * w.reshape(-1)[order].to(x.dtype).unsqueeze(-1)).float())
+        return out.to(x.dtype)
+
+    ref, got = a2a(), p2p()
+    arena.check()
+    err, scale = (ref.float() - got.float()).abs().max().item(), ref.float().abs().max().item()
+    assert err <= 2e-2 * scale + 0.05, (err, scale)        # the collective path rounds w * row to bf16 first
+    for name, fn in (("p2p", p2p), ("nccl_a2a", a2a)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        s, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(10):
+            fn()
+        e_.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([s.elapsed_time(e_) / 10], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            print(f"TIMING moe round trip {name}: {ms.item():.3f} ms (T={t}/rank, k={k}, H={h}, {world} ranks)", flush=True)
+
+
+CASES = {"moe_dispatch_timing": case_moe_dispatch_timing, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":
