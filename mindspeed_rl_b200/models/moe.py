@@ -455,6 +455,6 @@ class MoELayer(nn.Module):
         from ..rollout.moe import MoEWeights
 
         return MoEWeights(self.cfg, self.router.weight.data, self._w1().data, self._w2().data,
-                          self.ep_group, self.ep_size, self.ep_rank,
+                          self.ep_group, self.ep_size, self.ep_rank, p2p=self._p2p_dispatcher,
                           shared=(self.shared_experts.linear_fc1.weight.data,
                                   self.shared_experts.linear_fc2.weight.data) if self.shared_experts else None)

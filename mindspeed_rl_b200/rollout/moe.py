@@ -22,13 +22,14 @@ from ..models.moe import route
 class MoEWeights:
     def __init__(self, cfg, router_w: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, ep_group=None,
                  ep_size: int = 1, ep_rank: int = 0, shared: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                 log2phy: Optional[torch.Tensor] = None, collect_counts: bool = False):
+                 log2phy: Optional[torch.Tensor] = None, collect_counts: bool = False, p2p=None):
         """``w1 [H, E_local, 2F]``, ``w2 [E_local, F, H]`` (views are fine)."""
         self.cfg = cfg
         self.router_w, self.w1, self.w2 = router_w, w1, w2
         self.ep_group, self.ep_size, self.ep_rank = ep_group, ep_size, ep_rank
         self.num_local = w2.shape[0]
         self.shared = shared
+        self.p2p = p2p                      # callable(x) -> peer-memory dispatcher of the EP group, or None
         self.log2phy = log2phy              # [E_logical, max_replicas] physical ids (-1 padded) or None
         self.collect_counts = collect_counts
         self.counts = torch.zeros(cfg.num_experts, dtype=torch.int64)
@@ -60,6 +61,18 @@ class MoEWeights:
             gu = K.grouped_gemm(K.moe_permute(x, plan), plan, self.w1.reshape(h, n_phys * 2 * f), True, 2 * f, 0, 2 * f)
             y = K.grouped_gemm(ops.swiglu_fwd(gu), plan, self.w2.reshape(n_phys * f, h), True, 0, f, h)
             out = K.moe_combine(y, plan, top_p)
+            return self._add_shared(out, x, comm)
+        disp = self.p2p(x) if (self.p2p is not None and self.ep_size > 1) else None
+        if disp is not None and disp.e_local == self.num_local:
+            # tokens go straight into the expert slabs of their ranks and the outputs are pulled back:
+            # no collective, no host round trip
+            from ..ops import moe as K
+            h, f = x.shape[1], self.w2.shape[1]
+            e = self.num_local
+            rt = disp.dispatch(x, phys)
+            gu = K.grouped_gemm(disp.slab, rt.plan, self.w1.reshape(h, e * 2 * f), True, 2 * f, 0, 2 * f)
+            K.grouped_gemm(ops.swiglu_fwd(gu), rt.plan, self.w2.reshape(e * f, h), True, 0, f, h, out=disp.out_slab)
+            out, _ = disp.combine(rt, top_p)
             return self._add_shared(out, x, comm)
         flat = phys.reshape(-1)
         order = torch.argsort(flat, stable=True)

@@ -317,6 +317,13 @@ def case_moe_ep(rank, world, p2p_rows=0):
     lp, _ = model.forward_logprob(ids, labels, meta)
     lp.sum().backward()
     check_status(torch.device("cuda", torch.cuda.current_device()), "moe ep")
+    # the rollout view of the layer (forward only, same dispatcher) agrees with the training forward
+    layer = model.decoder.layers[0]
+    xs = torch.randn(257 + 64 * rank, h, device="cuda", generator=g).bfloat16()
+    with torch.no_grad():
+        y_train, _ = layer.mlp.forward_tokens(xs, layer.comm, False)
+        y_roll = layer.mlp.rollout_view().forward(xs, None)
+    assert (y_train.float() - y_roll.float()).abs().max().item() <= 2e-2 * y_train.float().abs().max().item() + 1e-3
     if p2p_rows:
         from mindspeed_rl_b200.parallel import moe_dispatch
         arena.check()
