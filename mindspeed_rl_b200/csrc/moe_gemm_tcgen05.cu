@@ -80,13 +80,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   fence_after();
   const uint32_t tmem = tmem_slot;
 
-  // tile order: row tiles fastest, so that CTAs running together work on the same expert's columns
+  // tile order: column tiles fastest, so that the CTAs running together cover a few dozen row tiles of
+  // one expert with all its weight columns: both stay in L2 and are read from DRAM once
   if (warp == 4) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int mt = tile % p.n_m_tiles, nt = tile / p.n_m_tiles;
+        const int mt = tile / n_tiles, nt = tile % n_tiles;
         const int e = p.tile_expert[mt];
         if (e < 0) continue;
         const int m0 = mt * BM, n0 = nt * BN;
@@ -116,7 +117,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        if (p.tile_expert[tile % p.n_m_tiles] < 0) continue;
+        if (p.tile_expert[tile / n_tiles] < 0) continue;
         const uint32_t buf = local & 1;
         if (local >= 2) {
           ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, p.error, ERR_ACC);
@@ -147,7 +148,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     unsigned char* patch = smem + (size_t)STAGES * STAGE_BYTES + (size_t)warp * (32 * EPI_PITCH);
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int mt = tile % p.n_m_tiles, nt = tile / p.n_m_tiles;
+      const int mt = tile / n_tiles, nt = tile % n_tiles;
       if (p.tile_expert[mt] < 0) continue;
       const uint32_t buf = local & 1;
       const int m0 = mt * BM, n0 = nt * BN;
