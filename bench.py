@@ -42,9 +42,9 @@ def parse_args():
     ap.add_argument("--min-response", type=int, default=256)
     ap.add_argument("--max-response", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (development only)")
-    ap.add_argument("--pack-tokens", type=int, default=16384, help="token budget of one training micro-batch")
+    ap.add_argument("--pack-tokens", type=int, default=8192, help="token budget of one training micro-batch")
     ap.add_argument("--eager", action="store_true", help="disable CUDA-graph decode")
-    ap.add_argument("--keep-layers", type=int, default=14,
+    ap.add_argument("--keep-layers", type=int, default=28,
                     help="layers whose activations stay resident (the others are fully recomputed in the backward)")
     return ap.parse_args()
 
