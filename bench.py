@@ -146,7 +146,7 @@ def main():
         lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, adam_beta1=0.9, adam_beta2=0.95,
         stage="ray_grpo", train_iters=10 ** 6, seed=1234, bf16=True, use_distributed_optimizer=True,
         recompute_granularity="full", recompute_method="block" if args.keep_layers else None,
-        recompute_num_layers=(args.layers or catalogue[args.model]["num_layers"]) - args.keep_layers
+        recompute_num_layers=max(0, (args.layers or catalogue[args.model]["num_layers"]) - args.keep_layers)
         if args.keep_layers else None, recompute_activation_function=True,
         reset_attention_mask=True, sequence_parallel=False), catalogue)
     rl = RLConfig(dict(
