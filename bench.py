@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--max-response", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (development only)")
     ap.add_argument("--pack-tokens", type=int, default=8192, help="token budget of one training micro-batch")
+    ap.add_argument("--fwd-pack-tokens", type=int, default=32768,
+                    help="token budget of one forward-only micro-batch (reference log-probs)")
     ap.add_argument("--eager", action="store_true", help="disable CUDA-graph decode")
     ap.add_argument("--keep-layers", type=int, default=28,
                     help="layers whose activations stay resident (the others are fully recomputed in the backward)")
@@ -153,7 +155,8 @@ def main():
         n_samples_per_prompt=n, mini_batch_size=gbs, epochs=1, clip_ratio=0.2, init_kl_coef=0.001,
         kl_penalty="low_var_kl", adv_estimator="group_norm", verifier_function=["contains_token_7"],
         verifier_weight=[1.0], actor_resource={"num_gpus": world}, use_remove_padding=True,
-        use_dynamic_bsz=True, max_packing_token_size=args.pack_tokens, log_max_throughput=False))
+        use_dynamic_bsz=True, max_packing_token_size=args.pack_tokens,
+        ref_max_packing_token_size=args.fwd_pack_tokens, log_max_throughput=False))
     gen = GenerateConfig(dict(
         infer_tensor_parallel_size=1, max_num_seqs=args.prompts_per_gpu * n, max_model_len=max_len,
         max_num_batched_tokens=8192, kv_block_size=16, enable_prefix_caching=False,
