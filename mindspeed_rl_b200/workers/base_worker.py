@@ -38,6 +38,20 @@ def pad_batch(ragged: Dict[str, List[torch.Tensor]], pad_id: int, multiple: int 
     return out
 
 
+def check_device_status(stage: str = "") -> None:
+    """Stage boundary: read the status words the kernels' bounded waits report through (tcgen05
+    pipelines, peer-memory barriers and slabs) and raise if one of them gave up, instead of handing
+    a silently incomplete result to the next stage.  One small device-to-host read per stage; no-op
+    when no such kernel ran in this process."""
+    from ..ops import gemm
+    from ..parallel.symm import get_arena
+    for dev in list(gemm._status):
+        gemm.check_status(dev, f"stage {stage}: tcgen05 kernel")
+    arena = get_arena()
+    if arena is not None:
+        arena.check()
+
+
 def profiled_stage(role: str):
     """Wrap a worker stage with an NVTX range and, when the run's profiler config selects this
     rank / stage / iteration, a ``torch.profiler`` session (reference hook sites:
@@ -52,7 +66,9 @@ def profiled_stage(role: str):
             dump = getattr(self, "tensor_dump", None)
             try:
                 with nvtx_range(role):
-                    return fn(self, *a, **kw)
+                    out = fn(self, *a, **kw)
+                check_device_status(role)
+                return out
             finally:
                 profiler_stop(prof)
                 if dump is not None and role in ("actor_update", "critic_update"):

@@ -72,3 +72,30 @@ def test_flops_dense_matches_closed_form():
     moe = types.SimpleNamespace(**vars(cfg), num_experts=8, moe_router_topk=2, moe_ffn_hidden_size=32,
                                 n_shared_experts=1, first_k_dense_replace=1)
     assert num_floating_point_operations(moe, 5) != want
+
+
+def test_stage_boundary_raises_when_a_kernel_wait_gave_up():
+    """A worker stage ends with a look at the device status words: a code left by a bounded wait
+    turns into an exception at the stage boundary (injected here by writing the word on the host)."""
+    import pytest
+    import torch
+
+    from mindspeed_rl_b200.ops import gemm
+    from mindspeed_rl_b200.workers.base_worker import check_device_status, profiled_stage
+
+    class W:
+        @profiled_stage("actor_update")
+        def update(self):
+            return 7
+
+    dev = torch.device("cpu")
+    word = gemm._status_word(dev)
+    try:
+        assert W().update() == 7
+        word.fill_(3)
+        with pytest.raises(gemm.KernelTimeout, match="actor_update"):
+            W().update()
+        assert int(word.item()) == 0                      # the word is re-armed for the next stage
+        check_device_status("again")
+    finally:
+        gemm._status.pop(dev, None)
