@@ -72,7 +72,7 @@ FUSION = dict(
 PARALLEL = dict(
     tensor_model_parallel_size=1, pipeline_model_parallel_size=1,
     expert_model_parallel_size=1, context_parallel_size=1,
-    context_parallel_algo="ulysses_cp_algo", sequence_parallel=False,
+    context_parallel_algo="ulysses_cp_algo", ulysses_degree_in_cp=None, sequence_parallel=False,
     num_layers_per_virtual_pipeline_stage=None, num_layer_list=None, noop_layers=None,
     use_tp_pp_dp_mapping=False, use_cp_send_recv_overlap=False,
     use_distributed_optimizer=False, overlap_grad_reduce=False, overlap_param_gather=False,

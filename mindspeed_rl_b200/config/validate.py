@@ -16,7 +16,7 @@ from typing import Optional
 from .rl_options import GenerateConfig, RLConfig
 from .training_config import MegatronConfig
 
-_CP_ALGOS = ("ulysses_cp_algo", "megatron_cp_algo")
+_CP_ALGOS = ("ulysses_cp_algo", "megatron_cp_algo", "hybrid_cp_algo")
 
 
 def get_node_nums() -> int:

@@ -100,6 +100,7 @@ class TrainingEngine:
         cpi = context_parallel or {}         # {"group", "size", "rank", "algo"} when CP > 1
         self.cp_group, self.cp_size = cpi.get("group"), int(cpi.get("size", 1) or 1)
         self.cp_rank, self.cp_algo = int(cpi.get("rank", 0) or 0), cpi.get("algo")
+        self.cp_ulysses = int(cpi.get("ulysses_degree", 1) or 1)
         self.core: GPTModel = _unwrap(model)
         self.optimizer, self.opt_param_scheduler = optimizer, opt_param_scheduler
         self.stage, self.role = stage, role
@@ -190,7 +191,8 @@ class TrainingEngine:
         if cp is None:
             from ..parallel.context_parallel import ContextParallel
 
-            cp = ContextParallel(self.cp_group, self.cp_size, self.cp_rank, self.cp_algo, mb.cu_host, self.device)
+            cp = ContextParallel(self.cp_group, self.cp_size, self.cp_rank, self.cp_algo, mb.cu_host, self.device,
+                                 ulysses_degree=self.cp_ulysses)
             mb._cp = cp
         return cp
 

@@ -24,6 +24,11 @@ block's probabilities from the merged log-sum-exp, adds dQ locally and returns e
 dK/dV to the rank that owns those keys (reference: ring attention of
 ``docs/zh/features/context_parallel.md:52-86``).
 
+``hybrid_cp_algo`` composes the two: ``cp = ring x ulysses``.  Neighbouring ranks form Ulysses
+sub-groups of ``ulysses_degree`` members that hold contiguous pieces of one ring position's
+zig-zag pair of chunks; an all-to-all inside the sub-group turns them into ``heads / ulysses``
+heads of the whole pair, and the ring runs between the sub-groups (members with the same index).
+
 Per-token outputs (log-probs, values) are all-gathered and put back in global order; in the
 backward every rank keeps the gradient of its own tokens, scaled by ``cp`` because the
 data-parallel averaging that follows divides by ``dp * cp``.
@@ -78,13 +83,52 @@ class _GatherTokens(torch.autograd.Function):
         return d[cp.local_index_dev] * float(cp.size), None
 
 
+_sub_groups = {}
+
+
+def hybrid_sub_groups(group, size: int, rank: int, ulysses: int):
+    """``(ring group, ulysses group)`` of this rank for ``cp = ring x ulysses`` (created once per CP
+    group; only the members of a sub-group take part in its creation)."""
+    members = dist.get_process_group_ranks(group)
+    key = (tuple(members), ulysses)
+    if key not in _sub_groups:
+        ring_n = size // ulysses
+        mine_ring = mine_uly = None
+        for j in range(ulysses):                   # ring groups: same index inside the ulysses sub-group
+            ranks = [members[i * ulysses + j] for i in range(ring_n)]
+            if members[rank] in ranks:
+                mine_ring = dist.new_group(ranks, use_local_synchronization=True)
+        for i in range(ring_n):                    # ulysses groups: neighbouring ranks
+            ranks = members[i * ulysses:(i + 1) * ulysses]
+            if members[rank] in ranks:
+                mine_uly = dist.new_group(ranks, use_local_synchronization=True)
+        _sub_groups[key] = (mine_ring, mine_uly)
+    return _sub_groups[key]
+
+
 class ContextParallel:
-    def __init__(self, group, size: int, rank: int, algo: str, cu_padded: torch.Tensor, device):
+    def __init__(self, group, size: int, rank: int, algo: str, cu_padded: torch.Tensor, device,
+                 ulysses_degree: int = 1):
         self.group, self.size, self.rank, self.algo = group, size, rank, algo or RING
         self.device = torch.device(device)
         self.cu_full = cu_padded.to(torch.int32)
         zigzag = self.algo != ULYSSES
-        per_rank = [split_index(cu_padded.cpu(), size, r, zigzag) for r in range(size)]
+        self.outer = self.inner = None
+        if self.algo == HYBRID:
+            u = max(int(ulysses_degree or 1), 1)
+            if size % u:
+                raise ValueError(f"ulysses_degree_in_cp {u} must divide the context-parallel size {size}")
+            ring_n = size // u
+            ring_group, uly_group = hybrid_sub_groups(group, size, rank, u)
+            self.outer = ContextParallel(ring_group, ring_n, rank // u, RING, cu_padded, device)
+            cu_ring = self.outer.cu_local.cpu().to(torch.int64)
+            self.inner = ContextParallel(uly_group, u, rank % u, ULYSSES, cu_ring, device)
+            per_rank = []
+            for k in range(size):
+                ring_tokens = split_index(cu_padded.cpu(), ring_n, k // u, True)
+                per_rank.append(ring_tokens[split_index(cu_ring, u, k % u, False)])
+        else:
+            per_rank = [split_index(cu_padded.cpu(), size, r, zigzag) for r in range(size)]
         self.local_index = per_rank[rank]
         order = torch.cat(per_rank)                     # rank-major order -> global position
         restore = torch.empty_like(order)
@@ -246,7 +290,27 @@ class ContextParallel:
                 f"({lay.num_heads} query / {lay.num_kv_heads} key-value heads)")
         return QKVLayout(lay.num_heads // self.size, lay.num_kv_heads // self.size, lay.head_dim, interleaved=False)
 
+    def _hybrid_fwd(self, qkv: torch.Tensor, lay: QKVLayout):
+        inner, outer = self.inner, self.outer
+        inner._head_layout(lay)                           # the ulysses degree must divide the head counts
+        q, k, v = (inner._a2a(t.contiguous(), True).contiguous() for t in lay.split(qkv))
+        out, lse = outer._ring_fwd(q, k, v)
+        tr = q.shape[0]
+        back = inner._a2a(out.view(tr, q.shape[1], lay.head_dim), False)
+        return back.reshape(qkv.shape[0], lay.num_heads * lay.head_dim), ("hybrid", q, k, v, lse, out)
+
+    def _hybrid_bwd(self, dattn: torch.Tensor, saved, lay: QKVLayout) -> torch.Tensor:
+        _, q, k, v, lse, out = saved
+        inner, outer = self.inner, self.outer
+        tl = dattn.shape[0]
+        d_out = inner._a2a(dattn.reshape(tl, lay.num_heads, lay.head_dim).contiguous(), True)
+        dq, dk, dv = outer._ring_bwd(d_out.reshape(d_out.shape[0], -1).contiguous(), q, k, v, out, lse)
+        dq, dk, dv = (inner._a2a(t.contiguous(), False) for t in (dq, dk, dv))
+        return lay.merge(dq, dk, dv)
+
     def attention_fwd(self, qkv: torch.Tensor, lay: QKVLayout, meta) -> Tuple[torch.Tensor, Any]:
+        if self.algo == HYBRID:
+            return self._hybrid_fwd(qkv, lay)
         if self.use_ring(lay):
             q, k, v = (t.contiguous() for t in lay.split(qkv))
             out, lse = self._ring_fwd(q, k, v)
@@ -263,6 +327,8 @@ class ContextParallel:
 
     def attention_bwd(self, dattn: torch.Tensor, qkv: torch.Tensor, attn: torch.Tensor, saved: Any, lay: QKVLayout,
                       meta) -> torch.Tensor:
+        if saved[0] == "hybrid":
+            return self._hybrid_bwd(dattn, saved, lay)
         if saved[0] == "ring":
             _, q, k, v, lse = saved
             dq, dk, dv = self._ring_bwd(dattn.contiguous(), q, k, v, attn, lse)

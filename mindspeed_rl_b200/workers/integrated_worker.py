@@ -181,7 +181,9 @@ class IntegratedWorker(BaseWorker):
                       dp_group=ps.group("dp_cp"), dp_size=dp, device=self.device,
                       dynamic_max_batch_size=rl.actor_dynamic_max_batch_size, pipeline=self.pipeline,
                       context_parallel=dict(group=ps.group("cp"), size=ps.size("cp"), rank=ps.rank_in("cp"),
-                                            algo=ac.context_parallel_algo) if ps.size("cp") > 1 else None)
+                                            algo=ac.context_parallel_algo,
+                                            ulysses_degree=getattr(ac, "ulysses_degree_in_cp", None) or 1)
+                      if ps.size("cp") > 1 else None)
         self.actor = TrainingEngine(
             self.model, self.optimizer, self.scheduler, role="actor",
             micro_batch_size=ac.micro_batch_size or 1,

@@ -397,7 +397,7 @@ def test_pipeline_1f1b_matches_single_process():
     run_distributed(_pp_worker, 4, 2)        # fewer micro-batches than stages
 
 
-def _cp_worker(rank, world, algo, ring=False):
+def _cp_worker(rank, world, algo, ring=False, ulysses=1):
     """Context parallel (zig-zag or contiguous split, head-parallel or ring attention) == single process."""
     import os
     os.environ["MSRL_CP_RING"] = "1" if ring else "0"
@@ -417,9 +417,11 @@ def _cp_worker(rank, world, algo, ring=False):
     ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
     ref_lp, _ = full.forward_logprob(ids, labels, meta, 1.0, False)
     (ref_lp * w).sum().backward()
-    cp = ContextParallel(ps.group("cp"), world, rank, algo, meta.cu_seqlens.to(torch.int64), "cpu")
+    cp = ContextParallel(ps.group("cp"), world, rank, algo, meta.cu_seqlens.to(torch.int64), "cpu",
+                         ulysses_degree=ulysses)
     assert cp.local_index.numel() == t // world
-    assert cp.use_ring(model.decoder.layers[0].self_attention.layout) == (ring or world == 3)
+    if algo != "hybrid_cp_algo":
+        assert cp.use_ring(model.decoder.layers[0].self_attention.layout) == (ring or world == 3)
     m_local = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(meta.positions), cp=cp)
     lp_l, _ = model.forward_logprob(cp.take_local(ids), cp.take_local(labels), m_local, 1.0, False)
     lp = cp.gather_tokens(lp_l)
@@ -434,6 +436,10 @@ def _cp_worker(rank, world, algo, ring=False):
 def test_context_parallel_matches_single_process():
     run_distributed(_cp_worker, 2, "megatron_cp_algo")
     run_distributed(_cp_worker, 2, "ulysses_cp_algo")
+
+
+def test_hybrid_context_parallel_matches_single_process():
+    run_distributed(_cp_worker, 4, "hybrid_cp_algo", False, 2)      # 2 ring positions x 2 ulysses ranks
 
 
 def test_ring_attention_matches_single_process():

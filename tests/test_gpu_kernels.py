@@ -370,3 +370,34 @@ def test_swap_attention_and_reuse_fp32_param_on_gpu():
             ref_master = full
     for a, b in zip(*outs):
         assert (a - b).abs().max() <= 2 ** -7 * a.abs().max()
+
+
+def test_device_barrier_gives_up_when_a_peer_never_arrives():
+    """The peer-memory barrier waits a bounded time for a flag; here nothing ever sets it (the
+    "peer" is a second flag array in this GPU's own memory), so the kernel must come back with a
+    status code and leave the context usable."""
+    import ctypes
+    import time
+
+    from mindspeed_rl_b200.ops import _lib
+    lib = _lib.load()
+    flags = torch.zeros(2, 16, dtype=torch.int32, device=DEV)           # flag arrays of "rank 0" and "rank 1"
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ptrs = (ctypes.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    epochs = (ctypes.c_uint * 2)(0, 1)
+    t0 = time.time()
+    rc = lib.msrl_symm_barrier(ptrs, ctypes.c_int(0), ctypes.c_int(2), epochs, ctypes.c_uint(0b10),
+                               _lib.ptr(status), _lib.stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 10.0
+    assert int(status.item()) == 101                                    # gave up waiting for peer 1
+    assert int(flags[1, 0].item()) == 1                                 # my arrival was published
+    # the context still works, and a barrier whose flag is set passes at once
+    flags[0, 1] = 2
+    status.zero_()
+    epochs = (ctypes.c_uint * 2)(0, 2)
+    lib.msrl_symm_barrier(ptrs, ctypes.c_int(0), ctypes.c_int(2), epochs, ctypes.c_uint(0b10), _lib.ptr(status),
+                          _lib.stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
