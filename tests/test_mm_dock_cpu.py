@@ -55,3 +55,23 @@ def test_reuse_image_embeds_changes_the_readers():
     merged = merge_mm_columns(dict(vit_embeds=[emb], image_grid_thw=[grid], image_num=[2], video_num=[0]))
     un = unpack_mm_experience(merged, merge_size=2)
     assert un["vit_embeds"][0].shape == (5, 3) and torch.equal(un["vit_embeds"][0], emb)
+
+
+def test_mrope_positions_for_text_image_text():
+    from mindspeed_rl_b200.datasets.mm_utils import get_rope_index
+    IMG, START = 9, 8
+    # 2 text tokens, vision start, a 1 x 4 x 6 image (merge 2 -> 2 x 3 = 6 placeholders), 3 text tokens, 2 pads
+    ids = torch.tensor([[5, 6, START] + [IMG] * 6 + [7, 7, 7] + [0, 0]])
+    mask = torch.tensor([[1] * 12 + [0, 0]])
+    pos, delta = get_rope_index(ids, torch.tensor([[1, 4, 6]]), None, mask, spatial_merge_size=2,
+                                image_token_id=IMG, vision_start_token_id=START)
+    t, h, w = pos[0, 0].tolist(), pos[1, 0].tolist(), pos[2, 0].tolist()
+    assert t[:3] == h[:3] == w[:3] == [0, 1, 2]
+    assert t[3:9] == [3] * 6                       # one temporal slice
+    assert h[3:9] == [3, 3, 3, 4, 4, 4] and w[3:9] == [3, 4, 5, 3, 4, 5]
+    assert t[9:12] == h[9:12] == w[9:12] == [6, 7, 8]      # continues after the largest index used (5) + 1
+    assert t[12:] == [1, 1]                         # padding
+    assert delta.tolist() == [[9 - 14]]
+    # text only: plain positions
+    pos, delta = get_rope_index(torch.tensor([[4, 4, 4, 0]]), attention_mask=torch.tensor([[1, 1, 1, 0]]))
+    assert pos[:, 0].tolist() == [[0, 1, 2, 1]] * 3 and delta.tolist() == [[3 - 4]]
