@@ -269,6 +269,27 @@ def _launch_worker(rank, world, train_tp, infer_tp):
         assert all(m["timing/rollout"] > 0 and "actor/pg_loss" in m for m in hist)
 
 
+def _launch_moe_ep_worker(rank, world):
+    """Whole GRPO iterations of a small MoE model with expert parallelism 2: the two ranks are
+    data-parallel replicas for rollout and training, exchange tokens in every MoE layer and
+    therefore step their rollout engines together."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        "actor_config.expert_model_parallel_size=2", f"rl_config.actor_resource.num_gpus={world}",
+        "+model.tiny_qwen2.num_experts=4", "+model.tiny_qwen2.moe_router_topk=2",
+        "+model.tiny_qwen2.moe_ffn_hidden_size=32", "+model.tiny_qwen2.norm_topk_prob=true",
+        "+model.tiny_qwen2.moe_aux_loss_coeff=0.001"])
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == 2
+        assert all(m["timing/rollout"] > 0 and "actor/pg_loss" in m for m in hist)
+
+
+def test_launch_grpo_moe_expert_parallel():
+    run_distributed(_launch_moe_ep_worker, 2)
+
+
 def test_launch_grpo_tp2_rollout_tp1_reshard():
     """Full ``run_rl`` on 2 gloo ranks: training TP=2, rollout TP=1 (two rollout replicas) through
     the resharding plan's gathered fallback."""
