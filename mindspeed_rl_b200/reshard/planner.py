@@ -250,8 +250,9 @@ class Resharder:
         layout = train_state.layout
         if layout.world_size % infer_tp:
             raise ValueError("the rollout TP size must divide the world size")
-        if cfg.is_moe and layout.ep > 1:
-            raise NotImplementedError("resharding keeps experts in place; expert re-homing is not planned yet")
+        if cfg.is_moe and layout.ep > 1 and (layout.pp > 1 or getattr(layout, "expert_tp", 1) > 1):
+            raise NotImplementedError("with expert parallelism the experts stay on their training ranks: only the "
+                                      "dense tensors are resharded, which needs pp = 1 and unsplit experts")
         self.infer_state = ParallelState(RankLayout(layout.world_size, tp=infer_tp), train_state.rank,
                                          backend=train_state.backend, rank_offset=train_state.rank_offset)
         tp_group = self.infer_state.group("tp")
@@ -275,7 +276,9 @@ class Resharder:
                              block_size=gc.kv_block_size, enable_prefix_caching=gc.enable_prefix_caching,
                              enforce_eager=gc.enforce_eager, graph_batch_sizes=tuple(gc.graph_batch_sizes),
                              eos_token_id=worker.eos_token_id, pad_token_id=worker.pad_token_id, comm=comm,
-                             seed=worker.seed)
+                             seed=worker.seed,
+                             lockstep_group=worker.parallel_state.group("ep")
+                             if (worker.tcfg.is_moe and worker.parallel_state.size("ep") > 1) else None)
 
         return cls(worker.tcfg, worker.model, worker.parallel_state, gc.infer_tensor_parallel_size, worker.device,
                    factory, arena=get_arena(),
