@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -101,12 +102,23 @@ def build_decode_groups(group_ids: Sequence, prefix_lens: Sequence[int], group_m
     return key_start, rows_out, prefix_out, shared
 
 
+def _prefix_splits(batch: int, nkv: int, device) -> int:
+    """Splits of the shared prompt per (group, KV head): as many as fill one wave of the prefix kernel
+    (two CTAs per SM) with groups of about eight members; ``MSRL_PREFIX_SPLITS`` overrides."""
+    env = os.environ.get("MSRL_PREFIX_SPLITS")
+    if env:
+        return max(1, min(8, int(env)))
+    slots = 2 * torch.cuda.get_device_properties(device).multi_processor_count
+    ctas = max(1, (batch + 7) // 8) * nkv
+    return max(1, min(8, slots // ctas))
+
+
 def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.Tensor,
                            v_cache: torch.Tensor, block_tables: torch.Tensor,
                            context_lens: torch.Tensor, max_context: int,
                            out: Optional[torch.Tensor] = None,
                            groups: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
-                           prefix_splits: int = 4) -> torch.Tensor:
+                           prefix_splits: Optional[int] = None) -> torch.Tensor:
     """One query token per sequence against its paged KV (which already holds that token).
 
     ``groups = (key_start [B], group_rows [G, 8], group_prefix [G])`` (int32, device) enables the
@@ -124,6 +136,8 @@ def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.
         nsplit = L.msrl_paged_decode_nsplit(c_int(b), c_int(nkv), c_int(int(max_context)))
         if groups is not None:
             key_start, group_rows, group_prefix = groups
+            if prefix_splits is None:
+                prefix_splits = _prefix_splits(b, nkv, qkv.device)
             slots = nsplit + prefix_splits
             part_o = _workspace("decode_part_o", b * nh * slots * hd, qkv.device)
             part_ml = _workspace("decode_part_ml", b * nh * slots * 2, qkv.device)
