@@ -36,6 +36,11 @@ from ..ops import _lib
 _HEADER_BYTES = 4096          # flags (one u32 per rank) live at the start of every arena
 
 
+class ArenaUnavailable(RuntimeError):
+    """Peer-mapped memory could not be set up on at least one rank; raised on EVERY rank of the team,
+    so that all of them fall back to collectives together."""
+
+
 class SymmetricTimeout(RuntimeError):
     pass
 
@@ -70,27 +75,42 @@ class SymmetricArena:
         handle = (ctypes.c_ubyte * 64)()
         base = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            _lib.check(self.lib.msrl_symm_alloc(ctypes.c_longlong(self.nbytes), ctypes.byref(base), handle),
-                       "symm_alloc")
-        self.base = int(base.value)
+            rc = int(self.lib.msrl_symm_alloc(ctypes.c_longlong(self.nbytes), ctypes.byref(base), handle))
+        self.base = int(base.value) if rc == 0 else 0
         self.peer_base: List[int] = [0] * self.world
         self.peer_base[self.rank] = self.base
+        self._closed = False
+        if self.world == 1 and rc != 0:
+            raise ArenaUnavailable(f"allocation of {self.nbytes} bytes failed (CUDA error {rc})")
         if self.world > 1:
+            # a failure on one rank must become the same exception on all of them (no rank may be left
+            # waiting in a collective): exchange the outcome together with the handles, then the
+            # outcome of mapping the peers
             handles: List[Optional[bytes]] = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle), group=group)
-            with torch.cuda.device(self.device):
-                for r, h in enumerate(handles):
-                    if r == self.rank:
-                        continue
-                    p = ctypes.c_void_p()
-                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
-                    _lib.check(self.lib.msrl_symm_open(buf, ctypes.byref(p)), "symm_open")
-                    self.peer_base[r] = int(p.value)
+            dist.all_gather_object(handles, bytes(handle) if rc == 0 else None, group=group)
+            failed = [r for r, h in enumerate(handles) if h is None]
+            opened = 0
+            if not failed:
+                with torch.cuda.device(self.device):
+                    for r, h in enumerate(handles):
+                        if r == self.rank:
+                            continue
+                        p = ctypes.c_void_p()
+                        buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                        if int(self.lib.msrl_symm_open(buf, ctypes.byref(p))) != 0:
+                            break
+                        self.peer_base[r] = int(p.value)
+                        opened += 1
+            ok = [None] * self.world
+            dist.all_gather_object(ok, (not failed) and opened == self.world - 1, group=group)
+            if not all(ok):
+                self._release()
+                raise ArenaUnavailable(f"peer-mapped memory unavailable (allocation failed on ranks {failed}, "
+                                       f"mapping ok per rank: {ok})")
         self._cursor = _HEADER_BYTES
         self._epochs = [0] * self.world
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._whole = torch.as_tensor(_Span(self.base, self.nbytes, self), device=self.device)
-        self._closed = False
         if self.world > 1:
             dist.barrier(group=group)        # every arena is zeroed and mapped before first use
 
@@ -259,11 +279,19 @@ class SymmetricArena:
         torch.cuda.synchronize(self.device)
         if self.world > 1:
             dist.barrier(group=self.group)   # nobody is still reading a peer that is about to unmap
+        self._release()
+
+    def _release(self) -> None:
+        """Unmap the peers that were mapped and free the local allocation (no collective)."""
         for r, p in enumerate(self.peer_base):
             if r != self.rank and p:
                 self.lib.msrl_symm_close(ctypes.c_void_p(p))
+                self.peer_base[r] = 0
         self._whole = None
-        self.lib.msrl_symm_free(ctypes.c_void_p(self.base))
+        if self.base:
+            self.lib.msrl_symm_free(ctypes.c_void_p(self.base))
+            self.base = 0
+        self._closed = True
 
 
 COPY_DESC_DTYPE = np.dtype([("src_off", "<i8"), ("dst_off", "<i8"), ("src_pitch", "<i8"), ("dst_pitch", "<i8"),
@@ -293,5 +321,6 @@ def init_arena(nbytes: int, group=None, device=None) -> SymmetricArena:
     global _ARENA
     if _ARENA is not None:
         _ARENA.close()
-    _ARENA = SymmetricArena(nbytes, group, device)
+    _ARENA = None
+    _ARENA = SymmetricArena(nbytes, group, device)      # ArenaUnavailable leaves no arena behind
     return _ARENA

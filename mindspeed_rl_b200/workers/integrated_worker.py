@@ -73,7 +73,14 @@ class IntegratedWorker(BaseWorker):
             tp = self.parallel_state.size("tp")
             extra = 2 * m_local * self.tcfg.hidden_size * 2 * (1 + tp) + (1 << 20)
         extra += self._moe_p2p_bytes()
-        init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20) + extra, device=self.device)
+        from ..parallel.symm import ArenaUnavailable
+        try:
+            init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20) + extra, device=self.device)
+        except ArenaUnavailable as e:
+            # raised on every rank together: the job carries on with NCCL collectives and gathered resharding
+            import logging
+            logging.getLogger(__name__).warning("peer-mapped memory unavailable, using collectives: %s", e)
+            self.tcfg.moe_p2p_dispatch_rows = 0
 
     def _moe_p2p_bytes(self) -> int:
         """Expert-parallel MoE models can move tokens between ranks through peer-mapped slabs
