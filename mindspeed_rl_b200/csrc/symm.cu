@@ -155,13 +155,21 @@ static PeerPtrs to_peers(void* const* ptrs, int world) {
 // ---- arena management (host) -------------------------------------------------------------------
 MSRL_API int msrl_symm_alloc(long long bytes, void** ptr_out, unsigned char* handle64_out) {
   void* p = nullptr;
+  // a failure here is an ordinary outcome (the caller falls back to collectives): leave no
+  // allocation and no pending error behind
   cudaError_t e = cudaMalloc(&p, (size_t)bytes);
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return (int)e;
+  }
   e = cudaMemset(p, 0, (size_t)bytes);
-  if (e != cudaSuccess) return (int)e;
   cudaIpcMemHandle_t h;
-  e = cudaIpcGetMemHandle(&h, p);
-  if (e != cudaSuccess) return (int)e;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    cudaGetLastError();
+    return (int)e;
+  }
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   memcpy(handle64_out, &h, 64);
   *ptr_out = p;

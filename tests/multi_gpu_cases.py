@@ -434,7 +434,27 @@ def case_moe_dispatch_timing(rank, world):
             print(f"TIMING moe round trip {name}: {ms.item():.3f} ms (T={t}/rank, k={k}, H={h}, {world} ranks)", flush=True)
 
 
-CASES = {"moe_dispatch_timing": case_moe_dispatch_timing, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+def case_arena_fallback(rank, world):
+    """One rank cannot allocate its arena (it asks for far more than the device has; the allocation
+    call returns an error code): every rank gets the same exception, nobody is left waiting in a
+    collective, and a normal arena can be created afterwards."""
+    from mindspeed_rl_b200.parallel.symm import ArenaUnavailable, get_arena, init_arena
+    try:
+        init_arena((1 << 45) if rank == world - 1 else (8 << 20))
+        raise AssertionError("the oversized arena must not come up")
+    except ArenaUnavailable as e:
+        assert f"[{world - 1}]" in str(e), str(e)
+    assert get_arena() is None
+    arena = init_arena(8 << 20)
+    x = arena.alloc(1024, torch.float32)
+    x.fill_(float(rank + 1))
+    arena.barrier()
+    arena.check()
+    torch.cuda.synchronize()
+    assert float(x[0]) == rank + 1
+
+
+CASES = {"arena_fallback": case_arena_fallback, "moe_dispatch_timing": case_moe_dispatch_timing, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

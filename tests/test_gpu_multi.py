@@ -60,3 +60,8 @@ def test_moe_expert_parallel():
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_ring_attention_context_parallel():
     _run("cp_ring", 2)
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_arena_setup_failure_is_collective():
+    _run("arena_fallback", 2)
