@@ -250,3 +250,29 @@ def attn_kv_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
         dk[ks:ke] = dki.view(nkv, rep, ke - ks, hd).sum(1).transpose(0, 1)
         dv[ks:ke] = dvi.view(nkv, rep, ke - ks, hd).sum(1).transpose(0, 1)
     return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
+def attn_merge_(acc_o: torch.Tensor, acc_l: torch.Tensor, o: torch.Tensor, l: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> None:
+    """Fold a block result into the running result of an attention over disjoint key sets, in place:
+    ``acc_o [T, nh, hd]`` fp32 and ``acc_l [nh, T]`` (log-sum-exp) absorb ``o [Tb, nh*hd]`` /
+    ``l [nh, Tb]``; ``rows`` (int64 ``[Tb]``) names the running rows the block rows belong to."""
+    t, nh, hd = acc_o.shape
+    tb = o.shape[0]
+    if _lib.use_kernels(acc_o, acc_l, o, l) and o.dtype == torch.bfloat16 and acc_o.is_contiguous() \
+            and acc_l.is_contiguous() and hd % 8 == 0:
+        check(_lib.load().msrl_attn_merge(ptr(acc_o), ptr(acc_l), c_ll(t), ptr(o.contiguous()), ptr(l.contiguous()),
+                                          c_ll(tb), ptr(rows), c_int(nh), c_int(hd), stream()), "attn_merge")
+        return
+    ob = o.float().view(tb, nh, hd)
+    if rows is None:
+        lt = torch.logaddexp(acc_l, l)
+        wa, wb = torch.exp(acc_l - lt), torch.exp(l - lt)
+        acc_o.mul_(torch.nan_to_num(wa).t().unsqueeze(-1)).add_(ob * torch.nan_to_num(wb).t().unsqueeze(-1))
+        acc_l.copy_(lt)
+    else:
+        al = acc_l[:, rows]
+        lt = torch.logaddexp(al, l)
+        wa, wb = torch.nan_to_num(torch.exp(al - lt)), torch.nan_to_num(torch.exp(l - lt))
+        acc_o[rows] = acc_o[rows] * wa.t().unsqueeze(-1) + ob * wb.t().unsqueeze(-1)
+        acc_l[:, rows] = lt

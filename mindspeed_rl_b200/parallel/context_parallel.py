@@ -189,7 +189,7 @@ class ContextParallel:
         nxt = torch.empty_like(cur) if n > 1 else None
         reqs = self._post([(cur, r + 1)], [(nxt, r - 1)]) if n > 1 else []     # K/V for step 1 travel during step 0
         o, lse = ops.attn_kv_fwd(q, k, v, self.cu_local, self.cu_local, self.max_local, True)
-        acc_o, acc_l = o.float().view(tl, nh, hd), lse.clone()                 # [Tl, nh, hd], [nh, Tl]
+        acc_o, acc_l = o.float().view(tl, nh, hd).contiguous(), lse.clone()    # [Tl, nh, hd], [nh, Tl]
         for s in range(1, n):
             self._wait(reqs)
             cur = nxt                                      # K/V of rank j
@@ -200,18 +200,11 @@ class ContextParallel:
             if j < r:
                 kj, vj = cur[0][self.first_idx], cur[1][self.first_idx]
                 o, l = ops.attn_kv_fwd(q, kj, vj, self.cu_local, self.cu_half, self.max_local, False)
-                lt = torch.logaddexp(acc_l, l)
-                acc_o = acc_o * torch.exp(acc_l - lt).t().unsqueeze(-1) + \
-                    o.float().view(tl, nh, hd) * torch.exp(l - lt).t().unsqueeze(-1)
-                acc_l = lt
+                ops.attn_merge_(acc_o, acc_l, o, l)
             else:
                 idx = self.second_idx
                 o, l = ops.attn_kv_fwd(q[idx], cur[0], cur[1], self.cu_half, self.cu_local, self.max_half, False)
-                al = acc_l[:, idx]
-                lt = torch.logaddexp(al, l)
-                acc_o[idx] = acc_o[idx] * torch.exp(al - lt).t().unsqueeze(-1) + \
-                    o.float().view(-1, nh, hd) * torch.exp(l - lt).t().unsqueeze(-1)
-                acc_l[:, idx] = lt
+                ops.attn_merge_(acc_o, acc_l, o, l, idx)
         return acc_o.reshape(tl, nh * hd).to(q.dtype), acc_l
 
     def _ring_bwd(self, dout, q, k, v, out, lse):

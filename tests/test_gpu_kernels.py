@@ -401,3 +401,24 @@ def test_device_barrier_gives_up_when_a_peer_never_arrives():
                           _lib.stream())
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+
+
+def test_attention_merge_kernel():
+    """Folding a block result into the running (out, log-sum-exp) pair: kernel against the PyTorch
+    formulation, whole-tensor and row-subset forms, including rows that saw no key on one side."""
+    torch.manual_seed(8)
+    t, nh, hd = 700, 6, 128
+    for rows in (None, torch.randperm(t, device=DEV)[:333].sort().values):
+        tb = t if rows is None else rows.numel()
+        acc_o = torch.randn(t, nh, hd, device=DEV)
+        acc_l = torch.randn(nh, t, device=DEV) * 3
+        acc_l[0, :5] = float("-inf")
+        acc_o[:5, 0] = 0
+        o = torch.randn(tb, nh * hd, device=DEV).bfloat16()
+        l = torch.randn(nh, tb, device=DEV) * 3
+        ro, rl = acc_o.cpu().clone(), acc_l.cpu().clone()
+        ops.attn_merge_(ro, rl, o.cpu(), l.cpu(), None if rows is None else rows.cpu())
+        ops.attn_merge_(acc_o, acc_l, o, l, rows)
+        close(acc_o, ro, 1e-4, 1e-4, "merged out")
+        assert torch.equal(torch.isinf(acc_l).cpu(), torch.isinf(rl))      # rows no block touched keep -inf
+        close(torch.nan_to_num(acc_l, neginf=0.0), torch.nan_to_num(rl, neginf=0.0), 1e-4, 1e-4, "merged lse")
