@@ -279,9 +279,12 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeParams p)
 // against each 64-key chunk of the shared prefix, which is therefore read from HBM once per group.
 // Grid (group, kv head, prefix split); partial results go to slots [0, npre) of every member and
 // are merged with the members' own suffix partials by the merge kernel.
+// keys per pipeline stage of the shared-prefix kernel: 32 keeps a CTA at 52 KB of shared memory (D = 128),
+// so that four CTAs share an SM and hide each other's load latency
+constexpr int kPrefixChunk = 32;
 template <int D>
 __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodeParams p) {
-  constexpr int CH = 64, LD = D + 8, THREADS = 128, ROWS = 64;
+  constexpr int CH = kPrefixChunk, LD = D + 8, THREADS = 128, ROWS = 64;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // 64 x LD
   __nv_bfloat16* sK = sQ + ROWS * LD;                               // 2 x CH x LD
@@ -856,7 +859,7 @@ static int launch_paged_decode(const void* q, const long long* q_layout4, const 
   dim3 grid(B, nkv, nsplit);
   cudaError_t e;
   if (grouped) {
-    const size_t psmem = (size_t)(64 + 4 * 64) * LD * sizeof(__nv_bfloat16);
+    const size_t psmem = (size_t)(64 + 4 * kPrefixChunk) * LD * sizeof(__nv_bfloat16);
     dim3 pgrid(n_groups, nkv, npre);
     if (D == 128) {
       e = cudaFuncSetAttribute(paged_decode_prefix_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);

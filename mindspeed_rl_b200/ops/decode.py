@@ -104,11 +104,11 @@ def build_decode_groups(group_ids: Sequence, prefix_lens: Sequence[int], group_m
 
 def _prefix_splits(batch: int, nkv: int, device) -> int:
     """Splits of the shared prompt per (group, KV head): as many as fill one wave of the prefix kernel
-    (two CTAs per SM) with groups of about eight members; ``MSRL_PREFIX_SPLITS`` overrides."""
+    (four CTAs per SM) with groups of about eight members; ``MSRL_PREFIX_SPLITS`` overrides."""
     env = os.environ.get("MSRL_PREFIX_SPLITS")
     if env:
         return max(1, min(8, int(env)))
-    slots = 2 * torch.cuda.get_device_properties(device).multi_processor_count
+    slots = 4 * torch.cuda.get_device_properties(device).multi_processor_count
     ctas = max(1, (batch + 7) // 8) * nkv
     return max(1, min(8, slots // ctas))
 
