@@ -629,6 +629,7 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   __shared__ uint64_t kv_full, qdo_full[BWD_STAGES], qdo_empty[BWD_STAGES], s_full[2], s_free[2], p_ready, p_free;
   __shared__ uint32_t tmem_slot;
+  __shared__ __align__(16) float stat_s[BWD_STAGES][2][64];   // per stage: log2-domain lse and delta of its 64 query rows
 
   const int b = blockIdx.z, hk = blockIdx.y, nt = blockIdx.x;
   const int q0 = p.cu_q[b], qlen = p.cu_q[b + 1] - q0;
@@ -671,19 +672,31 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const uint32_t tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 384;
 
   if (warp == TMA_WARP) {
+    // lane 0 issues the TMA loads; all lanes stage the per-query statistics of the tile (two rows each)
+    const int kc = head_col(0, p.k_group_stride, p.k_hpg, p.k_head_stride, hk);
+    const int vc = head_col(0, p.v_group_stride, p.v_hpg, p.v_head_stride, hk);
     if (lane == 0) {
-      const int kc = head_col(0, p.k_group_stride, p.k_hpg, p.k_head_stride, hk);
-      const int vc = head_col(0, p.v_group_stride, p.v_hpg, p.v_head_stride, hk);
       mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
       tma_load_2d(smem + KV_SMEM_K, &map_k, &kv_full, kc, k0 + kb);
       tma_load_2d(smem + KV_SMEM_K + TILE_HALF, &map_k, &kv_full, kc + 64, k0 + kb);
       tma_load_2d(smem + KV_SMEM_V, &map_v, &kv_full, vc, k0 + kb);
       tma_load_2d(smem + KV_SMEM_V + TILE_HALF, &map_v, &kv_full, vc + 64, k0 + kb);
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % BWD_STAGES;
-        const uint32_t use = it / BWD_STAGES;
-        if (use > 0 && !mbar_wait(&qdo_empty[st], (use - 1) & 1, p.error, ERR_EMPTY)) break;
-        const int hq = hk * rep + it / nq, qi = i_start + it % nq;
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it % BWD_STAGES;
+      const uint32_t use = it / BWD_STAGES;
+      if (use > 0 && !mbar_wait(&qdo_empty[st], (use - 1) & 1, p.error, ERR_EMPTY)) break;
+      const int hq = hk * rep + it / nq, qi = i_start + it % nq;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int q = qi * 64 + half * 32 + lane;
+        const bool okq = q < qlen;
+        const long long gi = (long long)hq * p.Tq + q0 + q;
+        stat_s[st][0][half * 32 + lane] = okq ? __ldg(p.lse + gi) * LOG2E : INFINITY;   // +inf: P is exactly 0
+        stat_s[st][1][half * 32 + lane] = okq ? __ldg(p.delta + gi) : 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) {
         const int qc = head_col(0, p.q_group_stride, p.q_hpg, p.q_head_stride, hq);
         mbar_expect_tx(&qdo_full[st], BWD_STAGE_BYTES);
         unsigned char* sq = smem + KV_SMEM_QDO + st * BWD_STAGE_BYTES;
@@ -692,6 +705,7 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tma_load_2d(sq + T64_BYTES, &map_do, &qdo_full[st], hq * D, q0 + qi * 64);
         tma_load_2d(sq + T64_BYTES + T64_HALF, &map_do, &qdo_full[st], hq * D + 64, q0 + qi * 64);
       }
+      __syncwarp();
     }
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
@@ -748,19 +762,23 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const int sb = it & 1;
       const int hq = hk * rep + it / nq, qi = i_start + it % nq;
       const int qbase = qi * 64 + wg * 32;                 // first query row of this thread's 32 columns
-      // per-column statistics, the same address in every lane (one broadcast transaction each)
-      float lse2[32], dl[32];
-      const float* lse_p = p.lse + (long long)hq * p.Tq + q0 + qbase;
-      const float* dl_p = p.delta + (long long)hq * p.Tq + q0 + qbase;
-      const int nvalid = qlen - qbase;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        lse2[i] = (i < nvalid) ? __ldg(lse_p + i) * LOG2E : INFINITY;
-        dl[i] = (i < nvalid) ? __ldg(dl_p + i) : 0.f;
-      }
+      const int st = it % BWD_STAGES;
       ok = mbar_wait(&s_full[sb], (it >> 1) & 1, p.error, ERR_S);
       if (!ok) break;
       fence_after();
+      // the statistics of this stage were written before its "full" arrival, which the MMA thread saw
+      // before it issued the MMAs this wait is about; waiting on the stage barrier as well makes the
+      // ordering direct (the phase cannot advance before this iteration's P is handed over)
+      ok = mbar_wait(&qdo_full[st], (it / BWD_STAGES) & 1, p.error, ERR_Q);
+      if (!ok) break;
+      float lse2[32], dl[32];
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(&stat_s[st][0][wg * 32 + i]);
+        const float4 b4 = *reinterpret_cast<const float4*>(&stat_s[st][1][wg * 32 + i]);
+        lse2[i] = a.x; lse2[i + 1] = a.y; lse2[i + 2] = a.z; lse2[i + 3] = a.w;
+        dl[i] = b4.x; dl[i + 1] = b4.y; dl[i + 2] = b4.z; dl[i + 3] = b4.w;
+      }
       float s[32], dp[32];
       tmem_ld32(tmem + lane_base + sb * 64 + wg * 32, s);
       tmem_ld32(tmem_dp + lane_base + sb * 64 + wg * 32, dp);
