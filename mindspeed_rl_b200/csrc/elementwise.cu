@@ -175,9 +175,8 @@ __global__ void headnorm_bwd_kernel(__nv_bfloat16* __restrict__ dy_dx,
                                     const __nv_bfloat16* __restrict__ w,
                                     const float* __restrict__ rstd, float* __restrict__ dw_partial,
                                     long long T, int nheads, int hd) {
-  __shared__ float sdw[256];
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) sdw[i] = 0.f;
-  __syncthreads();
+  __shared__ float sdw[8][256];    // one row per warp (256 threads): summed in warp order, so that the
+                                   // result does not depend on which warp finishes first
   const int lane = threadIdx.x & 31;
   const long long warps_total = ((long long)gridDim.x * blockDim.x) >> 5;
   const bool act = lane * 8 < hd;
@@ -210,12 +209,15 @@ __global__ void headnorm_bwd_kernel(__nv_bfloat16* __restrict__ dy_dx,
       st8(dy_dx + off + lane * 8, pack8(o));
     }
   }
-  if (act) {
+  const int warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) atomicAdd(&sdw[lane * 8 + k], dw_acc[k]);
-  }
+  for (int k = 0; k < 8; ++k) sdw[warp][lane * 8 + k] = act ? dw_acc[k] : 0.f;
   __syncthreads();
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) dw_partial[(long long)blockIdx.x * hd + i] = sdw[i];
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sdw[w][i];
+    dw_partial[(long long)blockIdx.x * hd + i] = t;
+  }
 }
 
 // --------------------------------------------------------------------------------------------
