@@ -28,6 +28,29 @@ __global__ void sumsq_kernel(const T* __restrict__ g, long long n, float* __rest
   if (threadIdx.x == 0) atomicAdd(out, s);
 }
 
+// Order-independent variant: every block stores its partial sum, then one block adds the partials in
+// index order (a fixed tree), so the result is the same bit pattern on every run.
+template <typename T>
+__global__ void sumsq_partial_kernel(const T* __restrict__ g, long long n, float* __restrict__ partials) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = to_f32<T>(g[i]);
+    s += v * v;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+
+__global__ void sumsq_finish_kernel(const float* __restrict__ partials, int n_part, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n_part; i += blockDim.x) s += partials[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) *out += s;
+}
+
 // coef = min(1, max_norm / (sqrt(sumsq) + 1e-6)) * extra_scale ; norm_out = sqrt(sumsq)
 __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm, float extra_scale,
                                  float* __restrict__ coef, float* __restrict__ norm_out) {
@@ -84,6 +107,21 @@ MSRL_API int msrl_sumsq(const void* g, int is_bf16, long long n, float* out, cud
     sumsq_kernel<__nv_bfloat16><<<stream_grid(n), 256, 0, st>>>((const __nv_bfloat16*)g, n, out);
   else
     sumsq_kernel<float><<<stream_grid(n), 256, 0, st>>>((const float*)g, n, out);
+  MSRL_LAUNCH_CHECK();
+}
+
+// partials: scratch of at least `max_blocks` floats
+MSRL_API int msrl_sumsq_ordered(const void* g, int is_bf16, long long n, float* partials, int max_blocks, float* out,
+                                cudaStream_t st) {
+  if (n == 0) return 0;
+  int grid = (int)stream_grid(n);
+  if (grid > max_blocks) grid = max_blocks;
+  if (grid < 1) return (int)cudaErrorInvalidValue;
+  if (is_bf16)
+    sumsq_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)g, n, partials);
+  else
+    sumsq_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)g, n, partials);
+  sumsq_finish_kernel<<<1, 256, 0, st>>>(partials, grid, out);
   MSRL_LAUNCH_CHECK();
 }
 

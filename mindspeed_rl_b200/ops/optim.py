@@ -15,8 +15,11 @@ from ._lib import c_float, c_int, c_ll, check, ptr, stream
 def sumsq_accumulate(g: torch.Tensor, out: torch.Tensor) -> None:
     """``out[0] += sum(g^2)`` (``out`` fp32, zeroed by the caller beforehand)."""
     if _lib.use_kernels(g, out) and g.dtype in (torch.bfloat16, torch.float32) and g.is_contiguous():
-        check(_lib.load().msrl_sumsq(ptr(g), c_int(1 if g.dtype == torch.bfloat16 else 0),
-                                     c_ll(g.numel()), ptr(out), stream()), "sumsq")
+        # block partials are added in index order: the norm is the same bit pattern on every run
+        from .elementwise import _workspace
+        part = _workspace("sumsq_partials", 4096, g.device)
+        check(_lib.load().msrl_sumsq_ordered(ptr(g), c_int(1 if g.dtype == torch.bfloat16 else 0),
+                                             c_ll(g.numel()), ptr(part), c_int(4096), ptr(out), stream()), "sumsq")
         return
     out.add_(g.float().pow(2).sum())
 
