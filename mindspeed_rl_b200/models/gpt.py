@@ -324,6 +324,18 @@ class _LayerFn(torch.autograd.Function):
 # ---------------------------------------------------------------------------------------------------
 # Embedding / output
 # ---------------------------------------------------------------------------------------------------
+def embedding_grad_accumulate(g: torch.Tensor, ids: torch.Tensor, d: torch.Tensor) -> None:
+    """``g[ids[t]] += d[t]`` with the rows of one id summed in fp32 in token order: the result does not
+    depend on the order in which atomics land (``index_add_`` into a bf16 buffer rounds after every
+    addition, in a different order on every run)."""
+    if ids.numel() == 0:
+        return
+    order = torch.argsort(ids, stable=True)
+    uniq, counts = torch.unique_consecutive(ids[order], return_counts=True)
+    rows = torch.segment_reduce(d[order].float(), "sum", lengths=counts, axis=0, unsafe=True)
+    g[uniq] = (g[uniq].float() + rows).to(g.dtype)
+
+
 class _EmbedFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, weight: torch.Tensor, ids: torch.Tensor, comm: TPComm, vocab_start: int):
@@ -351,7 +363,7 @@ class _EmbedFn(torch.autograd.Function):
             if mine.numel():
                 d = d * mine.unsqueeze(-1).to(d.dtype)
                 local = local.clamp(0, weight.shape[0] - 1)
-            g.index_add_(0, local, d.to(g.dtype))
+            embedding_grad_accumulate(g, local, d)
         return None, None, None, None
 
 

@@ -422,3 +422,35 @@ def test_attention_merge_kernel():
         close(acc_o, ro, 1e-4, 1e-4, "merged out")
         assert torch.equal(torch.isinf(acc_l).cpu(), torch.isinf(rl))      # rows no block touched keep -inf
         close(torch.nan_to_num(acc_l, neginf=0.0), torch.nan_to_num(rl, neginf=0.0), 1e-4, 1e-4, "merged lse")
+
+
+def test_forward_backward_is_bit_reproducible():
+    """Two runs of the same forward + backward give identical log-probs and identical gradient
+    buffers: no result depends on the order in which atomics land (attention, norms with and without
+    per-head norm, embedding gradient, LM head)."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    kw = dict(num_layers=2, hidden_size=512, ffn_hidden_size=1024, num_attention_heads=4, num_query_groups=2,
+              vocab_size=2048, kv_channels=128, max_position_embeddings=4096, add_qkv_bias=True, qk_layernorm=True)
+    lens = [700, 1523, 300]
+    meta = PackedMeta.from_lengths(lens, DEV)
+    t = sum(lens)
+    g = torch.Generator(device=DEV).manual_seed(2)
+    ids = torch.randint(0, 2048, (t,), device=DEV, generator=g)
+    labels = torch.randint(0, 2048, (t,), device=DEV, generator=g)
+    m = DistributedDataParallel(GPTModel(TransformerConfig(**kw), device=DEV, seed=4))
+    opt = DistributedOptimizer(m.buffers, lr=1e-3, clip_grad=1.0)
+    runs = []
+    for _ in range(2):
+        m.zero_grad_buffer()
+        lp, _ = m.module.forward_logprob(ids, labels, meta)
+        lp.sum().backward()
+        norm = opt.compute_grad_norm().clone() if hasattr(opt, "compute_grad_norm") else None
+        torch.cuda.synchronize()
+        runs.append((lp.detach().clone(), [b.grad_data.clone() for b in m.buffers], opt._sumsq.clone()))
+    assert torch.equal(runs[0][0], runs[1][0])
+    for a, b in zip(runs[0][1], runs[1][1]):
+        assert torch.equal(a, b)
+    assert torch.equal(runs[0][2], runs[1][2])           # sum of squares of the gradients
