@@ -121,3 +121,31 @@ def test_flash_attention_bwd_tcgen05(nh, nkv, interleaved, causal, monkeypatch):
     dqkv_r = ops.attn_varlen_bwd(dout.cpu(), qkv.cpu(), out_r, lse_r, lay, cu, max(lens), causal=causal)
     torch.testing.assert_close(dqkv.float().cpu(), dqkv_r.float(), rtol=3e-2, atol=5e-2)
     torch.testing.assert_close(dqkv.float(), dqkv_m.float(), rtol=3e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_block_attention_with_separate_kv(causal):
+    """The block primitives of ring attention (queries against a separate K/V block, log-sum-exp of the
+    whole row given to the backward) against the fp32 formulation: ragged query and key lengths,
+    non-causal and bottom-right causal."""
+    from mindspeed_rl_b200 import ops
+    torch.manual_seed(21)
+    nh, nkv, hd = 6, 2, 128
+    ql, kl = [130, 64, 500], [257, 64, 900]
+    cu_q = torch.tensor([0] + list(torch.tensor(ql).cumsum(0)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(kl).cumsum(0)), dtype=torch.int32)
+    tq, tk = int(cu_q[-1]), int(cu_k[-1])
+    q = (0.7 * torch.randn(tq, nh, hd, device="cuda")).bfloat16()
+    k = (0.7 * torch.randn(tk, nkv, hd, device="cuda")).bfloat16()
+    v = (0.7 * torch.randn(tk, nkv, hd, device="cuda")).bfloat16()
+    do = (0.5 * torch.randn(tq, nh * hd, device="cuda")).bfloat16()
+    out, lse = ops.attn_kv_fwd(q, k, v, cu_q.cuda(), cu_k.cuda(), max(ql), causal)
+    dq, dk, dv = ops.attn_kv_bwd(do, q, k, v, out, lse, cu_q.cuda(), cu_k.cuda(), max(ql), max(kl), causal)
+    G.check_status(torch.device("cuda", torch.cuda.current_device()), "block attention")
+    out_r, lse_r = ops.attn_kv_fwd(q.cpu().float(), k.cpu().float(), v.cpu().float(), cu_q, cu_k, max(ql), causal)
+    dq_r, dk_r, dv_r = ops.attn_kv_bwd(do.cpu().float(), q.cpu().float(), k.cpu().float(), v.cpu().float(), out_r, lse_r,
+                                       cu_q, cu_k, max(ql), max(kl), causal)
+    torch.testing.assert_close(out.float().cpu(), out_r, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(lse.cpu(), lse_r, rtol=1e-2, atol=2e-2)
+    for a, b in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
+        torch.testing.assert_close(a.float().cpu(), b, rtol=3e-2, atol=5e-2)
