@@ -71,3 +71,36 @@ def test_moe_layer_kernels(t, k, e, h, f):
     dw_r = M.moe_slot_dot(dout.cpu().float(), y.cpu().float(), cplan)
     torch.testing.assert_close(dw.cpu(), dw_r, rtol=2e-2, atol=2e-2)
     G.check_status(torch.device("cuda", torch.cuda.current_device()), "grouped gemm")
+
+
+def test_peer_memory_dispatch_single_rank():
+    """The peer-memory dispatch / combine kernels with a team of one rank (its own arena is the only
+    "peer"): slab layout, rows, tile table and the weighted combine agree with the plan / permute /
+    combine path."""
+    from mindspeed_rl_b200.parallel.moe_dispatch import P2PDispatcher
+    from mindspeed_rl_b200.parallel.symm import SymmetricArena
+    torch.manual_seed(3)
+    t, k, e, h = 517, 4, 8, 256
+    rows = M.max_rows(t * k, e)
+    arena = SymmetricArena(P2PDispatcher.bytes_needed(1, e, h, rows) + (4 << 20))
+    try:
+        disp = P2PDispatcher(arena, [0], e, h, rows)
+        x = torch.randn(t, h, device="cuda").bfloat16()
+        idx = torch.stack([torch.randperm(e, device="cuda")[:k] for _ in range(t)])
+        w = torch.rand(t, k, device="cuda")
+        route = disp.dispatch(x, idx)
+        plan = M.moe_plan(idx, e)
+        used = int(plan.offsets[-1])
+        assert route.plan.counts.tolist() == plan.counts.tolist()
+        assert route.plan.offsets.tolist() == plan.offsets.tolist()
+        assert route.plan.tile_expert.tolist() == plan.tile_expert.tolist()
+        assert route.slot_row.tolist() == plan.pos.tolist() and int(route.slot_rank.max()) == 0
+        assert torch.equal(disp.slab[:used], M.moe_permute(x, plan)[:used])
+        disp.out_slab.copy_(disp.slab * 2)                    # stand-in for the expert MLP
+        out, kept = disp.combine(route, w, keep_rows=True)
+        ref = M.moe_combine(M.moe_permute(x, plan) * 2, plan, w)
+        torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+        assert torch.equal(kept.view(t, k, h)[5, 2], disp.out_slab[int(plan.pos[5 * k + 2])])
+        arena.check()
+    finally:
+        arena.close()
