@@ -65,3 +65,8 @@ def test_ring_attention_context_parallel():
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_arena_setup_failure_is_collective():
     _run("arena_fallback", 2)
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_tp_model_with_fused_linears():
+    _run("tp_model", 2)
