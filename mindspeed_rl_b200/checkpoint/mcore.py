@@ -44,8 +44,13 @@ def rank_dir_name(tp_rank: int, pp_rank: int = 0, pp_size: int = 1, ep_rank: int
 
 
 def _coords(ps) -> Tuple[int, int, int, int, int, int]:
-    return (ps.rank_in("tp"), ps.rank_in("pp"), ps.size("pp"), ps.rank_in("ep"), ps.size("ep"),
-            ps.rank_in("dp_cp"))
+    # With expert parallelism the EP ranks are carved out of the data-parallel group and each holds
+    # different experts: every EP rank has a directory of its own, and inside it the replicas are
+    # told apart by the expert-data-parallel rank (replica 0 writes the model file, as Megatron does
+    # with ``expert_data_parallel_rank == 0``).  Dense-only models use the data-parallel rank.
+    ep_size = ps.size("ep")
+    replica = ps.rank_in("edp") if ep_size > 1 else ps.rank_in("dp_cp")
+    return (ps.rank_in("tp"), ps.rank_in("pp"), ps.size("pp"), ps.rank_in("ep"), ep_size, replica)
 
 
 def read_tracker(root: str) -> Tuple[Optional[int], bool]:

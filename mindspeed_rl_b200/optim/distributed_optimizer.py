@@ -93,7 +93,7 @@ class DistributedOptimizer:
         self.state: List[Dict[str, torch.Tensor]] = []
         self.norm_duplicate_filter = norm_duplicate_filter
         for buf in buffers:
-            s, e = buf.shard_range(dp_rank)
+            s, e = self._range(buf)
             shard = buf.param_data[s:e]
             if offload_to_host:
                 pin = shard.is_cuda
@@ -130,7 +130,7 @@ class DistributedOptimizer:
         if self._rep_ranges is None:
             out = []
             for bi, buf in enumerate(self.buffers):
-                s, e = buf.shard_range(self.dp_rank)
+                s, e = self._range(buf)
                 for p, slot in zip(buf.params, buf.slots):
                     if slot.name.endswith(self._REPLICATED_SUFFIXES) or getattr(p, "tp_replicated", False):
                         lo, hi = max(slot.start, s), min(slot.start + slot.numel, e)
@@ -139,8 +139,14 @@ class DistributedOptimizer:
             self._rep_ranges = out
         return self._rep_ranges
 
+    def _range(self, buf: ParamAndGradBuffer) -> Tuple[int, int]:
+        """This rank's shard of ``buf``: buffers that carry their own replica group (expert
+        weights: expert-data-parallel ranks) are sharded over it, the others over ``dp_group``."""
+        own = getattr(buf, "group", None) is not None or getattr(buf, "is_expert", False)
+        return buf.shard_range(buf.dp_rank if own else self.dp_rank)
+
     def _grad_shard(self, buf: ParamAndGradBuffer) -> torch.Tensor:
-        s, e = buf.shard_range(self.dp_rank)
+        s, e = self._range(buf)
         return buf.grad_data[s:e]
 
     def compute_grad_norm(self) -> torch.Tensor:
@@ -155,7 +161,10 @@ class DistributedOptimizer:
                 ops.sumsq_accumulate(self.buffers[bi].grad_data[lo:hi], dup)
             self._sumsq -= dup
         if dist.is_available() and dist.is_initialized():
-            if self.dp_group is not None and buffers_dp(self.buffers) > 1:
+            # every element of every shard (dense: one shard per DP rank; experts: one shard per
+            # (EP, expert-DP) rank, all inside the DP group) is counted exactly once by this sum
+            if self.dp_group is not None and dist.get_world_size(self.dp_group) > 1 and (
+                    buffers_dp(self.buffers) > 1 or any(getattr(b, "is_expert", False) for b in self.buffers)):
                 dist.all_reduce(self._sumsq, group=self.dp_group)
             if self.mp_group is not None and dist.get_world_size(self.mp_group) > 1:
                 dist.all_reduce(self._sumsq, group=self.mp_group)
@@ -168,7 +177,7 @@ class DistributedOptimizer:
         self.compute_grad_norm()
         ops.clip_coefficient(self._sumsq, float(self.clip_grad or 0.0), 1.0, self._coef, self._norm)
         for buf, st in zip(self.buffers, self.state):
-            s, e = buf.shard_range(self.dp_rank)
+            s, e = self._range(buf)
             grad = buf.grad_data[s:e]
             p16 = buf.param_data[s:e] if buf.param_dtype != torch.float32 else None
             if self.offload_to_host and grad.is_cuda:
@@ -263,7 +272,7 @@ class DistributedOptimizer:
     def reload_model_params(self) -> None:
         """Refresh the fp32 master weights from the (externally modified) model parameters."""
         for buf, st in zip(self.buffers, self.state):
-            s, e = buf.shard_range(self.dp_rank)
+            s, e = self._range(buf)
             if "master_lo" in st:
                 st["master_lo"].zero_()
             else:
@@ -275,7 +284,7 @@ class DistributedOptimizer:
         for buf, st in zip(self.buffers, self.state):
             d = {k: v.detach().cpu() for k, v in st.items() if k != "master_lo"}
             if "master_lo" in st:        # checkpoints always carry full fp32 master weights
-                s, e = buf.shard_range(self.dp_rank)
+                s, e = self._range(buf)
                 d["master"] = self.compose_master(buf.param_data[s:e], st["master_lo"]).cpu()
             shards.append(d)
         return dict(step=self.step_count, param_groups=self.param_groups, shards=shards)
@@ -285,7 +294,7 @@ class DistributedOptimizer:
         for buf, st, src in zip(self.buffers, self.state, sd["shards"]):
             for k in st:
                 if k == "master_lo":
-                    s, e = buf.shard_range(self.dp_rank)
+                    s, e = self._range(buf)
                     self.split_master(src["master"].to(st[k].device), buf.param_data[s:e], st[k])
                 else:
                     st[k].copy_(src[k])

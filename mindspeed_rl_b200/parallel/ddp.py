@@ -39,7 +39,17 @@ class ParamAndGradBuffer:
     ALIGN = 64  # elements; keeps every parameter 128-byte aligned in bf16
 
     def __init__(self, named_params: Iterable[Tuple[str, nn.Parameter]], dp_size: int = 1,
-                 grad_dtype: Optional[torch.dtype] = None, bucket_numel: Optional[int] = None):
+                 grad_dtype: Optional[torch.dtype] = None, bucket_numel: Optional[int] = None,
+                 group=None, dp_rank: Optional[int] = None, grad_scale: Optional[float] = None,
+                 is_expert: bool = False):
+        # ``group`` / ``dp_rank`` / ``dp_size``: the ranks that hold replicas of these parameters.
+        # Dense parameters are replicated over the whole data-parallel group; expert parameters
+        # only over the expert-data-parallel group (the EP ranks hold different experts), but their
+        # gradient average still runs over all data-parallel ranks' tokens (``grad_scale``).
+        self.group, self.is_expert = group, is_expert
+        self.dp_rank = dp_rank if dp_rank is not None else (
+            dist.get_rank(group) if (group is not None and dist.is_initialized()) else 0)
+        self.grad_scale = grad_scale if grad_scale is not None else 1.0 / max(dp_size, 1)
         params = [(n, p) for n, p in named_params if p.requires_grad]
         if not params:
             raise ValueError("no trainable parameters")
@@ -81,17 +91,13 @@ class ParamAndGradBuffer:
             p.grad = None
             self.params.append(p)
         self.by_name: Dict[str, ParamSlot] = {s.name: s for s in self.slots}
-        # bucket boundaries (multiples of ALIGN*dp) used by the overlapped reduce / gather
-        self.buckets: List[Tuple[int, int]] = []
-        step = _align(bucket_numel or self.numel, self.ALIGN * max(dp_size, 1))
-        for s in range(0, self.numel, step):
-            self.buckets.append((s, min(self.numel, s + step)))
 
     # ------------------------------------------------------------------------------------------
     def zero_grad(self) -> None:
         self.grad_data.zero_()
 
-    def shard_range(self, dp_rank: int) -> Tuple[int, int]:
+    def shard_range(self, dp_rank: Optional[int] = None) -> Tuple[int, int]:
+        dp_rank = self.dp_rank if dp_rank is None else dp_rank
         per = self.numel // self.dp_size
         return dp_rank * per, (dp_rank + 1) * per
 
@@ -106,18 +112,24 @@ class ParamAndGradBuffer:
     def reduce_grads(self, group=None, average: bool = True, to_shards: bool = False) -> None:
         """Sum (or average) gradients over DP.  ``to_shards=True`` leaves each rank with the
         reduced values of its own shard only (reduce-scatter, distributed optimizer)."""
+        group = self.group if self.group is not None else group
+        scale = self.grad_scale if average else 1.0
         if self.dp_size == 1 or group is None:
+            if self.is_expert and scale != 1.0:   # experts without replicas still average over the DP tokens
+                self.grad_data.mul_(scale)
             return
         if self.arena is not None and to_shards:
             # one pull kernel: sum the peers' copies of my shard, scale, write my slice in place
             per = self.numel // self.dp_size
             r = dist.get_rank(group)
+            # the ranks reach this point after unequal work (differently packed micro-batches):
+            # a stream-ordered collective lines them up before the bounded device barrier
+            self.arena.align(group)
             self.arena.reduce_scatter(self.grad_data, self.grad_data[r * per:(r + 1) * per],
-                                      scale=1.0 / self.dp_size if average else 1.0,
-                                      ranks=self.arena.team_ranks(group))
+                                      scale=scale, ranks=self.arena.team_ranks(group))
             return
-        if average:
-            self.grad_data.div_(self.dp_size)
+        if scale != 1.0:
+            self.grad_data.mul_(scale)
         if to_shards:
             per = self.numel // self.dp_size
             r = dist.get_rank(group)
@@ -128,6 +140,7 @@ class ParamAndGradBuffer:
 
     def gather_params(self, group=None) -> None:
         """All-gather the parameter shards updated by the distributed optimizer."""
+        group = self.group if self.group is not None else group
         if self.dp_size == 1 or group is None:
             return
         per = self.numel // self.dp_size
@@ -139,25 +152,54 @@ class ParamAndGradBuffer:
                                     group=group)
 
 
+def is_expert_param(name: str, p: nn.Parameter) -> bool:
+    """Routed-expert weights: different on every expert-parallel rank (shared experts and the
+    router are ordinary replicated parameters)."""
+    return bool(getattr(p, "is_expert", False)) or ".experts." in f".{name}"
+
+
+def expert_replica_groups(ps, cfg) -> dict:
+    """Keyword arguments of :class:`DistributedDataParallel` that describe where the replicas of
+    this rank's experts live (empty for dense models and without expert parallelism)."""
+    if not getattr(cfg, "is_moe", False) or ps.size("ep") <= 1:
+        return {}
+    return dict(expert_dp_group=ps.group("edp"), expert_dp_size=ps.size("edp"), expert_dp_rank=ps.rank_in("edp"))
+
+
 class DistributedDataParallel(nn.Module):
     """Wraps a model chunk, owns its :class:`ParamAndGradBuffer` and the DP group."""
 
     def __init__(self, module: nn.Module, dp_group=None, dp_size: int = 1,
-                 grad_in_fp32: bool = False, bucket_numel: Optional[int] = None):
+                 grad_in_fp32: bool = False, bucket_numel: Optional[int] = None,
+                 expert_dp_group=None, expert_dp_size: Optional[int] = None,
+                 expert_dp_rank: Optional[int] = None):
+        """``expert_dp_*`` describe the ranks that hold replicas of this rank's experts (Megatron's
+        expert-data-parallel group).  When given, the expert weights get a buffer of their own that
+        is reduced, sharded (optimizer state) and gathered over that group only; without it
+        every parameter is treated as replicated over ``dp_group``."""
         super().__init__()
         self.module = module
         self.dp_group, self.dp_size = dp_group, dp_size
         fp32_params = [(n, p) for n, p in module.named_parameters()
                        if p.requires_grad and p.dtype == torch.float32 and
                        next(module.parameters()).dtype != torch.float32]
+        split_experts = expert_dp_size is not None and expert_dp_size != dp_size
+        experts = [(n, p) for n, p in module.named_parameters()
+                   if p.requires_grad and split_experts and is_expert_param(n, p)]
+        taken = [q for _, q in fp32_params] + [q for _, q in experts]
         main = [(n, p) for n, p in module.named_parameters()
-                if p.requires_grad and not any(p is q for _, q in fp32_params)]
+                if p.requires_grad and not any(p is q for q in taken)]
         self.buffers: List[ParamAndGradBuffer] = []
+        gdt = torch.float32 if grad_in_fp32 else None
         if main:
-            self.buffers.append(ParamAndGradBuffer(main, dp_size, torch.float32 if grad_in_fp32 else None,
-                                                   bucket_numel))
+            self.buffers.append(ParamAndGradBuffer(main, dp_size, gdt, bucket_numel, group=dp_group))
+        if experts:
+            self.buffers.append(ParamAndGradBuffer(
+                experts, expert_dp_size, gdt, bucket_numel, group=expert_dp_group, dp_rank=expert_dp_rank,
+                grad_scale=1.0 / max(dp_size, 1), is_expert=True))
         if fp32_params:  # e.g. the fp32 value head
-            self.buffers.append(ParamAndGradBuffer(fp32_params, dp_size, torch.float32, bucket_numel))
+            self.buffers.append(ParamAndGradBuffer(fp32_params, dp_size, torch.float32, bucket_numel,
+                                                   group=dp_group))
 
     def forward(self, *a, **kw):
         return self.module(*a, **kw)

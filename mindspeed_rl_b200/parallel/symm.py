@@ -178,6 +178,19 @@ class SymmetricArena:
                                               ep, ctypes.c_uint(mask), _lib.ptr(self.status), _lib.stream()),
                    "symm_barrier")
 
+    def align(self, group=None) -> None:
+        """Line the ranks of ``group`` up on the current stream with a one-element library
+        all-reduce.  The device barrier's wait is bounded (about two seconds); where it follows
+        long, unequal work (differently packed micro-batches, rollout replicas that finish at
+        different times) a healthy straggler must not run it out, so such call sites align first:
+        the all-reduce has the process group's (long) timeout, and the barrier kernel behind it
+        starts on every rank within microseconds of the others."""
+        if self.world == 1 or not dist.is_initialized():
+            return
+        if getattr(self, "_align_token", None) is None:
+            self._align_token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        dist.all_reduce(self._align_token, group=group if group is not None else self.group)
+
     def check(self) -> None:
         """Synchronise and raise if a barrier gave up waiting for a peer."""
         code = int(self.status.item())

@@ -334,10 +334,23 @@ class Resharder:
         buf = self._main_buffer()
         if self.buffer is None:
             self.buffer = torch.empty(plan.nbytes, dtype=torch.uint8, device=self.device)
+        timed = self.device.type == "cuda"
+        if timed:
+            # device time of the move itself (entry barrier + copy-plan kernel + exit barrier); the
+            # events are read by ``device_ms`` after the caller's next synchronisation
+            self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self._events[0].record()
         if self._use_arena():
+            # the ranks arrive from the update stage at different times: line them up before the
+            # bounded device barrier (outside the timed interval: it is waiting, not resharding)
+            self.arena.align()
+            if timed:
+                self._events[0].record()
             self.arena.copy_plan(self._plan_dev[0], self._plan_dev[1], self.buffer, sync=True)
         else:
             self._gathered_copy(plan, buf)
+        if timed:
+            self._events[1].record()
         self.last_bytes = sum(d[3] * d[4] for d in plan.desc)
         return weights_from_buffer(self.infer_cfg, self.infer_tp, self.infer_state.rank_in("tp"), plan, self.buffer,
                                    buf.param_dtype, self._moe_builder(core) if self.cfg.is_moe else None)
@@ -359,6 +372,14 @@ class Resharder:
         else:
             sources = {ps.rank: local}
         execute_plan_torch(plan, sources, self.buffer)
+
+    def device_ms(self) -> Optional[float]:
+        """Device time of the last :meth:`reshard` in milliseconds (synchronises on its end event)."""
+        ev = getattr(self, "_events", None)
+        if ev is None:
+            return None
+        ev[1].synchronize()
+        return float(ev[0].elapsed_time(ev[1]))
 
     def release(self) -> None:
         self.buffer = None

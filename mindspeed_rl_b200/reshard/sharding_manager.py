@@ -122,7 +122,17 @@ class ShardingManager:
             return 256
         free, total = torch.cuda.mem_get_info(dev)
         budget = min(free - (2 << 30), int(total * self.gpu_memory_utilization))
-        return max(int(budget // self.engine.kv_bytes_per_block()), 16)
+        blocks = max(int(budget // self.engine.kv_bytes_per_block()), 16)
+        comm = getattr(self.engine, "comm", None)
+        if comm is not None and comm.world_size > 1 and comm.group is not None:
+            # the ranks of a rollout TP group run identical schedulers: they must agree on the cache
+            # size (free memory differs a little from GPU to GPU), so all take the smallest
+            import torch.distributed as dist
+
+            t = torch.tensor([blocks], dtype=torch.int64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=comm.group)
+            blocks = int(t.item())
+        return blocks
 
     def enter_infer_mode(self) -> float:
         t0 = time.time()
@@ -139,11 +149,16 @@ class ShardingManager:
         else:
             weights = alias_rollout_weights(self.core)
         self.engine.runner.bind_weights(weights)
+        self._sync()
+        t_kv = time.time()
         self.engine.init_cache(self._kv_blocks())
         self._sync()
         self.mode = "infer"
         dt = time.time() - t0
         self.last_timing["enter_infer"] = dt
+        self.last_timing["kv_cache_alloc"] = time.time() - t_kv
+        ms = self.resharder.device_ms() if self.resharder is not None else None
+        self.last_timing["reshard_device"] = (ms or 0.0) / 1e3
         return dt
 
     def exit_infer_mode(self) -> float:

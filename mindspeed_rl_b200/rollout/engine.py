@@ -139,7 +139,10 @@ class LLMEngine(BaseInferEngine):
     # ---- request API ---------------------------------------------------------------------------
     def add_request(self, request_id: Optional[str], prompt_token_ids: Seq_[int],
                     params: SamplingParams) -> str:
-        rid = request_id or uuid.uuid4().hex[:12]
+        # generated ids must be the same on every rank of a rollout TP group (they seed the
+        # per-request sampling stream, and the ranks must draw the same tokens): a counter, not a uuid
+        self._request_counter = getattr(self, "_request_counter", 0) + 1
+        rid = request_id or f"req-{self._request_counter:010d}"
         if rid in self.scheduler.groups:
             raise ValueError(f"request id {rid} is already in flight")
         lead = Sequence(rid, list(int(t) for t in prompt_token_ids), params, sample_index=0)

@@ -22,7 +22,7 @@ from ..models.gpt import GPTModel
 from ..models.training_engine import TrainingEngine
 from ..models.transformer_config import TransformerConfig
 from ..optim.distributed_optimizer import DistributedOptimizer, OptimizerParamScheduler
-from ..parallel.ddp import DistributedDataParallel
+from ..parallel.ddp import DistributedDataParallel, expert_replica_groups
 from ..parallel.state import get_parallel_state
 from ..parallel.tp_comm import TPComm
 from ..reshard.sharding_manager import ShardingManager
@@ -161,7 +161,8 @@ class IntegratedWorker(BaseWorker):
         dp = ps.size("dp_cp")
         self._maybe_init_arena(core, bool(ac.accumulate_allreduce_grads_in_fp32))
         self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
-                                             grad_in_fp32=bool(ac.accumulate_allreduce_grads_in_fp32))
+                                             grad_in_fp32=bool(ac.accumulate_allreduce_grads_in_fp32),
+                                             **expert_replica_groups(ps, tcfg))
         self._maybe_attach_fused_tp()
         self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(ac.sequence_parallel))
         self.optimizer = DistributedOptimizer(
@@ -263,8 +264,17 @@ class IntegratedWorker(BaseWorker):
         """Reshard into the rollout engine and keep it resident (DAPO re-sampling rounds)."""
         if self.sharding_manager.mode != "infer":
             self._t_enter = self.sharding_manager.enter_infer_mode()
-            self.update_metrics("timing/resharding_enter_infer", [self._t_enter])
+            self._report_enter_infer()
             self._held_infer = True
+
+    def _report_enter_infer(self) -> None:
+        """``timing/resharding_enter_infer`` is the host time of the whole transition; the weight
+        move alone (device time of barrier + copy-plan kernel + barrier) and the KV-cache
+        allocation are logged beside it."""
+        t = self.sharding_manager.last_timing
+        self.update_metrics("timing/resharding_enter_infer", [self._t_enter])
+        self.update_metrics("timing/resharding_device", [t.get("reshard_device", 0.0)])
+        self.update_metrics("timing/resharding_kv_cache", [t.get("kv_cache_alloc", 0.0)])
 
     def exit_infer_mode(self) -> None:
         if self.sharding_manager.mode == "infer":
@@ -279,7 +289,7 @@ class IntegratedWorker(BaseWorker):
         held = getattr(self, "_held_infer", False)
         if not held:
             self._t_enter = self.sharding_manager.enter_infer_mode()
-            self.update_metrics("timing/resharding_enter_infer", [self._t_enter])
+            self._report_enter_infer()
         main_td = self.td
         if getattr(self, "sampling_td", None) is not None:
             self.td = self.sampling_td          # rollouts of DAPO go to the sampling dock

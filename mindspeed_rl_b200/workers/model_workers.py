@@ -16,7 +16,7 @@ from ..models.gpt import GPTModel
 from ..models.training_engine import TrainingEngine
 from ..models.transformer_config import TransformerConfig
 from ..optim.distributed_optimizer import DistributedOptimizer, OptimizerParamScheduler
-from ..parallel.ddp import DistributedDataParallel
+from ..parallel.ddp import DistributedDataParallel, expert_replica_groups
 from ..parallel.tp_comm import TPComm
 from ..reshard.sharding_manager import GradBufferOffloader, ParamOffloader
 from .base_worker import BaseWorker, profiled_stage
@@ -65,7 +65,8 @@ class _ModelWorker(BaseWorker):
                       max_packing_token_size=rl.max_packing_token_size)
         if self.trainable:
             self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
-                                                 grad_in_fp32=bool(mc.accumulate_allreduce_grads_in_fp32))
+                                                 grad_in_fp32=bool(mc.accumulate_allreduce_grads_in_fp32),
+                                                 **expert_replica_groups(ps, tcfg))
             self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(mc.sequence_parallel))
             self.optimizer = DistributedOptimizer(
                 self.model.buffers, lr=mc.lr or 1e-6, betas=(mc.adam_beta1, mc.adam_beta2),

@@ -180,6 +180,73 @@ def test_expert_parallel_matches_single_rank():
     run_distributed(_ep_worker, 2)
 
 
+def _ep_optimizer_worker(rank, world, tmp):
+    """One optimizer step with EP=2 (experts differ per rank, dense weights are replicated) equals the
+    step of a single-rank model that holds all experts and sees both ranks' tokens; a checkpoint
+    written afterwards reloads into a fresh model with every rank's own experts."""
+    from mindspeed_rl_b200.checkpoint.mcore import load_checkpoint, save_checkpoint
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel, expert_replica_groups
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel, set_parallel_state
+    kw = dict(num_layers=1, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, params_dtype=torch.float32, max_position_embeddings=64, num_experts=4,
+              moe_router_topk=2, moe_ffn_hidden_size=16, norm_topk_prob=True, moe_aux_loss_coeff=0.0)
+    set_parallel_state(None)
+    full = DistributedDataParallel(GPTModel(TransformerConfig(**kw), device="cpu", seed=3))
+    full_opt = DistributedOptimizer(full.buffers, lr=1e-2, clip_grad=1e9, weight_decay=0.0)
+    ps = initialize_model_parallel(expert_model_parallel_size=world)
+    cfg = TransformerConfig(expert_model_parallel_size=world, **kw)
+
+    def shard(sd):
+        per, out = 4 // world, dict(sd)
+        for k in list(out):
+            if k.endswith("experts.weight1"):
+                out[k] = out[k].view(32, 4, 32)[:, rank * per:(rank + 1) * per].reshape(32, -1).contiguous()
+            if k.endswith("experts.weight2"):
+                out[k] = out[k].view(4, 16, 32)[rank * per:(rank + 1) * per].reshape(-1, 32).contiguous()
+        return out
+
+    core = GPTModel(cfg, device="cpu", seed=3)
+    core.load_state_dict(shard({k: v.clone() for k, v in full.module.state_dict().items()}))
+    model = DistributedDataParallel(core, ps.group("dp_cp"), world, **expert_replica_groups(ps, cfg))
+    assert any(b.is_expert for b in model.buffers) and len(model.buffers) == 2
+    opt = DistributedOptimizer(model.buffers, lr=1e-2, clip_grad=1e9, weight_decay=0.0, dp_group=ps.group("dp_cp"),
+                               dp_rank=ps.rank_in("dp_cp"), model_parallel_group=ps.group("mp"))
+    meta = PackedMeta.from_lengths([9], "cpu")
+    for r in range(world):                      # the single-rank model sees every rank's tokens
+        g = torch.Generator().manual_seed(100 + r)
+        ids, labels = torch.randint(0, 64, (9,), generator=g), torch.randint(0, 64, (9,), generator=g)
+        (full.module.forward_logprob(ids, labels, meta)[0].sum() / world).backward()
+        if r == rank:
+            core.forward_logprob(ids, labels, meta)[0].sum().backward()
+    for p in list(full.module.parameters()) + list(core.parameters()):
+        if p.grad is not None:                  # layers accumulate into main_grad themselves
+            p.main_grad.add_(p.grad)
+    model.finish_grad_sync(to_shards=True)
+    _, norm, _ = opt.step()
+    _, full_norm, _ = full_opt.step()
+    assert torch.allclose(norm, full_norm, rtol=1e-4), (norm, full_norm)
+    want = shard(full.module.state_dict())
+    for k, v in core.state_dict().items():
+        assert torch.allclose(v, want[k], atol=2e-5), (k, (v - want[k]).abs().max())
+    mine = core.decoder.layers[0].mlp.experts.weight2.detach().clone()
+    both = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(both, mine)
+    assert not torch.allclose(both[0], both[1]), "the expert-parallel ranks ended up with identical experts"
+    # checkpoint round trip: every EP rank has a directory of its own
+    save_checkpoint(tmp, 1, core, opt, None, ps, None)
+    fresh = GPTModel(cfg, device="cpu", seed=77)
+    load_checkpoint(tmp, fresh, None, None, ps, None)
+    for k, v in fresh.state_dict().items():
+        assert torch.equal(v, core.state_dict()[k]), k
+
+
+def test_expert_parallel_optimizer_step_and_checkpoint(tmp_path):
+    run_distributed(_ep_optimizer_worker, 2, str(tmp_path))
+
+
 def _ep_rollout_worker(rank, world):
     """Expert-parallel rollout engines step together: a rank with fewer (or no) requests keeps
     joining the token exchanges, and every rank's greedy tokens equal the single-rank model's."""
