@@ -59,7 +59,7 @@ def parse_args():
     ap.add_argument("--min-response", type=int, default=256)
     ap.add_argument("--max-response", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (development only)")
-    ap.add_argument("--pack-tokens", type=int, default=8192, help="token budget of one training micro-batch")
+    ap.add_argument("--pack-tokens", type=int, default=8192, help="token budget of one training micro-batch per TP rank (multiplied by the training TP size)")
     ap.add_argument("--fwd-pack-tokens", type=int, default=32768,
                     help="token budget of one forward-only micro-batch (reference log-probs)")
     ap.add_argument("--eager", action="store_true", help="disable CUDA-graph decode")
@@ -175,6 +175,9 @@ def main():
     parallelism = (f"train tp{train_tp} x dp{world // train_tp} (sequence parallel) -> "
                    f"rollout tp{infer_tp} x dp{world // infer_tp}") if train_tp > 1 else f"dp{world}"
 
+    # micro-batches grow with the training TP size: the activations of a packed micro-batch are
+    # sharded over the TP group, so per-GPU memory and per-GPU GEMM sizes stay those of TP1
+    pack_tokens, fwd_pack_tokens = args.pack_tokens * train_tp, args.fwd_pack_tokens * train_tp
     n, gbs = args.samples, args.prompts_per_gpu * world
     max_len = args.prompt_len + args.max_response
     catalogue = load_model_catalogue([args.model])
@@ -196,8 +199,8 @@ def main():
         n_samples_per_prompt=n, mini_batch_size=gbs, epochs=1, clip_ratio=0.2, init_kl_coef=0.001,
         kl_penalty="low_var_kl", adv_estimator="group_norm", verifier_function=["contains_token_7"],
         verifier_weight=[1.0], actor_resource={"num_gpus": world}, use_remove_padding=True,
-        use_dynamic_bsz=True, max_packing_token_size=args.pack_tokens,
-        ref_max_packing_token_size=args.fwd_pack_tokens, log_max_throughput=False))
+        use_dynamic_bsz=True, max_packing_token_size=pack_tokens,
+        ref_max_packing_token_size=fwd_pack_tokens, log_max_throughput=False))
     gen = GenerateConfig(dict(
         infer_tensor_parallel_size=infer_tp, max_num_seqs=args.prompts_per_gpu * n * infer_tp,
         max_model_len=max_len, max_num_batched_tokens=8192, kv_block_size=16, enable_prefix_caching=False,
@@ -262,6 +265,7 @@ def main():
                        "prompt_len": args.prompt_len, "response_len": f"uniform {args.min_response}-{args.max_response}",
                        "mean_response_len": mean("response_length/mean"), "parallelism": parallelism,
                        "layout": args.layout, "train_tp": train_tp, "rollout_tp": infer_tp,
+                       "update_micro_batch_tokens": pack_tokens, "forward_micro_batch_tokens": fwd_pack_tokens,
                        "tokens_per_sec_per_gpu": value / world, "layers_not_recomputed": args.keep_layers,
                        "peak_device_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1) if on_gpu else None,
                        "l2": "working set >> L2: every pass streams >= 3.8 GB of weights per GPU",

@@ -115,6 +115,15 @@ def validate_rl_args(actor_config: MegatronConfig, ref_config: Optional[Megatron
     _require(actor_config.bf16 is not False and gen.dtype == "bfloat16",
              "bf16 must be true and generate_config.dtype must be bfloat16")
 
+    # -- tied embeddings need the first and last pipeline stage to share one gradient --------
+    for name, cfg in (("Actor", actor_config), ("Reference", ref_config), ("Critic", critic_config)):
+        if cfg is None:
+            continue
+        tied = getattr(cfg, "untie_embeddings_and_output_weights", True) is False
+        _require(not (tied and (cfg.pipeline_model_parallel_size or 1) > 1),
+                 f"{name}: tied input/output embeddings are not supported with pipeline_model_parallel_size > 1 "
+                 f"(the two stages' copies would drift apart); set untie_embeddings_and_output_weights: true")
+
     # -- co-location ----------------------------------------------------------------------
     if rl.use_integrated_worker:
         _require(rl.reference_resource is None,

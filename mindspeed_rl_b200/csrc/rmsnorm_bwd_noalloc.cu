@@ -139,6 +139,21 @@ int msrl_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const
     return (int)cudaErrorInvalidValue;
   }
   if (rows == 0) return (int)cudaSuccess;
+  // The kernels move 128-bit vectors through these buffers: a missing or misaligned pointer must
+  // become an error code here, not a fault on the GPU.
+  const struct { const void* p; const char* name; bool required; } ptrs[] = {
+      {dy, "dy", true}, {x, "x", true}, {w, "w", true}, {dx, "dx", true}, {dres, "dres", false}};
+  for (const auto& a : ptrs) {
+    if (a.p == nullptr ? a.required : (reinterpret_cast<uintptr_t>(a.p) & 15) != 0) {
+      std::fprintf(stderr, "msrl_rmsnorm_bwd_noalloc: %s must be %s16-byte aligned device memory\n", a.name,
+                   a.required ? "non-null, " : "null or ");
+      return (int)cudaErrorInvalidValue;
+    }
+  }
+  if (rstd == nullptr || (reinterpret_cast<uintptr_t>(rstd) & 3) != 0) {
+    std::fprintf(stderr, "msrl_rmsnorm_bwd_noalloc: rstd must be non-null fp32 device memory\n");
+    return (int)cudaErrorInvalidValue;
+  }
   float* scratch = nullptr;
   cudaError_t e = scratch_for_current_device(&scratch);
   if (e != cudaSuccess) {
@@ -163,6 +178,7 @@ int msrl_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const
     noalloc_rmsnorm_bwd_kernel<4><<<nb, kThreads, 0, stream>>>(dyb, xb, wb, rstd, rb, dxb, scratch, rows, H);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
+  if (dw_f32 == nullptr && dw_bf16 == nullptr) return (int)cudaSuccess;   // weight gradient not wanted
   noalloc_reduce_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, nb, H, dw_f32,
                                                             static_cast<__nv_bfloat16*>(dw_bf16), accumulate);
   return (int)cudaGetLastError();

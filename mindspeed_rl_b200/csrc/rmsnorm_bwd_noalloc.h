@@ -45,7 +45,9 @@ extern "C" {
 // dx[rows, H] = d loss / d x of y = x * rsqrt(mean(x^2) + eps) * w   (+ dres when dres != NULL)
 // dw (+)= sum over rows of dy * x * rstd, written to dw_f32 and/or dw_bf16 (either may be NULL);
 // accumulate != 0 adds to the existing contents.  All matrices are contiguous bf16 [rows, H];
-// rstd is the fp32 [rows] vector produced by the forward.  Returns a cudaError_t as int.
+// rstd is the fp32 [rows] vector produced by the forward.  dy, x, w, dx (and dres when given) must
+// be 16-byte aligned; a NULL or misaligned one is refused with cudaErrorInvalidValue before
+// anything is launched.  With both dw outputs NULL only dx is computed.  Returns a cudaError_t as int.
 int msrl_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
                              const void* dres, void* dx, float* dw_f32, void* dw_bf16, int accumulate,
                              long long rows, int H, cudaStream_t stream);

@@ -65,11 +65,9 @@ def accum_wgrad(p: torch.Tensor, dy: torch.Tensor, x: torch.Tensor) -> None:
     """``grad(p) += dy^T x`` for a weight ``p [out, in]``."""
     if not p.requires_grad:
         return
-    g = grad_buffer(p)
-    if g.dtype == dy.dtype:
-        g.addmm_(dy.t(), x)
-    else:
-        g.add_(torch.matmul(dy.t(), x).to(g.dtype))
+    from ..ops.gemm import linear_wgrad_
+
+    linear_wgrad_(grad_buffer(p), dy, x)
 
 
 def accum_vec(p: torch.Tensor, v: torch.Tensor) -> None:
@@ -510,7 +508,9 @@ class GPTModel(nn.Module):
         h = self.hidden_states(ids, meta)
         x, _, _ = ops.rmsnorm_fwd(h, self.decoder.final_layernorm.weight, self.cfg.norm_epsilon,
                                   want_rstd=False)
-        return torch.matmul(self.comm.gather_seq(x), self.output_weight().t())
+        from ..ops.gemm import linear_fwd
+
+        return linear_fwd(self.comm.gather_seq(x), self.output_weight())
 
 
 class _NormFn(torch.autograd.Function):

@@ -32,6 +32,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .. import ops
+from ..ops import gemm as _gemm
 from ..parallel.state import get_parallel_state
 
 
@@ -257,9 +258,9 @@ class MoELayer(nn.Module):
         out = out.to(x.dtype)
         shared_ctx = None
         if self.shared_experts is not None:
-            gu = torch.matmul(x, self.shared_experts.linear_fc1.weight.t())
+            gu = _gemm.linear_fwd(x, self.shared_experts.linear_fc1.weight)
             act = ops.swiglu_fwd(gu)
-            out = out + comm.reduce_out(torch.matmul(act, self.shared_experts.linear_fc2.weight.t()))
+            out = out + comm.reduce_out(_gemm.linear_fwd(act, self.shared_experts.linear_fc2.weight))
             shared_ctx = (gu, act) if keep else None
         if not keep:
             return out, None
@@ -269,9 +270,9 @@ class MoELayer(nn.Module):
 
     # ---- all experts on this rank: dispatch plan + grouped GEMMs, no host round trip in the forward ----
     def _shared_fwd(self, x, comm, keep):
-        gu = torch.matmul(x, self.shared_experts.linear_fc1.weight.t())
+        gu = _gemm.linear_fwd(x, self.shared_experts.linear_fc1.weight)
         act = ops.swiglu_fwd(gu)
-        y = comm.reduce_out(torch.matmul(act, self.shared_experts.linear_fc2.weight.t()))
+        y = comm.reduce_out(_gemm.linear_fwd(act, self.shared_experts.linear_fc2.weight))
         return y, ((gu, act) if keep else None)
 
     def _forward_local(self, x, xr, top_p, top_idx, aux, comm, keep):
@@ -402,10 +403,10 @@ class MoELayer(nn.Module):
             gu, act = ctx["shared"]
             fc1, fc2 = self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight
             d_sh = comm.reduce_out_bwd(dout)
-            dact = torch.matmul(d_sh, fc2)
+            dact = _gemm.linear_dgrad(d_sh, fc2)
             accum_wgrad(fc2, d_sh, act)
             dgu = ops.swiglu_bwd(gu, dact)
-            dx += torch.matmul(dgu, fc1).float()
+            dx += _gemm.linear_dgrad(dgu, fc1).float()
             accum_wgrad(fc1, dgu, x)
         return dx.to(x.dtype)
 
@@ -442,10 +443,10 @@ class MoELayer(nn.Module):
             gu, act = ctx["shared"]
             fc1, fc2 = self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight
             d_sh = comm.reduce_out_bwd(dout)
-            dact = torch.matmul(d_sh, fc2)
+            dact = _gemm.linear_dgrad(d_sh, fc2)
             accum_wgrad(fc2, d_sh, act)
             dgu = ops.swiglu_bwd(gu, dact)
-            dx += torch.matmul(dgu, fc1).float()
+            dx += _gemm.linear_dgrad(dgu, fc1).float()
             accum_wgrad(fc1, dgu, x)
         return dx.to(x.dtype)
 

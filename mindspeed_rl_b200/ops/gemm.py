@@ -8,6 +8,7 @@ value means one of their bounded waits expired and the result must be discarded.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -61,6 +62,85 @@ def gemm_bf16_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] =
                                         c_ll(out.stride(0)), c_int(m), c_int(n), c_int(k),
                                         ptr(_status_word(a.device)), stream()), "gemm_bf16_tn")
     return out
+
+
+_OUT_MODES = {"store": 0, "acc_f32": 1, "acc_bf16": 2}
+
+
+def _ok_matrix(t: torch.Tensor) -> bool:
+    return (t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
+            and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0)
+
+
+def pair_usable(*tensors: torch.Tensor) -> bool:
+    """True when the CTA-pair GEMM can take these bf16 matrices as operands (CUDA, contiguous rows,
+    16-byte aligned, leading dimensions and row lengths multiples of 8)."""
+    return all(_ok_matrix(t) and t.shape[1] % 8 == 0 for t in tensors) and _lib.available()
+
+
+def gemm_pair(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+              out: Optional[torch.Tensor] = None, mode: str = "store",
+              bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense GEMM on CTA pairs (``csrc/gemm2cta_tcgen05.cu``): ``C[M, N] (+)= op(a) @ op(b).T``.
+
+    ``a`` is ``[M, K]`` (``a_mn=False``) or stored transposed ``[K, M]`` (``a_mn=True``); ``b`` is
+    ``[N, K]`` or stored transposed ``[K, N]``.  ``mode``: ``store`` (bf16 result, optional bias
+    ``[N]``), ``acc_f32`` / ``acc_bf16`` (add into an existing fp32 / bf16 ``out``)."""
+    m, k = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    n = b.shape[1] if b_mn else b.shape[0]
+    if (b.shape[0] if b_mn else b.shape[1]) != k:
+        raise ValueError("inner dimensions do not match")
+    if out is None:
+        if mode != "store":
+            raise ValueError("accumulating modes need an output tensor")
+        out = torch.empty(m, n, device=a.device, dtype=torch.bfloat16)
+    check(_lib.load().msrl_gemm_pair_bf16(
+        ptr(a), c_ll(a.stride(0)), c_int(int(a_mn)), ptr(b), c_ll(b.stride(0)), c_int(int(b_mn)), ptr(out),
+        c_ll(out.stride(0)), c_int(_OUT_MODES[mode]), ptr(bias), c_int(m), c_int(n), c_int(k),
+        ptr(_status_word(a.device)), stream()), "gemm_pair_bf16")
+    return out
+
+
+def pair_enabled() -> bool:
+    """``MSRL_PAIR_GEMM=0`` sends the dense linears to the library GEMM (comparison runs)."""
+    return os.environ.get("MSRL_PAIR_GEMM", "1") == "1"
+
+
+def _pair_pays(m: int, n: int) -> bool:
+    """The pair kernel works on 256 x 256 output tiles, one pair of SMs each: below a few dozen
+    tiles (decode-sized problems) most of the machine would idle, so those go to the library."""
+    return pair_enabled() and ((m + 255) // 256) * ((n + 255) // 256) >= 48
+
+
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [T, K] @ w [N, K].T (+ bias)``: the forward of every dense linear."""
+    if (x.is_cuda and _pair_pays(x.shape[0], w.shape[0]) and pair_usable(x, w) and _lib.use_kernels(x, w)
+            and (bias is None or bias.dtype == torch.bfloat16)):
+        return gemm_pair(x, w, bias=bias)
+    y = torch.matmul(x, w.t())
+    if bias is not None:
+        y += bias
+    return y
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``dy [T, N] @ w [N, K]``: input gradient of a linear, reading ``w`` where it is."""
+    if dy.is_cuda and _pair_pays(dy.shape[0], w.shape[1]) and pair_usable(dy, w) and _lib.use_kernels(dy, w):
+        return gemm_pair(dy, w, b_mn=True)
+    return torch.matmul(dy, w)
+
+
+def linear_wgrad_(grad: torch.Tensor, dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """``grad [N, K] += dy [T, N].T @ x [T, K]`` in place (``grad`` bf16 or fp32)."""
+    if (dy.is_cuda and _pair_pays(dy.shape[1], x.shape[1]) and pair_usable(dy, x) and _lib.use_kernels(dy, x, grad)
+            and grad.dim() == 2 and grad.stride(1) == 1 and dy.shape[0] % 8 == 0 and grad.stride(0) % 8 == 0
+            and grad.dtype in (torch.float32, torch.bfloat16) and grad.data_ptr() % 16 == 0):
+        gemm_pair(dy, x, a_mn=True, b_mn=True, out=grad,
+                  mode="acc_f32" if grad.dtype == torch.float32 else "acc_bf16")
+        return grad
+    if grad.dtype == dy.dtype:
+        return grad.addmm_(dy.t(), x)
+    return grad.add_(torch.matmul(dy.t(), x))
 
 
 def lmhead_stats(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, inv_temp: float,

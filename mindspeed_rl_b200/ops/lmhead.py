@@ -73,7 +73,7 @@ def lmhead_logprob_fwd(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, i
             return logp, ent, lse
         for s in range(0, t, chunk):
             e = min(t, s + chunk)
-            z = torch.matmul(h[s:e], w.t())                      # [c, V] bf16
+            z = _gemm.linear_fwd(h[s:e], w)                      # [c, V] bf16
             st = torch.empty(e - s, 4, device=dev, dtype=torch.float32)
             check(L.msrl_logprob_stats(ptr(z), c_ll(z.stride(0)), c_ll(e - s), c_int(v),
                                        c_int(vocab_offset), ptr(labels[s:e]), c_float(inv_temp),
@@ -123,18 +123,18 @@ def lmhead_logprob_bwd(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, l
         L = _lib.load()
         for s in range(0, t, chunk):
             e = min(t, s + chunk)
-            z = torch.matmul(h[s:e], w.t())
+            z = _gemm.linear_fwd(h[s:e], w)
             check(L.msrl_logprob_bwd(ptr(z), c_ll(z.stride(0)), c_ll(e - s), c_int(v),
                                      c_int(vocab_offset), ptr(labels[s:e]), c_float(inv_temp),
                                      ptr(lse[s:e]), ptr(entropy[s:e]) if dent is not None else None,
                                      ptr(dlogp[s:e]), ptr(dent[s:e]) if dent is not None else None,
                                      stream()), "logprob_bwd")
-            torch.matmul(z, w, out=dh[s:e])
+            if _gemm._pair_pays(e - s, h.shape[1]) and _gemm.pair_usable(z, w):
+                _gemm.gemm_pair(z, w, b_mn=True, out=dh[s:e])
+            else:
+                torch.matmul(z, w, out=dh[s:e])
             if dw_accum is not None:
-                if dw_accum.dtype == z.dtype:
-                    dw_accum.addmm_(z.t(), h[s:e])
-                else:
-                    dw_accum.add_(torch.matmul(z.t(), h[s:e]).to(dw_accum.dtype))
+                _gemm.linear_wgrad_(dw_accum, z, h[s:e])
         return dh
     for s in range(0, t, chunk):
         e = min(t, s + chunk)

@@ -81,8 +81,36 @@ def case_gemm(small: bool, iters: int):
         out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
         ms = timeit(lambda: G.gemm_bf16_tn(a, b, out), iters)
         report(f"gemm_tcgen05 {m}x{n}x{k}", ms, flops=2.0 * m * n * k)
+        ms = timeit(lambda: G.gemm_pair(a, b, out=out), iters)
+        report(f"gemm_pair fwd   {m}x{n}x{k}", ms, flops=2.0 * m * n * k, note="cta_group::2, 256x256 tiles")
         ms = timeit(lambda: torch.matmul(a, b.t(), out=out), iters)
         report(f"gemm_cublas  {m}x{n}x{k}", ms, flops=2.0 * m * n * k, note="library baseline")
+    G.check_status("cuda")
+
+
+def case_gemm_pair(small: bool, iters: int):
+    """The three GEMMs of a linear layer (forward, data gradient, weight gradient) on the CTA-pair
+    kernel against the library calls they replace, on the 7B shapes at 8192 tokens."""
+    t = 1024 if small else 8192
+    layers = [("qkv", 4608, 3584), ("proj", 3584, 3584), ("fc1", 37888, 3584), ("fc2", 3584, 18944)]
+    if small:
+        layers = [("small", 2048, 1024)]
+    for name, n, k in layers:
+        x = torch.randn(t, k, device="cuda").bfloat16()
+        w = (0.02 * torch.randn(n, k, device="cuda")).bfloat16()
+        dy = torch.randn(t, n, device="cuda").bfloat16()
+        y = torch.empty(t, n, device="cuda", dtype=torch.bfloat16)
+        dx = torch.empty(t, k, device="cuda", dtype=torch.bfloat16)
+        g32 = torch.zeros(n, k, device="cuda", dtype=torch.float32)
+        g16 = torch.zeros(n, k, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * t * n * k
+        report(f"pair fwd   {name} T={t}", timeit(lambda: G.gemm_pair(x, w, out=y), iters), flops=fl)
+        report(f"cublas fwd {name} T={t}", timeit(lambda: torch.matmul(x, w.t(), out=y), iters), flops=fl)
+        report(f"pair dgrad   {name} T={t}", timeit(lambda: G.gemm_pair(dy, w, b_mn=True, out=dx), iters), flops=fl)
+        report(f"cublas dgrad {name} T={t}", timeit(lambda: torch.matmul(dy, w, out=dx), iters), flops=fl)
+        report(f"pair wgrad(bf16 acc) {name} T={t}", timeit(lambda: G.linear_wgrad_(g16, dy, x), iters), flops=fl)
+        report(f"cublas wgrad(bf16 addmm_) {name} T={t}", timeit(lambda: g16.addmm_(dy.t(), x), iters), flops=fl)
+        report(f"pair wgrad(fp32 acc) {name} T={t}", timeit(lambda: G.linear_wgrad_(g32, dy, x), iters), flops=fl)
     G.check_status("cuda")
 
 
@@ -252,7 +280,7 @@ def case_moe(small: bool, iters: int):
     G.check_status("cuda", "grouped gemm")
 
 
-CASES = {"moe": case_moe, "gemm": case_gemm, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
+CASES = {"moe": case_moe, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
          "elementwise": case_elementwise, "adam": case_adam, "sampler": case_sampler,
          "fused_single": case_fused_single}
 

@@ -17,6 +17,8 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from ..ops.gemm import linear_dgrad, linear_fwd
+
 
 class TPComm:
     def __init__(self, group=None, sequence_parallel: bool = False, world_size: Optional[int] = None,
@@ -79,7 +81,7 @@ class TPComm:
             y, xg = self.fused.ag_gemm(x, w)
         else:
             xg = self.gather_seq(x)
-            y = torch.matmul(xg, w.t())
+            return linear_fwd(xg, w, bias), xg
         if bias is not None:
             y += bias
         return y, xg
@@ -88,7 +90,7 @@ class TPComm:
         """``reduce_out(a @ w.T)``."""
         if self._fused_ok(a) and self.fused.fits_rs(a, w):
             return self.fused.gemm_rs(a, w)
-        return self.reduce_out(torch.matmul(a, w.t()))
+        return self.reduce_out(linear_fwd(a, w))
 
     def column_linear_bwd(self, dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """Input gradient of :meth:`column_linear`: ``gather_seq_bwd(dy @ w)``."""
@@ -96,7 +98,7 @@ class TPComm:
             wt = self.fused.transposed(w)
             if self.fused.fits_rs(dy, wt):
                 return self.fused.gemm_rs(dy, wt)
-        return self.gather_seq_bwd(torch.matmul(dy, w))
+        return self.gather_seq_bwd(linear_dgrad(dy, w))
 
     def row_linear_bwd(self, dout: torch.Tensor, w: torch.Tensor):
         """Input gradient of :meth:`row_linear`: ``(reduce_out_bwd(dout) @ w, reduce_out_bwd(dout))``
@@ -106,7 +108,7 @@ class TPComm:
             if self.fused.fits_ag(dout, wt):
                 return self.fused.ag_gemm(dout, wt)
         d_full = self.reduce_out_bwd(dout)
-        return torch.matmul(d_full, w), d_full
+        return linear_dgrad(d_full, w), d_full
 
 
 NO_TP = TPComm()

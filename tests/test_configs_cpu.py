@@ -53,3 +53,13 @@ def test_dataset_and_tool_configs_load():
     for p in glob.glob(os.path.join(ROOT, "tools", "*.yaml")):
         tools = build_tool_map(yaml.safe_load(open(p))["tools"])
         assert len(tools) == 1
+
+
+def test_tied_embeddings_with_pipeline_parallel_are_refused():
+    """The first and the last pipeline stage would each train a copy of the tied matrix and nothing
+    keeps the copies equal, so the validator stops such a run."""
+    cfg = compose("grpo_tiny_cpu", None, ["actor_config.pipeline_model_parallel_size=2",
+                                          "rl_config.actor_resource.num_gpus=2",
+                                          "+model.tiny_qwen2.untie_embeddings_and_output_weights=false"])
+    with pytest.raises(ValueError, match="tied input/output embeddings"):
+        parse_training_config(cfg)

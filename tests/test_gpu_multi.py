@@ -16,10 +16,18 @@ def _n_gpus() -> int:
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as s:          # two test runs on one box must not meet on a fixed port
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def _run(case: str, nproc: int, timeout: int = 600) -> str:
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29617",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "multi_gpu_cases.py"), case]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
     out = res.stdout + res.stderr

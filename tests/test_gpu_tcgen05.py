@@ -17,10 +17,55 @@ def test_gemm_bf16_tn(m, n, k):
     b = (torch.randn(n, k, device=DEV) * 0.5).bfloat16()
     c = G.gemm_bf16_tn(a, b)
     G.check_status(DEV)
-    ref = a.float() @ b.float().t()
+    _assert_close(c, a.float() @ b.float().t(), k)
+
+
+def _assert_close(c, ref, k, scale=0.25):
+    """bf16 output of an fp32-accumulated product of entries of magnitude ~``sqrt(scale)``: the result
+    has standard deviation ``scale * sqrt(k)`` and carries one bf16 rounding (relative 2^-8), so the
+    band is 1 % relative plus 1 % of that standard deviation."""
     err = (c.float() - ref).abs()
-    tol = 2e-2 * ref.abs() + 0.25
+    tol = 1e-2 * ref.abs() + 1e-2 * scale * (k ** 0.5)
     assert bool((err <= tol).all()), f"max err {err.max().item()} ref max {ref.abs().max().item()}"
+
+
+PAIR_SHAPES = [(256, 256, 64), (128, 256, 128), (300, 520, 192), (1024, 3584, 3584), (77, 1000, 4096), (640, 72, 200)]
+
+
+@pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
+def test_gemm_pair_forward_and_bias(m, n, k):
+    torch.manual_seed(0)
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    b = (torch.randn(n, k, device=DEV) * 0.5).bfloat16()
+    bias = torch.randn(n, device=DEV).bfloat16()
+    ref = a.float() @ b.float().t()
+    _assert_close(G.gemm_pair(a, b), ref, k)
+    _assert_close(G.gemm_pair(a, b, bias=bias), ref + bias.float(), k)
+    G.check_status(DEV)
+
+
+@pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
+def test_gemm_pair_data_and_weight_gradient_forms(m, n, k):
+    """``dy @ w`` with ``w`` as an MN-major B operand, and ``dy.T @ x`` with both operands MN-major,
+    stored and accumulated into fp32 / bf16 gradient buffers."""
+    torch.manual_seed(1)
+    dy = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()         # [T, N_lin] : reduction over its columns
+    w = (torch.randn(k, n, device=DEV) * 0.5).bfloat16()          # [N_lin, K_lin] read as stored
+    _assert_close(G.gemm_pair(dy, w, b_mn=True), dy.float() @ w.float(), k)
+    t = k                                                          # tokens are the reduction of the weight gradient
+    t8 = (t + 7) // 8 * 8
+    g_out = (torch.randn(t8, m // 8 * 8 or 8, device=DEV) * 0.5).bfloat16()
+    x_in = (torch.randn(t8, n // 8 * 8 or 8, device=DEV) * 0.5).bfloat16()
+    ref = g_out.float().t() @ x_in.float()
+    _assert_close(G.gemm_pair(g_out, x_in, a_mn=True, b_mn=True), ref, t8)
+    for dt in (torch.float32, torch.bfloat16):
+        base = torch.randn(ref.shape, device=DEV).to(dt)
+        grad = base.clone()
+        mode = "acc_f32" if dt == torch.float32 else "acc_bf16"
+        G.gemm_pair(g_out, x_in, a_mn=True, b_mn=True, out=grad, mode=mode)
+        G.gemm_pair(g_out, x_in, a_mn=True, b_mn=True, out=grad, mode=mode)
+        _assert_close(grad, base.float() + 2 * ref, 4 * t8)
+    G.check_status(DEV)
 
 
 @pytest.mark.parametrize("t,v,h", [(200, 1000, 256), (513, 5000, 896)])

@@ -55,6 +55,35 @@ def _run_case(fn, rows, h, with_residual, seed):
     assert bool((err_dx <= 3e-2 + 3e-2 * dx_ref.float().abs()).all()), err_dx.max()
     err_dw = (dw - dw_ref).abs()
     assert bool((err_dw <= 5e-2 * rows ** 0.5 + 2e-2 * dw_ref.abs()).all()), err_dw.max()
+    # the same outputs from the textbook fp32 formulation (not only from the sibling kernel)
+    dx32, dw32 = _fp32_rmsnorm_bwd(dy, x, w, rstd, dres)
+    err = (dx.float() - dx32).abs()
+    assert bool((err <= 3e-2 + 3e-2 * dx32.abs()).all()), err.max()
+    err = (dw - (0.5 + dw32)).abs()
+    assert bool((err <= 5e-2 * rows ** 0.5 + 2e-2 * dw32.abs()).all()), err.max()
+    # accumulate = 0 overwrites whatever the output held, and the bf16 gradient output works alone
+    dw_over = torch.full((h,), 123.0, device=dev, dtype=torch.float32)
+    dw16 = torch.full((h,), 7.0, device=dev, dtype=torch.bfloat16)
+    dx2 = torch.empty_like(x)
+    assert fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr() if dres is not None else None,
+              dx2.data_ptr(), dw_over.data_ptr(), None, 0, rows, h, stream) == 0
+    assert fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr() if dres is not None else None,
+              dx2.data_ptr(), None, dw16.data_ptr(), 0, rows, h, stream) == 0
+    torch.cuda.synchronize()
+    tol = 5e-2 * rows ** 0.5 + 2e-2 * dw32.abs()
+    assert bool(((dw_over - dw32).abs() <= tol).all())
+    assert bool(((dw16.float() - dw32).abs() <= tol + 1e-2 * dw32.abs()).all())
+    assert torch.equal(dx2, dx)
+
+
+def _fp32_rmsnorm_bwd(dy, x, w, rstd, dres):
+    """y = x * rstd * w  ->  dx = rstd * (g - x_hat * mean(g * x_hat)) (+ dres), dw = sum_rows dy * x_hat."""
+    xf, g = x.float(), dy.float() * w.float()
+    x_hat = xf * rstd.float().unsqueeze(-1)
+    dx = rstd.float().unsqueeze(-1) * (g - x_hat * (g * x_hat).mean(-1, keepdim=True))
+    if dres is not None:
+        dx = dx + dres.float()
+    return dx, (dy.float() * x_hat).sum(0)
 
 
 def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
@@ -73,3 +102,23 @@ def test_noalloc_rmsnorm_bwd_rejects_oversized_rows():
     rc = fn(t.data_ptr(), t.data_ptr(), t[0].data_ptr(), r.data_ptr(), None, t.data_ptr(), None, None, 0, 2, h,
             torch.cuda.current_stream().cuda_stream)
     assert rc == CUDA_ERROR_INVALID_VALUE
+
+
+def test_noalloc_rmsnorm_bwd_rejects_bad_pointers_without_launching():
+    """A null or misaligned buffer is answered with an error code on the host; nothing runs on the GPU."""
+    fn = _entry()
+    h = 1024
+    t = torch.zeros(4, h + 8, device="cuda", dtype=torch.bfloat16)
+    good, odd = t[:, :h], t.view(-1)[1:1 + 2 * h].view(2, h)       # `odd` starts 2 bytes past a 16-byte boundary
+    r = torch.ones(4, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(h, device="cuda")
+    args = lambda dy, x, dx: (dy, x, w.data_ptr(), r.data_ptr(), None, dx, dw.data_ptr(), None, 0, 2, h, st)
+    p = good.data_ptr()
+    assert fn(*args(None, p, p)) == CUDA_ERROR_INVALID_VALUE
+    assert fn(*args(p, None, p)) == CUDA_ERROR_INVALID_VALUE
+    assert fn(*args(p, p, None)) == CUDA_ERROR_INVALID_VALUE
+    assert fn(*args(odd.data_ptr(), p, p)) == CUDA_ERROR_INVALID_VALUE
+    assert fn(p, p, w.data_ptr(), None, None, p, dw.data_ptr(), None, 0, 2, h, st) == CUDA_ERROR_INVALID_VALUE
+    torch.cuda.synchronize()
