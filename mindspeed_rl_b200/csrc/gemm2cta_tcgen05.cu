@@ -25,6 +25,7 @@
 // backend (mindspeed_rl/config_cls/megatron_config.py:365-368 selects their fused Ascend forms).
 #include <cuda.h>
 #include <cudaTypedefs.h>
+#include <stdlib.h>
 
 #include "tcgen05_utils.cuh"
 
@@ -51,6 +52,7 @@ struct Params {
   long long ldc;
   const __nv_bfloat16* bias;   // OUT_BF16 only, may be null
   int* error;
+  int flags;                   // experiment switches (MSRL_G2_FLAGS): 1 fence per stage, 4 no stores, bits 4-7 ring depth
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -79,6 +81,13 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
+}
+// One lane of a fully active warp.  The compiler knows that code under this predicate runs in a
+// single thread of a converged warp, which lets it keep descriptors and addresses in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void umma_pair(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
@@ -111,6 +120,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int total_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int RS = ((p.flags >> 4) & 15) ? ((p.flags >> 4) & 15) : STAGES;   // ring depth in use
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -136,42 +146,46 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (warp == 4) {
     // ---------------- TMA producer (one thread in each CTA) ----------------
-    if (lane == 0) {
+    {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
         const int mt = tile % m_tiles, nt = tile / m_tiles;
         const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN + (int)rank * HN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t use = it / STAGES;
+          const int s = it % RS;
+          const uint32_t use = it / RS;
           if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, p.error, ERR_EMPTY)) {
             ok = false;
             break;
           }
-          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
           const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
           unsigned char* sa = smem + (size_t)s * STAGE_BYTES;
-          if (A_MN) {
+          if (elect_one()) {
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+            if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < HM / 64; ++i)       // [64 k rows x 64 m columns] blocks of 8 KiB
-              tma_load_2d_pair(sa + i * 8192, &map_a, bar, m0 + i * 64, kb * BK);
-          } else {
-            tma_load_2d_pair(sa, &map_a, bar, kb * BK, m0);
-          }
-          if (B_MN) {
+              for (int i = 0; i < HM / 64; ++i)       // [64 k rows x 64 m columns] blocks of 8 KiB
+                tma_load_2d_pair(sa + i * 8192, &map_a, bar, m0 + i * 64, kb * BK);
+            } else {
+              tma_load_2d_pair(sa, &map_a, bar, kb * BK, m0);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int i = 0; i < HN / 64; ++i)
-              tma_load_2d_pair(sa + SMEM_A + i * 8192, &map_b, bar, n0 + i * 64, kb * BK);
-          } else {
-            tma_load_2d_pair(sa + SMEM_A, &map_b, bar, kb * BK, n0);
+              for (int i = 0; i < HN / 64; ++i)
+                tma_load_2d_pair(sa + SMEM_A + i * 8192, &map_b, bar, n0 + i * 64, kb * BK);
+            } else {
+              tma_load_2d_pair(sa + SMEM_A, &map_b, bar, kb * BK, n0);
+            }
           }
+          __syncwarp();
         }
       }
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer (leader CTA only) ----------------
-    if (lane == 0 && rank == 0) {
+    // the whole warp walks the loop and waits on the barriers; one elected lane issues
+    if (rank == 0) {
       constexpr uint32_t idesc = idesc_pair(A_MN, B_MN);
       uint32_t it = 0, local = 0;
       bool ok = true;
@@ -184,21 +198,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         const uint32_t tmem_acc = tmem + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, p.error, ERR_FULL);
+          const int s = it % RS;
+          ok = mbar_wait(&full_bar[s], (it / RS) & 1, p.error, ERR_FULL);
           if (!ok) break;
-          fence_after();
+          // the operands were written by TMA and are ordered by the barrier itself; a tcgen05 fence
+          // here would only hold back the MMA issue
+          if (p.flags & 1) fence_after();
           const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
           const uint32_t b_addr = a_addr + SMEM_A;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = A_MN ? desc_sw128(a_addr + k * 2048, 8192, 1024) : desc_sw128(a_addr + k * 32, 16, 1024);
-            const uint64_t db = B_MN ? desc_sw128(b_addr + k * 2048, 8192, 1024) : desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_pair(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t da = A_MN ? desc_sw128(a_addr + k * 2048, 8192, 1024) : desc_sw128(a_addr + k * 32, 16, 1024);
+              const uint64_t db = B_MN ? desc_sw128(b_addr + k * 2048, 8192, 1024) : desc_sw128(b_addr + k * 32, 16, 1024);
+              umma_pair(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            commit_pair(&empty_bar[s]);   // the slot is free in both CTAs once these MMAs have read it
           }
-          commit_pair(&empty_bar[s]);     // the slot is free in both CTAs once these MMAs have read it
+          __syncwarp();
         }
-        commit_pair(&acc_full[buf]);      // accumulator complete (or abandoned) for both epilogues
+        if (elect_one()) commit_pair(&acc_full[buf]);   // accumulator complete (or abandoned) for both epilogues
+        __syncwarp();
       }
     }
   } else {
@@ -240,7 +260,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               *reinterpret_cast<bf16x8*>(patch + lane * EPI_PITCH + h * 64 + q * 16) = pack8(v + q * 8);
           }
           __syncwarp();
-          if (vec_ok) {
+          if (p.flags & 4) {
+          } else if (vec_ok) {
             // whole 128-byte row segments per store instruction: 4 rows x 8 lanes x 16 bytes
             const int col = n0 + c * 64 + (lane & 7) * 8;
 #pragma unroll
@@ -397,6 +418,8 @@ MSRL_API int msrl_gemm_pair_bf16(const void* A, long long lda, int a_mn, const v
   p.ldc = ldc;
   p.bias = out_mode == g2::OUT_BF16 ? reinterpret_cast<const __nv_bfloat16*>(bias) : nullptr;
   p.error = error;
+  static const int flags = [] { const char* e = getenv("MSRL_G2_FLAGS"); return e ? atoi(e) : 0; }();
+  p.flags = flags;
   if (!a_mn && !b_mn && out_mode == g2::OUT_BF16) return g2::launch<false, false, g2::OUT_BF16>(A, lda, B, ldb, p, st);
   if (!a_mn && b_mn && out_mode == g2::OUT_BF16) return g2::launch<false, true, g2::OUT_BF16>(A, lda, B, ldb, p, st);
   if (a_mn && b_mn && out_mode == g2::OUT_BF16) return g2::launch<true, true, g2::OUT_BF16>(A, lda, B, ldb, p, st);

@@ -49,6 +49,10 @@ def timeit(fn: Callable[[], None], iters: int, warmup: int = 3) -> float:
         _flush.zero_()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # a short busy kernel ahead of the start event lets the host finish enqueueing `fn` while the
+        # GPU is still occupied, so the interval holds device time only (as in a training step, where
+        # launches run ahead of the GPU), not the host's launch latency
+        torch.cuda._sleep(200_000)
         e0.record()
         fn()
         e1.record()
@@ -111,6 +115,30 @@ def case_gemm_pair(small: bool, iters: int):
         report(f"pair wgrad(bf16 acc) {name} T={t}", timeit(lambda: G.linear_wgrad_(g16, dy, x), iters), flops=fl)
         report(f"cublas wgrad(bf16 addmm_) {name} T={t}", timeit(lambda: g16.addmm_(dy.t(), x), iters), flops=fl)
         report(f"pair wgrad(fp32 acc) {name} T={t}", timeit(lambda: G.linear_wgrad_(g32, dy, x), iters), flops=fl)
+    G.check_status("cuda")
+
+
+def case_gemm_pair_prof(small: bool, iters: int):
+    """One mid-size forward GEMM on the CTA-pair kernel (operands and output together larger than
+    L2, 8 full waves of tiles): the case meant for a profiler capture of that kernel."""
+    m, n, k = 4096, 9472, 3584
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    report(f"gemm_pair fwd {m}x{n}x{k}", timeit(lambda: G.gemm_pair(a, b, out=out), iters, warmup=1), flops=2.0 * m * n * k)
+    G.check_status("cuda")
+
+
+def case_gemm_pair_ksweep(small: bool, iters: int):
+    """Time of the CTA-pair kernel against the reduction length at a fixed 8-wave output: the slope
+    is the main-loop rate, the intercept the fixed cost per launch and per tile."""
+    m, n = 4096, 9472
+    for k in (256, 512, 1024, 2048, 3584, 7168):
+        a = torch.randn(m, k, device="cuda").bfloat16()
+        b = torch.randn(n, k, device="cuda").bfloat16()
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        report(f"gemm_pair fwd {m}x{n}x{k}", timeit(lambda: G.gemm_pair(a, b, out=out), iters), flops=2.0 * m * n * k)
+        report(f"cublas    fwd {m}x{n}x{k}", timeit(lambda: torch.matmul(a, b.t(), out=out), iters), flops=2.0 * m * n * k)
     G.check_status("cuda")
 
 
@@ -280,7 +308,7 @@ def case_moe(small: bool, iters: int):
     G.check_status("cuda", "grouped gemm")
 
 
-CASES = {"moe": case_moe, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
+CASES = {"moe": case_moe, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_pair_prof": case_gemm_pair_prof, "gemm_pair_ksweep": case_gemm_pair_ksweep, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
          "elementwise": case_elementwise, "adam": case_adam, "sampler": case_sampler,
          "fused_single": case_fused_single}
 

@@ -133,10 +133,16 @@ class ParallelState:
             "ep": layout.expert_groups("ep"), "edp": layout.expert_groups("edp"),
             "etp": layout.expert_groups("etp"),
         }
+        # "all": every rank of this model.  When that is the whole job the default group serves.
+        inited = dist.is_available() and dist.is_initialized()
+        covers_job = inited and rank_offset == 0 and layout.world_size == dist.get_world_size()
+        specs["all"] = [list(range(layout.world_size))]
         for name, glist in specs.items():
             for members in glist:
                 g = None
-                if create_groups and dist.is_available() and dist.is_initialized() and len(members) > 1:
+                if name == "all" and (covers_job or not inited):
+                    pass
+                elif create_groups and dist.is_available() and dist.is_initialized() and len(members) > 1:
                     kw = {"timeout": timeout} if timeout is not None else {}
                     g = dist.new_group([m + rank_offset for m in members], backend=backend, **kw)
                 if rank in members:

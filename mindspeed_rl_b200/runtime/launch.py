@@ -19,8 +19,9 @@ import torch.distributed as dist
 
 from ..config import load_config, parse_training_config
 from ..obs.loggers import Loggers
-from ..parallel.state import initialize_model_parallel
+from ..parallel.state import initialize_model_parallel, set_parallel_state
 from ..utils.tokenizer import get_tokenizer
+from .placement import plan_placement
 from .worker_group import SPMDWorkerGroup, spmd_init
 
 logger = Loggers("launch")
@@ -78,13 +79,25 @@ def build_data_iter(actor_config, rl_config, tokenizer, consumed_train_samples: 
     return loader if reiterable else InfiniteLoader(loader)
 
 
+def role_parallel_state(mc, placement, role: str, rank: int):
+    """Process groups of a role that owns a rank range of its own.  Collective over the whole job:
+    every rank creates every group, the members keep them."""
+    from ..parallel.state import ParallelState, RankLayout
+
+    ranks = placement.of(role)
+    layout = RankLayout(len(ranks), mc.tensor_model_parallel_size or 1, mc.pipeline_model_parallel_size or 1,
+                        mc.context_parallel_size or 1, mc.expert_model_parallel_size or 1,
+                        bool(mc.moe_tp_extend_ep), bool(mc.use_tp_pp_dp_mapping))
+    return ParallelState(layout, rank - ranks[0], rank_offset=ranks[0])
+
+
 def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
     """``algorithm`` in {"grpo", "dapo", "ppo"}; returns the metric history of rank 0."""
     from ..trainer.dapo_trainer import RayDAPOTrainer
     from ..trainer.grpo_trainer import RayGRPOTrainer
     from ..trainer.ppo_trainer import RayPPOTrainer
     from ..workers.integrated_worker import IntegratedWorker
-    from ..workers.model_workers import CriticWorker, RewardWorker
+    from ..workers.model_workers import CriticWorker, ReferenceWorker, RewardWorker
     from ..workers.rule_reward import RuleReward
 
     cfg = parse_training_config(config, with_critic=(algorithm == "ppo"))
@@ -92,30 +105,50 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
     apply_runtime_env(rl_config.runtime_env_path)
     os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
     spmd_init(actor_config.distributed_backend if torch.cuda.is_available() else "gloo")
-    initialize_model_parallel(
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    # which ranks run which role: all on the actor's ranks (co-located) or on ranges of their own
+    placement = plan_placement(world, rl_config, torch.cuda.device_count() or None)
+    disjoint = placement.disjoint_roles()
+    states = {"actor": initialize_model_parallel(
         actor_config.tensor_model_parallel_size, actor_config.pipeline_model_parallel_size,
         actor_config.context_parallel_size, actor_config.expert_model_parallel_size,
-        actor_config.moe_tp_extend_ep, actor_config.use_tp_pp_dp_mapping)
+        actor_config.moe_tp_extend_ep, actor_config.use_tp_pp_dp_mapping,
+        world_size=len(placement.of("actor")), rank=rank)}
+    role_configs = {"reference": cfg["ref_config"], "reward": cfg.get("reward_config"),
+                    "critic": cfg.get("critic_config")}
+    for role, mc in role_configs.items():
+        if role in placement.ranks and mc is not None:
+            # every rank of the job takes part in creating the role's process groups
+            states[role] = role_parallel_state(mc, placement, role, rank)
+            if placement.contains(role, rank):
+                set_parallel_state(states[role])      # model code on this rank sees its own role's groups
     tokenizer = build_tokenizer(actor_config)
     eos = tokenizer.eod if tokenizer.eod is not None else actor_config.padded_vocab_size - 1
     pad = tokenizer.pad if tokenizer.pad is not None else 0
+    own_ref_ranks = "reference" in placement.ranks
     with_ref = algorithm != "dapo"
-    worker = IntegratedWorker(actor_config, rl_config, generate_config, eos_token_id=eos, pad_token_id=pad,
-                              ref_config=cfg["ref_config"], with_reference=with_ref)
+    worker = None
+    if placement.contains("actor", rank):
+        worker = IntegratedWorker(actor_config, rl_config, generate_config, eos_token_id=eos, pad_token_id=pad,
+                                  ref_config=cfg["ref_config"], with_reference=with_ref and not own_ref_ranks,
+                                  external_reference=with_ref and own_ref_ranks)
+        worker._state = states["actor"]
     from ..obs.profiler import TensorDump, enable_range_markers, seed_all
 
     prof_cfg = (cfg.get("profiler_config") or {}).get("integrated")
-    worker.profiler_config = prof_cfg
     enable_range_markers(bool(getattr(prof_cfg, "mstx", False)))
-    if cfg.get("msprobe_config") is not None and getattr(cfg["msprobe_config"], "msprobe", False):
-        worker.tensor_dump = TensorDump(cfg["msprobe_config"])
-        worker.tensor_dump.save_configs({"actor": actor_config, "rl": rl_config, "generate": generate_config})
+    if worker is not None:
+        worker.profiler_config = prof_cfg
+        if cfg.get("msprobe_config") is not None and getattr(cfg["msprobe_config"], "msprobe", False):
+            worker.tensor_dump = TensorDump(cfg["msprobe_config"])
+            worker.tensor_dump.save_configs({"actor": actor_config, "rl": rl_config, "generate": generate_config})
     seed_all(actor_config.seed or 1234, deterministic=bool(getattr(actor_config, "use_deter_comp", False)))
-    world = dist.get_world_size() if dist.is_initialized() else 1
-    actor_group = SPMDWorkerGroup(worker, world).initialize()
-    if rl_config.multi_turn_enable:
+    actor_group = SPMDWorkerGroup(worker, ranks=placement.of("actor"), overlapping=disjoint).initialize()
+    actor_group.rl_config, actor_group.megatron_config = rl_config, actor_config
+    if worker is not None and rl_config.multi_turn_enable:
         worker.attach_tools(tokenizer)
-    if actor_config.load:
+    if worker is not None and actor_config.load:
         from ..checkpoint.mcore import load_checkpoint
 
         it, consumed = load_checkpoint(actor_config.load, worker.model.module, worker.optimizer, worker.scheduler,
@@ -123,10 +156,19 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
         worker.iteration, worker.consumed_train_samples = it, consumed
         if worker.ref_model is not None:
             worker.ref_model.load_state_dict(worker.model.module.state_dict())
+
+    def role_group(role: str, cls, mc, **kw):
+        """Worker group of a stand-alone role: on the role's own ranks, or on the actor's."""
+        def factory():
+            w = cls(mc, rl_config, generate_config, pad_token_id=pad, **kw)
+            w._state = states.get(role, states["actor"])
+            return w
+        return SPMDWorkerGroup(factory=factory, ranks=placement.of(role), overlapping=disjoint).initialize()
+
+    ref_group = role_group("reference", ReferenceWorker, cfg["ref_config"]) if (with_ref and own_ref_ranks) else None
     rewards = []
     if rl_config.reward_resource:
-        rw = RewardWorker(cfg["reward_config"], rl_config, generate_config, pad_token_id=pad)
-        rewards.append(SPMDWorkerGroup(rw, world).initialize())
+        rewards.append(role_group("reward", RewardWorker, cfg["reward_config"]))
     if rl_config.rule_reward:
         rewards.append(RuleReward(rl_config, tokenizer, actor_config))
     common = dict(
@@ -144,18 +186,20 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
         wandb_save_dir=rl_config.wandb_save_dir, swanlab_project=rl_config.swanlab_project,
         swanlab_exp_name=rl_config.swanlab_exp_name, swanlab_save_dir=rl_config.swanlab_save_dir,
         swanlab_mode=rl_config.swanlab_mode, pad_token_id=pad)
+    consumed = actor_group.get_consumed_train_samples()
     if algorithm == "grpo":
-        trainer = RayGRPOTrainer(actor_group, reward_list=rewards, **common)
-        data = build_data_iter(actor_config, rl_config, tokenizer, worker.consumed_train_samples)
+        trainer = RayGRPOTrainer(actor_group, ref_worker=ref_group, reward_list=rewards, **common)
+        data = build_data_iter(actor_config, rl_config, tokenizer, consumed)
     elif algorithm == "dapo":
         trainer = RayDAPOTrainer(actor_group, reward_list=rewards, **common)
-        data = build_data_iter(actor_config, rl_config, tokenizer, worker.consumed_train_samples, reiterable=True)
+        data = build_data_iter(actor_config, rl_config, tokenizer, consumed, reiterable=True)
     elif algorithm == "ppo":
-        critic = CriticWorker(cfg["critic_config"], rl_config, generate_config, pad_token_id=pad,
-                              offload_between_stages=bool(generate_config.offload_train_param))
-        critic_group = SPMDWorkerGroup(critic, world).initialize()
-        trainer = RayPPOTrainer(actor_group, reward_list=rewards, critic_worker=critic_group, **common)
-        data = build_data_iter(actor_config, rl_config, tokenizer, worker.consumed_train_samples)
+        critic_group = role_group("critic", CriticWorker, cfg["critic_config"],
+                                  offload_between_stages=bool(generate_config.offload_train_param)
+                                  and placement.colocated("critic", "actor"))
+        trainer = RayPPOTrainer(actor_group, ref_worker=ref_group, reward_list=rewards, critic_worker=critic_group,
+                                **common)
+        data = build_data_iter(actor_config, rl_config, tokenizer, consumed)
     else:
         raise ValueError(f"unknown algorithm '{algorithm}'")
     history = trainer.fit(data)

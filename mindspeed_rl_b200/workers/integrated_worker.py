@@ -38,11 +38,15 @@ def _now() -> float:
 class IntegratedWorker(BaseWorker):
     def __init__(self, actor_config, rl_config, generate_config, td=None, *, eos_token_id: int = -1,
                  pad_token_id: int = 0, device=None, ref_config=None, with_reference: bool = True,
-                 sampling_overrides: Optional[dict] = None, seed: Optional[int] = None):
+                 sampling_overrides: Optional[dict] = None, seed: Optional[int] = None,
+                 external_reference: bool = False):
         super().__init__(td, pad_token_id)
         self.actor_config, self.rl_config, self.generate_config = actor_config, rl_config, generate_config
         self.ref_config = ref_config or actor_config
         self.with_reference = with_reference
+        # a reference worker on other ranks writes ``ref_log_prob``: the update consumes it although
+        # this worker holds no reference model itself
+        self.uses_ref_log_prob = with_reference or external_reference
         self.eos_token_id = eos_token_id
         self.device = torch.device(device if device is not None
                                    else ("cuda" if torch.cuda.is_available() else "cpu"))
@@ -62,7 +66,8 @@ class IntegratedWorker(BaseWorker):
 
         from ..parallel.symm import get_arena, init_arena
 
-        if (self.device.type != "cuda" or not dist.is_initialized() or dist.get_world_size() == 1
+        team = self.parallel_state.layout.world_size        # the ranks of this role (the whole job when co-located)
+        if (self.device.type != "cuda" or not dist.is_initialized() or team == 1
                 or dist.get_world_size() > torch.cuda.device_count() or get_arena() is not None
                 or os.environ.get("MSRL_SYMM", "1") != "1"):
             return
@@ -75,7 +80,8 @@ class IntegratedWorker(BaseWorker):
         extra += self._moe_p2p_bytes()
         from ..parallel.symm import ArenaUnavailable
         try:
-            init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20) + extra, device=self.device)
+            init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20) + extra,
+                       group=self.parallel_state.group("all"), device=self.device)
         except ArenaUnavailable as e:
             # raised on every rank together: the job carries on with NCCL collectives and gathered resharding
             import logging
@@ -470,7 +476,7 @@ class IntegratedWorker(BaseWorker):
         columns = ["responses", "advantages", "input_ids", "response_length", "prompt_length"]
         if not skip_actor_log_prob:
             columns.append("old_log_prob")
-        if self.with_reference and (self.actor_config.stage or "ray_grpo") != "ray_dapo":
+        if self.uses_ref_log_prob and (self.actor_config.stage or "ray_grpo") != "ray_dapo":
             columns.append("ref_log_prob")
         if rl.multi_turn_enable:
             columns.append("response_mask")

@@ -17,6 +17,8 @@ def _free_port() -> int:
 def _entry(rank, world_size, port, fn, args, errors):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world_size),
                       LOCAL_RANK=str(rank))
+    # the ranks share this machine's cores: without a cap every rank starts one thread per core
+    torch.set_num_threads(max(1, (os.cpu_count() or world_size) // world_size))
     try:
         dist.init_process_group("gloo", rank=rank, world_size=world_size)
         fn(rank, world_size, *args)

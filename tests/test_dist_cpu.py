@@ -336,6 +336,47 @@ def _launch_worker(rank, world, train_tp, infer_tp):
         assert all(m["timing/rollout"] > 0 and "actor/pg_loss" in m for m in hist)
 
 
+def _launch_disaggregated_worker(rank, world):
+    """Actor on ranks 0-1 and reference model on ranks 2-3 (two data-parallel replicas each) with
+    non-blocking stages: the reference forward runs on its own ranks while the actor ranks go on,
+    and the update consumes the ``ref_log_prob`` column the other group wrote.  Both models start
+    from the same seed, so the first update sees a KL of (almost) zero."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        "rl_config.use_integrated_worker=false", "rl_config.blocking=false",
+        "rl_config.actor_resource.num_gpus=2", "+rl_config.reference_resource.num_gpus=2",
+        "+ref_config.model=tiny_qwen2", "+ref_config.micro_batch_size=4"])
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == 2
+        for m in hist:
+            assert m["timing/rollout"] > 0 and m["timing/reference_model"] > 0
+            assert "actor/kl_loss" in m and "actor/pg_loss" in m
+        assert abs(hist[0]["actor/kl_loss"]) < 1e-4, hist[0]["actor/kl_loss"]
+
+
+def test_launch_grpo_disaggregated_reference_group():
+    run_distributed(_launch_disaggregated_worker, 4)
+
+
+def test_placement_plan():
+    from mindspeed_rl_b200.config import RLConfig
+    from mindspeed_rl_b200.runtime.placement import plan_placement
+    co = plan_placement(8, RLConfig(dict(actor_resource={"num_gpus": 8})))
+    assert co.of("reference") == list(range(8)) and not co.disjoint_roles()
+    rl = RLConfig(dict(use_integrated_worker=False, actor_resource={"num_gpus": 8}, reference_resource={"num_gpus": 4},
+                       critic_resource={"num_gpus": 4}))
+    p = plan_placement(16, rl, gpus_per_node=8)
+    assert p.of("actor") == list(range(8)) and p.of("reference") == [8, 9, 10, 11] and p.of("critic") == [12, 13, 14, 15]
+    assert p.of("reward") == p.of("actor") and p.disjoint_roles() and not p.colocated("critic", "actor")
+    rl = RLConfig(dict(use_integrated_worker=False, actor_resource={"num_gpus": 6}, reference_resource={"num_gpus": 4}))
+    assert plan_placement(16, rl, gpus_per_node=8).of("reference") == [8, 9, 10, 11]      # not split over two nodes
+    import pytest
+    with pytest.raises(ValueError):
+        plan_placement(8, rl, gpus_per_node=8)
+
+
 def _launch_moe_ep_worker(rank, world):
     """Whole GRPO iterations of a small MoE model with expert parallelism 2: the two ranks are
     data-parallel replicas for rollout and training, exchange tokens in every MoE layer and
