@@ -126,7 +126,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   if (warp == TMA_WARP) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    if (elect_one()) {
       const int qc = head_col(p.q_col0, p.q_group_stride, p.q_hpg, p.q_head_stride, h);
       const int kc = head_col(p.k_col0, p.k_group_stride, p.k_hpg, p.k_head_stride, hk);
       const int vc = head_col(p.v_col0, p.v_group_stride, p.v_hpg, p.v_head_stride, hk);
@@ -153,7 +153,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
   } else if (warp == MMA_WARP) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    if (elect_one()) {
       constexpr uint32_t id_s = idesc_bf16(BM, BN, false);
       constexpr uint32_t id_o = idesc_bf16(BM, D, true);
       const uint32_t q_addr = smem_u32(smem + SMEM_Q), p_addr = smem_u32(smem + SMEM_P);
@@ -504,7 +504,7 @@ fa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const uint32_t tmem_dp = tmem + 128, tmem_dq = tmem + 256;
 
   if (warp == TMA_WARP) {
-    if (lane == 0) {
+    if (elect_one()) {
       const int qc = head_col(0, p.q_group_stride, p.q_hpg, p.q_head_stride, h);
       const int kc = head_col(0, p.k_group_stride, p.k_hpg, p.k_head_stride, hk);
       const int vc = head_col(0, p.v_group_stride, p.v_hpg, p.v_head_stride, hk);
@@ -526,7 +526,7 @@ fa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
     }
   } else if (warp == MMA_WARP) {
-    if (lane == 0) {
+    if (elect_one()) {
       constexpr uint32_t id_s = idesc_bf16(BM, 64, false);
       constexpr uint32_t id_o = idesc_bf16(BM, D, true);
       const uint32_t q_addr = smem_u32(smem + DQ_SMEM_Q), do_addr = smem_u32(smem + DQ_SMEM_DO);
@@ -708,7 +708,7 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       __syncwarp();
     }
   } else if (warp == MMA_WARP) {
-    if (lane == 0) {
+    if (elect_one()) {
       constexpr uint32_t id_s = idesc_bf16(BM, 64, false);
       constexpr uint32_t id_o = idesc_bf16(BM, D, true);
       const uint32_t k_addr = smem_u32(smem + KV_SMEM_K), v_addr = smem_u32(smem + KV_SMEM_V);

@@ -82,13 +82,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
-// One lane of a fully active warp.  The compiler knows that code under this predicate runs in a
-// single thread of a converged warp, which lets it keep descriptors and addresses in uniform registers.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
-  return pred != 0;
-}
 __device__ __forceinline__ void umma_pair(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
                ::"r"(tmem_c), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
@@ -102,6 +95,19 @@ __device__ __forceinline__ void commit_pair(uint64_t* bar) {
 constexpr uint32_t idesc_pair(bool a_mn, bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// Tile order: panels of GROUP_M row tiles; inside a panel row tiles run fastest, then column tiles.
+// The pairs working at the same time then share a few column tiles of B and at most GROUP_M row tiles
+// of A (about 29 MB at K = 3584), which stay in L2 while the panel sweeps over all of B.
+constexpr int GROUP_M = 16;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int per_panel = GROUP_M * n_tiles;
+  const int panel = tile / per_panel, rem = tile - panel * per_panel;
+  const int first = panel * GROUP_M;
+  const int rows = (m_tiles - first) < GROUP_M ? (m_tiles - first) : GROUP_M;
+  mt = first + rem % rows;
+  nt = rem / rows;
 }
 
 template <bool A_MN, bool B_MN, int OUT>
@@ -146,11 +152,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (warp == 4) {
     // ---------------- TMA producer (one thread in each CTA) ----------------
-    {
+    if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
+      const uint32_t full0 = map_to_rank(smem_u32(&full_bar[0]), 0);     // the leader's barriers
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
-        const int mt = tile % m_tiles, nt = tile / m_tiles;
+        int mt, nt;
+        tile_coords(tile, m_tiles, n_tiles, mt, nt);
         const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN + (int)rank * HN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % RS;
@@ -159,34 +167,37 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             ok = false;
             break;
           }
-          const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
+          const uint32_t bar = full0 + (uint32_t)s * 8;
           unsigned char* sa = smem + (size_t)s * STAGE_BYTES;
-          if (elect_one()) {
-            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
-            if (A_MN) {
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+          if (A_MN) {
 #pragma unroll
-              for (int i = 0; i < HM / 64; ++i)       // [64 k rows x 64 m columns] blocks of 8 KiB
-                tma_load_2d_pair(sa + i * 8192, &map_a, bar, m0 + i * 64, kb * BK);
-            } else {
-              tma_load_2d_pair(sa, &map_a, bar, kb * BK, m0);
-            }
-            if (B_MN) {
-#pragma unroll
-              for (int i = 0; i < HN / 64; ++i)
-                tma_load_2d_pair(sa + SMEM_A + i * 8192, &map_b, bar, n0 + i * 64, kb * BK);
-            } else {
-              tma_load_2d_pair(sa + SMEM_A, &map_b, bar, kb * BK, n0);
-            }
+            for (int i = 0; i < HM / 64; ++i)       // [64 k rows x 64 m columns] blocks of 8 KiB
+              tma_load_2d_pair(sa + i * 8192, &map_a, bar, m0 + i * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(sa, &map_a, bar, kb * BK, m0);
           }
-          __syncwarp();
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < HN / 64; ++i)
+              tma_load_2d_pair(sa + SMEM_A + i * 8192, &map_b, bar, n0 + i * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(sa + SMEM_A, &map_b, bar, kb * BK, n0);
+          }
         }
       }
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer (leader CTA only) ----------------
-    // the whole warp walks the loop and waits on the barriers; one elected lane issues
-    if (rank == 0) {
+    // one elected lane of the converged warp runs the whole issue loop
+    if (rank == 0 && elect_one()) {
       constexpr uint32_t idesc = idesc_pair(A_MN, B_MN);
+      // descriptors of stage 0, k-step 0; a later stage / k-step only adds to the 14-bit address field
+      // (shared memory ends below 256 KiB, so the sum never carries out of it)
+      const uint32_t smem0 = smem_u32(smem);
+      const uint64_t da0 = A_MN ? desc_sw128(smem0, 8192, 1024) : desc_sw128(smem0, 16, 1024);
+      const uint64_t db0 = B_MN ? desc_sw128(smem0 + SMEM_A, 8192, 1024) : desc_sw128(smem0 + SMEM_A, 16, 1024);
+      constexpr uint32_t KA = (A_MN ? 2048 : 32) >> 4, KB_ = (B_MN ? 2048 : 32) >> 4;
       uint32_t it = 0, local = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++local) {
@@ -204,21 +215,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           // the operands were written by TMA and are ordered by the barrier itself; a tcgen05 fence
           // here would only hold back the MMA issue
           if (p.flags & 1) fence_after();
-          const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + SMEM_A;
-          if (elect_one()) {
+          const uint64_t so = (uint64_t)((uint32_t)s * (STAGE_BYTES >> 4));
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k) {
-              const uint64_t da = A_MN ? desc_sw128(a_addr + k * 2048, 8192, 1024) : desc_sw128(a_addr + k * 32, 16, 1024);
-              const uint64_t db = B_MN ? desc_sw128(b_addr + k * 2048, 8192, 1024) : desc_sw128(b_addr + k * 32, 16, 1024);
-              umma_pair(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            }
-            commit_pair(&empty_bar[s]);   // the slot is free in both CTAs once these MMAs have read it
-          }
-          __syncwarp();
+          for (int k = 0; k < BK / 16; ++k)
+            umma_pair(tmem_acc, da0 + so + k * KA, db0 + so + k * KB_, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          commit_pair(&empty_bar[s]);     // the slot is free in both CTAs once these MMAs have read it
         }
-        if (elect_one()) commit_pair(&acc_full[buf]);   // accumulator complete (or abandoned) for both epilogues
-        __syncwarp();
+        commit_pair(&acc_full[buf]);      // accumulator complete (or abandoned) for both epilogues
       }
     }
   } else {
@@ -230,7 +233,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t acc_empty_leader1 = map_to_rank(smem_u32(&acc_empty[1]), 0);
     for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++local) {
       const uint32_t buf = local & 1;
-      const int mt = tile % m_tiles, nt = tile / m_tiles;
+      int mt, nt;
+      tile_coords(tile, m_tiles, n_tiles, mt, nt);
       const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN;
       ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, ERR_ACC) &&
            (*reinterpret_cast<volatile int*>(p.error) == 0);
@@ -276,51 +280,68 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           __syncwarp();
         }
-      } else if (OUT == OUT_ACC_F32) {
-        float* C = reinterpret_cast<float*>(p.C);
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= p.N) break;
-          float v[32];
-          tmem_ld32(t_row + c * 32, v);
-          if (row < p.M) {
-            float* dst = C + (long long)row * p.ldc + col;
-            if (col + 32 <= p.N && (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float4 o = *reinterpret_cast<const float4*>(dst + q * 4);
-                o.x += v[q * 4]; o.y += v[q * 4 + 1]; o.z += v[q * 4 + 2]; o.w += v[q * 4 + 3];
-                *reinterpret_cast<float4*>(dst + q * 4) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] += v[j];
-            }
-          }
-        }
       } else {
-        __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C);
+        // Accumulating epilogues (weight gradients): C += acc through the warp's shared-memory patch, so
+        // that the read-modify-write of C moves whole 128-byte (fp32) / 64-byte (bf16) row segments per
+        // group of lanes instead of one 16-byte piece per lane and row.  32 columns per step, fp32 staging.
+        const long long crow0 = m0 + warp * 32;
+        const bool f32 = (OUT == OUT_ACC_F32);
+        const bool vec_ok = f32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
+                                : ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= p.N) break;
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
           float v[32];
           tmem_ld32(t_row + c * 32, v);
-          if (row < p.M) {
-            __nv_bfloat16* dst = C + (long long)row * p.ldc + col;
-            if (col + 32 <= p.N && (p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                float f[8];
-                unpack8(ld8(dst + q * 8), f);
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(patch + lane * EPI_PITCH + q * 16) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          __syncwarp();
+          if (vec_ok && col0 + 32 <= p.N) {
+            if (f32) {
+              float* C = reinterpret_cast<float*>(p.C);
+              const int cc = (lane & 7) * 4;                    // 8 lanes x 16 B = one 128-byte row segment
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += v[q * 8 + j];
-                st8(dst + q * 8, pack8(f));
+              for (int i = 0; i < 8; ++i) {
+                const int r = i * 4 + (lane >> 3);
+                if (crow0 + r < p.M) {
+                  float* dst = C + (crow0 + r) * p.ldc + col0 + cc;
+                  float4 o = *reinterpret_cast<const float4*>(dst);
+                  const float4 a = *reinterpret_cast<const float4*>(patch + r * EPI_PITCH + cc * 4);
+                  o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
+                  *reinterpret_cast<float4*>(dst) = o;
+                }
               }
             } else {
-              for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __float2bfloat16(__bfloat162float(dst[j]) + v[j]);
+              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C);
+              const int cc = (lane & 3) * 8;                    // 4 lanes x 16 B = one 64-byte row segment
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int r = i * 8 + (lane >> 2);
+                if (crow0 + r < p.M) {
+                  __nv_bfloat16* dst = C + (crow0 + r) * p.ldc + col0 + cc;
+                  float f[8];
+                  unpack8(ld8(dst), f);
+                  const float4 a0 = *reinterpret_cast<const float4*>(patch + r * EPI_PITCH + cc * 4);
+                  const float4 a1 = *reinterpret_cast<const float4*>(patch + r * EPI_PITCH + cc * 4 + 16);
+                  f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
+                  f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+                  st8(dst, pack8(f));
+                }
+              }
+            }
+          } else if (row < p.M) {
+            const float* src = reinterpret_cast<const float*>(patch + lane * EPI_PITCH);
+            if (f32) {
+              float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+              for (int jj = 0; jj < 32 && col0 + jj < p.N; ++jj) dst[jj] += src[jj];
+            } else {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+              for (int jj = 0; jj < 32 && col0 + jj < p.N; ++jj) dst[jj] = __float2bfloat16(__bfloat162float(dst[jj]) + src[jj]);
             }
           }
+          __syncwarp();
         }
       }
       // hand the accumulator back to the leader's MMA thread

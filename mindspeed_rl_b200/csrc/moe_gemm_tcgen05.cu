@@ -83,7 +83,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // tile order: column tiles fastest, so that the CTAs running together cover a few dozen row tiles of
   // one expert with all its weight columns: both stay in L2 and are read from DRAM once
   if (warp == 4) {
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -112,7 +112,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    if (elect_one()) {
       constexpr uint32_t idesc = idesc_bf16(BM, BN, B_MN);
       uint32_t it = 0, local = 0;
       bool ok = true;

@@ -49,16 +49,12 @@ class MicroBatch:
         cu = torch.zeros(b + 1, dtype=torch.int64)
         cu[1:] = torch.cumsum(padded, 0)
         total = int(cu[-1])
-        col = torch.arange(s).unsqueeze(0)
-        valid = col < lens.unsqueeze(1)
-        dest = (cu[:-1].unsqueeze(1) + col)[valid]
-        ids = torch.zeros(total, dtype=torch.int64)
-        ids[dest] = ids2d[valid]
-        shifted = torch.cat([ids2d[:, 1:], ids2d.new_zeros(b, 1)], dim=1)
-        shifted = shifted.masked_fill(col == (lens - 1).unsqueeze(1), 0)
-        labels = torch.zeros(total, dtype=torch.int64)
-        labels[dest] = shifted[valid]
-        pos = torch.arange(total) - torch.repeat_interleave(cu[:-1], padded)
+        # the packed ids / next-token labels / positions are built by ``ops.packing.pack_tokens``: on
+        # the device when the micro-batch is moved there (only the padded rows and three small
+        # vectors cross PCIe), on the host the first time something asks for them
+        ids2d = ids2d[:, :max(int(lens.max()) if b else 0, 1)].contiguous()      # columns no row uses stay behind
+        self._ids2d, self._p_len, self._r_len = ids2d, p_len.to(torch.int32), r_len.to(torch.int32)
+        self._packed = None
         width = data["responses"].shape[1]
         j = torch.arange(width).unsqueeze(0)
         self.resp_valid = j < r_len.unsqueeze(1)
@@ -66,18 +62,43 @@ class MicroBatch:
         self.resp_index = torch.where(self.resp_valid, self.resp_index, torch.zeros_like(self.resp_index))
         self.last_index = cu[:-1] + lens - 1
         self.rows = rows_t
-        self.ids, self.labels, self.positions = ids, labels, pos.to(torch.int32)
         self.cu = cu.to(torch.int32)
         self.cu_host = cu.clone()          # stays on the host (context-parallel index arithmetic)
         self.max_seqlen = int(padded.max()) if b else 0
         self.num_tokens = total
         self.data = {k: v[rows_t] for k, v in data.items() if torch.is_tensor(v) and v.shape[:1] == data["input_ids"].shape[:1]}
 
+    def _pack(self):
+        if self._packed is None:
+            from ..ops.packing import pack_tokens
+
+            self._packed = pack_tokens(self._ids2d, self._p_len, self._r_len, self.cu, self.num_tokens)
+        return self._packed
+
+    ids = property(lambda self: self._pack()[0])
+    labels = property(lambda self: self._pack()[1])
+    positions = property(lambda self: self._pack()[2])
+
     def to(self, device) -> "MicroBatch":
-        for k in ("ids", "labels", "positions", "cu", "resp_index", "resp_valid", "last_index"):
+        for k in ("cu", "resp_index", "resp_valid", "last_index", "_p_len", "_r_len"):
             t = getattr(self, k)
             setattr(self, k, to_device(t, t.dtype, device))
+        ids2d = self._ids2d
+        if torch.device(device).type == "cuda" and ids2d.numel() and int(ids2d.max()) < 2 ** 31:
+            ids2d = ids2d.to(torch.int32)              # half the bytes over PCIe
+        self._ids2d = to_device(ids2d, ids2d.dtype, device)
+        self._packed = None
         return self
+
+    def response_rows(self, per_token: torch.Tensor) -> torch.Tensor:
+        """Per-token values of the packed stream ``[T]`` -> ``[b, R]`` response rows (zeros beyond each
+        response).  Without autograd this is one gather kernel; with it, an index + mask that
+        autograd knows how to invert."""
+        if not (torch.is_grad_enabled() and per_token.requires_grad) and per_token.dim() == 1:
+            from ..ops.packing import unpack_response
+
+            return unpack_response(per_token, self.cu, self._p_len, self._r_len, self.resp_index.shape[1])
+        return per_token[self.resp_index] * self.resp_valid
 
     def meta(self) -> PackedMeta:
         return PackedMeta(self.cu, self.max_seqlen, self.positions)
@@ -157,20 +178,20 @@ class TrainingEngine:
                 v = cp.gather_tokens(core.forward_values(x, meta))
                 if self.role == "reward":
                     return v[mb.last_index].unsqueeze(-1), None
-                return v[mb.resp_index] * mb.resp_valid, None
+                return mb.response_rows(v), None
             logp, ent = core.forward_logprob(x, cp.take_local(mb.labels), meta, self.temperature, want_entropy)
             logp = cp.gather_tokens(logp)
-            lp = logp[mb.resp_index] * mb.resp_valid
-            en = cp.gather_tokens(ent)[mb.resp_index] * mb.resp_valid if want_entropy else None
+            lp = mb.response_rows(logp)
+            en = mb.response_rows(cp.gather_tokens(ent)) if want_entropy else None
             return lp, en
         if self.loss_func.output_kind == "value":
             v = core.forward_values(x, mb.meta())
             if self.role == "reward":
                 return v[mb.last_index].unsqueeze(-1), None
-            return v[mb.resp_index] * mb.resp_valid, None
+            return mb.response_rows(v), None
         logp, ent = core.forward_logprob(x, mb.labels, mb.meta(), self.temperature, want_entropy)
-        lp = logp[mb.resp_index] * mb.resp_valid
-        en = ent[mb.resp_index] * mb.resp_valid if want_entropy else None
+        lp = mb.response_rows(logp)
+        en = mb.response_rows(ent) if want_entropy else None
         return lp, en
 
     def _stage_forward(self, mb: MicroBatch, h_in: Optional[torch.Tensor], want_entropy: bool):

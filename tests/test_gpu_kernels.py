@@ -454,3 +454,31 @@ def test_forward_backward_is_bit_reproducible():
     for a, b in zip(runs[0][1], runs[1][1]):
         assert torch.equal(a, b)
     assert torch.equal(runs[0][2], runs[1][2])           # sum of squares of the gradients
+
+
+def test_pack_tokens_and_unpack_response_kernels_match_reference():
+    """K14: the device kernels against the PyTorch index arithmetic (exact equality), int32 and int64
+    ids, ragged lengths, block padding, a stream padded at its end."""
+    from mindspeed_rl_b200.ops.packing import pack_tokens, unpack_response
+    torch.manual_seed(5)
+    b, s = 37, 129
+    p_len = torch.randint(1, 40, (b,), dtype=torch.int32)
+    r_len = torch.randint(0, 89, (b,), dtype=torch.int32)
+    ids2d = torch.randint(1, 150000, (b, s))
+    lens = (p_len + r_len).long().clamp(max=s)
+    padded = (lens + 7) // 8 * 8
+    padded[-1] += 128
+    cu = torch.zeros(b + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(padded, 0)
+    total = int(cu[-1])
+    want = pack_tokens(ids2d, p_len, r_len, cu, total)
+    for dt in (torch.int64, torch.int32):
+        got = pack_tokens(ids2d.to(dt).cuda(), p_len.cuda(), r_len.cuda(), cu.cuda(), total)
+        for g, w in zip(got, want):
+            assert torch.equal(g.cpu(), w)
+    src = torch.randn(total)
+    want_rows = unpack_response(src, cu, p_len, r_len, 96)
+    got_rows = unpack_response(src.cuda(), cu.cuda(), p_len.cuda(), r_len.cuda(), 96)
+    assert torch.equal(got_rows.cpu(), want_rows)
+    got16 = unpack_response(src.bfloat16().cuda(), cu.cuda(), p_len.cuda(), r_len.cuda(), 96)
+    assert torch.equal(got16.cpu(), unpack_response(src.bfloat16(), cu, p_len, r_len, 96))

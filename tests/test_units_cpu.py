@@ -253,3 +253,34 @@ def test_reuse_fp32_param_split_is_exact_and_tracks_fp32_master():
     assert (wa - wb).abs().max() <= 2 ** -7 * wa.abs().max()      # at most one bf16 ulp apart (tie rounding)
     full = ob.state_dict()["shards"][0]["master"]
     torch.testing.assert_close(full, oa.state[0]["master"], rtol=1e-6, atol=1e-7)
+
+
+def test_pack_tokens_and_unpack_response_reference_path():
+    """The packing op against the definition: ids / shifted labels / restarting positions of every
+    block, zeros in block padding; response rows start at the position that predicts the first
+    response token."""
+    import torch
+    from mindspeed_rl_b200.ops.packing import pack_tokens, unpack_response
+    g = torch.Generator().manual_seed(0)
+    p_len = torch.tensor([3, 5, 1], dtype=torch.int32)
+    r_len = torch.tensor([4, 2, 6], dtype=torch.int32)
+    s = 10
+    ids2d = torch.randint(1, 100, (3, s), generator=g)
+    lens = (p_len + r_len).long()
+    padded = (lens + 3) // 4 * 4
+    cu = torch.zeros(4, dtype=torch.int32)
+    cu[1:] = torch.cumsum(padded, 0)
+    total = int(cu[-1])
+    ids, labels, pos = pack_tokens(ids2d, p_len, r_len, cu, total)
+    for b in range(3):
+        lo, n = int(cu[b]), int(lens[b])
+        assert ids[lo:lo + n].tolist() == ids2d[b, :n].tolist()
+        assert labels[lo:lo + n - 1].tolist() == ids2d[b, 1:n].tolist() and int(labels[lo + n - 1]) == 0
+        assert ids[lo + n:int(cu[b + 1])].sum() == 0 and labels[lo + n:int(cu[b + 1])].sum() == 0
+        assert pos[lo:int(cu[b + 1])].tolist() == list(range(int(padded[b])))
+    src = torch.arange(total, dtype=torch.float32) + 1
+    out = unpack_response(src, cu, p_len, r_len, 6)
+    for b in range(3):
+        start = int(cu[b]) + int(p_len[b]) - 1
+        want = [float(src[start + j]) if j < int(r_len[b]) else 0.0 for j in range(6)]
+        assert out[b].tolist() == want
