@@ -142,6 +142,94 @@ __global__ void symm_copy_plan_kernel(const __grid_constant__ PeerPtrs src, unsi
   }
 }
 
+// ---- all-reduce of small activations (rollout decode under tensor parallelism) -------------------
+// Every rank owns a region [flags | slots] in its arena.  flags: 2 parities x kMaxRanks u32; slots:
+// 2 parities x world x slot_bytes.  A call with sequence number q (kept in device memory, so that a
+// CUDA graph can replay the launch unchanged) uses parity q & 1:
+//   1. push: every CTA stores its part of x into slot [parity][me] of EVERY peer (posted remote
+//      stores: one NVLink crossing, no round trip); the last CTA to finish releases
+//      flags[parity][me] = q + 1 on every peer;
+//   2. wait (bounded) until flags[parity][p] == q + 1 for every peer p in this rank's own region;
+//   3. out = sum over ranks in rank order (own x at its own position), fp32 accumulation: every rank
+//      adds the same numbers in the same order and gets bit-identical results;
+//   4. the last CTA to leave re-arms the local counters and advances q.
+// Parity double-buffering is enough: a rank can start call q + 2 (same parity as q) only after every
+// peer has pushed for q + 1, which a peer does after it has finished reading its slots of call q.
+struct ArState {
+  unsigned int seq, pushed, left, pad;
+};
+constexpr int kArFlagBytes = 2 * kMaxRanks * 4;      // 128 B, padded to 256 by the host
+constexpr int kArHeader = 256;
+
+__global__ void symm_allreduce_push_kernel(const __grid_constant__ PeerPtrs region, int rank, int world,
+                                           const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                           long long n_vec8, long long slot_bytes, ArState* state, int* status) {
+  __shared__ unsigned int s_seq;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_seq = *reinterpret_cast<volatile unsigned int*>(&state->seq);
+  __syncthreads();
+  const unsigned int q = s_seq, parity = q & 1u;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  // 1. push my values into my slot on every peer
+  for (int i = 1; i < world; ++i) {
+    const int p = (rank + i) % world;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(region.p[p]) + kArHeader +
+                                                          ((long long)parity * world + rank) * slot_bytes);
+    for (long long k = first; k < n_vec8; k += stride) st8(dst + k * 8, ld8(x + k * 8));
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(&state->pushed, 1u) == gridDim.x - 1) {
+      for (int i = 1; i < world; ++i) {
+        const int p = (rank + i) % world;
+        st_release_sys(reinterpret_cast<unsigned int*>(region.p[p]) + parity * kMaxRanks + rank, q + 1);
+      }
+    }
+    // 2. wait for every peer's push of this call
+    int ok = 1;
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(region.p[rank]) + parity * kMaxRanks;
+    const long long t0 = clock64();
+    for (int i = 1; i < world && ok; ++i) {
+      const int p = (rank + i) % world;
+      while (ld_acquire_sys(mine + p) != q + 1) {
+        if (clock64() - t0 > kBarrierCycles) {
+          atomicCAS(status, 0, 200 + p);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  // 3. reduce in rank order
+  if (s_ok) {
+    const unsigned char* slots = reinterpret_cast<const unsigned char*>(region.p[rank]) + kArHeader +
+                                 (long long)parity * world * slot_bytes;
+    for (long long k = first; k < n_vec8; k += stride) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < world; ++r) {
+        const __nv_bfloat16* src = (r == rank) ? x : reinterpret_cast<const __nv_bfloat16*>(slots + r * slot_bytes);
+        float f[8];
+        unpack8(ld8(src + k * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+      st8(out + k * 8, pack8(acc));
+    }
+  }
+  // 4. last CTA out re-arms the counters and advances the sequence number
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(&state->left, 1u) == gridDim.x - 1) {
+    state->pushed = 0;
+    state->left = 0;
+    __threadfence();
+    *reinterpret_cast<volatile unsigned int*>(&state->seq) = q + 1;
+  }
+}
+
 }  // namespace msrl
 
 using namespace msrl;
@@ -223,6 +311,28 @@ MSRL_API int msrl_symm_reduce_scatter(void* const* src_ptrs, long long element_o
   else
     symm_reduce_scatter_f32_kernel<<<copy_grid(n / 4), 256, 0, st>>>(to_peers(src_ptrs, world), element_offset,
                                                                     out_f32, n / 4, world, rank, scale);
+  MSRL_LAUNCH_CHECK();
+}
+
+MSRL_API int msrl_symm_allreduce_header_bytes() { return kArHeader; }
+MSRL_API int msrl_symm_allreduce_state_bytes() { return (int)sizeof(ArState); }
+
+// out = sum over the team of x (bf16, n elements, multiple of 8; x and out may alias).  region_ptrs[r]:
+// rank r's all-reduce region (header + 2 x world x slot_bytes, zero-initialised once); state: this
+// rank's ArState in ordinary device memory (zero-initialised once).  All ranks must issue the same
+// sequence of calls on this region.  The launch reads its sequence number from `state`, so a CUDA
+// graph may replay it.
+MSRL_API int msrl_symm_allreduce_push(void* const* region_ptrs, int rank, int world, const void* x, void* out,
+                                      long long n, long long slot_bytes, void* state, int* status, cudaStream_t st) {
+  if (world > kMaxRanks || n % 8 != 0 || n * 2 > slot_bytes || slot_bytes % 16 != 0) return (int)cudaErrorInvalidValue;
+  if (n == 0) return 0;
+  // every CTA spins on the peers' flags: the grid must be resident at once
+  long long blocks = ceil_div(n / 8, 256 * 4);
+  const long long cap = sm_count();
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  symm_allreduce_push_kernel<<<(unsigned)blocks, 256, 0, st>>>(to_peers(region_ptrs, world), rank, world,
+                                                              (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n / 8,
+                                                              slot_bytes, (ArState*)state, status);
   MSRL_LAUNCH_CHECK();
 }
 

@@ -196,6 +196,8 @@ class SymmetricArena:
         code = int(self.status.item())
         if code != 0:
             self.status.zero_()
+            if 200 <= code < 300:
+                raise SymmetricTimeout(f"rank {self.rank}: all-reduce timed out waiting for peer {code - 200}")
             if code >= 300:
                 raise RuntimeError(f"rank {self.rank}: the expert slab of EP member {code - 300} would overflow "
                                    f"(raise moe_p2p_dispatch_rows)")
@@ -272,6 +274,11 @@ class SymmetricArena:
         if sync:
             self.barrier(ranks)
 
+    def make_all_reduce(self, max_bytes: int, ranks: Optional[Sequence[int]] = None) -> "PeerAllReduce":
+        """Reserve the slots of a small-message all-reduce among ``ranks`` (team positions; call on all
+        members in the same order)."""
+        return PeerAllReduce(self, max_bytes, ranks)
+
     def copy_plan(self, plan: torch.Tensor, n_desc: int, dst: torch.Tensor,
                   ranks: Optional[Sequence[int]] = None, sync: bool = True) -> None:
         """Run a resharding plan (device array of copy descriptors, see ``reshard.planner``):
@@ -305,6 +312,48 @@ class SymmetricArena:
             self.lib.msrl_symm_free(ctypes.c_void_p(self.base))
             self.base = 0
         self._closed = True
+
+
+class PeerAllReduce:
+    """Sum of a small bf16 tensor over a sub-team, for the two all-reduces per layer of a decode step
+    under rollout tensor parallelism (reference: the row-parallel linears of the rollout engine,
+    ``mindspeed_rl/models/rollout/vllm_engine.py:424-504``, all-reduce through HCCL).
+
+    One kernel per call: every rank stores its values into its slot on every peer (posted NVLink
+    stores), raises a flag there, waits for the peers' flags and adds the slots in rank order, so all
+    ranks obtain bit-identical sums.  The call's sequence number lives in device memory, which makes
+    the launch replayable inside a CUDA graph.  Messages larger than ``max_bytes`` are not taken
+    (``fits``): bandwidth-bound sizes belong to the library collective."""
+
+    def __init__(self, arena: "SymmetricArena", max_bytes: int, ranks: Optional[Sequence[int]] = None):
+        self.arena = arena
+        self.members, self.me = arena._members(ranks)
+        w = len(self.members)
+        self.slot_bytes = _align(int(max_bytes), 256)
+        header = int(arena.lib.msrl_symm_allreduce_header_bytes())
+        region = arena.alloc(header + 2 * w * self.slot_bytes, torch.uint8)
+        region.zero_()
+        self.region_offset = arena.offset_of(region)
+        self.state = torch.zeros(int(arena.lib.msrl_symm_allreduce_state_bytes()), dtype=torch.uint8,
+                                 device=arena.device)
+        self._ptrs = arena.peer_ptrs(self.region_offset, self.members)
+        if arena.world > 1:
+            dist.barrier(group=arena.group)      # every region is zeroed before a peer may push into it
+
+    def fits(self, t: torch.Tensor) -> bool:
+        return (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() % 8 == 0
+                and t.numel() * 2 <= self.slot_bytes and t.data_ptr() % 16 == 0)
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In place; every member must call with the same shape in the same order."""
+        if len(self.members) == 1:
+            return t
+        a = self.arena
+        _lib.check(a.lib.msrl_symm_allreduce_push(
+            self._ptrs, ctypes.c_int(self.me), ctypes.c_int(len(self.members)), _lib.ptr(t), _lib.ptr(t),
+            ctypes.c_longlong(t.numel()), ctypes.c_longlong(self.slot_bytes), _lib.ptr(self.state),
+            _lib.ptr(a.status), _lib.stream()), "symm_allreduce_push")
+        return t
 
 
 COPY_DESC_DTYPE = np.dtype([("src_off", "<i8"), ("dst_off", "<i8"), ("src_pitch", "<i8"), ("dst_pitch", "<i8"),

@@ -33,6 +33,7 @@ class TPComm:
         self.rank = rank
         self.sequence_parallel = sequence_parallel and world_size > 1
         self.fused = None  # optional object with ag_gemm / gemm_rs (parallel.fused_tp)
+        self.peer_ar = None  # optional parallel.symm.PeerAllReduce for small bf16 messages (decode steps)
 
     # forward direction ---------------------------------------------------------------------------
     def gather_seq(self, x: torch.Tensor) -> torch.Tensor:
@@ -52,8 +53,7 @@ class TPComm:
                               dtype=y.dtype)
             dist.reduce_scatter_tensor(out, y.contiguous(), group=self.group)
             return out
-        dist.all_reduce(y, group=self.group)
-        return y
+        return self.all_reduce(y)
 
     # backward direction (transposes of the above) -----------------------------------------------------
     def gather_seq_bwd(self, dx_full: torch.Tensor) -> torch.Tensor:
@@ -65,6 +65,8 @@ class TPComm:
         return self.gather_seq(dy)
 
     def all_reduce(self, t: torch.Tensor, op=None) -> torch.Tensor:
+        if self.world_size > 1 and op is None and self.peer_ar is not None and self.peer_ar.fits(t):
+            return self.peer_ar.all_reduce(t)      # one peer-memory kernel instead of a library collective
         if self.world_size > 1:
             dist.all_reduce(t, op=op or dist.ReduceOp.SUM, group=self.group)
         return t

@@ -239,6 +239,23 @@ def weights_from_buffer(cfg: TransformerConfig, infer_tp: int, tp_rank: int, pla
                           vocab_start=tp_rank * (cfg.vocab_size // infer_tp))
 
 
+DECODE_ALL_REDUCE_TOKENS = 1024     # largest token count whose hidden states go through the peer-memory all-reduce
+
+
+def attach_peer_all_reduce(comm: TPComm, arena, hidden_size: int) -> None:
+    """Give the rollout's TP communicator the peer-memory all-reduce for decode-sized messages
+    (``MSRL_PEER_ALLREDUCE=0`` keeps the library collective).  Collective over the arena's team: every
+    rank of the job calls it at the same point."""
+    import os
+
+    if arena is None or comm.world_size <= 1 or comm.group is None or os.environ.get("MSRL_PEER_ALLREDUCE", "1") != "1":
+        return
+    need = DECODE_ALL_REDUCE_TOKENS * hidden_size * 2
+    if arena.free_bytes() < 2 * comm.world_size * need + (1 << 20):
+        return
+    comm.peer_ar = arena.make_all_reduce(need, arena.team_ranks(comm.group))
+
+
 class Resharder:
     """Owns the rollout-side parallel state, engine and weight buffer of one worker."""
 
@@ -257,6 +274,7 @@ class Resharder:
                                          backend=train_state.backend, rank_offset=train_state.rank_offset)
         tp_group = self.infer_state.group("tp")
         self.comm = TPComm(tp_group, False, world_size=infer_tp, rank=self.infer_state.rank_in("tp"))
+        attach_peer_all_reduce(self.comm, arena, cfg.hidden_size)
         self.infer_cfg = dataclasses.replace(cfg, tensor_model_parallel_size=infer_tp, sequence_parallel=False)
         self.engine = engine_factory(self.infer_cfg, self.comm if infer_tp > 1 else None)
         self.buffer: Optional[torch.Tensor] = None

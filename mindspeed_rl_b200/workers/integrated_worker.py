@@ -234,6 +234,11 @@ class IntegratedWorker(BaseWorker):
             # expert-parallel replicas exchange tokens in every forward: their engines step together
             lockstep_group=ps.group("ep") if (tcfg.is_moe and ps.size("ep") > 1) else None)
         resharder = None
+        if not (gc.infer_tensor_parallel_size != tp or ps.size("pp") > 1) and tp > 1:
+            from ..parallel.symm import get_arena
+            from ..reshard.planner import attach_peer_all_reduce
+
+            attach_peer_all_reduce(self.comm, get_arena(), tcfg.hidden_size)   # rollout shares the training TP group
         if gc.infer_tensor_parallel_size != tp or ps.size("pp") > 1:
             from ..reshard.planner import Resharder
 

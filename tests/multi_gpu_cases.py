@@ -101,6 +101,77 @@ def case_collectives(rank, world):
     arena.close()
 
 
+def case_peer_all_reduce(rank, world):
+    """The small-message all-reduce of the decode step: against the library collective (bit-identical
+    results on all ranks), over many consecutive calls with changing sizes (parity double-buffering),
+    in place, replayed from a CUDA graph, and on sub-teams of two when there are four ranks or more."""
+    from mindspeed_rl_b200.parallel.symm import SymmetricArena
+
+    arena = SymmetricArena(256 << 20)
+    ar = arena.make_all_reduce(1024 * 3584 * 2)
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    for call, tokens in enumerate([256, 1, 8, 512, 1024, 3, 256, 256, 64, 1000]):
+        x = torch.randn(tokens, 3584, device="cuda", generator=g).bfloat16()
+        want = x.float()
+        dist.all_reduce(want)
+        got = ar.all_reduce(x.clone())
+        arena.check()
+        assert torch.allclose(got.float(), want, atol=2e-2 * world, rtol=2e-2), (call, (got.float() - want).abs().max())
+        every = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(every, got)
+        assert all(torch.equal(every[0], e) for e in every), f"call {call}: ranks disagree bit-wise"
+    assert not ar.fits(torch.empty(2048, 3584, device="cuda", dtype=torch.bfloat16))
+    # CUDA-graph replay: the launch reads its sequence number from device memory
+    static = torch.zeros(256, 3584, device="cuda", dtype=torch.bfloat16)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ar.all_reduce(static)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ar.all_reduce(static)
+        ar.all_reduce(static)
+    for it in range(5):
+        static.fill_(float(rank + it))
+        graph.replay()
+        arena.check()
+        s1 = sum(r + it for r in range(world))
+        assert torch.all(static.float() == float(s1 * world)), (it, static[0, 0])
+    if world >= 4:
+        pair = [rank - rank % 2, rank - rank % 2 + 1]
+        sub = arena.make_all_reduce(64 * 1024, pair)
+        y = torch.full((8, 1024), float(rank), device="cuda", dtype=torch.bfloat16)
+        sub.all_reduce(y)
+        arena.check()
+        assert torch.all(y.float() == float(pair[0] + pair[1]))
+
+    def timed(fn, iters=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    for tokens in (64, 256, 512):
+        x = torch.randn(tokens, 3584, device="cuda").bfloat16()
+        t_peer = timed(lambda: ar.all_reduce(x))
+        t_nccl = timed(lambda: dist.all_reduce(x))
+        if rank == 0:
+            print(f"TIMING all_reduce world={world} tokens={tokens} ({tokens * 7168 / 1e6:.2f} MB) "
+                  f"peer={t_peer * 1e3:.1f}us nccl={t_nccl * 1e3:.1f}us", flush=True)
+    arena.check()
+    arena.close()
+
+
 def case_reshard(rank, world):
     """Train TP=world -> rollout TP=1 and TP=world/2 through the copy-plan kernel vs the torch executor."""
     from mindspeed_rl_b200.models.gpt import GPTModel
@@ -454,7 +525,7 @@ def case_arena_fallback(rank, world):
     assert float(x[0]) == rank + 1
 
 
-CASES = {"arena_fallback": case_arena_fallback, "moe_dispatch_timing": case_moe_dispatch_timing, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+CASES = {"peer_all_reduce": case_peer_all_reduce, "arena_fallback": case_arena_fallback, "moe_dispatch_timing": case_moe_dispatch_timing, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

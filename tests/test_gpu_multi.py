@@ -78,3 +78,11 @@ def test_arena_setup_failure_is_collective():
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_tp_model_with_fused_linears():
     _run("tp_model", 2)
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_peer_memory_all_reduce_for_decode():
+    out = _run("peer_all_reduce", 2)
+    print([l for l in out.splitlines() if l.startswith("TIMING")])
+    if _n_gpus() >= 4:
+        _run("peer_all_reduce", 4)
