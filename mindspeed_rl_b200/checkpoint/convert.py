@@ -123,6 +123,69 @@ def _layer_split(num_layers: int, pp: int, num_layer_list: Optional[List[int]] =
     return out
 
 
+# ---- multi-head latent attention (DeepSeek) ---------------------------------------------------
+# Hugging Face stores the rotary slice of a head with (even, odd) pairs interleaved; the kernels here
+# rotate halves, so the rotary rows are reordered on the way in and back on the way out.  The tensor
+# names come from the architecture's name table (``reshard.weight_adaptor``).
+def _rope_perm(d: int, inverse: bool = False) -> torch.Tensor:
+    perm = torch.cat([torch.arange(0, d, 2), torch.arange(1, d, 2)])
+    return torch.argsort(perm) if inverse else perm
+
+
+def _mla_reorder(name: str, w: torch.Tensor, cfg, inverse: bool) -> torch.Tensor:
+    nope, rope = cfg.qk_head_dim, cfg.qk_pos_emb_head_dim
+    perm = _rope_perm(rope, inverse)
+    if name.endswith(("q_b_proj.weight", "q_proj.weight")):
+        v = w.view(-1, nope + rope, w.shape[-1]).clone()          # [heads, nope + rope, in]
+        v[:, nope:] = v[:, nope:][:, perm]
+        return v.reshape(w.shape)
+    if name.endswith("kv_a_proj_with_mqa.weight"):
+        out = w.clone()
+        out[cfg.kv_lora_rank:] = w[cfg.kv_lora_rank:][perm]
+        return out
+    return w
+
+
+_MLA_HF = ("q_a_proj.weight", "q_a_layernorm.weight", "q_b_proj.weight", "kv_a_proj_with_mqa.weight",
+           "kv_a_layernorm.weight", "kv_b_proj.weight")
+
+
+def _mla_hf_to_mcore(hf, sd, src: str, dst: str, layer: int, local: int, cfg, tp: int, t: int) -> None:
+    from ..reshard.weight_adaptor import get_weight_adaptor
+
+    ad = get_weight_adaptor("DeepseekV3ForCausalLM")
+    for tail in _MLA_HF:
+        name = src + "self_attn." + tail
+        if name not in hf:
+            continue
+        target = ad.replace_name_i2t(name).replace(f"layers.{layer}.", f"layers.{local}.", 1)
+        w = _mla_reorder(name, hf[name], cfg, inverse=False)
+        sd[target] = shard_rows(w, tp, t) if tail in ("q_b_proj.weight", "kv_b_proj.weight") else w.clone()
+    if src + "self_attn.q_proj.weight" in hf:       # no query bottleneck (DeepSeek-V2-Lite)
+        w = _mla_reorder(src + "self_attn.q_proj.weight", hf[src + "self_attn.q_proj.weight"], cfg, inverse=False)
+        sd[dst + "self_attention.linear_q_proj.weight"] = shard_rows(w, tp, t)
+    sd[dst + "self_attention.linear_proj.weight"] = shard_cols(hf[src + "self_attn.o_proj.weight"], tp, t)
+
+
+def _mla_mcore_to_hf(shards, hf, src: str, dst: str, layer: int, local: int, p: int, cfg, tp: int) -> None:
+    from ..reshard.weight_adaptor import get_weight_adaptor
+
+    ad = get_weight_adaptor("DeepseekV3ForCausalLM")
+    s0 = shards[(0, p, 0)]
+    for key in list(s0):
+        if not key.startswith(src + "self_attention.") or key.endswith("linear_proj.weight"):
+            continue
+        if key.endswith("linear_q_proj.weight"):
+            name = dst + "self_attn.q_proj.weight"
+        else:
+            name = ad.replace_name_t2i(key.replace(f"layers.{local}.", f"layers.{layer}.", 1))
+        split = key.endswith(("linear_q_up_proj.weight", "linear_kv_up_proj.weight", "linear_q_proj.weight"))
+        w = torch.cat([shards[(t, p, 0)][key] for t in range(tp)], 0) if split else s0[key]
+        hf[name] = _mla_reorder(name, w, cfg, inverse=True).contiguous()
+    hf[dst + "self_attn.o_proj.weight"] = torch.cat(
+        [shards[(t, p, 0)][src + "self_attention.linear_proj.weight"] for t in range(tp)], 1)
+
+
 # ----------------------------------------------------------------------------------------------
 # HF -> mcore
 # ----------------------------------------------------------------------------------------------
@@ -150,19 +213,25 @@ def hf_to_mcore(hf: Dict[str, torch.Tensor], cfg, tp: int = 1, pp: int = 1, ep: 
                     src, dst = f"model.layers.{layer}.", f"decoder.layers.{local}."
                     sd[dst + "input_layernorm.weight"] = hf[src + "input_layernorm.weight"].clone()
                     sd[dst + "pre_mlp_layernorm.weight"] = hf[src + "post_attention_layernorm.weight"].clone()
-                    qkv = qkv_hf_to_mcore(hf[src + "self_attn.q_proj.weight"], hf[src + "self_attn.k_proj.weight"],
-                                          hf[src + "self_attn.v_proj.weight"], nh, nkv, hd)
-                    sd[dst + "self_attention.linear_qkv.weight"] = shard_qkv(qkv, nkv, tp, t)
-                    if src + "self_attn.q_proj.bias" in hf:
-                        qb = qkv_hf_to_mcore(hf[src + "self_attn.q_proj.bias"], hf[src + "self_attn.k_proj.bias"],
-                                             hf[src + "self_attn.v_proj.bias"], nh, nkv, hd)
-                        sd[dst + "self_attention.linear_qkv.bias"] = shard_qkv(qb, nkv, tp, t)
-                    sd[dst + "self_attention.linear_proj.weight"] = shard_cols(hf[src + "self_attn.o_proj.weight"], tp, t)
+                    mla = src + "self_attn.kv_a_proj_with_mqa.weight" in hf
+                    if mla:
+                        _mla_hf_to_mcore(hf, sd, src, dst, layer, local, cfg, tp, t)
+                    else:
+                        qkv = qkv_hf_to_mcore(hf[src + "self_attn.q_proj.weight"], hf[src + "self_attn.k_proj.weight"],
+                                              hf[src + "self_attn.v_proj.weight"], nh, nkv, hd)
+                        sd[dst + "self_attention.linear_qkv.weight"] = shard_qkv(qkv, nkv, tp, t)
+                        if src + "self_attn.q_proj.bias" in hf:
+                            qb = qkv_hf_to_mcore(hf[src + "self_attn.q_proj.bias"], hf[src + "self_attn.k_proj.bias"],
+                                                 hf[src + "self_attn.v_proj.bias"], nh, nkv, hd)
+                            sd[dst + "self_attention.linear_qkv.bias"] = shard_qkv(qb, nkv, tp, t)
+                        sd[dst + "self_attention.linear_proj.weight"] = shard_cols(hf[src + "self_attn.o_proj.weight"], tp, t)
                     if src + "self_attn.q_norm.weight" in hf:
                         sd[dst + "self_attention.q_layernorm.weight"] = hf[src + "self_attn.q_norm.weight"].clone()
                         sd[dst + "self_attention.k_layernorm.weight"] = hf[src + "self_attn.k_norm.weight"].clone()
                     if src + "mlp.gate.weight" in hf:      # MoE layer
                         sd[dst + "mlp.router.weight"] = hf[src + "mlp.gate.weight"].clone()
+                        if src + "mlp.gate.e_score_correction_bias" in hf:
+                            sd[dst + "mlp.router.expert_bias"] = hf[src + "mlp.gate.e_score_correction_bias"].float().clone()
                         ep_rank = (e * tp + t) if moe_tp_extend_ep else e
                         per = n_exp // ep_total
                         w1, w2 = [], []
@@ -244,19 +313,24 @@ def mcore_to_hf(shards: Dict[tuple, Dict[str, torch.Tensor]], cfg, tp: int = 1, 
             s0 = shards[(0, p, 0)]
             hf[dst + "input_layernorm.weight"] = s0[src + "input_layernorm.weight"]
             hf[dst + "post_attention_layernorm.weight"] = s0[src + "pre_mlp_layernorm.weight"]
-            q, k, v = qkv_mcore_to_hf(cat(src + "self_attention.linear_qkv.weight", p, 0), nh, nkv, hd)
-            hf[dst + "self_attn.q_proj.weight"], hf[dst + "self_attn.k_proj.weight"], \
-                hf[dst + "self_attn.v_proj.weight"] = q.contiguous(), k.contiguous(), v.contiguous()
-            if src + "self_attention.linear_qkv.bias" in s0:
-                qb, kb, vb = qkv_mcore_to_hf(cat(src + "self_attention.linear_qkv.bias", p, 0), nh, nkv, hd)
-                hf[dst + "self_attn.q_proj.bias"], hf[dst + "self_attn.k_proj.bias"], \
-                    hf[dst + "self_attn.v_proj.bias"] = qb.contiguous(), kb.contiguous(), vb.contiguous()
-            hf[dst + "self_attn.o_proj.weight"] = cat(src + "self_attention.linear_proj.weight", p, 1)
-            if src + "self_attention.q_layernorm.weight" in s0:
+            if src + "self_attention.linear_kv_down_proj.weight" in s0:
+                _mla_mcore_to_hf(shards, hf, src, dst, layer, local, p, cfg, tp)
+            else:
+                q, k, v = qkv_mcore_to_hf(cat(src + "self_attention.linear_qkv.weight", p, 0), nh, nkv, hd)
+                hf[dst + "self_attn.q_proj.weight"], hf[dst + "self_attn.k_proj.weight"], \
+                    hf[dst + "self_attn.v_proj.weight"] = q.contiguous(), k.contiguous(), v.contiguous()
+                if src + "self_attention.linear_qkv.bias" in s0:
+                    qb, kb, vb = qkv_mcore_to_hf(cat(src + "self_attention.linear_qkv.bias", p, 0), nh, nkv, hd)
+                    hf[dst + "self_attn.q_proj.bias"], hf[dst + "self_attn.k_proj.bias"], \
+                        hf[dst + "self_attn.v_proj.bias"] = qb.contiguous(), kb.contiguous(), vb.contiguous()
+                hf[dst + "self_attn.o_proj.weight"] = cat(src + "self_attention.linear_proj.weight", p, 1)
+            if src + "self_attention.q_layernorm.weight" in s0 and src + "self_attention.k_layernorm.weight" in s0:
                 hf[dst + "self_attn.q_norm.weight"] = s0[src + "self_attention.q_layernorm.weight"]
                 hf[dst + "self_attn.k_norm.weight"] = s0[src + "self_attention.k_layernorm.weight"]
             if src + "mlp.router.weight" in s0:
                 hf[dst + "mlp.gate.weight"] = s0[src + "mlp.router.weight"]
+                if src + "mlp.router.expert_bias" in s0:
+                    hf[dst + "mlp.gate.e_score_correction_bias"] = s0[src + "mlp.router.expert_bias"]
                 per = n_exp // ep_total
                 f_e = cfg.moe_ffn_hidden_size
                 for t in range(tp if moe_tp_extend_ep else 1):

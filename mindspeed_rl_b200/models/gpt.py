@@ -146,7 +146,12 @@ class TransformerLayer(nn.Module):
         self.comm = comm
         dt = cfg.params_dtype
         self.input_layernorm = _Holder(torch.ones(cfg.hidden_size, dtype=dt, device=device))
-        self.self_attention = SelfAttention(cfg, device, gen)
+        if cfg.multi_latent_attention:
+            from .mla import MLASelfAttention
+
+            self.self_attention = MLASelfAttention(cfg, device, gen)
+        else:
+            self.self_attention = SelfAttention(cfg, device, gen)
         self.pre_mlp_layernorm = _Holder(torch.ones(cfg.hidden_size, dtype=dt, device=device))
         if cfg.layer_is_moe(layer_number):
             from .moe import MoELayer
@@ -194,16 +199,23 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
     cfg, comm, sa = layer.cfg, layer.comm, layer.self_attention
     eps = cfg.norm_epsilon
     x1, rstd1, _ = ops.rmsnorm_fwd(h, layer.input_layernorm.weight, eps, want_rstd=keep)
-    # column linears = (all-gather tokens ->) GEMM, row linears = GEMM (-> reduce-scatter tokens);
-    # ``comm`` runs each pair as one fused kernel when it can
-    qkv, x1g = comm.column_linear(x1, sa.linear_qkv.weight, sa.linear_qkv.bias)
     lo: Dict[str, torch.Tensor] = {}      # adapter intermediates (only for adapted linears)
-    if lora.active(sa.linear_qkv):
-        lo["qkv"] = lora.column_fwd(sa.linear_qkv, x1g, qkv)
-    attn, lse, pre, rq, rk = _attention_core_fwd(layer, qkv, meta)
-    proj = comm.row_linear(attn, sa.linear_proj.weight)
-    if lora.active(sa.linear_proj):
-        lo["proj"] = lora.row_fwd(sa.linear_proj, attn, proj, comm)[1]
+    qkv = attn = lse = pre = rq = rk = None
+    if cfg.multi_latent_attention:
+        # latent attention: one differentiable block, re-run in the backward (only its input is kept)
+        x1g = comm.gather_seq(x1)
+        with torch.no_grad():
+            proj = comm.reduce_out(sa(x1g, meta))
+    else:
+        # column linears = (all-gather tokens ->) GEMM, row linears = GEMM (-> reduce-scatter tokens);
+        # ``comm`` runs each pair as one fused kernel when it can
+        qkv, x1g = comm.column_linear(x1, sa.linear_qkv.weight, sa.linear_qkv.bias)
+        if lora.active(sa.linear_qkv):
+            lo["qkv"] = lora.column_fwd(sa.linear_qkv, x1g, qkv)
+        attn, lse, pre, rq, rk = _attention_core_fwd(layer, qkv, meta)
+        proj = comm.row_linear(attn, sa.linear_proj.weight)
+        if lora.active(sa.linear_proj):
+            lo["proj"] = lora.row_fwd(sa.linear_proj, attn, proj, comm)[1]
     h1 = ops.add(h, proj)
     x2, rstd2, _ = ops.rmsnorm_fwd(h1, layer.pre_mlp_layernorm.weight, eps, want_rstd=keep)
     if isinstance(layer.mlp, MLP):
@@ -230,7 +242,7 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
 def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMeta, dh2: torch.Tensor
                    ) -> torch.Tensor:
     cfg, comm, sa = layer.cfg, layer.comm, layer.self_attention
-    lay = sa.layout
+    lay = getattr(sa, "layout", None)
     # ---- MLP ----
     if isinstance(layer.mlp, MLP):
         gu, y = ctx["mlp_ctx"]
@@ -253,6 +265,10 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
     dh1 = ops.rmsnorm_bwd(dx2, ctx["h1"], layer.pre_mlp_layernorm.weight, ctx["rstd2"],
                           grad_buffer(layer.pre_mlp_layernorm.weight), dres=dh2)
     # ---- attention ----
+    if cfg.multi_latent_attention:
+        dx1 = _mla_backward(sa, ctx["x1g"], meta, comm, dh1)
+        return ops.rmsnorm_bwd(dx1, ctx["h"], layer.input_layernorm.weight, ctx["rstd1"],
+                               grad_buffer(layer.input_layernorm.weight), dres=dh1)
     lo = ctx.get("lora") or {}
     dattn, d_proj = comm.row_linear_bwd(dh1, sa.linear_proj.weight)
     if "proj" in lo:
@@ -278,6 +294,21 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
     dh = ops.rmsnorm_bwd(dx1, ctx["h"], layer.input_layernorm.weight, ctx["rstd1"],
                          grad_buffer(layer.input_layernorm.weight), dres=dh1)
     return dh
+
+
+def _mla_backward(sa, x1g: torch.Tensor, meta: PackedMeta, comm: TPComm, dh1: torch.Tensor) -> torch.Tensor:
+    """Backward of the latent-attention block: re-run it with autograd on, feed the gathered output
+    gradient, add the parameter gradients to their buffers and return the input gradient (token
+    shard under sequence parallelism)."""
+    d_full = comm.reduce_out_bwd(dh1)
+    params = [p for p in sa.parameters() if p.requires_grad]
+    with torch.enable_grad():
+        x = x1g.detach().requires_grad_(True)
+        y = sa(x, meta)
+        grads = torch.autograd.grad(y, [x] + params, d_full)
+    for p, g in zip(params, grads[1:]):
+        accum_vec(p, g)
+    return comm.gather_seq_bwd(grads[0])
 
 
 class _LayerFn(torch.autograd.Function):

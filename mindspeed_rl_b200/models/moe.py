@@ -55,15 +55,18 @@ class _Experts(nn.Module):
         self.weight2 = nn.Parameter(w2)
 
 
-def route(logits: torch.Tensor, cfg) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def route(logits: torch.Tensor, cfg, expert_bias: Optional[torch.Tensor] = None
+          ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Router logits ``[T, E]`` (fp32) -> ``(top-k probabilities [T, k], expert ids [T, k], full
-    score matrix [T, E])``; differentiable w.r.t. ``logits``."""
+    score matrix [T, E])``; differentiable w.r.t. ``logits``.  ``expert_bias`` (load balancing without
+    an auxiliary loss, ``moe_router_enable_expert_bias``) shifts the scores for the CHOICE of experts
+    only; the combine weights stay the unbiased scores."""
     k = cfg.moe_router_topk
     if cfg.moe_router_score_function == "sigmoid":
         scores = torch.sigmoid(logits)
     else:
         scores = torch.softmax(logits, dim=-1)
-    pick = scores
+    pick = scores if expert_bias is None else scores.detach() + expert_bias.to(scores.dtype)
     if cfg.moe_router_num_groups and cfg.moe_router_group_topk:
         t, e = scores.shape
         g = cfg.moe_router_num_groups
@@ -106,6 +109,10 @@ class MoELayer(nn.Module):
         dt, std = cfg.params_dtype, cfg.init_method_std
         out_std = std / math.sqrt(2.0 * cfg.num_layers)
         self.router = _W(_normal((e, h), std, torch.float32, device, gen))
+        if cfg.moe_router_enable_expert_bias:
+            # not trained by gradients: nudged after every optimizer step towards an even load
+            self.router.register_buffer("expert_bias", torch.zeros(e, dtype=torch.float32, device=device))
+            self._load_since_update = torch.zeros(e, dtype=torch.float32, device=device)
         self.experts = _Experts(_normal((h, self.num_local * 2 * f), std, dt, device, gen),
                                 _normal((self.num_local * f, h), out_std, dt, device, gen))
         self.shared_experts = None
@@ -115,6 +122,19 @@ class MoELayer(nn.Module):
             self.shared_experts = MLP(cfg, device, gen, ffn=f * cfg.n_shared_experts)
         self.last_aux_loss: Optional[torch.Tensor] = None
         self.token_counts: Optional[torch.Tensor] = None   # per-expert routed tokens (EPLB statistics)
+
+    @torch.no_grad()
+    def update_expert_bias(self, rate: float = 1e-3, group=None) -> None:
+        """Auxiliary-loss-free balancing: after an optimizer step, raise the bias of experts that got
+        fewer tokens than the mean since the last update and lower it for the others (all ranks of
+        ``group`` see the same global load)."""
+        if not self.cfg.moe_router_enable_expert_bias:
+            return
+        load = self._load_since_update
+        if group is not None and dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(load, group=group)
+        self.router.expert_bias += rate * torch.sign(load.mean() - load)
+        load.zero_()
 
     # ------------------------------------------------------------------------------------------
     def _w1(self) -> torch.Tensor:
@@ -237,11 +257,13 @@ class MoELayer(nn.Module):
         with torch.enable_grad():
             xr = x.detach().float().requires_grad_(keep)
             logits = torch.matmul(xr, self.router.weight.t())
-            top_p, top_idx, scores = route(logits, cfg)
+            top_p, top_idx, scores = route(logits, cfg, getattr(self.router, "expert_bias", None))
             aux = aux_loss(scores, top_idx, cfg.num_experts, cfg.moe_router_topk, cfg.moe_aux_loss_coeff) \
                 if (keep and cfg.moe_aux_loss_coeff) else None
         self.last_aux_loss = aux.detach() if aux is not None else None
         self.token_counts = torch.bincount(top_idx.reshape(-1), minlength=cfg.num_experts)
+        if cfg.moe_router_enable_expert_bias and torch.is_grad_enabled():
+            self._load_since_update += self.token_counts.float()
         if self.ep_size == 1:
             return self._forward_local(x, xr, top_p, top_idx, aux, comm, keep)
         disp = self._p2p_dispatcher(x)
@@ -457,5 +479,7 @@ class MoELayer(nn.Module):
 
         return MoEWeights(self.cfg, self.router.weight.data, self._w1().data, self._w2().data,
                           self.ep_group, self.ep_size, self.ep_rank, p2p=self._p2p_dispatcher,
+                          expert_bias=getattr(self.router, "expert_bias", None),
+                          collect_counts=bool(getattr(self, "collect_rollout_counts", False)),
                           shared=(self.shared_experts.linear_fc1.weight.data,
                                   self.shared_experts.linear_fc2.weight.data) if self.shared_experts else None)

@@ -325,6 +325,10 @@ class TrainingEngine:
         if self.optimizer is None:
             return True, 0.0, 0
         result = self.optimizer.step()
+        if getattr(self.core.cfg, "moe_router_enable_expert_bias", False):
+            for layer in self.core.decoder.layers:
+                if hasattr(layer.mlp, "update_expert_bias"):
+                    layer.mlp.update_expert_bias(group=self.dp_group)
         fused = getattr(self.core.comm, "fused", None)
         if fused is not None:
             fused.invalidate_weights()       # cached transposed weights are stale now

@@ -36,6 +36,13 @@ class TransformerConfig:
     moe_router_enable_expert_bias: bool = False
     moe_router_num_groups: Optional[int] = None
     moe_router_group_topk: Optional[int] = None
+    # multi-head latent attention (DeepSeek): low-rank query / key-value bottlenecks
+    multi_latent_attention: bool = False
+    q_lora_rank: Optional[int] = None
+    kv_lora_rank: Optional[int] = None
+    qk_head_dim: int = 128                # non-rotary part of a query / key head
+    qk_pos_emb_head_dim: int = 64         # rotary part
+    v_head_dim: int = 128
     # rope scaling (YaRN); None = plain RoPE
     rope_scaling: Optional[dict] = None
     # numerics / memory
@@ -62,6 +69,12 @@ class TransformerConfig:
             self.kv_channels = self.hidden_size // self.num_attention_heads
         if self.num_query_groups is None:
             self.num_query_groups = self.num_attention_heads
+        if self.multi_latent_attention:
+            if not self.kv_lora_rank:
+                raise ValueError("multi_latent_attention needs kv_lora_rank")
+            # the rollout engine stores full per-head keys (one KV head per query head)
+            self.num_query_groups = self.num_attention_heads
+            self.kv_channels = self.qk_head_dim + self.qk_pos_emb_head_dim
 
     @property
     def head_dim(self) -> int:
@@ -106,6 +119,11 @@ class TransformerConfig:
             moe_router_num_groups=cfg.moe_router_num_groups,
             moe_router_group_topk=cfg.moe_router_group_topk,
             rope_scaling=rope_scaling,
+            multi_latent_attention=bool(getattr(cfg, "multi_latent_attention", False)),
+            q_lora_rank=getattr(cfg, "q_lora_rank", None), kv_lora_rank=getattr(cfg, "kv_lora_rank", None),
+            qk_head_dim=getattr(cfg, "qk_head_dim", None) or 128,
+            qk_pos_emb_head_dim=getattr(cfg, "qk_pos_emb_head_dim", None) or 64,
+            v_head_dim=getattr(cfg, "v_head_dim", None) or 128,
             params_dtype=torch.bfloat16 if cfg.bf16 else torch.float32,
             recompute_granularity=cfg.recompute_granularity, recompute_method=cfg.recompute_method,
             recompute_num_layers=cfg.recompute_num_layers,

@@ -34,6 +34,7 @@ class LayerWeights:
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
     moe: Optional[object] = None      # rollout.moe.MoEWeights for expert layers
+    mla: Optional[object] = None      # models.mla.MLASelfAttention of a latent-attention layer (replaces qkv_w)
 
 
 @dataclass
@@ -93,7 +94,7 @@ class ModelRunner:
 
     @staticmethod
     def _signature(w: RolloutWeights):
-        return (w.embed.data_ptr(), w.lm_head.data_ptr(), tuple(l.qkv_w.data_ptr() for l in w.layers))
+        return (w.embed.data_ptr(), w.lm_head.data_ptr(), tuple((l.qkv_w if l.qkv_w is not None else l.o_w).data_ptr() for l in w.layers))
 
     def bind_cache(self, cache: Optional[KVCache]) -> None:
         self.cache = cache
@@ -122,15 +123,19 @@ class ModelRunner:
         x, _, resid = ops.rmsnorm_fwd(delta, lw.input_norm, cfg.norm_epsilon, residual=resid,
                                       want_rstd=False) if resid is not None else \
             (*ops.rmsnorm_fwd(delta, lw.input_norm, cfg.norm_epsilon, want_rstd=False)[:2], delta)
-        if lw.qkv_b is not None:
-            qkv = torch.addmm(lw.qkv_b, x, lw.qkv_w.t())
-        else:
-            qkv = torch.matmul(x, lw.qkv_w.t())
         lay = self.weights.qkv_layout
-        if lw.q_norm is not None:
-            ops.headnorm_fwd_(qkv, lay, "q", lw.q_norm, cfg.norm_epsilon)
-            ops.headnorm_fwd_(qkv, lay, "k", lw.k_norm, cfg.norm_epsilon)
-        ops.rope_(qkv, lay, positions, self.rope_table())
+        if lw.mla is not None:
+            # latent attention: full per-head q / k / v (rotary and soft-max scale already applied)
+            qkv = lw.mla.rollout_qkv(x, positions)
+        else:
+            if lw.qkv_b is not None:
+                qkv = torch.addmm(lw.qkv_b, x, lw.qkv_w.t())
+            else:
+                qkv = torch.matmul(x, lw.qkv_w.t())
+            if lw.q_norm is not None:
+                ops.headnorm_fwd_(qkv, lay, "q", lw.q_norm, cfg.norm_epsilon)
+                ops.headnorm_fwd_(qkv, lay, "k", lw.k_norm, cfg.norm_epsilon)
+            ops.rope_(qkv, lay, positions, self.rope_table())
         attn = attend(li, qkv, lay)
         delta = self.comm.all_reduce(torch.matmul(attn, lw.o_w.t()))
         x, _, resid = ops.rmsnorm_fwd(delta, lw.post_norm, cfg.norm_epsilon, residual=resid,

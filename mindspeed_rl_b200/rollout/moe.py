@@ -22,7 +22,8 @@ from ..models.moe import route
 class MoEWeights:
     def __init__(self, cfg, router_w: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, ep_group=None,
                  ep_size: int = 1, ep_rank: int = 0, shared: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                 log2phy: Optional[torch.Tensor] = None, collect_counts: bool = False, p2p=None):
+                 log2phy: Optional[torch.Tensor] = None, collect_counts: bool = False, p2p=None,
+                 expert_bias: Optional[torch.Tensor] = None):
         """``w1 [H, E_local, 2F]``, ``w2 [E_local, F, H]`` (views are fine)."""
         self.cfg = cfg
         self.router_w, self.w1, self.w2 = router_w, w1, w2
@@ -32,6 +33,7 @@ class MoEWeights:
         self.p2p = p2p                      # callable(x) -> peer-memory dispatcher of the EP group, or None
         self.log2phy = log2phy              # [E_logical, max_replicas] physical ids (-1 padded) or None
         self.collect_counts = collect_counts
+        self.expert_bias = expert_bias      # selection bias of aux-loss-free balancing, or None
         self.counts = torch.zeros(cfg.num_experts, dtype=torch.int64)
 
     def _physical(self, top_idx: torch.Tensor) -> torch.Tensor:
@@ -48,7 +50,7 @@ class MoEWeights:
         cfg = self.cfg
         t, k = x.shape[0], cfg.moe_router_topk
         logits = torch.matmul(x.float(), self.router_w.float().t())
-        top_p, top_idx, _ = route(logits, cfg)
+        top_p, top_idx, _ = route(logits, cfg, self.expert_bias)
         if self.collect_counts:
             self.counts += torch.bincount(top_idx.reshape(-1).cpu(), minlength=cfg.num_experts)
         phys = self._physical(top_idx)

@@ -164,6 +164,11 @@ class IntegratedWorker(BaseWorker):
                 ps.get_pipeline_model_parallel_next_rank(), tcfg.hidden_size, dtype, self.device,
                 seq_shard=tp if (ac.sequence_parallel and tp > 1) else 1)
         core = GPTModel(tcfg, self.comm, device=self.device, seed=self.seed, **stage_kw)
+        if tcfg.is_moe and gc.eplb_token_collects:
+            # expert-load statistics of the rollout (input of cli/eplb_generate_map.py)
+            for layer in core.decoder.layers:
+                if hasattr(layer.mlp, "rollout_view"):
+                    layer.mlp.collect_rollout_counts = True
         dp = ps.size("dp_cp")
         self._maybe_init_arena(core, bool(ac.accumulate_allreduce_grads_in_fp32))
         self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
@@ -332,10 +337,26 @@ class IntegratedWorker(BaseWorker):
         finally:
             self.td = main_td
             self._state = train_state
+        self._dump_expert_load()
         if not held:
             t_exit = self.sharding_manager.exit_infer_mode()
             self.update_metrics("timing/resharding_exit_infer", [t_exit])
             self.update_metrics("timing/resharding_to_infer", [self._t_enter + t_exit])
+
+    def _dump_expert_load(self) -> None:
+        """``generate_config.eplb_token_collects``: write the tokens every expert received during this
+        rollout to ``eplb_token_save_path/eplb_token_collects_<rank>.json`` (one entry per MoE layer)."""
+        gc = self.generate_config
+        weights = getattr(self.engine.runner, "weights", None)
+        if not (self.tcfg.is_moe and gc.eplb_token_collects and weights is not None):
+            return
+        import os
+
+        os.makedirs(gc.eplb_token_save_path, exist_ok=True)
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        for li, lw in enumerate(weights.layers):
+            if lw.moe is not None and lw.moe.collect_counts:
+                lw.moe.dump_counts(gc.eplb_token_save_path, li, rank)
 
     def _generate_batch(self, batch: Dict[str, torch.Tensor], idx: List[int], n: int) -> None:
         prompts, plen = batch["prompts"], batch["prompt_length"].reshape(-1)

@@ -30,6 +30,8 @@ def _shard_state(full, cfg, tp, r):
         elif k.endswith("linear_fc1.weight"):
             g, u = v.chunk(2, 0)
             out[k] = C.shard_fc1(g, u, tp, r)
+        elif k.endswith(("linear_q_up_proj.weight", "linear_kv_up_proj.weight", "linear_q_proj.weight")):
+            out[k] = C.shard_rows(v, tp, r)          # latent attention: head-major rows
         elif k.endswith("linear_proj.weight") or k.endswith("linear_fc2.weight"):
             out[k] = C.shard_cols(v, tp, r)
         elif k.endswith("word_embeddings.weight") or k.endswith("output_layer.weight"):
@@ -443,6 +445,46 @@ def _tp_grad_sync_worker(rank, world):
     full_norm = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in full.parameters()))
     norm = torch.sqrt(opt.compute_grad_norm())
     assert torch.allclose(norm.reshape(()), full_norm, rtol=1e-4), (float(norm), float(full_norm))
+
+
+def _mla_tp_worker(rank, world):
+    """Latent attention under TP + SP: heads are split, the down-projections and their norms are
+    replicated; their gradients (each rank sees its own heads only) are summed by ``finish_grad_sync``."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+    ps = initialize_model_parallel(tensor_model_parallel_size=world)
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=4,
+              vocab_size=64, params_dtype=torch.float32, max_position_embeddings=128, multi_latent_attention=True,
+              q_lora_rank=12, kv_lora_rank=8, qk_head_dim=8, qk_pos_emb_head_dim=8, v_head_dim=8)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=5)
+    cfg = TransformerConfig(tensor_model_parallel_size=world, sequence_parallel=True, **kw)
+    comm = TPComm(ps.group("tp"), True, world_size=world, rank=rank)
+    core = GPTModel(cfg, comm, device="cpu")
+    core.load_state_dict(_shard_state(full.state_dict(), cfg, world, rank))
+    model = DistributedDataParallel(core, None, 1)
+    model.attach_tensor_parallel(ps.group("tp"), world, True)
+    meta = PackedMeta.from_lengths([6, 10], "cpu", align=world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator().manual_seed(1)
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    ref = full.forward_logprob(ids, labels, meta, 1.0, False)[0]
+    (ref * w).sum().backward()
+    got = core.forward_logprob(ids, labels, meta, 1.0, False)[0]
+    assert torch.allclose(got, ref, atol=1e-4), (got - ref).abs().max()
+    (got * w).sum().backward()
+    model.finish_grad_sync()
+    want = _shard_state({n: (p.grad if p.grad is not None else p.main_grad) for n, p in full.named_parameters()},
+                        cfg, world, rank)
+    for n, p in core.named_parameters():
+        have = p.main_grad if p.grad is None else p.main_grad + p.grad
+        assert torch.allclose(have, want[n], atol=2e-4, rtol=1e-3), (n, (have - want[n]).abs().max())
+
+
+def test_latent_attention_tensor_parallel_matches_single_rank():
+    run_distributed(_mla_tp_worker, 2)
 
 
 def test_tp_replicated_grad_sync_and_norm():
