@@ -45,6 +45,12 @@ constexpr int EPI_PITCH = 144;
 constexpr uint32_t EPI_BYTES = 4 * 32 * EPI_PITCH;
 enum { ERR_FULL = 31, ERR_EMPTY = 32, ERR_ACC = 33 };
 enum OutMode { OUT_BF16 = 0, OUT_ACC_F32 = 1, OUT_ACC_BF16 = 2 };
+enum CommMode { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
+enum { ERR_GATHER = 34, ERR_PEERS = 35 };
+constexpr int MAX_RANKS = 16;
+constexpr int COMM_THREADS = 128;     // four extra warps move data over NVLink while the tensor cores work
+constexpr int AG_PIECES = 16;         // a 128-row unit is gathered as 16 pieces of 8 rows
+constexpr int RS_CHUNKS = 16;         // a 128-row unit is reduced as 16 column chunks
 
 struct Params {
   int M, N, K;
@@ -53,6 +59,19 @@ struct Params {
   const __nv_bfloat16* bias;   // OUT_BF16 only, may be null
   int* error;
   int flags;                   // experiment switches (MSRL_G2_FLAGS): 1 fence per stage, 4 no stores, bits 4-7 ring depth
+  // communication-fused variants (tensor-parallel linears under sequence parallelism)
+  int rank, world;
+  int m_local;                 // rows owned by one rank (multiple of 256); M = world * m_local
+  void* peer[MAX_RANKS];       // AG: every rank's A shard [m_local, K]; RS: every rank's staging area
+                               //     [world, m_local, N] bf16 (slot s holds rank s's partial sums)
+  unsigned int* peer_flag[MAX_RANKS];   // RS: every rank's arrival counters, one per 128-row unit
+  long long ld_peer;           // AG: leading dimension of the peers' shards
+  __nv_bfloat16* gathered;     // AG: local [M, K] buffer the shards are pulled into
+  unsigned int* tile_ready;    // AG: local piece counters, one per 128-row unit (zeroed before launch)
+  unsigned int rs_target;      // RS: counter value that means "all partial sums of this call arrived"
+  unsigned int* rs_done;       // RS: reducer units that passed their wait, per 128-row unit
+  __nv_bfloat16* rs_out;       // RS: [m_local, N] reduced output
+  long long ld_out;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -101,6 +120,50 @@ constexpr uint32_t idesc_pair(bool a_mn, bool b_mn) {
 // The pairs working at the same time then share a few column tiles of B and at most GROUP_M row tiles
 // of A (about 29 MB at K = 3584), which stay in L2 while the panel sweeps over all of B.
 constexpr int GROUP_M = 16;
+// Communication-fused orders.  AG: this rank's own row block first, then the peers' blocks in ring
+// order (the order their shards arrive in), column tiles fastest.  RS: row tile i of every
+// destination rank in turn (starting with the next rank), so that the owners can reduce row tile i
+// while row tile i + 1 is being multiplied.
+__device__ __forceinline__ void tile_coords_ag(int tile, int n_tiles, int rank, int world, int mt_local, int& mt,
+                                               int& nt) {
+  const int per_block = mt_local * n_tiles;
+  const int pos = tile / per_block, rem = tile % per_block;
+  mt = ((rank + pos) % world) * mt_local + rem / n_tiles;
+  nt = rem % n_tiles;
+}
+__device__ __forceinline__ void tile_coords_rs(int tile, int n_tiles, int rank, int world, int mt_local, int& mt,
+                                               int& nt) {
+  const int per_row = n_tiles * world;
+  const int i = tile / per_row, rem = tile % per_row;
+  nt = rem / world;
+  mt = ((rank + 1 + rem % world) % world) * mt_local + i;
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded spin until *p >= target (wrap-around compare); SYS: the counter is bumped by other GPUs.
+template <bool SYS>
+__device__ __forceinline__ bool wait_counter(const unsigned int* p, unsigned int target, int* err, int code) {
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while ((int)((SYS ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p)) - target) < 0) {
+    if ((++polls & 63u) == 0) {
+      if (*reinterpret_cast<volatile int*>(err) != 0) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        atomicCAS(err, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
   const int per_panel = GROUP_M * n_tiles;
   const int panel = tile / per_panel, rem = tile - panel * per_panel;
@@ -110,10 +173,10 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   nt = rem / rows;
 }
 
-template <bool A_MN, bool B_MN, int OUT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+template <bool A_MN, bool B_MN, int OUT, int COMM>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(COMM == COMM_NONE ? 192 : 192 + COMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ Params p) {
+                 const __grid_constant__ CUtensorMap map_a_local, const __grid_constant__ Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -126,6 +189,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int total_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int mt_local = (COMM == COMM_NONE) ? m_tiles : p.m_local / BM;       // row tiles of one rank's block
+  const int units_local = (COMM == COMM_NONE) ? 0 : p.m_local / HM;          // 128-row units of one rank's block
+  auto coords = [&](int tile, int& mt, int& nt) {
+    if (COMM == COMM_AG) tile_coords_ag(tile, n_tiles, p.rank, p.world, mt_local, mt, nt);
+    else if (COMM == COMM_RS) tile_coords_rs(tile, n_tiles, p.rank, p.world, mt_local, mt, nt);
+    else tile_coords(tile, m_tiles, n_tiles, mt, nt);
+  };
   const int RS = ((p.flags >> 4) & 15) ? ((p.flags >> 4) & 15) : STAGES;   // ring depth in use
 
   if (threadIdx.x == 0) {
@@ -158,8 +228,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t full0 = map_to_rank(smem_u32(&full_bar[0]), 0);     // the leader's barriers
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
         int mt, nt;
-        tile_coords(tile, m_tiles, n_tiles, mt, nt);
+        coords(tile, mt, nt);
         const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN + (int)rank * HN;
+        const CUtensorMap* amap = &map_a;
+        int a_row = m0;
+        if (COMM == COMM_AG) {
+          const int unit = m0 / HM;                     // 128-row unit this CTA loads
+          if (unit / units_local == p.rank) {
+            // rows of this rank's own block are read from the shard where it already is: no wait
+            amap = &map_a_local;
+            a_row = (unit % units_local) * HM;
+          } else {
+            // the comm warps of the grid must have landed all pieces of this unit in the gathered buffer
+            ok = wait_counter<false>(p.tile_ready + unit, AG_PIECES, p.error, ERR_GATHER);
+            if (!ok) break;
+            asm volatile("fence.proxy.async;\n" ::: "memory");   // generic-proxy stores -> TMA reads
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % RS;
           const uint32_t use = it / RS;
@@ -175,7 +260,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int i = 0; i < HM / 64; ++i)       // [64 k rows x 64 m columns] blocks of 8 KiB
               tma_load_2d_pair(sa + i * 8192, &map_a, bar, m0 + i * 64, kb * BK);
           } else {
-            tma_load_2d_pair(sa, &map_a, bar, kb * BK, m0);
+            tma_load_2d_pair(sa, amap, bar, kb * BK, a_row);
           }
           if (B_MN) {
 #pragma unroll
@@ -224,7 +309,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         commit_pair(&acc_full[buf]);      // accumulator complete (or abandoned) for both epilogues
       }
     }
-  } else {
+  } else if (warp < 4) {
     // ---------------- epilogue: warp w owns TMEM lanes 32w .. 32w+31 of this CTA's half ----------------
     uint32_t local = 0;
     bool ok = true;
@@ -234,7 +319,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++local) {
       const uint32_t buf = local & 1;
       int mt, nt;
-      tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      coords(tile, mt, nt);
       const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN;
       ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, ERR_ACC) &&
            (*reinterpret_cast<volatile int*>(p.error) == 0);
@@ -244,8 +329,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16) + buf * BN;
       if (OUT == OUT_BF16) {
         __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C);
-        const long long crow0 = m0 + warp * 32;
-        const bool vec_ok = (p.N % 8 == 0) && (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        long long crow0 = m0 + warp * 32, ldc = p.ldc;
+        long long row_limit = p.M;
+        if (COMM == COMM_RS) {
+          // the partial tile goes to slot `rank` of the staging area on the rank that owns these rows
+          const int dest = mt / mt_local;
+          C = reinterpret_cast<__nv_bfloat16*>(p.peer[dest]) + (long long)p.rank * p.m_local * p.N;
+          ldc = p.N;
+          crow0 -= (long long)dest * p.m_local;
+          row_limit = p.m_local;
+        }
+        const bool vec_ok = (p.N % 8 == 0) && (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           if (n0 + c * 64 >= p.N) break;
@@ -271,14 +365,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int r = i * 4 + (lane >> 3);
-              if (crow0 + r < p.M && col < p.N)
-                st8(C + (crow0 + r) * p.ldc + col, *reinterpret_cast<const bf16x8*>(patch + r * EPI_PITCH + (lane & 7) * 16));
+              if (crow0 + r < row_limit && col < p.N)
+                st8(C + (crow0 + r) * ldc + col, *reinterpret_cast<const bf16x8*>(patch + r * EPI_PITCH + (lane & 7) * 16));
             }
-          } else if (row < p.M) {
+          } else if (crow0 + lane < row_limit) {
             const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(patch + lane * EPI_PITCH);
-            for (int j = 0; j < 64 && n0 + c * 64 + j < p.N; ++j) C[(long long)row * p.ldc + n0 + c * 64 + j] = src[j];
+            for (int j = 0; j < 64 && n0 + c * 64 + j < p.N; ++j) C[(crow0 + lane) * ldc + n0 + c * 64 + j] = src[j];
           }
           __syncwarp();
+        }
+        if (COMM == COMM_RS) {
+          // publish: this warp's 32 rows of the partial tile are in place on the destination rank
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) {
+            const int unit = (mt % mt_local) * 2 + (int)rank;
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;\n" ::"l"(p.peer_flag[mt / mt_local] + unit), "r"(1u)
+                         : "memory");
+          }
         }
       } else {
         // Accumulating epilogues (weight gradients): C += acc through the warp's shared-memory patch, so
@@ -350,6 +454,103 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (lane == 0) mbar_arrive_remote(buf ? acc_empty_leader1 : acc_empty_leader0);
     }
   }
+  if (COMM == COMM_AG && warp >= 6) {
+    // ---------------- comm warps: pull the peers' A shards into the gathered buffer ----------------
+    const int ct = threadIdx.x - 192;
+    const int row_vecs = p.K / 8;                          // 16-byte vectors per row
+    const int piece_vecs = (HM / AG_PIECES) * row_vecs;
+    const int n_units = p.M / HM;
+    const int n_pieces = n_units * AG_PIECES;
+    for (int piece = blockIdx.x; piece < n_pieces; piece += gridDim.x) {
+      const int q = piece / AG_PIECES, sub = piece % AG_PIECES;
+      // peers first (in the order their tiles are consumed), this rank's own shard last: nobody waits
+      // for the self-copy, it only completes the gathered buffer for the weight gradient
+      const int src_rank = (p.rank + 1 + q / units_local) % p.world;
+      const int unit = src_rank * units_local + q % units_local;
+      const int r0 = (q % units_local) * HM + sub * (HM / AG_PIECES);       // first row inside the shard
+      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.peer[src_rank]);
+      __nv_bfloat16* dst = p.gathered + ((long long)src_rank * p.m_local + r0) * p.K;
+      // batches of 8 independent 16-byte loads per thread before any store: the loads must all be in
+      // flight together to cover the NVLink round trip
+      for (int v0 = ct; v0 < piece_vecs; v0 += COMM_THREADS * 8) {
+        bf16x8 buf[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int v = v0 + u * COMM_THREADS;
+          if (v < piece_vecs) buf[u] = ld8(src + (long long)(r0 + v / row_vecs) * p.ld_peer + (v % row_vecs) * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int v = v0 + u * COMM_THREADS;
+          if (v < piece_vecs) st8(dst + (long long)(v / row_vecs) * p.K + (v % row_vecs) * 8, buf[u]);
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;\n" ::"n"(COMM_THREADS) : "memory");
+      if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], %1;\n" ::"l"(p.tile_ready + unit), "r"(1u) : "memory");
+    }
+  } else if (COMM == COMM_RS && warp >= 6) {
+    // ---------------- comm warps: reduce the staged partial sums of my row block ----------------
+    __shared__ int comm_ok;
+    const int ct = threadIdx.x - 192;
+    const int chunk_cols = ((p.N / 8 + RS_CHUNKS - 1) / RS_CHUNKS) * 8;
+    const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.peer[p.rank]);
+    const long long slot = (long long)p.m_local * p.N;
+    const int units = units_local * RS_CHUNKS;
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const int i = u / RS_CHUNKS, ch = u % RS_CHUNKS;
+      if (ct == 0) {
+        unsigned int* flag = p.peer_flag[p.rank] + i;
+        comm_ok = wait_counter<true>(flag, p.rs_target, p.error, ERR_PEERS) ? 1 : 0;
+        // the last of the unit's reducers to get here re-arms the counters for the call after next
+        // (the next call uses the other parity's counters)
+        if (comm_ok && atomicAdd(p.rs_done + i, 1u) == RS_CHUNKS - 1) {
+          p.rs_done[i] = 0;
+          *reinterpret_cast<volatile unsigned int*>(flag) = 0;
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(COMM_THREADS) : "memory");
+      const int good = comm_ok;
+      asm volatile("bar.sync 1, %0;\n" ::"n"(COMM_THREADS) : "memory");
+      if (!good) break;
+      const int c0 = ch * chunk_cols;
+      const int c1 = (c0 + chunk_cols < p.N) ? c0 + chunk_cols : p.N;
+      const int vecs = (c1 - c0) / 8;
+      const int total = HM * vecs;
+      for (int v0 = ct; v0 < total; v0 += COMM_THREADS * 4) {
+        float acc[4][8];
+        long long off[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int v = v0 + x * COMM_THREADS;
+          const int vv = v < total ? v : v0;
+          off[x] = (long long)(i * HM + vv / vecs) * p.N + c0 + (vv % vecs) * 8;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[x][j] = 0.f;
+        }
+        for (int sr = 0; sr < p.world; ++sr) {
+          bf16x8 raw[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) raw[x] = ld8(stage + sr * slot + off[x]);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            float f[8];
+            unpack8(raw[x], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[x][j] += f[j];
+          }
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int v = v0 + x * COMM_THREADS;
+          if (v < total) {
+            const int rr = i * HM + v / vecs, cc = c0 + (v % vecs) * 8;
+            st8(p.rs_out + (long long)rr * p.ld_out + cc, pack8(acc[x]));
+          }
+        }
+      }
+    }
+  }
   // Nobody leaves while its partner may still read its shared memory, signal its barriers or use the
   // paired tensor-memory allocation.
   fence_before();
@@ -388,18 +589,21 @@ static bool make_map(CUtensorMap* map, const void* base, long long inner, long l
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, int OUT>
-static int launch(const void* A, long long lda, const void* B, long long ldb, const Params& p, cudaStream_t st) {
-  CUtensorMap ma, mb;
+template <bool A_MN, bool B_MN, int OUT, int COMM = COMM_NONE>
+static int launch(const void* A, long long lda, const void* B, long long ldb, const Params& p, cudaStream_t st,
+                  const void* A_local = nullptr, long long lda_local = 0) {
+  CUtensorMap ma, mb, ml;
   // K-major: [rows, K], box 64 k x 128 rows; MN-major: [K, rows], box 64 rows x 64 k
   const bool oka = A_MN ? make_map(&ma, A, p.M, p.K, lda, 64, 64) : make_map(&ma, A, p.K, p.M, lda, BK, HM);
   const bool okb = B_MN ? make_map(&mb, B, p.N, p.K, ldb, 64, 64) : make_map(&mb, B, p.K, p.N, ldb, BK, HN);
   if (!oka || !okb) return (int)cudaErrorInvalidValue;
-  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT>;
+  ml = ma;
+  if (A_local != nullptr && !make_map(&ml, A_local, p.K, p.m_local, lda_local, BK, HM)) return (int)cudaErrorInvalidValue;
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT, COMM>;
   const size_t smem = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 1024;
   static int max_clusters = 0;   // per instantiation
   cudaLaunchConfig_t cfg = {};          // the pair (cluster of 2) is a compile-time attribute of the kernel
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(COMM == COMM_NONE ? 192 : 192 + COMM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   if (max_clusters == 0) {
@@ -411,9 +615,11 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
     max_clusters = n < sm_count() / 2 ? n : sm_count() / 2;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  // the fused variants always launch every pair: their comm warps share the copy / reduce work of the
+  // whole grid, and every CTA must be resident for the counters to advance
+  const int clusters = (COMM != COMM_NONE || tiles >= max_clusters) ? max_clusters : tiles;
   cfg.gridDim = dim3(2 * clusters, 1, 1);
-  return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
+  return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, ml, p);
 }
 
 }  // namespace g2
@@ -447,4 +653,48 @@ MSRL_API int msrl_gemm_pair_bf16(const void* A, long long lda, int a_mn, const v
   if (a_mn && b_mn && out_mode == g2::OUT_ACC_F32) return g2::launch<true, true, g2::OUT_ACC_F32>(A, lda, B, ldb, p, st);
   if (a_mn && b_mn && out_mode == g2::OUT_ACC_BF16) return g2::launch<true, true, g2::OUT_ACC_BF16>(A, lda, B, ldb, p, st);
   return (int)cudaErrorInvalidValue;
+}
+
+// ---- communication-fused forms on CTA pairs (same contracts as msrl_ag_gemm_bf16_tn / msrl_gemm_rs_bf16_tn,
+// token shards in multiples of 256 rows) ------------------------------------------------------------
+MSRL_API int msrl_ag_gemm_pair_bf16_tn(void* const* peer_a, long long ld_peer, void* gathered, const void* B,
+                                       long long ldb, void* C, long long ldc, int m_local, int N, int K, int rank,
+                                       int world, unsigned int* tile_ready, int* error, cudaStream_t st) {
+  if (m_local == 0 || N == 0) return 0;
+  if (K % 8 != 0 || m_local % g2::BM != 0 || world > g2::MAX_RANKS || ld_peer % 8 != 0) return (int)cudaErrorInvalidValue;
+  g2::Params p{};
+  p.M = m_local * world; p.N = N; p.K = K;
+  p.C = C;
+  p.ldc = ldc;
+  p.error = error;
+  p.rank = rank; p.world = world; p.m_local = m_local;
+  for (int r = 0; r < world; ++r) p.peer[r] = peer_a[r];
+  p.ld_peer = ld_peer;
+  p.gathered = (__nv_bfloat16*)gathered;
+  p.tile_ready = tile_ready;
+  cudaError_t e = cudaMemsetAsync(tile_ready, 0, sizeof(unsigned int) * (size_t)(p.M / g2::HM), st);
+  if (e != cudaSuccess) return (int)e;
+  return g2::launch<false, false, g2::OUT_BF16, g2::COMM_AG>(gathered, K, B, ldb, p, st, peer_a[rank], ld_peer);
+}
+
+MSRL_API int msrl_gemm_rs_pair_bf16_tn(const void* A, long long lda, const void* B, long long ldb,
+                                       void* const* peer_stage, void* const* peer_flag, unsigned int* done, void* out,
+                                       long long ld_out, int m_local, int N, int K, int rank, int world,
+                                       unsigned int target, int* error, cudaStream_t st) {
+  if (m_local == 0 || N == 0) return 0;
+  if (K % 8 != 0 || N % 8 != 0 || m_local % g2::BM != 0 || world > g2::MAX_RANKS || ld_out % 8 != 0)
+    return (int)cudaErrorInvalidValue;
+  g2::Params p{};
+  p.M = m_local * world; p.N = N; p.K = K;
+  p.error = error;
+  p.rank = rank; p.world = world; p.m_local = m_local;
+  for (int r = 0; r < world; ++r) {
+    p.peer[r] = peer_stage[r];
+    p.peer_flag[r] = (unsigned int*)peer_flag[r];
+  }
+  p.rs_target = target;
+  p.rs_done = done;
+  p.rs_out = (__nv_bfloat16*)out;
+  p.ld_out = ld_out;
+  return g2::launch<false, false, g2::OUT_BF16, g2::COMM_RS>(A, lda, B, ldb, p, st);
 }

@@ -467,7 +467,11 @@ class GPTModel(nn.Module):
 
     def __init__(self, cfg: TransformerConfig, comm: Optional[TPComm] = None, pre_process: bool = True,
                  post_process: bool = True, layer_numbers: Optional[List[int]] = None, device=None,
-                 seed: int = 1234):
+                 seed: int = 1234, chunk_sizes: Optional[List[int]] = None):
+        """``chunk_sizes``: with an interleaved (virtual) pipeline the rank's layers form several
+        chunks that are run separately (``hidden_states(..., chunk=c)``); ``layer_numbers`` lists the
+        layers of all chunks in order.  The embedding belongs to chunk 0 of the first rank, the head to
+        the last chunk of the last rank."""
         super().__init__()
         self.cfg = cfg
         self.comm = comm or NO_TP
@@ -476,6 +480,13 @@ class GPTModel(nn.Module):
         gen = torch.Generator(device=device).manual_seed(seed + 7919 * self.comm.rank)
         layer_numbers = list(range(cfg.num_layers)) if layer_numbers is None else layer_numbers
         self.layer_numbers = layer_numbers
+        sizes = list(chunk_sizes) if chunk_sizes else [len(layer_numbers)]
+        if sum(sizes) != len(layer_numbers):
+            raise ValueError("chunk sizes do not add up to the number of layers of this stage")
+        self.chunk_bounds = [0]
+        for n_ in sizes:
+            self.chunk_bounds.append(self.chunk_bounds[-1] + n_)
+        self.num_chunks = len(sizes)
         if cfg.vocab_size % cfg.tensor_model_parallel_size:
             raise ValueError("vocab size must be divisible by the TP size")
         self.vocab_start = self.comm.rank * (cfg.vocab_size // cfg.tensor_model_parallel_size)
@@ -503,32 +514,40 @@ class GPTModel(nn.Module):
     def embed(self, ids: torch.Tensor) -> torch.Tensor:
         return _EmbedFn.apply(self.embedding.word_embeddings.weight, ids, self.comm, self.vocab_start)
 
-    def run_layers(self, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
-        for layer in self.decoder.layers:
+    def run_layers(self, h: torch.Tensor, meta: PackedMeta, chunk: Optional[int] = None) -> torch.Tensor:
+        layers = self.decoder.layers if chunk is None else \
+            list(self.decoder.layers)[self.chunk_bounds[chunk]:self.chunk_bounds[chunk + 1]]
+        for layer in layers:
             h = layer(h, meta)
         return h
 
-    def hidden_states(self, ids_or_h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
-        h = self.embed(ids_or_h) if self.pre_process else ids_or_h
+    def is_first_chunk(self, chunk: Optional[int]) -> bool:
+        return self.pre_process and (chunk is None or chunk == 0)
+
+    def is_last_chunk(self, chunk: Optional[int]) -> bool:
+        return self.post_process and (chunk is None or chunk == self.num_chunks - 1)
+
+    def hidden_states(self, ids_or_h: torch.Tensor, meta: PackedMeta, chunk: Optional[int] = None) -> torch.Tensor:
+        h = self.embed(ids_or_h) if self.is_first_chunk(chunk) else ids_or_h
         if torch.is_grad_enabled() and not h.requires_grad and \
                 any(p.requires_grad for p in self.decoder.parameters()):
             # layer nodes only run their backward when an input requires grad
             h = h.detach().requires_grad_(True)
-        return self.run_layers(h, meta)
+        return self.run_layers(h, meta, chunk)
 
     def forward_logprob(self, ids_or_h: torch.Tensor, labels: torch.Tensor, meta: PackedMeta,
-                        temperature: float = 1.0, want_entropy: bool = False
+                        temperature: float = 1.0, want_entropy: bool = False, chunk: Optional[int] = None
                         ) -> Tuple[torch.Tensor, torch.Tensor]:
         """Packed ids (or the previous stage's hidden states) -> per-token ``(logp, entropy)``."""
-        h = self.hidden_states(ids_or_h, meta)
-        if not self.post_process:
+        h = self.hidden_states(ids_or_h, meta, chunk)
+        if not self.is_last_chunk(chunk):
             return h, None
         return _LogProbHeadFn.apply(h, self, labels, 1.0 / temperature, want_entropy)
 
-    def forward_values(self, ids_or_h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+    def forward_values(self, ids_or_h: torch.Tensor, meta: PackedMeta, chunk: Optional[int] = None) -> torch.Tensor:
         """Per-token scalar from the value head (fp32), ``[T]``."""
-        h = self.hidden_states(ids_or_h, meta)
-        if not self.post_process:
+        h = self.hidden_states(ids_or_h, meta, chunk)
+        if not self.is_last_chunk(chunk):
             return h
         x = _NormFn.apply(h, self.decoder.final_layernorm.weight, self.cfg.norm_epsilon)
         xg = self.comm.gather_seq(x) if not torch.is_grad_enabled() else _GatherSeq.apply(x, self.comm)

@@ -36,7 +36,7 @@ class MicroBatch:
     def __init__(self, data: Dict[str, torch.Tensor], rows: Sequence[int], align: int, total_align: int = 1):
         """``align``: every sequence is padded to a multiple of it (TP x CP token sharding);
         ``total_align``: the last sequence takes extra padding so that the whole stream is a
-        multiple of it (128 x TP lets the communication-fused GEMMs tile the token shards)."""
+        multiple of it (256 x TP lets the communication-fused GEMMs tile the token shards)."""
         rows_t = torch.as_tensor(list(rows), dtype=torch.int64)
         ids2d = data["input_ids"][rows_t].to(torch.int64)
         b, s = ids2d.shape
@@ -146,11 +146,11 @@ class TrainingEngine:
 
     # ------------------------------------------------------------------------------------------
     def _total_align(self) -> int:
-        """Token-count multiple of a packed stream: 128 per TP rank when the communication-fused
-        linears are attached (they tile each rank's token shard in 128-row tiles)."""
+        """Token-count multiple of a packed stream: 256 per TP rank when the communication-fused
+        linears are attached (their CTA pairs tile each rank's token shard in 256-row tiles)."""
         comm = self.core.comm
         if getattr(comm, "fused", None) is not None and comm.sequence_parallel:
-            return 128 * comm.world_size
+            return 256 * comm.world_size
         return 1
 
     def _split(self, data: Dict[str, torch.Tensor], rows: List[int], update: bool) -> List[List[int]]:
@@ -162,11 +162,13 @@ class TrainingEngine:
         parts = rearrange_micro_batches(lens, budget, self.dynamic_max_batch_size, self.dp_group)
         return [[rows[i] for i in p] for p in parts if p]
 
-    def _run_model(self, mb: MicroBatch, want_entropy: bool, h_in: Optional[torch.Tensor] = None):
+    def _run_model(self, mb: MicroBatch, want_entropy: bool, h_in: Optional[torch.Tensor] = None,
+                   chunk: Optional[int] = None):
         """Returns the role's per-response-token outputs ``[b, R]`` (autograd-connected).
         ``h_in``: hidden states received from the previous pipeline stage (``None`` on the first)."""
         core = self.core
         x = mb.ids if h_in is None else h_in
+        kw = {} if chunk is None else {"chunk": chunk}
         cp = self._context_parallel(mb)
         if cp is not None:
             # every CP rank runs its own tokens of every sequence; per-token outputs are gathered
@@ -175,34 +177,36 @@ class TrainingEngine:
                 x = cp.take_local(mb.ids)
             meta = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(mb.positions), cp=cp)
             if self.loss_func.output_kind == "value":
-                v = cp.gather_tokens(core.forward_values(x, meta))
+                v = cp.gather_tokens(core.forward_values(x, meta, **kw))
                 if self.role == "reward":
                     return v[mb.last_index].unsqueeze(-1), None
                 return mb.response_rows(v), None
-            logp, ent = core.forward_logprob(x, cp.take_local(mb.labels), meta, self.temperature, want_entropy)
+            logp, ent = core.forward_logprob(x, cp.take_local(mb.labels), meta, self.temperature, want_entropy, **kw)
             logp = cp.gather_tokens(logp)
             lp = mb.response_rows(logp)
             en = mb.response_rows(cp.gather_tokens(ent)) if want_entropy else None
             return lp, en
         if self.loss_func.output_kind == "value":
-            v = core.forward_values(x, mb.meta())
+            v = core.forward_values(x, mb.meta(), **kw)
             if self.role == "reward":
                 return v[mb.last_index].unsqueeze(-1), None
             return mb.response_rows(v), None
-        logp, ent = core.forward_logprob(x, mb.labels, mb.meta(), self.temperature, want_entropy)
+        logp, ent = core.forward_logprob(x, mb.labels, mb.meta(), self.temperature, want_entropy, **kw)
         lp = mb.response_rows(logp)
         en = mb.response_rows(ent) if want_entropy else None
         return lp, en
 
-    def _stage_forward(self, mb: MicroBatch, h_in: Optional[torch.Tensor], want_entropy: bool):
-        """One pipeline stage: hidden states for inner stages, role outputs on the last stage."""
-        if not self.core.post_process:
+    def _stage_forward(self, mb: MicroBatch, h_in: Optional[torch.Tensor], want_entropy: bool,
+                       chunk: Optional[int] = None):
+        """One (virtual) pipeline stage: hidden states for inner stages, role outputs on the last one."""
+        if not self.core.is_last_chunk(chunk):
+            kw = {} if chunk is None else {"chunk": chunk}
             cp = self._context_parallel(mb)
             if cp is None:
-                return self.core.hidden_states(mb.ids if h_in is None else h_in, mb.meta())
+                return self.core.hidden_states(mb.ids if h_in is None else h_in, mb.meta(), **kw)
             meta = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(mb.positions), cp=cp)
-            return self.core.hidden_states(cp.take_local(mb.ids) if h_in is None else h_in, meta)
-        return self._run_model(mb, want_entropy, h_in)
+            return self.core.hidden_states(cp.take_local(mb.ids) if h_in is None else h_in, meta, **kw)
+        return self._run_model(mb, want_entropy, h_in, chunk)
 
     def _context_parallel(self, mb: MicroBatch):
         """Context-parallel helper of this micro-batch (cached on it), ``None`` without CP."""
@@ -239,7 +243,7 @@ class TrainingEngine:
             mbs = [MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
                    for rows in self._split(data, list(range(n)), update=False)]
             outs = self.pipeline.forward_only(mbs, lambda m: m.num_tokens // self.cp_size,
-                                              lambda m, h: self._stage_forward(m, h, False))
+                                              lambda m, h, c=None: self._stage_forward(m, h, False, c))
             results = [(m.rows.tolist(), o[0].float()) for m, o in zip(mbs, outs)]
         else:
             for rows in self._split(data, list(range(n)), update=False):
@@ -285,8 +289,24 @@ class TrainingEngine:
         if self.optimizer is not None and not hasattr(self.model, "zero_grad_buffer"):
             self.optimizer.zero_grad()
 
+    def _pad_to_pipeline(self, parts: List[List[int]]) -> List[List[int]]:
+        """The interleaved schedule walks groups of ``pp`` micro-batches: split the largest ones until the
+        count is a multiple of the pipeline size (same decision on every rank of the replica)."""
+        pp = self.pipeline.size
+        parts = [list(p) for p in parts]
+        while len(parts) % pp:
+            big = max(range(len(parts)), key=lambda i: len(parts[i]))
+            if len(parts[big]) < 2:
+                raise ValueError(f"cannot form a multiple of {pp} micro-batches from {sum(map(len, parts))} samples; "
+                                 f"raise the mini-batch size or lower the virtual pipeline size")
+            half = len(parts[big]) // 2
+            parts[big:big + 1] = [parts[big][:half], parts[big][half:]]
+        return parts
+
     def _forward_backward(self, data, mini: List[int]) -> Dict[str, torch.Tensor]:
         parts = self._split(data, mini, update=True)
+        if self.pipeline is not None and self.pipeline.num_chunks > 1:
+            parts = self._pad_to_pipeline(parts)
         n_micro = len(parts)
         sums: Dict[str, torch.Tensor] = {}
 
@@ -312,7 +332,8 @@ class TrainingEngine:
         if self.pipeline is not None:
             mbs = [MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device) for rows in parts]
             self.pipeline.forward_backward(mbs, lambda m: m.num_tokens // self.cp_size,
-                                           lambda m, h: self._stage_forward(m, h, self.want_entropy), loss_backward)
+                                           lambda m, h, c=None: self._stage_forward(m, h, self.want_entropy, c),
+                                           loss_backward)
             return sums
         for rows in parts:
             mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)

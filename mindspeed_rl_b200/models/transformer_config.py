@@ -7,6 +7,17 @@ from typing import Optional
 import torch
 
 
+def parse_noop_layers(value) -> list:
+    """``noop_layers`` as a list of slot indices (accepts a list or a comma-separated string)."""
+    if value is None or value == "":
+        return []
+    if isinstance(value, str):
+        return sorted({int(x) for x in value.split(",") if x.strip()})
+    if isinstance(value, int):
+        return [value]
+    return sorted({int(x) for x in value})
+
+
 @dataclass
 class TransformerConfig:
     num_layers: int
@@ -101,7 +112,9 @@ class TransformerConfig:
                 beta_fast=cfg.beta_fast, beta_slow=cfg.beta_slow, mscale=cfg.rope_scaling_mscale,
                 mscale_all_dim=cfg.rope_scaling_mscale_all_dim)
         kw = dict(
-            num_layers=cfg.num_layers, hidden_size=cfg.hidden_size,
+            # the training config counts layer slots; empty (no-op) slots hold no layer
+            num_layers=cfg.num_layers - len(parse_noop_layers(getattr(cfg, "noop_layers", None))),
+            hidden_size=cfg.hidden_size,
             ffn_hidden_size=cfg.ffn_hidden_size, num_attention_heads=cfg.num_attention_heads,
             num_query_groups=nqg, vocab_size=vocab, kv_channels=cfg.kv_channels,
             norm_epsilon=cfg.norm_epsilon, rotary_base=float(cfg.rotary_base),

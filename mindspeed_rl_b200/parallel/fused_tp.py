@@ -46,6 +46,8 @@ class FusedTP:
         self.world = len(self.ranks)
         self.me = self.ranks.index(arena.rank)
         self.lib = _lib.load()
+        import os
+        self.use_pair = os.environ.get("MSRL_FUSED_TP_PAIR", "1") == "1"
         self.max_m = (max_local_tokens + _TILE - 1) // _TILE * _TILE
         self.max_k, self.max_n = max_k, max_n
         tiles = self.max_m // _TILE
@@ -91,7 +93,9 @@ class FusedTP:
         gathered = torch.empty(m, k, dtype=torch.bfloat16, device=x.device)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
         peers = self.arena.peer_ptrs(self.arena.offset_of(slot), self.ranks)
-        _lib.check(self.lib.msrl_ag_gemm_bf16_tn(
+        # token shards in multiples of 256 rows run on CTA pairs (cta_group::2 main loop)
+        fn = self.lib.msrl_ag_gemm_pair_bf16_tn if (ml % 256 == 0 and self.use_pair) else self.lib.msrl_ag_gemm_bf16_tn
+        _lib.check(fn(
             peers, c_ll(k), _lib.ptr(gathered), _lib.ptr(w), c_ll(w.stride(0)), _lib.ptr(out), c_ll(n),
             c_int(ml), c_int(n), c_int(k), c_int(self.me), c_int(self.world), _lib.ptr(self.tile_ready),
             _lib.ptr(_status_word(x.device)), _lib.stream()), "ag_gemm")
@@ -109,7 +113,8 @@ class FusedTP:
         stage_off = self.arena.offset_of(self.stage[par])
         flag_off = self.arena.offset_of(self.flags[par])
         tiles_n = int(self.lib.msrl_gemm_rs_tiles(c_int(n)))
-        _lib.check(self.lib.msrl_gemm_rs_bf16_tn(
+        fn = self.lib.msrl_gemm_rs_pair_bf16_tn if (ml % 256 == 0 and self.use_pair) else self.lib.msrl_gemm_rs_bf16_tn
+        _lib.check(fn(
             _lib.ptr(a), c_ll(a.stride(0)), _lib.ptr(w), c_ll(w.stride(0)),
             self.arena.peer_ptrs(stage_off, self.ranks), self.arena.peer_ptrs(flag_off, self.ranks),
             _lib.ptr(self.done[par]), _lib.ptr(out), c_ll(n), c_int(ml), c_int(n), c_int(k), c_int(self.me),

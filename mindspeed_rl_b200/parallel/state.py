@@ -133,6 +133,10 @@ class ParallelState:
             "ep": layout.expert_groups("ep"), "edp": layout.expert_groups("edp"),
             "etp": layout.expert_groups("etp"),
         }
+        if layout.pp > 1:
+            # second group over the pipeline ranks: gradients of the interleaved schedule travel here, so
+            # that with two stages (next == previous rank) they cannot be taken for activations
+            specs["pp_grad"] = layout.groups("pp")
         # "all": every rank of this model.  When that is the whole job the default group serves.
         inited = dist.is_available() and dist.is_initialized()
         covers_job = inited and rank_offset == 0 and layout.world_size == dist.get_world_size()

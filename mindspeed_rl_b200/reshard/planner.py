@@ -85,12 +85,54 @@ def _contig(src_rank: int, src_off: int, dst_off: int, nbytes: int) -> List[Desc
 
 
 def stage_layers(num_layers: int, pp: int, num_layer_list: Optional[Sequence[int]] = None) -> List[List[int]]:
-    counts = list(num_layer_list) if num_layer_list else [num_layers // pp] * pp
+    """Layers of every pipeline stage (no virtual stages, no empty slots)."""
+    return [sum(chunks, []) for chunks in stage_chunks(num_layers, pp, num_layer_list)]
+
+
+def pipeline_layout(mc, pp: int) -> List[List[List[int]]]:
+    """``stage_chunks`` of a training config (``num_layers`` slots, ``num_layer_list``,
+    ``num_layers_per_virtual_pipeline_stage``, ``noop_layers``)."""
+    from ..models.transformer_config import parse_noop_layers
+
+    per_virtual = getattr(mc, "num_layers_per_virtual_pipeline_stage", None)
+    vpp = 1
+    if per_virtual and pp > 1:
+        if (mc.num_layers // pp) % per_virtual:
+            raise ValueError("num_layers_per_virtual_pipeline_stage must divide the layer slots of a stage")
+        vpp = mc.num_layers // pp // per_virtual
+    return stage_chunks(mc.num_layers, pp, getattr(mc, "num_layer_list", None), vpp,
+                        parse_noop_layers(getattr(mc, "noop_layers", None)))
+
+
+def stage_chunks(num_layers: int, pp: int, num_layer_list: Optional[Sequence[int]] = None, vpp: int = 1,
+                 noop_layers: Sequence[int] = ()) -> List[List[List[int]]]:
+    """``[stage][chunk] -> layer numbers``.  ``num_layers`` counts layer SLOTS: with ``noop_layers``
+    (slot indices that hold no layer, used to even out stages: reference flag ``noop_layers``,
+    ``mindspeed_rl/config_cls/megatron_config.py:357``) the real layers are numbered consecutively
+    in slot order.  Slots are dealt to virtual stages in order: virtual stage ``c * pp + s`` is
+    chunk ``c`` of stage ``s`` (interleaved schedule, ``num_layers_per_virtual_pipeline_stage``);
+    ``num_layer_list`` gives uneven slot counts per stage and excludes virtual stages."""
+    vpp = max(int(vpp or 1), 1)
+    if num_layer_list:
+        if vpp > 1:
+            raise ValueError("num_layer_list and a virtual pipeline cannot be combined")
+        counts = list(num_layer_list)
+    else:
+        if num_layers % (pp * vpp):
+            raise ValueError(f"{num_layers} layer slots do not divide into {pp} x {vpp} (virtual) stages")
+        counts = [num_layers // (pp * vpp)] * (pp * vpp)
     if sum(counts) != num_layers:
         raise ValueError("pipeline layer counts do not add up to num_layers")
-    out, s = [], 0
-    for c in counts:
-        out.append(list(range(s, s + c)))
+    noop = set(int(i) for i in (noop_layers or ()))
+    real, nxt = {}, 0
+    for slot in range(num_layers):
+        if slot not in noop:
+            real[slot] = nxt
+            nxt += 1
+    out: List[List[List[int]]] = [[] for _ in range(pp)]
+    s = 0
+    for v, c in enumerate(counts):
+        out[v % pp].append([real[i] for i in range(s, s + c) if i in real])
         s += c
     return out
 
@@ -250,6 +292,8 @@ def attach_peer_all_reduce(comm: TPComm, arena, hidden_size: int) -> None:
 
     if arena is None or comm.world_size <= 1 or comm.group is None or os.environ.get("MSRL_PEER_ALLREDUCE", "1") != "1":
         return
+    if comm.world_size > 2 and os.environ.get("MSRL_PEER_ALLREDUCE_WIDE", "0") != "1":
+        return     # pushing to three or more peers multiplies the bytes sent: measured slower than the library there
     need = DECODE_ALL_REDUCE_TOKENS * hidden_size * 2
     if arena.free_bytes() < 2 * comm.world_size * need + (1 << 20):
         return
@@ -260,7 +304,8 @@ class Resharder:
     """Owns the rollout-side parallel state, engine and weight buffer of one worker."""
 
     def __init__(self, cfg: TransformerConfig, ddp, train_state: ParallelState, infer_tp: int, device,
-                 engine_factory: Callable, arena=None, num_layer_list: Optional[Sequence[int]] = None):
+                 engine_factory: Callable, arena=None, num_layer_list: Optional[Sequence[int]] = None,
+                 layers_of_stage: Optional[Sequence[Sequence[int]]] = None):
         self.cfg, self.ddp, self.train_state, self.infer_tp = cfg, ddp, train_state, infer_tp
         self.device = torch.device(device)
         self.arena = arena
@@ -280,7 +325,8 @@ class Resharder:
         self.buffer: Optional[torch.Tensor] = None
         self._plan: Optional[ReshardPlan] = None
         self._plan_dev = None
-        self._layers = stage_layers(cfg.num_layers, layout.pp, num_layer_list)
+        self._layers = [list(l) for l in layers_of_stage] if layers_of_stage is not None else \
+            stage_layers(cfg.num_layers, layout.pp, num_layer_list)
         self.last_bytes = 0
 
     @classmethod
@@ -300,7 +346,8 @@ class Resharder:
 
         return cls(worker.tcfg, worker.model, worker.parallel_state, gc.infer_tensor_parallel_size, worker.device,
                    factory, arena=get_arena(),
-                   num_layer_list=getattr(worker.actor_config, "num_layer_list", None))
+                   layers_of_stage=[sum(ch, []) for ch in
+                                    pipeline_layout(worker.actor_config, worker.parallel_state.size("pp"))])
 
     # ------------------------------------------------------------------------------------------
     def _main_buffer(self):

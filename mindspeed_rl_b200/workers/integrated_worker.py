@@ -111,7 +111,7 @@ class IntegratedWorker(BaseWorker):
         return P2PDispatcher.bytes_needed(ep, e_local, c.hidden_size, rows) + (1 << 20)
 
     def _fused_tp_rows(self) -> int:
-        """Largest token shard (rows per TP rank, multiple of 128) a packed micro-batch can have,
+        """Largest token shard (rows per TP rank, multiple of 256) a packed micro-batch can have,
         or 0 when the communication-fused TP linears do not apply (no TP / no sequence parallel /
         ``MSRL_FUSED_TP=0``)."""
         import os
@@ -124,8 +124,8 @@ class IntegratedWorker(BaseWorker):
                   rl.ref_forward_micro_batch_size or 1)
         tokens = max(rl.update_max_packing_token_size or 0, rl.actor_max_packing_token_size or 0,
                      rl.ref_max_packing_token_size or 0, mbs * (ac.seq_length or 0))
-        tokens += 128 * tp + mbs * tp * 2
-        return (tokens // tp + 127) // 128 * 128
+        tokens += 256 * tp + mbs * tp * 2
+        return (tokens // tp + 255) // 256 * 256
 
     def _maybe_attach_fused_tp(self) -> None:
         from ..parallel.symm import get_arena
@@ -152,17 +152,19 @@ class IntegratedWorker(BaseWorker):
         self.tcfg = tcfg
         # pipeline stage of this rank: embedding on the first, head on the last, a slice of layers each
         from ..parallel.pipeline import PipelineSchedule
-        from ..reshard.planner import stage_layers
+        from ..reshard.planner import pipeline_layout
 
         pp, pp_rank = ps.size("pp"), ps.rank_in("pp")
+        chunks = pipeline_layout(ac, pp)[pp_rank]          # this stage's model chunks (virtual stages)
         stage_kw = dict(pre_process=pp_rank == 0, post_process=pp_rank == pp - 1,
-                        layer_numbers=stage_layers(tcfg.num_layers, pp, getattr(ac, "num_layer_list", None))[pp_rank])
+                        layer_numbers=sum(chunks, []), chunk_sizes=[len(c) for c in chunks])
         self.pipeline = None
         if pp > 1:
             self.pipeline = PipelineSchedule(
                 ps.group("pp"), pp_rank, pp, ps.get_pipeline_model_parallel_prev_rank(),
                 ps.get_pipeline_model_parallel_next_rank(), tcfg.hidden_size, dtype, self.device,
-                seq_shard=tp if (ac.sequence_parallel and tp > 1) else 1)
+                seq_shard=tp if (ac.sequence_parallel and tp > 1) else 1, num_chunks=len(chunks),
+                grad_group=ps.group("pp_grad"))
         core = GPTModel(tcfg, self.comm, device=self.device, seed=self.seed, **stage_kw)
         if tcfg.is_moe and gc.eplb_token_collects:
             # expert-load statistics of the rollout (input of cli/eplb_generate_map.py)

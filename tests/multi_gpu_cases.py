@@ -222,7 +222,11 @@ def case_fused_tp(rank, world):
     f = FusedTP(arena, list(range(world)), ml, hidden, hidden)
     g = torch.Generator(device="cuda").manual_seed(7 + rank)
     rnd = lambda *s: (torch.randn(*s, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
-    for it in range(3):                                       # several calls: parity buffers, counter re-arming
+    ml_max = ml
+    # many consecutive calls with changing token counts: parity buffers, counter re-arming, both the
+    # CTA-pair kernels (shards in multiples of 256 rows) and the single-CTA ones (multiples of 128)
+    shapes = [ml_max, ml_max, ml_max // 4, ml_max // 4 + 128, ml_max // 2 + 256, ml_max, ml_max // 8, ml_max]
+    for it, ml in enumerate(shapes):
         x, w = rnd(ml, hidden), rnd(n_col, hidden)
         y, xg = f.ag_gemm(x, w)
         want_x = torch.empty(world * ml, hidden, dtype=torch.bfloat16, device="cuda")
@@ -241,6 +245,8 @@ def case_fused_tp(rank, world):
         ref = want.float()
         err = (out.float() - ref).abs().max().item()
         assert err <= 3e-2 * ref.abs().max().item() + 1e-3, f"gemm_rs error {err} (call {it})"
+
+    ml = ml_max
 
     def timed(fn, iters=10):
         for _ in range(3):
@@ -271,6 +277,9 @@ def case_fused_tp(rank, world):
 
     t = dict(ag_fused=timed(lambda: f.ag_gemm(x, w)), ag_nccl=timed(base_ag),
              rs_fused=timed(lambda: f.gemm_rs(a, w2)), rs_nccl=timed(base_rs))
+    f.use_pair = False                      # the single-CTA kernels on the same shapes, for comparison
+    t.update(ag_single=timed(lambda: f.ag_gemm(x, w)), rs_single=timed(lambda: f.gemm_rs(a, w2)))
+    f.use_pair = True
     check_status(torch.device("cuda", torch.cuda.current_device()),"fused timing loop")
     arena.check()
     if rank == 0:
@@ -279,7 +288,8 @@ def case_fused_tp(rank, world):
         print(f"TIMING fused_tp world={world} m_local={ml} ag_gemm[N={n_col},K={hidden}] fused={t['ag_fused']:.3f}ms "
               f"({fl_ag / t['ag_fused'] / 1e9:.0f} TFLOP/s) nccl+cublas={t['ag_nccl']:.3f}ms | "
               f"gemm_rs[N={hidden},K={k_row}] fused={t['rs_fused']:.3f}ms ({fl_rs / t['rs_fused'] / 1e9:.0f} TFLOP/s) "
-              f"cublas+nccl={t['rs_nccl']:.3f}ms", flush=True)
+              f"cublas+nccl={t['rs_nccl']:.3f}ms | single-CTA kernels: ag {t['ag_single']:.3f}ms rs {t['rs_single']:.3f}ms",
+              flush=True)
     arena.close()
 
 

@@ -562,6 +562,92 @@ def _pp_worker(rank, world, n_micro):
         assert all(torch.allclose(o[0], b, atol=1e-5) for o, b in zip(outs, want_lp))
 
 
+def _vpp_worker(rank, world, n_micro, vpp, noop):
+    """Interleaved (virtual-stage) schedule with an empty layer slot: gradients and outputs of the
+    single-process model."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.pipeline import PipelineSchedule
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    from mindspeed_rl_b200.reshard.planner import stage_chunks
+    ps = initialize_model_parallel(pipeline_model_parallel_size=world)
+    slots = world * vpp * 2
+    chunks = stage_chunks(slots, world, None, vpp, noop)[rank]
+    layers = sum(chunks, [])
+    n_real = slots - len(noop)
+    cfg = TransformerConfig(num_layers=n_real, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4,
+                            num_query_groups=2, vocab_size=64, add_qkv_bias=True, params_dtype=torch.float32,
+                            max_position_embeddings=128)
+    full = GPTModel(cfg, device="cpu", seed=5)
+    stage = GPTModel(cfg, device="cpu", pre_process=rank == 0, post_process=rank == world - 1, layer_numbers=layers,
+                     chunk_sizes=[len(c) for c in chunks])
+    sd = {}
+    for k, v in full.state_dict().items():
+        if k.startswith("decoder.layers."):
+            idx = int(k.split(".")[2])
+            if idx in layers:
+                sd[f"decoder.layers.{layers.index(idx)}." + k.split(".", 3)[3]] = v
+        elif k.startswith("embedding."):
+            if rank == 0:
+                sd[k] = v
+        elif rank == world - 1:
+            sd[k] = v
+    stage.load_state_dict(sd)
+    g = torch.Generator().manual_seed(3)
+    mbs = []
+    for i in range(n_micro):
+        meta = PackedMeta.from_lengths([5 + i, 9], "cpu")
+        t = int(meta.cu_seqlens[-1])
+        mbs.append(dict(meta=meta, t=t, ids=torch.randint(0, 64, (t,), generator=g),
+                        labels=torch.randint(0, 64, (t,), generator=g), w=torch.randn(t, generator=g)))
+    want_lp = []
+    for mb in mbs:
+        lp, _ = full.forward_logprob(mb["ids"], mb["labels"], mb["meta"], 1.0, False)
+        (lp * mb["w"]).sum().backward()
+        want_lp.append(lp.detach())
+    sched = PipelineSchedule(ps.group("pp"), rank, world, ps.get_pipeline_model_parallel_prev_rank(),
+                             ps.get_pipeline_model_parallel_next_rank(), cfg.hidden_size, torch.float32, "cpu",
+                             num_chunks=vpp, grad_group=ps.group("pp_grad"))
+
+    def stage_fwd(mb, h_in, chunk):
+        x = mb["ids"] if h_in is None else h_in
+        if not stage.is_last_chunk(chunk):
+            return stage.hidden_states(x, mb["meta"], chunk)
+        return stage.forward_logprob(x, mb["labels"], mb["meta"], 1.0, False, chunk)
+
+    got = {}
+
+    def last_bwd(mb, out):
+        lp, _ = out
+        got[id(mb)] = lp.detach()
+        (lp * mb["w"]).sum().backward()
+
+    sched.forward_backward(mbs, lambda m: m["t"], stage_fwd, last_bwd)
+    if rank == world - 1:
+        assert len(got) == n_micro and all(torch.allclose(got[id(m)], b, atol=1e-5) for m, b in zip(mbs, want_lp))
+    full_grads = {n: p.grad for n, p in full.named_parameters()}
+    for n, p in stage.named_parameters():
+        if n.startswith("decoder.layers."):
+            idx = layers[int(n.split(".")[2])]
+            ref = full_grads[f"decoder.layers.{idx}." + n.split(".", 3)[3]]
+        else:
+            ref = full_grads[n]
+        assert torch.allclose(p.grad, ref, atol=2e-5, rtol=1e-4), (n, (p.grad - ref).abs().max())
+    with torch.no_grad():
+        outs = sched.forward_only(mbs, lambda m: m["t"], stage_fwd)
+    if rank == world - 1:
+        assert all(torch.allclose(o[0], b, atol=1e-5) for o, b in zip(outs, want_lp))
+
+
+def test_interleaved_pipeline_matches_single_process():
+    from mindspeed_rl_b200.reshard.planner import stage_chunks
+    # 8 slots on 2 stages x 2 chunks, slot 7 empty: stage 0 holds layers [0,1 | 4,5], stage 1 [2,3 | 6]
+    assert stage_chunks(8, 2, None, 2, [7]) == [[[0, 1], [4, 5]], [[2, 3], [6]]]
+    run_distributed(_vpp_worker, 2, 4, 2, [7])        # two groups of micro-batches: warm-up, steady state, cool-down
+    run_distributed(_vpp_worker, 2, 2, 2, [])         # micro-batches == stages: all forwards, then all backwards
+    run_distributed(_vpp_worker, 3, 6, 2, [3])        # three stages
+
+
 def test_pipeline_1f1b_matches_single_process():
     run_distributed(_pp_worker, 2, 3)
     run_distributed(_pp_worker, 4, 6)
@@ -696,3 +782,23 @@ def _launch_pp_worker(rank, world):
 def test_launch_grpo_pp2():
     """GRPO with a 2-stage pipeline for training and a full-depth rollout replica per rank."""
     run_distributed(_launch_pp_worker, 2)
+
+
+def _launch_vpp_worker(rank, world):
+    """GRPO with an interleaved pipeline (2 stages x 2 chunks over 4 layer slots, one of them empty):
+    training through virtual stages, then the 3 real layers gathered into a full-depth rollout replica."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        "actor_config.pipeline_model_parallel_size=2", "actor_config.no_pad_to_seq_lengths=true",
+        "+actor_config.num_layers_per_virtual_pipeline_stage=1", "+actor_config.noop_layers=3",
+        "+model.tiny_qwen2.num_layers=4", "generate_config.infer_tensor_parallel_size=1",
+        "megatron_training.train_iters=2", f"rl_config.actor_resource.num_gpus={world}"])
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == 2 and all("actor/pg_loss" in m and m["timing/update"] > 0 for m in hist)
+        assert abs(hist[0]["actor/kl_loss"]) < 1e-4
+
+
+def test_launch_grpo_interleaved_pipeline_with_empty_slot():
+    run_distributed(_launch_vpp_worker, 2)
