@@ -46,6 +46,12 @@ MLA = dict(
     q_lora_rank=None, kv_lora_rank=None, v_head_dim=None,
 )
 
+# --- vision-language models ----------------------------------------------------------
+VISION = dict(
+    image_token_id=151655, video_token_id=151656, vision_start_token_id=151652, vision_end_token_id=151653,
+    patch_size=14, spatial_merge_size=2, mrope_section=None,
+)
+
 # --- mixture of experts -------------------------------------------------------------
 MOE = dict(
     num_experts=None, moe_router_topk=2, moe_ffn_hidden_size=None, n_shared_experts=None,
@@ -134,7 +140,7 @@ class MegatronConfig(SchemaConfig):
     (reference: ``megatron_config.py:381-385``).
     """
 
-    SCHEMA = merge_schemas(ARCH, ROPE_SCALING, MLA, MOE, FUSION, PARALLEL, OPTIM, MEMORY, RUN,
+    SCHEMA = merge_schemas(ARCH, ROPE_SCALING, MLA, VISION, MOE, FUSION, PARALLEL, OPTIM, MEMORY, RUN,
                            CKPT, ADAPT)
 
     def __init__(self, training_config=None, model_config=None):

@@ -79,3 +79,35 @@ def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tenso
         out[:, row, keep] = pos.to(out.device)
         deltas.append(nxt - s)
     return out, torch.tensor(deltas, device=input_ids.device).view(-1, 1)
+
+
+def mrope_table(position_ids: torch.Tensor, base_table: torch.Tensor, sections=(16, 24, 24)) -> torch.Tensor:
+    """Per-token rotary table for three-axis positions.  ``position_ids [T, 3]`` (temporal, height,
+    width), ``base_table [max_pos, d] = [cos | sin]`` of the one-axis rotary embedding, ``sections``:
+    how many of the ``d / 2`` frequencies follow each axis (scaled when ``d / 2`` differs from their
+    sum).  Returns ``[T, d]``: token ``t`` uses row ``t`` (rotate-half pairing, as ``ops.rope_`` expects)."""
+    half = base_table.shape[1] // 2
+    total = sum(sections)
+    bounds, acc = [0], 0
+    for sct in sections:
+        acc += sct
+        bounds.append(round(acc * half / total))
+    pos = position_ids.long().clamp(0, base_table.shape[0] - 1)
+    out = torch.empty(pos.shape[0], 2 * half, dtype=base_table.dtype, device=base_table.device)
+    for axis in range(3):
+        lo, hi = bounds[axis], bounds[axis + 1]
+        rows = base_table[pos[:, axis].to(base_table.device)]
+        out[:, lo:hi] = rows[:, lo:hi]
+        out[:, half + lo:half + hi] = rows[:, half + lo:half + hi]
+    return out
+
+
+def extend_positions(prompt_pos: torch.Tensor, n_new: int) -> torch.Tensor:
+    """Three-axis positions of a prompt ``[P, 3]`` followed by ``n_new`` text tokens: generated tokens
+    advance all axes together from the largest position of the prompt."""
+    if prompt_pos.numel() == 0:
+        start = 0
+    else:
+        start = int(prompt_pos.max()) + 1
+    tail = torch.arange(start, start + n_new, dtype=prompt_pos.dtype).unsqueeze(-1).expand(n_new, 3)
+    return torch.cat([prompt_pos, tail], dim=0)

@@ -37,6 +37,12 @@ class PackedMeta:
     max_seqlen: int
     positions: torch.Tensor           # [T]
     cp: Any = None                    # context-parallel helper (parallel.context_parallel), optional
+    # vision-language inputs (optional): rows of the vision tower's output that replace the embeddings of
+    # the image placeholder tokens at ``image_index`` (packed positions), and a per-token rotary table
+    # ``[T, head_dim]`` built from three-axis position ids (then ``positions`` just numbers the tokens)
+    image_index: Optional[torch.Tensor] = None
+    image_embeds: Optional[torch.Tensor] = None
+    rope_table: Optional[torch.Tensor] = None
 
     @classmethod
     def from_lengths(cls, lengths, device, align: int = 1) -> "PackedMeta":
@@ -185,7 +191,7 @@ def _attention_core_fwd(layer: TransformerLayer, qkv: torch.Tensor, meta: Packed
         pre = qkv.clone()
         rq = ops.headnorm_fwd_(qkv, lay, "q", sa.q_layernorm.weight, layer.cfg.norm_epsilon)
         rk = ops.headnorm_fwd_(qkv, lay, "k", sa.k_layernorm.weight, layer.cfg.norm_epsilon)
-    ops.rope_(qkv, lay, meta.positions, layer.rope_table(qkv.device))
+    ops.rope_(qkv, lay, meta.positions, meta.rope_table if meta.rope_table is not None else layer.rope_table(qkv.device))
     if meta.cp is not None:
         attn, lse = meta.cp.attention_fwd(qkv, lay, meta)
     else:
@@ -279,7 +285,8 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
     else:
         dqkv = ops.attn_varlen_bwd(dattn, ctx["qkv"], ctx["attn"], ctx["lse"], lay, meta.cu_seqlens,
                                    meta.max_seqlen, causal=True)
-    ops.rope_(dqkv, lay, meta.positions, layer.rope_table(dqkv.device), inverse=True)
+    ops.rope_(dqkv, lay, meta.positions, meta.rope_table if meta.rope_table is not None else layer.rope_table(dqkv.device),
+              inverse=True)
     if sa.q_layernorm is not None:
         ops.headnorm_bwd_(dqkv, ctx["pre"], lay, "q", sa.q_layernorm.weight, ctx["rq"],
                           grad_buffer(sa.q_layernorm.weight))
@@ -514,6 +521,17 @@ class GPTModel(nn.Module):
     def embed(self, ids: torch.Tensor) -> torch.Tensor:
         return _EmbedFn.apply(self.embedding.word_embeddings.weight, ids, self.comm, self.vocab_start)
 
+    def _place_image_embeds(self, h: torch.Tensor, meta: PackedMeta) -> torch.Tensor:
+        """Replace the embeddings of the image placeholder tokens by the vision tower's rows (constants:
+        the tower is frozen).  Under sequence parallelism ``h`` holds this rank's token shard."""
+        idx, rows = meta.image_index.long(), meta.image_embeds.to(h.dtype)
+        if self.comm.sequence_parallel:
+            per = h.shape[0]
+            lo = self.comm.rank * per
+            keep = (idx >= lo) & (idx < lo + per)
+            idx, rows = idx[keep] - lo, rows[keep]
+        return h.index_copy(0, idx, rows) if idx.numel() else h
+
     def run_layers(self, h: torch.Tensor, meta: PackedMeta, chunk: Optional[int] = None) -> torch.Tensor:
         layers = self.decoder.layers if chunk is None else \
             list(self.decoder.layers)[self.chunk_bounds[chunk]:self.chunk_bounds[chunk + 1]]
@@ -529,6 +547,8 @@ class GPTModel(nn.Module):
 
     def hidden_states(self, ids_or_h: torch.Tensor, meta: PackedMeta, chunk: Optional[int] = None) -> torch.Tensor:
         h = self.embed(ids_or_h) if self.is_first_chunk(chunk) else ids_or_h
+        if self.is_first_chunk(chunk) and meta.image_index is not None and meta.image_index.numel():
+            h = self._place_image_embeds(h, meta)
         if torch.is_grad_enabled() and not h.requires_grad and \
                 any(p.requires_grad for p in self.decoder.parameters()):
             # layer nodes only run their backward when an input requires grad

@@ -67,6 +67,33 @@ class MicroBatch:
         self.max_seqlen = int(padded.max()) if b else 0
         self.num_tokens = total
         self.data = {k: v[rows_t] for k, v in data.items() if torch.is_tensor(v) and v.shape[:1] == data["input_ids"].shape[:1]}
+        # vision-language rows: ``data["mm"][r] = dict(vit_embeds [n_r, H], position_ids [P_r, 3])`` per sample
+        self.image_index = self.image_embeds = self.pos3 = None
+        self.image_token_id = data.get("image_token_id")
+        mm = data.get("mm")
+        if mm is not None:
+            from ..datasets.mm_utils import extend_positions
+
+            embeds, pos3, index = [], [], []
+            for j, r in enumerate(rows_t.tolist()):
+                item = mm[r] or {}
+                n_tok = int(lens[j])
+                row_ids = ids2d[j, :n_tok]
+                where = torch.nonzero(row_ids == self.image_token_id).reshape(-1)
+                e = item.get("vit_embeds")
+                if e is not None and where.numel():
+                    if e.shape[0] != where.numel():
+                        raise ValueError(f"sample {r}: {where.numel()} image tokens but {e.shape[0]} embedding rows")
+                    embeds.append(e)
+                    index.append(where + int(cu[j]))
+                pp = item.get("position_ids")
+                pp = pp[:n_tok] if pp is not None else torch.arange(min(int(p_len[j]), n_tok)).unsqueeze(-1).expand(-1, 3)
+                full = extend_positions(pp, max(n_tok - pp.shape[0], 0))
+                pad = int(padded[j]) - n_tok
+                pos3.append(torch.cat([full, full.new_zeros(pad, 3)]) if pad else full)
+            self.pos3 = torch.cat(pos3) if pos3 else None
+            if embeds:
+                self.image_index, self.image_embeds = torch.cat(index), torch.cat(embeds)
 
     def _pack(self):
         if self._packed is None:
@@ -88,6 +115,10 @@ class MicroBatch:
             ids2d = ids2d.to(torch.int32)              # half the bytes over PCIe
         self._ids2d = to_device(ids2d, ids2d.dtype, device)
         self._packed = None
+        for k in ("image_index", "image_embeds", "pos3"):
+            t = getattr(self, k)
+            if t is not None:
+                setattr(self, k, to_device(t, t.dtype, device))
         return self
 
     def response_rows(self, per_token: torch.Tensor) -> torch.Tensor:
@@ -100,8 +131,18 @@ class MicroBatch:
             return unpack_response(per_token, self.cu, self._p_len, self._r_len, self.resp_index.shape[1])
         return per_token[self.resp_index] * self.resp_valid
 
-    def meta(self) -> PackedMeta:
-        return PackedMeta(self.cu, self.max_seqlen, self.positions)
+    def meta(self, rope_table_of=None) -> PackedMeta:
+        """``rope_table_of(device)``: the model's one-axis rotary table, needed to build the per-token table
+        of three-axis positions (vision-language rows only)."""
+        if self.pos3 is None:
+            return PackedMeta(self.cu, self.max_seqlen, self.positions)
+        from ..datasets.mm_utils import mrope_table
+
+        if getattr(self, "_rope_tab", None) is None:
+            self._rope_tab = mrope_table(self.pos3, rope_table_of(self.pos3.device))
+        order = torch.arange(self.num_tokens, dtype=torch.int32, device=self.pos3.device)
+        return PackedMeta(self.cu, self.max_seqlen, order, image_index=self.image_index, image_embeds=self.image_embeds,
+                          rope_table=self._rope_tab)
 
 
 class TrainingEngine:
@@ -187,11 +228,11 @@ class TrainingEngine:
             en = mb.response_rows(cp.gather_tokens(ent)) if want_entropy else None
             return lp, en
         if self.loss_func.output_kind == "value":
-            v = core.forward_values(x, mb.meta(), **kw)
+            v = core.forward_values(x, mb.meta(self._rope_table_of), **kw)
             if self.role == "reward":
                 return v[mb.last_index].unsqueeze(-1), None
             return mb.response_rows(v), None
-        logp, ent = core.forward_logprob(x, mb.labels, mb.meta(), self.temperature, want_entropy, **kw)
+        logp, ent = core.forward_logprob(x, mb.labels, mb.meta(self._rope_table_of), self.temperature, want_entropy, **kw)
         lp = mb.response_rows(logp)
         en = mb.response_rows(ent) if want_entropy else None
         return lp, en
@@ -203,10 +244,13 @@ class TrainingEngine:
             kw = {} if chunk is None else {"chunk": chunk}
             cp = self._context_parallel(mb)
             if cp is None:
-                return self.core.hidden_states(mb.ids if h_in is None else h_in, mb.meta(), **kw)
+                return self.core.hidden_states(mb.ids if h_in is None else h_in, mb.meta(self._rope_table_of), **kw)
             meta = PackedMeta(cp.cu_local, cp.max_local, cp.take_local(mb.positions), cp=cp)
             return self.core.hidden_states(cp.take_local(mb.ids) if h_in is None else h_in, meta, **kw)
         return self._run_model(mb, want_entropy, h_in, chunk)
+
+    def _rope_table_of(self, device) -> torch.Tensor:
+        return self.core.decoder.layers[0].rope_table(device)
 
     def _context_parallel(self, mb: MicroBatch):
         """Context-parallel helper of this micro-batch (cached on it), ``None`` without CP."""

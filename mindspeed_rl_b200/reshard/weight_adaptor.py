@@ -50,6 +50,26 @@ _MLA = [
 ]
 
 
+_VISION = [      # Qwen2.5-VL: vision tower ("visual.") beside the language model
+    ("visual.patch_embed.proj.weight", "vision_model.patch_embed.weight"),
+    ("visual.blocks.{i}.norm1.weight", "vision_model.blocks.{i}.norm1.weight"),
+    ("visual.blocks.{i}.norm2.weight", "vision_model.blocks.{i}.norm2.weight"),
+    ("visual.blocks.{i}.attn.qkv.weight", "vision_model.blocks.{i}.qkv.weight"),
+    ("visual.blocks.{i}.attn.qkv.bias", "vision_model.blocks.{i}.qkv.bias"),
+    ("visual.blocks.{i}.attn.proj.weight", "vision_model.blocks.{i}.proj.weight"),
+    ("visual.blocks.{i}.attn.proj.bias", "vision_model.blocks.{i}.proj.bias"),
+    ("visual.blocks.{i}.mlp.gate_up_proj.weight", "vision_model.blocks.{i}.gate_up.weight"),
+    ("visual.blocks.{i}.mlp.gate_up_proj.bias", "vision_model.blocks.{i}.gate_up.bias"),
+    ("visual.blocks.{i}.mlp.down_proj.weight", "vision_model.blocks.{i}.down.weight"),
+    ("visual.blocks.{i}.mlp.down_proj.bias", "vision_model.blocks.{i}.down.bias"),
+    ("visual.merger.ln_q.weight", "vision_model.merger_norm.weight"),
+    ("visual.merger.mlp.0.weight", "vision_model.merger.0.weight"),
+    ("visual.merger.mlp.0.bias", "vision_model.merger.0.bias"),
+    ("visual.merger.mlp.2.weight", "vision_model.merger.2.weight"),
+    ("visual.merger.mlp.2.bias", "vision_model.merger.2.bias"),
+]
+
+
 def _compile(pattern: str) -> re.Pattern:
     rx = re.escape(pattern).replace(r"\{i\}", r"(?P<i>\d+)").replace(r"\{e\}", r"(?P<e>\d+)")
     return re.compile("^" + rx + "$")
@@ -149,6 +169,7 @@ def get_weight_adaptor(arch: str) -> WeightAdaptor:
 
 register_weight_adaptor(["Qwen2ForCausalLM", "LlamaForCausalLM", "CustomQwen2ForCausalLM"], _DENSE)
 register_weight_adaptor(["Qwen3ForCausalLM"], _DENSE + _QK_NORM)
+register_weight_adaptor(["Qwen2_5_VLForConditionalGeneration", "Qwen2VLForConditionalGeneration"], _DENSE + _VISION)
 register_weight_adaptor(["Qwen3MoeForCausalLM", "CustomQwen3MoeForCausalLM"], _DENSE + _QK_NORM + _MOE)
 register_weight_adaptor(["DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM", "CustomDeepseekV3ForCausalLM"],
                         [r for r in _DENSE if "qkv_proj" not in r[0]] + _MLA + _MOE)

@@ -138,7 +138,9 @@ class LLMEngine(BaseInferEngine):
 
     # ---- request API ---------------------------------------------------------------------------
     def add_request(self, request_id: Optional[str], prompt_token_ids: Seq_[int],
-                    params: SamplingParams) -> str:
+                    params: SamplingParams, mm: Optional[dict] = None) -> str:
+        """``mm`` (vision-language prompt): ``dict(vit_embeds [n, H], position_ids [P, 3], image_token_id)``;
+        the placeholder tokens' embeddings are replaced by the rows of ``vit_embeds`` in the prefill."""
         # generated ids must be the same on every rank of a rollout TP group (they seed the
         # per-request sampling stream, and the ranks must draw the same tokens): a counter, not a uuid
         self._request_counter = getattr(self, "_request_counter", 0) + 1
@@ -146,6 +148,16 @@ class LLMEngine(BaseInferEngine):
         if rid in self.scheduler.groups:
             raise ValueError(f"request id {rid} is already in flight")
         lead = Sequence(rid, list(int(t) for t in prompt_token_ids), params, sample_index=0)
+        if mm is not None and mm.get("vit_embeds") is not None:
+            if self.enable_prefix_caching:
+                raise ValueError("prefix caching keys blocks by token ids only and cannot tell two images apart; "
+                                 "turn enable_prefix_caching off for vision-language rollouts")
+            self.image_token_id = int(mm.get("image_token_id", 151655))
+            lead.mm_embeds = mm["vit_embeds"]
+            pos3 = mm.get("position_ids")
+            if pos3 is not None:
+                lead.mm_positions = pos3[:len(lead.prompt_ids)]
+                lead.pos_delta = int(lead.mm_positions.max()) + 1 - len(lead.prompt_ids) if len(lead.prompt_ids) else 0
         self.scheduler.add_group(RequestGroup(rid, params, [lead]))
         return rid
 
@@ -289,7 +301,7 @@ class LLMEngine(BaseInferEngine):
             prefix = dict(block_tables=to_device(bt, torch.int32, dev), token_seq=pt[0].to(torch.int32),
                           token_pos=pt[1].to(torch.int32), cu_k=to_device(cu_k, torch.int32, dev))
         logits = self.runner.prefill(t_ids, t_pos, t_slots, t_cu, max(it.length for it in items), t_last,
-                                     prefix)
+                                     prefix, self._prefill_mm(items, ids, pos))
         self.stats["prefill_tokens"] += len(ids)
         for it in items:
             it.seq.num_computed = it.start + it.length
@@ -315,6 +327,38 @@ class LLMEngine(BaseInferEngine):
         for s, tok_, lp in zip(seqs, tokens, lps):
             self._append_token(s, tok_, lp)
 
+    def _prefill_mm(self, items, ids: List[int], pos: List[int]) -> Optional[dict]:
+        """Vision-language part of a prefill batch (``None`` for text-only batches): packed positions of the
+        image placeholder tokens with their embedding rows, and the per-token rotary table."""
+        if not any(it.seq.mm_embeds is not None for it in items):
+            return None
+        from ..datasets.mm_utils import extend_positions, mrope_table
+
+        index, rows, pos3, base = [], [], [], 0
+        for it in items:
+            s = it.seq
+            chunk = ids[base:base + it.length]
+            if s.mm_embeds is not None:
+                tok = self.image_token_id
+                before = sum(1 for t in s.all_ids[:it.start] if t == tok)       # placeholders of earlier chunks
+                where = [j for j, t in enumerate(chunk) if t == tok]
+                if where:
+                    index.extend(base + j for j in where)
+                    rows.append(s.mm_embeds[before:before + len(where)])
+            if s.mm_positions is not None:
+                full = extend_positions(s.mm_positions, max(it.start + it.length - s.mm_positions.shape[0], 0))
+                pos3.append(full[it.start:it.start + it.length])
+            else:
+                pos3.append(torch.tensor(pos[base:base + it.length]).unsqueeze(-1).expand(-1, 3))
+            base += it.length
+        dev = self.device
+        table = mrope_table(torch.cat(pos3), self.runner.rope_table())
+        out = dict(rope_table=table.to(dev))
+        if index:
+            out["image_index"] = to_device(index, torch.int64, dev)
+            out["image_embeds"] = torch.cat(rows).to(dev)
+        return out
+
     def _launch_decode(self, seqs: List[Sequence], prev: Optional[dict] = None) -> dict:
         """Launch one decode step and its sampling; nothing is read back.
 
@@ -332,7 +376,7 @@ class LLMEngine(BaseInferEngine):
         else:
             row_of = {id(s): i for i, s in enumerate(prev["seqs"])}
             last = [row_of[id(s)] for s in seqs]          # rows of the pending step's token tensor
-        rows = [last, [n - 1 for n in lens], slots, lens, keys]
+        rows = [last, [n - 1 + s.pos_delta for s, n in zip(seqs, lens)], slots, lens, keys]
         grouped = False
         if self.shared_prefix_decode and dev.type == "cuda":
             # samples of one prompt share the prompt's K/V: read it once per group
@@ -436,12 +480,13 @@ class LLMEngine(BaseInferEngine):
 
     # ---- convenience -----------------------------------------------------------------------------
     def generate(self, prompts: Seq_[Seq_[int]], params: SamplingParams,
-                 request_ids: Optional[Seq_[str]] = None) -> List[RequestOutput]:
+                 request_ids: Optional[Seq_[str]] = None, mm: Optional[Seq_[Optional[dict]]] = None
+                 ) -> List[RequestOutput]:
         """Blocking generation; results come back in the order of ``prompts``.  ``params`` may be
         one ``SamplingParams`` or a list with one entry per prompt."""
         per_prompt = isinstance(params, (list, tuple))
         rids = [self.add_request(None if request_ids is None else request_ids[i], p,
-                                 params[i] if per_prompt else params)
+                                 params[i] if per_prompt else params, None if mm is None else mm[i])
                 for i, p in enumerate(prompts)]
         done: Dict[str, RequestOutput] = {}
         while self.any_unfinished_requests():

@@ -118,7 +118,7 @@ class ModelRunner:
         h = w.embed[local.clamp(0, w.embed.shape[0] - 1)] * mine.unsqueeze(-1).to(w.embed.dtype)
         return self.comm.all_reduce(h)
 
-    def _layer(self, li: int, lw: LayerWeights, resid, delta, positions, attend):
+    def _layer(self, li: int, lw: LayerWeights, resid, delta, positions, attend, rope_tab=None):
         cfg = self.cfg
         x, _, resid = ops.rmsnorm_fwd(delta, lw.input_norm, cfg.norm_epsilon, residual=resid,
                                       want_rstd=False) if resid is not None else \
@@ -135,7 +135,7 @@ class ModelRunner:
             if lw.q_norm is not None:
                 ops.headnorm_fwd_(qkv, lay, "q", lw.q_norm, cfg.norm_epsilon)
                 ops.headnorm_fwd_(qkv, lay, "k", lw.k_norm, cfg.norm_epsilon)
-            ops.rope_(qkv, lay, positions, self.rope_table())
+            ops.rope_(qkv, lay, positions, self.rope_table() if rope_tab is None else rope_tab)
         attn = attend(li, qkv, lay)
         delta = self.comm.all_reduce(torch.matmul(attn, lw.o_w.t()))
         x, _, resid = ops.rmsnorm_fwd(delta, lw.post_norm, cfg.norm_epsilon, residual=resid,
@@ -157,12 +157,19 @@ class ModelRunner:
             if lw.moe is not None:
                 lw.moe.forward(empty, self.comm)
 
-    def _forward(self, ids, positions, attend) -> torch.Tensor:
-        """Returns the final hidden states ``[T, H]`` (after the last norm)."""
+    def _forward(self, ids, positions, attend, mm: Optional[dict] = None) -> torch.Tensor:
+        """Returns the final hidden states ``[T, H]`` (after the last norm).  ``mm`` (vision-language
+        prompts): ``image_index`` / ``image_embeds`` replace placeholder embeddings, ``rope_table [T, d]``
+        is the per-token rotary table of three-axis positions (``positions`` then numbers the tokens)."""
         w = self.weights
         resid, delta = None, self._embed(ids)
+        rope_tab = None
+        if mm is not None:
+            if mm.get("image_index") is not None and mm["image_index"].numel():
+                delta = delta.index_copy(0, mm["image_index"], mm["image_embeds"].to(delta.dtype))
+            rope_tab = mm.get("rope_table")
         for li, lw in enumerate(w.layers):
-            resid, delta = self._layer(li, lw, resid, delta, positions, attend)
+            resid, delta = self._layer(li, lw, resid, delta, positions, attend, rope_tab)
         x, _, _ = ops.rmsnorm_fwd(delta, w.final_norm, self.cfg.norm_epsilon, residual=resid,
                                   want_rstd=False)
         return x
@@ -174,7 +181,7 @@ class ModelRunner:
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
                 cu_q: torch.Tensor, max_q: int, last_index: torch.Tensor,
-                prefix: Optional[dict] = None) -> torch.Tensor:
+                prefix: Optional[dict] = None, mm: Optional[dict] = None) -> torch.Tensor:
         """Run packed prompt chunks. ``last_index`` selects the rows whose logits are needed.
 
         ``prefix`` (for chunks that start inside a sequence) carries ``block_tables``,
@@ -194,7 +201,7 @@ class ModelRunner:
                                          cu_seqlens_k=prefix["cu_k"])
             return out
 
-        x = self._forward(ids, positions, attend)
+        x = self._forward(ids, positions, attend, mm)
         return self._logits(x[last_index])
 
     # ------------------------------------------------------------------------------------------

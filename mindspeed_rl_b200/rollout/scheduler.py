@@ -73,6 +73,11 @@ class Sequence:
     num_preemptions: int = 0
     prefill_target: int = 0        # tokens to prefill since the last admission
     arrival: int = 0
+    # vision-language prompts: rows of the vision tower for the image placeholder tokens (in order),
+    # three-axis positions of the prompt, and what decoding adds to its one-axis position counter
+    mm_embeds: Optional[object] = None
+    mm_positions: Optional[object] = None
+    pos_delta: int = 0
 
     @property
     def all_ids(self) -> List[int]:
@@ -261,6 +266,7 @@ class Scheduler:
         created = []
         for i in range(1, g.params.n):
             child = Sequence(lead.request_id, list(lead.prompt_ids), g.params, sample_index=i)
+            child.mm_embeds, child.mm_positions, child.pos_delta = lead.mm_embeds, lead.mm_positions, lead.pos_delta
             child.arrival = next(self._clock)
             child.status = SeqStatus.RUNNING
             child.num_computed = lead.num_computed

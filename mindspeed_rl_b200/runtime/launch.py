@@ -79,6 +79,20 @@ def build_data_iter(actor_config, rl_config, tokenizer, consumed_train_samples: 
     return loader if reiterable else InfiniteLoader(loader)
 
 
+def build_mm_data_iter(actor_config, rl_config, tokenizer):
+    """Prompt iterator of a vision-language run (``datasets.multimodal_dataset``); only the driver reads it."""
+    from ..datasets.image_processor import ImageProcessor
+    from ..datasets.multimodal_dataset import MultiModalDataset, MultiModalPromptLoader
+
+    proc = ImageProcessor(actor_config.patch_size, actor_config.spatial_merge_size)
+    ds = MultiModalDataset(actor_config.data_path, tokenizer, proc, max_prompt_length=rl_config.max_prompt_length,
+                           image_token_id=actor_config.image_token_id,
+                           vision_start_token_id=actor_config.vision_start_token_id,
+                           vision_end_token_id=actor_config.vision_end_token_id, truncation="left")
+    return iter(MultiModalPromptLoader(ds, actor_config.global_batch_size, actor_config.seed or 0,
+                                       shuffle=not actor_config.no_shuffle))
+
+
 def role_parallel_state(mc, placement, role: str, rank: int):
     """Process groups of a role that owns a rank range of its own.  Collective over the whole job:
     every rank creates every group, the members keep them."""
@@ -187,9 +201,21 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
         swanlab_exp_name=rl_config.swanlab_exp_name, swanlab_save_dir=rl_config.swanlab_save_dir,
         swanlab_mode=rl_config.swanlab_mode, pad_token_id=pad)
     consumed = actor_group.get_consumed_train_samples()
+    vit_group = None
+    if rl_config.is_multimodal:
+        # vision-language run: the vision tower is a stage of its own (on the actor's ranks, or on
+        # ``vit_resource``), the prompts come from the multimodal dataset
+        from ..workers.vit_worker import VitWorker
+
+        def vit_factory():
+            w = VitWorker(cfg.get("vit_config"), rl_config, actor_config.hidden_size)
+            w._state = states["actor"] if placement.colocated("vit", "actor") else None
+            return w
+        vit_group = SPMDWorkerGroup(factory=vit_factory, ranks=placement.of("vit"), overlapping=disjoint).initialize()
     if algorithm == "grpo":
-        trainer = RayGRPOTrainer(actor_group, ref_worker=ref_group, reward_list=rewards, **common)
-        data = build_data_iter(actor_config, rl_config, tokenizer, consumed)
+        trainer = RayGRPOTrainer(actor_group, ref_worker=ref_group, reward_list=rewards, vit_worker=vit_group, **common)
+        data = build_mm_data_iter(actor_config, rl_config, tokenizer) if rl_config.is_multimodal else \
+            build_data_iter(actor_config, rl_config, tokenizer, consumed)
     elif algorithm == "dapo":
         trainer = RayDAPOTrainer(actor_group, reward_list=rewards, **common)
         data = build_data_iter(actor_config, rl_config, tokenizer, consumed, reiterable=True)

@@ -20,8 +20,9 @@ from .compute_utils import compute_advantage, compute_grpo_data_metrics
 
 
 class RayGRPOTrainer(RayBaseTrainer):
-    def __init__(self, actor_worker, ref_worker=None, reward_list=None, **kw):
+    def __init__(self, actor_worker, ref_worker=None, reward_list=None, vit_worker=None, **kw):
         super().__init__(actor_worker, ref_worker or actor_worker, reward_list, **kw)
+        self.vit_worker = vit_worker          # vision-encoder stage of vision-language runs (or None)
         self.enable_partial_rollout = self.partial_rollout_max_split > 1
         self.metrics = Metric()
         self.td_max_len = self.global_batch_size * (2 if self.enable_partial_rollout else 1)
@@ -37,9 +38,20 @@ class RayGRPOTrainer(RayBaseTrainer):
                                   max_age=self.partial_rollout_max_split, GBS_train=self.global_batch_size,
                                   addition_columns=self.dataset_additional_keys)
         self.transfer_dock = self._share_dock(dock)
-        self.actor_worker.sync_init_transfer_dock(self.transfer_dock)
+        self.mm_transfer_dock = None
+        rl = getattr(self.actor_worker, "rl_config", None)
+        if rl is not None and rl.is_multimodal:
+            from ..data.mm_transfer_dock import MMGRPOTransferDock
+
+            mm = MMGRPOTransferDock(self.td_max_len, self.n_samples_per_prompt, rl.reuse_image_embeds) \
+                if self.is_driver else None
+            self._dock_descriptor = None
+            self.mm_transfer_dock = self._share_dock(mm, "mm_td")
+        self.actor_worker.sync_init_transfer_dock(self.transfer_dock, self.mm_transfer_dock)
+        if self.vit_worker is not None:
+            self.vit_worker.sync_init_transfer_dock(self.transfer_dock, self.mm_transfer_dock)
         if self.ref_worker is not self.actor_worker:
-            self.ref_worker.sync_init_transfer_dock(self.transfer_dock)
+            self.ref_worker.sync_init_transfer_dock(self.transfer_dock, self.mm_transfer_dock)
         for r in self.reward_list:
             (getattr(r, "sync_init_transfer_dock", None) or r.init_transfer_dock)(self.transfer_dock)
 
@@ -67,7 +79,15 @@ class RayGRPOTrainer(RayBaseTrainer):
                                                    self.dataset_additional_keys,
                                                    add_another_batch=self.enable_partial_rollout)
                 td.put_experience(padding_dict_to_tensor_dict(data), idx, is_prompt=True)
+                if self.mm_transfer_dock is not None and batch.get("mm"):
+                    n_prompts = len(batch["prompts"])
+                    first = idx[0] // self.n_samples_per_prompt
+                    self.mm_transfer_dock.put_experience(batch["mm"], list(range(first, first + n_prompts)))
             self._driver_section_done()
+            # vision-language runs: the vision tower runs once per prompt, everyone else reads its output
+            if self.vit_worker is not None:
+                self.vit_worker.compute_image_embeds(blocking=True)
+                self._driver_section_done()
             # rollout
             self.actor_worker.generate_sequences(blocking=self.blocking)
             # rewards + advantages (driver-side CPU stages)
@@ -114,6 +134,8 @@ class RayGRPOTrainer(RayBaseTrainer):
                 self.log_metrics(m, iteration, self.train_iters)
                 history.append(m)
                 td.clear()
+                if self.mm_transfer_dock is not None:
+                    self.mm_transfer_dock.clear()
             self._driver_section_done()
             if self.save_interval and (iteration % self.save_interval == 0 or iteration == self.train_iters):
                 self.save_checkpoint(iteration)

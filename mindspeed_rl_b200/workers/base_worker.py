@@ -38,6 +38,19 @@ def pad_batch(ragged: Dict[str, List[torch.Tensor]], pad_id: int, multiple: int 
     return out
 
 
+def _align_mm(mm, cols):
+    """One dict per sample with the per-prompt items of the requested columns (``None`` for fillers)."""
+    names = list(cols)
+    out, k = [], 0
+    for m in mm:
+        if m is None:
+            out.append(None)
+            continue
+        out.append({c: cols[c][k] for c in names})
+        k += 1
+    return out
+
+
 def check_device_status(stage: str = "") -> None:
     """Stage boundary: read the status words the kernels' bounded waits report through (tcgen05
     pipelines, peer-memory barriers and slabs) and raise if one of them gave up, instead of handing
@@ -118,10 +131,11 @@ class BaseWorker:
     def dispatch_transfer_dock_data(self, consumer: str, columns: Sequence[str], experience_count: int,
                                     pad_multiple: int = 1, indexes: Optional[List[int]] = None,
                                     get_n_samples: bool = True, use_batch_seqlen_balance: bool = False,
-                                    dp_size: int = 1
+                                    dp_size: int = 1, mm_columns: Optional[Sequence[str]] = None
                                     ) -> Tuple[Optional[Dict[str, torch.Tensor]], Optional[List[int]], bool]:
         """Returns ``(batch, indexes, finished)``.  ``finished`` is True when the consumer has
-        nothing left to process in this iteration (then ``batch`` is ``None``)."""
+        nothing left to process in this iteration (then ``batch`` is ``None``).  ``mm_columns``: per-prompt
+        columns of the multimodal store to attach as ``batch["mm"]`` (one dict per sample)."""
         group, src, size = self._replica_group()
         payload = None
         if self.is_replica_leader():
@@ -132,7 +146,14 @@ class BaseWorker:
                                                     dp_size=dp_size, indexes=indexes,
                                                     get_n_samples=get_n_samples,
                                                     use_batch_seqlen_balance=use_batch_seqlen_balance)
-                payload = (batch, idx, False)
+                mm = None
+                mm_td = getattr(self, "mm_td", None)
+                if mm_columns and mm_td is not None and idx:
+                    cols = mm_td.get_experience_dict(list(mm_columns), [i for i in idx if i >= 0], get_n_samples=False)
+                    mm = _align_mm([({} if i >= 0 else None) for i in idx], cols)
+                payload = (batch, idx, False, mm)
+        if payload is not None and len(payload) == 3:
+            payload = payload + (None,)
         if size > 1 and dist.is_initialized():
             channel = self._side_channel(group, src, size)
             if channel is not None:          # host-side ZeroMQ fan-out, no collective on the device stream
@@ -141,11 +162,14 @@ class BaseWorker:
                 box = [payload]
                 dist.broadcast_object_list(box, src=src, group=group)
                 payload = box[0]
-        batch, idx, finished = payload
+        batch, idx, finished, mm = payload
         if finished or not batch or not idx:
             return None, None, finished
         ragged = remove_padding_tensor_dict_to_dict(batch)
-        return pad_batch(ragged, self.pad_token_id, pad_multiple), idx, False
+        out = pad_batch(ragged, self.pad_token_id, pad_multiple)
+        if mm is not None:
+            out["mm"] = mm
+        return out, idx, False
 
     def collect_transfer_dock_data(self, output: Dict[str, torch.Tensor], indexes: List[int],
                                    lengths: Optional[torch.Tensor] = None) -> None:

@@ -269,7 +269,19 @@ class IntegratedWorker(BaseWorker):
 
     def init_transfer_dock(self, td, mm_td=None, sampling_transfer_dock=None) -> None:
         self.td = td
+        self.mm_td = mm_td
         self.sampling_td = sampling_transfer_dock
+
+    # vision-language runs: what the language model reads from the multimodal store per sample
+    MM_COLUMNS = ("vit_embeds", "position_ids")
+
+    def _mm_columns(self):
+        return self.MM_COLUMNS if (getattr(self, "mm_td", None) is not None and self.rl_config.is_multimodal) else None
+
+    def _with_image_token(self, batch):
+        if batch is not None and "mm" in batch:
+            batch["image_token_id"] = int(getattr(self.actor_config, "image_token_id", None) or 151655)
+        return batch
 
     def get_iteration(self) -> int:
         return self.iteration
@@ -322,7 +334,8 @@ class IntegratedWorker(BaseWorker):
         try:
             while True:
                 batch, idx, finished = self.dispatch_transfer_dock_data(
-                    "actor_rollout", columns, rl.actor_rollout_dispatch_size, get_n_samples=not partial)
+                    "actor_rollout", columns, rl.actor_rollout_dispatch_size, get_n_samples=not partial,
+                    mm_columns=self._mm_columns())
                 if finished:
                     break
                 if batch is None:
@@ -364,7 +377,11 @@ class IntegratedWorker(BaseWorker):
         prompts, plen = batch["prompts"], batch["prompt_length"].reshape(-1)
         uniq = list(range(0, len(idx), n))                   # the store holds n copies per prompt
         prompt_lists = [prompts[i, :int(plen[i])].tolist() for i in uniq]
-        outs = self.engine.generate(prompt_lists, self.sampling_params)
+        mm = None
+        if batch.get("mm") is not None:
+            tok = int(getattr(self.actor_config, "image_token_id", None) or 151655)
+            mm = [dict(batch["mm"][i] or {}, image_token_id=tok) for i in uniq]
+        outs = self.engine.generate(prompt_lists, self.sampling_params, mm=mm)
         vocab = self.tcfg.vocab_size
         responses, input_ids, lengths = [], [], []
         for p, o in zip(prompt_lists, outs):
@@ -467,13 +484,13 @@ class IntegratedWorker(BaseWorker):
         while True:
             batch, idx, finished = self.dispatch_transfer_dock_data(
                 consumer, columns, dispatch_size, pad_multiple=1, get_n_samples=False,
-                use_batch_seqlen_balance=self.rl_config.use_dp_batch_balance)
+                use_batch_seqlen_balance=self.rl_config.use_dp_batch_balance, mm_columns=self._mm_columns())
             if finished:
                 break
             if batch is None:
                 time.sleep(0.002)
                 continue
-            lp = engine.forward(batch)
+            lp = engine.forward(self._with_image_token(batch))
             self.collect_transfer_dock_data({out_column: lp}, idx, lengths=batch["response_length"])
         self.update_metrics(timing_key, [round(_now(), 4), round(start, 4)])
 
@@ -512,13 +529,13 @@ class IntegratedWorker(BaseWorker):
         while True:
             batch, idx, finished = self.dispatch_transfer_dock_data(
                 "actor_train", columns, rl.actor_update_dispatch_size, get_n_samples=False,
-                use_batch_seqlen_balance=rl.use_dp_batch_balance)
+                use_batch_seqlen_balance=rl.use_dp_batch_balance, mm_columns=self._mm_columns())
             if finished:
                 break
             if batch is None:
                 time.sleep(0.002)
                 continue
-            metrics = self.actor.update(batch, kl_ctrl)
+            metrics = self.actor.update(self._with_image_token(batch), kl_ctrl)
             self.consumed_train_samples += len(idx) * self.parallel_state.size("dp_cp")
             if self.is_writer():
                 self.td.update_metrics("", value=metrics, cumulate=True)
