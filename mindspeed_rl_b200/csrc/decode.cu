@@ -89,6 +89,7 @@ struct DecodeParams {
   const int* group_rows;    // [n_groups, kGroupMax] batch rows (-1 = empty)
   const int* group_prefix;  // [n_groups] shared keys of the group
   int npre;                 // prefix splits (slots 0 .. npre-1)
+  int block_shift;          // log2(block_size), or -1 when it is not a power of two
 };
 
 constexpr int kGroupMax = 8;
@@ -129,8 +130,15 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeParams p)
       const int key = base + r;
       const bool ok = key < kend;
       const int kk = ok ? key : kbeg;
-      const int blk = bt[kk / p.block_size];
-      const long long src = (((long long)blk * p.block_size + kk % p.block_size) * p.nkv + hk) * D + c * 8;
+      int blk, off;
+      if (p.block_shift >= 0) {
+        blk = __ldg(bt + (kk >> p.block_shift));
+        off = kk & (p.block_size - 1);
+      } else {
+        blk = __ldg(bt + kk / p.block_size);
+        off = kk % p.block_size;
+      }
+      const long long src = (((long long)blk * p.block_size + off) * p.nkv + hk) * D + c * 8;
       cp_async16(sK + (stage * CH + r) * LD + c * 8, p.k_cache + src, ok);
       cp_async16(sV + (stage * CH + r) * LD + c * 8, p.v_cache + src, ok);
     }
@@ -279,16 +287,20 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeParams p)
 // against each 64-key chunk of the shared prefix, which is therefore read from HBM once per group.
 // Grid (group, kv head, prefix split); partial results go to slots [0, npre) of every member and
 // are merged with the members' own suffix partials by the merge kernel.
-// keys per pipeline stage of the shared-prefix kernel: 32 keeps a CTA at 52 KB of shared memory (D = 128),
-// so that four CTAs share an SM and hide each other's load latency
+// Pipeline of the shared-prefix kernel: 32 keys per stage, three stages (two chunks in flight while one
+// is multiplied), 70 KB of shared memory per CTA at D = 128, so three CTAs share an SM.  The kernel is
+// bound by instruction issue and load latency, not by bytes, hence: block ids by shift / mask when the
+// block size is a power of two, the query fragments held in registers for the whole pass, and the
+// rescale of the output accumulators skipped while no row of the warp raised its running maximum.
 constexpr int kPrefixChunk = 32;
+constexpr int kPrefixStages = 3;
 template <int D>
 __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodeParams p) {
-  constexpr int CH = kPrefixChunk, LD = D + 8, THREADS = 128, ROWS = 64;
+  constexpr int CH = kPrefixChunk, LD = D + 8, THREADS = 128, ROWS = 64, ST = kPrefixStages;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // 64 x LD
-  __nv_bfloat16* sK = sQ + ROWS * LD;                               // 2 x CH x LD
-  __nv_bfloat16* sV = sK + 2 * CH * LD;                             // 2 x CH x LD
+  __nv_bfloat16* sK = sQ + ROWS * LD;                               // ST x CH x LD
+  __nv_bfloat16* sV = sK + ST * CH * LD;                            // ST x CH x LD
 
   const int g = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
   const int rep = p.nh / p.nkv;
@@ -314,22 +326,39 @@ __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodePa
     const __nv_bfloat16* src = p.q + head_offset(p.Lq, ok ? b : lead, hk * rep + r % rep) + c * 8;
     cp_async16(sQ + r * LD + c * 8, src, ok);
   }
+  cp_async_commit();
   const int* bt = p.block_tables + (long long)lead * p.max_blocks;
+  const int shift = p.block_shift, mask = p.block_size - 1;
+  const long long row_elems = (long long)p.nkv * D;
+  const int my_r = threadIdx.x / (D / 8), my_c = (threadIdx.x % (D / 8)) * 8;   // first row / column of this thread
+  constexpr int RSTEP = THREADS / (D / 8);                                      // rows between its copies
   auto issue = [&](int chunk, int stage) {
     const int base = kbeg + chunk * CH;
-    for (int i = threadIdx.x; i < CH * (D / 8); i += THREADS) {
-      const int r = i / (D / 8), c = i % (D / 8);
+#pragma unroll
+    for (int it = 0; it < CH / RSTEP; ++it) {
+      const int r = my_r + it * RSTEP;
       const int key = base + r;
       const bool ok = key < kend;
       const int kk = ok ? key : kbeg;
-      const int blk = bt[kk / p.block_size];
-      const long long src = (((long long)blk * p.block_size + kk % p.block_size) * p.nkv + hk) * D + c * 8;
-      cp_async16(sK + (stage * CH + r) * LD + c * 8, p.k_cache + src, ok);
-      cp_async16(sV + (stage * CH + r) * LD + c * 8, p.v_cache + src, ok);
+      int blk, off;
+      if (shift >= 0) {
+        blk = __ldg(bt + (kk >> shift));
+        off = kk & mask;
+      } else {
+        blk = __ldg(bt + kk / p.block_size);
+        off = kk % p.block_size;
+      }
+      const long long src = ((long long)blk * p.block_size + off) * row_elems + (long long)hk * D + my_c;
+      cp_async16(sK + (stage * CH + r) * LD + my_c, p.k_cache + src, ok);
+      cp_async16(sV + (stage * CH + r) * LD + my_c, p.v_cache + src, ok);
     }
   };
-  if (n_chunks > 0) issue(0, 0);
-  cp_async_commit();
+  // prologue: ST - 1 chunks in flight (one commit group per chunk, empty groups keep the count uniform)
+#pragma unroll
+  for (int s = 0; s < ST - 1; ++s) {
+    if (s < n_chunks) issue(s, s);
+    cp_async_commit();
+  }
 
   float o_acc[D / 8][4];
 #pragma unroll
@@ -337,17 +366,25 @@ __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodePa
 #pragma unroll
     for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  const __nv_bfloat16* tQ = sQ + warp * 16 * LD;   // this warp's 16 query rows
+
+  // this warp's 16 query rows as A fragments, loaded once
+  cp_async_wait<ST - 1>();          // the query group (the oldest) has landed
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+  {
+    const __nv_bfloat16* tQ = sQ + warp * 16 * LD;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+      ldmatrix_x4(qf[kk], smem_u32(tQ + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8));
+  }
 
   for (int ch = 0; ch < n_chunks; ++ch) {
-    const int st = ch & 1;
-    if (ch + 1 < n_chunks) {
-      issue(ch + 1, st ^ 1);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    const int st = ch % ST;
+    // chunk ch + ST - 1 goes into the stage that chunk ch - 1 has just left (all warps passed the
+    // barrier at the end of the previous iteration)
+    if (ch + ST - 1 < n_chunks) issue(ch + ST - 1, (ch + ST - 1) % ST);
+    cp_async_commit();
+    cp_async_wait<ST - 1>();        // chunk ch is complete; the ST - 1 younger groups may still fly
     __syncthreads();
     float s[CH / 8][4];
 #pragma unroll
@@ -356,29 +393,29 @@ __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodePa
       for (int j = 0; j < 4; ++j) s[nt][j] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
-      uint32_t a[4];
-      ldmatrix_x4(a, smem_u32(tQ + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8));
 #pragma unroll
       for (int kt = 0; kt < CH / 16; ++kt) {
         uint32_t bfr[4];
         const __nv_bfloat16* tK = sK + (st * CH + kt * 16) * LD;
         ldmatrix_x4(bfr, smem_u32(tK + ((lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8));
-        mma_16816(s[2 * kt], a, bfr[0], bfr[1]);
-        mma_16816(s[2 * kt + 1], a, bfr[2], bfr[3]);
+        mma_16816(s[2 * kt], qf[kk], bfr[0], bfr[1]);
+        mma_16816(s[2 * kt + 1], qf[kk], bfr[2], bfr[3]);
       }
     }
     const int key0 = kbeg + ch * CH;
+    const bool ragged = key0 + CH > kend;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < CH / 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int key = key0 + nt * 8 + fcol + (j & 1);
-        const float v = (key < kend) ? s[nt][j] * p.scale_log2 : -INFINITY;
+        float v = s[nt][j] * p.scale_log2;
+        if (ragged && key0 + nt * 8 + fcol + (j & 1) >= kend) v = -INFINITY;
         s[nt][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
       }
     float corr[2], m_use[2];
+    bool moved = false;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -386,6 +423,7 @@ __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodePa
       const float m_new = fmaxf(m_run[r], mx[r]);
       m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
       corr[r] = exp2f(m_run[r] - m_use[r]);
+      moved = moved || (m_new != m_run[r]);
       m_run[r] = m_new;
     }
     float rs[2] = {0.f, 0.f};
@@ -399,12 +437,14 @@ __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodePa
       }
 #pragma unroll
     for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + rs[r];
+    if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt) {
-      o_acc[dt][0] *= corr[0];
-      o_acc[dt][1] *= corr[0];
-      o_acc[dt][2] *= corr[1];
-      o_acc[dt][3] *= corr[1];
+      for (int dt = 0; dt < D / 8; ++dt) {
+        o_acc[dt][0] *= corr[0];
+        o_acc[dt][1] *= corr[0];
+        o_acc[dt][2] *= corr[1];
+        o_acc[dt][3] *= corr[1];
+      }
     }
 #pragma unroll
     for (int kt = 0; kt < CH / 16; ++kt) {
@@ -440,10 +480,8 @@ __global__ void __launch_bounds__(128) paged_decode_prefix_kernel(const DecodePa
     const int h = hk * rep + row % rep;
     const long long pi = ((long long)b * p.nh + h) * p.slot_total + sp;
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt) {
-      p.part_o[pi * D + dt * 8 + fcol] = o_acc[dt][2 * r];
-      p.part_o[pi * D + dt * 8 + fcol + 1] = o_acc[dt][2 * r + 1];
-    }
+    for (int dt = 0; dt < D / 8; ++dt)
+      *reinterpret_cast<float2*>(p.part_o + pi * D + dt * 8 + fcol) = make_float2(o_acc[dt][2 * r], o_acc[dt][2 * r + 1]);
     if ((lane & 3) == 0) {
       p.part_ml[pi * 2] = m_run[r];
       p.part_ml[pi * 2 + 1] = l_run[r];
@@ -848,6 +886,10 @@ static int launch_paged_decode(const void* q, const long long* q_layout4, const 
   p.part_ml = part_ml;
   p.max_blocks = max_blocks;
   p.block_size = block_size;
+  p.block_shift = -1;
+  if (block_size > 0 && (block_size & (block_size - 1)) == 0)
+    for (int sft = 0; sft < 31; ++sft)
+      if ((1 << sft) == block_size) p.block_shift = sft;
   p.nh = nh;
   p.nkv = nkv;
   p.nsplit = nsplit;
@@ -859,7 +901,7 @@ static int launch_paged_decode(const void* q, const long long* q_layout4, const 
   dim3 grid(B, nkv, nsplit);
   cudaError_t e;
   if (grouped) {
-    const size_t psmem = (size_t)(64 + 4 * kPrefixChunk) * LD * sizeof(__nv_bfloat16);
+    const size_t psmem = (size_t)(64 + 2 * kPrefixStages * kPrefixChunk) * LD * sizeof(__nv_bfloat16);
     dim3 pgrid(n_groups, nkv, npre);
     if (D == 128) {
       e = cudaFuncSetAttribute(paged_decode_prefix_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);

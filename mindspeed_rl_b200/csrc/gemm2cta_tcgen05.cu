@@ -44,7 +44,7 @@ constexpr uint32_t TMEM_COLS = 512;               // two 128 x 256 fp32 accumula
 constexpr int EPI_PITCH = 144;
 constexpr uint32_t EPI_BYTES = 4 * 32 * EPI_PITCH;
 enum { ERR_FULL = 31, ERR_EMPTY = 32, ERR_ACC = 33 };
-enum OutMode { OUT_BF16 = 0, OUT_ACC_F32 = 1, OUT_ACC_BF16 = 2 };
+enum OutMode { OUT_BF16 = 0, OUT_ACC_F32 = 1, OUT_ACC_BF16 = 2, OUT_PART_F32 = 3 };
 enum CommMode { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
 enum { ERR_GATHER = 34, ERR_PEERS = 35 };
 constexpr int MAX_RANKS = 16;
@@ -58,6 +58,8 @@ struct Params {
   long long ldc;
   const __nv_bfloat16* bias;   // OUT_BF16 only, may be null
   int* error;
+  int k_splits;                // OUT_PART_F32: pieces the reduction is cut into (one work item per tile and piece;
+                               // piece s writes its fp32 partial tile into slab s of C, [k_splits, M, ldc])
   int flags;                   // experiment switches (MSRL_G2_FLAGS): 1 fence per stage, 4 no stores, bits 4-7 ring depth
   // communication-fused variants (tensor-parallel linears under sequence parallelism)
   int rank, world;
@@ -186,12 +188,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();            // 0: leader (issues the MMAs), 1: its partner
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
+  const int total_tiles = m_tiles * n_tiles * ((OUT == OUT_PART_F32) ? p.k_splits : 1);
   const int num_kb = (p.K + BK - 1) / BK;
+  // split reduction (small-M, weight-streaming problems): work item = (tile, piece of K)
+  const int k_splits = (OUT == OUT_PART_F32) ? p.k_splits : 1;
+  const int kb_per = (num_kb + k_splits - 1) / k_splits;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int mt_local = (COMM == COMM_NONE) ? m_tiles : p.m_local / BM;       // row tiles of one rank's block
   const int units_local = (COMM == COMM_NONE) ? 0 : p.m_local / HM;          // 128-row units of one rank's block
   auto coords = [&](int tile, int& mt, int& nt) {
+    if (OUT == OUT_PART_F32) tile /= k_splits;
     if (COMM == COMM_AG) tile_coords_ag(tile, n_tiles, p.rank, p.world, mt_local, mt, nt);
     else if (COMM == COMM_RS) tile_coords_rs(tile, n_tiles, p.rank, p.world, mt_local, mt, nt);
     else tile_coords(tile, m_tiles, n_tiles, mt, nt);
@@ -245,7 +251,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             asm volatile("fence.proxy.async;\n" ::: "memory");   // generic-proxy stores -> TMA reads
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (OUT == OUT_PART_F32) ? (tile % k_splits) * kb_per : 0;
+        const int kb1 = (OUT == OUT_PART_F32) ? ((kb0 + kb_per < num_kb) ? kb0 + kb_per : num_kb) : num_kb;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % RS;
           const uint32_t use = it / RS;
           if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, p.error, ERR_EMPTY)) {
@@ -293,7 +301,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           fence_after();
         }
         const uint32_t tmem_acc = tmem + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (OUT == OUT_PART_F32) ? (tile % k_splits) * kb_per : 0;
+        const int kb1 = (OUT == OUT_PART_F32) ? ((kb0 + kb_per < num_kb) ? kb0 + kb_per : num_kb) : num_kb;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % RS;
           ok = mbar_wait(&full_bar[s], (it / RS) & 1, p.error, ERR_FULL);
           if (!ok) break;
@@ -303,7 +313,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint64_t so = (uint64_t)((uint32_t)s * (STAGE_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            umma_pair(tmem_acc, da0 + so + k * KA, db0 + so + k * KB_, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_pair(tmem_acc, da0 + so + k * KA, db0 + so + k * KB_, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           commit_pair(&empty_bar[s]);     // the slot is free in both CTAs once these MMAs have read it
         }
         commit_pair(&acc_full[buf]);      // accumulator complete (or abandoned) for both epilogues
@@ -389,7 +399,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // that the read-modify-write of C moves whole 128-byte (fp32) / 64-byte (bf16) row segments per
         // group of lanes instead of one 16-byte piece per lane and row.  32 columns per step, fp32 staging.
         const long long crow0 = m0 + warp * 32;
-        const bool f32 = (OUT == OUT_ACC_F32);
+        const bool f32 = (OUT == OUT_ACC_F32 || OUT == OUT_PART_F32);
+        // split reduction: this piece's slab of the partial-sum buffer; an empty piece (more pieces than
+        // k-blocks) was never multiplied and stores zeros
+        float* const Cf = reinterpret_cast<float*>(p.C) +
+                          ((OUT == OUT_PART_F32) ? (long long)(tile % k_splits) * p.M * p.ldc : 0);
+        const bool empty_piece = (OUT == OUT_PART_F32) && (tile % k_splits) * kb_per >= num_kb;
         const bool vec_ok = f32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                 : ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
 #pragma unroll 1
@@ -398,23 +413,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (col0 >= p.N) break;
           float v[32];
           tmem_ld32(t_row + c * 32, v);
+          if (empty_piece) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
 #pragma unroll
           for (int q = 0; q < 8; ++q)
             *reinterpret_cast<float4*>(patch + lane * EPI_PITCH + q * 16) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
           __syncwarp();
           if (vec_ok && col0 + 32 <= p.N) {
             if (f32) {
-              float* C = reinterpret_cast<float*>(p.C);
+              float* C = Cf;
               const int cc = (lane & 7) * 4;                    // 8 lanes x 16 B = one 128-byte row segment
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int r = i * 4 + (lane >> 3);
                 if (crow0 + r < p.M) {
                   float* dst = C + (crow0 + r) * p.ldc + col0 + cc;
-                  float4 o = *reinterpret_cast<const float4*>(dst);
                   const float4 a = *reinterpret_cast<const float4*>(patch + r * EPI_PITCH + cc * 4);
-                  o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
-                  *reinterpret_cast<float4*>(dst) = o;
+                  if (OUT == OUT_PART_F32) {
+                    *reinterpret_cast<float4*>(dst) = a;
+                  } else {
+                    float4 o = *reinterpret_cast<const float4*>(dst);
+                    o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
+                    *reinterpret_cast<float4*>(dst) = o;
+                  }
                 }
               }
             } else {
@@ -438,8 +461,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           } else if (row < p.M) {
             const float* src = reinterpret_cast<const float*>(patch + lane * EPI_PITCH);
             if (f32) {
-              float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
-              for (int jj = 0; jj < 32 && col0 + jj < p.N; ++jj) dst[jj] += src[jj];
+              float* dst = Cf + (long long)row * p.ldc + col0;
+              for (int jj = 0; jj < 32 && col0 + jj < p.N; ++jj) dst[jj] = (OUT == OUT_PART_F32) ? src[jj] : dst[jj] + src[jj];
             } else {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
               for (int jj = 0; jj < 32 && col0 + jj < p.N; ++jj) dst[jj] = __float2bfloat16(__bfloat162float(dst[jj]) + src[jj]);
@@ -614,12 +637,41 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2;
     max_clusters = n < sm_count() / 2 ? n : sm_count() / 2;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (OUT == OUT_PART_F32 ? p.k_splits : 1);
   // the fused variants always launch every pair: their comm warps share the copy / reduce work of the
   // whole grid, and every CTA must be resident for the counters to advance
   const int clusters = (COMM != COMM_NONE || tiles >= max_clusters) ? max_clusters : tiles;
   cfg.gridDim = dim3(2 * clusters, 1, 1);
   return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, ml, p);
+}
+
+// Sum of the split-reduction slabs: out[M, N] bf16 = sum_s part[s][M, N] (+ bias[N]), slabs added in
+// index order so that the result does not depend on which pair produced which piece.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, long long slab, int splits,
+                                                             __nv_bfloat16* __restrict__ out, long long ldo,
+                                                             const __nv_bfloat16* __restrict__ bias, int M, int N) {
+  const int vec_per_row = N / 8;
+  const long long total = (long long)M * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row), c = (int)(i % vec_per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    const float* src = part + (long long)r * N + c;
+    for (int sidx = 0; sidx < splits; ++sidx) {
+      const float4 a = *reinterpret_cast<const float4*>(src + sidx * slab);
+      const float4 b = *reinterpret_cast<const float4*>(src + sidx * slab + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    if (bias != nullptr) {
+      float f[8];
+      unpack8(ld8(bias + c), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    st8(out + (long long)r * ldo + c, pack8(acc));
+  }
 }
 
 }  // namespace g2
@@ -653,6 +705,55 @@ MSRL_API int msrl_gemm_pair_bf16(const void* A, long long lda, int a_mn, const v
   if (a_mn && b_mn && out_mode == g2::OUT_ACC_F32) return g2::launch<true, true, g2::OUT_ACC_F32>(A, lda, B, ldb, p, st);
   if (a_mn && b_mn && out_mode == g2::OUT_ACC_BF16) return g2::launch<true, true, g2::OUT_ACC_BF16>(A, lda, B, ldb, p, st);
   return (int)cudaErrorInvalidValue;
+}
+
+// Split-reduction form for small M (decode): the reduction is cut into `splits` pieces so that
+// tiles x pieces fills the machine, every piece writes an fp32 partial tile into `part`
+// ([splits, M, N] floats), and a second kernel adds the slabs in order into C (bf16, + optional bias).
+// A [M, K] and B [N, K] row-major; N a multiple of 8.  msrl_gemm_pair_splitk_plan suggests `splits`
+// (0: the plain kernel or the library is the better choice).
+MSRL_API int msrl_gemm_pair_splitk_plan(int M, int N, int K) {
+  const int tiles = ((M + g2::BM - 1) / g2::BM) * ((N + g2::BN - 1) / g2::BN);
+  const int pairs = sm_count() / 2;
+  const int num_kb = (K + g2::BK - 1) / g2::BK;
+  if (tiles == 0 || N % 8 != 0 || K % 8 != 0) return 0;
+  int splits = pairs / tiles;
+  if (splits > num_kb / 8) splits = num_kb / 8;                   // at least 8 k-blocks per piece
+  // the partial sums are written and read back once: keep them under about a third of the weight bytes
+  const long long cap = (long long)(0.35 * K) / (4LL * (M < 1 ? 1 : M));
+  if (splits > cap) splits = (int)cap;
+  if (splits > 16) splits = 16;
+  if (splits < 2) return 0;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  return (num_kb + kb_per - 1) / kb_per;                          // no empty piece
+}
+
+MSRL_API int msrl_gemm_pair_splitk_bf16(const void* A, long long lda, const void* B, long long ldb, float* part,
+                                        void* C, long long ldc, const void* bias, int M, int N, int K, int splits,
+                                        int* error, cudaStream_t st) {
+  if (M == 0 || N == 0) return 0;
+  if (K <= 0 || K % 8 != 0 || N % 8 != 0 || ldc % 8 != 0 || splits < 1 || splits > 64 ||
+      (reinterpret_cast<uintptr_t>(part) & 15) != 0 || (reinterpret_cast<uintptr_t>(C) & 15) != 0)
+    return (int)cudaErrorInvalidValue;
+  {   // no piece may be empty: the pipeline hands an accumulator over only after at least one MMA
+    const int num_kb = (K + g2::BK - 1) / g2::BK;
+    const int kb_per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + kb_per - 1) / kb_per;
+  }
+  g2::Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = part;
+  p.ldc = N;
+  p.k_splits = splits;
+  p.error = error;
+  int rc = g2::launch<false, false, g2::OUT_PART_F32>(A, lda, B, ldb, p, st);
+  if (rc != 0) return rc;
+  const long long vecs = (long long)M * (N / 8);
+  long long blocks = (vecs + 255) / 256;
+  if (blocks > 4LL * sm_count()) blocks = 4LL * sm_count();
+  g2::splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, st>>>(part, (long long)M * N, splits, (__nv_bfloat16*)C, ldc,
+                                                              (const __nv_bfloat16*)bias, M, N);
+  return (int)cudaGetLastError();
 }
 
 // ---- communication-fused forms on CTA pairs (same contracts as msrl_ag_gemm_bf16_tn / msrl_gemm_rs_bf16_tn,

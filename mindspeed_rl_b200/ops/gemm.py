@@ -109,18 +109,47 @@ def pair_enabled() -> bool:
 def _pair_pays(m: int, n: int) -> bool:
     """The pair kernel works on 256 x 256 output tiles, one pair of SMs each: below a few dozen
     tiles (decode-sized problems) most of the machine would idle, so those go to the library."""
-    return pair_enabled() and ((m + 255) // 256) * ((n + 255) // 256) >= 48
+    return pair_enabled() and m > 128 and ((m + 255) // 256) * ((n + 255) // 256) >= 48
+
+
+def gemm_pair_splitk(x: torch.Tensor, w: torch.Tensor, splits: int, bias: Optional[torch.Tensor] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [M, K] @ w [N, K].T (+ bias)`` for small ``M`` (decode steps) on the CTA-pair kernel with the
+    reduction cut into ``splits`` pieces: tiles x pieces fills the machine although ``M x N`` alone is a
+    handful of tiles, each piece streams its part of the weight once, and a second kernel adds the
+    fp32 partial tiles in a fixed order."""
+    m, k = x.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty(m, n, device=x.device, dtype=torch.bfloat16)
+    part = torch.empty(splits * m * n, device=x.device, dtype=torch.float32)
+    check(_lib.load().msrl_gemm_pair_splitk_bf16(
+        ptr(x), c_ll(x.stride(0)), ptr(w), c_ll(w.stride(0)), ptr(part), ptr(out), c_ll(out.stride(0)), ptr(bias),
+        c_int(m), c_int(n), c_int(k), c_int(splits), ptr(_status_word(x.device)), stream()), "gemm_pair_splitk_bf16")
+    return out
+
+
+def splitk_plan(m: int, n: int, k: int) -> int:
+    """Pieces to cut the reduction of a small-``M`` GEMM into (0: do not split)."""
+    if not pair_enabled() or os.environ.get("MSRL_SPLITK_GEMM", "1") != "1":
+        return 0
+    return int(_lib.load().msrl_gemm_pair_splitk_plan(c_int(m), c_int(n), c_int(k)))
 
 
 def linear_fwd(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x [T, K] @ w [N, K].T (+ bias)``: the forward of every dense linear."""
-    if (x.is_cuda and _pair_pays(x.shape[0], w.shape[0]) and pair_usable(x, w) and _lib.use_kernels(x, w)
-            and (bias is None or bias.dtype == torch.bfloat16)):
-        return gemm_pair(x, w, bias=bias)
-    y = torch.matmul(x, w.t())
+    if (x.is_cuda and pair_usable(x, w) and _lib.use_kernels(x, w)
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.data_ptr() % 16 == 0))):
+        m, n, k = x.shape[0], w.shape[0], x.shape[1]
+        if _pair_pays(m, n):
+            return gemm_pair(x, w, bias=bias)
+        if 128 < m <= 256:
+            splits = splitk_plan(m, n, k)
+            if splits >= 2:
+                return gemm_pair_splitk(x, w, splits, bias=bias)
     if bias is not None:
-        y += bias
-    return y
+        return torch.addmm(bias, x, w.t())
+    return torch.matmul(x, w.t())
 
 
 def linear_dgrad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

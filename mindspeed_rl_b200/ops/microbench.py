@@ -142,6 +142,27 @@ def case_gemm_pair_ksweep(small: bool, iters: int):
     G.check_status("cuda")
 
 
+def case_gemm_decode(small: bool, iters: int):
+    """The four weight GEMMs of a decode step (256 tokens against the 7B layer weights): weight bytes
+    streamed per second on the CTA-pair kernel and on the library call."""
+    m = 256
+    layers = [("qkv", 4608, 3584), ("proj", 3584, 3584), ("gate_up", 37888, 3584), ("down", 3584, 18944)]
+    if small:
+        layers = [("small", 4096, 1024)]
+    for name, n, k in layers:
+        x = torch.randn(m, k, device="cuda").bfloat16()
+        w = (0.02 * torch.randn(n, k, device="cuda")).bfloat16()
+        y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        by = 2.0 * n * k
+        report(f"pair   decode {name} M={m}", timeit(lambda: G.gemm_pair(x, w, out=y), iters), bytes_=by)
+        report(f"cublas decode {name} M={m}", timeit(lambda: torch.matmul(x, w.t(), out=y), iters), bytes_=by)
+        plan = G.splitk_plan(m, n, k)
+        for splits in sorted({plan, 4} - {0}):
+            report(f"pair split-K x{splits} decode {name} M={m}" + (" (planned)" if splits == plan else ""),
+                   timeit(lambda: G.gemm_pair_splitk(x, w, splits, out=y), iters), bytes_=by)
+    G.check_status("cuda")
+
+
 def case_fused_single(small: bool, iters: int):
     """Communication-fused GEMM variants with a team of one rank: the comm warps copy / reduce
     through local memory only, which isolates their cost from the NVLink transfer."""
@@ -233,6 +254,36 @@ def case_decode(small: bool, iters: int):
            note=f"unique K/V bytes; {ms_plain / ms:.2f}x faster than the plain kernel on the same cache")
 
 
+def case_decode_prefix(small: bool, iters: int):
+    """Shared-prefix decode with short own suffixes, so that the prefix pass dominates: sweep of the
+    number of prefix splits per (group, KV head)."""
+    from .decode import build_decode_groups, decode_group_max
+
+    nh, nkv, hd, bs = 28, 4, 128, 16
+    lay = QKVLayout(nh, nkv, hd, True)
+    b, n, prompt = (256, 8, 1024) if not small else (64, 8, 1024)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    q = torch.randn(b, lay.width, device="cuda").bfloat16()
+    for own in (16, 512):
+        ctx = prompt + own
+        per = (ctx + bs - 1) // bs
+        nblk = b * per
+        kc = torch.randn(nblk, bs, nkv, hd, device="cuda").bfloat16()
+        vc = torch.randn(nblk, bs, nkv, hd, device="cuda").bfloat16()
+        bt = torch.randperm(nblk, device="cuda").to(torch.int32).view(b, per)
+        shared = prompt // bs
+        for g in range(b // n):
+            bt[g * n:(g + 1) * n, :shared] = bt[g * n, :shared].clone()
+        cl = torch.full((b,), ctx, dtype=torch.int32, device="cuda")
+        ks, rows, pre, _ = build_decode_groups([i // n for i in range(b)], [prompt] * b, decode_group_max(nh, nkv))
+        groups = (i32(ks), i32(rows), i32(pre))
+        unique = 2.0 * (b // n * prompt + b * own) * nkv * hd * 2
+        for splits in (1, 2, 4, 8):
+            ms = timeit(lambda: paged_decode_attention(q, lay, kc, vc, bt, cl, ctx, groups=groups,
+                                                       prefix_splits=splits), iters)
+            report(f"paged_decode grouped B={b} prompt={prompt} own={own} prefix_splits={splits}", ms, bytes_=unique)
+
+
 def case_elementwise(small: bool, iters: int):
     rows, h, f = (16384, 3584, 18944) if not small else (4096, 3584, 4096)
     x = torch.randn(rows, h, device="cuda").bfloat16()
@@ -308,7 +359,7 @@ def case_moe(small: bool, iters: int):
     G.check_status("cuda", "grouped gemm")
 
 
-CASES = {"moe": case_moe, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_pair_prof": case_gemm_pair_prof, "gemm_pair_ksweep": case_gemm_pair_ksweep, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode,
+CASES = {"moe": case_moe, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_pair_prof": case_gemm_pair_prof, "gemm_pair_ksweep": case_gemm_pair_ksweep, "gemm_decode": case_gemm_decode, "lmhead": case_lmhead, "attention": case_attention, "decode": case_decode, "decode_prefix": case_decode_prefix,
          "elementwise": case_elementwise, "adam": case_adam, "sampler": case_sampler,
          "fused_single": case_fused_single}
 

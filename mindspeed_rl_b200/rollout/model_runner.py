@@ -19,6 +19,7 @@ import torch
 from .. import ops
 from ..models.transformer_config import TransformerConfig
 from ..ops import QKVLayout
+from ..ops.gemm import linear_fwd
 from ..parallel.tp_comm import NO_TP, TPComm
 
 
@@ -128,23 +129,20 @@ class ModelRunner:
             # latent attention: full per-head q / k / v (rotary and soft-max scale already applied)
             qkv = lw.mla.rollout_qkv(x, positions)
         else:
-            if lw.qkv_b is not None:
-                qkv = torch.addmm(lw.qkv_b, x, lw.qkv_w.t())
-            else:
-                qkv = torch.matmul(x, lw.qkv_w.t())
+            qkv = linear_fwd(x, lw.qkv_w, lw.qkv_b)
             if lw.q_norm is not None:
                 ops.headnorm_fwd_(qkv, lay, "q", lw.q_norm, cfg.norm_epsilon)
                 ops.headnorm_fwd_(qkv, lay, "k", lw.k_norm, cfg.norm_epsilon)
             ops.rope_(qkv, lay, positions, self.rope_table() if rope_tab is None else rope_tab)
         attn = attend(li, qkv, lay)
-        delta = self.comm.all_reduce(torch.matmul(attn, lw.o_w.t()))
+        delta = self.comm.all_reduce(linear_fwd(attn, lw.o_w))
         x, _, resid = ops.rmsnorm_fwd(delta, lw.post_norm, cfg.norm_epsilon, residual=resid,
                                       want_rstd=False)
         if lw.moe is not None:
             delta = lw.moe.forward(x, self.comm)
         else:
-            y = ops.swiglu_fwd(torch.matmul(x, lw.gate_up_w.t()))
-            delta = self.comm.all_reduce(torch.matmul(y, lw.down_w.t()))
+            y = ops.swiglu_fwd(linear_fwd(x, lw.gate_up_w))
+            delta = self.comm.all_reduce(linear_fwd(y, lw.down_w))
         return resid, delta
 
     @torch.no_grad()
@@ -175,7 +173,7 @@ class ModelRunner:
         return x
 
     def _logits(self, x: torch.Tensor) -> torch.Tensor:
-        return torch.matmul(x, self.weights.lm_head.t())
+        return linear_fwd(x, self.weights.lm_head)
 
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()

@@ -163,7 +163,8 @@ def test_paged_decode_and_cache(nh, nkv, hd, bs):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,bs,n_samples,prompt", [(28, 4, 128, 16, 8, 200), (8, 2, 64, 16, 5, 70),
-                                                           (16, 16, 128, 32, 8, 33)])
+                                                           (16, 16, 128, 32, 8, 33), (28, 4, 128, 16, 8, 1100),
+                                                           (8, 2, 64, 24, 5, 100)])
 def test_paged_decode_shared_prefix(nh, nkv, hd, bs, n_samples, prompt):
     """Groups of samples share their prompt blocks; the grouped kernels (prefix read once per
     group + per-sample suffix + merge) must equal the plain per-sequence path."""

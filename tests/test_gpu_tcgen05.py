@@ -44,6 +44,35 @@ def test_gemm_pair_forward_and_bias(m, n, k):
     G.check_status(DEV)
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(256, 512, 2048, 4), (200, 1000, 4096, 5), (256, 3584, 18944, 5),
+                                          (130, 264, 1536, 3), (64, 256, 640, 16)])
+def test_gemm_pair_split_reduction(m, n, k, splits):
+    """Small-M form: the reduction cut into pieces (including pieces of unequal length and more pieces
+    asked for than the planner would give), partial tiles added in a fixed order, optional bias."""
+    torch.manual_seed(2)
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    b = (torch.randn(n, k, device=DEV) * 0.5).bfloat16()
+    bias = torch.randn(n, device=DEV).bfloat16()
+    ref = a.float() @ b.float().t()
+    out1 = G.gemm_pair_splitk(a, b, splits)
+    _assert_close(out1, ref, k)
+    _assert_close(G.gemm_pair_splitk(a, b, splits, bias=bias), ref + bias.float(), k)
+    assert torch.equal(out1, G.gemm_pair_splitk(a, b, splits))      # fixed summation order
+    G.check_status(DEV)
+
+
+def test_linear_fwd_routes_decode_shapes():
+    """256-token decode shapes: wide outputs on the plain pair kernel, long reductions on the split
+    form, the rest on the library; all three agree with the fp32 product."""
+    torch.manual_seed(3)
+    for n, k in [(37888 // 8, 3584), (3584, 18944), (4608, 3584)]:
+        x = (torch.randn(256, k, device=DEV) * 0.5).bfloat16()
+        w = (torch.randn(n, k, device=DEV) * 0.5).bfloat16()
+        _assert_close(G.linear_fwd(x, w), x.float() @ w.float().t(), k)
+    assert G.splitk_plan(256, 3584, 18944) >= 2 and G.splitk_plan(256, 4608, 3584) == 0
+    G.check_status(DEV)
+
+
 @pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
 def test_gemm_pair_data_and_weight_gradient_forms(m, n, k):
     """``dy @ w`` with ``w`` as an MN-major B operand, and ``dy.T @ x`` with both operands MN-major,
