@@ -855,12 +855,20 @@ MSRL_API int msrl_paged_decode_nsplit(int B, int nkv, int max_ctx) {
   return ns;
 }
 
+// tcgen05 form of the shared-prefix pass (decode_prefix_tcgen05.cu)
+extern "C" int msrl_paged_prefix_tcgen05(const void* q, const long long* q_layout4, const void* k_cache,
+                                         const void* v_cache, long long num_blocks, const int* block_tables,
+                                         int max_blocks, const int* group_rows, const int* group_prefix, int n_groups,
+                                         float* part_o, float* part_ml, int nh, int nkv, int D, int block_size,
+                                         int slot_total, int npre, int* error, cudaStream_t st);
+
 static int launch_paged_decode(const void* q, const long long* q_layout4, const void* k_cache,
                                const void* v_cache, const int* block_tables, int max_blocks,
                                const int* context_lens, void* out, long long out_stride,
                                float* part_o, float* part_ml, int B, int nh, int nkv, int D,
                                int block_size, int nsplit, const int* key_start, const int* group_rows,
-                               const int* group_prefix, int n_groups, int npre, cudaStream_t st) {
+                               const int* group_prefix, int n_groups, int npre, cudaStream_t st,
+                               long long num_blocks = 0, int prefix_tile = 0, int* error = nullptr) {
   if (B == 0) return 0;
   if (nh % nkv != 0 || nh / nkv > 16 || (D != 64 && D != 128) || nsplit < 1)
     return (int)cudaErrorInvalidValue;
@@ -900,7 +908,16 @@ static int launch_paged_decode(const void* q, const long long* q_layout4, const 
   if (merge_smem > smem) smem = merge_smem;
   dim3 grid(B, nkv, nsplit);
   cudaError_t e;
-  if (grouped) {
+  bool prefix_done = false;
+  if (grouped && prefix_tile > 0 && error != nullptr) {
+    // the caller rounded every shared prefix down to a multiple of the tensor-core kernel's key tile
+    const int rc = msrl_paged_prefix_tcgen05(q, q_layout4, k_cache, v_cache, num_blocks, block_tables, max_blocks,
+                                             group_rows, group_prefix, n_groups, part_o, part_ml, nh, nkv, D,
+                                             block_size, p.slot_total, npre, error, st);
+    if (rc == 0) prefix_done = true;
+    else if (rc != (int)cudaErrorNotSupported) return rc;
+  }
+  if (grouped && !prefix_done) {
     const size_t psmem = (size_t)(64 + 2 * kPrefixStages * kPrefixChunk) * LD * sizeof(__nv_bfloat16);
     dim3 pgrid(n_groups, nkv, npre);
     if (D == 128) {
@@ -954,18 +971,21 @@ MSRL_API int msrl_paged_decode_group_max(int nh, int nkv) {
 // group_rows [n_groups, 8] lists the members' batch rows (-1 padded, at most
 // msrl_paged_decode_group_max members); the members of a group share their first group_prefix[g]
 // keys (same tokens, hence the same K/V, read through the first member's block table);
-// key_start[b] = prefix of b's group.  Scratch: part_o B*nh*(npre+nsplit)*D floats, part_ml
+// key_start[b] = prefix of b's group.  prefix_tile > 0 states that every group_prefix is a multiple of
+// that many keys (msrl_paged_prefix_tcgen05_tile): the shared pass then runs on the tcgen05 kernel, which
+// needs the number of cache blocks and a device status word.  Scratch: part_o B*nh*(npre+nsplit)*D floats, part_ml
 // B*nh*(npre+nsplit)*2 floats.
 MSRL_API int msrl_paged_decode_grouped(const void* q, const long long* q_layout4, const void* k_cache,
                                        const void* v_cache, const int* block_tables, int max_blocks,
                                        const int* context_lens, const int* key_start, const int* group_rows,
                                        const int* group_prefix, int n_groups, void* out, long long out_stride,
                                        float* part_o, float* part_ml, int B, int nh, int nkv, int D,
-                                       int block_size, int nsplit, int npre, cudaStream_t st) {
+                                       int block_size, int nsplit, int npre, long long num_blocks,
+                                       int prefix_tile, int* error, cudaStream_t st) {
   if (n_groups < 1) return (int)cudaErrorInvalidValue;
   return launch_paged_decode(q, q_layout4, k_cache, v_cache, block_tables, max_blocks, context_lens, out,
                              out_stride, part_o, part_ml, B, nh, nkv, D, block_size, nsplit, key_start, group_rows,
-                             group_prefix, n_groups, npre, st);
+                             group_prefix, n_groups, npre, st, num_blocks, prefix_tile, error);
 }
 
 MSRL_API int msrl_sample_rec_bytes() { return (int)sizeof(SampleRec); }

@@ -9,7 +9,7 @@ from .layouts import QKVLayout
 from .elementwise import (add, colsum_accumulate, headnorm_bwd_, headnorm_fwd_, rmsnorm_bwd,
                           rmsnorm_fwd, rope_, rope_table, swiglu_bwd, swiglu_fwd)
 from .attention import attn_kv_bwd, attn_kv_fwd, attn_merge_, attn_varlen_bwd, attn_varlen_fwd
-from .decode import (build_decode_groups, decode_group_max, kv_cache_gather, kv_cache_write,
+from .decode import (build_decode_groups, decode_group_max, decode_prefix_tile, kv_cache_gather, kv_cache_write,
                      paged_decode_attention, sample)
 from .rl import (gae, group_norm_advantage, loss_weights, policy_loss_fwd_bwd,
                  policy_loss_reference, value_loss_fwd_bwd, value_loss_reference)

@@ -16,6 +16,7 @@ import torch
 from . import _lib
 from ._lib import c_float, c_int, c_ll, c_ull, check, ptr, stream
 from .elementwise import _workspace
+from .gemm import _status_word
 from .layouts import QKVLayout
 
 
@@ -65,20 +66,33 @@ def kv_cache_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: 
     return k_cache.view(-1, nkv, hd)[slot], v_cache.view(-1, nkv, hd)[slot]
 
 
-def decode_group_max(num_heads: int, num_kv_heads: int) -> int:
-    """Largest group the shared-prefix decode kernel serves with one CTA (members x query heads
-    per KV head must fit 64 rows)."""
-    return max(1, min(8, 64 // max(num_heads // num_kv_heads, 1)))
+def decode_prefix_tile(num_heads: int, num_kv_heads: int, head_dim: int, block_size: int) -> int:
+    """Key tile of the tcgen05 shared-prefix kernel for this shape, or 0 when the shape is served by
+    the ``mma.sync`` kernel (other head sizes, block sizes that do not divide the tile, no GPU library,
+    ``MSRL_PREFIX_TCGEN05=0``).  With a non-zero tile the groups' shared prefix must be rounded down to
+    a multiple of it (``build_decode_groups(..., multiple=tile)``)."""
+    if os.environ.get("MSRL_PREFIX_TCGEN05", "1") != "1" or not torch.cuda.is_available() or not _lib.available():
+        return 0
+    return int(_lib.load().msrl_paged_prefix_tcgen05_tile(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+                                                          c_int(block_size)))
 
 
-def build_decode_groups(group_ids: Sequence, prefix_lens: Sequence[int], group_max: int):
+def decode_group_max(num_heads: int, num_kv_heads: int, prefix_tile: int = 0) -> int:
+    """Largest group the shared-prefix decode kernel serves with one CTA: members x query heads per
+    KV head must fit the kernel's query rows (128 on the tcgen05 kernel, 64 on the ``mma.sync`` one)."""
+    rows = 128 if prefix_tile else 64
+    return max(1, min(8, rows // max(num_heads // num_kv_heads, 1)))
+
+
+def build_decode_groups(group_ids: Sequence, prefix_lens: Sequence[int], group_max: int, multiple: int = 1):
     """Host-side grouping for the shared-prefix decode path.
 
     ``group_ids[i]`` identifies the prompt of batch row ``i`` and ``prefix_lens[i]`` the number of
     leading tokens it shares with the other rows of that prompt.  Returns
     ``(key_start [B], group_rows [B][8], group_prefix [B], any_shared)`` as python lists padded to
     ``B`` groups (unused groups have first member -1), so the arrays have a fixed shape per batch
-    size (CUDA-graph friendly).
+    size (CUDA-graph friendly); groups with members come first.  ``multiple`` rounds every shared prefix
+    down to a multiple of that many keys (the remainder is then read per sequence).
     """
     b = len(group_ids)
     by_id = {}
@@ -91,6 +105,7 @@ def build_decode_groups(group_ids: Sequence, prefix_lens: Sequence[int], group_m
         for s in range(0, len(members), group_max):
             chunk = members[s:s + group_max]
             prefix = min(prefix_lens[i] for i in chunk) if len(chunk) > 1 else 0
+            prefix = prefix // multiple * multiple
             shared = shared or prefix > 0
             for i in chunk:
                 key_start[i] = prefix
@@ -102,15 +117,14 @@ def build_decode_groups(group_ids: Sequence, prefix_lens: Sequence[int], group_m
     return key_start, rows_out, prefix_out, shared
 
 
-def _prefix_splits(batch: int, nkv: int, device) -> int:
+def _prefix_splits(n_groups: int, nkv: int, device, per_sm: int) -> int:
     """Splits of the shared prompt per (group, KV head): as many as fill one wave of the prefix kernel
-    (four CTAs per SM) with groups of about eight members; ``MSRL_PREFIX_SPLITS`` overrides."""
+    (``per_sm`` CTAs per SM); ``MSRL_PREFIX_SPLITS`` overrides."""
     env = os.environ.get("MSRL_PREFIX_SPLITS")
     if env:
         return max(1, min(8, int(env)))
-    slots = 4 * torch.cuda.get_device_properties(device).multi_processor_count
-    ctas = max(1, (batch + 7) // 8) * nkv
-    return max(1, min(8, slots // ctas))
+    slots = per_sm * torch.cuda.get_device_properties(device).multi_processor_count
+    return max(1, min(8, slots // max(1, n_groups * nkv)))
 
 
 def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.Tensor,
@@ -118,13 +132,16 @@ def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.
                            context_lens: torch.Tensor, max_context: int,
                            out: Optional[torch.Tensor] = None,
                            groups: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
-                           prefix_splits: Optional[int] = None) -> torch.Tensor:
+                           prefix_splits: Optional[int] = None, prefix_tile: int = 0) -> torch.Tensor:
     """One query token per sequence against its paged KV (which already holds that token).
 
     ``groups = (key_start [B], group_rows [G, 8], group_prefix [G])`` (int32, device) enables the
     shared-prefix path: the members of a group (the n samples of one prompt) have identical
     first ``group_prefix`` tokens, whose K/V is then read once per group instead of once per
-    member.  Every row must belong to exactly one group; the result is the same either way.
+    member.  Every row must belong to exactly one group; the result is the same either way.  The group
+    tables may list fewer groups than rows (the launch covers ``group_rows.shape[0]`` groups).
+    ``prefix_tile`` (``decode_prefix_tile``) states that every ``group_prefix`` is a multiple of that many
+    keys and sends the shared pass to the tcgen05 kernel.
     """
     b = qkv.shape[0]
     nh, nkv, hd = layout.num_heads, layout.num_kv_heads, layout.head_dim
@@ -137,7 +154,8 @@ def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.
         if groups is not None:
             key_start, group_rows, group_prefix = groups
             if prefix_splits is None:
-                prefix_splits = _prefix_splits(b, nkv, qkv.device)
+                # tcgen05 kernel: two CTAs per SM; mma.sync kernel: three
+                prefix_splits = _prefix_splits(group_rows.shape[0], nkv, qkv.device, 2 if prefix_tile else 3)
             slots = nsplit + prefix_splits
             part_o = _workspace("decode_part_o", b * nh * slots * hd, qkv.device)
             part_ml = _workspace("decode_part_ml", b * nh * slots * 2, qkv.device)
@@ -147,6 +165,7 @@ def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.
                 c_int(block_tables.shape[1]), ptr(context_lens), ptr(key_start), ptr(group_rows),
                 ptr(group_prefix), c_int(group_rows.shape[0]), ptr(out), c_ll(nh * hd), ptr(part_o), ptr(part_ml),
                 c_int(b), c_int(nh), c_int(nkv), c_int(hd), c_int(bs), c_int(nsplit), c_int(prefix_splits),
+                c_ll(k_cache.shape[0]), c_int(prefix_tile), ptr(_status_word(qkv.device)),
                 stream()), "paged_decode_grouped")
             return out
         part_o = _workspace("decode_part_o", b * nh * nsplit * hd, qkv.device)

@@ -242,14 +242,19 @@ def case_decode(small: bool, iters: int):
     bt2 = bt.clone()
     for g in range(b // n):
         bt2[g * n:(g + 1) * n, :shared] = bt[g * n, :shared]
-    ks, rows, pre, _ = build_decode_groups([i // n for i in range(b)], [prompt] * b, decode_group_max(nh, nkv))
+    from .decode import decode_prefix_tile
+
+    tile = decode_prefix_tile(nh, nkv, hd, bs)
+    ks, rows, pre, _ = build_decode_groups([i // n for i in range(b)], [prompt] * b, decode_group_max(nh, nkv, tile),
+                                           multiple=max(1, tile))
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
-    groups = (i32(ks), i32(rows), i32(pre))
+    real = sum(1 for r in rows if r[0] >= 0)
+    groups = (i32(ks), i32(rows[:real]), i32(pre[:real]))
     unique_bytes = 2.0 * (b // n * prompt + b * (ctx - prompt)) * nkv * hd * 2
     ms_plain = timeit(lambda: paged_decode_attention(q, lay, kc, vc, bt2, cl, ctx), iters)
     report(f"paged_decode shared-prompt layout, plain kernel B={b}", ms_plain, bytes_=2.0 * b * ctx * nkv * hd * 2,
            note="every sample re-reads the shared prompt")
-    ms = timeit(lambda: paged_decode_attention(q, lay, kc, vc, bt2, cl, ctx, groups=groups), iters)
+    ms = timeit(lambda: paged_decode_attention(q, lay, kc, vc, bt2, cl, ctx, groups=groups, prefix_tile=tile), iters)
     report(f"paged_decode shared-prefix kernels B={b} (8 x 1024 shared + 1024 own)", ms, bytes_=unique_bytes,
            note=f"unique K/V bytes; {ms_plain / ms:.2f}x faster than the plain kernel on the same cache")
 
@@ -257,7 +262,7 @@ def case_decode(small: bool, iters: int):
 def case_decode_prefix(small: bool, iters: int):
     """Shared-prefix decode with short own suffixes, so that the prefix pass dominates: sweep of the
     number of prefix splits per (group, KV head)."""
-    from .decode import build_decode_groups, decode_group_max
+    from .decode import build_decode_groups, decode_group_max, decode_prefix_tile
 
     nh, nkv, hd, bs = 28, 4, 128, 16
     lay = QKVLayout(nh, nkv, hd, True)
@@ -275,13 +280,18 @@ def case_decode_prefix(small: bool, iters: int):
         for g in range(b // n):
             bt[g * n:(g + 1) * n, :shared] = bt[g * n, :shared].clone()
         cl = torch.full((b,), ctx, dtype=torch.int32, device="cuda")
-        ks, rows, pre, _ = build_decode_groups([i // n for i in range(b)], [prompt] * b, decode_group_max(nh, nkv))
-        groups = (i32(ks), i32(rows), i32(pre))
         unique = 2.0 * (b // n * prompt + b * own) * nkv * hd * 2
-        for splits in (1, 2, 4, 8):
-            ms = timeit(lambda: paged_decode_attention(q, lay, kc, vc, bt, cl, ctx, groups=groups,
-                                                       prefix_splits=splits), iters)
-            report(f"paged_decode grouped B={b} prompt={prompt} own={own} prefix_splits={splits}", ms, bytes_=unique)
+        for tile in sorted({0, decode_prefix_tile(nh, nkv, hd, bs)}):
+            ks, rows, pre, _ = build_decode_groups([i // n for i in range(b)], [prompt] * b,
+                                                   decode_group_max(nh, nkv, tile), multiple=max(1, tile))
+            real = sum(1 for r in rows if r[0] >= 0)
+            groups = (i32(ks), i32(rows[:real]), i32(pre[:real]))
+            kind = "tcgen05" if tile else "mma.sync"
+            for splits in (1, 2, 4, 8):
+                ms = timeit(lambda: paged_decode_attention(q, lay, kc, vc, bt, cl, ctx, groups=groups,
+                                                           prefix_splits=splits, prefix_tile=tile), iters)
+                report(f"paged_decode grouped ({kind} prefix pass) B={b} prompt={prompt} own={own} "
+                       f"prefix_splits={splits}", ms, bytes_=unique)
 
 
 def case_elementwise(small: bool, iters: int):

@@ -88,7 +88,12 @@ class LLMEngine(BaseInferEngine):
         self._step_counter = 0
         self.host_time = collections.defaultdict(float)   # wall-clock seconds per host-side section
         nkv_local = max(cfg.num_query_groups // self.comm.world_size, 1)
-        self._group_max = ops.decode_group_max(cfg.num_attention_heads // self.comm.world_size, nkv_local)
+        nh_local = cfg.num_attention_heads // self.comm.world_size
+        # shared prompts are rounded down to the tensor-core prefix kernel's key tile (0: the mma.sync kernel takes any length)
+        self._prefix_tile = ops.decode_prefix_tile(nh_local, nkv_local, cfg.head_dim, block_size) \
+            if torch.device(device).type == "cuda" else 0
+        self.runner.prefix_tile = self._prefix_tile
+        self._group_max = ops.decode_group_max(nh_local, nkv_local, self._prefix_tile)
         self.shared_prefix_decode = os.environ.get("MSRL_SHARED_PREFIX_DECODE", "1") == "1"
         self.lookahead_decode = os.environ.get("MSRL_LOOKAHEAD_DECODE", "1") == "1" and lockstep_group is None
         self.stats = dict(prefill_tokens=0, decode_tokens=0, steps=0, preemptions=0, lookahead_steps=0)
@@ -381,7 +386,8 @@ class LLMEngine(BaseInferEngine):
         if self.shared_prefix_decode and dev.type == "cuda":
             # samples of one prompt share the prompt's K/V: read it once per group
             ks, grows, gpre, grouped = ops.build_decode_groups(
-                [s.request_id for s in seqs], [len(s.prompt_ids) for s in seqs], self._group_max)
+                [s.request_id for s in seqs], [len(s.prompt_ids) for s in seqs], self._group_max,
+                multiple=max(1, self._prefix_tile))
             if grouped:
                 rows += [ks, gpre] + [list(col) for col in zip(*grows)]
         t1 = time.perf_counter()
@@ -391,7 +397,8 @@ class LLMEngine(BaseInferEngine):
         bt = to_device(self.bm.block_tables([s.seq_id for s in seqs], max_blocks), torch.int32, dev)
         groups = None
         if grouped:
-            groups = (it_[5].to(torch.int32), it_[7:15].t().contiguous().to(torch.int32), it_[6].to(torch.int32))
+            groups = (it_[5].to(torch.int32), it_[7:15].t().contiguous().to(torch.int32), it_[6].to(torch.int32),
+                      sum(1 for grp in grows if grp[0] >= 0))
         ids = it_[0]
         if prev is not None:
             ids = prev["tokens"] if last == list(range(len(prev["seqs"]))) else prev["tokens"][it_[0]]

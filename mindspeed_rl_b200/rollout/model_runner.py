@@ -82,8 +82,9 @@ class ModelRunner:
         self.weights: Optional[RolloutWeights] = None
         self.cache: Optional[KVCache] = None
         self._rope = None
-        self._graphs: Dict[int, dict] = {}
+        self._graphs: Dict[tuple, dict] = {}
         self._static: Optional[dict] = None
+        self.prefix_tile = 0      # key tile of the tcgen05 shared-prefix kernel (set by the engine; 0 = mma.sync kernel)
 
     # ------------------------------------------------------------------------------------------
     def bind_weights(self, weights: Optional[RolloutWeights]) -> None:
@@ -209,7 +210,8 @@ class ModelRunner:
         def attend(li, qkv, lay):
             ops.kv_cache_write(qkv, lay, slots, cache.k[li], cache.v[li])
             return ops.paged_decode_attention(qkv, lay, cache.k[li], cache.v[li], block_tables,
-                                              context_lens, max_context, groups=groups)
+                                              context_lens, max_context, groups=groups,
+                                              prefix_tile=self.prefix_tile if groups is not None else 0)
 
         return self._logits(self._forward(ids, positions, attend))
 
@@ -235,10 +237,20 @@ class ModelRunner:
                block_tables: torch.Tensor, context_lens: torch.Tensor, max_context: int,
                groups=None) -> torch.Tensor:
         """One token per sequence -> logits ``[B, V_local]``.  ``groups`` (see
-        ``ops.paged_decode_attention``) turns on shared-prefix attention for n-sample groups."""
+        ``ops.paged_decode_attention``; an optional fourth entry gives the number of groups that have
+        members, which come first in the tables) turns on shared-prefix attention for n-sample groups.
+        Shared prefixes must be multiples of ``self.prefix_tile`` keys when that is non-zero."""
         b = ids.shape[0]
         bucket = next((s for s in self.graph_batch_sizes if s >= b), None)
+        n_groups = b
+        if groups is not None:
+            if len(groups) > 3:
+                # the shared pass launches one CTA per listed group: list a power of two that covers the real ones
+                n_groups = min(b, 1 << max(0, int(groups[3]) - 1).bit_length())
+            groups = tuple(groups[:3])
         if self.enforce_eager or bucket is None:
+            if groups is not None:
+                groups = (groups[0], groups[1][:n_groups], groups[2][:n_groups])
             return self._decode_eager(ids, positions, slots, block_tables, context_lens, max_context, groups)
         max_blocks = (self.max_model_len + self.cache.block_size - 1) // self.cache.block_size
         st = self._ensure_static(max_blocks)
@@ -256,14 +268,15 @@ class ModelRunner:
             st["group_rows"][:b].copy_(groups[1])
             st["group_rows"][b:bucket].fill_(-1)
             st["group_prefix"][:b].copy_(groups[2])
-        g = self._graphs.get((bucket, grouped))
+        n_groups = min(n_groups, bucket) if grouped else 0
+        g = self._graphs.get((bucket, grouped, n_groups))
         if g is None:
-            g = self._capture(bucket, st, grouped)
+            g = self._capture(bucket, st, grouped, n_groups)
         g["graph"].replay()
         return g["logits"][:b]
 
-    def _capture(self, bucket: int, st: dict, grouped: bool = False) -> dict:
-        groups = (st["key_start"][:bucket], st["group_rows"][:bucket], st["group_prefix"][:bucket]) if grouped else None
+    def _capture(self, bucket: int, st: dict, grouped: bool = False, n_groups: int = 0) -> dict:
+        groups = (st["key_start"][:bucket], st["group_rows"][:n_groups], st["group_prefix"][:n_groups]) if grouped else None
         args = (st["ids"][:bucket], st["positions"][:bucket], st["slots"][:bucket],
                 st["block_tables"][:bucket], st["context_lens"][:bucket], self.max_model_len, groups)
         side = torch.cuda.Stream()
@@ -275,5 +288,5 @@ class ModelRunner:
         with torch.cuda.graph(graph):
             logits = self._decode_eager(*args)
         rec = dict(graph=graph, logits=logits)
-        self._graphs[(bucket, grouped)] = rec
+        self._graphs[(bucket, grouped, n_groups)] = rec
         return rec

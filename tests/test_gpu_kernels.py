@@ -205,13 +205,26 @@ def test_paged_decode_shared_prefix(nh, nkv, hd, bs, n_samples, prompt):
     btd = bt.to(DEV)
     plain = ops.paged_decode_attention(q, lay, kc, vc, btd, ctx, max(lens))
     ids = [g for g in range(n_prompts) for _ in range(n_samples)] + ["solo"]
-    ks, rows, pre, shared_any = ops.build_decode_groups(ids, [prompt] * (b - 1) + [90], ops.decode_group_max(nh, nkv))
-    assert shared_any and sorted(r for grp in rows for r in grp if r >= 0) == list(range(b))
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    grouped = ops.paged_decode_attention(q, lay, kc, vc, btd, ctx, max(lens), groups=(i32(ks), i32(rows), i32(pre)))
-    close(grouped, plain, 1e-2, 1e-2, "shared-prefix decode")
     ref = ops.paged_decode_attention(q.cpu(), lay, kc.cpu(), vc.cpu(), bt, ctx.cpu(), max(lens))
-    close(grouped, ref, 2e-2, 2e-2, "shared-prefix decode vs reference")
+    # the mma.sync shared pass (any prefix), then the tcgen05 one where it covers the shape (prefix rounded
+    # down to its key tile, the rest read per sequence; group tables cut to the groups that have members)
+    for tile in sorted({0, ops.decode_prefix_tile(nh, nkv, hd, bs)}):
+        ks, rows, pre, shared_any = ops.build_decode_groups(ids, [prompt] * (b - 1) + [90],
+                                                            ops.decode_group_max(nh, nkv, tile), multiple=max(1, tile))
+        assert sorted(r for grp in rows for r in grp if r >= 0) == list(range(b))
+        assert shared_any == (prompt >= max(1, tile)) and all(x % max(1, tile) == 0 for x in pre)
+        real = sum(1 for grp in rows if grp[0] >= 0)
+        grouped = ops.paged_decode_attention(q, lay, kc, vc, btd, ctx, max(lens),
+                                             groups=(i32(ks), i32(rows[:real]), i32(pre[:real])), prefix_tile=tile)
+        close(grouped, plain, 1e-2, 1e-2, f"shared-prefix decode (tile {tile})")
+        close(grouped, ref, 2e-2, 2e-2, f"shared-prefix decode vs reference (tile {tile})")
+        for splits in (1, 3):
+            again = ops.paged_decode_attention(q, lay, kc, vc, btd, ctx, max(lens), prefix_splits=splits,
+                                               groups=(i32(ks), i32(rows), i32(pre)), prefix_tile=tile)
+            close(again, plain, 1e-2, 1e-2, f"shared-prefix decode (tile {tile}, {splits} splits)")
+    from mindspeed_rl_b200.ops import gemm as G
+    G.check_status(DEV, "shared-prefix decode")
 
 
 def test_lmhead_logprob_fwd_bwd():
