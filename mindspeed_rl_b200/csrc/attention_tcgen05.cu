@@ -211,7 +211,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
-      ok = mbar_wait(&s_full[sb], (j >> 1) & 1, p.error, ERR_S);
+      ok = mbar_wait_warp(&s_full[sb], (j >> 1) & 1, p.error, ERR_S);
       if (!ok) break;
       fence_after();
       const int kbase = j * BN;
@@ -282,7 +282,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       m_run = m_new;
       if (j > 0) {
         // the previous P V product must be finished before P is overwritten or O is rescaled
-        ok = mbar_wait(&pv_done, (j - 1) & 1, p.error, ERR_PV);
+        ok = mbar_wait_warp(&pv_done, (j - 1) & 1, p.error, ERR_PV);
         if (!ok) break;
         fence_after();
         if (__any_sync(0xffffffffu, corr != 1.f)) {
@@ -306,7 +306,7 @@ fa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, p.error, ERR_PV);
+    if (ok && n_tiles > 0) ok = mbar_wait_warp(&pv_done, (n_tiles - 1) & 1, p.error, ERR_PV);
     // the two partial sums of a row meet in shared memory
     l_part[wg][row] = l_run;
     asm volatile("bar.sync 1, 256;\n" ::: "memory");        // every soft-max thread reaches this once
@@ -579,7 +579,7 @@ fa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
-      ok = mbar_wait(&s_full[sb], (j >> 1) & 1, p.error, ERR_S);
+      ok = mbar_wait_warp(&s_full[sb], (j >> 1) & 1, p.error, ERR_S);
       if (!ok) break;
       fence_after();
       float s[32], dp[32];
@@ -596,7 +596,7 @@ fa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         s[i] = pr * (dp[i] - delta);
       }
       if (j > 0) {
-        ok = mbar_wait(&ds_free, (j - 1) & 1, p.error, ERR_PV);
+        ok = mbar_wait_warp(&ds_free, (j - 1) & 1, p.error, ERR_PV);
         if (!ok) break;
       }
       write_row_chunks(ds_tile, row, wg * 4, s);
@@ -604,7 +604,7 @@ fa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_ready);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(&ds_free, (n_tiles - 1) & 1, p.error, ERR_PV);
+    if (ok && n_tiles > 0) ok = mbar_wait_warp(&ds_free, (n_tiles - 1) & 1, p.error, ERR_PV);
     if (ok) {
       fence_after();
       const int qc = head_col(0, p.q_group_stride, p.q_hpg, p.q_head_stride, h);
@@ -763,13 +763,13 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const int hq = hk * rep + it / nq, qi = i_start + it % nq;
       const int qbase = qi * 64 + wg * 32;                 // first query row of this thread's 32 columns
       const int st = it % BWD_STAGES;
-      ok = mbar_wait(&s_full[sb], (it >> 1) & 1, p.error, ERR_S);
+      ok = mbar_wait_warp(&s_full[sb], (it >> 1) & 1, p.error, ERR_S);
       if (!ok) break;
       fence_after();
       // the statistics of this stage were written before its "full" arrival, which the MMA thread saw
       // before it issued the MMAs this wait is about; waiting on the stage barrier as well makes the
       // ordering direct (the phase cannot advance before this iteration's P is handed over)
-      ok = mbar_wait(&qdo_full[st], (it / BWD_STAGES) & 1, p.error, ERR_Q);
+      ok = mbar_wait_warp(&qdo_full[st], (it / BWD_STAGES) & 1, p.error, ERR_Q);
       if (!ok) break;
       float lse2[32], dl[32];
 #pragma unroll
@@ -794,7 +794,7 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         dp[i] = pr * (dp[i] - dl[i]);
       }
       if (it > 0) {
-        ok = mbar_wait(&p_free, (it - 1) & 1, p.error, ERR_PV);
+        ok = mbar_wait_warp(&p_free, (it - 1) & 1, p.error, ERR_PV);
         if (!ok) break;
       }
       write_row_chunks(smem + KV_SMEM_P, row, wg * 4, s);
@@ -803,7 +803,7 @@ fa_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
     }
-    if (ok && n_it > 0) ok = mbar_wait(&p_free, (n_it - 1) & 1, p.error, ERR_PV);
+    if (ok && n_it > 0) ok = mbar_wait_warp(&p_free, (n_it - 1) & 1, p.error, ERR_PV);
     if (ok) {
       fence_after();
       const int kc = head_col(0, p.k_group_stride, p.k_hpg, p.k_head_stride, hk);

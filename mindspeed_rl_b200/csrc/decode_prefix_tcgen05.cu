@@ -258,7 +258,7 @@ prefix_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
       // warp-uniform outcome: the tcgen05.ld / st below are warp-wide instructions
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1, p.error, ERR_S));
+      ok = mbar_wait_warp(&s_full[sb], (j >> 1) & 1, p.error, ERR_S);
       if (!ok) break;
       fence_after();
       float s[HALF], t[32];
@@ -316,7 +316,7 @@ prefix_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       m_run = m_new;
       if (j > 0) {
         // the previous P V product must be finished before P is overwritten or O is rescaled
-        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (j - 1) & 1, p.error, ERR_PV));
+        ok = mbar_wait_warp(&pv_done, (j - 1) & 1, p.error, ERR_PV);
         if (!ok) break;
         fence_after();
         if (__any_sync(0xffffffffu, corr != 1.f)) {
@@ -340,7 +340,7 @@ prefix_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready);
     }
-    if (ok) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, p.error, ERR_PV);
+    if (ok) ok = mbar_wait_warp(&pv_done, (n_tiles - 1) & 1, p.error, ERR_PV);
     // the two partial sums of a row meet in shared memory
     l_part[wg][row] = l_run;
     asm volatile("bar.sync 1, 256;\n" ::: "memory");        // every soft-max thread reaches this once

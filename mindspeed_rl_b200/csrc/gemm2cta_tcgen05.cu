@@ -331,8 +331,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int mt, nt;
       coords(tile, mt, nt);
       const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN;
-      ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, ERR_ACC) &&
-           (*reinterpret_cast<volatile int*>(p.error) == 0);
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, ERR_ACC) &&
+                                       (*reinterpret_cast<volatile int*>(p.error) == 0));
       if (!ok) break;
       fence_after();
       const int row = m0 + warp * 32 + lane;

@@ -370,8 +370,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int mt, nt;
       tile_coords<COMM>(tile, m_tiles, n_tiles, p.rank, p.world, mt_local, mt, nt);
       const int m0 = mt * G_BM, n0 = nt * G_BN;
-      ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, GEMM_TIMEOUT_ACC) &&
-           (*reinterpret_cast<volatile int*>(p.error) == 0);
+      // the lanes agree on the outcome: the tcgen05.ld below is a warp-wide instruction
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, GEMM_TIMEOUT_ACC) &&
+                                       (*reinterpret_cast<volatile int*>(p.error) == 0));
       if (!ok) break;
       tcgen05_fence_after();
       const int row = m0 + warp * 32 + lane;

@@ -152,7 +152,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (p.tile_expert[mt] < 0) continue;
       const uint32_t buf = local & 1;
       const int m0 = mt * BM, n0 = nt * BN;
-      ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, p.error, ERR_ACC);
+      ok = mbar_wait_warp(&acc_full[buf], (local >> 1) & 1, p.error, ERR_ACC);
       if (!ok) break;
       fence_after();
       const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16) + buf * BN;

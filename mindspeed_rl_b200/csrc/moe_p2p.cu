@@ -37,7 +37,7 @@ __global__ void moe_p2p_publish_kernel(const __grid_constant__ P2PPeers tables, 
 // One block of 1024 threads.  all_counts [ep][ep * e_local] (row = source rank).
 __global__ void __launch_bounds__(1024)
 moe_p2p_layout_kernel(const int* all_counts, int ep, int e_local, int me, int cap_rows, int* my_base, int* counts_l,
-                      int* offsets_l, int* tile_expert, int* status) {
+                      int* offsets_l, int* tile_expert, int* status, int* overflow) {
   __shared__ int padded[1024];
   const int n_total = ep * e_local;
   // every (destination, local expert) pair g: rows before mine, total rows
@@ -63,9 +63,12 @@ moe_p2p_layout_kernel(const int* all_counts, int ep, int e_local, int me, int ca
       if (d == me) offsets_l[e] = run;
       run += sz;
     }
+    // every member evaluates every destination from the same table, so all of them reach the same
+    // verdict and can leave the peer-memory path together
+    if (overflow != nullptr && run > cap_rows) atomicMax(overflow, 1);
     if (d == me) {
       offsets_l[e_local] = run;
-      if (run > cap_rows) atomicCAS(status, 0, 300 + me);     // this rank's slab would overflow
+      if (status != nullptr && run > cap_rows) atomicCAS(status, 0, 300 + me);     // this rank's slab would overflow
     }
   }
   __syncthreads();
@@ -161,10 +164,13 @@ MSRL_API int msrl_moe_p2p_publish(void* const* tables, const int* counts, int n_
 }
 
 MSRL_API int msrl_moe_p2p_layout(const int* all_counts, int ep, int e_local, int me, int cap_rows, int* my_base,
-                                 int* counts_l, int* offsets_l, int* tile_expert, int* status, cudaStream_t st) {
+                                 int* counts_l, int* offsets_l, int* tile_expert, int* status, int* overflow,
+                                 cudaStream_t st) {
+  // `overflow` (optional, zeroed by the caller): set to 1 on EVERY member when any member's slab would
+  // overflow; `status` (optional): 300 + me recorded when this rank's own slab would
   if (ep * e_local > 1024 || cap_rows % P2P_PAD != 0) return (int)cudaErrorInvalidValue;
   moe_p2p_layout_kernel<<<1, 1024, 0, st>>>(all_counts, ep, e_local, me, cap_rows, my_base, counts_l, offsets_l,
-                                            tile_expert, status);
+                                            tile_expert, status, overflow);
   return (int)cudaGetLastError();
 }
 

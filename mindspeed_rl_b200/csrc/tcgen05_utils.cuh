@@ -41,6 +41,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
   }
   return true;
 }
+// The same wait for a whole converged warp whose lanes go on to warp-wide (.sync.aligned) tcgen05
+// instructions: the lanes agree on the outcome, so that a wait which gave up in some lanes only can never
+// leave a partial warp in front of such an instruction.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* err, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, err, code));
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");

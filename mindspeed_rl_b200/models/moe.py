@@ -268,7 +268,10 @@ class MoELayer(nn.Module):
             return self._forward_local(x, xr, top_p, top_idx, aux, comm, keep)
         disp = self._p2p_dispatcher(x)
         if disp is not None:
-            return self._forward_p2p(disp, x, xr, top_p, top_idx, aux, comm, keep)
+            done = self._forward_p2p(disp, x, xr, top_p, top_idx, aux, comm, keep)
+            if done is not None:
+                return done
+            # the routing would overflow a member's slab: every member takes the all-to-all path below
         xp, plan = self._dispatch(x, top_idx)
         y_local, ectx = self._experts_fwd(xp, plan["local_counts"], keep)
         y_sorted = self._undispatch(y_local, plan)
@@ -325,7 +328,8 @@ class MoELayer(nn.Module):
             return None
         from ..parallel.moe_dispatch import dispatcher_for
         from ..parallel.symm import get_arena
-        return dispatcher_for(get_arena(), self.ep_group, self.num_local, self.cfg.hidden_size, rows, x.dtype)
+        return dispatcher_for(get_arena(), self.ep_group, self.num_local, self.cfg.hidden_size, rows, x.dtype,
+                              fallback=bool(getattr(self.cfg, "moe_p2p_overflow_fallback", True)))
 
     def _forward_p2p(self, disp, x, xr, top_p, top_idx, aux, comm, keep):
         from ..ops import moe as K
@@ -334,6 +338,8 @@ class MoELayer(nn.Module):
         e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
         w1, w2 = self._w1().reshape(h, e * 2 * f), self._w2().reshape(e * f, h)
         route = disp.dispatch(x, top_idx)
+        if route is None:
+            return None
         gu = K.grouped_gemm(disp.slab, route.plan, w1, True, 2 * f, 0, 2 * f)
         act = ops.swiglu_fwd(gu)
         K.grouped_gemm(act, route.plan, w2, True, 0, f, h, out=disp.out_slab)

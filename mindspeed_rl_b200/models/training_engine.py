@@ -21,6 +21,7 @@ import torch
 import torch.distributed as dist
 
 from ..obs.io_counter import to_device, to_host
+from ..utils.device_status import check_device_status
 from ..utils.seqlen_balancing import get_reverse_idx, rearrange_micro_batches
 from .gpt import GPTModel, PackedMeta
 from .loss.registry import BaseLossFunc, LossFuncFactory
@@ -389,6 +390,10 @@ class TrainingEngine:
             self.model.finish_grad_sync(to_shards=True)
         if self.optimizer is None:
             return True, 0.0, 0
+        # a kernel whose bounded wait gave up (a late or absent peer) left incomplete gradients behind:
+        # raise before they reach the weights (the optimizer step reads the gradient norm back anyway)
+        if self.device.type == "cuda":
+            check_device_status("gradients")
         result = self.optimizer.step()
         if getattr(self.core.cfg, "moe_router_enable_expert_bias", False):
             for layer in self.core.decoder.layers:

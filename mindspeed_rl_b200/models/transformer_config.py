@@ -63,6 +63,7 @@ class TransformerConfig:
     recompute_num_layers: Optional[int] = None
     recompute_activation_function: bool = False     # rebuild silu(g)*u in the backward instead of storing it
     moe_p2p_dispatch_rows: int = 0                  # rows of the peer-memory expert slabs (0: all-to-all collectives)
+    moe_p2p_overflow_fallback: bool = True          # a routing that overflows a slab takes the all-to-all path for that call
     swap_attention: bool = False                    # kept activations wait for the backward in pinned host memory
     # parallel sizes seen by the model code
     tensor_model_parallel_size: int = 1

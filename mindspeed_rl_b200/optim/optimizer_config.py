@@ -67,16 +67,23 @@ class OptimizerConfig:
             raise ValueError(f"optimizer {out.optimizer!r} is not supported (adam / adamw / fused_adamw)")
         return out
 
-    def build(self, buffers, dp_group=None, dp_rank: int = 0, model_parallel_group=None, tp_rank: int = 0):
-        """``(DistributedOptimizer, OptimizerParamScheduler)`` for the flat parameter buffers of a model."""
+    def build(self, buffers, dp_group=None, dp_rank: int = 0, model_parallel_group=None, tp_rank: int = 0,
+              total_steps: Optional[int] = None, warmup_steps: Optional[int] = None, default_lr: float = 0.0):
+        """``(DistributedOptimizer, OptimizerParamScheduler)`` for the flat parameter buffers of a model.
+        ``total_steps`` / ``warmup_steps`` give the schedule's length in the unit the caller steps it
+        with (the RL workers count samples); by default they come from the iteration fields."""
         from .distributed_optimizer import DistributedOptimizer, OptimizerParamScheduler
 
+        lr = self.lr if self.lr else default_lr
         opt = DistributedOptimizer(
-            buffers, lr=self.lr or 0.0, betas=(self.adam_beta1, self.adam_beta2), eps=self.adam_eps,
+            buffers, lr=lr, betas=(self.adam_beta1, self.adam_beta2), eps=self.adam_eps,
             weight_decay=self.weight_decay, clip_grad=self.clip_grad, dp_group=dp_group, dp_rank=dp_rank,
             model_parallel_group=model_parallel_group, offload_to_host=self.swap_optimizer,
             swap_chunks=self.swap_optimizer_times, tp_rank=tp_rank, reuse_fp32_param=self.reuse_fp32_param)
-        total = self.lr_decay_iters or self.train_iters or 0
-        warm = self.lr_warmup_iters or int((self.lr_warmup_fraction or 0.0) * total)
-        sched = OptimizerParamScheduler(opt, self.lr or 0.0, self.min_lr or 0.0, warm, total, self.lr_decay_style)
+        total = total_steps if total_steps is not None else (self.lr_decay_iters or self.train_iters or 0)
+        if warmup_steps is not None:
+            warm = warmup_steps
+        else:
+            warm = self.lr_warmup_iters or int((self.lr_warmup_fraction or 0.0) * total)
+        sched = OptimizerParamScheduler(opt, lr, self.min_lr or 0.0, warm, total, self.lr_decay_style or "constant")
         return opt, sched

@@ -37,10 +37,13 @@ class Route:
 
 class P2PDispatcher:
     def __init__(self, arena: SymmetricArena, ranks: Sequence[int], experts_local: int, hidden: int, cap_rows: int,
-                 dtype: torch.dtype = torch.bfloat16):
+                 dtype: torch.dtype = torch.bfloat16, fallback: bool = True):
         """``ranks``: positions of the expert-parallel group's members inside the arena's team (this
         rank included), in expert order; ``cap_rows``: rows of the slabs (multiple of 128), the same
-        on every rank."""
+        on every rank.  ``fallback``: a routing so skewed that some member's slab would overflow makes
+        ``dispatch`` return ``None`` on every member (the caller then takes the all-to-all path for that
+        call) at the price of one small device-to-host read per call; without it the overflow is
+        recorded in the arena's status word and raised at the next stage boundary."""
         if dtype != torch.bfloat16 or hidden % 8:
             raise ValueError("the peer-memory dispatcher moves bf16 rows whose length is a multiple of 8")
         self.arena, self.ranks = arena, list(ranks)
@@ -56,6 +59,9 @@ class P2PDispatcher:
         self.out_slab = arena.alloc((self.cap_rows, hidden), dtype)
         dev = self.slab.device
         self.my_base = torch.empty(self.n_total, dtype=torch.int32, device=dev)
+        self.fallback = fallback
+        self.over = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.overflows = 0          # calls that left the peer-memory path
         self._table_ptrs = arena.peer_ptrs(arena.offset_of(self.table), self.ranks)
         self._slab_ptrs = arena.peer_ptrs(arena.offset_of(self.slab), self.ranks)
         self._out_ptrs = arena.peer_ptrs(arena.offset_of(self.out_slab), self.ranks)
@@ -67,9 +73,10 @@ class P2PDispatcher:
         return ep * ep * experts_local * 4 + 2 * cap * hidden * 2 + 3 * 256
 
     def dispatch(self, x: torch.Tensor, expert_ids: torch.Tensor, scale: Optional[torch.Tensor] = None,
-                 route: Optional[Route] = None) -> Route:
+                 route: Optional[Route] = None) -> Optional[Route]:
         """Send ``x[t]`` (times ``scale[t, j]``) to the rank of expert ``expert_ids[t, j]`` (global
-        ids).  With ``route`` (the forward's) the counts and the layout are reused as they are."""
+        ids).  Returns ``None`` (on every member alike, nothing sent) when a slab would overflow and
+        ``fallback`` is on."""
         lib, st = self.arena.lib, stream()
         t, k = expert_ids.shape
         dev = x.device
@@ -84,7 +91,12 @@ class P2PDispatcher:
         tiles = torch.empty(self.cap_rows // K.PAD, dtype=torch.int32, device=dev)
         check(lib.msrl_moe_p2p_layout(ptr(self.table), c_int(self.ep), c_int(self.e_local), c_int(self.me),
                                       c_int(self.cap_rows), ptr(self.my_base), ptr(counts_l), ptr(offsets_l),
-                                      ptr(tiles), ptr(self.arena.status), st), "moe_p2p_layout")
+                                      ptr(tiles), None if self.fallback else ptr(self.arena.status),
+                                      ptr(self.over) if self.fallback else None, st), "moe_p2p_layout")
+        if self.fallback and int(self.over.item()):
+            self.over.zero_()
+            self.overflows += 1
+            return None
         slot_rank = torch.empty(t * k, dtype=torch.int32, device=dev)
         slot_row = torch.empty(t * k, dtype=torch.int32, device=dev)
         wf = None if scale is None else scale.reshape(-1).float().contiguous()
@@ -118,7 +130,7 @@ _dispatchers = {}
 
 
 def dispatcher_for(arena: Optional[SymmetricArena], ep_group, experts_local: int, hidden: int, cap_rows: int,
-                   dtype: torch.dtype) -> Optional[P2PDispatcher]:
+                   dtype: torch.dtype, fallback: bool = True) -> Optional[P2PDispatcher]:
     """The shared dispatcher of this expert-parallel group, created on first use (every member
     reaches this call at the same point, so the arena offsets agree); ``None`` when the buffers do
     not fit or the shapes are outside the kernels' cover."""
@@ -128,6 +140,6 @@ def dispatcher_for(arena: Optional[SymmetricArena], ep_group, experts_local: int
     if key not in _dispatchers:
         ranks = arena.team_ranks(ep_group)
         need = P2PDispatcher.bytes_needed(len(ranks), experts_local, hidden, cap_rows)
-        _dispatchers[key] = P2PDispatcher(arena, ranks, experts_local, hidden, cap_rows, dtype) \
+        _dispatchers[key] = P2PDispatcher(arena, ranks, experts_local, hidden, cap_rows, dtype, fallback=fallback) \
             if arena.free_bytes() >= need else None
     return _dispatchers[key]

@@ -72,10 +72,11 @@ class MoEWeights:
             h, f = x.shape[1], self.w2.shape[1]
             e = self.num_local
             rt = disp.dispatch(x, phys)
-            gu = K.grouped_gemm(disp.slab, rt.plan, self.w1.reshape(h, e * 2 * f), True, 2 * f, 0, 2 * f)
-            K.grouped_gemm(ops.swiglu_fwd(gu), rt.plan, self.w2.reshape(e * f, h), True, 0, f, h, out=disp.out_slab)
-            out, _ = disp.combine(rt, top_p)
-            return self._add_shared(out, x, comm)
+            if rt is not None:       # None: some member's slab would overflow, all members use the collectives below
+                gu = K.grouped_gemm(disp.slab, rt.plan, self.w1.reshape(h, e * 2 * f), True, 2 * f, 0, 2 * f)
+                K.grouped_gemm(ops.swiglu_fwd(gu), rt.plan, self.w2.reshape(e * f, h), True, 0, f, h, out=disp.out_slab)
+                out, _ = disp.combine(rt, top_p)
+                return self._add_shared(out, x, comm)
         flat = phys.reshape(-1)
         order = torch.argsort(flat, stable=True)
         token_of = order // k

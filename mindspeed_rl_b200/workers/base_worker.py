@@ -18,6 +18,7 @@ import torch.distributed as dist
 
 from ..obs.profiler import nvtx_range, profiler_start, profiler_stop
 from ..parallel.state import ParallelState, get_parallel_state
+from ..utils.device_status import check_device_status
 from ..utils.pad_process import (pad_rows, padding_dict_to_tensor_dict,
                                  remove_padding_tensor_dict_to_dict, truncate_rows)
 
@@ -49,20 +50,6 @@ def _align_mm(mm, cols):
         out.append({c: cols[c][k] for c in names})
         k += 1
     return out
-
-
-def check_device_status(stage: str = "") -> None:
-    """Stage boundary: read the status words the kernels' bounded waits report through (tcgen05
-    pipelines, peer-memory barriers and slabs) and raise if one of them gave up, instead of handing
-    a silently incomplete result to the next stage.  One small device-to-host read per stage; no-op
-    when no such kernel ran in this process."""
-    from ..ops import gemm
-    from ..parallel.symm import get_arena
-    for dev in list(gemm._status):
-        gemm.check_status(dev, f"stage {stage}: tcgen05 kernel")
-    arena = get_arena()
-    if arena is not None:
-        arena.check()
 
 
 def profiled_stage(role: str):

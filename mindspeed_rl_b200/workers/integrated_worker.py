@@ -21,7 +21,7 @@ import torch.distributed as dist
 from ..models.gpt import GPTModel
 from ..models.training_engine import TrainingEngine
 from ..models.transformer_config import TransformerConfig
-from ..optim.distributed_optimizer import DistributedOptimizer, OptimizerParamScheduler
+from ..optim.optimizer_config import OptimizerConfig
 from ..parallel.ddp import DistributedDataParallel, expert_replica_groups
 from ..parallel.state import get_parallel_state
 from ..parallel.tp_comm import TPComm
@@ -178,18 +178,13 @@ class IntegratedWorker(BaseWorker):
                                              **expert_replica_groups(ps, tcfg))
         self._maybe_attach_fused_tp()
         self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(ac.sequence_parallel))
-        self.optimizer = DistributedOptimizer(
-            self.model.buffers, lr=ac.lr or 1e-6, betas=(ac.adam_beta1, ac.adam_beta2),
-            weight_decay=ac.weight_decay, clip_grad=ac.clip_grad, dp_group=ps.group("dp_cp"),
-            dp_rank=ps.rank_in("dp_cp"), model_parallel_group=ps.group("mp"),
-            offload_to_host=bool(ac.swap_optimizer), tp_rank=ps.rank_in("tp"),
-            reuse_fp32_param=bool(getattr(ac, "reuse_fp32_param", False)))
         iters = ac.train_iters or 1
         n_updates = iters * max(1, (ac.global_batch_size * rl.n_samples_per_prompt) // max(rl.mini_batch_size, 1))
-        samples = n_updates * rl.mini_batch_size
-        warm = int((ac.lr_warmup_fraction or 0.0) * samples)
-        self.scheduler = OptimizerParamScheduler(self.optimizer, ac.lr or 1e-6, ac.min_lr or 0.0, warm,
-                                                 samples, ac.lr_decay_style or "constant")
+        samples = n_updates * rl.mini_batch_size            # the schedule is stepped in samples
+        self.optimizer, self.scheduler = OptimizerConfig.from_training_config(ac).build(
+            self.model.buffers, dp_group=ps.group("dp_cp"), dp_rank=ps.rank_in("dp_cp"),
+            model_parallel_group=ps.group("mp"), tp_rank=ps.rank_in("tp"), total_steps=samples,
+            warmup_steps=int((ac.lr_warmup_fraction or 0.0) * samples), default_lr=1e-6)
         loss_opts = dict(clip_ratio=rl.clip_ratio, kl_penalty=rl.kl_penalty, entropy_coeff=rl.entropy_coeff,
                          token_level_loss=rl.token_level_loss, clip_higher_enable=rl.clip_higher_enable,
                          clip_ratio_low=rl.clip_ratio_low, clip_ratio_high=rl.clip_ratio_high,

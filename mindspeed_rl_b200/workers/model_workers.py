@@ -15,7 +15,7 @@ import torch
 from ..models.gpt import GPTModel
 from ..models.training_engine import TrainingEngine
 from ..models.transformer_config import TransformerConfig
-from ..optim.distributed_optimizer import DistributedOptimizer, OptimizerParamScheduler
+from ..optim.optimizer_config import OptimizerConfig
 from ..parallel.ddp import DistributedDataParallel, expert_replica_groups
 from ..parallel.tp_comm import TPComm
 from ..reshard.sharding_manager import GradBufferOffloader, ParamOffloader
@@ -68,14 +68,10 @@ class _ModelWorker(BaseWorker):
                                                  grad_in_fp32=bool(mc.accumulate_allreduce_grads_in_fp32),
                                                  **expert_replica_groups(ps, tcfg))
             self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(mc.sequence_parallel))
-            self.optimizer = DistributedOptimizer(
-                self.model.buffers, lr=mc.lr or 1e-6, betas=(mc.adam_beta1, mc.adam_beta2),
-                weight_decay=mc.weight_decay, clip_grad=mc.clip_grad, dp_group=ps.group("dp_cp"),
-                dp_rank=ps.rank_in("dp_cp"), model_parallel_group=ps.group("mp"),
-                offload_to_host=bool(mc.swap_optimizer), tp_rank=ps.rank_in("tp"),
-            reuse_fp32_param=bool(getattr(mc, "reuse_fp32_param", False)))
-            self.scheduler = OptimizerParamScheduler(self.optimizer, mc.lr or 1e-6, mc.min_lr or 0.0, 0,
-                                                     max(mc.train_iters or 1, 1), mc.lr_decay_style or "constant")
+            self.optimizer, self.scheduler = OptimizerConfig.from_training_config(mc).build(
+                self.model.buffers, dp_group=ps.group("dp_cp"), dp_rank=ps.rank_in("dp_cp"),
+                model_parallel_group=ps.group("mp"), tp_rank=ps.rank_in("tp"),
+                total_steps=max(mc.train_iters or 1, 1), warmup_steps=0, default_lr=1e-6)
             self.engine = TrainingEngine(self.model, self.optimizer, self.scheduler, role=self.role,
                                          mini_batch_size_per_dp=max(rl.mini_batch_size // dp, 1),
                                          epochs=rl.epochs, shuffle_mini_batch=rl.shuffle_mini_batch,

@@ -69,35 +69,6 @@ def case_collectives(rank, world):
         arena.all_gather(src, dst, ranks=pair)
         arena.check()
         assert dst[:1024].eq(pair[0]).all() and dst[1024:].eq(pair[1]).all()
-    # timing: device time of the pull kernels against NCCL on the same sizes
-    big = arena.alloc(64 << 20, torch.bfloat16)
-    bper = big.numel() // world
-    tmp = torch.empty_like(big)
-
-    def timed(fn, iters=5):
-        for _ in range(2):
-            fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / iters], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
-
-    t_ag = timed(lambda: arena.all_gather_inplace(big))
-    t_ag_nccl = timed(lambda: dist.all_gather_into_tensor(tmp, big[rank * bper:(rank + 1) * bper]))
-    t_rs = timed(lambda: arena.reduce_scatter(big, big[rank * bper:(rank + 1) * bper], scale=0.5))
-    t_rs_nccl = timed(lambda: dist.reduce_scatter_tensor(tmp[rank * bper:(rank + 1) * bper], big))
-    arena.check()
-    if rank == 0:
-        mb = big.numel() * 2 / 1e6
-        print(f"TIMING world={world} size={mb:.0f}MB all_gather symm={t_ag:.3f}ms nccl={t_ag_nccl:.3f}ms "
-              f"reduce_scatter symm={t_rs:.3f}ms nccl={t_rs_nccl:.3f}ms", flush=True)
     arena.close()
 
 
@@ -146,28 +117,6 @@ def case_peer_all_reduce(rank, world):
         arena.check()
         assert torch.all(y.float() == float(pair[0] + pair[1]))
 
-    def timed(fn, iters=50):
-        for _ in range(5):
-            fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / iters], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
-
-    for tokens in (64, 256, 512):
-        x = torch.randn(tokens, 3584, device="cuda").bfloat16()
-        t_peer = timed(lambda: ar.all_reduce(x))
-        t_nccl = timed(lambda: dist.all_reduce(x))
-        if rank == 0:
-            print(f"TIMING all_reduce world={world} tokens={tokens} ({tokens * 7168 / 1e6:.2f} MB) "
-                  f"peer={t_peer * 1e3:.1f}us nccl={t_nccl * 1e3:.1f}us", flush=True)
     arena.check()
     arena.close()
 
@@ -246,50 +195,7 @@ def case_fused_tp(rank, world):
         err = (out.float() - ref).abs().max().item()
         assert err <= 3e-2 * ref.abs().max().item() + 1e-3, f"gemm_rs error {err} (call {it})"
 
-    ml = ml_max
-
-    def timed(fn, iters=10):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a_.record()
-        for _ in range(iters):
-            fn()
-        b_.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a_.elapsed_time(b_) / iters], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
-
-    x, w = rnd(ml, hidden), rnd(n_col, hidden)
-    a, w2 = rnd(world * ml, k_row), rnd(hidden, k_row)
-    xg = torch.empty(world * ml, hidden, dtype=torch.bfloat16, device="cuda")
-    o = torch.empty(ml, hidden, dtype=torch.bfloat16, device="cuda")
-
-    def base_ag():
-        dist.all_gather_into_tensor(xg, x)
-        return torch.matmul(xg, w.t())
-
-    def base_rs():
-        dist.reduce_scatter_tensor(o, torch.matmul(a, w2.t()))
-
-    t = dict(ag_fused=timed(lambda: f.ag_gemm(x, w)), ag_nccl=timed(base_ag),
-             rs_fused=timed(lambda: f.gemm_rs(a, w2)), rs_nccl=timed(base_rs))
-    f.use_pair = False                      # the single-CTA kernels on the same shapes, for comparison
-    t.update(ag_single=timed(lambda: f.ag_gemm(x, w)), rs_single=timed(lambda: f.gemm_rs(a, w2)))
-    f.use_pair = True
-    check_status(torch.device("cuda", torch.cuda.current_device()),"fused timing loop")
     arena.check()
-    if rank == 0:
-        fl_ag = 2.0 * world * ml * hidden * n_col
-        fl_rs = 2.0 * world * ml * k_row * hidden
-        print(f"TIMING fused_tp world={world} m_local={ml} ag_gemm[N={n_col},K={hidden}] fused={t['ag_fused']:.3f}ms "
-              f"({fl_ag / t['ag_fused'] / 1e9:.0f} TFLOP/s) nccl+cublas={t['ag_nccl']:.3f}ms | "
-              f"gemm_rs[N={hidden},K={k_row}] fused={t['rs_fused']:.3f}ms ({fl_rs / t['rs_fused'] / 1e9:.0f} TFLOP/s) "
-              f"cublas+nccl={t['rs_nccl']:.3f}ms | single-CTA kernels: ag {t['ag_single']:.3f}ms rs {t['rs_single']:.3f}ms",
-              flush=True)
     arena.close()
 
 
@@ -457,64 +363,6 @@ def case_cp_ring(rank, world):
             (n, (gr / world - ref).abs().max().item(), ref.abs().max().item())
 
 
-def case_moe_dispatch_timing(rank, world):
-    """Device time (max over ranks) of one MoE token round trip between expert-parallel ranks:
-    peer-memory dispatch + combine against count exchange + two all-to-all collectives."""
-    from mindspeed_rl_b200.ops import moe as K
-    from mindspeed_rl_b200.parallel.moe_dispatch import P2PDispatcher
-    from mindspeed_rl_b200.parallel.symm import init_arena
-    t, k, h, e_local = 8192, 8, 2048, 16
-    e = e_local * world
-    rows = 2 * t * k + e_local * 128
-    arena = init_arena(P2PDispatcher.bytes_needed(world, e_local, h, rows) + (8 << 20))
-    disp = P2PDispatcher(arena, list(range(world)), e_local, h, rows)
-    g = torch.Generator(device="cuda").manual_seed(rank)
-    x = torch.randn(t, h, device="cuda", generator=g).bfloat16()
-    idx = torch.stack([torch.randperm(e, device="cuda", generator=g)[:k] for _ in range(256)]).repeat(t // 256, 1)
-    w = torch.rand(t, k, device="cuda", generator=g)
-
-    def p2p():
-        route = disp.dispatch(x, idx)
-        disp.out_slab.copy_(disp.slab)                      # stand-in for the expert MLP
-        return disp.combine(route, w)[0]
-
-    def a2a():
-        flat = idx.reshape(-1)
-        order = torch.argsort(flat, stable=True)
-        xp = x[order // k]
-        send = torch.bincount(flat, minlength=e).view(world, e_local)
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send)
-        send_rows, recv_rows = send.sum(1).tolist(), recv.sum(1).tolist()
-        got = torch.empty(sum(recv_rows), h, device="cuda", dtype=x.dtype)
-        dist.all_to_all_single(got, xp, recv_rows, send_rows)
-        back = torch.empty_like(xp)
-        dist.all_to_all_single(back, got, send_rows, recv_rows)
-        out = torch.zeros(t, h, device="cuda", dtype=torch.float32)
-        out.index_add_(0, order // k, (back * w.reshape(-1)[order].to(x.dtype).unsqueeze(-1)).float())
-        return out.to(x.dtype)
-
-    ref, got = a2a(), p2p()
-    arena.check()
-    err, scale = (ref.float() - got.float()).abs().max().item(), ref.float().abs().max().item()
-    assert err <= 2e-2 * scale + 0.05, (err, scale)        # the collective path rounds w * row to bf16 first
-    for name, fn in (("p2p", p2p), ("nccl_a2a", a2a)):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        s, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(10):
-            fn()
-        e_.record()
-        torch.cuda.synchronize()
-        ms = torch.tensor([s.elapsed_time(e_) / 10], device="cuda")
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        if rank == 0:
-            print(f"TIMING moe round trip {name}: {ms.item():.3f} ms (T={t}/rank, k={k}, H={h}, {world} ranks)", flush=True)
-
-
 def case_arena_fallback(rank, world):
     """One rank cannot allocate its arena (it asks for far more than the device has; the allocation
     call returns an error code): every rank gets the same exception, nobody is left waiting in a
@@ -535,7 +383,7 @@ def case_arena_fallback(rank, world):
     assert float(x[0]) == rank + 1
 
 
-CASES = {"peer_all_reduce": case_peer_all_reduce, "arena_fallback": case_arena_fallback, "moe_dispatch_timing": case_moe_dispatch_timing, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+CASES = {"peer_all_reduce": case_peer_all_reduce, "arena_fallback": case_arena_fallback, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

@@ -176,6 +176,20 @@ def _ep_worker(rank, world):
     fw = full.decoder.layers[0].mlp.experts.weight2.grad.view(4, 16, 32).clone()
     dist.all_reduce(fw)
     assert torch.allclose(gw.view(per, 16, 32), fw[rank * per:(rank + 1) * per], atol=2e-4)
+    # a peer-memory dispatcher that reports a slab overflow (dispatch -> None on every member) sends the
+    # layer to the all-to-all path: same result
+    class _Overflowing:
+        calls = 0
+
+        def dispatch(self, x, idx):
+            _Overflowing.calls += 1
+            return None
+
+    moe = model.decoder.layers[0].mlp
+    moe._p2p_dispatcher = lambda x: _Overflowing()
+    with torch.no_grad():
+        lp2, _ = model.forward_logprob(ids, labels, meta)
+    assert _Overflowing.calls == 1 and torch.allclose(lp2, lp.detach(), atol=1e-6)
 
 
 def test_expert_parallel_matches_single_rank():

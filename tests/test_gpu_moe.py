@@ -73,6 +73,31 @@ def test_moe_layer_kernels(t, k, e, h, f):
     G.check_status(torch.device("cuda", torch.cuda.current_device()), "grouped gemm")
 
 
+def test_peer_memory_dispatch_overflow_falls_back():
+    """A slab too small for the routing: with the fallback on, ``dispatch`` returns ``None`` and leaves the
+    status word alone; with it off, the overflow is recorded for the stage-boundary check."""
+    from mindspeed_rl_b200.parallel.moe_dispatch import P2PDispatcher
+    from mindspeed_rl_b200.parallel.symm import SymmetricArena
+    torch.manual_seed(4)
+    t, k, e, h = 400, 4, 8, 128
+    rows = 512                                            # far below the t * k = 1600 rows this routing needs
+    arena = SymmetricArena(2 * P2PDispatcher.bytes_needed(1, e, h, rows) + (4 << 20))
+    try:
+        x = torch.randn(t, h, device="cuda").bfloat16()
+        idx = torch.stack([torch.randperm(e, device="cuda")[:k] for _ in range(t)])
+        soft = P2PDispatcher(arena, [0], e, h, rows, fallback=True)
+        assert soft.dispatch(x, idx) is None and soft.overflows == 1
+        arena.check()                                     # nothing recorded
+        small = idx[:64]                                  # 256 rows + padding fit
+        assert soft.dispatch(x[:64], small) is not None and soft.overflows == 1
+        hard = P2PDispatcher(arena, [0], e, h, rows, fallback=False)
+        hard.dispatch(x, idx)
+        with pytest.raises(RuntimeError, match="overflow"):
+            arena.check()
+    finally:
+        arena.close()
+
+
 def test_peer_memory_dispatch_single_rank():
     """The peer-memory dispatch / combine kernels with a team of one rank (its own arena is the only
     "peer"): slab layout, rows, tile table and the weighted combine agree with the plan / permute /
