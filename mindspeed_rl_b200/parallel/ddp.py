@@ -41,7 +41,7 @@ class ParamAndGradBuffer:
     def __init__(self, named_params: Iterable[Tuple[str, nn.Parameter]], dp_size: int = 1,
                  grad_dtype: Optional[torch.dtype] = None, bucket_numel: Optional[int] = None,
                  group=None, dp_rank: Optional[int] = None, grad_scale: Optional[float] = None,
-                 is_expert: bool = False):
+                 is_expert: bool = False, releasable_params: bool = False, releasable_grads: bool = False):
         # ``group`` / ``dp_rank`` / ``dp_size``: the ranks that hold replicas of these parameters.
         # Dense parameters are replicated over the whole data-parallel group; expert parameters
         # only over the expert-data-parallel group (the EP ranks hold different experts), but their
@@ -67,21 +67,34 @@ class ParamAndGradBuffer:
         self.numel = _align(off, self.ALIGN * max(dp_size, 1))
         # With a symmetric arena the flat buffers are peer-mapped: gradient reduce-scatter,
         # parameter all-gather and rollout resharding then run as direct NVLink pull kernels.
-        self.arena = None
+        # A buffer marked releasable gets a peer-mapped segment of its own (same team as the arena)
+        # instead of a slice of the job-wide arena, so that it can be unmapped and freed while the
+        # rollout needs the memory and mapped again afterwards (``release_*`` / ``restore_*``).
+        self.param_arena = self.grad_arena = None
+        self._own = {"param": False, "grad": False}
+        self._team = None
         if self.device.type == "cuda":
             from .symm import get_arena
 
             arena = get_arena()
-            need = self.numel * (torch.empty(0, dtype=self.param_dtype).element_size()
-                                 + torch.empty(0, dtype=self.grad_dtype).element_size()) + 1024
-            if arena is not None and arena.free_bytes() >= need:
-                self.arena = arena
-        if self.arena is not None:
-            self.param_data = self.arena.alloc(self.numel, self.param_dtype).zero_()
-            self.grad_data = self.arena.alloc(self.numel, self.grad_dtype).zero_()
-        else:
-            self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=self.device)
-            self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
+            if arena is not None:
+                self._team = arena.group
+                p_bytes = self.numel * torch.empty(0, dtype=self.param_dtype).element_size() + 512
+                g_bytes = self.numel * torch.empty(0, dtype=self.grad_dtype).element_size() + 512
+                if releasable_params:
+                    self.param_arena = self._segment(p_bytes)
+                    self._own["param"] = self.param_arena is not None
+                if releasable_grads:
+                    self.grad_arena = self._segment(g_bytes)
+                    self._own["grad"] = self.grad_arena is not None
+                shared = (0 if releasable_params else p_bytes) + (0 if releasable_grads else g_bytes)
+                if shared and arena.free_bytes() >= shared:
+                    if not releasable_params:
+                        self.param_arena = arena
+                    if not releasable_grads:
+                        self.grad_arena = arena
+        self.param_data = self._new_flat(self.param_arena, self.param_dtype)
+        self.grad_data = self._new_flat(self.grad_arena, self.grad_dtype)
         self.params: List[nn.Parameter] = []
         for (n, p), slot in zip(params, self.slots):
             view = self.param_data[slot.start:slot.start + slot.numel].view(slot.shape)
@@ -91,6 +104,73 @@ class ParamAndGradBuffer:
             p.grad = None
             self.params.append(p)
         self.by_name: Dict[str, ParamSlot] = {s.name: s for s in self.slots}
+
+    # ---- storage -------------------------------------------------------------------------------------
+    @property
+    def arena(self):
+        """A peer-mapped home of (one of) the flat buffers, or ``None`` when both are plain allocations."""
+        return self.param_arena if self.param_arena is not None else self.grad_arena
+
+    def _segment(self, nbytes: int):
+        """A peer-mapped segment of its own over the arena's team; ``None`` when it cannot be set up
+        (the outcome is the same on every rank of the team)."""
+        from .symm import ArenaUnavailable, SymmetricArena
+
+        try:
+            return SymmetricArena(nbytes, self._team, self.device)
+        except ArenaUnavailable:
+            return None
+
+    def _new_flat(self, arena, dtype: torch.dtype) -> torch.Tensor:
+        if arena is not None:
+            return arena.alloc(self.numel, dtype).zero_()
+        return torch.zeros(self.numel, dtype=dtype, device=self.device)
+
+    def release_grads(self) -> bool:
+        """Free the gradient buffer (it holds no state between steps).  A slice of the job-wide arena
+        cannot be freed: returns ``False`` and keeps it.  Collective over the team for a segment."""
+        if self.grad_arena is not None and not self._own["grad"]:
+            return False
+        self.grad_data = torch.empty(0, dtype=self.grad_dtype, device=self.device)
+        for p in self.params:
+            p.main_grad = None
+        if self.grad_arena is not None:
+            self.grad_arena.close()
+            self.grad_arena = None
+        return True
+
+    def restore_grads(self) -> None:
+        if self.grad_data.numel():
+            return
+        if self._own["grad"]:
+            self.grad_arena = self._segment(self.numel * self.grad_data.element_size() + 512)
+        self.grad_data = self._new_flat(self.grad_arena, self.grad_dtype)
+        self.rebind()
+
+    def release_params(self, host: torch.Tensor) -> bool:
+        """Copy the parameters to ``host`` (pinned) and free the device buffer.  Same rule as for the
+        gradients: only a plain allocation or a segment of its own can go."""
+        if self.param_arena is not None and not self._own["param"]:
+            return False
+        host.copy_(self.param_data, non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        self.param_data = torch.empty(0, dtype=self.param_dtype, device=self.device)
+        for p in self.params:
+            p.data = self.param_data
+        if self.param_arena is not None:
+            self.param_arena.close()
+            self.param_arena = None
+        return True
+
+    def restore_params(self, host: torch.Tensor) -> None:
+        if self.param_data.numel():
+            return
+        if self._own["param"]:
+            self.param_arena = self._segment(self.numel * self.param_data.element_size() + 512)
+        self.param_data = self._new_flat(self.param_arena, self.param_dtype)
+        self.param_data.copy_(host, non_blocking=True)
+        self.rebind()
 
     # ------------------------------------------------------------------------------------------
     def zero_grad(self) -> None:
@@ -118,15 +198,15 @@ class ParamAndGradBuffer:
             if self.is_expert and scale != 1.0:   # experts without replicas still average over the DP tokens
                 self.grad_data.mul_(scale)
             return
-        if self.arena is not None and to_shards:
+        if self.grad_arena is not None and to_shards:
             # one pull kernel: sum the peers' copies of my shard, scale, write my slice in place
             per = self.numel // self.dp_size
             r = dist.get_rank(group)
             # the ranks reach this point after unequal work (differently packed micro-batches):
             # a stream-ordered collective lines them up before the bounded device barrier
-            self.arena.align(group)
-            self.arena.reduce_scatter(self.grad_data, self.grad_data[r * per:(r + 1) * per],
-                                      scale=scale, ranks=self.arena.team_ranks(group))
+            self.grad_arena.align(group)
+            self.grad_arena.reduce_scatter(self.grad_data, self.grad_data[r * per:(r + 1) * per],
+                                           scale=scale, ranks=self.grad_arena.team_ranks(group))
             return
         if scale != 1.0:
             self.grad_data.mul_(scale)
@@ -145,8 +225,8 @@ class ParamAndGradBuffer:
             return
         per = self.numel // self.dp_size
         r = dist.get_rank(group)
-        if self.arena is not None:
-            self.arena.all_gather_inplace(self.param_data, ranks=self.arena.team_ranks(group))
+        if self.param_arena is not None:
+            self.param_arena.all_gather_inplace(self.param_data, ranks=self.param_arena.team_ranks(group))
             return
         dist.all_gather_into_tensor(self.param_data, self.param_data[r * per:(r + 1) * per].clone(),
                                     group=group)
@@ -172,11 +252,19 @@ class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, dp_group=None, dp_size: int = 1,
                  grad_in_fp32: bool = False, bucket_numel: Optional[int] = None,
                  expert_dp_group=None, expert_dp_size: Optional[int] = None,
-                 expert_dp_rank: Optional[int] = None):
+                 expert_dp_rank: Optional[int] = None, releasable_params: bool = False,
+                 releasable_grads: bool = False, releasable_experts: bool = True):
         """``expert_dp_*`` describe the ranks that hold replicas of this rank's experts (Megatron's
         expert-data-parallel group).  When given, the expert weights get a buffer of their own that
         is reduced, sharded (optimizer state) and gathered over that group only; without it
-        every parameter is treated as replicated over ``dp_group``."""
+        every parameter is treated as replicated over ``dp_group``.
+
+        ``releasable_params`` / ``releasable_grads``: on a machine with a peer-mapped arena give the flat
+        parameter / gradient buffer a peer-mapped segment of its own, which the memory choreography of a
+        co-located rollout can free and map again (``offload_train_param`` / ``offload_train_grad``);
+        creating, freeing and re-creating a segment are collective over the arena's team, so every rank
+        of the team must hold the same buffers (``releasable_experts=False`` leaves the expert buffer in
+        the arena where pipeline stages differ in whether they have experts)."""
         super().__init__()
         self.module = module
         self.dp_group, self.dp_size = dp_group, dp_size
@@ -192,11 +280,15 @@ class DistributedDataParallel(nn.Module):
         self.buffers: List[ParamAndGradBuffer] = []
         gdt = torch.float32 if grad_in_fp32 else None
         if main:
-            self.buffers.append(ParamAndGradBuffer(main, dp_size, gdt, bucket_numel, group=dp_group))
+            self.buffers.append(ParamAndGradBuffer(main, dp_size, gdt, bucket_numel, group=dp_group,
+                                                   releasable_params=releasable_params,
+                                                   releasable_grads=releasable_grads))
         if experts:
             self.buffers.append(ParamAndGradBuffer(
                 experts, expert_dp_size, gdt, bucket_numel, group=expert_dp_group, dp_rank=expert_dp_rank,
-                grad_scale=1.0 / max(dp_size, 1), is_expert=True))
+                grad_scale=1.0 / max(dp_size, 1), is_expert=True,
+                releasable_params=releasable_params and releasable_experts,
+                releasable_grads=releasable_grads and releasable_experts))
         if fp32_params:  # e.g. the fp32 value head
             self.buffers.append(ParamAndGradBuffer(fp32_params, dp_size, torch.float32, bucket_numel,
                                                    group=dp_group))

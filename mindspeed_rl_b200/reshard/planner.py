@@ -353,14 +353,19 @@ class Resharder:
     def _main_buffer(self):
         return self.ddp.buffers[0]
 
+    def _param_arena(self):
+        """The peer-mapped home of the training parameters (the job-wide arena or the buffer's own
+        segment), or ``None`` when they are a plain allocation."""
+        return getattr(self._main_buffer(), "param_arena", None) if self.arena is not None else None
+
     def _use_arena(self) -> bool:
-        return self.arena is not None and self.arena.contains(self._main_buffer().param_data)
+        return self._param_arena() is not None
 
     def _build(self) -> None:
         ps = self.train_state
         buf = self._main_buffer()
         mine = {s.name: Slot(s.start, tuple(s.shape)) for s in buf.slots}
-        base = self.arena.offset_of(buf.param_data) if self._use_arena() else 0
+        base = self._param_arena().offset_of(buf.param_data) if self._use_arena() else 0
         stage = ps.rank_in("pp")
         info = (ps.rank, stage, base, mine if ps.rank_in("tp") == 0 else None)
         if dist.is_initialized() and ps.size("mp") > 1:
@@ -408,10 +413,11 @@ class Resharder:
         if self._use_arena():
             # the ranks arrive from the update stage at different times: line them up before the
             # bounded device barrier (outside the timed interval: it is waiting, not resharding)
-            self.arena.align()
+            home = self._param_arena()
+            home.align()
             if timed:
                 self._events[0].record()
-            self.arena.copy_plan(self._plan_dev[0], self._plan_dev[1], self.buffer, sync=True)
+            home.copy_plan(self._plan_dev[0], self._plan_dev[1], self.buffer, sync=True)
         else:
             self._gathered_copy(plan, buf)
         if timed:

@@ -24,7 +24,9 @@ from .alias import alias_rollout_weights
 
 
 class GradBufferOffloader:
-    """Release / re-create the flat gradient buffers (they hold no state between steps)."""
+    """Release / re-create the flat gradient buffers (they hold no state between steps).  A buffer that
+    is a slice of the job-wide peer-mapped arena stays resident; one with a peer-mapped segment of its
+    own (``DistributedDataParallel(releasable_grads=True)``) or a plain allocation is really freed."""
 
     def __init__(self, ddp: Optional[DistributedDataParallel]):
         self.ddp = ddp
@@ -34,26 +36,20 @@ class GradBufferOffloader:
         if self.ddp is None or self.released:
             return
         for b in self.ddp.buffers:
-            if b.arena is not None:      # peer-mapped buffers stay resident for the life of the job
-                continue
-            b.grad_data = torch.empty(0, dtype=b.grad_dtype, device=b.device)
-            for p in b.params:
-                p.main_grad = None
+            b.release_grads()
         self.released = True
 
     def restore(self) -> None:
         if self.ddp is None or not self.released:
             return
         for b in self.ddp.buffers:
-            if b.arena is not None:
-                continue
-            b.grad_data = torch.zeros(b.numel, dtype=b.grad_dtype, device=b.device)
-            b.rebind()
+            b.restore_grads()
         self.released = False
 
 
 class ParamOffloader:
-    """Swap a flat parameter buffer between the device and a pinned host twin."""
+    """Swap the flat parameter buffers between the device and pinned host twins (same rule: a slice of
+    the job-wide arena stays where it is)."""
 
     def __init__(self, ddp: Optional[DistributedDataParallel]):
         self.ddp = ddp
@@ -63,30 +59,18 @@ class ParamOffloader:
     def offload(self) -> None:
         if self.ddp is None or self.offloaded:
             return
-        if any(b.arena is not None for b in self.ddp.buffers):
-            return                       # peer-mapped parameter buffers are never swapped out
         if not self.host:
             self.host = [torch.empty(b.numel, dtype=b.param_dtype, pin_memory=b.device.type == "cuda")
                          for b in self.ddp.buffers]
         for b, h in zip(self.ddp.buffers, self.host):
-            h.copy_(b.param_data, non_blocking=True)
-        if self.ddp.buffers[0].device.type == "cuda":
-            torch.cuda.current_stream().synchronize()
-        for b in self.ddp.buffers:
-            b.param_data = torch.empty(0, dtype=b.param_dtype, device=b.device)
-            for p in b.params:
-                p.data = b.param_data
+            b.release_params(h)
         self.offloaded = True
 
     def onload(self) -> None:
         if self.ddp is None or not self.offloaded:
             return
         for b, h in zip(self.ddp.buffers, self.host):
-            b.param_data = torch.empty(b.numel, dtype=b.param_dtype, device=b.device)
-            b.param_data.copy_(h, non_blocking=True)
-            grads = b.grad_data
-            b.rebind()
-            b.grad_data = grads
+            b.restore_params(h)
         self.offloaded = False
 
 

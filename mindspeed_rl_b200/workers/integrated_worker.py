@@ -72,6 +72,10 @@ class IntegratedWorker(BaseWorker):
                 or os.environ.get("MSRL_SYMM", "1") != "1"):
             return
         n = sum(p.numel() for p in core.parameters())
+        gc = self.generate_config
+        # buffers that the rollout phase frees get peer-mapped segments of their own, not arena space
+        per_elem = (0 if getattr(gc, "offload_train_param", False) else 2) + \
+                   (0 if getattr(gc, "offload_train_grad", False) else (4 if grads_fp32 else 2))
         extra = 0
         m_local = self._fused_tp_rows()
         if m_local:
@@ -80,7 +84,7 @@ class IntegratedWorker(BaseWorker):
         extra += self._moe_p2p_bytes()
         from ..parallel.symm import ArenaUnavailable
         try:
-            init_arena(int(n * (2 + (4 if grads_fp32 else 2)) * 1.02) + (64 << 20) + extra,
+            init_arena(int(n * per_elem * 1.02) + (64 << 20) + extra,
                        group=self.parallel_state.group("all"), device=self.device)
         except ArenaUnavailable as e:
             # raised on every rank together: the job carries on with NCCL collectives and gathered resharding
@@ -173,8 +177,12 @@ class IntegratedWorker(BaseWorker):
                     layer.mlp.collect_rollout_counts = True
         dp = ps.size("dp_cp")
         self._maybe_init_arena(core, bool(ac.accumulate_allreduce_grads_in_fp32))
+        gc = self.generate_config
         self.model = DistributedDataParallel(core, ps.group("dp_cp"), dp,
                                              grad_in_fp32=bool(ac.accumulate_allreduce_grads_in_fp32),
+                                             releasable_params=bool(getattr(gc, "offload_train_param", False)),
+                                             releasable_grads=bool(getattr(gc, "offload_train_grad", False)),
+                                             releasable_experts=ps.size("pp") == 1,
                                              **expert_replica_groups(ps, tcfg))
         self._maybe_attach_fused_tp()
         self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(ac.sequence_parallel))

@@ -363,6 +363,58 @@ def case_cp_ring(rank, world):
             (n, (gr / world - ref).abs().max().item(), ref.abs().max().item())
 
 
+def case_buffer_release(rank, world):
+    """Flat buffers with peer-mapped segments of their own: the pull-kernel reduce-scatter / all-gather work
+    on them, releasing them gives the memory back to the device, and after restoring them the parameters are
+    intact and the collectives work again."""
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.symm import init_arena
+    from mindspeed_rl_b200.reshard.sharding_manager import GradBufferOffloader, ParamOffloader
+
+    init_arena(32 << 20)
+    torch.manual_seed(5)
+    net = torch.nn.Sequential(torch.nn.Linear(4096, 4096, bias=False), torch.nn.Linear(4096, 2048, bias=False))
+    net = net.to("cuda", torch.bfloat16)
+    ddp = DistributedDataParallel(net, dist.group.WORLD, world, releasable_params=True, releasable_grads=True)
+    buf = ddp.buffers[0]
+    assert buf._own == {"param": True, "grad": True} and buf.param_arena is not buf.grad_arena
+    want_params = buf.param_data.clone()
+
+    def reduce_and_check(seed):
+        g = torch.Generator(device="cuda").manual_seed(seed + rank)
+        buf.grad_data.copy_(torch.randn(buf.numel, device="cuda", generator=g))
+        ref = buf.grad_data.float().clone()
+        dist.all_reduce(ref)
+        ddp.finish_grad_sync(to_shards=True)
+        buf.grad_arena.check()
+        s, e = buf.shard_range()
+        assert torch.allclose(buf.grad_data[s:e].float(), ref[s:e] / world, atol=2e-2, rtol=2e-2)
+
+    reduce_and_check(10)
+    grads, params = GradBufferOffloader(ddp), ParamOffloader(ddp)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    grads.release()
+    params.offload()
+    torch.cuda.synchronize()
+    free1 = torch.cuda.mem_get_info()[0]
+    assert free1 - free0 >= 2 * buf.numel * 2 - (8 << 20), (free0, free1)      # both 48 MB buffers went back
+    assert buf.grad_data.numel() == 0 and buf.param_data.numel() == 0 and net[0].weight.main_grad is None
+    params.onload()
+    grads.restore()
+    assert buf.param_arena is not None and buf.grad_arena is not None
+    assert torch.equal(buf.param_data, want_params) and net[0].weight.data_ptr() == buf.param_data.data_ptr()
+    reduce_and_check(20)
+    # parameter all-gather on the restored segment: every rank rewrites its own shard, all see all shards
+    s, e = buf.shard_range()
+    buf.param_data[s:e].fill_(float(rank + 1))
+    buf.gather_params()
+    buf.param_arena.check()
+    per = buf.numel // world
+    for r in range(world):
+        assert torch.all(buf.param_data[r * per:(r + 1) * per].float() == float(r + 1))
+
+
 def case_arena_fallback(rank, world):
     """One rank cannot allocate its arena (it asks for far more than the device has; the allocation
     call returns an error code): every rank gets the same exception, nobody is left waiting in a
@@ -383,7 +435,7 @@ def case_arena_fallback(rank, world):
     assert float(x[0]) == rank + 1
 
 
-CASES = {"peer_all_reduce": case_peer_all_reduce, "arena_fallback": case_arena_fallback, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+CASES = {"peer_all_reduce": case_peer_all_reduce, "buffer_release": case_buffer_release, "arena_fallback": case_arena_fallback, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

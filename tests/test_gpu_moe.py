@@ -80,7 +80,7 @@ def test_peer_memory_dispatch_overflow_falls_back():
     from mindspeed_rl_b200.parallel.symm import SymmetricArena
     torch.manual_seed(4)
     t, k, e, h = 400, 4, 8, 128
-    rows = 512                                            # far below the t * k = 1600 rows this routing needs
+    rows = 1024                                           # the routing below needs 8 experts x 256 padded rows
     arena = SymmetricArena(2 * P2PDispatcher.bytes_needed(1, e, h, rows) + (4 << 20))
     try:
         x = torch.randn(t, h, device="cuda").bfloat16()
@@ -88,7 +88,7 @@ def test_peer_memory_dispatch_overflow_falls_back():
         soft = P2PDispatcher(arena, [0], e, h, rows, fallback=True)
         assert soft.dispatch(x, idx) is None and soft.overflows == 1
         arena.check()                                     # nothing recorded
-        small = idx[:64]                                  # 256 rows + padding fit
+        small = idx[:64]                                  # 8 experts x 128 padded rows fit exactly
         assert soft.dispatch(x[:64], small) is not None and soft.overflows == 1
         hard = P2PDispatcher(arena, [0], e, h, rows, fallback=False)
         hard.dispatch(x, idx)

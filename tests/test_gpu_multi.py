@@ -85,3 +85,8 @@ def test_peer_memory_all_reduce_for_decode():
     _run("peer_all_reduce", 2)
     if _n_gpus() >= 4:
         _run("peer_all_reduce", 4)
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_releasable_peer_mapped_buffers():
+    _run("buffer_release", 2)

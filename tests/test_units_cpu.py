@@ -284,3 +284,28 @@ def test_pack_tokens_and_unpack_response_reference_path():
         start = int(cu[b]) + int(p_len[b]) - 1
         want = [float(src[start + j]) if j < int(r_len[b]) else 0.0 for j in range(6)]
         assert out[b].tolist() == want
+
+
+def test_flat_buffers_release_and_restore_plain_allocations():
+    """Without peer-mapped memory the offloaders free plain allocations: gradients come back zeroed,
+    parameters come back from the pinned-host twin, and the parameters point at the new storage."""
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.reshard.sharding_manager import GradBufferOffloader, ParamOffloader
+
+    torch.manual_seed(0)
+    net = torch.nn.Linear(16, 8)
+    ddp = DistributedDataParallel(net, None, 1, releasable_params=True, releasable_grads=True)
+    buf = ddp.buffers[0]
+    assert buf.arena is None and buf._own == {"param": False, "grad": False}
+    want = buf.param_data.clone()
+    net.weight.main_grad.fill_(3.0)
+    grads, params = GradBufferOffloader(ddp), ParamOffloader(ddp)
+    grads.release()
+    params.offload()
+    assert buf.grad_data.numel() == 0 and buf.param_data.numel() == 0 and net.weight.main_grad is None
+    params.onload()
+    grads.restore()
+    assert torch.equal(buf.param_data, want) and float(buf.grad_data.abs().sum()) == 0.0
+    assert net.weight.data_ptr() == buf.param_data.data_ptr() and net.weight.main_grad.shape == net.weight.shape
+    grads.restore()        # idempotent
+    params.onload()
