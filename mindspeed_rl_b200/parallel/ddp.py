@@ -41,7 +41,8 @@ class ParamAndGradBuffer:
     def __init__(self, named_params: Iterable[Tuple[str, nn.Parameter]], dp_size: int = 1,
                  grad_dtype: Optional[torch.dtype] = None, bucket_numel: Optional[int] = None,
                  group=None, dp_rank: Optional[int] = None, grad_scale: Optional[float] = None,
-                 is_expert: bool = False, releasable_params: bool = False, releasable_grads: bool = False):
+                 is_expert: bool = False, releasable_params: bool = False, releasable_grads: bool = False,
+                 with_grads: bool = True):
         # ``group`` / ``dp_rank`` / ``dp_size``: the ranks that hold replicas of these parameters.
         # Dense parameters are replicated over the whole data-parallel group; expert parameters
         # only over the expert-data-parallel group (the EP ranks hold different experts), but their
@@ -50,7 +51,10 @@ class ParamAndGradBuffer:
         self.dp_rank = dp_rank if dp_rank is not None else (
             dist.get_rank(group) if (group is not None and dist.is_initialized()) else 0)
         self.grad_scale = grad_scale if grad_scale is not None else 1.0 / max(dp_size, 1)
-        params = [(n, p) for n, p in named_params if p.requires_grad]
+        # ``with_grads=False``: a parameter-only buffer for frozen weights (the base weights under LoRA), so
+        # that they too sit in peer-mapped memory where the rollout resharding can read them
+        self.with_grads = with_grads
+        params = [(n, p) for n, p in named_params if p.requires_grad or not with_grads]
         if not params:
             raise ValueError("no trainable parameters")
         self.param_dtype = params[0][1].dtype
@@ -84,24 +88,27 @@ class ParamAndGradBuffer:
                 if releasable_params:
                     self.param_arena = self._segment(p_bytes)
                     self._own["param"] = self.param_arena is not None
-                if releasable_grads:
+                if releasable_grads and with_grads:
                     self.grad_arena = self._segment(g_bytes)
                     self._own["grad"] = self.grad_arena is not None
-                shared = (0 if releasable_params else p_bytes) + (0 if releasable_grads else g_bytes)
+                want_g = with_grads and not releasable_grads
+                shared = (0 if releasable_params else p_bytes) + (g_bytes if want_g else 0)
                 if shared and arena.free_bytes() >= shared:
                     if not releasable_params:
                         self.param_arena = arena
-                    if not releasable_grads:
+                    if want_g:
                         self.grad_arena = arena
         self.param_data = self._new_flat(self.param_arena, self.param_dtype)
-        self.grad_data = self._new_flat(self.grad_arena, self.grad_dtype)
+        self.grad_data = self._new_flat(self.grad_arena, self.grad_dtype) if with_grads else \
+            torch.empty(0, dtype=self.grad_dtype, device=self.device)
         self.params: List[nn.Parameter] = []
         for (n, p), slot in zip(params, self.slots):
             view = self.param_data[slot.start:slot.start + slot.numel].view(slot.shape)
             view.copy_(p.data)
             p.data = view
-            p.main_grad = self.grad_data[slot.start:slot.start + slot.numel].view(slot.shape)
-            p.grad = None
+            if with_grads:
+                p.main_grad = self.grad_data[slot.start:slot.start + slot.numel].view(slot.shape)
+                p.grad = None
             self.params.append(p)
         self.by_name: Dict[str, ParamSlot] = {s.name: s for s in self.slots}
 
@@ -253,7 +260,7 @@ class DistributedDataParallel(nn.Module):
                  grad_in_fp32: bool = False, bucket_numel: Optional[int] = None,
                  expert_dp_group=None, expert_dp_size: Optional[int] = None,
                  expert_dp_rank: Optional[int] = None, releasable_params: bool = False,
-                 releasable_grads: bool = False, releasable_experts: bool = True):
+                 releasable_grads: bool = False, releasable_experts: bool = True, frozen_buffer: bool = False):
         """``expert_dp_*`` describe the ranks that hold replicas of this rank's experts (Megatron's
         expert-data-parallel group).  When given, the expert weights get a buffer of their own that
         is reduced, sharded (optimizer state) and gathered over that group only; without it
@@ -264,7 +271,8 @@ class DistributedDataParallel(nn.Module):
         co-located rollout can free and map again (``offload_train_param`` / ``offload_train_grad``);
         creating, freeing and re-creating a segment are collective over the arena's team, so every rank
         of the team must hold the same buffers (``releasable_experts=False`` leaves the expert buffer in
-        the arena where pipeline stages differ in whether they have experts)."""
+        the arena where pipeline stages differ in whether they have experts).  ``frozen_buffer``: also
+        flatten the parameters that do not train (see ``frozen_buffer`` below)."""
         super().__init__()
         self.module = module
         self.dp_group, self.dp_size = dp_group, dp_size
@@ -292,6 +300,15 @@ class DistributedDataParallel(nn.Module):
         if fp32_params:  # e.g. the fp32 value head
             self.buffers.append(ParamAndGradBuffer(fp32_params, dp_size, torch.float32, bucket_numel,
                                                    group=dp_group))
+        # frozen weights of a partly trainable model (base weights under LoRA): one parameter-only flat
+        # buffer, outside ``buffers`` (no gradients, no optimizer state, nothing to reduce or gather)
+        self.frozen_buffer: Optional[ParamAndGradBuffer] = None
+        if frozen_buffer and main:
+            dt = main[0][1].dtype
+            frozen = [(n, p) for n, p in module.named_parameters() if not p.requires_grad and p.dtype == dt]
+            if frozen:
+                self.frozen_buffer = ParamAndGradBuffer(frozen, dp_size, None, bucket_numel, group=dp_group,
+                                                        with_grads=False)
 
     def forward(self, *a, **kw):
         return self.module(*a, **kw)

@@ -21,6 +21,16 @@ Here the move is planned once on the host and executed by one kernel per reshard
 Fused-QKV needs no un-interleaving: the training layout groups ``[q.. k v]`` per KV group, a row
 split by KV group is therefore a contiguous row range, and the rollout kernels read that layout
 directly.
+
+Routed experts move through the same plan when the rollout's expert layout differs from training
+(``ExpertPlacement``): a rollout rank lists the logical experts it hosts (its share of an
+``infer_expert_parallel_size``-way split, or the entry of an expert-load-balancing map, which may
+host an expert on several ranks) and the plan pulls each expert's ``[gate | up]`` column block and
+its down-projection rows from the training rank that owns it (reference: EP -> TP conversion, EP
+growth, expert send / receive and redundant experts in ``vllm_weight_container.py:226-266,336-420,
+487-588``).  Low-rank adapters travel as ordinary tensors (``B`` cut like the weight's output rows,
+``A`` like its input columns) and are folded into the rollout copy of the weights after the copy,
+``W += (alpha / r) B A``, so the rollout never sees an adapter.
 """
 from __future__ import annotations
 
@@ -45,15 +55,25 @@ _MAX_CHUNK = 64 << 20                              # contiguous copies are cut i
 class Slot:
     start: int            # element offset inside the owning rank's flat parameter buffer
     shape: Tuple[int, ...]
+    buf: int = 0          # which of the rank's flat buffers (0: trainable dense, then experts, frozen)
+
+
+@dataclass
+class ExpertPlacement:
+    """Where the routed experts of the rollout come from."""
+    e_local_train: int                          # experts per training expert-parallel rank
+    hosted: Callable[[int], Sequence[int]]      # global layer number -> logical expert ids this rollout rank hosts
+    src_rank: Callable[[int, int], int]         # (training expert-parallel index, pipeline stage) -> global rank
 
 
 def partition_kind(name: str) -> str:
     """How training tensor parallelism cuts a parameter."""
-    if name.endswith(("linear_qkv.weight", "linear_qkv.bias", "word_embeddings.weight", "output_layer.weight")):
+    if name.endswith(("linear_qkv.weight", "linear_qkv.bias", "word_embeddings.weight", "output_layer.weight",
+                      "linear_qkv.lora_B")):
         return "rows"
-    if name.endswith("linear_fc1.weight"):
+    if name.endswith(("linear_fc1.weight", "linear_fc1.lora_B")):
         return "glu"
-    if name.endswith(("linear_proj.weight", "linear_fc2.weight")):
+    if name.endswith(("linear_proj.weight", "linear_fc2.weight", "linear_proj.lora_A", "linear_fc2.lora_A")):
         return "cols"
     return "local"
 
@@ -142,18 +162,29 @@ class ReshardPlan:
     desc: List[Desc]
     tensors: Dict[str, Tuple[int, Tuple[int, ...]]]   # global name -> (byte offset in dst, shape)
     nbytes: int
+    desc_buf: Optional[List[int]] = None              # source buffer index of every descriptor (None: all 0)
+
+    def buf_of(self, i: int) -> int:
+        return self.desc_buf[i] if self.desc_buf is not None else 0
 
 
 def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: int,
                stage_slots: Sequence[Dict[str, Slot]], layers_of_stage: Sequence[Sequence[int]],
-               src_base: Callable[[int], int], esz: int = 2) -> ReshardPlan:
+               src_base: Callable[..., int], esz: int = 2,
+               experts: Optional[ExpertPlacement] = None) -> ReshardPlan:
     """Plan for global rank ``rank``.
 
     ``stage_slots[s]`` maps the state-dict names of pipeline stage ``s`` (local layer indices) to
-    their slots; ``src_base(r)`` is the byte address offset of rank ``r``'s parameter buffer
-    (arena offset, or 0 when the sources are separate gathered buffers).  Destination names use
-    *global* layer indices.
+    their slots; ``src_base(r, buf)`` is the byte address offset of flat buffer ``buf`` of rank ``r``
+    (arena offset, or 0 when the sources are separate gathered buffers; a one-argument callable is
+    taken to ignore ``buf``).  Destination names use *global* layer indices.  ``experts``: re-home the
+    routed experts (otherwise expert tensors are copied as they are on this rank).
     """
+    import inspect
+
+    if len(inspect.signature(src_base).parameters) == 1:
+        _one = src_base
+        src_base = lambda r, b=0: _one(r)
     tp_t = train.tp
     coords = train.coords(rank)
     j = rank % infer_tp                                   # rollout TP rank (TP is the fastest dim)
@@ -162,8 +193,13 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
         return train.rank_of(tp=tp_idx, pp=stage, dp=coords["dp"], cp=coords["cp"])
 
     desc: List[Desc] = []
+    desc_buf: List[int] = []
     tensors: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
     cursor = 0
+
+    def add(items: List[Desc], buf: int) -> None:
+        desc.extend(items)
+        desc_buf.extend([buf] * len(items))
 
     def place(name: str, shape: Tuple[int, ...]) -> int:
         nonlocal cursor
@@ -186,7 +222,7 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
             # replicated / expert-local tensors and unchanged TP: take this rank's own TP index
             r = src_rank(coords["tp"] if kind == "local" else j, stage)
             dst = place(gname, shape)
-            desc.extend(_contig(r, src_base(r) + slot.start * esz, dst, shape[0] * inner if shape else esz))
+            add(_contig(r, src_base(r, slot.buf) + slot.start * esz, dst, shape[0] * inner if shape else esz), slot.buf)
             return
         if kind == "rows":
             full = shape[0] * tp_t
@@ -194,7 +230,8 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
             dst = place(gname, dshape)
             for s, s0, d0, ln in intervals(full, tp_t, infer_tp, j):
                 r = src_rank(s, stage)
-                desc.extend(_contig(r, src_base(r) + slot.start * esz + s0 * inner, dst + d0 * inner, ln * inner))
+                add(_contig(r, src_base(r, slot.buf) + slot.start * esz + s0 * inner, dst + d0 * inner, ln * inner),
+                    slot.buf)
         elif kind == "glu":
             half_t = shape[0] // 2
             full = half_t * tp_t
@@ -204,8 +241,8 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
             for blk in (0, 1):                            # gate rows, then up rows
                 for s, s0, d0, ln in intervals(full, tp_t, infer_tp, j):
                     r = src_rank(s, stage)
-                    desc.extend(_contig(r, src_base(r) + slot.start * esz + (blk * half_t + s0) * inner,
-                                        dst + (blk * half_i + d0) * inner, ln * inner))
+                    add(_contig(r, src_base(r, slot.buf) + slot.start * esz + (blk * half_t + s0) * inner,
+                                dst + (blk * half_i + d0) * inner, ln * inner), slot.buf)
         elif kind == "cols":
             rows, k_t = shape[0], shape[1]
             full = k_t * tp_t
@@ -213,10 +250,32 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
             dst = place(gname, (rows, k_i))
             for s, s0, d0, ln in intervals(full, tp_t, infer_tp, j):
                 r = src_rank(s, stage)
-                desc.append((r, src_base(r) + slot.start * esz + s0 * esz, dst + d0 * esz, rows, ln * esz,
-                             k_t * esz, k_i * esz))
+                add([(r, src_base(r, slot.buf) + slot.start * esz + s0 * esz, dst + d0 * esz, rows, ln * esz,
+                      k_t * esz, k_i * esz)], slot.buf)
         else:
             raise ValueError(kind)
+
+    def emit_experts(gname: str, lname: str, stage: int, layer: int) -> None:
+        """Gather the hosted experts of ``layer`` from their training owners into rollout slot order."""
+        slot = stage_slots[stage][lname]
+        ids = list(experts.hosted(layer))
+        e_t, n_loc = experts.e_local_train, len(ids)
+        if lname.endswith("experts.weight1"):                # [H, E_local * 2F]: one column block per expert
+            h, cols = slot.shape
+            w = cols // e_t
+            dst = place(gname, (h, n_loc * w))
+            for q, e in enumerate(ids):
+                r = experts.src_rank(e // e_t, stage)
+                add([(r, src_base(r, slot.buf) + (slot.start + (e % e_t) * w) * esz, dst + q * w * esz, h, w * esz,
+                      cols * esz, n_loc * w * esz)], slot.buf)
+        else:                                                # [E_local * F, H]: one block of rows per expert
+            rows, h = slot.shape
+            f = rows // e_t
+            dst = place(gname, (n_loc * f, h))
+            for q, e in enumerate(ids):
+                r = experts.src_rank(e // e_t, stage)
+                add(_contig(r, src_base(r, slot.buf) + (slot.start + (e % e_t) * f * h) * esz, dst + q * f * h * esz,
+                            f * h * esz), slot.buf)
 
     for stage, layer_ids in enumerate(layers_of_stage):
         table = stage_slots[stage]
@@ -225,19 +284,25 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
         for local, layer in enumerate(layer_ids):
             prefix = f"decoder.layers.{local}."
             for lname in table:
-                if lname.startswith(prefix):
-                    emit(f"decoder.layers.{layer}." + lname[len(prefix):], lname, stage)
+                if not lname.startswith(prefix):
+                    continue
+                gname = f"decoder.layers.{layer}." + lname[len(prefix):]
+                if experts is not None and lname.endswith(("experts.weight1", "experts.weight2")):
+                    emit_experts(gname, lname, stage, layer)
+                else:
+                    emit(gname, lname, stage)
         for lname in ("decoder.final_layernorm.weight", "output_layer.weight"):
             if lname in table:
                 emit(lname, lname, stage)
-    return ReshardPlan(desc, tensors, (cursor + 255) // 256 * 256)
+    return ReshardPlan(desc, tensors, (cursor + 255) // 256 * 256, desc_buf if any(desc_buf) else None)
 
 
 def execute_plan_torch(plan: ReshardPlan, sources: Dict[int, torch.Tensor], dst: torch.Tensor) -> None:
     """Reference executor: ``sources[r]`` is rank r's parameter buffer viewed as bytes (uint8),
     ``dst`` the destination bytes.  Used on CPU and as the oracle of the copy-plan kernel."""
-    for src_rank, src_off, dst_off, rows, row_bytes, sp, dp in plan.desc:
-        s = sources[src_rank]
+    for i, (src_rank, src_off, dst_off, rows, row_bytes, sp, dp) in enumerate(plan.desc):
+        b = plan.buf_of(i)
+        s = sources[(src_rank, b)] if (src_rank, b) in sources else sources[src_rank]
         if rows == 1:
             dst[dst_off:dst_off + row_bytes] = s[src_off:src_off + row_bytes]
         else:
@@ -258,9 +323,20 @@ def weights_from_buffer(cfg: TransformerConfig, infer_tp: int, tp_rank: int, pla
             n *= d
         return buf[off:off + n * buf.new_empty(0, dtype=dtype).element_size()].view(dtype).view(shape)
 
+    def fold(prefix: str) -> None:
+        """``W += (alpha / r) B A`` on the rollout copy of an adapted linear (fp32 sum, one rounding)."""
+        a, b, w = t(prefix + ".lora_A"), t(prefix + ".lora_B"), t(prefix + ".weight")
+        if a is None or b is None or w is None:
+            return
+        scale = float(cfg.lora_alpha) / float(cfg.lora_r)
+        w.copy_((w.float() + scale * torch.matmul(b.float(), a.float())).to(w.dtype))
+
     layers = []
     for li in range(cfg.num_layers):
         p = f"decoder.layers.{li}."
+        if getattr(cfg, "lora_r", 0):
+            for holder in ("self_attention.linear_qkv", "self_attention.linear_proj", "mlp.linear_fc1", "mlp.linear_fc2"):
+                fold(p + holder)
         kw = dict(input_norm=t(p + "input_layernorm.weight"), qkv_w=t(p + "self_attention.linear_qkv.weight"),
                   qkv_b=t(p + "self_attention.linear_qkv.bias"), o_w=t(p + "self_attention.linear_proj.weight"),
                   post_norm=t(p + "pre_mlp_layernorm.weight"), q_norm=t(p + "self_attention.q_layernorm.weight"),
@@ -300,23 +376,56 @@ def attach_peer_all_reduce(comm: TPComm, arena, hidden_size: int) -> None:
     comm.peer_ar = arena.make_all_reduce(need, arena.team_ranks(comm.group))
 
 
+def wanted_infer_ep(cfg: TransformerConfig, layout: RankLayout, gc) -> Optional[int]:
+    """Expert-parallel size of the rollout asked for by the generation config, or ``None`` when the
+    experts can stay where training has them (dense model, same size, nothing configured)."""
+    if not cfg.is_moe:
+        return None
+    want = getattr(gc, "infer_expert_parallel_size", None)
+    if not want or int(want) == layout.ep_total:
+        return None
+    return int(want)
+
+
 class Resharder:
     """Owns the rollout-side parallel state, engine and weight buffer of one worker."""
 
     def __init__(self, cfg: TransformerConfig, ddp, train_state: ParallelState, infer_tp: int, device,
                  engine_factory: Callable, arena=None, num_layer_list: Optional[Sequence[int]] = None,
-                 layers_of_stage: Optional[Sequence[Sequence[int]]] = None):
+                 layers_of_stage: Optional[Sequence[Sequence[int]]] = None, infer_ep: Optional[int] = None,
+                 expert_map: Optional[dict] = None):
+        """``infer_ep``: expert-parallel size of the rollout (``None``: the experts stay where training has
+        them); ``expert_map``: placement produced by the expert-load balancer (``rollout.eplb.
+        expert_map_from_counts``: per MoE layer and rollout expert-parallel rank the logical experts it
+        hosts, possibly with replicas)."""
         self.cfg, self.ddp, self.train_state, self.infer_tp = cfg, ddp, train_state, infer_tp
         self.device = torch.device(device)
         self.arena = arena
         layout = train_state.layout
         if layout.world_size % infer_tp:
             raise ValueError("the rollout TP size must divide the world size")
-        if cfg.is_moe and layout.ep > 1 and (layout.pp > 1 or getattr(layout, "expert_tp", 1) > 1):
-            raise NotImplementedError("with expert parallelism the experts stay on their training ranks: only the "
-                                      "dense tensors are resharded, which needs pp = 1 and unsplit experts")
-        self.infer_state = ParallelState(RankLayout(layout.world_size, tp=infer_tp), train_state.rank,
-                                         backend=train_state.backend, rank_offset=train_state.rank_offset)
+        self.expert_map = expert_map
+        self.infer_ep = layout.ep_total if (infer_ep is None or not cfg.is_moe) else int(infer_ep)
+        # the experts move when the rollout wants another expert layout than training has
+        self.rehome = bool(cfg.is_moe and (self.infer_ep != layout.ep_total or expert_map is not None
+                                           or (layout.pp > 1 and layout.ep_total > 1)))
+        if cfg.is_moe and layout.ep_total > 1 and layout.expert_tp > 1:
+            raise NotImplementedError("experts that training splits over tensor-parallel ranks cannot be resharded; "
+                                      "use moe_tp_extend_ep or tensor_model_parallel_size = 1 for expert models")
+        if self.rehome and layout.pp > 1 and getattr(cfg, "moe_router_enable_expert_bias", False):
+            raise NotImplementedError("the routers' selection bias lives on the stage that owns the layer: re-homing "
+                                      "experts across pipeline stages is not supported with aux-loss-free balancing")
+        if self.rehome:
+            n_phys = self._physical_experts()
+            if n_phys % self.infer_ep or layout.world_size % (infer_tp * self.infer_ep):
+                raise ValueError(f"{n_phys} rollout expert slots / {layout.world_size} ranks do not divide into "
+                                 f"tp {infer_tp} x ep {self.infer_ep}")
+            self.infer_state = ParallelState(RankLayout(layout.world_size, tp=infer_tp, ep=self.infer_ep),
+                                             train_state.rank, backend=train_state.backend,
+                                             rank_offset=train_state.rank_offset)
+        else:
+            self.infer_state = ParallelState(RankLayout(layout.world_size, tp=infer_tp), train_state.rank,
+                                             backend=train_state.backend, rank_offset=train_state.rank_offset)
         tp_group = self.infer_state.group("tp")
         self.comm = TPComm(tp_group, False, world_size=infer_tp, rank=self.infer_state.rank_in("tp"))
         attach_peer_all_reduce(self.comm, arena, cfg.hidden_size)
@@ -334,66 +443,190 @@ class Resharder:
         from ..parallel.symm import get_arena
         from ..rollout.engine import LLMEngine
 
+        expert_map = None
+        if worker.tcfg.is_moe and getattr(gc, "expert_map_path", None):
+            import json
+
+            with open(gc.expert_map_path) as fh:
+                expert_map = json.load(fh)
+        infer_ep = wanted_infer_ep(worker.tcfg, worker.parallel_state.layout, gc)
+        holder = {}
+
         def factory(icfg, comm):
+            # the engines of one rollout expert-parallel group exchange tokens in every forward: they
+            # step together (the group is known once the rollout state exists)
             return LLMEngine(icfg, worker.device, max_num_seqs=gc.max_num_seqs,
                              max_num_batched_tokens=gc.max_num_batched_tokens, max_model_len=gc.max_model_len,
                              block_size=gc.kv_block_size, enable_prefix_caching=gc.enable_prefix_caching,
                              enforce_eager=gc.enforce_eager, graph_batch_sizes=tuple(gc.graph_batch_sizes),
                              eos_token_id=worker.eos_token_id, pad_token_id=worker.pad_token_id, comm=comm,
-                             seed=worker.seed,
-                             lockstep_group=worker.parallel_state.group("ep")
-                             if (worker.tcfg.is_moe and worker.parallel_state.size("ep") > 1) else None)
+                             seed=worker.seed, lockstep_group=holder["self"]._lockstep_group())
 
-        return cls(worker.tcfg, worker.model, worker.parallel_state, gc.infer_tensor_parallel_size, worker.device,
-                   factory, arena=get_arena(),
-                   layers_of_stage=[sum(ch, []) for ch in
-                                    pipeline_layout(worker.actor_config, worker.parallel_state.size("pp"))])
+        self = cls.__new__(cls)
+        holder["self"] = self
+        self.__init__(worker.tcfg, worker.model, worker.parallel_state, gc.infer_tensor_parallel_size, worker.device,
+                      factory, arena=get_arena(),
+                      layers_of_stage=[sum(ch, []) for ch in
+                                       pipeline_layout(worker.actor_config, worker.parallel_state.size("pp"))],
+                      infer_ep=infer_ep, expert_map=expert_map)
+        return self
+
+    def _lockstep_group(self):
+        if not self.cfg.is_moe:
+            return None
+        if self.rehome:
+            return self.infer_state.group("ep") if self.infer_ep > 1 else None
+        return self.train_state.group("ep") if self.train_state.size("ep") > 1 else None
+
+    # ---- expert placement ------------------------------------------------------------------------
+    def _physical_experts(self) -> int:
+        """Expert slots of the rollout over all its expert-parallel ranks (logical experts + replicas)."""
+        if self.expert_map is None:
+            return self.cfg.num_experts
+        first = self.expert_map["layer_list"][0]
+        if first["device_count"] != self.infer_ep:
+            raise ValueError(f"the expert map places experts on {first['device_count']} devices, the rollout has "
+                             f"{self.infer_ep} expert-parallel ranks")
+        return sum(len(d["device_expert"]) for d in first["device_list"])
+
+    def _moe_index(self, layer: int) -> int:
+        return sum(1 for i in range(layer) if self.cfg.layer_is_moe(i))
+
+    def hosted_experts(self, layer: int, ep_rank: Optional[int] = None) -> List[int]:
+        """Logical ids of the experts that rollout expert-parallel rank ``ep_rank`` (default: this rank's)
+        hosts for ``layer``, in slot order."""
+        ei = self.infer_state.rank_in("ep") if ep_rank is None else ep_rank
+        if self.expert_map is not None:
+            entry = self.expert_map["layer_list"][self._moe_index(layer)]
+            return list(entry["device_list"][ei]["device_expert"])
+        n_loc = self.cfg.num_experts // self.infer_ep
+        return list(range(ei * n_loc, (ei + 1) * n_loc))
+
+    def log2phy(self, layer: int) -> Optional[torch.Tensor]:
+        """``[E, max_replicas]`` physical slot ids of every logical expert (-1 padded), or ``None`` when
+        slot ``i`` simply holds expert ``i``."""
+        if self.expert_map is None:
+            return None
+        where: List[List[int]] = [[] for _ in range(self.cfg.num_experts)]
+        slot = 0
+        for ei in range(self.infer_ep):
+            for e in self.hosted_experts(layer, ei):
+                where[e].append(slot)
+                slot += 1
+        if any(not w for w in where):
+            raise ValueError(f"the expert map hosts no copy of some expert of layer {layer}")
+        width = max(len(w) for w in where)
+        return torch.tensor([w + [-1] * (width - len(w)) for w in where], dtype=torch.int64)
+
+    def _expert_placement(self) -> Optional[ExpertPlacement]:
+        if not self.rehome:
+            return None
+        layout, me = self.train_state.layout, self.train_state.rank
+        mine = layout.expert_coords(me)
+
+        def src_rank(ep_index: int, stage: int) -> int:
+            # the training rank of my own expert-data-parallel replica that owns this expert shard
+            stage_rank = mine["etp"] + layout.expert_tp * (ep_index + layout.ep_total * mine["edp"])
+            tp = stage_rank % layout.tp
+            cp = (stage_rank // layout.tp) % layout.cp
+            dp = stage_rank // (layout.tp * layout.cp)
+            return layout.rank_of(tp=tp, cp=cp, dp=dp, pp=stage)
+
+        return ExpertPlacement(self.cfg.num_experts // layout.ep_total, self.hosted_experts, src_rank)
 
     # ------------------------------------------------------------------------------------------
     def _main_buffer(self):
         return self.ddp.buffers[0]
 
-    def _param_arena(self):
-        """The peer-mapped home of the training parameters (the job-wide arena or the buffer's own
-        segment), or ``None`` when they are a plain allocation."""
-        return getattr(self._main_buffer(), "param_arena", None) if self.arena is not None else None
+    def _source_buffers(self) -> list:
+        """The flat buffers that hold rollout-relevant parameters, in ``Slot.buf`` order: the trainable
+        bf16 buffers (dense, then experts) and the frozen one (base weights under LoRA)."""
+        dt = self._main_buffer().param_dtype
+        out = [b for b in self.ddp.buffers if b.param_dtype == dt]
+        frozen = getattr(self.ddp, "frozen_buffer", None)
+        if frozen is not None:
+            out.append(frozen)
+        return out
+
+    def _home(self, buf):
+        """Peer-mapped home of a flat buffer (the job-wide arena or the buffer's own segment), or
+        ``None`` when it is a plain allocation."""
+        return getattr(buf, "param_arena", None) if self.arena is not None else None
 
     def _use_arena(self) -> bool:
-        return self._param_arena() is not None
+        return all(self._home(b) is not None for b in self._source_buffers())
 
     def _build(self) -> None:
         ps = self.train_state
-        buf = self._main_buffer()
-        mine = {s.name: Slot(s.start, tuple(s.shape)) for s in buf.slots}
-        base = self._param_arena().offset_of(buf.param_data) if self._use_arena() else 0
+        bufs = self._source_buffers()
+        mine: Dict[str, Slot] = {}
+        for bi, b in enumerate(bufs):
+            for sl in b.slots:
+                mine[sl.name] = Slot(sl.start, tuple(sl.shape), bi)
+        use_arena = self._use_arena()
+        bases = [self._home(b).offset_of(b.param_data) if use_arena else 0 for b in bufs]
         stage = ps.rank_in("pp")
-        info = (ps.rank, stage, base, mine if ps.rank_in("tp") == 0 else None)
-        if dist.is_initialized() and ps.size("mp") > 1:
-            box: List = [None] * ps.size("mp")
-            dist.all_gather_object(box, info, group=ps.group("mp"))
+        # expert sources sit on other data-parallel ranks: their buffer offsets are needed too
+        group_name = "all" if self.rehome else "mp"
+        # the slot tables are the same on all tensor- and data-parallel ranks of a stage: one sender each
+        sender = ps.rank_in("tp") == 0 and (not self.rehome or ps.rank_in("dp_cp") == 0)
+        info = (ps.rank, stage, bases, mine if sender else None)
+        if dist.is_initialized() and ps.size(group_name) > 1:
+            box: List = [None] * ps.size(group_name)
+            dist.all_gather_object(box, info, group=ps.group(group_name))
         else:
             box = [info]
         tables: List[Optional[Dict[str, Slot]]] = [None] * ps.size("pp")
-        bases: Dict[int, int] = {}
+        all_bases: Dict[int, List[int]] = {}
         for r, st, b, table in box:
-            bases[r] = b
+            all_bases[r] = b
             if table is not None:
                 tables[st] = table
-        if self._use_arena():
-            # arena ranks are positions in the arena's team; the team is the whole job here
-            src_base = lambda r: bases[r]
-        else:
-            src_base = lambda r: 0
-        esz = buf.param_data.element_size()
-        self._plan = build_plan(self.cfg, ps.layout, self.infer_tp, ps.rank, tables, self._layers, src_base, esz)
-        if self._use_arena():
+        src_base = (lambda r, buf=0: all_bases[r][buf]) if use_arena else (lambda r, buf=0: 0)
+        esz = bufs[0].param_data.element_size()
+        self._plan = build_plan(self.cfg, ps.layout, self.infer_tp, ps.rank, tables, self._layers, src_base, esz,
+                                experts=self._expert_placement())
+        if use_arena:
             from ..parallel.symm import plan_to_device
 
-            self._plan_dev = plan_to_device(self._plan.desc, self.device)
+            # one launch per peer-mapped home: buffers inside the job-wide arena share one, a buffer
+            # with a segment of its own is read through that segment's peer pointers
+            groups: Dict[int, List[Desc]] = {}
+            for i, d in enumerate(self._plan.desc):
+                groups.setdefault(self._plan.buf_of(i), []).append(d)
+            merged: Dict[int, Tuple[int, List[Desc]]] = {}
+            for bi, descs in sorted(groups.items()):
+                key = id(self._home(bufs[bi]))
+                merged.setdefault(key, (bi, []))[1].extend(descs)
+            self._plan_dev = [(bi, plan_to_device(descs, self.device)) for bi, descs in merged.values()]
 
     def _moe_builder(self, core):
+        if not self.rehome:
+            def build(li, t):
+                return core.decoder.layers[li].mlp.rollout_view()
+            return build
+
+        from ..rollout.moe import MoEWeights
+
+        cfg = self.cfg
+        h, f = cfg.hidden_size, cfg.moe_ffn_hidden_size
+        ep_group = self.infer_state.group("ep") if self.infer_ep > 1 else None
+
         def build(li, t):
-            return core.decoder.layers[li].mlp.rollout_view()
+            p = f"decoder.layers.{li}.mlp."
+            n_loc = len(self.hosted_experts(li))
+            numbers = list(core.layer_numbers)
+            layer = core.decoder.layers[numbers.index(li)].mlp if li in numbers else None
+            shared = None
+            if t(p + "shared_experts.linear_fc1.weight") is not None:
+                shared = (t(p + "shared_experts.linear_fc1.weight"), t(p + "shared_experts.linear_fc2.weight"))
+            bias = getattr(getattr(layer, "router", None), "expert_bias", None) if layer is not None else None
+            table = self.log2phy(li)
+            return MoEWeights(cfg, t(p + "router.weight"), t(p + "experts.weight1").view(h, n_loc, 2 * f),
+                              t(p + "experts.weight2").view(n_loc, f, h), ep_group, self.infer_ep,
+                              self.infer_state.rank_in("ep") if self.infer_ep > 1 else 0, shared=shared,
+                              log2phy=table.to(self.device) if table is not None else None, expert_bias=bias,
+                              collect_counts=bool(getattr(layer, "collect_rollout_counts", False)))
         return build
 
     @torch.no_grad()
@@ -401,7 +634,7 @@ class Resharder:
         if self._plan is None:
             self._build()
         plan = self._plan
-        buf = self._main_buffer()
+        bufs = self._source_buffers()
         if self.buffer is None:
             self.buffer = torch.empty(plan.nbytes, dtype=torch.uint8, device=self.device)
         timed = self.device.type == "cuda"
@@ -413,35 +646,39 @@ class Resharder:
         if self._use_arena():
             # the ranks arrive from the update stage at different times: line them up before the
             # bounded device barrier (outside the timed interval: it is waiting, not resharding)
-            home = self._param_arena()
-            home.align()
+            self._home(bufs[0]).align()
             if timed:
                 self._events[0].record()
-            home.copy_plan(self._plan_dev[0], self._plan_dev[1], self.buffer, sync=True)
+            for bi, dev_plan in self._plan_dev:
+                self._home(bufs[bi]).copy_plan(dev_plan[0], dev_plan[1], self.buffer, sync=True)
         else:
-            self._gathered_copy(plan, buf)
+            self._gathered_copy(plan, bufs)
         if timed:
             self._events[1].record()
         self.last_bytes = sum(d[3] * d[4] for d in plan.desc)
         return weights_from_buffer(self.infer_cfg, self.infer_tp, self.infer_state.rank_in("tp"), plan, self.buffer,
-                                   buf.param_dtype, self._moe_builder(core) if self.cfg.is_moe else None)
+                                   bufs[0].param_dtype, self._moe_builder(core) if self.cfg.is_moe else None)
 
-    def _gathered_copy(self, plan: ReshardPlan, buf) -> None:
-        """Library fallback: all-gather the parameter buffers of the model-parallel group, then
-        run the plan locally."""
+    def _gathered_copy(self, plan: ReshardPlan, bufs) -> None:
+        """Library fallback: all-gather the parameter buffers of the ranks that hold sources (the
+        model-parallel group; every rank of the job when experts move), then run the plan locally."""
         ps = self.train_state
-        local = buf.param_data.view(torch.uint8)
-        if dist.is_initialized() and ps.size("mp") > 1:
-            sizes = [None] * ps.size("mp")
-            dist.all_gather_object(sizes, int(local.numel()), group=ps.group("mp"))
-            cap = max(sizes)
-            padded = torch.zeros(cap, dtype=torch.uint8, device=local.device)
-            padded[:local.numel()] = local
-            got = [torch.empty_like(padded) for _ in sizes]
-            dist.all_gather(got, padded, group=ps.group("mp"))
-            sources = {r: g for r, g in zip(ps.ranks("mp"), got)}
+        group_name = "all" if self.rehome else "mp"
+        local = [b.param_data.view(torch.uint8) for b in bufs]
+        if dist.is_initialized() and ps.size(group_name) > 1:
+            sources = {}
+            for bi, loc in enumerate(local):
+                sizes = [None] * ps.size(group_name)
+                dist.all_gather_object(sizes, int(loc.numel()), group=ps.group(group_name))
+                cap = max(sizes)
+                padded = torch.zeros(cap, dtype=torch.uint8, device=loc.device)
+                padded[:loc.numel()] = loc
+                got = [torch.empty_like(padded) for _ in sizes]
+                dist.all_gather(got, padded, group=ps.group(group_name))
+                for r, g in zip(ps.ranks(group_name), got):
+                    sources[(r, bi)] = g
         else:
-            sources = {ps.rank: local}
+            sources = {(ps.rank, bi): loc for bi, loc in enumerate(local)}
         execute_plan_torch(plan, sources, self.buffer)
 
     def device_ms(self) -> Optional[float]:

@@ -183,6 +183,7 @@ class IntegratedWorker(BaseWorker):
                                              releasable_params=bool(getattr(gc, "offload_train_param", False)),
                                              releasable_grads=bool(getattr(gc, "offload_train_grad", False)),
                                              releasable_experts=ps.size("pp") == 1,
+                                             frozen_buffer=tcfg.lora_r > 0,
                                              **expert_replica_groups(ps, tcfg))
         self._maybe_attach_fused_tp()
         self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(ac.sequence_parallel))
@@ -244,12 +245,19 @@ class IntegratedWorker(BaseWorker):
             # expert-parallel replicas exchange tokens in every forward: their engines step together
             lockstep_group=ps.group("ep") if (tcfg.is_moe and ps.size("ep") > 1) else None)
         resharder = None
-        if not (gc.infer_tensor_parallel_size != tp or ps.size("pp") > 1) and tp > 1:
+        from ..reshard.planner import wanted_infer_ep
+
+        # the rollout needs its own copy of the weights when its layout differs from training's: another
+        # TP size, pipeline stages to gather, another expert-parallel size or an expert placement map
+        move = (gc.infer_tensor_parallel_size != tp or ps.size("pp") > 1
+                or wanted_infer_ep(tcfg, ps.layout, gc) is not None
+                or (tcfg.is_moe and bool(getattr(gc, "expert_map_path", None))))
+        if not move and tp > 1:
             from ..parallel.symm import get_arena
             from ..reshard.planner import attach_peer_all_reduce
 
             attach_peer_all_reduce(self.comm, get_arena(), tcfg.hidden_size)   # rollout shares the training TP group
-        if gc.infer_tensor_parallel_size != tp or ps.size("pp") > 1:
+        if move:
             from ..reshard.planner import Resharder
 
             resharder = Resharder.for_worker(self, gc)

@@ -50,3 +50,10 @@ def test_bench_reference_arm_reports_unavailable():
                          capture_output=True, text=True, timeout=120, cwd=ROOT)
     out = json.loads(res.stdout.strip().splitlines()[-1])
     assert res.returncode == 0 and out["impl"] == "reference" and "unavailable" in out
+
+
+def test_bench_baseline_layout_eight_ranks():
+    """The headline layout of the 8-GPU run: training TP4 x DP2 resharded to rollout TP2 x DP4 every step."""
+    out = _bench(8, "--steps", "1", "--warmup", "1", "--model-override", "num_query_groups=4")
+    assert out["n_gpus"] == 8 and out["config"]["train_tp"] == 4 and out["config"]["rollout_tp"] == 2
+    assert out["config"]["parallelism"].startswith("train tp4 x dp2") and out["value"] > 0

@@ -311,6 +311,73 @@ def test_expert_parallel_rollout_steps_together():
     run_distributed(_ep_rollout_worker, 2)
 
 
+def _ep_rehome_worker(rank, world):
+    """Training EP2 (x expert-DP2) on four ranks; the rollout re-homes the experts to EP4, to one full copy per
+    rank (EP1), and to an EP2 placement with a redundant expert slot per rank: greedy tokens always equal the
+    single-rank model's."""
+    from mindspeed_rl_b200.models.gpt import GPTModel
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel, expert_replica_groups
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel, set_parallel_state
+    from mindspeed_rl_b200.reshard.alias import alias_rollout_weights
+    from mindspeed_rl_b200.reshard.planner import Resharder
+    from mindspeed_rl_b200.rollout.engine import LLMEngine
+    from mindspeed_rl_b200.rollout.eplb import expert_map_from_counts
+    from mindspeed_rl_b200.rollout.scheduler import SamplingParams
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, params_dtype=torch.float32, max_position_embeddings=64, num_experts=4,
+              moe_router_topk=2, moe_ffn_hidden_size=16, norm_topk_prob=True, moe_aux_loss_coeff=0.0)
+    set_parallel_state(None)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=3)
+    for p in full.parameters():
+        p.data.mul_(3.0)
+    ps = initialize_model_parallel(expert_model_parallel_size=2)
+    cfg = TransformerConfig(expert_model_parallel_size=2, **kw)
+    model = GPTModel(cfg, device="cpu", seed=3)
+    er = ps.rank_in("ep")
+    sd = full.state_dict()
+    for k in list(sd):
+        if k.endswith("experts.weight1"):
+            sd[k] = sd[k].view(32, 4, 32)[:, er * 2:(er + 1) * 2].reshape(32, -1).contiguous()
+        if k.endswith("experts.weight2"):
+            sd[k] = sd[k].view(4, 16, 32)[er * 2:(er + 1) * 2].reshape(-1, 32).contiguous()
+    model.load_state_dict(sd)
+    ddp = DistributedDataParallel(model, ps.group("dp_cp"), ps.size("dp_cp"), **expert_replica_groups(ps, cfg))
+    assert len(ddp.buffers) == 2                             # dense + experts
+
+    ref_engine = LLMEngine(full.cfg, "cpu", max_num_seqs=4, max_num_batched_tokens=64, max_model_len=32, block_size=4)
+    ref_engine.runner.bind_weights(alias_rollout_weights(full))
+    ref_engine.init_cache(32)
+    prompts = [[3 + rank, 9, 27, 5], [1, 2, 3, 4, 5, 6 + rank]] if rank != 2 else []      # one rank has nothing to do
+    params = SamplingParams(n=1, temperature=0.0, max_tokens=6)
+    want = [o.outputs[0].token_ids for o in ref_engine.generate(prompts, params)] if prompts else []
+    torch.manual_seed(1)
+    emap = expert_map_from_counts(torch.randint(1, 50, (2, 4)), 2, 1)          # 2 ranks x (2 + 1) slots
+    for infer_ep, mapping in ((4, None), (1, None), (2, emap)):
+        r = Resharder(cfg, ddp, ps, 1, "cpu",
+                      lambda icfg, comm: LLMEngine(icfg, "cpu", max_num_seqs=4, max_num_batched_tokens=64,
+                                                   max_model_len=32, block_size=4),
+                      infer_ep=infer_ep, expert_map=mapping)
+        assert r.rehome and r.infer_state.size("ep") == infer_ep
+        # the engines of a rollout expert-parallel group step together
+        r.engine.lockstep_group, r.engine.lookahead_decode = r._lockstep_group(), False
+        w = r.reshard(model)
+        n_slots = (4 + (2 if mapping else 0)) // infer_ep
+        assert w.layers[0].moe.num_local == n_slots and w.layers[0].moe.ep_size == infer_ep
+        if mapping:
+            assert w.layers[0].moe.log2phy.shape[0] == 4 and int((w.layers[0].moe.log2phy >= 0).sum()) == 6
+        r.engine.runner.bind_weights(w)
+        r.engine.init_cache(32)
+        got = [o.outputs[0].token_ids for o in r.engine.generate(prompts, params)]
+        assert got == want, (infer_ep, bool(mapping), rank, got, want)
+        r.engine.free_cache()
+        dist.barrier()
+
+
+def test_rollout_rehomes_experts_over_four_ranks():
+    run_distributed(_ep_rehome_worker, 4)
+
+
 def _dock_worker(rank, world):
     from mindspeed_rl_b200.data.transfer_dock import GRPOTransferDock
     from mindspeed_rl_b200.runtime import rpc

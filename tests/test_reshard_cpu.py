@@ -106,3 +106,138 @@ def test_plan_matches_direct_sharding(tp_t, pp_t, tp_i, world):
         w = weights_from_buffer(cfg, tp_i, j, plan, dst, torch.float32)
         assert w.layers[0].qkv_w.shape[0] == (cfg.num_attention_heads + 2 * cfg.num_query_groups) // tp_i * 16
         assert w.vocab_start == j * cfg.vocab_size // tp_i
+
+
+def _moe_cfg(**kw):
+    return _cfg(num_layers=2, num_experts=8, moe_router_topk=2, moe_ffn_hidden_size=32, **kw)
+
+
+def _expert_shard(full, cfg, ep, r):
+    """State dict of training expert-parallel rank ``r`` of ``ep``: its block of every layer's experts."""
+    h, f, e = cfg.hidden_size, cfg.moe_ffn_hidden_size, cfg.num_experts
+    per = e // ep
+    out = {}
+    for k, v in full.items():
+        if k.endswith("experts.weight1"):
+            out[k] = v.view(h, e, 2 * f)[:, r * per:(r + 1) * per].reshape(h, -1).contiguous()
+        elif k.endswith("experts.weight2"):
+            out[k] = v.view(e, f, h)[r * per:(r + 1) * per].reshape(-1, h).contiguous()
+        else:
+            out[k] = v.clone()
+    return out
+
+
+@pytest.mark.parametrize("ep_t,pp_t,ep_i,redundant", [(2, 1, 4, 0), (4, 1, 1, 0), (2, 2, 4, 0), (2, 1, 2, 1), (1, 1, 4, 1)])
+def test_plan_rehomes_experts(ep_t, pp_t, ep_i, redundant):
+    """Expert growth (EP2 -> EP4), expert replication (EP4 -> every rank holds all), experts gathered from
+    pipeline stages, and a placement map with one redundant expert slot per rollout rank: every rollout
+    rank's expert tensors hold exactly the logical experts it is said to host, in slot order."""
+    from mindspeed_rl_b200.reshard.planner import ExpertPlacement
+    from mindspeed_rl_b200.rollout.eplb import expert_map_from_counts
+
+    cfg = _moe_cfg()
+    full = GPTModel(cfg, seed=5).state_dict()
+    world = 4 * pp_t
+    train = RankLayout(world, pp=pp_t, ep=ep_t)
+    layers = stage_layers(cfg.num_layers, pp_t)
+    h, f, e = cfg.hidden_size, cfg.moe_ffn_hidden_size, cfg.num_experts
+    buffers, tables = {}, [None] * pp_t
+    for r in range(world):
+        c, ec = train.coords(r), train.expert_coords(r)
+        st = _stage_state(_expert_shard(full, cfg, ep_t, ec["ep"]), layers[c["pp"]], c["pp"] == 0, c["pp"] == pp_t - 1)
+        slots, flat = _flatten(st)
+        tables[c["pp"]] = slots
+        buffers[r] = flat.view(torch.uint8)
+    emap = None
+    if redundant:
+        torch.manual_seed(1)
+        emap = expert_map_from_counts(torch.randint(1, 100, (cfg.num_layers, e)), ep_i, redundant)
+    infer = RankLayout(world, ep=ep_i)
+    for r in range(world):
+        ei = infer.expert_coords(r)["ep"]
+        mine = train.expert_coords(r)
+
+        def hosted(layer, ei=ei):
+            if emap is not None:
+                return emap["layer_list"][layer]["device_list"][ei]["device_expert"]
+            per = e // ep_i
+            return list(range(ei * per, (ei + 1) * per))
+
+        def src_rank(ep_index, stage, mine=mine):
+            stage_rank = mine["etp"] + train.expert_tp * (ep_index + train.ep_total * mine["edp"])
+            return train.rank_of(tp=stage_rank % train.tp, cp=(stage_rank // train.tp) % train.cp,
+                                 dp=stage_rank // (train.tp * train.cp), pp=stage)
+
+        plan = build_plan(cfg, train, 1, r, tables, layers, lambda rank: 0, esz=4,
+                          experts=ExpertPlacement(e // ep_t, hosted, src_rank))
+        dst = torch.zeros(plan.nbytes, dtype=torch.uint8)
+        execute_plan_torch(plan, buffers, dst)
+        for layer in range(cfg.num_layers):
+            ids = hosted(layer)
+            assert len(ids) == (e + redundant * ep_i) // ep_i and len(set(ids)) == len(ids)
+            for name, ref in (("weight1", full[f"decoder.layers.{layer}.mlp.experts.weight1"].view(h, e, 2 * f)[:, ids]),
+                              ("weight2", full[f"decoder.layers.{layer}.mlp.experts.weight2"].view(e, f, h)[ids])):
+                off, shape = plan.tensors[f"decoder.layers.{layer}.mlp.experts.{name}"]
+                got = dst[off:off + ref.numel() * 4].view(torch.float32).view(shape)
+                assert torch.equal(got, ref.reshape(shape)), (r, layer, name)
+            off, shape = plan.tensors[f"decoder.layers.{layer}.mlp.router.weight"]
+            assert torch.equal(dst[off:off + e * h * 4].view(torch.float32).view(shape),
+                               full[f"decoder.layers.{layer}.mlp.router.weight"])
+        # expert sources are ranks of my own expert-data-parallel replica that own the shard
+        for i, d in enumerate(plan.desc):
+            assert train.expert_coords(d[0])["edp"] == mine["edp"] or plan.buf_of(i) == 0
+
+
+def test_plan_carries_adapters_and_rollout_folds_them():
+    """LoRA under a TP change (train TP2 -> rollout TP1 and TP4): ``B`` is cut like the weight's output rows,
+    ``A`` like its input columns, and the rollout copy of the weight becomes ``W + (alpha / r) B A``."""
+    from mindspeed_rl_b200.models import lora
+
+    cfg = _cfg(num_layers=2, lora_r=4, lora_alpha=8, lora_target_modules=["linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"])
+    model = GPTModel(cfg, seed=7)
+    torch.manual_seed(0)
+    for hld in lora.holders(model):
+        hld.lora_B.data.normal_(0, 0.05)                   # B starts at zero: make the fold visible
+    full = model.state_dict()
+    merged = {n: lora.merged_weight(m) for n, m in model.named_modules() if getattr(m, "lora_A", None) is not None}
+
+    def shard_adapters(state, tp, r):
+        out = _shard({k: v for k, v in state.items() if "lora_" not in k}, cfg, tp, r)
+        for k, v in state.items():
+            if k.endswith("linear_qkv.lora_B"):
+                out[k] = C.shard_qkv(v, cfg.num_query_groups, tp, r)
+            elif k.endswith("linear_fc1.lora_B"):
+                g, u = v.chunk(2, 0)
+                out[k] = C.shard_fc1(g, u, tp, r)
+            elif k.endswith(("linear_proj.lora_A", "linear_fc2.lora_A")):
+                out[k] = C.shard_cols(v, tp, r)
+            elif "lora_" in k:
+                out[k] = v.clone()
+        return out
+
+    tp_t = 2
+    train = RankLayout(tp_t, tp=tp_t)
+    layers = stage_layers(cfg.num_layers, 1)
+    buffers, tables = {}, [None]
+    for r in range(tp_t):
+        slots, flat = _flatten(shard_adapters(full, tp_t, r))
+        tables[0] = slots
+        buffers[r] = flat.view(torch.uint8)
+    for tp_i in (1, 2):
+        world = max(tp_t, tp_i)
+        for r in range(tp_i):
+            plan = build_plan(cfg, RankLayout(world, tp=tp_t) if world != tp_t else train, tp_i, r, tables, layers,
+                              lambda rank: 0, esz=4)
+            dst = torch.zeros(plan.nbytes, dtype=torch.uint8)
+            execute_plan_torch(plan, buffers, dst)
+            w = weights_from_buffer(cfg, tp_i, r, plan, dst, torch.float32)
+            for li in range(cfg.num_layers):
+                p = f"decoder.layers.{li}."
+                want_qkv = C.shard_qkv(merged[p + "self_attention.linear_qkv"], cfg.num_query_groups, tp_i, r)
+                want_proj = C.shard_cols(merged[p + "self_attention.linear_proj"], tp_i, r)
+                g, u = merged[p + "mlp.linear_fc1"].chunk(2, 0)
+                want_fc1 = C.shard_fc1(g, u, tp_i, r)
+                want_fc2 = C.shard_cols(merged[p + "mlp.linear_fc2"], tp_i, r)
+                for got, want in ((w.layers[li].qkv_w, want_qkv), (w.layers[li].o_w, want_proj),
+                                  (w.layers[li].gate_up_w, want_fc1), (w.layers[li].down_w, want_fc2)):
+                    assert torch.allclose(got, want, atol=1e-6), (tp_i, r, li)
