@@ -2,7 +2,7 @@
 against the library collectives they replace.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m mindspeed_rl_b200.ops.microbench_multi [--only collectives,peer_all_reduce,fused_tp,moe_dispatch]
+        -m mindspeed_rl_b200.ops.microbench_multi [--only collectives,peer_all_reduce,fused_tp,moe_dispatch,tp_layers]
 
 One process per GPU over NCCL.  Rank 0 prints one JSON line per case.  Correctness of the same kernels is
 covered by the multi-GPU tests; this module only times them.
@@ -154,8 +154,65 @@ def case_moe_dispatch(rank: int, world: int) -> None:
     arena.close()
 
 
+def case_tp_layers(rank: int, world: int) -> None:
+    """A few 7B layers + LM head under tensor / sequence parallelism over all ranks: time per forward and
+    per forward + backward with the communication-fused linears and with library collectives around plain
+    GEMMs (``MSRL_BENCH_KERNEL_TABLE=1`` adds the top kernels by device time from ``torch.profiler``)."""
+    from ..models.gpt import GPTModel, PackedMeta
+    from ..models.transformer_config import TransformerConfig
+    from ..parallel.ddp import DistributedDataParallel
+    from ..parallel.fused_tp import FusedTP
+    from ..parallel.state import initialize_model_parallel
+    from ..parallel.symm import init_arena
+    from ..parallel.tp_comm import TPComm
+
+    ps = initialize_model_parallel(world, 1, 1)
+    tokens = int(os.environ.get("MSRL_BENCH_TOKENS_PER_RANK", "8192")) * world
+    layers = int(os.environ.get("MSRL_BENCH_LAYERS", "4"))
+    cfg = TransformerConfig(num_layers=layers, hidden_size=3584, ffn_hidden_size=18944, num_attention_heads=28,
+                            num_query_groups=4, vocab_size=152064, add_qkv_bias=True,
+                            tensor_model_parallel_size=world, sequence_parallel=world > 1, recompute_granularity=None,
+                            recompute_activation_function=True, max_position_embeddings=4096)
+    comm = TPComm(ps.group("tp"), True, world_size=world, rank=rank)
+    ml = tokens // world
+    arena = init_arena(int(2.5e9) + 2 * ml * 3584 * 2 * (1 + world) * 2, device=torch.device("cuda"))
+    core = GPTModel(cfg, comm, device="cuda", seed=1)
+    DistributedDataParallel(core, None, 1)
+    fused = FusedTP(arena, list(range(world)), ml, 3584, 3584) if world > 1 else None
+    meta = PackedMeta.from_lengths([2048] * (tokens // 2048), "cuda", align=world)
+    ids = torch.randint(0, 150000, (tokens,), device="cuda")
+    labels = torch.randint(0, 150000, (tokens,), device="cuda")
+
+    def fwd():
+        with torch.no_grad():
+            return core.forward_logprob(ids, labels, meta, 1.0, False)[0]
+
+    def fwdbwd():
+        core.forward_logprob(ids, labels, meta, 1.0, False)[0].sum().backward()
+
+    out = dict(case="tp_layers", world=world, tokens=tokens, layers=layers)
+    for use_fused in ((True, False) if fused is not None else (False,)):
+        comm.fused = fused if use_fused else None
+        tag = "fused" if use_fused else "library"
+        out[f"fwd_{tag}_ms"] = timed(fwd, 3, 2)
+        out[f"fwdbwd_{tag}_ms"] = timed(fwdbwd, 3, 2)
+        if os.environ.get("MSRL_BENCH_KERNEL_TABLE") == "1":
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                fwdbwd()
+                torch.cuda.synchronize()
+            if rank == 0:
+                rows = sorted(prof.key_averages(), key=lambda k: -k.device_time_total)[:16]
+                total = sum(k.device_time_total for k in prof.key_averages())
+                for k in rows:
+                    print(f"  [{tag}] {k.device_time_total / 1e3:9.2f} ms {100 * k.device_time_total / total:5.1f}% "
+                          f"x{k.count:4d}  {k.key[:90]}", flush=True)
+    report(rank, **out)
+
+
 CASES = {"collectives": case_collectives, "peer_all_reduce": case_peer_all_reduce, "fused_tp": case_fused_tp,
-         "moe_dispatch": case_moe_dispatch}
+         "moe_dispatch": case_moe_dispatch, "tp_layers": case_tp_layers}
 
 
 def main() -> None:
@@ -165,7 +222,7 @@ def main() -> None:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dist.init_process_group("nccl")
-    for name in ([n for n in args.only.split(",") if n] or list(CASES)):
+    for name in ([n for n in args.only.split(",") if n] or [n for n in CASES if n != "tp_layers"]):
         CASES[name](rank, world)
         dist.barrier()
     dist.destroy_process_group()
