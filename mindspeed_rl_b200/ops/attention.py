@@ -15,6 +15,8 @@ from typing import Optional, Tuple
 
 import torch
 
+from . import guard
+
 from . import _lib
 from ._lib import c_int, c_ll, check, ptr, stream
 from .elementwise import _workspace
@@ -90,8 +92,8 @@ def attn_varlen_fwd(qkv: torch.Tensor, layout: QKVLayout, cu_seqlens: torch.Tens
             ks = vs = (0, (nkv * hd, 0, nkv, hd))
             kb, vb = kv[0].contiguous().view(-1), kv[1].contiguous().view(-1)
         lay = _layout_array(qs, ks, vs)
-        out = torch.empty(t, nh * hd, device=qkv.device, dtype=qkv.dtype)
-        lse = torch.empty(nh, t, device=qkv.device, dtype=torch.float32)
+        out = guard.empty(t, nh * hd, device=qkv.device, dtype=qkv.dtype)
+        lse = guard.empty(nh, t, device=qkv.device, dtype=torch.float32)
         if hd == 128 and use_tcgen05_attention():
             from .gemm import _status_word
             tk = t if kv is None else kv[0].shape[0]
@@ -124,7 +126,7 @@ def attn_varlen_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, ls
     batch = cu_seqlens.numel() - 1
     if _lib.use_kernels(qkv, dout, out):
         flat = qkv.view(-1)
-        dqkv = torch.empty_like(qkv)
+        dqkv = guard.empty_like(qkv)
         dflat = dqkv.view(-1)
         qs, ks, vs = layout.q(), layout.k(), layout.v()
         lay = _layout_array(qs, ks, vs)
@@ -167,8 +169,8 @@ def attn_kv_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q: torch.T
     batch = cu_q.numel() - 1
     if _lib.use_kernels(q, k, v):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        out = torch.empty(tq, nh * hd, device=q.device, dtype=q.dtype)
-        lse = torch.empty(nh, tq, device=q.device, dtype=torch.float32)
+        out = guard.empty(tq, nh * hd, device=q.device, dtype=q.dtype)
+        lse = guard.empty(nh, tq, device=q.device, dtype=torch.float32)
         lay = (ctypes.c_longlong * 12)(nh * hd, 0, nh, hd, nkv * hd, 0, nkv, hd, nkv * hd, 0, nkv, hd)
         if hd == 128 and use_tcgen05_attention():
             from .gemm import _status_word
@@ -200,7 +202,7 @@ def attn_kv_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
     batch = cu_q.numel() - 1
     if _lib.use_kernels(q, k, v, dout):
         q, k, v, do = q.contiguous(), k.contiguous(), v.contiguous(), dout.contiguous()
-        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dq, dk, dv = guard.empty_like(q), guard.empty_like(k), guard.empty_like(v)
         delta = _workspace("attn_delta", nh * tq, q.device)
         # contiguous [T, heads, hd]: head h starts at column h * hd
         lay = (ctypes.c_longlong * 12)(nh * hd, 0, nh, hd, nkv * hd, 0, nkv, hd, nkv * hd, 0, nkv, hd)

@@ -13,6 +13,8 @@ from typing import Optional, Sequence, Tuple
 
 import torch
 
+from . import guard
+
 from . import _lib
 from ._lib import c_float, c_int, c_ll, c_ull, check, ptr, stream
 from .elementwise import _workspace
@@ -54,8 +56,8 @@ def kv_cache_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: 
     nb, bs, nkv, hd = k_cache.shape
     t = token_seq.numel()
     if _lib.use_kernels(k_cache, block_tables, token_seq):
-        k = torch.empty(t, nkv, hd, device=k_cache.device, dtype=k_cache.dtype)
-        v = torch.empty_like(k)
+        k = guard.empty(t, nkv, hd, device=k_cache.device, dtype=k_cache.dtype)
+        v = guard.empty_like(k)
         check(_lib.load().msrl_kv_cache_gather(ptr(k_cache), ptr(v_cache), ptr(block_tables),
                                                c_int(block_tables.shape[1]), ptr(token_seq),
                                                ptr(token_pos), ptr(k), ptr(v), c_ll(t), c_int(nkv),
@@ -147,7 +149,7 @@ def paged_decode_attention(qkv: torch.Tensor, layout: QKVLayout, k_cache: torch.
     nh, nkv, hd = layout.num_heads, layout.num_kv_heads, layout.head_dim
     bs = k_cache.shape[1]
     if out is None:
-        out = torch.empty(b, nh * hd, device=qkv.device, dtype=qkv.dtype)
+        out = guard.empty(b, nh * hd, device=qkv.device, dtype=qkv.dtype)
     if _lib.use_kernels(qkv, k_cache, block_tables, context_lens):
         L = _lib.load()
         nsplit = L.msrl_paged_decode_nsplit(c_int(b), c_int(nkv), c_int(int(max_context)))
@@ -223,19 +225,19 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torc
             tk = top_k.to(torch.int32) if top_k is not None else torch.zeros(b, dtype=torch.int32, device=dev)
             tp = top_p.float() if top_p is not None else torch.ones(b, device=dev)
             mp = min_p.float() if min_p is not None else torch.zeros(b, device=dev)
-            thresh = torch.empty(b, device=dev, dtype=torch.float32)
+            thresh = guard.empty(b, device=dev, dtype=torch.float32)
             check(L.msrl_sample_filter(ptr(logits), c_int(is_bf16), c_ll(logits.stride(0)), c_int(b),
                                        c_int(v), ptr(inv_t), ptr(tk), ptr(tp), ptr(mp), ptr(thresh),
                                        stream()), "sample_filter")
         nsplit = int(L.msrl_sample_nsplit(c_int(b), c_int(v)))      # vocabulary splits per row (one CTA each)
-        rec = torch.empty(b * nsplit * L.msrl_sample_rec_bytes(), device=dev, dtype=torch.uint8)
+        rec = guard.empty(b * nsplit * L.msrl_sample_rec_bytes(), device=dev, dtype=torch.uint8)
         ep = eos_prob.float() if eos_prob is not None else None
         check(L.msrl_sample(ptr(logits), c_int(is_bf16), c_ll(logits.stride(0)), c_int(b), c_int(v),
                             c_int(vocab_offset), ptr(inv_t), ptr(thresh), ptr(ep), c_int(eos_id),
                             ptr(row_keys), c_ull(seed & (2 ** 64 - 1)), ptr(rec), c_int(nsplit), stream()),
               "sample")
-        tokens = torch.empty(b, device=dev, dtype=torch.int64)
-        logprobs = torch.empty(b, device=dev, dtype=torch.float32)
+        tokens = guard.empty(b, device=dev, dtype=torch.int64)
+        logprobs = guard.empty(b, device=dev, dtype=torch.float32)
         check(L.msrl_sample_combine(ptr(rec), c_int(nsplit), c_int(b), ptr(ep), c_int(eos_id), ptr(row_keys),
                                     c_ull(seed & (2 ** 64 - 1)), ptr(tokens), ptr(logprobs), stream()),
               "sample_combine")
@@ -274,8 +276,8 @@ def _sample_reference(logits, inv_t, top_k, top_p, min_p, row_keys, seed, eos_pr
         forced = eos_prob >= 0
         zf[forced, eos_id] = float("-inf")
     lse = torch.logsumexp(zf, dim=1)
-    tokens = torch.empty(b, dtype=torch.int64)
-    logprobs = torch.empty(b, dtype=torch.float32)
+    tokens = guard.empty(b, dtype=torch.int64)
+    logprobs = guard.empty(b, dtype=torch.float32)
     for i in range(b):
         g = torch.Generator().manual_seed((int(seed) * 1000003 + int(row_keys[i])) % (2 ** 63))
         if inv_t[i] <= 0:

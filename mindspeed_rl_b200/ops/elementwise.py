@@ -12,6 +12,8 @@ from typing import Optional, Tuple
 
 import torch
 
+from . import guard
+
 from . import _lib
 from ._lib import c_float, c_int, c_ll, check, ptr, stream
 from .layouts import QKVLayout
@@ -26,7 +28,7 @@ def _workspace(key: str, numel: int, device, dtype=torch.float32) -> torch.Tenso
     if buf is None or buf.numel() < numel:
         if buf is not None and buf.is_cuda:
             _retired.append(buf)
-        buf = torch.empty(max(numel, 1), device=device, dtype=dtype)
+        buf = guard.empty(max(numel, 1), device=device, dtype=dtype)
         _scratch[(key, device, dtype)] = buf
     return buf
 
@@ -44,9 +46,9 @@ def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional
     rows = x.numel() // h
     if _lib.use_kernels(x, w):
         x2 = x.contiguous().view(rows, h)
-        y = torch.empty_like(x2)
-        rstd = torch.empty(rows, device=x.device, dtype=torch.float32) if want_rstd else None
-        summed = torch.empty_like(x2) if residual is not None else None
+        y = guard.empty_like(x2)
+        rstd = guard.empty(rows, device=x.device, dtype=torch.float32) if want_rstd else None
+        summed = guard.empty_like(x2) if residual is not None else None
         res = residual.contiguous().view(rows, h) if residual is not None else None
         check(_lib.load().msrl_rmsnorm_fwd(ptr(x2), ptr(res), ptr(w), ptr(y), ptr(summed), ptr(rstd),
                                            c_ll(rows), c_int(h), c_float(eps), stream()),
@@ -67,7 +69,7 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.
     if _lib.use_kernels(dy, x, w):
         L = _lib.load()
         dy2, x2 = dy.contiguous().view(rows, h), x.contiguous().view(rows, h)
-        dx = torch.empty_like(x2)
+        dx = guard.empty_like(x2)
         nb = L.msrl_rmsnorm_bwd_blocks(c_ll(rows))
         part = _workspace("rmsnorm_dw", nb * h, x.device)
         dres2 = dres.contiguous().view(rows, h) if dres is not None else None
@@ -109,7 +111,7 @@ def headnorm_fwd_(qkv: torch.Tensor, layout: QKVLayout, which: str, w: torch.Ten
     hd = layout.head_dim
     off, (st, gs, hpg, hs) = _head_spec(layout, which)
     if _lib.use_kernels(qkv, w):
-        rstd = torch.empty(t * n, device=qkv.device, dtype=torch.float32)
+        rstd = guard.empty(t * n, device=qkv.device, dtype=torch.float32)
         base = qkv.view(-1)[off:]
         check(_lib.load().msrl_headnorm_fwd(ptr(base), c_ll(st), c_int(gs), c_int(hpg), c_int(hs), ptr(w),
                                             ptr(base), ptr(rstd), c_ll(t), c_int(n), c_int(hd),
@@ -251,7 +253,7 @@ def swiglu_fwd(gate_up: torch.Tensor) -> torch.Tensor:
     rows = gate_up.numel() // (2 * f)
     if _lib.use_kernels(gate_up):
         x = gate_up.contiguous()
-        out = torch.empty(*x.shape[:-1], f, device=x.device, dtype=x.dtype)
+        out = guard.empty(*x.shape[:-1], f, device=x.device, dtype=x.dtype)
         check(_lib.load().msrl_swiglu_fwd(ptr(x), ptr(out), c_ll(rows), c_int(f), stream()), "swiglu_fwd")
         return out
     g, u = gate_up.float().split(f, dim=-1)
@@ -263,7 +265,7 @@ def swiglu_bwd(gate_up: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
     rows = gate_up.numel() // (2 * f)
     if _lib.use_kernels(gate_up, dy):
         x, d = gate_up.contiguous(), dy.contiguous()
-        out = torch.empty_like(x)
+        out = guard.empty_like(x)
         check(_lib.load().msrl_swiglu_bwd(ptr(x), ptr(d), ptr(out), c_ll(rows), c_int(f), stream()),
               "swiglu_bwd")
         return out
@@ -293,7 +295,7 @@ def colsum_accumulate(m: torch.Tensor, out: torch.Tensor) -> None:
 def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     if _lib.use_kernels(a, b) and a.dtype == torch.bfloat16 and a.numel() % 8 == 0 \
             and a.is_contiguous() and b.is_contiguous():
-        out = torch.empty_like(a)
+        out = guard.empty_like(a)
         check(_lib.load().msrl_add(ptr(a), ptr(b), ptr(out), c_ll(a.numel()), stream()), "add")
         return out
     return a + b

@@ -13,6 +13,8 @@ from typing import Optional, Tuple
 
 import torch
 
+from . import guard
+
 from . import _lib
 from ._lib import c_float, c_int, c_ll, check, ptr, stream
 
@@ -57,7 +59,7 @@ def gemm_bf16_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] =
     m, k = a.shape
     n = b.shape[0]
     if out is None:
-        out = torch.empty(m, n, device=a.device, dtype=torch.bfloat16)
+        out = guard.empty(m, n, device=a.device, dtype=torch.bfloat16)
     check(_lib.load().msrl_gemm_bf16_tn(ptr(a), c_ll(a.stride(0)), ptr(b), c_ll(b.stride(0)), ptr(out),
                                         c_ll(out.stride(0)), c_int(m), c_int(n), c_int(k),
                                         ptr(_status_word(a.device)), stream()), "gemm_bf16_tn")
@@ -93,7 +95,7 @@ def gemm_pair(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: boo
     if out is None:
         if mode != "store":
             raise ValueError("accumulating modes need an output tensor")
-        out = torch.empty(m, n, device=a.device, dtype=torch.bfloat16)
+        out = guard.empty(m, n, device=a.device, dtype=torch.bfloat16)
     check(_lib.load().msrl_gemm_pair_bf16(
         ptr(a), c_ll(a.stride(0)), c_int(int(a_mn)), ptr(b), c_ll(b.stride(0)), c_int(int(b_mn)), ptr(out),
         c_ll(out.stride(0)), c_int(_OUT_MODES[mode]), ptr(bias), c_int(m), c_int(n), c_int(k),
@@ -121,8 +123,8 @@ def gemm_pair_splitk(x: torch.Tensor, w: torch.Tensor, splits: int, bias: Option
     m, k = x.shape
     n = w.shape[0]
     if out is None:
-        out = torch.empty(m, n, device=x.device, dtype=torch.bfloat16)
-    part = torch.empty(splits * m * n, device=x.device, dtype=torch.float32)
+        out = guard.empty(m, n, device=x.device, dtype=torch.bfloat16)
+    part = guard.empty(splits * m * n, device=x.device, dtype=torch.float32)
     check(_lib.load().msrl_gemm_pair_splitk_bf16(
         ptr(x), c_ll(x.stride(0)), ptr(w), c_ll(w.stride(0)), ptr(part), ptr(out), c_ll(out.stride(0)), ptr(bias),
         c_int(m), c_int(n), c_int(k), c_int(splits), ptr(_status_word(x.device)), stream()), "gemm_pair_splitk_bf16")
@@ -182,7 +184,7 @@ def lmhead_stats(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, inv_tem
     n = w.shape[0]
     L = _lib.load()
     tiles = L.msrl_lmhead_stats_tiles(c_int(n))
-    stats = torch.empty(tiles, m, 4, device=h.device, dtype=torch.float32)
+    stats = guard.empty(tiles, m, 4, device=h.device, dtype=torch.float32)
     check(L.msrl_lmhead_stats(ptr(h), c_ll(h.stride(0)), ptr(w), c_ll(w.stride(0)), ptr(labels),
                               c_int(vocab_offset), c_float(inv_temp), ptr(stats), c_int(m), c_int(n),
                               c_int(k), ptr(_status_word(h.device)), stream()), "lmhead_stats")

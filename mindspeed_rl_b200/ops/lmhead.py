@@ -14,6 +14,8 @@ from __future__ import annotations
 from typing import Optional, Tuple
 
 import torch
+
+from . import guard
 import torch.distributed as dist
 
 import os
@@ -38,7 +40,7 @@ def _combine_stats(stats: torch.Tensor, group) -> Tuple[torch.Tensor, int]:
     ws = _world(group)
     if ws == 1:
         return stats.unsqueeze(0), 1
-    out = torch.empty(ws, *stats.shape, device=stats.device, dtype=stats.dtype)
+    out = guard.empty(ws, *stats.shape, device=stats.device, dtype=stats.dtype)
     dist.all_gather_into_tensor(out.view(-1), stats.view(-1).contiguous(), group=group)
     return out, ws
 
@@ -51,9 +53,9 @@ def lmhead_logprob_fwd(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, i
     t = h.shape[0]
     v = w.shape[0]
     dev = h.device
-    logp = torch.empty(t, device=dev, dtype=torch.float32)
-    ent = torch.empty(t, device=dev, dtype=torch.float32) if want_entropy else None
-    lse = torch.empty(t, device=dev, dtype=torch.float32)
+    logp = guard.empty(t, device=dev, dtype=torch.float32)
+    ent = guard.empty(t, device=dev, dtype=torch.float32) if want_entropy else None
+    lse = guard.empty(t, device=dev, dtype=torch.float32)
     labels = labels.to(torch.int64).contiguous()
     if _lib.use_kernels(h, w, labels) and h.dtype == torch.bfloat16:
         L = _lib.load()
@@ -74,7 +76,7 @@ def lmhead_logprob_fwd(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, i
         for s in range(0, t, chunk):
             e = min(t, s + chunk)
             z = _gemm.linear_fwd(h[s:e], w)                      # [c, V] bf16
-            st = torch.empty(e - s, 4, device=dev, dtype=torch.float32)
+            st = guard.empty(e - s, 4, device=dev, dtype=torch.float32)
             check(L.msrl_logprob_stats(ptr(z), c_ll(z.stride(0)), c_ll(e - s), c_int(v),
                                        c_int(vocab_offset), ptr(labels[s:e]), c_float(inv_temp),
                                        ptr(st), stream()), "logprob_stats")
@@ -115,7 +117,7 @@ def lmhead_logprob_bwd(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, l
     reduction) and accumulates ``dW`` into ``dw_accum`` (same shape as ``w``; may be ``None``)."""
     t = h.shape[0]
     v = w.shape[0]
-    dh = torch.empty_like(h)
+    dh = guard.empty_like(h)
     labels = labels.to(torch.int64).contiguous()
     dlogp = dlogp.float().contiguous()
     dent = dent.float().contiguous() if dent is not None else None

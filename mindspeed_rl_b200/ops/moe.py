@@ -16,6 +16,8 @@ from typing import Optional
 
 import torch
 
+from . import guard
+
 from . import _lib
 from ._lib import c_int, c_ll, check, ptr, stream
 
@@ -48,12 +50,12 @@ def moe_plan(expert_of: torch.Tensor, num_experts: int) -> MoePlan:
     dev = expert_of.device
     flat = expert_of.reshape(-1).contiguous()
     if _lib.use_kernels(expert_of):
-        counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
-        offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
-        pos = torch.empty(n, dtype=torch.int32, device=dev)
-        tiles = torch.empty(rows // PAD, dtype=torch.int32, device=dev)
+        counts = guard.empty(num_experts, dtype=torch.int32, device=dev)
+        offsets = guard.empty(num_experts + 1, dtype=torch.int32, device=dev)
+        pos = guard.empty(n, dtype=torch.int32, device=dev)
+        tiles = guard.empty(rows // PAD, dtype=torch.int32, device=dev)
         blocks = (n + 255) // 256
-        scratch = torch.empty(blocks * num_experts + n + 1, dtype=torch.int32, device=dev)
+        scratch = guard.empty(blocks * num_experts + n + 1, dtype=torch.int32, device=dev)
         check(_lib.load().msrl_moe_plan(ptr(flat), c_int(n), c_int(num_experts), ptr(scratch), ptr(counts),
                                         ptr(offsets), ptr(pos), ptr(tiles), c_int(rows // PAD), stream()), "moe_plan")
         return MoePlan(counts, offsets, pos, tiles, rows, t, k, num_experts)
@@ -62,7 +64,7 @@ def moe_plan(expert_of: torch.Tensor, num_experts: int) -> MoePlan:
     offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=dev)
     offsets[1:] = padded.cumsum(0)
     order = torch.argsort(flat, stable=True)
-    rank = torch.empty(n, dtype=torch.int64, device=dev)
+    rank = guard.empty(n, dtype=torch.int64, device=dev)
     start = counts.cumsum(0) - counts
     rank[order] = torch.arange(n, device=dev) - start[flat[order]]
     pos = offsets[flat] + rank
@@ -78,7 +80,7 @@ def moe_permute(x: torch.Tensor, plan: MoePlan, w: Optional[torch.Tensor] = None
     t, h = x.shape
     if _lib.use_kernels(x):
         x = x.contiguous()
-        xp = torch.empty(plan.max_rows, h, dtype=x.dtype, device=x.device)
+        xp = guard.empty(plan.max_rows, h, dtype=x.dtype, device=x.device)
         wf = None if w is None else w.reshape(-1).float().contiguous()
         check(_lib.load().msrl_moe_permute(ptr(x), c_ll(h), ptr(plan.pos), ptr(wf), c_int(t), c_int(plan.k), c_int(h),
                                            c_int(plan.num_experts), ptr(plan.counts), ptr(plan.offsets), ptr(xp),
@@ -96,7 +98,7 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, w: Optional[torch.Tensor] = None
     """``out[t] = sum_j w[t, j] * y[pos(t, j)]`` (fp32 accumulation), ``[T, H]`` in ``y``'s dtype."""
     h = y.shape[1]
     if _lib.use_kernels(y):
-        out = torch.empty(plan.tokens, h, dtype=y.dtype, device=y.device)
+        out = guard.empty(plan.tokens, h, dtype=y.dtype, device=y.device)
         wf = None if w is None else w.reshape(-1).float().contiguous()
         check(_lib.load().msrl_moe_combine(ptr(y), c_ll(y.stride(0)), ptr(plan.pos), ptr(wf), c_int(plan.tokens),
                                            c_int(plan.k), c_int(h), ptr(out), c_ll(h), c_int(0), stream()),
@@ -113,7 +115,7 @@ def moe_slot_dot(dout: torch.Tensor, y: torch.Tensor, plan: MoePlan) -> torch.Te
     h = y.shape[1]
     if _lib.use_kernels(dout, y):
         dout = dout.contiguous()
-        dw = torch.empty(plan.tokens, plan.k, dtype=torch.float32, device=y.device)
+        dw = guard.empty(plan.tokens, plan.k, dtype=torch.float32, device=y.device)
         check(_lib.load().msrl_moe_slot_dot(ptr(dout), c_ll(h), ptr(y), c_ll(y.stride(0)), ptr(plan.pos),
                                             c_int(plan.tokens), c_int(plan.k), c_int(h), ptr(dw), stream()),
               "moe_slot_dot")
@@ -136,7 +138,7 @@ def grouped_gemm(a: torch.Tensor, plan: MoePlan, b2d: torch.Tensor, b_mn_major: 
     if _lib.use_kernels(a, b2d):
         from .gemm import _status_word
         assert a.is_contiguous() and b2d.is_contiguous() and rows == plan.max_rows
-        c = torch.empty(rows, n, dtype=a.dtype, device=a.device) if out is None else out
+        c = guard.empty(rows, n, dtype=a.dtype, device=a.device) if out is None else out
         assert c.shape == (rows, n) and c.is_contiguous()
         rc = _lib.load().msrl_moe_grouped_gemm(
             ptr(a), c_ll(k), ptr(b2d), c_ll(b2d.shape[0]), c_ll(b2d.shape[1]), c_ll(b2d.shape[1]),

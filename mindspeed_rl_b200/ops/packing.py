@@ -12,6 +12,8 @@ from typing import Tuple
 
 import torch
 
+from . import guard
+
 from . import _lib
 from ._lib import c_int, c_ll, check, ptr, stream
 
@@ -27,9 +29,9 @@ def pack_tokens(ids2d: torch.Tensor, p_len: torch.Tensor, r_len: torch.Tensor, c
         ids2d = ids2d if ids2d.stride(1) == 1 else ids2d.contiguous()
         if ids2d.dtype not in (torch.int32, torch.int64):
             ids2d = ids2d.long()
-        out_ids = torch.empty(total, dtype=torch.int64, device=dev)
-        out_lab = torch.empty(total, dtype=torch.int64, device=dev)
-        out_pos = torch.empty(total, dtype=torch.int32, device=dev)
+        out_ids = guard.empty(total, dtype=torch.int64, device=dev)
+        out_lab = guard.empty(total, dtype=torch.int64, device=dev)
+        out_pos = guard.empty(total, dtype=torch.int32, device=dev)
         check(_lib.load().msrl_pack_tokens(
             ptr(ids2d), c_int(1 if ids2d.dtype == torch.int64 else 0), c_ll(ids2d.stride(0)), ptr(p_len), ptr(r_len),
             ptr(cu), c_int(b), c_int(s), c_ll(total), ptr(out_ids), ptr(out_lab), ptr(out_pos), stream()), "pack_tokens")
@@ -54,7 +56,7 @@ def unpack_response(src: torch.Tensor, cu: torch.Tensor, p_len: torch.Tensor, r_
     b = p_len.numel()
     if _lib.use_kernels(src, cu, p_len, r_len) and src.dtype in (torch.float32, torch.bfloat16):
         src = src.contiguous()
-        out = torch.empty(b, width, dtype=torch.float32, device=src.device)
+        out = guard.empty(b, width, dtype=torch.float32, device=src.device)
         check(_lib.load().msrl_unpack_response(
             ptr(src), c_int(1 if src.dtype == torch.bfloat16 else 0), ptr(cu), ptr(p_len), ptr(r_len), c_int(b),
             c_int(width), c_ll(src.numel()), ptr(out), stream()), "unpack_response")

@@ -13,6 +13,8 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
+from . import guard
+
 from . import _lib
 from ._lib import c_float, c_int, c_ll, check, ptr, stream
 from ..utils.compute import compute_kl_penalty
@@ -76,8 +78,8 @@ def policy_loss_fwd_bwd(logp: torch.Tensor, old_logp: Optional[torch.Tensor],
         lp = logp.detach().float().contiguous()
         w_loss = (loss_weights(mask, token_level) * loss_scale).contiguous()
         w_stat = loss_weights(mask, True).contiguous()
-        dlogp = torch.empty_like(lp)
-        st = torch.empty(4, device=lp.device, dtype=torch.float32)
+        dlogp = guard.empty_like(lp)
+        st = guard.empty(4, device=lp.device, dtype=torch.float32)
         old = old_logp.float().contiguous() if old_logp is not None else None
         ref = ref_logp.float().contiguous() if use_kl else None
         check(_lib.load().msrl_policy_loss(ptr(lp), ptr(old), ptr(ref), ptr(adv.float().contiguous()),
@@ -116,8 +118,8 @@ def value_loss_fwd_bwd(vpreds, values, returns, mask, clip: float, loss_scale: f
     if _lib.use_kernels(vpreds, values, returns, mask):
         v = vpreds.detach().float().contiguous()
         w = (loss_weights(mask, True) * loss_scale).contiguous()
-        dv = torch.empty_like(v)
-        st = torch.empty(2, device=v.device, dtype=torch.float32)
+        dv = guard.empty_like(v)
+        st = guard.empty(2, device=v.device, dtype=torch.float32)
         check(_lib.load().msrl_value_loss(ptr(v), ptr(values.float().contiguous()),
                                           ptr(returns.float().contiguous()), ptr(w), ptr(dv), ptr(st),
                                           c_ll(v.numel()), c_float(clip), stream()), "value_loss")
@@ -139,8 +141,8 @@ def gae(token_level_rewards: torch.Tensor, values: torch.Tensor, mask: torch.Ten
     b, l = token_level_rewards.shape
     r, v = token_level_rewards.float().contiguous(), values.float().contiguous()
     if _lib.use_kernels(r, v):
-        adv = torch.empty_like(r)
-        ret = torch.empty_like(r)
+        adv = guard.empty_like(r)
+        ret = guard.empty_like(r)
         check(_lib.load().msrl_gae(ptr(r), ptr(v), ptr(adv), ptr(ret), c_int(b), c_int(l),
                                    c_float(gamma), c_float(lam), stream()), "gae")
     else:
@@ -164,7 +166,7 @@ def group_norm_advantage(scores: torch.Tensor, mask: torch.Tensor, n_samples: in
     rows, l = mask.shape
     s = scores.reshape(-1).float().contiguous()
     if _lib.use_kernels(s, mask):
-        adv = torch.empty(rows, l, device=mask.device, dtype=torch.float32)
+        adv = guard.empty(rows, l, device=mask.device, dtype=torch.float32)
         check(_lib.load().msrl_group_norm_adv(ptr(s), ptr(mask.float().contiguous()), ptr(adv),
                                               c_int(rows), c_int(n_samples), c_int(l), c_float(eps),
                                               stream()), "group_norm_adv")

@@ -27,7 +27,7 @@ from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 
-from ..ops import _lib
+from ..ops import _lib, guard
 from ..ops.gemm import _ok_operand, _status_word
 from ..ops._lib import c_int, c_ll
 
@@ -90,8 +90,8 @@ class FusedTP:
         slot.copy_(x)
         self.arena.barrier(self.ranks)       # every shard is in place (and the previous user of the other slot done)
         m = ml * self.world
-        gathered = torch.empty(m, k, dtype=torch.bfloat16, device=x.device)
-        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+        gathered = guard.empty(m, k, dtype=torch.bfloat16, device=x.device)
+        out = guard.empty(m, n, dtype=torch.bfloat16, device=x.device)
         peers = self.arena.peer_ptrs(self.arena.offset_of(slot), self.ranks)
         # token shards in multiples of 256 rows run on CTA pairs (cta_group::2 main loop)
         fn = self.lib.msrl_ag_gemm_pair_bf16_tn if (ml % 256 == 0 and self.use_pair) else self.lib.msrl_ag_gemm_bf16_tn
@@ -109,7 +109,7 @@ class FusedTP:
         ml = m // self.world
         par = self._rs_calls & 1
         self._rs_calls += 1
-        out = torch.empty(ml, n, dtype=torch.bfloat16, device=a.device)
+        out = guard.empty(ml, n, dtype=torch.bfloat16, device=a.device)
         stage_off = self.arena.offset_of(self.stage[par])
         flag_off = self.arena.offset_of(self.flags[par])
         tiles_n = int(self.lib.msrl_gemm_rs_tiles(c_int(n)))

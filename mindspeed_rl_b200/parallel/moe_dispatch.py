@@ -20,7 +20,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-from ..ops import _lib
+from ..ops import _lib, guard
 from ..ops import moe as K
 from ..ops._lib import c_int, c_ll, check, ptr, stream
 from .symm import SymmetricArena
@@ -58,7 +58,7 @@ class P2PDispatcher:
         self.slab = arena.alloc((self.cap_rows, hidden), dtype)
         self.out_slab = arena.alloc((self.cap_rows, hidden), dtype)
         dev = self.slab.device
-        self.my_base = torch.empty(self.n_total, dtype=torch.int32, device=dev)
+        self.my_base = guard.empty(self.n_total, dtype=torch.int32, device=dev)
         self.fallback = fallback
         self.over = torch.zeros(1, dtype=torch.int32, device=dev)
         self.overflows = 0          # calls that left the peer-memory path
@@ -86,9 +86,9 @@ class P2PDispatcher:
         check(lib.msrl_moe_p2p_publish(self._table_ptrs, ptr(plan_src.counts), c_int(self.n_total), c_int(self.me),
                                        c_int(self.ep), st), "moe_p2p_publish")
         self.arena.barrier(self.ranks)
-        counts_l = torch.empty(self.e_local, dtype=torch.int32, device=dev)
-        offsets_l = torch.empty(self.e_local + 1, dtype=torch.int32, device=dev)
-        tiles = torch.empty(self.cap_rows // K.PAD, dtype=torch.int32, device=dev)
+        counts_l = guard.empty(self.e_local, dtype=torch.int32, device=dev)
+        offsets_l = guard.empty(self.e_local + 1, dtype=torch.int32, device=dev)
+        tiles = guard.empty(self.cap_rows // K.PAD, dtype=torch.int32, device=dev)
         check(lib.msrl_moe_p2p_layout(ptr(self.table), c_int(self.ep), c_int(self.e_local), c_int(self.me),
                                       c_int(self.cap_rows), ptr(self.my_base), ptr(counts_l), ptr(offsets_l),
                                       ptr(tiles), None if self.fallback else ptr(self.arena.status),
@@ -97,8 +97,8 @@ class P2PDispatcher:
             self.over.zero_()
             self.overflows += 1
             return None
-        slot_rank = torch.empty(t * k, dtype=torch.int32, device=dev)
-        slot_row = torch.empty(t * k, dtype=torch.int32, device=dev)
+        slot_rank = guard.empty(t * k, dtype=torch.int32, device=dev)
+        slot_row = guard.empty(t * k, dtype=torch.int32, device=dev)
         wf = None if scale is None else scale.reshape(-1).float().contiguous()
         check(lib.msrl_moe_p2p_dispatch(ptr(x), c_ll(x.shape[1]), ptr(flat), ptr(plan_src.pos), ptr(plan_src.offsets),
                                         ptr(wf), c_int(t), c_int(k), c_int(self.hidden), c_int(self.e_local),
@@ -116,8 +116,8 @@ class P2PDispatcher:
         the pulled rows ``[T*k, H]`` (what the gradient of the weights needs)."""
         self.arena.barrier(self.ranks)                             # every rank's expert outputs are in its out_slab
         dev = self.slab.device
-        out = torch.empty(route.tokens, self.hidden, dtype=self.slab.dtype, device=dev)
-        rows = torch.empty(route.tokens * route.k, self.hidden, dtype=self.slab.dtype, device=dev) if keep_rows else None
+        out = guard.empty(route.tokens, self.hidden, dtype=self.slab.dtype, device=dev)
+        rows = guard.empty(route.tokens * route.k, self.hidden, dtype=self.slab.dtype, device=dev) if keep_rows else None
         wf = None if weights is None else weights.reshape(-1).float().contiguous()
         check(self.arena.lib.msrl_moe_p2p_combine(self._out_ptrs, c_int(self.ep), ptr(route.slot_rank),
                                                   ptr(route.slot_row), ptr(wf), c_int(route.tokens), c_int(route.k),

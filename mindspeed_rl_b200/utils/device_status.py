@@ -14,3 +14,6 @@ def check_device_status(stage: str = "") -> None:
     arena = get_arena()
     if arena is not None:
         arena.check()
+    from ..ops import guard
+    if guard.enabled():
+        guard.check(f"stage {stage}")      # debug mode: canary pads around the kernels' outputs

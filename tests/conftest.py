@@ -20,3 +20,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _canary_pads_intact(request):
+    """With ``MSRL_DEBUG_CANARY=1`` every GPU test ends with a check that no kernel wrote outside the
+    outputs the ops allocated for it."""
+    yield
+    if "gpu" in request.keywords and os.environ.get("MSRL_DEBUG_CANARY") == "1":
+        from mindspeed_rl_b200.ops import guard
+
+        guard.check(request.node.name)

@@ -841,6 +841,21 @@ def _lora_tp_worker(rank, world, sp):
             assert torch.allclose(p.main_grad, want[n], atol=2e-4, rtol=1e-3), (n, (p.main_grad - want[n]).abs().max())
             checked += 1
     assert checked == 2 * 4 * 2
+    # rollout at another TP size: the frozen base weights and the adapters travel through the reshard plan and
+    # the rollout copy holds W + (alpha / r) B A of the whole model
+    from mindspeed_rl_b200.reshard.planner import Resharder
+    from mindspeed_rl_b200.rollout.engine import LLMEngine
+
+    again = DistributedDataParallel(core, None, 1, frozen_buffer=True)
+    assert again.frozen_buffer is not None and len(again.frozen_buffer.params) > 0
+    r = Resharder(cfg, again, ps, 1, "cpu", lambda icfg, c: LLMEngine(icfg, "cpu", max_num_seqs=2, max_model_len=32,
+                                                                      block_size=4))
+    rw = r.reshard(core)
+    for li, layer in enumerate(full.decoder.layers):
+        for got, holder in ((rw.layers[li].qkv_w, layer.self_attention.linear_qkv),
+                            (rw.layers[li].o_w, layer.self_attention.linear_proj),
+                            (rw.layers[li].gate_up_w, layer.mlp.linear_fc1), (rw.layers[li].down_w, layer.mlp.linear_fc2)):
+            assert torch.allclose(got, lora.merged_weight(holder), atol=1e-5), (li, (got - lora.merged_weight(holder)).abs().max())
 
 
 def test_lora_tensor_parallel_matches_single_rank():

@@ -496,3 +496,24 @@ def test_pack_tokens_and_unpack_response_kernels_match_reference():
     assert torch.equal(got_rows.cpu(), want_rows)
     got16 = unpack_response(src.bfloat16().cuda(), cu.cuda(), p_len.cuda(), r_len.cuda(), 96)
     assert torch.equal(got16.cpu(), unpack_response(src.bfloat16(), cu, p_len, r_len, 96))
+
+
+def test_canary_pads_catch_a_write_past_the_output(monkeypatch):
+    """Debug allocator: outputs carry pads of a known pattern; a write one element past the end is reported
+    with the allocation site, an in-bounds write is not."""
+    from mindspeed_rl_b200.ops import guard
+
+    monkeypatch.setenv("MSRL_DEBUG_CANARY", "1")
+    guard.check("before")
+    x = torch.randn(37, 3584, device=DEV).bfloat16()
+    w = torch.ones(3584, device=DEV).bfloat16()
+    y, _, _ = ops.rmsnorm_fwd(x, w, 1e-6)                  # a real kernel writing a guarded output
+    assert guard.check("rmsnorm") >= 1
+    t = guard.empty(100, dtype=torch.float32, device=DEV)
+    t.fill_(1.0)
+    assert guard.check("inside") >= 1
+    flat = torch.as_strided(t, (101,), (1,))               # one element past the end
+    flat[100] = 7.0
+    with pytest.raises(RuntimeError, match="after the tensor"):
+        guard.check("past the end")
+    del y, t, flat

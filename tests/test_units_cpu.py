@@ -309,3 +309,13 @@ def test_flat_buffers_release_and_restore_plain_allocations():
     assert net.weight.data_ptr() == buf.param_data.data_ptr() and net.weight.main_grad.shape == net.weight.shape
     grads.restore()        # idempotent
     params.onload()
+
+
+def test_canary_guard_passthrough_on_cpu(monkeypatch):
+    """The debug allocator is a plain ``torch.empty`` for host tensors and when the mode is off."""
+    from mindspeed_rl_b200.ops import guard
+
+    monkeypatch.setenv("MSRL_DEBUG_CANARY", "1")
+    t = guard.empty(3, 5, dtype=torch.float32, device="cpu")
+    assert t.shape == (3, 5) and guard.check("cpu") == 0
+    assert guard.empty_like(t).shape == (3, 5) and guard.empty((2, 2), dtype=torch.int32).dtype == torch.int32
