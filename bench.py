@@ -69,6 +69,10 @@ def parse_args():
                     help="baseline: train TP4xDP2 -> rollout TP2xDP4 scaled to the GPU count; dp: data parallel only")
     ap.add_argument("--train-tp", type=int, default=None, help="override the training TP size")
     ap.add_argument("--infer-tp", type=int, default=None, help="override the rollout TP size")
+    ap.add_argument("--train-ep", type=int, default=1, help="expert-parallel size of training (expert models)")
+    ap.add_argument("--infer-ep", type=int, default=None,
+                    help="expert-parallel size of the rollout (default: the training size; another value re-homes "
+                         "the experts in the reshard plan)")
     ap.add_argument("--model-override", action="append", default=[], metavar="KEY=INT",
                     help="override an integer field of the model catalogue entry (development only)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
@@ -174,6 +178,8 @@ def main():
     initialize_model_parallel(train_tp, 1, 1)
     parallelism = (f"train tp{train_tp} x dp{world // train_tp} (sequence parallel) -> "
                    f"rollout tp{infer_tp} x dp{world // infer_tp}") if train_tp > 1 else f"dp{world}"
+    if args.train_ep > 1:
+        parallelism += f", experts ep{args.train_ep} -> rollout ep{args.infer_ep or args.train_ep}"
 
     # micro-batches grow with the training TP size: the activations of a packed micro-batch are
     # sharded over the TP group, so per-GPU memory and per-GPU GEMM sizes stay those of TP1
@@ -191,6 +197,8 @@ def main():
         lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, adam_beta1=0.9, adam_beta2=0.95,
         stage="ray_grpo", train_iters=10 ** 6, seed=1234, bf16=True, use_distributed_optimizer=True,
         tensor_model_parallel_size=train_tp, sequence_parallel=train_tp > 1,
+        expert_model_parallel_size=args.train_ep, moe_tp_extend_ep=bool(args.train_ep > 1 and train_tp > 1),
+        moe_p2p_capacity_factor=2.0 if args.train_ep > 1 else 0.0,
         recompute_granularity="full", recompute_method="block" if args.keep_layers else None,
         recompute_num_layers=max(0, (args.layers or catalogue[args.model]["num_layers"]) - args.keep_layers)
         if args.keep_layers else None, recompute_activation_function=True,
@@ -202,7 +210,8 @@ def main():
         use_dynamic_bsz=True, max_packing_token_size=pack_tokens,
         ref_max_packing_token_size=fwd_pack_tokens, log_max_throughput=False))
     gen = GenerateConfig(dict(
-        infer_tensor_parallel_size=infer_tp, max_num_seqs=args.prompts_per_gpu * n * infer_tp,
+        infer_tensor_parallel_size=infer_tp, infer_expert_parallel_size=args.infer_ep or args.train_ep,
+        max_num_seqs=args.prompts_per_gpu * n * infer_tp,
         max_model_len=max_len, max_num_batched_tokens=8192, kv_block_size=16, enable_prefix_caching=False,
         enforce_eager=bool(args.eager), gpu_memory_utilization=0.9, offload_train_grad=True,
         sampling_config=dict(max_tokens=args.max_response, temperature=1.0, top_k=-1, top_p=1.0, seed=None)))

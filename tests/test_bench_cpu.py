@@ -57,3 +57,11 @@ def test_bench_baseline_layout_eight_ranks():
     out = _bench(8, "--steps", "1", "--warmup", "1", "--model-override", "num_query_groups=4")
     assert out["n_gpus"] == 8 and out["config"]["train_tp"] == 4 and out["config"]["rollout_tp"] == 2
     assert out["config"]["parallelism"].startswith("train tp4 x dp2") and out["value"] > 0
+
+
+def test_bench_expert_parallel_model_with_rehomed_rollout():
+    """An expert model through the benchmark driver: training EP2, rollout with every expert on each rank."""
+    out = _bench(2, "--layout", "dp", "--steps", "1", "--warmup", "1", "--train-ep", "2", "--infer-ep", "1",
+                 "--model-override", "num_experts=4", "--model-override", "moe_router_topk=2",
+                 "--model-override", "moe_ffn_hidden_size=16")
+    assert out["n_gpus"] == 2 and "experts ep2 -> rollout ep1" in out["config"]["parallelism"] and out["value"] > 0
