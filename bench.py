@@ -175,7 +175,8 @@ def main():
     train_tp, infer_tp = args.train_tp or train_tp, args.infer_tp or infer_tp
     if world % train_tp or world % infer_tp:
         raise SystemExit(f"TP sizes {train_tp}/{infer_tp} do not divide {world} GPUs")
-    initialize_model_parallel(train_tp, 1, 1)
+    initialize_model_parallel(train_tp, 1, 1, expert_model_parallel_size=args.train_ep,
+                              moe_tp_extend_ep=bool(args.train_ep > 1 and train_tp > 1))
     parallelism = (f"train tp{train_tp} x dp{world // train_tp} (sequence parallel) -> "
                    f"rollout tp{infer_tp} x dp{world // infer_tp}") if train_tp > 1 else f"dp{world}"
     if args.train_ep > 1:
