@@ -55,7 +55,8 @@ _MAX_CHUNK = 64 << 20                              # contiguous copies are cut i
 class Slot:
     start: int            # element offset inside the owning rank's flat parameter buffer
     shape: Tuple[int, ...]
-    buf: int = 0          # which of the rank's flat buffers (0: trainable dense, then experts, frozen)
+    buf: int = 0          # which of the rank's flat buffers (0: trainable dense, then experts, frozen, fp32)
+    esz: int = 0          # bytes per element (0: the plan's default), e.g. 4 for an fp32 router in a bf16 model
 
 
 @dataclass
@@ -163,6 +164,7 @@ class ReshardPlan:
     tensors: Dict[str, Tuple[int, Tuple[int, ...]]]   # global name -> (byte offset in dst, shape)
     nbytes: int
     desc_buf: Optional[List[int]] = None              # source buffer index of every descriptor (None: all 0)
+    esz_of: Optional[Dict[str, int]] = None           # element size of tensors that differ from the plan's default
 
     def buf_of(self, i: int) -> int:
         return self.desc_buf[i] if self.desc_buf is not None else 0
@@ -201,6 +203,9 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
         desc.extend(items)
         desc_buf.extend([buf] * len(items))
 
+    esz_of: Dict[str, int] = {}
+    default_esz = esz
+
     def place(name: str, shape: Tuple[int, ...]) -> int:
         nonlocal cursor
         off = (cursor + 255) // 256 * 256
@@ -209,10 +214,14 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
             n *= d
         cursor = off + n
         tensors[name] = (off, tuple(shape))
+        if esz != default_esz:
+            esz_of[name] = esz
         return off
 
     def emit(gname: str, lname: str, stage: int) -> None:
+        nonlocal esz
         slot = stage_slots[stage][lname]
+        esz = slot.esz or default_esz
         kind = partition_kind(lname)
         shape = tuple(slot.shape)
         inner = esz
@@ -257,7 +266,9 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
 
     def emit_experts(gname: str, lname: str, stage: int, layer: int) -> None:
         """Gather the hosted experts of ``layer`` from their training owners into rollout slot order."""
+        nonlocal esz
         slot = stage_slots[stage][lname]
+        esz = slot.esz or default_esz
         ids = list(experts.hosted(layer))
         e_t, n_loc = experts.e_local_train, len(ids)
         if lname.endswith("experts.weight1"):                # [H, E_local * 2F]: one column block per expert
@@ -294,7 +305,8 @@ def build_plan(cfg: TransformerConfig, train: RankLayout, infer_tp: int, rank: i
         for lname in ("decoder.final_layernorm.weight", "output_layer.weight"):
             if lname in table:
                 emit(lname, lname, stage)
-    return ReshardPlan(desc, tensors, (cursor + 255) // 256 * 256, desc_buf if any(desc_buf) else None)
+    return ReshardPlan(desc, tensors, (cursor + 255) // 256 * 256, desc_buf if any(desc_buf) else None,
+                       esz_of or None)
 
 
 def execute_plan_torch(plan: ReshardPlan, sources: Dict[int, torch.Tensor], dst: torch.Tensor) -> None:
@@ -321,7 +333,10 @@ def weights_from_buffer(cfg: TransformerConfig, infer_tp: int, tp_rank: int, pla
         n = 1
         for d in shape:
             n *= d
-        return buf[off:off + n * buf.new_empty(0, dtype=dtype).element_size()].view(dtype).view(shape)
+        dt = dtype
+        if plan.esz_of and name in plan.esz_of:
+            dt = {4: torch.float32, 2: torch.bfloat16 if dtype != torch.float16 else torch.float16}[plan.esz_of[name]]
+        return buf[off:off + n * buf.new_empty(0, dtype=dt).element_size()].view(dt).view(shape)
 
     def fold(prefix: str) -> None:
         """``W += (alpha / r) B A`` on the rollout copy of an adapted linear (fp32 sum, one rounding)."""
@@ -546,6 +561,8 @@ class Resharder:
         frozen = getattr(self.ddp, "frozen_buffer", None)
         if frozen is not None:
             out.append(frozen)
+        # parameters kept in fp32 inside a 16-bit model (routers): their buffer comes last
+        out += [b for b in self.ddp.buffers if b.param_dtype != dt]
         return out
 
     def _home(self, buf):
@@ -562,7 +579,8 @@ class Resharder:
         mine: Dict[str, Slot] = {}
         for bi, b in enumerate(bufs):
             for sl in b.slots:
-                mine[sl.name] = Slot(sl.start, tuple(sl.shape), bi)
+                mine[sl.name] = Slot(sl.start, tuple(sl.shape), bi,
+                                     0 if b.param_dtype == bufs[0].param_dtype else b.param_data.element_size())
         use_arena = self._use_arena()
         bases = [self._home(b).offset_of(b.param_data) if use_arena else 0 for b in bufs]
         stage = ps.rank_in("pp")

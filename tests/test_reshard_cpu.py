@@ -241,3 +241,49 @@ def test_plan_carries_adapters_and_rollout_folds_them():
                 for got, want in ((w.layers[li].qkv_w, want_qkv), (w.layers[li].o_w, want_proj),
                                   (w.layers[li].gate_up_w, want_fc1), (w.layers[li].down_w, want_fc2)):
                     assert torch.allclose(got, want, atol=1e-6), (tp_i, r, li)
+
+
+def test_plan_mixes_element_sizes_and_buffers():
+    """A bf16 model whose routers stay fp32 in a flat buffer of their own: the plan addresses both buffers and
+    sizes every tensor by its own element size."""
+    from mindspeed_rl_b200.reshard.planner import ExpertPlacement
+
+    cfg = _moe_cfg()
+    full = GPTModel(cfg, seed=9).state_dict()
+    e, ep_t = cfg.num_experts, 2
+    train = RankLayout(2, ep=ep_t)
+    layers = stage_layers(cfg.num_layers, 1)
+    sources, table = {}, None
+    for r in range(2):
+        st = _expert_shard(full, cfg, ep_t, train.expert_coords(r)["ep"])
+        main = {k: v.to(torch.bfloat16) for k, v in st.items() if not k.endswith("router.weight")}
+        fp32 = {k: v for k, v in st.items() if k.endswith("router.weight")}
+        slots, off, chunks = {}, 0, []
+        for k, v in main.items():
+            slots[k] = Slot(off, tuple(v.shape), 0)
+            chunks.append(v.reshape(-1))
+            off += v.numel()
+        sources[(r, 0)] = torch.cat(chunks).contiguous().view(torch.uint8)
+        off, chunks = 0, []
+        for k, v in fp32.items():
+            slots[k] = Slot(off, tuple(v.shape), 1, 4)
+            chunks.append(v.reshape(-1))
+            off += v.numel()
+        sources[(r, 1)] = torch.cat(chunks).contiguous().view(torch.uint8)
+        table = slots
+    hosted = lambda layer: list(range(e))                      # every rollout rank hosts all experts
+    src = lambda ep_index, stage: train.rank_of(dp=ep_index)
+    for r in range(2):
+        plan = build_plan(cfg, train, 1, r, [table], layers, lambda rank, buf=0: 0, esz=2,
+                          experts=ExpertPlacement(e // ep_t, hosted, src))
+        assert plan.desc_buf is not None and plan.esz_of
+        dst = torch.zeros(plan.nbytes, dtype=torch.uint8)
+        execute_plan_torch(plan, sources, dst)
+        w = weights_from_buffer(cfg, 1, 0, plan, dst, torch.bfloat16,
+                                moe_builder=lambda li, t: (t(f"decoder.layers.{li}.mlp.router.weight"),
+                                                           t(f"decoder.layers.{li}.mlp.experts.weight1")))
+        for li in range(cfg.num_layers):
+            router, w1 = w.layers[li].moe
+            assert router.dtype == torch.float32 and torch.equal(router, full[f"decoder.layers.{li}.mlp.router.weight"])
+            assert w1.dtype == torch.bfloat16 and torch.equal(
+                w1, full[f"decoder.layers.{li}.mlp.experts.weight1"].to(torch.bfloat16))
