@@ -86,14 +86,17 @@ class P2PDispatcher:
         check(lib.msrl_moe_p2p_publish(self._table_ptrs, ptr(plan_src.counts), c_int(self.n_total), c_int(self.me),
                                        c_int(self.ep), st), "moe_p2p_publish")
         self.arena.barrier(self.ranks)
+        # the verdict is read on the host, which a stream capture (decode steps replayed from a CUDA graph)
+        # does not allow: there the overflow goes to the status word and is raised at the stage boundary
+        ask = self.fallback and not torch.cuda.is_current_stream_capturing()
         counts_l = guard.empty(self.e_local, dtype=torch.int32, device=dev)
         offsets_l = guard.empty(self.e_local + 1, dtype=torch.int32, device=dev)
         tiles = guard.empty(self.cap_rows // K.PAD, dtype=torch.int32, device=dev)
         check(lib.msrl_moe_p2p_layout(ptr(self.table), c_int(self.ep), c_int(self.e_local), c_int(self.me),
                                       c_int(self.cap_rows), ptr(self.my_base), ptr(counts_l), ptr(offsets_l),
-                                      ptr(tiles), None if self.fallback else ptr(self.arena.status),
-                                      ptr(self.over) if self.fallback else None, st), "moe_p2p_layout")
-        if self.fallback and int(self.over.item()):
+                                      ptr(tiles), None if ask else ptr(self.arena.status),
+                                      ptr(self.over) if ask else None, st), "moe_p2p_layout")
+        if ask and int(self.over.item()):
             self.over.zero_()
             self.overflows += 1
             return None
