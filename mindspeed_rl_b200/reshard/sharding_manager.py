@@ -79,7 +79,7 @@ class ShardingManager:
                  offload_train_optimizer: bool = False, offload_train_grad: bool = False,
                  offload_train_param: bool = False, num_kv_blocks: Optional[int] = None,
                  gpu_memory_utilization: float = 0.5, resharder=None,
-                 build_weights: Optional[Callable] = None):
+                 build_weights: Optional[Callable] = None, headroom_bytes: int = 2 << 30):
         self.train_model = train_model
         self.core = train_model.module if hasattr(train_model, "module") else train_model
         self.engine = rollout_engine
@@ -89,6 +89,7 @@ class ShardingManager:
         self.offload_train_param = offload_train_param
         self.num_kv_blocks = num_kv_blocks
         self.gpu_memory_utilization = gpu_memory_utilization
+        self.headroom_bytes = int(headroom_bytes)     # left free beside the KV cache for the forward's temporaries
         self.resharder = resharder           # reshard.planner.Resharder when layouts differ
         self.build_weights = build_weights
         ddp = train_model if isinstance(train_model, DistributedDataParallel) else None
@@ -105,7 +106,7 @@ class ShardingManager:
         if dev.type != "cuda":
             return 256
         free, total = torch.cuda.mem_get_info(dev)
-        budget = min(free - (2 << 30), int(total * self.gpu_memory_utilization))
+        budget = min(free - self.headroom_bytes, int(total * self.gpu_memory_utilization))
         blocks = max(int(budget // self.engine.kv_bytes_per_block()), 16)
         comm = getattr(self.engine, "comm", None)
         if comm is not None and comm.world_size > 1 and comm.group is not None:

@@ -273,7 +273,10 @@ class IntegratedWorker(BaseWorker):
         self.sharding_manager = ShardingManager(
             self.model, self.engine, self.optimizer, offload_train_optimizer=gc.offload_train_optimizer,
             offload_train_grad=gc.offload_train_grad, offload_train_param=gc.offload_train_param,
-            gpu_memory_utilization=gc.gpu_memory_utilization, resharder=resharder)
+            gpu_memory_utilization=gc.gpu_memory_utilization, resharder=resharder,
+            # expert layers permute every token top-k times through several temporaries per forward
+            headroom_bytes=(2 << 30) + (16 * gc.max_num_batched_tokens * tcfg.moe_router_topk * tcfg.hidden_size * 2
+                                        if tcfg.is_moe else 0))
         self.sampling_params = SamplingParams.from_config(gc.sampling_config, n=rl.n_samples_per_prompt,
                                                           **self.sampling_overrides)
         self.initialized = True
