@@ -248,16 +248,19 @@ def rope_(qkv: torch.Tensor, layout: QKVLayout, positions: torch.Tensor, table: 
 # ------------------------------------------------------------------------------------------------
 # SwiGLU
 # ------------------------------------------------------------------------------------------------
-def swiglu_fwd(gate_up: torch.Tensor) -> torch.Tensor:
+def swiglu_fwd(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up`` of ``[..., gate | up]``; ``out`` (contiguous, ``[..., F]``) receives the result."""
     f = gate_up.shape[-1] // 2
     rows = gate_up.numel() // (2 * f)
     if _lib.use_kernels(gate_up):
         x = gate_up.contiguous()
-        out = guard.empty(*x.shape[:-1], f, device=x.device, dtype=x.dtype)
+        if out is None:
+            out = guard.empty(*x.shape[:-1], f, device=x.device, dtype=x.dtype)
         check(_lib.load().msrl_swiglu_fwd(ptr(x), ptr(out), c_ll(rows), c_int(f), stream()), "swiglu_fwd")
         return out
     g, u = gate_up.float().split(f, dim=-1)
-    return (torch.nn.functional.silu(g) * u).to(gate_up.dtype)
+    y = (torch.nn.functional.silu(g) * u).to(gate_up.dtype)
+    return y if out is None else out.copy_(y)
 
 
 def swiglu_bwd(gate_up: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:

@@ -73,8 +73,15 @@ class MoEWeights:
             e = self.num_local
             rt = disp.dispatch(x, phys)
             if rt is not None:       # None: some member's slab would overflow, all members use the collectives below
-                gu = K.grouped_gemm(disp.slab, rt.plan, self.w1.reshape(h, e * 2 * f), True, 2 * f, 0, 2 * f)
-                K.grouped_gemm(ops.swiglu_fwd(gu), rt.plan, self.w2.reshape(e * f, h), True, 0, f, h, out=disp.out_slab)
+                # slab-sized intermediates come from grow-only scratch shared by all layers (and by all
+                # captured decode graphs, which would otherwise each keep a private copy)
+                from ..ops.elementwise import _workspace
+                rows = disp.slab.shape[0]
+                gu = _workspace("rollout_moe_gu", rows * 2 * f, x.device, x.dtype)[:rows * 2 * f].view(rows, 2 * f)
+                act = _workspace("rollout_moe_act", rows * f, x.device, x.dtype)[:rows * f].view(rows, f)
+                K.grouped_gemm(disp.slab, rt.plan, self.w1.reshape(h, e * 2 * f), True, 2 * f, 0, 2 * f, out=gu)
+                K.grouped_gemm(ops.swiglu_fwd(gu, out=act), rt.plan, self.w2.reshape(e * f, h), True, 0, f, h,
+                               out=disp.out_slab)
                 out, _ = disp.combine(rt, top_p)
                 return self._add_shared(out, x, comm)
         flat = phys.reshape(-1)
