@@ -57,6 +57,56 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+// One-pass form for rows that fit the block's registers (H <= THREADS * VPT * 8): the row is read
+// once into registers (with the optional residual added and the rounded sum written back), reduced,
+// scaled and stored; no shared-memory staging of the row.
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_fwd_regs_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                        __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd_out, int H,
+                        float eps) {
+  __shared__ float red[32];
+  const long long r = blockIdx.x;
+  const int nvec = H >> 3;
+  float f[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < nvec) {
+      unpack8(ld8(x + r * H + i * 8), f[j]);
+      if (res != nullptr) {
+        float g[8];
+        unpack8(ld8(res + r * H + i * 8), g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[j][k] += g[k];
+        if (sum_out != nullptr) {
+          const bf16x8 s = pack8(f[j]);
+          st8(sum_out + r * H + i * 8, s);
+          unpack8(s, f[j]);  // normalise exactly what was stored
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += f[j][k] * f[j][k];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[r] = rstd;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    if (i < nvec) {
+      float wv[8], o[8];
+      unpack8(ld8(w + i * 8), wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = f[j][k] * rstd * wv[k];
+      st8(y + r * H + i * 8, pack8(o));
+    }
+  }
+}
+
 // RMSNorm backward, stage 1: each block walks rows blockIdx.x, +gridDim.x, ... and
 //   dx = rstd * (dy*w) - x * rstd^3 * mean(dy*w*x)   (optionally dx += dres)
 // while keeping partial sums of dw = sum_rows dy * x * rstd in registers; the partials go to
@@ -352,6 +402,18 @@ MSRL_API int msrl_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               float* rstd, long long rows, int H, float eps, cudaStream_t st) {
   if (rows == 0) return 0;
   if (H % 8 != 0 || H > 16384) return (int)cudaErrorInvalidValue;
+  if (H <= 128 * 4 * 8) {        // the usual hidden sizes: the row lives in registers
+    rmsnorm_fwd_regs_kernel<128, 4><<<(unsigned)rows, 128, 0, st>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+        (__nv_bfloat16*)y, (__nv_bfloat16*)sum_out, rstd, H, eps);
+    MSRL_LAUNCH_CHECK();
+  }
+  if (H <= 256 * 4 * 8) {
+    rmsnorm_fwd_regs_kernel<256, 4><<<(unsigned)rows, 256, 0, st>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+        (__nv_bfloat16*)y, (__nv_bfloat16*)sum_out, rstd, H, eps);
+    MSRL_LAUNCH_CHECK();
+  }
   size_t smem = (size_t)H * sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {

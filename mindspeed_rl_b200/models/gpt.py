@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -318,6 +318,11 @@ def _mla_backward(sa, x1g: torch.Tensor, meta: PackedMeta, comm: TPComm, dh1: to
     return comm.gather_seq_bwd(grads[0])
 
 
+# Called with a layer right after its backward (one slot: the data-parallel wrapper installs itself while the
+# last micro-batch of a step runs, so that bucketed gradient reduction overlaps the rest of the backward).
+grads_ready_hook: List[Optional[Callable]] = [None]
+
+
 class _LayerFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h: torch.Tensor, layer: TransformerLayer, meta: PackedMeta):
@@ -354,6 +359,9 @@ class _LayerFn(torch.autograd.Function):
                 saved = swapper_for(dh2.device).restore(saved)
         with torch.no_grad():
             dh = layer_backward(layer, saved, meta, dh2.contiguous())
+        hook = grads_ready_hook[0]
+        if hook is not None:
+            hook(layer)          # this layer's gradients are final for the micro-batch: their reduction may start
         return dh, None, None
 
 

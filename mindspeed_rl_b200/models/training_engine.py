@@ -380,8 +380,10 @@ class TrainingEngine:
                                            lambda m, h, c=None: self._stage_forward(m, h, self.want_entropy, c),
                                            loss_backward)
             return sums
-        for rows in parts:
+        for i, rows in enumerate(parts):
             mb = MicroBatch(data, rows, self.pad_multiple, self._total_align()).to(self.device)
+            if i == n_micro - 1 and hasattr(self.model, "begin_last_microbatch"):
+                self.model.begin_last_microbatch()     # overlapped gradient reduction, when enabled
             loss_backward(mb, self._run_model(mb, want_entropy=self.want_entropy))
         return sums
 

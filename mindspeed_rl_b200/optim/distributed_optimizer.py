@@ -74,8 +74,13 @@ class DistributedOptimizer:
                  eps: float = 1e-8, weight_decay: float = 0.01, clip_grad: float = 1.0,
                  dp_group=None, dp_rank: int = 0, model_parallel_group=None,
                  offload_to_host: bool = False, swap_chunks: int = 16,
-                 norm_duplicate_filter=None, tp_rank: int = 0, reuse_fp32_param: bool = False):
+                 norm_duplicate_filter=None, tp_rank: int = 0, reuse_fp32_param: bool = False,
+                 overlap_param_gather: bool = False, gather_chunks: int = 8):
         self.buffers = buffers
+        # update the shard chunk by chunk and fetch finished chunks from the peers meanwhile
+        self.overlap_param_gather = bool(overlap_param_gather) and not offload_to_host
+        self.gather_chunks = max(1, int(gather_chunks))
+        self._gatherers: Dict[int, object] = {}
         # bf16 parameters double as the upper half of the fp32 master weights: only a 16-bit residual
         # is kept per element (2 bytes instead of 4; reference flag ``reuse_fp32_param``,
         # docs/zh/features/reuse_fp32_param.md in MindSpeed)
@@ -185,6 +190,9 @@ class DistributedOptimizer:
                                 p16 is None)
             elif self.reuse_fp32_param:
                 self._step_reuse(st, grad, p16, g)
+            elif self.overlap_param_gather and buf.dp_size > 1 and (buf.group is not None or self.dp_group is not None):
+                self._step_pipelined(buf, st, grad, p16, g, s)
+                continue
             else:
                 ops.adamw_step(st["master"], st["exp_avg"], st["exp_avg_sq"], grad, p16, g["lr"],
                                g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"],
@@ -193,6 +201,26 @@ class DistributedOptimizer:
                     buf.param_data[s:e].copy_(st["master"])
             buf.gather_params(self.dp_group)
         return True, self._norm.clone(), 0
+
+    def _step_pipelined(self, buf, st, grad, p16, g, s: int) -> None:
+        """AdamW on the shard in chunks, each chunk's all-gather launched behind its update."""
+        from ..parallel.ddp import ChunkedParamGather
+
+        gatherer = self._gatherers.get(id(buf))
+        if gatherer is None or gatherer.buf.param_data.data_ptr() != buf.param_data.data_ptr():
+            gatherer = self._gatherers[id(buf)] = ChunkedParamGather(buf, self.dp_group, self.gather_chunks)
+        for c, (lo, hi) in enumerate(gatherer.bounds):
+            if self.reuse_fp32_param:
+                self._step_reuse({k: (v[lo:hi] if torch.is_tensor(v) else v) for k, v in st.items()}, grad[lo:hi],
+                                 p16[lo:hi], g)
+            else:
+                ops.adamw_step(st["master"][lo:hi], st["exp_avg"][lo:hi], st["exp_avg_sq"][lo:hi], grad[lo:hi],
+                               p16[lo:hi] if p16 is not None else None, g["lr"], g["betas"][0], g["betas"][1],
+                               g["eps"], g["weight_decay"], self.step_count, self._coef)
+                if p16 is None:
+                    buf.param_data[s + lo:s + hi].copy_(st["master"][lo:hi])
+            gatherer.launch(c)
+        gatherer.finish()
 
     # ---- fp32 master = (bf16 parameter, int16 residual) ------------------------------------------
     @staticmethod

@@ -79,7 +79,8 @@ class OptimizerConfig:
             buffers, lr=lr, betas=(self.adam_beta1, self.adam_beta2), eps=self.adam_eps,
             weight_decay=self.weight_decay, clip_grad=self.clip_grad, dp_group=dp_group, dp_rank=dp_rank,
             model_parallel_group=model_parallel_group, offload_to_host=self.swap_optimizer,
-            swap_chunks=self.swap_optimizer_times, tp_rank=tp_rank, reuse_fp32_param=self.reuse_fp32_param)
+            swap_chunks=self.swap_optimizer_times, tp_rank=tp_rank, reuse_fp32_param=self.reuse_fp32_param,
+            overlap_param_gather=self.overlap_param_gather)
         total = total_steps if total_steps is not None else (self.lr_decay_iters or self.train_iters or 0)
         if warmup_steps is not None:
             warm = warmup_steps

@@ -195,6 +195,53 @@ class ParamAndGradBuffer:
             p.main_grad = self.grad_data[slot.start:slot.start + slot.numel].view(slot.shape) \
                 if self.grad_data is not None and self.grad_data.numel() else None
 
+    # ---- buckets: contiguous ranges of whole parameters, in backward order ---------------------------
+    def make_buckets(self, bucket_numel: int) -> List[Tuple[int, int]]:
+        """Cut the buffer into ranges of at least ``bucket_numel`` elements that end on parameter
+        boundaries, last parameters first (the order in which the backward finishes them)."""
+        out: List[Tuple[int, int]] = []
+        end = self.numel
+        start = end
+        for slot in reversed(self.slots):
+            start = slot.start
+            if end - start >= bucket_numel:
+                out.append((start, end))
+                end = start
+        if end > 0:
+            out.append((0, end))
+        self.bucket_ranges = out
+        self.bucket_of: Dict[int, int] = {}
+        for pi, slot in enumerate(self.slots):
+            for bi, (s0, e0) in enumerate(out):
+                if s0 <= slot.start < e0:
+                    self.bucket_of[pi] = bi
+        return out
+
+    def reduce_bucket(self, bi: int, group=None, average: bool = True, async_op: bool = False):
+        """Reduce one bucket over the data-parallel group so that EVERY rank holds the reduced values of
+        the range (a superset of what the distributed optimizer needs of it).  Peer-mapped buffers run
+        the pull reduce-scatter and all-gather kernels on the range; otherwise one all-reduce, whose
+        handle is returned when ``async_op``."""
+        group = self.group if self.group is not None else group
+        s0, e0 = self.bucket_ranges[bi]
+        view = self.grad_data[s0:e0]
+        scale = self.grad_scale if average else 1.0
+        if self.dp_size == 1 or group is None:
+            if self.is_expert and scale != 1.0:
+                view.mul_(scale)
+            return None
+        if self.grad_arena is not None and (e0 - s0) % (8 * self.dp_size) == 0:
+            ranks = self.grad_arena.team_ranks(group)
+            per = (e0 - s0) // self.dp_size
+            r = dist.get_rank(group)
+            self.grad_arena.align(group)
+            self.grad_arena.reduce_scatter(view, view[r * per:(r + 1) * per], scale=scale, ranks=ranks)
+            self.grad_arena.all_gather_inplace(view, ranks=ranks)
+            return None
+        if scale != 1.0:
+            view.mul_(scale)
+        return dist.all_reduce(view, group=group, async_op=async_op)
+
     # ---- gradient reduction over the data-parallel group --------------------------------------------
     def reduce_grads(self, group=None, average: bool = True, to_shards: bool = False) -> None:
         """Sum (or average) gradients over DP.  ``to_shards=True`` leaves each rank with the
@@ -237,6 +284,72 @@ class ParamAndGradBuffer:
             return
         dist.all_gather_into_tensor(self.param_data, self.param_data[r * per:(r + 1) * per].clone(),
                                     group=group)
+
+
+class ChunkedParamGather:
+    """Parameter all-gather pipelined against the optimizer's update (``overlap_param_gather``; reference
+    switch: ``mindspeed_rl/config_cls/megatron_config.py:353``).
+
+    The distributed optimizer updates its contiguous shard chunk by chunk; as soon as chunk ``c`` is
+    written on every rank, chunk ``c`` of every shard is fetched by all the others on a side stream
+    (peer-mapped buffers: one copy-plan pull kernel between two device barriers; otherwise an
+    asynchronous ``all_gather`` into the chunks' places), while the update of chunk ``c + 1`` runs.
+    ``finish`` joins the side stream: when the optimizer step returns, every rank holds all parameters,
+    exactly as after the plain one-shot all-gather."""
+
+    def __init__(self, buf: "ParamAndGradBuffer", group, chunks: int = 8):
+        self.buf, self.group = buf, buf.group if buf.group is not None else group
+        self.world = buf.dp_size
+        self.me = dist.get_rank(self.group)
+        self.per = buf.numel // buf.dp_size
+        esz = buf.param_data.element_size()
+        unit = 16 // esz * 8                                   # chunk boundaries on 128-byte multiples
+        n = max(1, min(chunks, self.per // unit))
+        step = (self.per // n + unit - 1) // unit * unit
+        self.bounds = [(lo, min(lo + step, self.per)) for lo in range(0, self.per, step)]
+        self.side = torch.cuda.Stream() if buf.device.type == "cuda" else None
+        self.handles: list = []
+        self._plans: Dict[int, tuple] = {}
+
+    def launch(self, c: int) -> None:
+        """Chunk ``c`` of this rank's shard has been updated (on the current stream)."""
+        buf, (lo, hi) = self.buf, self.bounds[c]
+        arena = buf.param_arena
+        if arena is not None:
+            from .symm import plan_to_device
+
+            if c not in self._plans:
+                esz = buf.param_data.element_size()
+                base = arena.offset_of(buf.param_data)
+                ranks = arena.team_ranks(self.group)
+                desc = [(ranks[r], base + (r * self.per + lo) * esz, (r * self.per + lo) * esz, 1, (hi - lo) * esz, 0, 0)
+                        for r in range(self.world) if r != self.me]
+                self._plans[c] = (plan_to_device(desc, buf.device), ranks)
+            (plan, n_desc), ranks = self._plans[c]
+            self.side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.side):
+                arena.barrier(ranks)          # every member has written its chunk c
+                arena.copy_plan(plan, n_desc, buf.param_data.view(torch.uint8), sync=False)
+            return
+        outs = [buf.param_data[r * self.per + lo:r * self.per + hi] for r in range(self.world)]
+        mine = outs[self.me].clone()
+        if self.side is not None:
+            self.side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.side):
+                dist.all_gather(outs, mine, group=self.group)
+        else:
+            self.handles.append(dist.all_gather(outs, mine, group=self.group, async_op=True))
+
+    def finish(self) -> None:
+        if self.side is not None:
+            if self.buf.param_arena is not None:
+                with torch.cuda.stream(self.side):
+                    # nobody runs ahead into the next write of a chunk that a peer is still reading
+                    self.buf.param_arena.barrier(self.buf.param_arena.team_ranks(self.group))
+            torch.cuda.current_stream().wait_stream(self.side)
+        for h in self.handles:
+            h.wait()
+        self.handles = []
 
 
 def is_expert_param(name: str, p: nn.Parameter) -> bool:
@@ -344,7 +457,84 @@ class DistributedDataParallel(nn.Module):
                     out.append(p.main_grad)
         return out
 
+    # ---- gradient reduction overlapped with the backward (``overlap_grad_reduce``) ----------------------
+    def enable_grad_overlap(self, bucket_numel: int = 40_000_000) -> None:
+        """Cut the buffers into buckets of whole parameters.  While the last micro-batch of a step runs
+        (``begin_last_microbatch``), the bucket of a layer is reduced over the data-parallel group as soon
+        as the layer's backward has finished, on a side stream (CUDA) or as an asynchronous collective
+        (CPU), while the backward of the earlier layers goes on; ``finish_grad_sync`` waits for those
+        reductions and reduces what is left (embedding, head, final norm).  Reference switch:
+        ``overlap_grad_reduce`` (``mindspeed_rl/config_cls/megatron_config.py:343``)."""
+        self._home: Dict[int, Tuple[int, int]] = {}
+        for bi, b in enumerate(self.buffers):
+            b.make_buckets(bucket_numel)
+            for pi, p in enumerate(b.params):
+                self._home[id(p)] = (bi, pi)
+        self.overlap_grad_reduce = True
+        self._overlap = None
+
+    def begin_last_microbatch(self) -> None:
+        """Arm the overlapped reduction for the backward that follows (no-op unless enabled)."""
+        if not getattr(self, "overlap_grad_reduce", False):
+            return
+        from ..models import gpt as _gpt
+
+        pending = []
+        for b in self.buffers:
+            count = [0] * len(b.bucket_ranges)
+            for pi in range(len(b.params)):
+                count[b.bucket_of[pi]] += 1
+            pending.append(count)
+        cuda = self.buffers[0].device.type == "cuda"
+        self._overlap = dict(pending=pending, launched=set(), handles=[],
+                             side=(getattr(self, "_side_stream", None) or torch.cuda.Stream()) if cuda else None)
+        if cuda:
+            self._side_stream = self._overlap["side"]
+        _gpt.grads_ready_hook[0] = self._layer_grads_ready
+
+    def _layer_grads_ready(self, layer: nn.Module) -> None:
+        st = self._overlap
+        if st is None:
+            return
+        for p in layer.parameters():
+            home = self._home.get(id(p))
+            if home is None:
+                continue
+            bi, pi = home
+            k = self.buffers[bi].bucket_of[pi]
+            st["pending"][bi][k] -= 1
+            if st["pending"][bi][k] == 0:
+                self._launch_bucket(bi, k)
+
+    def _launch_bucket(self, bi: int, k: int) -> None:
+        st, b = self._overlap, self.buffers[bi]
+        st["launched"].add((bi, k))
+        if st["side"] is not None:
+            st["side"].wait_stream(torch.cuda.current_stream())      # the bucket's gradients are complete
+            with torch.cuda.stream(st["side"]):
+                b.reduce_bucket(k, self.dp_group, average=True)
+        else:
+            h = b.reduce_bucket(k, self.dp_group, average=True, async_op=True)
+            if h is not None:
+                st["handles"].append(h)
+
+    def _finish_overlap(self) -> bool:
+        """Wait for the reductions started during the backward.  Returns True when the overlapped mode
+        was armed (the caller then reduces only the buckets that were not launched)."""
+        st = getattr(self, "_overlap", None)
+        if st is None:
+            return False
+        from ..models import gpt as _gpt
+
+        _gpt.grads_ready_hook[0] = None
+        if st["side"] is not None:
+            torch.cuda.current_stream().wait_stream(st["side"])
+        for h in st["handles"]:
+            h.wait()
+        return True
+
     def finish_grad_sync(self, to_shards: bool = False) -> None:
+        overlapped = self._finish_overlap()      # before anything else touches the gradient buffers
         if getattr(self, "tp_size", 1) > 1 and self.tp_group is not None:
             grads = self._tp_partial_grads()
             if grads:
@@ -354,5 +544,12 @@ class DistributedDataParallel(nn.Module):
                 for g in grads:
                     g.copy_(flat[off:off + g.numel()].view_as(g))
                     off += g.numel()
+        if overlapped:
+            st, self._overlap = self._overlap, None
+            for bi, b in enumerate(self.buffers):
+                for k in range(len(b.bucket_ranges)):
+                    if (bi, k) not in st["launched"]:
+                        b.reduce_bucket(k, self.dp_group, average=True)
+            return
         for b in self.buffers:
             b.reduce_grads(self.dp_group, average=True, to_shards=to_shards)

@@ -187,6 +187,12 @@ class IntegratedWorker(BaseWorker):
                                              **expert_replica_groups(ps, tcfg))
         self._maybe_attach_fused_tp()
         self.model.attach_tensor_parallel(ps.group("tp"), tp, bool(ac.sequence_parallel))
+        if getattr(ac, "overlap_grad_reduce", False) and dp > 1 and ps.size("pp") == 1 \
+                and not int(getattr(tcfg, "moe_p2p_dispatch_rows", 0) or 0):
+            # bucketed gradient reduction on a side stream while the backward continues (not with pipeline
+            # schedules, and not beside the peer-memory expert dispatch, whose device barriers involve the
+            # same pairs of ranks on the main stream)
+            self.model.enable_grad_overlap()
         iters = ac.train_iters or 1
         n_updates = iters * max(1, (ac.global_batch_size * rl.n_samples_per_prompt) // max(rl.mini_batch_size, 1))
         samples = n_updates * rl.mini_batch_size            # the schedule is stepped in samples

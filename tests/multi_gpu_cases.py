@@ -415,6 +415,58 @@ def case_buffer_release(rank, world):
         assert torch.all(buf.param_data[r * per:(r + 1) * per].float() == float(r + 1))
 
 
+def case_overlap(rank, world):
+    """Data-parallel training steps with the gradient reduction started from the layers' backward and the
+    parameter all-gather pipelined behind the optimizer's chunks, both on peer-mapped buffers, against the
+    plain path (library collectives after the backward) on ordinary allocations."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    from mindspeed_rl_b200.parallel.symm import get_arena, init_arena
+
+    ps = initialize_model_parallel()
+    cfg = TransformerConfig(num_layers=3, hidden_size=256, ffn_hidden_size=512, num_attention_heads=4,
+                            num_query_groups=2, vocab_size=1024, max_position_embeddings=256)
+
+    def train(overlap: bool):
+        core = GPTModel(cfg, device="cuda", seed=11)
+        ddp = DistributedDataParallel(core, ps.group("dp_cp"), world)
+        assert (ddp.buffers[0].grad_arena is not None) == overlap
+        if overlap:
+            ddp.enable_grad_overlap(bucket_numel=300_000)
+            assert len(ddp.buffers[0].bucket_ranges) >= 3
+        opt = DistributedOptimizer(ddp.buffers, lr=1e-3, betas=(0.9, 0.95), weight_decay=0.0, clip_grad=1.0,
+                                   dp_group=ps.group("dp_cp"), dp_rank=rank, overlap_param_gather=overlap,
+                                   gather_chunks=4)
+        g = torch.Generator(device="cuda").manual_seed(5 + rank)
+        for step in range(3):
+            ddp.zero_grad_buffer()
+            for micro in range(2):
+                meta = PackedMeta.from_lengths([70, 58], "cuda")
+                ids = torch.randint(0, 1024, (128,), device="cuda", generator=g)
+                labels = torch.randint(0, 1024, (128,), device="cuda", generator=g)
+                if micro == 1:
+                    ddp.begin_last_microbatch()
+                lp, _ = core.forward_logprob(ids, labels, meta, 1.0, False)
+                (-lp.mean()).backward()
+            ddp.finish_grad_sync(to_shards=True)
+            opt.step()
+            if get_arena() is not None:
+                get_arena().check()
+        return torch.cat([p.detach().float().reshape(-1) for p in core.parameters()])
+
+    plain = train(False)                 # no arena yet: ordinary buffers, NCCL collectives
+    init_arena(64 << 20)
+    fused = train(True)
+    every = [torch.empty_like(fused) for _ in range(world)]
+    dist.all_gather(every, fused)
+    assert all(torch.equal(every[0], e) for e in every), "ranks hold different parameters after the pipelined gather"
+    err = (plain - fused).abs().max().item()
+    assert err <= 2e-2, err              # bf16 parameters, different summation orders
+
+
 def case_arena_fallback(rank, world):
     """One rank cannot allocate its arena (it asks for far more than the device has; the allocation
     call returns an error code): every rank gets the same exception, nobody is left waiting in a
@@ -435,7 +487,7 @@ def case_arena_fallback(rank, world):
     assert float(x[0]) == rank + 1
 
 
-CASES = {"peer_all_reduce": case_peer_all_reduce, "buffer_release": case_buffer_release, "arena_fallback": case_arena_fallback, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
+CASES = {"peer_all_reduce": case_peer_all_reduce, "overlap": case_overlap, "buffer_release": case_buffer_release, "arena_fallback": case_arena_fallback, "cp_ring": case_cp_ring, "moe_ep": case_moe_ep, "moe_ep_p2p": case_moe_ep_p2p, "collectives": case_collectives, "reshard": case_reshard, "grpo_reshard": case_grpo_reshard,
          "fused_tp": case_fused_tp, "tp_model": case_tp_model}
 
 if __name__ == "__main__":

@@ -108,7 +108,7 @@ def test_sequence_parallel_matches_single_rank():
     run_distributed(_tp_worker, 2, True)
 
 
-def _zero1_worker(rank, world):
+def _zero1_worker(rank, world, pipelined_gather=False):
     from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
     from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
     from mindspeed_rl_b200.parallel.state import initialize_model_parallel
@@ -119,7 +119,8 @@ def _zero1_worker(rank, world):
     ref.load_state_dict(net.state_dict())
     ddp = DistributedDataParallel(net, ps.group("dp_cp"), world)
     opt = DistributedOptimizer(ddp.buffers, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, clip_grad=0.5,
-                               dp_group=ps.group("dp_cp"), dp_rank=rank)
+                               dp_group=ps.group("dp_cp"), dp_rank=rank, overlap_param_gather=pipelined_gather,
+                               gather_chunks=3)
     ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01)
     for step in range(3):
         xs = [torch.randn(4, 16, generator=torch.Generator().manual_seed(10 * step + r)) for r in range(world)]
@@ -139,8 +140,56 @@ def _zero1_worker(rank, world):
         assert torch.allclose(a, b, atol=1e-5), (a - b).abs().max()
 
 
+def _overlap_worker(rank, world):
+    """Bucketed gradient reduction started from the layers' backward (last micro-batch only) gives the
+    parameters of the plain reduce-after-backward path, bucket by bucket in backward order."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.training_engine import TrainingEngine
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel
+    ps = initialize_model_parallel()
+    cfg = TransformerConfig(num_layers=3, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+                            vocab_size=64, params_dtype=torch.float32, max_position_embeddings=64)
+    results = []
+    for overlap in (False, True):
+        core = GPTModel(cfg, device="cpu", seed=11)
+        ddp = DistributedDataParallel(core, ps.group("dp_cp"), world)
+        launched = []
+        if overlap:
+            ddp.enable_grad_overlap(bucket_numel=4000)
+            assert len(ddp.buffers[0].bucket_ranges) >= 3
+            orig = ddp._launch_bucket
+            ddp._launch_bucket = lambda bi, k: (launched.append((bi, k)), orig(bi, k))[1]
+        opt = DistributedOptimizer(ddp.buffers, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0, clip_grad=1.0,
+                                   dp_group=ps.group("dp_cp"), dp_rank=rank)
+        g = torch.Generator().manual_seed(5 + rank)
+        for step in range(2):
+            ddp.zero_grad_buffer()
+            for micro in range(2):                      # gradients accumulate; only the last micro-batch overlaps
+                meta = PackedMeta.from_lengths([7, 5], "cpu")
+                ids, labels = torch.randint(0, 64, (12,), generator=g), torch.randint(0, 64, (12,), generator=g)
+                if micro == 1:
+                    ddp.begin_last_microbatch()
+                lp, _ = core.forward_logprob(ids, labels, meta, 1.0, False)
+                (-lp.mean()).backward()
+            ddp.finish_grad_sync(to_shards=True)
+            opt.step()
+        if overlap:
+            # 3 layer buckets (or more) per step went out during the backward, last layers first
+            assert len(launched) >= 2 * 2 and launched[0][1] <= launched[1][1]
+        results.append(torch.cat([p.detach().reshape(-1) for p in core.parameters()]))
+    assert torch.allclose(results[0], results[1], atol=1e-6), (results[0] - results[1]).abs().max()
+
+
+def test_overlapped_bucketed_grad_reduce_matches_plain():
+    run_distributed(_overlap_worker, 2)
+
+
 def test_distributed_optimizer_matches_adamw():
     run_distributed(_zero1_worker, 2)
+    run_distributed(_zero1_worker, 2, True)        # shard updated in chunks, chunks gathered behind the update
 
 
 def _ep_worker(rank, world):

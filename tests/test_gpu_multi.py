@@ -90,3 +90,8 @@ def test_peer_memory_all_reduce_for_decode():
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_releasable_peer_mapped_buffers():
     _run("buffer_release", 2)
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_overlapped_grad_reduce_and_pipelined_param_gather():
+    _run("overlap", 2)
