@@ -57,52 +57,81 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-// One-pass form for rows that fit the block's registers (H <= THREADS * VPT * 8): the row is read
-// once into registers (with the optional residual added and the rounded sum written back), reduced,
-// scaled and stored; no shared-memory staging of the row.
+// One-pass form for rows that fit the block's registers (H <= THREADS * VPT * 8).  Persistent blocks
+// walk rows blockIdx.x, +gridDim.x, ...; the loads of the next row are issued before the current row
+// is reduced, scaled and stored, so that a block always has a row in flight (no shared-memory staging
+// of the row; with the optional residual the rounded sum is written back and normalised).
 template <int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_fwd_regs_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                         const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
-                        __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd_out, int H,
-                        float eps) {
-  __shared__ float red[32];
-  const long long r = blockIdx.x;
+                        __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd_out, long long rows,
+                        int H, float eps) {
+  __shared__ float red[2][32];
   const int nvec = H >> 3;
-  float f[VPT][8];
-  float ss = 0.f;
+  bf16x8 cur[VPT], cur_res[VPT], nxt[VPT], nxt_res[VPT];
+  auto fetch = [&](long long r, bf16x8 (&dst)[VPT], bf16x8 (&dst_res)[VPT]) {
 #pragma unroll
-  for (int j = 0; j < VPT; ++j) {
-    const int i = threadIdx.x + j * THREADS;
-    if (i < nvec) {
-      unpack8(ld8(x + r * H + i * 8), f[j]);
-      if (res != nullptr) {
-        float g[8];
-        unpack8(ld8(res + r * H + i * 8), g);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) f[j][k] += g[k];
-        if (sum_out != nullptr) {
-          const bf16x8 s = pack8(f[j]);
-          st8(sum_out + r * H + i * 8, s);
-          unpack8(s, f[j]);  // normalise exactly what was stored
-        }
+    for (int j = 0; j < VPT; ++j) {
+      const int i = threadIdx.x + j * THREADS;
+      if (i < nvec) {
+        dst[j] = ld8(x + r * H + i * 8);
+        if (res != nullptr) dst_res[j] = ld8(res + r * H + i * 8);
       }
-#pragma unroll
-      for (int k = 0; k < 8; ++k) ss += f[j][k] * f[j][k];
     }
-  }
-  ss = block_sum(ss, red);
-  const float rstd = rsqrtf(ss / (float)H + eps);
-  if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[r] = rstd;
+  };
+  long long r = blockIdx.x;
+  if (r < rows) fetch(r, cur, cur_res);
+  int flip = 0;
+  for (; r < rows; r += gridDim.x, flip ^= 1) {
+    const long long rn = r + gridDim.x;
+    if (rn < rows) fetch(rn, nxt, nxt_res);          // in flight while this row is processed
+    float f[VPT][8];
+    float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < VPT; ++j) {
-    const int i = threadIdx.x + j * THREADS;
-    if (i < nvec) {
-      float wv[8], o[8];
-      unpack8(ld8(w + i * 8), wv);
+    for (int j = 0; j < VPT; ++j) {
+      const int i = threadIdx.x + j * THREADS;
+      if (i < nvec) {
+        unpack8(cur[j], f[j]);
+        if (res != nullptr) {
+          float g[8];
+          unpack8(cur_res[j], g);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) o[k] = f[j][k] * rstd * wv[k];
-      st8(y + r * H + i * 8, pack8(o));
+          for (int k = 0; k < 8; ++k) f[j][k] += g[k];
+          if (sum_out != nullptr) {
+            const bf16x8 s = pack8(f[j]);
+            st8(sum_out + r * H + i * 8, s);
+            unpack8(s, f[j]);  // normalise exactly what was stored
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += f[j][k] * f[j][k];
+      }
+    }
+    {   // block sum with alternating scratch: one barrier per row is enough
+      const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+      ss = warp_sum(ss);
+      if (lane == 0) red[flip][wid] = ss;
+      __syncthreads();
+      ss = warp_sum(lane < THREADS / 32 ? red[flip][lane] : 0.f);
+    }
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[r] = rstd;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = threadIdx.x + j * THREADS;
+      if (i < nvec) {
+        float wv[8], o[8];
+        unpack8(ld8(w + i * 8), wv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = f[j][k] * rstd * wv[k];
+        st8(y + r * H + i * 8, pack8(o));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      cur[j] = nxt[j];
+      cur_res[j] = nxt_res[j];
     }
   }
 }
@@ -402,16 +431,18 @@ MSRL_API int msrl_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               float* rstd, long long rows, int H, float eps, cudaStream_t st) {
   if (rows == 0) return 0;
   if (H % 8 != 0 || H > 16384) return (int)cudaErrorInvalidValue;
-  if (H <= 128 * 4 * 8) {        // the usual hidden sizes: the row lives in registers
-    rmsnorm_fwd_regs_kernel<128, 4><<<(unsigned)rows, 128, 0, st>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
-        (__nv_bfloat16*)y, (__nv_bfloat16*)sum_out, rstd, H, eps);
-    MSRL_LAUNCH_CHECK();
-  }
-  if (H <= 256 * 4 * 8) {
-    rmsnorm_fwd_regs_kernel<256, 4><<<(unsigned)rows, 256, 0, st>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
-        (__nv_bfloat16*)y, (__nv_bfloat16*)sum_out, rstd, H, eps);
+  if (H <= 256 * 4 * 8) {        // the usual hidden sizes: the row lives in registers
+    // one wave of persistent blocks: four 128-thread (two 256-thread) blocks fit the registers of an SM
+    const long long cap = (long long)sm_count() * (H <= 128 * 4 * 8 ? 4 : 2);
+    const unsigned blocks = (unsigned)(rows < cap ? rows : cap);
+    if (H <= 128 * 4 * 8)
+      rmsnorm_fwd_regs_kernel<128, 4><<<blocks, 128, 0, st>>>(
+          (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+          (__nv_bfloat16*)y, (__nv_bfloat16*)sum_out, rstd, rows, H, eps);
+    else
+      rmsnorm_fwd_regs_kernel<256, 4><<<blocks, 256, 0, st>>>(
+          (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+          (__nv_bfloat16*)y, (__nv_bfloat16*)sum_out, rstd, rows, H, eps);
     MSRL_LAUNCH_CHECK();
   }
   size_t smem = (size_t)H * sizeof(float);
@@ -428,7 +459,7 @@ MSRL_API int msrl_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
 
 // Number of blocks (= rows of the dw scratch) the backward uses for a given problem.
 MSRL_API int msrl_rmsnorm_bwd_blocks(long long rows) {
-  long long cap = (long long)sm_count() * 2;
+  long long cap = (long long)sm_count() * 6;      // rows in flight per SM; the partial sums cost cap x H floats
   return (int)(rows < cap ? (rows < 1 ? 1 : rows) : cap);
 }
 

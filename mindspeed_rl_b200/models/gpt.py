@@ -222,8 +222,8 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
         proj = comm.row_linear(attn, sa.linear_proj.weight)
         if lora.active(sa.linear_proj):
             lo["proj"] = lora.row_fwd(sa.linear_proj, attn, proj, comm)[1]
-    h1 = ops.add(h, proj)
-    x2, rstd2, _ = ops.rmsnorm_fwd(h1, layer.pre_mlp_layernorm.weight, eps, want_rstd=keep)
+    # residual add fused into the norm: one pass writes h1 = h + proj and its normalised form
+    x2, rstd2, h1 = ops.rmsnorm_fwd(proj, layer.pre_mlp_layernorm.weight, eps, residual=h, want_rstd=keep)
     if isinstance(layer.mlp, MLP):
         gu, x2g = comm.column_linear(x2, layer.mlp.linear_fc1.weight)
         if lora.active(layer.mlp.linear_fc1):
