@@ -58,9 +58,14 @@ struct Params {
   long long ldc;
   const __nv_bfloat16* bias;   // OUT_BF16 only, may be null
   int* error;
+  // grouped reduction (expert weight gradients): `groups` independent products share the operands' M and N
+  // and split their rows: group g reduces over rows [seg[g], seg[g + 1]) (device array, multiples of 64,
+  // read by the kernel: no host round trip) and accumulates into C + g * c_group_stride
+  int groups;
+  const int* seg;
+  long long c_group_stride;
   int k_splits;                // OUT_PART_F32: pieces the reduction is cut into (one work item per tile and piece;
                                // piece s writes its fp32 partial tile into slab s of C, [k_splits, M, ldc])
-  int flags;                   // experiment switches (MSRL_G2_FLAGS): 1 fence per stage, 4 no stores, bits 4-7 ring depth
   // communication-fused variants (tensor-parallel linears under sequence parallelism)
   int rank, world;
   int m_local;                 // rows owned by one rank (multiple of 256); M = world * m_local
@@ -188,7 +193,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();            // 0: leader (issues the MMAs), 1: its partner
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles * ((OUT == OUT_PART_F32) ? p.k_splits : 1);
+  const int tiles_per_group = m_tiles * n_tiles;
+  const bool grouped = (OUT == OUT_ACC_F32 || OUT == OUT_ACC_BF16) && COMM == COMM_NONE && p.groups > 0;
+  const int total_tiles = tiles_per_group * ((OUT == OUT_PART_F32) ? p.k_splits : (grouped ? p.groups : 1));
   const int num_kb = (p.K + BK - 1) / BK;
   // split reduction (small-M, weight-streaming problems): work item = (tile, piece of K)
   const int k_splits = (OUT == OUT_PART_F32) ? p.k_splits : 1;
@@ -196,13 +203,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int mt_local = (COMM == COMM_NONE) ? m_tiles : p.m_local / BM;       // row tiles of one rank's block
   const int units_local = (COMM == COMM_NONE) ? 0 : p.m_local / HM;          // 128-row units of one rank's block
+  // k-block range of a work item; an empty range (an expert without tokens) is skipped by every role alike
+  auto krange = [&](int tile, int& kb0, int& kb1) {
+    if (OUT == OUT_PART_F32) {
+      kb0 = (tile % k_splits) * kb_per;
+      kb1 = (kb0 + kb_per < num_kb) ? kb0 + kb_per : num_kb;
+    } else if (grouped) {
+      const int g = tile / tiles_per_group;
+      kb0 = p.seg[g] / BK;
+      kb1 = p.seg[g + 1] / BK;
+    } else {
+      kb0 = 0;
+      kb1 = num_kb;
+    }
+  };
   auto coords = [&](int tile, int& mt, int& nt) {
     if (OUT == OUT_PART_F32) tile /= k_splits;
+    if (grouped) tile %= tiles_per_group;
     if (COMM == COMM_AG) tile_coords_ag(tile, n_tiles, p.rank, p.world, mt_local, mt, nt);
     else if (COMM == COMM_RS) tile_coords_rs(tile, n_tiles, p.rank, p.world, mt_local, mt, nt);
     else tile_coords(tile, m_tiles, n_tiles, mt, nt);
   };
-  const int RS = ((p.flags >> 4) & 15) ? ((p.flags >> 4) & 15) : STAGES;   // ring depth in use
+  constexpr int RS = STAGES;   // ring depth
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -233,7 +255,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       const uint32_t full0 = map_to_rank(smem_u32(&full_bar[0]), 0);     // the leader's barriers
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
-        int mt, nt;
+        int mt, nt, kb0, kb1;
+        krange(tile, kb0, kb1);
+        if (grouped && kb1 <= kb0) continue;
         coords(tile, mt, nt);
         const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN + (int)rank * HN;
         const CUtensorMap* amap = &map_a;
@@ -251,8 +275,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             asm volatile("fence.proxy.async;\n" ::: "memory");   // generic-proxy stores -> TMA reads
           }
         }
-        const int kb0 = (OUT == OUT_PART_F32) ? (tile % k_splits) * kb_per : 0;
-        const int kb1 = (OUT == OUT_PART_F32) ? ((kb0 + kb_per < num_kb) ? kb0 + kb_per : num_kb) : num_kb;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % RS;
           const uint32_t use = it / RS;
@@ -293,7 +315,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       constexpr uint32_t KA = (A_MN ? 2048 : 32) >> 4, KB_ = (B_MN ? 2048 : 32) >> 4;
       uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++local) {
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
+        int kb0, kb1;
+        krange(tile, kb0, kb1);
+        if (grouped && kb1 <= kb0) continue;
         const uint32_t buf = local & 1;
         if (local >= 2) {      // both CTAs' epilogues must have drained this accumulator
           ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, p.error, ERR_ACC);
@@ -301,15 +326,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           fence_after();
         }
         const uint32_t tmem_acc = tmem + buf * BN;
-        const int kb0 = (OUT == OUT_PART_F32) ? (tile % k_splits) * kb_per : 0;
-        const int kb1 = (OUT == OUT_PART_F32) ? ((kb0 + kb_per < num_kb) ? kb0 + kb_per : num_kb) : num_kb;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % RS;
           ok = mbar_wait(&full_bar[s], (it / RS) & 1, p.error, ERR_FULL);
           if (!ok) break;
           // the operands were written by TMA and are ordered by the barrier itself; a tcgen05 fence
-          // here would only hold back the MMA issue
-          if (p.flags & 1) fence_after();
+          // here would only hold back the MMA issue (measured)
           const uint64_t so = (uint64_t)((uint32_t)s * (STAGE_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
@@ -317,6 +339,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           commit_pair(&empty_bar[s]);     // the slot is free in both CTAs once these MMAs have read it
         }
         commit_pair(&acc_full[buf]);      // accumulator complete (or abandoned) for both epilogues
+        ++local;
       }
     }
   } else if (warp < 4) {
@@ -326,7 +349,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     unsigned char* patch = smem + (size_t)STAGES * STAGE_BYTES + (size_t)warp * (32 * EPI_PITCH);
     const uint32_t acc_empty_leader0 = map_to_rank(smem_u32(&acc_empty[0]), 0);
     const uint32_t acc_empty_leader1 = map_to_rank(smem_u32(&acc_empty[1]), 0);
-    for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++local) {
+    for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
+      {
+        int kb0, kb1;
+        krange(tile, kb0, kb1);
+        if (grouped && kb1 <= kb0) continue;
+      }
       const uint32_t buf = local & 1;
       int mt, nt;
       coords(tile, mt, nt);
@@ -368,8 +396,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               *reinterpret_cast<bf16x8*>(patch + lane * EPI_PITCH + h * 64 + q * 16) = pack8(v + q * 8);
           }
           __syncwarp();
-          if (p.flags & 4) {
-          } else if (vec_ok) {
+          if (vec_ok) {
             // whole 128-byte row segments per store instruction: 4 rows x 8 lanes x 16 bytes
             const int col = n0 + c * 64 + (lane & 7) * 8;
 #pragma unroll
@@ -402,7 +429,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const bool f32 = (OUT == OUT_ACC_F32 || OUT == OUT_PART_F32);
         // split reduction: this piece's slab of the partial-sum buffer; an empty piece (more pieces than
         // k-blocks) was never multiplied and stores zeros
-        float* const Cf = reinterpret_cast<float*>(p.C) +
+        const long long group_off = grouped ? (long long)(tile / tiles_per_group) * p.c_group_stride : 0;
+        float* const Cf = reinterpret_cast<float*>(p.C) + group_off +
                           ((OUT == OUT_PART_F32) ? (long long)(tile % k_splits) * p.M * p.ldc : 0);
         const bool empty_piece = (OUT == OUT_PART_F32) && (tile % k_splits) * kb_per >= num_kb;
         const bool vec_ok = f32 ? ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
@@ -441,7 +469,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
               }
             } else {
-              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C);
+              __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + group_off;
               const int cc = (lane & 3) * 8;                    // 4 lanes x 16 B = one 64-byte row segment
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -464,7 +492,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               float* dst = Cf + (long long)row * p.ldc + col0;
               for (int jj = 0; jj < 32 && col0 + jj < p.N; ++jj) dst[jj] = (OUT == OUT_PART_F32) ? src[jj] : dst[jj] + src[jj];
             } else {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + group_off + (long long)row * p.ldc + col0;
               for (int jj = 0; jj < 32 && col0 + jj < p.N; ++jj) dst[jj] = __float2bfloat16(__bfloat162float(dst[jj]) + src[jj]);
             }
           }
@@ -475,6 +503,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(buf ? acc_empty_leader1 : acc_empty_leader0);
+      ++local;
     }
   }
   if (COMM == COMM_AG && warp >= 6) {
@@ -637,7 +666,8 @@ static int launch(const void* A, long long lda, const void* B, long long ldb, co
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2;
     max_clusters = n < sm_count() / 2 ? n : sm_count() / 2;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (OUT == OUT_PART_F32 ? p.k_splits : 1);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) *
+                    (OUT == OUT_PART_F32 ? p.k_splits : (p.groups > 0 ? p.groups : 1));
   // the fused variants always launch every pair: their comm warps share the copy / reduce work of the
   // whole grid, and every CTA must be resident for the counters to advance
   const int clusters = (COMM != COMM_NONE || tiles >= max_clusters) ? max_clusters : tiles;
@@ -697,8 +727,6 @@ MSRL_API int msrl_gemm_pair_bf16(const void* A, long long lda, int a_mn, const v
   p.ldc = ldc;
   p.bias = out_mode == g2::OUT_BF16 ? reinterpret_cast<const __nv_bfloat16*>(bias) : nullptr;
   p.error = error;
-  static const int flags = [] { const char* e = getenv("MSRL_G2_FLAGS"); return e ? atoi(e) : 0; }();
-  p.flags = flags;
   if (!a_mn && !b_mn && out_mode == g2::OUT_BF16) return g2::launch<false, false, g2::OUT_BF16>(A, lda, B, ldb, p, st);
   if (!a_mn && b_mn && out_mode == g2::OUT_BF16) return g2::launch<false, true, g2::OUT_BF16>(A, lda, B, ldb, p, st);
   if (a_mn && b_mn && out_mode == g2::OUT_BF16) return g2::launch<true, true, g2::OUT_BF16>(A, lda, B, ldb, p, st);
@@ -754,6 +782,31 @@ MSRL_API int msrl_gemm_pair_splitk_bf16(const void* A, long long lda, const void
   g2::splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, st>>>(part, (long long)M * N, splits, (__nv_bfloat16*)C, ldc,
                                                               (const __nv_bfloat16*)bias, M, N);
   return (int)cudaGetLastError();
+}
+
+// Grouped weight gradient (mixture-of-experts layers): for every group g,
+//   C_g[M, N] += A[seg[g] : seg[g+1], :M]^T  B[seg[g] : seg[g+1], :N]
+// with A [rows, M] and B [rows, N] row-major bf16 (both read as MN-major operands), C_g = C + g * c_group_stride
+// (leading dimension ldc), out_mode 1: fp32 accumulate, 2: bf16 accumulate.  `seg` is a DEVICE array of
+// groups + 1 row offsets, multiples of 64 (the padded expert segments of the permuted token layout; pad rows
+// must be zero in A or B); groups without rows are skipped on the device, nothing is read back to the host.
+MSRL_API int msrl_gemm_pair_grouped_wgrad(const void* A, long long lda, const void* B, long long ldb, void* C,
+                                          long long ldc, long long c_group_stride, int out_mode, const int* seg,
+                                          int groups, int M, int N, long long rows, int* error, cudaStream_t st) {
+  if (groups <= 0 || M == 0 || N == 0 || rows == 0) return 0;
+  if (M % 8 != 0 || N % 8 != 0 || rows % 8 != 0 || rows > 0x7fffffffLL ||
+      (out_mode != g2::OUT_ACC_F32 && out_mode != g2::OUT_ACC_BF16))
+    return (int)cudaErrorInvalidValue;
+  g2::Params p{};
+  p.M = M; p.N = N; p.K = (int)rows;
+  p.C = C;
+  p.ldc = ldc;
+  p.error = error;
+  p.groups = groups;
+  p.seg = seg;
+  p.c_group_stride = c_group_stride;
+  if (out_mode == g2::OUT_ACC_F32) return g2::launch<true, true, g2::OUT_ACC_F32>(A, lda, B, ldb, p, st);
+  return g2::launch<true, true, g2::OUT_ACC_BF16>(A, lda, B, ldb, p, st);
 }
 
 // ---- communication-fused forms on CTA pairs (same contracts as msrl_ag_gemm_bf16_tn / msrl_gemm_rs_bf16_tn,

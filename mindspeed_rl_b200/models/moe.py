@@ -372,16 +372,7 @@ class MoELayer(nn.Module):
         dact = K.grouped_gemm(dy, plan, w2, False, 0, f, f)
         dgu = ops.swiglu_bwd(ctx["gu"], dact)
         if self.experts.weight1.requires_grad:
-            g1 = grad_buffer(self.experts.weight1).view(h, e, 2 * f)
-            g2 = grad_buffer(self.experts.weight2).view(e, f, h)
-            counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
-            xp, act = ctx["xp"], ctx["act"]
-            for j, n in enumerate(counts):
-                if n == 0:
-                    continue
-                r = slice(offsets[j], offsets[j] + n)
-                g2[j].add_(torch.matmul(act[r].t(), dy[r]).to(g2.dtype))
-                g1[:, j].add_(torch.matmul(xp[r].t(), dgu[r]).to(g1.dtype))
+            self._expert_wgrads(plan, ctx["xp"], ctx["act"], dy, dgu)
         K.grouped_gemm(dgu, plan, w1, False, 2 * f, 0, h, out=disp.out_slab)
         dx, _ = disp.combine(route, None)
         return self._router_and_shared_bwd(ctx, x, dout, comm, dx.float(), dprob)
@@ -400,18 +391,30 @@ class MoELayer(nn.Module):
         dgu = ops.swiglu_bwd(ctx["gu"], dact)
         dxp = K.grouped_gemm(dgu, plan, w1, False, 2 * f, 0, h)
         if self.experts.weight1.requires_grad:
-            g1 = grad_buffer(self.experts.weight1).view(h, e, 2 * f)
-            g2 = grad_buffer(self.experts.weight2).view(e, f, h)
-            counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
-            xp, act = ctx["xp"], ctx["act"]
-            for j, n in enumerate(counts):
-                if n == 0:
-                    continue
-                r = slice(offsets[j], offsets[j] + n)
-                g2[j].add_(torch.matmul(act[r].t(), dy[r]).to(g2.dtype))
-                g1[:, j].add_(torch.matmul(xp[r].t(), dgu[r]).to(g1.dtype))
+            self._expert_wgrads(plan, ctx["xp"], ctx["act"], dy, dgu)
         dx = K.moe_combine(dxp, plan).float()
         return self._router_and_shared_bwd(ctx, x, dout, comm, dx, dprob)
+
+    def _expert_wgrads(self, plan, xp, act, dy, dgu) -> None:
+        """``dW2_e += act_e^T dy_e`` and ``dW1_e += x_e^T dgu_e`` for all local experts: two launches of the
+        grouped weight-gradient GEMM that read the segment bounds on the device; the per-expert loop (which
+        needs the counts on the host) remains for inputs that kernel does not cover."""
+        from ..ops import moe as K
+        from .gpt import grad_buffer
+
+        c = self.cfg
+        e, h, f = self.num_local, c.hidden_size, c.moe_ffn_hidden_size
+        g1 = grad_buffer(self.experts.weight1).view(h, e, 2 * f)
+        g2 = grad_buffer(self.experts.weight2).view(e, f, h)
+        if K.grouped_wgrad_(g2, f * h, h, act, dy, plan) and K.grouped_wgrad_(g1, 2 * f, e * 2 * f, xp, dgu, plan):
+            return
+        counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
+        for j, n in enumerate(counts):
+            if n == 0:
+                continue
+            r = slice(offsets[j], offsets[j] + n)
+            g2[j].add_(torch.matmul(act[r].t(), dy[r]).to(g2.dtype))
+            g1[:, j].add_(torch.matmul(xp[r].t(), dgu[r]).to(g1.dtype))
 
     def _router_and_shared_bwd(self, ctx, x, dout, comm, dx, dprob) -> torch.Tensor:
         """Probabilities (+ auxiliary loss) back to logits, x and the router weight; shared experts."""

@@ -128,6 +128,29 @@ def _sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
+def grouped_wgrad_(grad: torch.Tensor, group_stride: int, ldc: int, a: torch.Tensor, b: torch.Tensor,
+                   plan: MoePlan) -> bool:
+    """``grad_e[M, N] += a[rows of e].T @ b[rows of e]`` for every expert e of ``plan`` in ONE launch of the
+    CTA-pair GEMM (``csrc/gemm2cta_tcgen05.cu``, grouped reduction): ``a [rows, M]`` and ``b [rows, N]`` are
+    permuted-layout activations whose pad rows are zero, ``grad`` is a view whose first element is expert 0's
+    block; expert ``e``'s block starts ``group_stride`` elements later and has leading dimension ``ldc``.
+    The segment bounds are read on the device (``plan.offsets``): no host round trip.  Returns ``False``
+    (nothing done) for inputs the kernel does not cover; the caller then loops over the experts."""
+    from .gemm import _status_word, pair_enabled, pair_usable
+
+    if not (a.is_cuda and pair_enabled() and pair_usable(a, b) and _lib.use_kernels(a, b, grad)
+            and grad.dtype in (torch.float32, torch.bfloat16) and grad.data_ptr() % 16 == 0
+            and ldc % 8 == 0 and group_stride % 8 == 0 and a.shape[0] == b.shape[0] and a.shape[0] % 8 == 0
+            and plan.offsets is not None and plan.offsets.dtype == torch.int32):
+        return False
+    groups = int(plan.offsets.numel()) - 1
+    check(_lib.load().msrl_gemm_pair_grouped_wgrad(
+        ptr(a), c_ll(a.stride(0)), ptr(b), c_ll(b.stride(0)), ptr(grad), c_ll(ldc), c_ll(group_stride),
+        c_int(1 if grad.dtype == torch.float32 else 2), ptr(plan.offsets), c_int(groups), c_int(a.shape[1]),
+        c_int(b.shape[1]), c_ll(a.shape[0]), ptr(_status_word(a.device)), stream()), "gemm_pair_grouped_wgrad")
+    return True
+
+
 def grouped_gemm(a: torch.Tensor, plan: MoePlan, b2d: torch.Tensor, b_mn_major: bool, ex: int, ey: int,
                  n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``c[r] = a[r] @ B_e`` for the rows of expert e.  ``b2d`` is a 2-D contiguous view of all

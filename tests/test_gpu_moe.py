@@ -129,3 +129,35 @@ def test_peer_memory_dispatch_single_rank():
         arena.check()
     finally:
         arena.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_grouped_weight_gradient_reads_segments_on_device(dtype):
+    """Expert weight gradients in one launch per weight: every expert's ``a_e^T b_e`` is added into its block
+    of the gradient view (blocks as column groups or as row groups), an expert without tokens is skipped, and
+    the result matches the per-expert products."""
+    torch.manual_seed(6)
+    t, k, e, h, f = 900, 2, 6, 256, 192
+    idx = torch.stack([torch.randperm(e - 1, device="cuda")[:k] + 1 for _ in range(t)])     # expert 0 gets nothing
+    plan = M.moe_plan(idx, e)
+    assert int(plan.counts[0]) == 0
+    x = torch.randn(t, h, device="cuda").bfloat16()
+    xp = M.moe_permute(x, plan)                                   # pad rows are zero
+    dgu = torch.randn(plan.max_rows, 2 * f, device="cuda").bfloat16()
+    act = torch.randn(plan.max_rows, f, device="cuda").bfloat16()
+    dy = M.moe_permute(torch.randn(t, h, device="cuda").bfloat16(), plan)
+    g1 = torch.randn(h, e, 2 * f, device="cuda").to(dtype)        # blocks = column groups
+    g2 = torch.randn(e, f, h, device="cuda").to(dtype)            # blocks = row groups
+    want1, want2 = g1.float().clone(), g2.float().clone()
+    counts, offsets = plan.counts.tolist(), plan.offsets.tolist()
+    for j, n in enumerate(counts):
+        r = slice(offsets[j], offsets[j] + n)
+        want1[:, j] += xp[r].float().t() @ dgu[r].float()
+        want2[j] += act[r].float().t() @ dy[r].float()
+    assert M.grouped_wgrad_(g1, 2 * f, e * 2 * f, xp, dgu, plan)
+    assert M.grouped_wgrad_(g2, f * h, h, act, dy, plan)
+    G.check_status("cuda", "grouped wgrad")
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-3
+    for got, want in ((g1, want1), (g2, want2)):
+        err = (got.float() - want).abs().max().item()
+        assert err <= tol * want.abs().max().item() + 1e-2, (dtype, err, want.abs().max().item())
