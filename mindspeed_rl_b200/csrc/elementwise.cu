@@ -57,6 +57,68 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+// Warp-per-row form (H <= 32 * VPT * 8): every warp owns whole rows (blockIdx / warp strided), reads a row
+// into registers with VPT independent 16-byte loads per lane, reduces it with shuffles only (no block
+// barrier anywhere), scales and stores it.  With five 128-thread blocks per SM about 140 KB of loads are in
+// flight per SM, which is what a streaming kernel with a reduction in the middle needs to stay near the
+// copy bandwidth.
+template <int VPT, bool RES>
+__global__ void __launch_bounds__(128)
+rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                        __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd_out, long long rows,
+                        int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  const long long warps = (long long)gridDim.x * 4;
+  for (long long r = (long long)blockIdx.x * 4 + (threadIdx.x >> 5); r < rows; r += warps) {
+    bf16x8 raw[VPT], raw_res[RES ? VPT : 1];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        raw[j] = ld8(x + r * H + i * 8);
+        if (RES) raw_res[j] = ld8(res + r * H + i * 8);
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        float f[8];
+        unpack8(raw[j], f);
+        if (RES) {
+          float g[8];
+          unpack8(raw_res[j], g);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f[k] += g[k];
+          raw[j] = pack8(f);                       // the rounded sum is what gets stored and normalised
+          if (sum_out != nullptr) st8(sum_out + r * H + i * 8, raw[j]);
+          unpack8(raw[j], f);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (lane == 0 && rstd_out != nullptr) rstd_out[r] = rstd;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        float f[8], wv[8], o[8];
+        unpack8(raw[j], f);
+        unpack8(ld8(w + i * 8), wv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = f[k] * rstd * wv[k];
+        st8(y + r * H + i * 8, pack8(o));
+      }
+    }
+  }
+}
+
 // One-pass form for rows that fit the block's registers (H <= THREADS * VPT * 8).  Persistent blocks
 // walk rows blockIdx.x, +gridDim.x, ...; the loads of the next row are issued before the current row
 // is reduced, scaled and stored, so that a block always has a row in flight (no shared-memory staging
@@ -431,7 +493,27 @@ MSRL_API int msrl_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               float* rstd, long long rows, int H, float eps, cudaStream_t st) {
   if (rows == 0) return 0;
   if (H % 8 != 0 || H > 16384) return (int)cudaErrorInvalidValue;
-  if (H <= 256 * 4 * 8) {        // the usual hidden sizes: the row lives in registers
+  if (H <= 32 * 16 * 8 && rows >= 4LL * sm_count()) {        // the usual hidden sizes, enough rows: a warp per row
+    const long long cap = (long long)sm_count() * 3;        // three blocks fit the registers of an SM
+    const long long want = (rows + 3) / 4;
+    const unsigned blocks = (unsigned)(want < cap ? want : cap);
+#define MSRL_RMS_WARP(V, R)                                                                            \
+    rmsnorm_fwd_warp_kernel<V, R><<<blocks, 128, 0, st>>>(                                             \
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, \
+        (__nv_bfloat16*)sum_out, rstd, rows, H, eps)
+    if (res != nullptr) {
+      if (H <= 32 * 8 * 8) MSRL_RMS_WARP(8, true);
+      else if (H <= 32 * 14 * 8) MSRL_RMS_WARP(14, true);
+      else MSRL_RMS_WARP(16, true);
+    } else {
+      if (H <= 32 * 8 * 8) MSRL_RMS_WARP(8, false);
+      else if (H <= 32 * 14 * 8) MSRL_RMS_WARP(14, false);
+      else MSRL_RMS_WARP(16, false);
+    }
+#undef MSRL_RMS_WARP
+    MSRL_LAUNCH_CHECK();
+  }
+  if (H <= 256 * 4 * 8) {        // few rows (decode steps) or wider rows: a block per row, the row in registers
     // one wave of persistent blocks: four 128-thread (two 256-thread) blocks fit the registers of an SM
     const long long cap = (long long)sm_count() * (H <= 128 * 4 * 8 ? 4 : 2);
     const unsigned blocks = (unsigned)(rows < cap ? rows : cap);
@@ -459,7 +541,7 @@ MSRL_API int msrl_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
 
 // Number of blocks (= rows of the dw scratch) the backward uses for a given problem.
 MSRL_API int msrl_rmsnorm_bwd_blocks(long long rows) {
-  long long cap = (long long)sm_count() * 6;      // rows in flight per SM; the partial sums cost cap x H floats
+  long long cap = (long long)sm_count() * 2;      // more blocks were measured slower (the partial sums cost cap x H floats)
   return (int)(rows < cap ? (rows < 1 ? 1 : rows) : cap);
 }
 

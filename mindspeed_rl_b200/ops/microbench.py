@@ -3,7 +3,7 @@
     python -m mindspeed_rl_b200.ops.microbench [--only NAME[,NAME..]] [--small] [--iters N]
 
 Each case reports the time per call (median of ``iters`` after warm-up; the L2 is flushed between
-timed calls by writing a 256 MiB buffer), the achieved bandwidth or FLOP rate, and the fraction of
+timed calls by writing a 256 MiB buffer and then reading another), the achieved bandwidth or FLOP rate, and the fraction of
 the measured machine peaks (``MEASURED_PEAKS.json`` at the repository root when present, else the
 documented fallback of 6.65 TB/s and 1.59 PFLOP/s).  ``--small`` shrinks every case to a few
 launches on a few hundred MB -- the size meant for profiler captures.
@@ -41,12 +41,17 @@ _flush = None
 def timeit(fn: Callable[[], None], iters: int, warmup: int = 3) -> float:
     global _flush
     if _flush is None:
-        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        _flush = (torch.empty(256 << 20, dtype=torch.uint8, device="cuda"),
+                  torch.zeros(64 << 20, dtype=torch.float32, device="cuda"))
     for _ in range(warmup):
         fn()
     times = []
     for _ in range(iters):
-        _flush.zero_()
+        # flush: write a buffer larger than L2, then read another one, so that the timed call starts with a
+        # cold L2 whose lines are clean (the dirty lines of the write would otherwise be written back during
+        # the timed kernel and count against its bandwidth)
+        _flush[0].zero_()
+        _flush[1].sum()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         # a short busy kernel ahead of the start event lets the host finish enqueueing `fn` while the

@@ -21,6 +21,24 @@ def close(a, b, atol, rtol, what=""):
     assert bool((err <= tol).all()), f"{what}: max err {err.max().item():.4g} (ref max {b.abs().max().item():.4g})"
 
 
+@pytest.mark.parametrize("rows,h", [(2000, 3584), (1501, 4096), (900, 1024), (777, 2048)])
+def test_rmsnorm_fwd_many_rows_warp_per_row(rows, h):
+    """Enough rows for the warp-per-row forward (three row widths of its template, with and without the
+    fused residual add) against the fp32 formulation."""
+    torch.manual_seed(1)
+    x = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(h, device=DEV)).bfloat16()
+    for r in (None, res):
+        y, rstd, s = ops.rmsnorm_fwd(x, w, 1e-6, residual=r)
+        xs = x.float() if r is None else (x.float() + r.float()).bfloat16().float()
+        want_rstd = torch.rsqrt(xs.pow(2).mean(-1) + 1e-6)
+        close(rstd, want_rstd, 1e-3, 1e-2, "rstd")
+        close(y, (xs * want_rstd[:, None] * w.float()).bfloat16(), 2e-2, 2e-2, "y")
+        if r is not None:
+            assert torch.equal(s, xs.bfloat16())
+
+
 @pytest.mark.parametrize("rows,h", [(37, 3584), (5, 4096), (300, 256), (9, 5120)])
 def test_rmsnorm_fwd_bwd(rows, h):
     torch.manual_seed(0)
