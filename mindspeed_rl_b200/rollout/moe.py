@@ -19,6 +19,9 @@ from .. import ops
 from ..models.moe import route
 
 
+_side_streams = {}
+
+
 class MoEWeights:
     def __init__(self, cfg, router_w: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, ep_group=None,
                  ep_size: int = 1, ep_rank: int = 0, shared: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
@@ -49,6 +52,7 @@ class MoEWeights:
     def forward(self, x: torch.Tensor, comm=None) -> torch.Tensor:
         cfg = self.cfg
         t, k = x.shape[0], cfg.moe_router_topk
+        fork = self._fork_shared(x)
         logits = torch.matmul(x.float(), self.router_w.float().t())
         top_p, top_idx, _ = route(logits, cfg, self.expert_bias)
         if self.collect_counts:
@@ -63,7 +67,7 @@ class MoEWeights:
             gu = K.grouped_gemm(K.moe_permute(x, plan), plan, self.w1.reshape(h, n_phys * 2 * f), True, 2 * f, 0, 2 * f)
             y = K.grouped_gemm(ops.swiglu_fwd(gu), plan, self.w2.reshape(n_phys * f, h), True, 0, f, h)
             out = K.moe_combine(y, plan, top_p)
-            return self._add_shared(out, x, comm)
+            return self._add_shared(out, x, comm, fork)
         disp = self.p2p(x) if (self.p2p is not None and self.ep_size > 1) else None
         if disp is not None and disp.e_local == self.num_local:
             # tokens go straight into the expert slabs of their ranks and the outputs are pulled back:
@@ -83,7 +87,7 @@ class MoEWeights:
                 K.grouped_gemm(ops.swiglu_fwd(gu, out=act), rt.plan, self.w2.reshape(e * f, h), True, 0, f, h,
                                out=disp.out_slab)
                 out, _ = disp.combine(rt, top_p)
-                return self._add_shared(out, x, comm)
+                return self._add_shared(out, x, comm, fork)
         flat = phys.reshape(-1)
         order = torch.argsort(flat, stable=True)
         token_of = order // k
@@ -117,14 +121,40 @@ class MoEWeights:
         w = top_p.reshape(-1)[order].to(x.dtype)
         out = torch.zeros(t, x.shape[1], device=x.device, dtype=torch.float32)
         out.index_add_(0, token_of, (y * w.unsqueeze(-1)).float())
-        return self._add_shared(out.to(x.dtype), x, comm)
+        return self._add_shared(out.to(x.dtype), x, comm, fork)
 
-    def _add_shared(self, out: torch.Tensor, x: torch.Tensor, comm) -> torch.Tensor:
-        if self.shared is not None:
-            fc1, fc2 = self.shared
-            sh = torch.matmul(ops.swiglu_fwd(torch.matmul(x, fc1.t())), fc2.t())
-            out = out + (comm.all_reduce(sh) if comm is not None else sh)
-        return out
+    def _shared_mlp(self, x: torch.Tensor) -> torch.Tensor:
+        from ..ops.gemm import linear_fwd
+
+        fc1, fc2 = self.shared
+        return linear_fwd(ops.swiglu_fwd(linear_fwd(x, fc1)), fc2)
+
+    def _fork_shared(self, x: torch.Tensor):
+        """Start the shared experts on a side stream, so that they run beside the routed experts' token
+        exchange and grouped GEMMs (reference: the shared-expert stream of the fused MoE layer,
+        ``models/rollout/vllm_adapter/fused_moe.py:230-373``).  Works inside a stream capture (the fork and
+        the join become edges of the graph).  ``MSRL_MOE_SHARED_STREAM=0`` keeps everything on one stream."""
+        if self.shared is None or not x.is_cuda or os.environ.get("MSRL_MOE_SHARED_STREAM", "1") != "1":
+            return None
+        side = _side_streams.get(x.device)
+        if side is None:
+            side = _side_streams[x.device] = torch.cuda.Stream(device=x.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            sh = self._shared_mlp(x)
+        x.record_stream(side)
+        return side, sh
+
+    def _add_shared(self, out: torch.Tensor, x: torch.Tensor, comm, fork=None) -> torch.Tensor:
+        if self.shared is None:
+            return out
+        if fork is not None:
+            side, sh = fork
+            torch.cuda.current_stream().wait_stream(side)
+            sh.record_stream(torch.cuda.current_stream())
+        else:
+            sh = self._shared_mlp(x)
+        return out + (comm.all_reduce(sh) if comm is not None else sh)
 
     def _expert(self, x: torch.Tensor, j: int, out: torch.Tensor) -> None:
         act = ops.swiglu_fwd(torch.matmul(x, self.w1[:, j]))

@@ -161,3 +161,49 @@ def test_grouped_weight_gradient_reads_segments_on_device(dtype):
     for got, want in ((g1, want1), (g2, want2)):
         err = (got.float() - want).abs().max().item()
         assert err <= tol * want.abs().max().item() + 1e-2, (dtype, err, want.abs().max().item())
+
+
+def test_rollout_moe_with_shared_experts_on_side_stream():
+    """Rollout expert layer with shared experts: computed on a side stream beside the routed experts (also
+    when the layer is replayed from a CUDA graph) and equal to the single-stream result and the fp32 formula."""
+    import os
+
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.rollout.moe import MoEWeights
+
+    torch.manual_seed(8)
+    t, e, k, h, f, fs = 300, 8, 2, 256, 128, 384
+    cfg = TransformerConfig(num_layers=1, hidden_size=h, ffn_hidden_size=fs, num_attention_heads=2, vocab_size=64,
+                            num_experts=e, moe_router_topk=k, moe_ffn_hidden_size=f, norm_topk_prob=True)
+    router = torch.randn(e, h, device="cuda")
+    w1 = (0.05 * torch.randn(h, e, 2 * f, device="cuda")).bfloat16()
+    w2 = (0.05 * torch.randn(e, f, h, device="cuda")).bfloat16()
+    shared = ((0.05 * torch.randn(2 * fs, h, device="cuda")).bfloat16(), (0.05 * torch.randn(h, fs, device="cuda")).bfloat16())
+    layer = MoEWeights(cfg, router, w1, w2, shared=shared)
+    x = torch.randn(t, h, device="cuda").bfloat16()
+    forked = layer.forward(x)
+    os.environ["MSRL_MOE_SHARED_STREAM"] = "0"
+    try:
+        plain = layer.forward(x)
+    finally:
+        del os.environ["MSRL_MOE_SHARED_STREAM"]
+    assert torch.equal(forked, plain)
+    without = MoEWeights(cfg, router, w1, w2).forward(x)
+    g, u = (x.float() @ shared[0].float().t()).chunk(2, -1)
+    want = without.float() + (torch.nn.functional.silu(g) * u).bfloat16().float() @ shared[1].float().t()
+    assert (forked.float() - want).abs().max().item() <= 3e-2 * want.abs().max().item() + 1e-2
+    # replay from a graph: the fork and the join are captured as graph edges
+    static_x = x.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer.forward(static_x)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = layer.forward(static_x)
+    static_x.copy_(torch.randn(t, h, device="cuda").bfloat16())
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, layer.forward(static_x))
+    G.check_status("cuda", "rollout moe")
