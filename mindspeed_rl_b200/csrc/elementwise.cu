@@ -479,6 +479,43 @@ __global__ void colsum_rows_kernel(const __nv_bfloat16* __restrict__ m, long lon
   partial[(long long)blockIdx.y * C + c] = s;
 }
 
+// Embedding gradient: g[id] += sum of the rows d[t] with ids[t] == id, rows of one id added in fp32 in
+// token order (no atomics: bit-reproducible).  `order` lists the tokens sorted by id (stable), segment s
+// covers order[seg_start[s] .. seg_start[s + 1]) and belongs to row seg_id[s] of g.  One block per
+// segment, 16-byte column vectors strided over the threads.
+template <typename G>
+__global__ void __launch_bounds__(128)
+embedding_grad_kernel(const __nv_bfloat16* __restrict__ d, long long ldd, const long long* __restrict__ order,
+                      const long long* __restrict__ seg_start, const long long* __restrict__ seg_id,
+                      G* __restrict__ g, long long ldg, int H) {
+  const long long s = blockIdx.x;
+  const long long t0 = seg_start[s], t1 = seg_start[s + 1];
+  G* row = g + seg_id[s] * ldg;
+  for (int c = threadIdx.x * 8; c < H; c += 128 * 8) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (long long t = t0; t < t1; ++t) {
+      float f[8];
+      unpack8(ld8(d + order[t] * ldd + c), f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += f[k];
+    }
+    if (sizeof(G) == 2) {
+      __nv_bfloat16* r16 = reinterpret_cast<__nv_bfloat16*>(row);
+      float cur[8];
+      unpack8(ld8(r16 + c), cur);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) cur[k] += acc[k];
+      st8(r16 + c, pack8(cur));
+    } else {
+      float* r32 = reinterpret_cast<float*>(row);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) r32[c + k] += acc[k];
+    }
+  }
+}
+
 }  // namespace msrl
 
 using namespace msrl;
@@ -657,5 +694,21 @@ MSRL_API int msrl_colsum(const void* m, long long rows, int C, float* partial, f
   if (e != cudaSuccess) return (int)e;
   colsum_partials_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, nb, C, out_f32,
                                                           (__nv_bfloat16*)out_bf16, accumulate);
+  MSRL_LAUNCH_CHECK();
+}
+
+// g[seg_id[s]] += sum over t in [seg_start[s], seg_start[s+1]) of d[order[t]]   (see embedding_grad_kernel).
+// d bf16 [T, H] (row pitch ldd), g bf16 or fp32 [V, H] (row pitch ldg); H a multiple of 8, rows 16-byte aligned.
+MSRL_API int msrl_embedding_grad(const void* d, long long ldd, const long long* order, const long long* seg_start,
+                                 const long long* seg_id, long long n_seg, void* g, long long ldg, int g_is_f32,
+                                 int H, cudaStream_t st) {
+  if (n_seg == 0) return 0;
+  if (H % 8 != 0 || ldd % 8 != 0 || ldg % 8 != 0 || n_seg > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+  if (g_is_f32)
+    embedding_grad_kernel<float><<<(unsigned)n_seg, 128, 0, st>>>((const __nv_bfloat16*)d, ldd, order, seg_start,
+                                                                  seg_id, (float*)g, ldg, H);
+  else
+    embedding_grad_kernel<__nv_bfloat16><<<(unsigned)n_seg, 128, 0, st>>>((const __nv_bfloat16*)d, ldd, order,
+                                                                          seg_start, seg_id, (__nv_bfloat16*)g, ldg, H);
   MSRL_LAUNCH_CHECK();
 }

@@ -376,6 +376,8 @@ def embedding_grad_accumulate(g: torch.Tensor, ids: torch.Tensor, d: torch.Tenso
         return
     order = torch.argsort(ids, stable=True)
     uniq, counts = torch.unique_consecutive(ids[order], return_counts=True)
+    if ops.embedding_grad_(g, d, order, uniq, counts):       # one block per id on the GPU
+        return
     rows = torch.segment_reduce(d[order].float(), "sum", lengths=counts, axis=0, unsafe=True)
     g[uniq] = (g[uniq].float() + rows).to(g.dtype)
 

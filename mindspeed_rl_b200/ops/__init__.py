@@ -6,7 +6,7 @@ on a GPU machine a missing kernel library is an error, never a silent fallback.
 from . import _lib
 from ._lib import available as kernels_available, launch_count, reset_launch_count
 from .layouts import QKVLayout
-from .elementwise import (add, colsum_accumulate, headnorm_bwd_, headnorm_fwd_, rmsnorm_bwd,
+from .elementwise import (add, colsum_accumulate, embedding_grad_, headnorm_bwd_, headnorm_fwd_, rmsnorm_bwd,
                           rmsnorm_fwd, rope_, rope_table, swiglu_bwd, swiglu_fwd)
 from .attention import attn_kv_bwd, attn_kv_fwd, attn_merge_, attn_varlen_bwd, attn_varlen_fwd
 from .decode import (build_decode_groups, decode_group_max, decode_prefix_tile, kv_cache_gather, kv_cache_write,

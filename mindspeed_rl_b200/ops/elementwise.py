@@ -302,3 +302,23 @@ def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         check(_lib.load().msrl_add(ptr(a), ptr(b), ptr(out), c_ll(a.numel()), stream()), "add")
         return out
     return a + b
+
+
+def embedding_grad_(g: torch.Tensor, d: torch.Tensor, order: torch.Tensor, uniq: torch.Tensor,
+                    counts: torch.Tensor) -> bool:
+    """``g[uniq[s]] += sum of d[order[t]]`` over segment ``s`` of the id-sorted tokens (``counts[s]`` tokens
+    each), rows of one id added in fp32 in token order.  Returns ``False`` (nothing done) when the kernel
+    does not cover the inputs; the caller then takes the PyTorch formulation."""
+    if not (_lib.use_kernels(g, d) and d.dtype == torch.bfloat16 and g.dtype in (torch.bfloat16, torch.float32)
+            and d.dim() == 2 and g.dim() == 2 and d.stride(1) == 1 and g.stride(1) == 1 and d.shape[1] % 8 == 0
+            and d.stride(0) % 8 == 0 and g.stride(0) % 8 == 0 and d.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0):
+        return False
+    n_seg = int(uniq.numel())
+    seg_start = torch.zeros(n_seg + 1, dtype=torch.int64, device=d.device)
+    torch.cumsum(counts, 0, out=seg_start[1:])
+    check(_lib.load().msrl_embedding_grad(ptr(d), c_ll(d.stride(0)), ptr(order.contiguous()), ptr(seg_start),
+                                          ptr(uniq.contiguous()), c_ll(n_seg), ptr(g), c_ll(g.stride(0)),
+                                          c_int(1 if g.dtype == torch.float32 else 0), c_int(d.shape[1]), stream()),
+          "embedding_grad")
+    return True
+

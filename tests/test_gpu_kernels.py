@@ -535,3 +535,25 @@ def test_canary_pads_catch_a_write_past_the_output(monkeypatch):
     with pytest.raises(RuntimeError, match="after the tensor"):
         guard.check("past the end")
     del y, t, flat
+
+
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+def test_embedding_grad_kernel_matches_fp32_sum(gdtype):
+    """Rows of equal token ids are summed in fp32 in token order into the embedding gradient; run twice, the
+    result is bit-identical."""
+    from mindspeed_rl_b200.models.gpt import embedding_grad_accumulate
+
+    torch.manual_seed(2)
+    v, h, t = 500, 3584, 3000
+    ids = torch.randint(0, 40, (t,), device=DEV)                 # many repeats per id
+    ids[::7] = torch.randint(0, v, (len(ids[::7]),), device=DEV)
+    d = torch.randn(t, h, device=DEV).bfloat16()
+    g0 = torch.randn(v, h, device=DEV).to(gdtype)
+    want = g0.float().clone()
+    want.index_add_(0, ids, d.float())
+    g1, g2 = g0.clone(), g0.clone()
+    embedding_grad_accumulate(g1, ids, d)
+    embedding_grad_accumulate(g2, ids, d)
+    assert torch.equal(g1, g2)
+    tol = 2e-2 if gdtype == torch.bfloat16 else 1e-3
+    close(g1.float(), want, tol * want.abs().max().item(), tol, "embedding grad")
