@@ -173,7 +173,8 @@ def test_rollout_moe_with_shared_experts_on_side_stream():
 
     torch.manual_seed(8)
     t, e, k, h, f, fs = 300, 8, 2, 256, 128, 384
-    cfg = TransformerConfig(num_layers=1, hidden_size=h, ffn_hidden_size=fs, num_attention_heads=2, vocab_size=64,
+    cfg = TransformerConfig(num_layers=1, hidden_size=h, ffn_hidden_size=fs, num_attention_heads=2, num_query_groups=2,
+                            vocab_size=64,
                             num_experts=e, moe_router_topk=k, moe_ffn_hidden_size=f, norm_topk_prob=True)
     router = torch.randn(e, h, device="cuda")
     w1 = (0.05 * torch.randn(h, e, 2 * f, device="cuda")).bfloat16()
