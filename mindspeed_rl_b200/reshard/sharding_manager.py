@@ -99,15 +99,54 @@ class ShardingManager:
         self.last_timing = {}
 
     # ------------------------------------------------------------------------------------------
+    def _kv_block_cap(self) -> Optional[int]:
+        """Blocks that ``max_num_seqs`` sequences of ``max_model_len`` tokens can occupy at once (plus one
+        block of slack each); ``None`` when extra blocks are useful as a prefix cache."""
+        e = self.engine
+        if getattr(e, "enable_prefix_caching", False):
+            return None
+        per_seq = (e.max_model_len + e.block_size - 1) // e.block_size + 1
+        return max(int(e.max_num_seqs) * per_seq, 16)
+
+    def _kv_budget(self) -> int:
+        """Bytes the KV cache may take right now: free memory minus the forward's head-room, at most the
+        configured fraction of the device."""
+        free, total = torch.cuda.mem_get_info(self.engine.device)
+        return min(free - self.headroom_bytes, int(total * self.gpu_memory_utilization))
+
+    def _release_needed(self) -> bool:
+        """Whether the training buffers marked for offload really have to go for the rollout: not when
+        the KV cache reaches its useful size (``_kv_block_cap``) without them.  Freeing and re-creating
+        peer-mapped segments is collective and costs a second per step on eight ranks, so the ranks of
+        the team agree (all must answer the same) and skip it when none of them needs the memory."""
+        if self.engine.device.type != "cuda" or self.num_kv_blocks:
+            return True
+        cap = self._kv_block_cap()
+        if cap is None:
+            return True
+        enough = self._kv_budget() >= cap * self.engine.kv_bytes_per_block()
+        import torch.distributed as dist
+
+        ddp = self.grad_offloader.ddp
+        owners = [b for b in (ddp.buffers if ddp is not None else []) if any(getattr(b, "_own", {}).values())]
+        if owners and dist.is_initialized():
+            # buffers with peer-mapped segments: the segment's team decides together (its group, or the
+            # whole job when the arena spans it); plain allocations are released rank by rank
+            t = torch.tensor([1 if enough else 0], dtype=torch.int32, device=self.engine.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=owners[0]._team)
+            enough = bool(int(t.item()))
+        return not enough
+
     def _kv_blocks(self) -> int:
         if self.num_kv_blocks:
             return self.num_kv_blocks
         dev = self.engine.device
         if dev.type != "cuda":
             return 256
-        free, total = torch.cuda.mem_get_info(dev)
-        budget = min(free - self.headroom_bytes, int(total * self.gpu_memory_utilization))
-        blocks = max(int(budget // self.engine.kv_bytes_per_block()), 16)
+        blocks = max(int(self._kv_budget() // self.engine.kv_bytes_per_block()), 16)
+        cap = self._kv_block_cap()
+        if cap is not None:
+            blocks = min(blocks, cap)          # more than every sequence at full length can use is only allocation time
         comm = getattr(self.engine, "comm", None)
         if comm is not None and comm.world_size > 1 and comm.group is not None:
             # the ranks of a rollout TP group run identical schedulers: they must agree on the cache
@@ -121,13 +160,15 @@ class ShardingManager:
 
     def enter_infer_mode(self) -> float:
         t0 = time.time()
-        if self.offload_train_grad:
-            self.grad_offloader.release()
         if self.offload_train_optimizer and self.optimizer is not None:
             self.optimizer.offload_state()
+        release = (self.offload_train_grad or (self.offload_train_param and self.resharder is not None)) \
+            and self._release_needed()
+        if self.offload_train_grad and release:
+            self.grad_offloader.release()
         if self.resharder is not None:
             weights = self.resharder.reshard(self.core)
-            if self.offload_train_param:
+            if self.offload_train_param and release:
                 self.param_offloader.offload()
         elif self.build_weights is not None:
             weights = self.build_weights(self.core)
