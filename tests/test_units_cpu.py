@@ -319,3 +319,19 @@ def test_canary_guard_passthrough_on_cpu(monkeypatch):
     t = guard.empty(3, 5, dtype=torch.float32, device="cpu")
     assert t.shape == (3, 5) and guard.check("cpu") == 0
     assert guard.empty_like(t).shape == (3, 5) and guard.empty((2, 2), dtype=torch.int32).dtype == torch.int32
+
+
+def test_kv_cache_cap_follows_the_engine_limits():
+    """The KV cache is capped at what the configured sequences can occupy, unless a prefix cache can use more."""
+    from types import SimpleNamespace
+
+    from mindspeed_rl_b200.reshard.sharding_manager import ShardingManager
+
+    eng = SimpleNamespace(device=torch.device("cpu"), max_model_len=3072, block_size=16, max_num_seqs=256,
+                          enable_prefix_caching=False)
+    sm = ShardingManager(torch.nn.Linear(2, 2), eng)
+    assert sm._kv_block_cap() == 256 * (3072 // 16 + 1)
+    eng.enable_prefix_caching = True
+    assert sm._kv_block_cap() is None
+    assert sm._release_needed()                      # no device memory to reason about on the CPU: release as asked
+    assert sm._kv_blocks() == 256
