@@ -98,6 +98,10 @@ OPTIM = dict(
 MEMORY = dict(
     recompute_granularity=None, recompute_method=None, recompute_num_layers=None,
     recompute_activation_function=False, swap_attention=False,
+    # accepted for recipe compatibility; both savings are built into the kernels' backward passes
+    # (the norm backward rebuilds the normalised rows, the SwiGLU backward rebuilds silu(g)*u)
+    recompute_activation_function_num_layers=None, recompute_norm=False, recompute_norm_num_layers=None,
+    swap_modules="input_norm,self_attention,post_attention_norm",
 )
 
 # --- batches, data, run control -----------------------------------------------------
@@ -105,7 +109,7 @@ RUN = dict(
     global_batch_size=None, micro_batch_size=None, seq_length=None, train_iters=None,
     eval_iters=100, eval_interval=1000, log_interval=100, log_throughput=False,
     skip_train=False, seed=1234, stage=None, algorithm=None, ai_framework=None,
-    npu_deterministic=False, enable_high_availability=False,
+    npu_deterministic=False, use_deterministic=False, enable_high_availability=False,
     tokenizer_type=None, tokenizer_name_or_path=None, tokenizer_not_use_fast=False,
     tokenizer_padding_side="right", prompt_type=None, prompt_type_path=TEMPLATES_DIR,
     data_path=None, split=None, dataloader_type=None, num_workers=2,

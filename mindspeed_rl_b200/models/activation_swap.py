@@ -20,6 +20,25 @@ import torch
 
 MIN_BYTES = 1 << 20          # smaller tensors (row statistics, log-sum-exp) stay on the device
 
+# entries of a layer's saved context by the part of the layer that produced them (``swap_modules`` names
+# the parts that take part; the rest stays on the device)
+MODULE_KEYS = {
+    "input_norm": ("h", "x1g"),
+    "self_attention": ("qkv", "attn", "pre", "lora"),
+    "post_attention_norm": ("h1", "x2g"),
+    "mlp": ("mlp_ctx",),
+}
+
+
+def keys_of(modules) -> Optional[frozenset]:
+    """Context entries covered by the named layer parts; unknown names are an error."""
+    out = set()
+    for m in modules:
+        if m not in MODULE_KEYS:
+            raise ValueError(f"swap_modules: unknown part {m!r}; known: {sorted(MODULE_KEYS)}")
+        out.update(MODULE_KEYS[m])
+    return frozenset(out)
+
 
 class _Swapped:
     """A tensor that currently lives in host memory."""
@@ -61,8 +80,9 @@ class ActivationSwapper:
         t.record_stream(self.stream)           # the allocator may reuse t only after the copy
         return _Swapped(host)
 
-    def offload(self, saved: Dict[str, Any]) -> SwapHandle:
-        """Move the large tensors of ``saved`` to the host; returns the handle the backward restores."""
+    def offload(self, saved: Dict[str, Any], keys: Optional[frozenset] = None) -> SwapHandle:
+        """Move the large tensors of ``saved`` (of its entries ``keys`` when given) to the host; returns
+        the handle the backward restores."""
         if self.cuda:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
         out: Dict[str, Any] = {}
@@ -77,10 +97,12 @@ class ActivationSwapper:
                 return seen[key]
             if isinstance(v, tuple):
                 return tuple(conv(x) for x in v)
+            if isinstance(v, dict):
+                return {k: conv(x) for k, x in v.items()}
             return v
         with ctx:
             for k, v in saved.items():
-                out[k] = conv(v)
+                out[k] = conv(v) if (keys is None or k in keys) else v
         handle = SwapHandle(out, self.last if (self.last is not None and not self.last.restored) else None)
         self.last = handle
         return handle
@@ -90,8 +112,8 @@ class ActivationSwapper:
         for v in saved.values():
             if isinstance(v, _Swapped):
                 yield v
-            elif isinstance(v, tuple):
-                for x in v:
+            elif isinstance(v, (tuple, dict)):
+                for x in (v.values() if isinstance(v, dict) else v):
                     if isinstance(x, _Swapped):
                         yield x
 
@@ -133,6 +155,8 @@ class ActivationSwapper:
                 return v.dev
             if isinstance(v, tuple):
                 return tuple(conv(x) for x in v)
+            if isinstance(v, dict):
+                return {k: conv(x) for k, x in v.items()}
             return v
         out = {k: conv(v) for k, v in handle.saved.items()}
         handle.restored = True

@@ -337,8 +337,8 @@ class _LayerFn(torch.autograd.Function):
             ctx.save_for_backward(h)
         elif getattr(layer.cfg, "swap_attention", False):
             # kept activations wait for their backward in pinned host memory
-            from .activation_swap import swapper_for
-            ctx.saved = swapper_for(h.device).offload(saved)
+            from .activation_swap import keys_of, swapper_for
+            ctx.saved = swapper_for(h.device).offload(saved, keys_of(layer.cfg.swap_modules))
             ctx.swapped = True
         else:
             ctx.saved = saved

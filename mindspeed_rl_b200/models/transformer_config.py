@@ -65,6 +65,8 @@ class TransformerConfig:
     moe_p2p_dispatch_rows: int = 0                  # rows of the peer-memory expert slabs (0: all-to-all collectives)
     moe_p2p_overflow_fallback: bool = True          # a routing that overflows a slab takes the all-to-all path for that call
     swap_attention: bool = False                    # kept activations wait for the backward in pinned host memory
+    # which parts of a layer take part: input_norm, self_attention, post_attention_norm, mlp
+    swap_modules: tuple = ("input_norm", "self_attention", "post_attention_norm", "mlp")
     # parallel sizes seen by the model code
     tensor_model_parallel_size: int = 1
     sequence_parallel: bool = False
@@ -143,6 +145,8 @@ class TransformerConfig:
             recompute_num_layers=cfg.recompute_num_layers,
             recompute_activation_function=bool(cfg.recompute_activation_function),
             swap_attention=bool(getattr(cfg, "swap_attention", False)),
+            swap_modules=_name_tuple(getattr(cfg, "swap_modules", None)
+                                     or "input_norm,self_attention,post_attention_norm"),
             tensor_model_parallel_size=cfg.tensor_model_parallel_size,
             sequence_parallel=bool(cfg.sequence_parallel) and cfg.tensor_model_parallel_size > 1,
             expert_model_parallel_size=cfg.expert_model_parallel_size,
@@ -151,3 +155,10 @@ class TransformerConfig:
         )
         kw.update(overrides)
         return cls(**kw)
+
+
+def _name_tuple(v) -> tuple:
+    """``"a, b"`` or a sequence of names -> tuple of stripped names."""
+    if isinstance(v, str):
+        v = v.split(",")
+    return tuple(str(x).strip() for x in v if str(x).strip())

@@ -157,7 +157,8 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
         if cfg.get("msprobe_config") is not None and getattr(cfg["msprobe_config"], "msprobe", False):
             worker.tensor_dump = TensorDump(cfg["msprobe_config"])
             worker.tensor_dump.save_configs({"actor": actor_config, "rl": rl_config, "generate": generate_config})
-    seed_all(actor_config.seed or 1234, deterministic=bool(getattr(actor_config, "use_deter_comp", False)))
+    seed_all(actor_config.seed or 1234, deterministic=bool(getattr(actor_config, "npu_deterministic", False)
+                                                             or getattr(actor_config, "use_deterministic", False)))
     actor_group = SPMDWorkerGroup(worker, ranks=placement.of("actor"), overlapping=disjoint).initialize()
     actor_group.rl_config, actor_group.megatron_config = rl_config, actor_config
     if worker is not None and rl_config.multi_turn_enable:

@@ -101,3 +101,15 @@ def test_swap_attention_gives_identical_gradients():
             assert sw.bytes_out == 0
     for n in grads[0]:
         assert torch.equal(grads[0][n], grads[1][n]), n
+    # restricted to some parts of a layer: fewer bytes leave, gradients unchanged; unknown names are refused
+    full_bytes = sw.bytes_out
+    m = GPTModel(TransformerConfig(swap_attention=True, swap_modules=("self_attention",), **kw), device="cpu", seed=4)
+    sw.bytes_out = sw.bytes_in = 0
+    lp, _ = m.forward_logprob(ids, labels, meta)
+    lp.sum().backward()
+    assert 0 < sw.bytes_out < full_bytes and sw.bytes_in == sw.bytes_out
+    for n, p_ in m.named_parameters():
+        assert torch.equal(grads[0][n], p_.grad), n
+    import pytest
+    with pytest.raises(ValueError):
+        activation_swap.keys_of(("attention_core",))
