@@ -12,7 +12,7 @@ import math
 import multiprocessing as mp
 import re
 import threading
-from typing import Any, Callable, List, Optional
+from typing import Any, Callable, List, Optional, Sequence
 
 # ----------------------------------------------------------------------------------------------
 # bounded execution
@@ -32,6 +32,20 @@ def call_with_timeout(fn: Callable, *args, timeout: float = 1.0, default: Any = 
     t.start()
     t.join(timeout)
     return box[0] if not t.is_alive() else default
+
+
+def bounded_map(fn: Callable, items: Sequence[Sequence[Any]], timeout: float = 1.0, default: Any = None,
+                total_timeout: Optional[float] = None) -> List[Any]:
+    """``[fn(*item) for item in items]``, every call under ``timeout`` seconds.  With more than one grading
+    process configured (``bounded_pool.set_parallel``) the calls run in worker processes, which are killed
+    and replaced when a call passes its limit; otherwise they run here, bounded by a thread join (a call
+    that never returns then leaves a sleeping daemon thread behind)."""
+    from . import bounded_pool
+
+    if bounded_pool.parallel() > 1 and len(items) > 0:
+        return bounded_pool.shared_pool().map(fn, items, timeout=timeout, default=default,
+                                              total_timeout=total_timeout)
+    return [call_with_timeout(fn, *item, timeout=timeout, default=default) for item in items]
 
 
 # ----------------------------------------------------------------------------------------------

@@ -54,28 +54,26 @@ def _strict_format_ok(s: str) -> bool:
 
 @register_verifier("strict_format")
 def strict_format_reward(sequences: Sequence[str], answers=None, **_) -> List[float]:
-    out = []
-    for s in sequences:
-        ok = G.call_with_timeout(_strict_format_ok, s, timeout=1.0, default=None)
-        out.append(0.0 if ok is None else (1.0 if ok else -0.5))
-    return out
+    oks = G.bounded_map(_strict_format_ok, [(s,) for s in sequences], timeout=1.0, default=None)
+    return [0.0 if ok is None else (1.0 if ok else -0.5) for ok in oks]
 
 
 @register_verifier("acc")
 def accuracy_reward(sequences: Sequence[str], answers: Sequence[str], **_) -> List[float]:
     """+1 correct, -0.5 boxed but wrong, -1 no boxed answer, 0 on timeout."""
-    out = []
-    for s, a in zip(sequences, answers):
+    out: List[float] = [-1.0] * len(sequences)
+    graded, pairs = [], []
+    for i, (s, a) in enumerate(zip(sequences, answers)):
         body = _strip_to_answer(s)
         if "boxed" not in body:
-            out.append(-1.0)
             continue
         pred = G.extract_answer(body)
         if pred is None or pred == "":
-            out.append(-1.0)
             continue
-        ok = G.call_with_timeout(G.math_equal, pred, a, timeout=1.0, default=None)
-        out.append(0.0 if ok is None else (1.0 if ok else -0.5))
+        graded.append(i)
+        pairs.append((pred, a))
+    for i, ok in zip(graded, G.bounded_map(G.math_equal, pairs, timeout=1.0, default=None)):
+        out[i] = 0.0 if ok is None else (1.0 if ok else -0.5)
     return out
 
 
@@ -91,12 +89,15 @@ def base_model_accuracy_reward(sequences: Sequence[str], answers: Sequence[str],
     return out
 
 
+def _boxed_correct(s: str, a: str) -> bool:
+    boxed = G.extract_boxed_content(s)
+    return boxed is not None and G.grade_answer(boxed, a)
+
+
 def _boxed_grade(sequences, answers) -> List[float]:
-    out = []
-    for s, a in zip(sequences, answers):
-        boxed = G.extract_boxed_content(s)
-        out.append(1.0 if boxed is not None and G.grade_answer(boxed, a) else 0.0)
-    return out
+    # grade_answer bounds its own symbolic step at 2 s; the outer limit only matters for worker processes
+    oks = G.bounded_map(_boxed_correct, list(zip(sequences, answers)), timeout=3.0, default=False)
+    return [1.0 if ok else 0.0 for ok in oks]
 
 
 @register_verifier("math_17k_acc")

@@ -58,6 +58,9 @@ def compute_verifier_score(batch: Dict[str, Sequence[torch.Tensor]], rl_config, 
                            ignore_token: int = -100) -> Tuple[torch.Tensor, Dict[str, List[float]], Optional[List[float]]]:
     """``batch`` holds ragged columns ``responses``, ``response_length`` and optionally ``labels``
     (+ extra dataset keys)."""
+    from . import bounded_pool
+
+    bounded_pool.set_parallel(int(getattr(rl_config, "verifier_parallel", 1) or 1))
     responses = [r.reshape(-1) for r in batch["responses"]]
     n = len(responses)
     names: List[str] = list(rl_config.verifier_function)
