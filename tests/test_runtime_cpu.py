@@ -71,3 +71,23 @@ def test_missing_acknowledgement_times_out():
     with pytest.raises(TimeoutError):
         server.broadcast("hello")
     server.close()
+
+
+def test_change_gate_chooses_the_tier_from_the_changed_files():
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "access_control_test", os.path.join(os.path.dirname(__file__), "..", "ci", "access_control_test.py"))
+    gate = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gate)
+    assert gate.choose_tier(["README.md", "profiles/x.md", "examples/grpo/a.sh"]) == "skip"
+    assert gate.choose_tier(["tests/test_units_cpu.py", "DESIGN.md"]) == "cpu"
+    assert gate.choose_tier(["tests/test_gpu_kernels.py"]) == "build"
+    assert gate.choose_tier(["mindspeed_rl_b200/csrc/decode.cu"]) == "build"
+    assert gate.choose_tier([]) == "build"
+    assert gate.commands_for("skip", gpu=True) == []
+    assert len(gate.commands_for("cpu", gpu=True)) == 1
+    cmds = gate.commands_for("build", gpu=True)
+    assert len(cmds) == 3 and cmds[-1][-1] == "gpu" and "build()" in cmds[0][-1]
+    assert len(gate.commands_for("build", gpu=False)) == 2
+    assert gate.main(["--files-from", os.devnull, "--dry-run"]) == 0
