@@ -81,7 +81,7 @@ def test_change_gate_chooses_the_tier_from_the_changed_files():
     gate = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(gate)
     assert gate.choose_tier(["README.md", "profiles/x.md", "examples/grpo/a.sh"]) == "skip"
-    assert gate.choose_tier(["tests/test_units_cpu.py", "DESIGN.md"]) == "cpu"
+    assert gate.choose_tier(["tests/test_units_cpu.py", "NOTES.md"]) == "cpu"
     assert gate.choose_tier(["tests/test_gpu_kernels.py"]) == "build"
     assert gate.choose_tier(["mindspeed_rl_b200/csrc/decode.cu"]) == "build"
     assert gate.choose_tier([]) == "build"
