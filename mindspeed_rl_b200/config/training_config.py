@@ -135,6 +135,20 @@ ADAPT = dict(
 )
 
 
+def _int_list(value, key: str):
+    """``"16,17,16,15"`` / ``[16, 17]`` / ``7`` -> list of ints; ``None`` and ``""`` stay ``None``."""
+    if value is None or value == "":
+        return None
+    if isinstance(value, str):
+        value = [v for v in value.replace(" ", "").split(",") if v]
+    elif isinstance(value, int):
+        value = [value]
+    try:
+        return [int(v) for v in value]
+    except (TypeError, ValueError):
+        raise ValueError(f"{key}: expected comma-separated integers, got {value!r}") from None
+
+
 class MegatronConfig(SchemaConfig):
     """Flat training config built from a role dict layered over a model dict.
 
@@ -162,6 +176,9 @@ class MegatronConfig(SchemaConfig):
     def _finalize(self):
         self.__dict__.pop("_model_catalogue", None)
         self.pad_to_multiple_of = self.tensor_model_parallel_size * self.context_parallel_size
+        # recipes write per-stage layer counts and empty slots as "16,17,16,15"
+        for key in ("num_layer_list", "noop_layers"):
+            self.__dict__[key] = _int_list(self.__dict__.get(key), key)
 
     # convenience accessors used by the backend ---------------------------------------
     @property

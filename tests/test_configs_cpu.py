@@ -25,6 +25,12 @@ def test_recipe_validates(name):
     assert actor.pad_to_multiple_of == actor.tensor_model_parallel_size * (actor.context_parallel_size or 1)
     if name.startswith("ppo_"):
         assert out["critic_config"] is not None and rl.critic_resource is not None
+    # the pipeline stages hold every layer exactly once (uneven stage sizes come from num_layer_list)
+    from mindspeed_rl_b200.reshard.planner import pipeline_layout
+    stages = pipeline_layout(actor, actor.pipeline_model_parallel_size)
+    layers = sorted(l for st in stages for chunk in st for l in chunk)
+    assert len(stages) == actor.pipeline_model_parallel_size and layers == list(range(len(layers)))
+    assert len(layers) == actor.num_layers - len(actor.noop_layers or [])
 
 
 def test_dpo_recipe_and_model_catalogue():
@@ -63,3 +69,15 @@ def test_tied_embeddings_with_pipeline_parallel_are_refused():
                                           "+model.tiny_qwen2.untie_embeddings_and_output_weights=false"])
     with pytest.raises(ValueError, match="tied input/output embeddings"):
         parse_training_config(cfg)
+
+
+def test_layer_lists_are_read_from_comma_separated_text():
+    from mindspeed_rl_b200.config.training_config import MegatronConfig
+    from mindspeed_rl_b200.reshard.planner import stage_layers
+    c = MegatronConfig({"num_layers": 64, "pipeline_model_parallel_size": 4, "num_layer_list": "16,17,16,15",
+                        "noop_layers": "0, 63"})
+    assert c.num_layer_list == [16, 17, 16, 15] and c.noop_layers == [0, 63]
+    assert [len(s) for s in stage_layers(64, 4, c.num_layer_list)] == [16, 17, 16, 15]
+    assert MegatronConfig({"num_layers": 4}).num_layer_list is None
+    with pytest.raises(ValueError):
+        MegatronConfig({"num_layers": 4, "num_layer_list": "2,x"})
