@@ -79,10 +79,24 @@ def test_intervals_cover_destination():
 @pytest.mark.parametrize("tp_t,pp_t,tp_i,world", [(4, 1, 2, 4), (2, 2, 1, 4), (2, 1, 4, 4), (2, 2, 2, 8),
                                                    (4, 2, 2, 8), (1, 2, 2, 4)])
 def test_plan_matches_direct_sharding(tp_t, pp_t, tp_i, world):
-    cfg = _cfg()
+    _check_plan(_cfg(), tp_t, pp_t, tp_i, world)
+
+
+# train TP x PP -> rollout TP of the shipped recipes (32B GRPO 4x4 -> 2, 32B DAPO long context 8x2 -> 4,
+# Qwen3-32B 8x2 -> 8, LoRA 4x4 -> 4, 235B 2x16 -> 4 scaled to 2x4 -> 4), one of them with uneven stages
+@pytest.mark.parametrize("tp_t,pp_t,tp_i,world,layer_list", [(4, 4, 2, 16, None), (8, 2, 4, 16, None),
+                                                              (8, 2, 8, 16, None), (4, 4, 4, 16, [1, 2, 1, 1]),
+                                                              (2, 4, 4, 8, None)])
+def test_plan_for_recipe_layouts(tp_t, pp_t, tp_i, world, layer_list):
+    cfg = _cfg(num_attention_heads=16, num_query_groups=8, kv_channels=8,
+               num_layers=sum(layer_list) if layer_list else 4)
+    _check_plan(cfg, tp_t, pp_t, tp_i, world, layer_list)
+
+
+def _check_plan(cfg, tp_t, pp_t, tp_i, world, layer_list=None):
     full = GPTModel(cfg, seed=3).state_dict()
     train = RankLayout(world, tp=tp_t, pp=pp_t)
-    layers = stage_layers(cfg.num_layers, pp_t)
+    layers = stage_layers(cfg.num_layers, pp_t, layer_list)
     buffers, tables = {}, [None] * pp_t
     for r in range(world):
         c = train.coords(r)
@@ -104,7 +118,7 @@ def test_plan_matches_direct_sharding(tp_t, pp_t, tp_i, world):
         mp = [m for g in train.groups("tp", "pp") if r in g for m in g]
         assert {d[0] for d in plan.desc} <= set(mp)
         w = weights_from_buffer(cfg, tp_i, j, plan, dst, torch.float32)
-        assert w.layers[0].qkv_w.shape[0] == (cfg.num_attention_heads + 2 * cfg.num_query_groups) // tp_i * 16
+        assert w.layers[0].qkv_w.shape[0] == (cfg.num_attention_heads + 2 * cfg.num_query_groups) // tp_i * cfg.kv_channels
         assert w.vocab_start == j * cfg.vocab_size // tp_i
 
 
