@@ -301,3 +301,55 @@ def test_plan_mixes_element_sizes_and_buffers():
             assert router.dtype == torch.float32 and torch.equal(router, full[f"decoder.layers.{li}.mlp.router.weight"])
             assert w1.dtype == torch.bfloat16 and torch.equal(
                 w1, full[f"decoder.layers.{li}.mlp.experts.weight1"].to(torch.bfloat16))
+
+
+def test_plan_for_expert_recipe_layout_with_experts_spread_over_tp():
+    """The 30B-A3B recipe's shape: train TP4 x EP2 with the experts spread over TP x EP (8 expert shards, expert
+    TP 1), rollout TP1 x EP8: dense weights are gathered over TP, every rollout rank ends up with its block of
+    experts, whichever training rank held them."""
+    from mindspeed_rl_b200.reshard.planner import ExpertPlacement
+
+    cfg = _moe_cfg()
+    full = GPTModel(cfg, seed=9).state_dict()
+    world, tp_t, ep_t, ep_i = 8, 4, 2, 8
+    train = RankLayout(world, tp=tp_t, ep=ep_t, moe_tp_extend_ep=True)
+    assert train.ep_total == 8 and train.expert_tp == 1
+    layers = stage_layers(cfg.num_layers, 1)
+    h, f, e = cfg.hidden_size, cfg.moe_ffn_hidden_size, cfg.num_experts
+    buffers, tables = {}, [None]
+    for r in range(world):
+        c, ec = train.coords(r), train.expert_coords(r)
+        st = _shard(_expert_shard(full, cfg, train.ep_total, ec["ep"]), cfg, tp_t, c["tp"])
+        slots, flat = _flatten(_stage_state(st, layers[0], True, True))
+        tables[0] = slots
+        buffers[r] = flat.view(torch.uint8)
+    infer = RankLayout(world, ep=ep_i)
+    for r in range(world):
+        ei = infer.expert_coords(r)["ep"]
+        mine = train.expert_coords(r)
+        per = e // ep_i
+
+        def hosted(layer, ei=ei):
+            return list(range(ei * per, (ei + 1) * per))
+
+        def src_rank(ep_index, stage, mine=mine):
+            stage_rank = mine["etp"] + train.expert_tp * (ep_index + train.ep_total * mine["edp"])
+            return train.rank_of(tp=stage_rank % train.tp, cp=(stage_rank // train.tp) % train.cp,
+                                 dp=stage_rank // (train.tp * train.cp), pp=stage)
+
+        plan = build_plan(cfg, train, 1, r, tables, layers, lambda rank: 0, esz=4,
+                          experts=ExpertPlacement(e // train.ep_total, hosted, src_rank))
+        dst = torch.zeros(plan.nbytes, dtype=torch.uint8)
+        execute_plan_torch(plan, buffers, dst)
+        want = _shard(full, cfg, 1, 0)
+        for name, (off, shape) in plan.tensors.items():
+            if ".experts." in name:
+                layer = int(name.split(".")[2])
+                ids = hosted(layer)
+                key = f"decoder.layers.{layer}.mlp.experts."
+                ref = (full[key + "weight1"].view(h, e, 2 * f)[:, ids] if name.endswith("weight1")
+                       else full[key + "weight2"].view(e, f, h)[ids]).reshape(shape)
+            else:
+                ref = want[name]
+            got = dst[off:off + ref.numel() * 4].view(torch.float32).view(shape)
+            assert torch.equal(got, ref), (r, name)
