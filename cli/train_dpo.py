@@ -61,11 +61,12 @@ def main(argv=None):
     train, _, _ = build_train_valid_test_datasets(mc.data_path, mc.split or "100,0,0", mc.seq_length,
                                                   [iters * mc.global_batch_size, 0, 0], PromptDataset, tokenizer,
                                                   no_shuffle=mc.no_shuffle, seed=mc.seed, extra_param=extra)
-    per_rank = max(mc.global_batch_size // ps.size("dp_cp"), 1)
-    loader = InfiniteLoader(PromptDataLoader(train, per_rank, 0, mc.seed + ps.rank_in("dp_cp"), no_shuffle=mc.no_shuffle,
+    # every rank draws the same global batches (same seed); the trainer keeps this replica's slice of the pairs
+    loader = InfiniteLoader(PromptDataLoader(train, mc.global_batch_size, 0, mc.seed, no_shuffle=mc.no_shuffle,
                                              is_pairwise_dataset=True, tokenizer=getattr(tokenizer, "tokenizer", None)))
     trainer = DPOTrainer(model, ref, opt, sch, beta=mc.dpo_beta, loss_type=mc.dpo_loss_type, train_iters=iters, device=device,
                          pad_multiple=ps.size("tp") * ps.size("cp"), log_interval=mc.log_interval or 1,
+                         dp_group=ps.group("dp_cp"), dp_rank=ps.rank_in("dp_cp"), dp_size=ps.size("dp_cp"),
                          save_fn=(lambda it: save_checkpoint(mc.save, it, core, opt, sch, ps, mc)) if mc.save else None,
                          save_interval=mc.save_interval or 0)
     hist = trainer.train(loader)

@@ -75,18 +75,45 @@ def dpo_loss(pi_c, pi_r, ref_c, ref_r, beta: float, loss_type: str = "sigmoid", 
 class DPOTrainer:
     def __init__(self, model, ref_model: Optional[GPTModel], optimizer, scheduler=None, *, beta: float = 0.1,
                  loss_type: str = "sigmoid", train_iters: int = 1, device=None, pad_multiple: int = 1,
-                 dp_group=None, log_interval: int = 1, save_fn=None, save_interval: int = 0):
+                 dp_group=None, dp_rank: int = 0, dp_size: int = 1, log_interval: int = 1, save_fn=None,
+                 save_interval: int = 0):
+        """``dp_size`` > 1: every rank is handed the same global batch and trains on its own slice of the pairs
+        (rows ``[rank * B / dp, (rank + 1) * B / dp)`` of the chosen and of the rejected half); the reported
+        numbers are averaged over ``dp_group``."""
         self.model = model
         self.core = model.module if hasattr(model, "module") else model
         self.ref_model, self.optimizer, self.scheduler = ref_model, optimizer, scheduler
         self.beta, self.loss_type, self.train_iters = beta, loss_type, train_iters
         self.device = device or next(self.core.parameters()).device
         self.pad_multiple, self.dp_group = pad_multiple, dp_group
+        self.dp_rank, self.dp_size = dp_rank, max(int(dp_size), 1)
         self.log_interval, self.save_fn, self.save_interval = log_interval, save_fn, save_interval
         self.logger = Loggers("DPOTrainer")
         self.iteration = 0
 
+    def _my_pairs(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        if self.dp_size == 1:
+            return batch
+        half = batch["input_ids"].shape[0] // 2
+        if half % self.dp_size:
+            raise ValueError(f"{half} pairs per step do not divide over {self.dp_size} data-parallel ranks")
+        per = half // self.dp_size
+        rows = torch.arange(self.dp_rank * per, (self.dp_rank + 1) * per)
+        rows = torch.cat([rows, half + rows])
+        return {k: (v[rows] if torch.is_tensor(v) and v.dim() > 0 and v.shape[0] == 2 * half else v)
+                for k, v in batch.items()}
+
+    def _mean_over_replicas(self, values: Dict[str, float]) -> Dict[str, float]:
+        if self.dp_size == 1 or not (dist.is_available() and dist.is_initialized()):
+            return values
+        keys = sorted(values)
+        dev = self.device if dist.get_backend(self.dp_group) == "nccl" else "cpu"
+        t = torch.tensor([values[k] for k in keys], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, group=self.dp_group)
+        return {k: float(v) / self.dp_size for k, v in zip(keys, t.tolist())}
+
     def train_step(self, batch: Dict[str, torch.Tensor]) -> Dict[str, float]:
+        batch = self._my_pairs(batch)
         half = batch["input_ids"].shape[0] // 2
         if hasattr(self.model, "zero_grad_buffer"):
             self.model.zero_grad_buffer()
@@ -103,10 +130,13 @@ class DPOTrainer:
         _, grad_norm, _ = self.optimizer.step()
         if self.scheduler is not None:
             self.scheduler.step(increment=2 * half)
-        return {"dpo/loss": float(loss), "dpo/rewards_chosen": float(cr.mean()),
-                "dpo/rewards_rejected": float(rr.mean()), "dpo/accuracy": float((cr > rr).float().mean()),
-                "dpo/margin": float((cr - rr).mean()), "grad_norm": float(grad_norm),
-                "lr": self.optimizer.param_groups[0]["lr"]}
+        out = self._mean_over_replicas({
+            "dpo/loss": float(loss.detach()), "dpo/rewards_chosen": float(cr.mean()), "dpo/rewards_rejected": float(rr.mean()),
+            "dpo/accuracy": float((cr > rr).float().mean()), "dpo/margin": float((cr - rr).mean())})
+        out["grad_norm"] = float(grad_norm)
+        out["lr"] = self.optimizer.param_groups[0]["lr"]
+        out["pairs"] = half * self.dp_size
+        return out
 
     def train(self, data_iter: Iterator[Dict[str, torch.Tensor]]) -> List[Dict[str, float]]:
         history = []
@@ -114,8 +144,8 @@ class DPOTrainer:
             t0 = time.time()
             m = self.train_step(next(data_iter))
             self.iteration += 1
-            m["samples_per_sec"] = 0.0
             dt = time.time() - t0
+            m["samples_per_sec"] = m.pop("pairs") / max(dt, 1e-9)
             m["time"] = dt
             history.append(m)
             if self.iteration % self.log_interval == 0:
