@@ -83,7 +83,8 @@ def main(argv=None):
         chunk = -(-len(rows) // cfg.n_subs)
         base = {k: v for k, v in cfg.dict().items()}
         jobs = [(base, rows[i * chunk:(i + 1) * chunk], i) for i in range(cfg.n_subs) if rows[i * chunk:(i + 1) * chunk]]
-        with mp.Pool(min(cfg.workers, len(jobs))) as pool:
+        # fresh interpreters: the parent may already run threads (tokenizers, torch), which a fork would copy mid-flight
+        with mp.get_context("spawn").Pool(min(cfg.workers, len(jobs))) as pool:
             parts = pool.map(_run_part, jobs)
         prefixes = {f: p.replace("_000_packed", "_packed") for f, p in parts[0].items()}
         _merge(parts, prefixes)

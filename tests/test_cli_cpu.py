@@ -1,0 +1,94 @@
+"""Command-line entry points end to end on CPU with the whitespace-integer tokenizer: raw JSON lines ->
+``cli/preprocess_data.py`` -> packed ``.bin/.idx`` -> datasets / the DPO trainer."""
+import importlib
+import json
+import os
+import random
+import sys
+
+import numpy as np
+import yaml
+
+ROOT = os.path.join(os.path.dirname(__file__), "..")
+
+
+def _cli(name):
+    if os.path.abspath(ROOT) not in [os.path.abspath(p) for p in sys.path]:
+        sys.path.insert(0, os.path.abspath(ROOT))
+    return importlib.import_module(f"cli.{name}")        # importable by name: its workers are pickled by reference
+
+
+def _numbers(rng, n):
+    return " ".join(str(rng.randint(3, 90)) for _ in range(n))
+
+
+def test_preprocess_pairwise_then_dpo_cli(tmp_path):
+    rng = random.Random(0)
+    rows = [{"question": _numbers(rng, 6), "chosen": _numbers(rng, 4), "rejected": _numbers(rng, 5), "system": ""}
+            for _ in range(16)]
+    (tmp_path / "pairs.jsonl").write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    (tmp_path / "out").mkdir()
+    yaml.safe_dump(dict(input=str(tmp_path / "pairs.jsonl"), tokenizer_name_or_path="none", tokenizer_type="Identity",
+                        pad_vocab_size_to=96, output_prefix=str(tmp_path / "out" / "pairs"),
+                        handler_name="AlpacaStylePairwiseHandler", workers=1, prompt_type="empty",
+                        map_keys={"prompt": "question", "query": "", "system": "system"}),
+                   open(tmp_path / "pairs.yaml", "w"))
+    prefixes = _cli("preprocess_data").main(["pairs", "--config-dir", str(tmp_path)])
+    assert set(prefixes) == {"chosen_input_ids", "chosen_labels", "rejected_input_ids", "rejected_labels"}
+    for p in prefixes.values():
+        assert os.path.getsize(p + ".bin") > 0 and os.path.getsize(p + ".idx") > 0
+
+    # the first pair comes back as written: prompt tokens masked in the labels, answers kept
+    from mindspeed_rl_b200.datasets.indexed_dataset import get_packed_indexed_dataset
+    ds = get_packed_indexed_dataset(str(tmp_path / "out" / "pairs"), None, True)
+    first = ds[0]
+    q = [int(t) for t in rows[0]["question"].split()]
+    c = [int(t) for t in rows[0]["chosen"].split()]
+    ids, labels = list(first["chosen_input_ids"]), list(first["chosen_labels"])
+    assert ids[:len(q)] == q and ids[len(q):len(q) + len(c)] == c
+    assert all(l == -100 for l in labels[:len(q)]) and labels[len(q):len(q) + len(c)] == c
+
+    recipe = {"defaults": [{"model": ["tiny_qwen2"]}],
+              "megatron_training": dict(model="tiny_qwen2", stage="dpo", is_pairwise_dataset=True, dpo_beta=0.1,
+                                        dpo_loss_type="sigmoid", tensor_model_parallel_size=1,
+                                        pipeline_model_parallel_size=1, global_batch_size=4, micro_batch_size=1,
+                                        seq_length=64, train_iters=3, lr=1e-4, min_lr=0, lr_decay_style="constant",
+                                        weight_decay=0.0, clip_grad=1.0, bf16=False, tokenizer_type="Identity",
+                                        tokenizer_name_or_path="none", data_path=str(tmp_path / "out" / "pairs"),
+                                        split="100,0,0", seed=1234, distributed_backend="gloo", log_interval=1,
+                                        save=str(tmp_path / "ckpt"), save_interval=3)}
+    yaml.safe_dump(recipe, open(tmp_path / "dpo_tiny.yaml", "w"))
+    hist = _cli("train_dpo").main(["--config-name", "dpo_tiny", "--config-dir", str(tmp_path)])
+    assert len(hist) == 3
+    assert abs(hist[0]["dpo/loss"] - float(np.log(2.0))) < 1e-5          # policy == reference at the start
+    assert all(np.isfinite(h["dpo/loss"]) and h["grad_norm"] > 0 and h["samples_per_sec"] > 0 for h in hist)
+    assert (tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
+
+
+def test_preprocess_prompts_in_parts_and_read_back(tmp_path):
+    """RL prompts with reference answers, tokenised by two worker processes and merged; the prompt dataset
+    serves every row once per epoch and keeps its shuffle index on disk."""
+    rng = random.Random(1)
+    rows = [{"problem": _numbers(rng, 5 + i % 3), "answer": str(i)} for i in range(20)]
+    (tmp_path / "prompts.jsonl").write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    (tmp_path / "out").mkdir()
+    yaml.safe_dump(dict(input=str(tmp_path / "prompts.jsonl"), tokenizer_name_or_path="none", tokenizer_type="Identity",
+                        pad_vocab_size_to=96, output_prefix=str(tmp_path / "out" / "data"),
+                        handler_name="R1AlpacaStyleInstructionHandler", workers=2, n_subs=2, prompt_type="empty",
+                        dataset_additional_keys=["labels"],
+                        map_keys={"prompt": "problem", "query": "", "response": "answer", "system": ""}),
+                   open(tmp_path / "prompts.yaml", "w"))
+    prefixes = _cli("preprocess_data").main(["prompts", "--config-dir", str(tmp_path)])
+    assert {"input_ids", "labels"} <= set(prefixes)
+
+    from mindspeed_rl_b200.datasets.prompt_dataset import PromptDataset, build_train_valid_test_datasets
+    extra = type("A", (), dict(is_pairwise_dataset=False, dataset_additional_keys=["labels"], max_prompt_length=None))()
+    train, valid, _ = build_train_valid_test_datasets(str(tmp_path / "out" / "data"), "100,0,0", 64, [20, 0, 0],
+                                                      PromptDataset, None, seed=3, extra_param=extra)
+    assert valid is None and len(train) == 20
+    seen = sorted(tuple(int(t) for t in train[i]["input_ids"]) for i in range(20))
+    want = sorted(tuple(int(t) for t in r["problem"].split()) for r in rows)
+    assert seen == want
+    answers = sorted(int(train[i]["labels"][0]) for i in range(20))
+    assert answers == list(range(20))
+    assert any(f.endswith(".npy") for f in os.listdir(tmp_path / "out")), "no shuffle-index cache was written"
