@@ -92,3 +92,57 @@ def test_preprocess_prompts_in_parts_and_read_back(tmp_path):
     answers = sorted(int(train[i]["labels"][0]) for i in range(20))
     assert answers == list(range(20))
     assert any(f.endswith(".npy") for f in os.listdir(tmp_path / "out")), "no shuffle-index cache was written"
+
+
+def test_convert_ckpt_cli_round_trip(tmp_path):
+    """HF layout -> mcore shards for TP2 x PP2 -> HF layout through the command line, for the tiny architecture;
+    the mcore shards also load into a TP1 model built from the same architecture file."""
+    import torch
+    from mindspeed_rl_b200.checkpoint import convert as C
+    from mindspeed_rl_b200.config import MegatronConfig
+    from mindspeed_rl_b200.config.loader import load_model_catalogue
+    from mindspeed_rl_b200.models.gpt import GPTModel
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+
+    cfg = MegatronConfig({"model": "tiny_qwen2"}, load_model_catalogue(["tiny_qwen2"]))
+    model = GPTModel(TransformerConfig.from_megatron(cfg, params_dtype=torch.float32), device="cpu", seed=2)
+    hf = C.mcore_to_hf({(0, 0, 0): model.state_dict()}, cfg)
+    C.save_hf_state(hf, str(tmp_path / "hf"))
+    cli = _cli("convert_ckpt")
+    cli.main(["hf2mcore", "--model", "tiny_qwen2", "--load", str(tmp_path / "hf"), "--save", str(tmp_path / "mcore"),
+              "--tp", "2", "--pp", "2"])
+    assert (tmp_path / "mcore" / "latest_checkpointed_iteration.txt").exists()
+    cli.main(["mcore2hf", "--model", "tiny_qwen2", "--load", str(tmp_path / "mcore"), "--save", str(tmp_path / "hf2"),
+              "--tp", "2", "--pp", "2"])
+    back = C.load_hf_state(str(tmp_path / "hf2"))
+    assert set(back) == set(hf)
+    for k in hf:
+        assert torch.equal(back[k], hf[k]), k
+    cli.main(["hf2mcore", "--model", "tiny_qwen2", "--load", str(tmp_path / "hf2"), "--save", str(tmp_path / "one")])
+    again = GPTModel(TransformerConfig.from_megatron(cfg, params_dtype=torch.float32), device="cpu", seed=5)
+    missing, unexpected = again.load_state_dict(C.read_mcore(str(tmp_path / "one"), 1, 1)[(0, 0, 0)], strict=False)
+    assert not missing and not unexpected
+    for (n, a), (_, b) in zip(model.named_parameters(), again.named_parameters()):
+        assert torch.equal(a, b), n
+
+
+def test_eplb_map_cli_from_dumped_counts(tmp_path):
+    """Routing counts dumped by two rollout ranks -> placement map with one redundant slot per device: every
+    expert is hosted somewhere, the hottest expert twice, and the slots of a layer fill all devices evenly."""
+    layers, experts, gpus = 3, 8, 4
+    rng = random.Random(4)
+    for rank in range(2):
+        data = {str(l): {str(e): rng.randint(1, 50) + (400 if e == 5 else 0) for e in range(experts)}
+                for l in range(layers)}
+        (tmp_path / f"eplb_token_collects_{rank}.json").write_text(json.dumps(data))
+    out = tmp_path / "expert_map.json"
+    _cli("eplb_generate_map").main(["--json_folder", str(tmp_path), "--num_gpus", str(gpus), "--num_redundancy", "1",
+                                    "--output", str(out)])
+    emap = json.loads(out.read_text())
+    assert emap["moe_layer_count"] == layers
+    for layer in emap["layer_list"]:
+        hosted = [d["device_expert"] for d in layer["device_list"]]
+        assert len(hosted) == gpus and all(len(h) == experts // gpus + 1 for h in hosted)
+        flat = [e for h in hosted for e in h]
+        assert set(flat) == set(range(experts)) and flat.count(5) >= 2
+        assert all(len(set(h)) == len(h) for h in hosted)
