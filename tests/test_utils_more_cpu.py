@@ -1,0 +1,176 @@
+"""Packing helpers, context-parallel slicing, vocabulary-parallel log-probabilities and the samplers,
+each against a direct PyTorch formulation."""
+from types import SimpleNamespace
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_distributed
+from mindspeed_rl_b200.utils import context_parallel as CP
+from mindspeed_rl_b200.utils import compute as U
+from mindspeed_rl_b200.utils.remove_padding import packed_layout, postprocess_packed_seqs, preprocess_packed_seqs
+
+
+def _padded_batch(lens, s, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(1, 100, (len(lens), s), generator=g)
+    mask = (torch.arange(s).unsqueeze(0) < torch.tensor(lens).unsqueeze(1)).long()
+    return ids * mask, mask
+
+
+def test_pack_and_unpack_padded_batch():
+    lens, s, align = [5, 9, 1, 12], 12, 4
+    ids, mask = _padded_batch(lens, s)
+    labels = ids + 1000
+    p_ids, pos, p_lab, seqlens, cu = preprocess_packed_seqs(ids, labels, mask, align)
+    assert seqlens.tolist() == lens and cu.tolist() == [0, 8, 20, 24, 36] and cu.dtype == torch.int32
+    assert p_ids.shape == (1, 36) and pos.shape == (1, 36)
+    for b, n in enumerate(lens):
+        lo, hi = int(cu[b]), int(cu[b + 1])
+        assert p_ids[0, lo:lo + n].tolist() == ids[b, :n].tolist()
+        assert p_lab[0, lo:lo + n].tolist() == labels[b, :n].tolist()
+        assert p_ids[0, lo + n:hi].abs().sum() == 0                      # alignment padding is zero
+        assert pos[0, lo:hi].tolist() == list(range(hi - lo))          # positions restart per block
+    padded, cu2 = packed_layout(torch.tensor(lens), align)
+    assert padded.tolist() == [8, 12, 4, 12] and torch.equal(cu2, cu)
+    # back to [B, S, F] with a trailing feature dim
+    feat = torch.stack([p_ids[0].float(), p_ids[0].float() * 2], dim=-1).unsqueeze(0)
+    back = postprocess_packed_seqs(feat, seqlens, cu, s)
+    assert back.shape == (4, s, 2)
+    assert torch.equal(back[..., 0].long(), ids) and torch.equal(back[..., 1].long(), 2 * ids)
+    # dropping the prompt: row b starts at the position that predicts the first response token
+    prompt = torch.tensor([2, 4, 1, 12])
+    out = postprocess_packed_seqs(p_ids.float(), seqlens, cu, 6, prompt_length=prompt)
+    for b, (n, p) in enumerate(zip(lens, prompt.tolist())):
+        if p - 1 < n:
+            want = ids[b, p - 1:n - 1].tolist()[:6]
+        else:
+            want = ids[b, :n].tolist()[:6]
+        assert out[b, :len(want)].long().tolist() == want, b
+        assert out[b, len(want):].abs().sum() == 0
+    with pytest.raises(ValueError):
+        preprocess_packed_seqs(ids, labels, mask[:, :-1], align)
+
+
+def test_context_parallel_slices_and_restore():
+    cfg = SimpleNamespace(context_parallel_size=2, context_parallel_algo=CP.RING, reset_attention_mask=False)
+    x = torch.arange(16).reshape(1, 16)
+    kept = []
+    for r in range(2):
+        out, idx = CP.get_batch_on_this_cp_rank(cfg, {"tokens": x, "attention_mask": None, "none": None}, cp_rank=r)
+        kept.append(idx)
+        assert out["tokens"].tolist() == [[*range(4 * r, 4 * r + 4), *range(16 - 4 * (r + 1), 16 - 4 * r)]]
+        assert out["attention_mask"] is None
+    perm = CP.restore_permutation(torch.cat(kept))
+    assert torch.cat([x[:, i] for i in kept], dim=1)[:, perm].tolist() == x.tolist()
+    # packed: the zig-zag applies to every block on its own
+    cfg.reset_attention_mask = True
+    cu = torch.tensor([0, 8, 24], dtype=torch.int32)
+    x = torch.arange(24).reshape(1, 24)
+    got = [CP.get_batch_on_this_cp_rank(cfg, {"tokens": x}, cu, cp_rank=r)[0]["tokens"][0].tolist() for r in range(2)]
+    assert got[0] == [0, 1, 6, 7, 8, 9, 10, 11, 20, 21, 22, 23]
+    assert got[1] == [2, 3, 4, 5, 12, 13, 14, 15, 16, 17, 18, 19]
+    # all-to-all flavour: contiguous chunks, no index
+    cfg.context_parallel_algo = CP.ULYSSES
+    out, idx = CP.get_batch_on_this_cp_rank(cfg, {"tokens": x}, cp_rank=1)
+    assert idx is None and out["tokens"][0].tolist() == list(range(12, 24))
+    # ring degree of the three algorithms
+    assert CP.get_ring_degree(SimpleNamespace(context_parallel_size=1)) == 1
+    assert CP.get_ring_degree(SimpleNamespace(context_parallel_size=4, context_parallel_algo=CP.RING)) == 4
+    assert CP.get_ring_degree(SimpleNamespace(context_parallel_size=4, context_parallel_algo=CP.ULYSSES)) == 1
+    hybrid = SimpleNamespace(context_parallel_size=4, context_parallel_algo="hybrid_cp_algo", ulysses_degree_in_cp=2)
+    assert CP.get_ring_degree(hybrid) == 2
+    hybrid.ulysses_degree_in_cp = 4
+    with pytest.raises(ValueError):
+        CP.get_ring_degree(hybrid)
+
+
+def _cp_gather_worker(rank, world):
+    full = torch.arange(48, dtype=torch.float32).reshape(2, 24)
+    cu = torch.tensor([0, 8, 24], dtype=torch.int32)
+    mine = full.index_select(1, CP.zigzag_index_packed(cu, world, rank))
+    assert torch.equal(CP.gather_cp_outputs(mine, world, None, cu, ring=True), full)
+    assert torch.equal(CP.get_tensor_allgather_cp_with_pack(mine, world, 1, None, cu), full)
+    mine = full.index_select(1, CP.zigzag_index_plain(24, world, rank))
+    assert torch.equal(CP.get_tensor_allgather_cp_without_pack(mine, world, 1), full)
+    mine = full.chunk(world, dim=1)[rank].clone().requires_grad_(True)
+    out = CP.gather_cp_outputs(mine, world)
+    assert torch.equal(out.detach(), full)
+    out.sum().backward()                                            # autograd flows through the local slice only
+    assert torch.equal(mine.grad, torch.ones_like(mine))
+
+
+def test_context_parallel_gather_restores_global_order():
+    run_distributed(_cp_gather_worker, 2)
+
+
+def _logprob_oracle(logits, labels):
+    lsm = torch.log_softmax(logits.double(), -1)
+    lp = lsm.gather(-1, labels.unsqueeze(-1)).squeeze(-1)
+    ent = -(lsm.exp() * lsm).sum(-1)
+    return lp, ent
+
+
+def test_log_probs_and_entropy_single_rank_with_gradients():
+    torch.manual_seed(0)
+    logits = torch.randn(3, 7, 50, dtype=torch.float64, requires_grad=True)
+    labels = torch.randint(0, 50, (3, 7))
+    lp, ent = U.log_probs_and_entropy(logits, labels)
+    want_lp, want_ent = _logprob_oracle(logits, labels)
+    assert torch.allclose(lp.double(), want_lp, atol=1e-5) and torch.allclose(ent.double(), want_ent, atol=1e-5)
+    w1, w2 = torch.randn(3, 7, dtype=torch.float64), torch.randn(3, 7, dtype=torch.float64)
+    (g,) = torch.autograd.grad((lp * w1).sum() + (ent * w2).sum(), logits)
+    (gw,) = torch.autograd.grad((want_lp * w1).sum() + (want_ent * w2).sum(), logits)
+    assert torch.allclose(g, gw, atol=1e-5)
+    assert U.log_probs_and_entropy(logits, labels, want_entropy=False)[1] is None
+    assert torch.equal(U.compute_log_probs(logits, labels), U.vocab_parallel_log_probs(logits, labels))
+
+
+def _vocab_parallel_worker(rank, world):
+    torch.manual_seed(1)
+    full = torch.randn(2, 5, 64, dtype=torch.float64)
+    labels = torch.randint(0, 64, (2, 5))
+    w1, w2 = torch.randn(2, 5, dtype=torch.float64), torch.randn(2, 5, dtype=torch.float64)
+    ref = full.clone().requires_grad_(True)
+    want_lp, want_ent = _logprob_oracle(ref, labels)
+    (gw,) = torch.autograd.grad((want_lp * w1).sum() + (want_ent * w2).sum(), ref)
+    part = 64 // world
+    shard = full[..., rank * part:(rank + 1) * part].clone().requires_grad_(True)
+    lp, ent = U.log_probs_and_entropy(shard, labels, dist.group.WORLD)
+    assert torch.allclose(lp.double(), want_lp, atol=1e-5) and torch.allclose(ent.double(), want_ent, atol=1e-5)
+    (g,) = torch.autograd.grad((lp * w1).sum() + (ent * w2).sum(), shard)
+    assert torch.allclose(g, gw[..., rank * part:(rank + 1) * part], atol=1e-5)
+
+
+def test_log_probs_and_entropy_over_a_sharded_vocabulary():
+    run_distributed(_vocab_parallel_worker, 2)
+
+
+def test_kl_penalties():
+    lp, ref = torch.tensor([-1.0, -2.0, -30.0]), torch.tensor([-1.5, -1.0, -1.0])
+    assert torch.allclose(U.compute_kl_penalty(lp, ref, "kl"), lp - ref)
+    assert torch.allclose(U.compute_kl_penalty(lp, ref, "abs"), (lp - ref).abs())
+    assert torch.allclose(U.compute_kl_penalty(lp, ref, "mse"), 0.5 * (lp - ref) ** 2)
+    k3 = U.compute_kl_penalty(lp, ref, "low_var_kl")
+    k = ref - lp
+    assert torch.allclose(k3[:2], torch.exp(k[:2]) - k[:2] - 1)
+    assert float(k3[2]) == 10.0                                   # exponent clamped at 20, value at 10
+    with pytest.raises(NotImplementedError):
+        U.compute_kl_penalty(lp, ref, "nope")
+
+
+def test_samplers_cover_their_slices_and_resume():
+    from mindspeed_rl_b200.datasets.dataloader import PretrainingSampler, PromptSampler
+    assert list(PromptSampler(10, 0, 4)) == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert list(PromptSampler(10, 4, 4, drop_last=False)) == [[4, 5, 6, 7], [8, 9]]      # resume after 4 samples
+    with pytest.raises(ValueError):
+        PromptSampler(10, 10, 4)
+    with pytest.raises(ValueError):
+        PromptSampler(0, 0, 4)
+    per_rank = [list(PretrainingSampler(12, 0, 2, r, 3)) for r in range(3)]
+    assert per_rank[0] == [[0, 1], [6, 7]] and per_rank[1] == [[2, 3], [8, 9]] and per_rank[2] == [[4, 5], [10, 11]]
+    assert list(PretrainingSampler(12, 6, 2, 1, 3)) == [[8, 9]]
+    assert list(PretrainingSampler(8, 0, 2, 0, 3, drop_last=False)) == [[0, 1], [6, 7]]
+    with pytest.raises(ValueError):
+        PretrainingSampler(8, 0, 2, 3, 3)
