@@ -20,7 +20,14 @@ from typing import Any, Callable, List, Optional, Sequence
 
 
 def _import(name: str) -> bool:
+    """Import ``name`` in the worker and run its ``warm_up()`` when it has one (slow first-use set-up that
+    must not count against a call's limit)."""
+    import sys
+
     __import__(name)
+    init = getattr(sys.modules[name], "warm_up", None)
+    if callable(init):
+        init()
     return True
 
 

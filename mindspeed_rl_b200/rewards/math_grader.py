@@ -17,9 +17,48 @@ from typing import Any, Callable, List, Optional, Sequence
 # ----------------------------------------------------------------------------------------------
 # bounded execution
 # ----------------------------------------------------------------------------------------------
+_warm = False
+
+
+def warm_up() -> None:
+    """Load the symbolic-algebra package once, outside any time limit: its first import takes seconds, which
+    would otherwise make the first graded answer of a process time out (and score as wrong)."""
+    global _warm
+    if _warm:
+        return
+    _warm = True
+    try:
+        import sympy
+        from sympy.parsing.sympy_parser import parse_expr
+
+        sympy.simplify(parse_expr("x + 1") - parse_expr("1 + x"))
+    except Exception:
+        pass
+    _latex_parser()
+
+
+_parse_latex: Any = False            # False: not looked up yet; None: unavailable
+
+
+def _latex_parser():
+    """sympy's LaTeX front end when its grammar runtime is installed (looked up once: the failed import alone
+    takes a second)."""
+    global _parse_latex
+    if _parse_latex is False:
+        try:
+            from sympy.parsing.latex import parse_latex
+
+            parse_latex("x")
+            _parse_latex = parse_latex
+        except Exception:
+            _parse_latex = None
+    return _parse_latex
+
+
 def call_with_timeout(fn: Callable, *args, timeout: float = 1.0, default: Any = None, **kw) -> Any:
     """Run ``fn`` in a daemon thread and give up after ``timeout`` seconds (returns ``default``).
     Exceptions inside ``fn`` also yield ``default``."""
+    warm_up()
     box: List[Any] = [default]
 
     def run():
@@ -176,9 +215,10 @@ def symbolic_equal(a: str, b: str) -> bool:
     except Exception:
         return False
 
+    latex = _latex_parser()
+
     def parse(s):
-        for f in (lambda x: __import__("sympy.parsing.latex", fromlist=["parse_latex"]).parse_latex(x),
-                  lambda x: parse_expr(x.replace("^", "**"))):
+        for f in ((latex,) if latex is not None else ()) + (lambda x: parse_expr(x.replace("^", "**")),):
             try:
                 return f(s)
             except Exception:

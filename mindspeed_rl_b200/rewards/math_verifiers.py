@@ -89,6 +89,10 @@ def base_model_accuracy_reward(sequences: Sequence[str], answers: Sequence[str],
     return out
 
 
+def warm_up() -> None:
+    G.warm_up()
+
+
 def _boxed_correct(s: str, a: str) -> bool:
     boxed = G.extract_boxed_content(s)
     return boxed is not None and G.grade_answer(boxed, a)
