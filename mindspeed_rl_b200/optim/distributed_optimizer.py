@@ -185,7 +185,7 @@ class DistributedOptimizer:
             s, e = self._range(buf)
             grad = buf.grad_data[s:e]
             p16 = buf.param_data[s:e] if buf.param_dtype != torch.float32 else None
-            if self.offload_to_host and grad.is_cuda:
+            if self.offload_to_host:
                 self._step_host(st, grad, p16 if p16 is not None else buf.param_data[s:e], g,
                                 p16 is None)
             elif self.reuse_fp32_param:
@@ -248,53 +248,64 @@ class DistributedOptimizer:
             self.split_master(master, p16[s:e], st["master_lo"][s:e])
 
     def _step_host(self, st, grad, p_out, g, fp32_params: bool) -> None:
-        """Chunked H2D -> AdamW -> D2H with double buffering."""
+        """Chunked H2D -> AdamW -> D2H with double buffering.  On a CPU tensor the same chunk loop runs without
+        streams (the copies are then plain copies), which is how the chunk arithmetic is tested."""
         n = grad.numel()
         chunk = (n + self.swap_chunks - 1) // self.swap_chunks
         chunk = (chunk + 63) // 64 * 64
         dev = grad.device
+        cuda = grad.is_cuda
         if self._streams is None:
-            self._streams = (torch.cuda.Stream(), torch.cuda.Stream())
+            self._streams = (torch.cuda.Stream(), torch.cuda.Stream()) if cuda else (None, None)
             self._stage = [
                 {k: torch.empty(chunk, dtype=torch.float32, device=dev) for k in ("master", "exp_avg", "exp_avg_sq")}
                 for _ in range(2)]
-            self._stage_events = [torch.cuda.Event(), torch.cuda.Event()]
         if self._stage[0]["master"].numel() < chunk:
             self._stage = [
                 {k: torch.empty(chunk, dtype=torch.float32, device=dev) for k in ("master", "exp_avg", "exp_avg_sq")}
                 for _ in range(2)]
         h2d, d2h = self._streams
-        main = torch.cuda.current_stream()
-        h2d.wait_stream(main)
-        d2h.wait_stream(main)
+        main = torch.cuda.current_stream() if cuda else None
+        if cuda:
+            h2d.wait_stream(main)
+            d2h.wait_stream(main)
         done_events = [None, None]
         for i, s in enumerate(range(0, n, chunk)):
             e = min(n, s + chunk)
             k = i & 1
             stage = self._stage[k]
-            if done_events[k] is not None:
-                h2d.wait_event(done_events[k])     # staging buffer free again
-            with torch.cuda.stream(h2d):
+            if cuda:
+                if done_events[k] is not None:
+                    h2d.wait_event(done_events[k])     # staging buffer free again
+                with torch.cuda.stream(h2d):
+                    for key in ("master", "exp_avg", "exp_avg_sq"):
+                        stage[key][:e - s].copy_(st[key][s:e], non_blocking=True)
+                    ready = torch.cuda.Event()
+                    ready.record(h2d)
+                main.wait_event(ready)
+            else:
                 for key in ("master", "exp_avg", "exp_avg_sq"):
-                    stage[key][:e - s].copy_(st[key][s:e], non_blocking=True)
-                ready = torch.cuda.Event()
-                ready.record(h2d)
-            main.wait_event(ready)
+                    stage[key][:e - s].copy_(st[key][s:e])
             ops.adamw_step(stage["master"][:e - s], stage["exp_avg"][:e - s], stage["exp_avg_sq"][:e - s],
                            grad[s:e], None if fp32_params else p_out[s:e], g["lr"], g["betas"][0],
                            g["betas"][1], g["eps"], g["weight_decay"], self.step_count, self._coef)
             if fp32_params:
                 p_out[s:e].copy_(stage["master"][:e - s])
-            computed = torch.cuda.Event()
-            computed.record(main)
-            d2h.wait_event(computed)
-            with torch.cuda.stream(d2h):
+            if cuda:
+                computed = torch.cuda.Event()
+                computed.record(main)
+                d2h.wait_event(computed)
+                with torch.cuda.stream(d2h):
+                    for key in ("master", "exp_avg", "exp_avg_sq"):
+                        st[key][s:e].copy_(stage[key][:e - s], non_blocking=True)
+                    done = torch.cuda.Event()
+                    done.record(d2h)
+                done_events[k] = done
+            else:
                 for key in ("master", "exp_avg", "exp_avg_sq"):
-                    st[key][s:e].copy_(stage[key][:e - s], non_blocking=True)
-                done = torch.cuda.Event()
-                done.record(d2h)
-            done_events[k] = done
-        main.wait_stream(d2h)
+                    st[key][s:e].copy_(stage[key][:e - s])
+        if cuda:
+            main.wait_stream(d2h)
 
     # ---- master <-> working copy ------------------------------------------------------------------
     def reload_model_params(self) -> None:
@@ -308,6 +319,8 @@ class DistributedOptimizer:
 
     # ---- checkpoint ---------------------------------------------------------------------------------
     def state_dict(self) -> dict:
+        if self.offload_to_host and torch.cuda.is_available():
+            torch.cuda.synchronize()        # the last step's device-to-host copies must have landed
         shards = []
         for buf, st in zip(self.buffers, self.state):
             d = {k: v.detach().cpu() for k, v in st.items() if k != "master_lo"}

@@ -174,3 +174,57 @@ def test_samplers_cover_their_slices_and_resume():
     assert list(PretrainingSampler(8, 0, 2, 0, 3, drop_last=False)) == [[0, 1], [6, 7]]
     with pytest.raises(ValueError):
         PretrainingSampler(8, 0, 2, 3, 3)
+
+
+def test_host_resident_optimizer_state_steps_in_chunks():
+    """Optimizer state kept on the host and streamed through staging buffers chunk by chunk (the last chunk
+    partial, two buffers of different size sharing the staging space) follows torch's AdamW; master weights can
+    be refreshed from externally changed parameters; the state survives a checkpoint round trip."""
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(37, 53), torch.nn.Linear(53, 11))
+    ref = torch.nn.Sequential(torch.nn.Linear(37, 53), torch.nn.Linear(53, 11))
+    ref.load_state_dict(net.state_dict())
+    ddp = DistributedDataParallel(net, None, 1)
+    opt = DistributedOptimizer(ddp.buffers, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, clip_grad=0.0,
+                               offload_to_host=True, swap_chunks=5)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01)
+
+    def one_step(seed):
+        x = torch.randn(6, 37, generator=torch.Generator().manual_seed(seed))
+        ddp.zero_grad_buffer()
+        net(x).pow(2).mean().backward()
+        for p in net.parameters():
+            p.main_grad.copy_(p.grad)
+            p.grad = None
+        ddp.finish_grad_sync(to_shards=True)
+        opt.step()
+        ropt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        ropt.step()
+
+    for step in range(3):
+        one_step(step)
+    for a, b in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(a, b, atol=1e-6), (a - b).abs().max()
+    n = sum(p.numel() for p in net.parameters())
+    assert opt._stage[0]["master"].numel() < n                      # really chunked
+    # parameters changed from outside (a checkpoint load): the master copy follows on request
+    with torch.no_grad():
+        for p, q in zip(net.parameters(), ref.parameters()):
+            p.mul_(0.5)
+            q.mul_(0.5)
+    opt.reload_model_params()
+    one_step(10)
+    for a, b in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(a, b, atol=1e-6)
+    # state round trip into a fresh optimizer
+    sd = opt.state_dict()
+    opt2 = DistributedOptimizer(ddp.buffers, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, clip_grad=0.0,
+                                offload_to_host=True, swap_chunks=3)
+    opt2.load_state_dict(sd)
+    assert opt2.step_count == opt.step_count
+    for a, b in zip(opt.state, opt2.state):
+        for k in a:
+            assert torch.equal(a[k], b[k]), k
