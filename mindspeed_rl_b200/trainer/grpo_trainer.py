@@ -33,10 +33,13 @@ class RayGRPOTrainer(RayBaseTrainer):
     # ------------------------------------------------------------------------------------------
     def transfer_dock_init(self) -> None:
         dock = None
+        cols = list(self.dataset_additional_keys)
+        if getattr(getattr(self.actor_worker, "rl_config", None), "multi_turn_enable", False):
+            cols += ["response_mask", "tool_call_num"]          # written by the multi-turn rollout loop
         if self.is_driver:
             dock = self._new_dock(self.td_max_len, self.n_samples_per_prompt, self.metrics,
                                   max_age=self.partial_rollout_max_split, GBS_train=self.global_batch_size,
-                                  addition_columns=self.dataset_additional_keys)
+                                  addition_columns=cols)
         self.transfer_dock = self._share_dock(dock)
         self.mm_transfer_dock = None
         rl = getattr(self.actor_worker, "rl_config", None)
@@ -118,7 +121,8 @@ class RayGRPOTrainer(RayBaseTrainer):
             if self.is_driver:
                 data_metrics = compute_grpo_data_metrics(td, self.global_batch_size * self.n_samples_per_prompt,
                                                          self.pad_token_id, self.global_batch_size,
-                                                         self.guarantee_order)
+                                                         self.guarantee_order,
+                                                         multi_turn_enable=rl.multi_turn_enable)
                 m = metrics_post_processing(td.get_metrics())
                 m.update(data_metrics)
                 time_all = time.time() - t0

@@ -29,10 +29,13 @@ class RayPPOTrainer(RayBaseTrainer):
 
     def transfer_dock_init(self) -> None:
         dock = None
+        cols = self.dataset_additional_keys + ["values"]
+        if getattr(getattr(self.actor_worker, "rl_config", None), "multi_turn_enable", False):
+            cols += ["response_mask", "tool_call_num"]          # written by the multi-turn rollout loop
         if self.is_driver:
             dock = self._new_dock(
                 self.global_batch_size, self.n_samples_per_prompt, self.metrics,
-                addition_columns=self.dataset_additional_keys + ["values"],
+                addition_columns=cols,
                 addition_consumers=["compute_kl", "critic_train", "critic_compute_values", "ppo_metrics"])
         self.transfer_dock = self._share_dock(dock)
         for w in {id(x): x for x in (self.actor_worker, self.ref_worker, self.critic_worker) if x is not None}.values():
@@ -72,7 +75,7 @@ class RayPPOTrainer(RayBaseTrainer):
                 t_a = time.time()
                 compute_advantage(td, self.gamma, self.lam, self.adv_estimator, rl.adv_dispatch_size,
                                   self.pad_token_id, gbs, self.guarantee_order, n,
-                                  use_kl_in_reward=self.use_kl_in_reward)
+                                  use_kl_in_reward=self.use_kl_in_reward, multi_turn_enable=rl.multi_turn_enable)
                 t_e = time.time()
                 td.update_metrics("timing/adv", value=[round(t_e, 4), round(t_a, 4)], cumulate=True)
                 td.update_metrics("end_time/end_adv_time", value=[round(t_e, 4)], cumulate=True)

@@ -136,3 +136,50 @@ def test_grpo_partial_rollout_cpu():
     assert len(hist) == 2 and all(m["response_length/max"] <= 24 for m in hist)
     assert any(max(lens) == 0 for lens, _ in rounds), "no fresh prompts were generated"
     assert any(min(lens) == 12 for lens, _ in rounds), "no half-finished response was continued"
+
+
+def test_grpo_multi_turn_tool_loop_cpu():
+    """GRPO with the multi-turn tool loop inside the worker: every sample's first turn is followed by a tool
+    turn (a scripted call to a registered tool), tool tokens are masked out of the loss (``response_mask``) and
+    the number of tool calls is reported."""
+    from test_e2e_grpo_cpu import build
+    from test_tools_cpu import CharTokenizer, EchoTool  # noqa: F401  (registers the tool class)
+    from mindspeed_rl_b200.tools.base import FunctionSchema, HermesToolParser, build_tool_map
+    from mindspeed_rl_b200.trainer.grpo_trainer import RayGRPOTrainer
+
+    torch.manual_seed(0)
+    actor, rl, gen = build(n_prompts=2, n_samples=2, max_tokens=12, iters=1)
+    rl.multi_turn_enable, rl.max_tool_calls, rl.max_parallel_calls = True, 1, 1
+    rl.max_total_response_length, rl.max_tool_response_length, rl.tool_parser_format = 120, 16, "hermes"
+    gen.max_model_len = 256
+    gen.enable_prefix_caching = True
+    worker = IntegratedWorker(actor, rl, gen, eos_token_id=-1, pad_token_id=0, device="cpu")
+    group = SPMDWorkerGroup(worker, num_gpus=1).initialize()
+    tok = CharTokenizer()
+    worker.attach_tools(tok, build_tool_map([{"class_name": "EchoTool", "tool_schema": FunctionSchema("echo").to_openai()}]))
+
+    class Scripted(HermesToolParser):
+        def extract_tool_calls(self, ids):
+            return self.extract_from_text('<tool_call>{"name": "echo", "arguments": {"k": 1}}</tool_call>')
+
+    worker.multi_turn.parser = Scripted(tok)
+    seen = {}
+    inner = worker.actor.update
+
+    def spy(batch, kl_ctrl=None):
+        seen["mask"] = batch["response_mask"].clone()
+        seen["len"] = batch["response_length"].reshape(-1).clone()
+        return inner(batch, kl_ctrl)
+
+    worker.actor.update = spy
+    trainer = RayGRPOTrainer(group, reward_list=[RuleReward(rl, None, actor)], train_iters=1, save_interval=0,
+                             adv_estimator="group_norm", kl_penalty="low_var_kl", init_kl_coef=0.001,
+                             global_batch_size=2, n_samples_per_prompt=2, pad_token_id=0)
+    hist = trainer.fit(iter(SyntheticPromptLoader(2, 16, 1024, seed=0)))
+    assert len(hist) == 1 and hist[0]["tool_call_num/mean"] == 1.0
+    assert hist[0]["tool_call_num/max"] == 1 and hist[0]["response_length/max"] <= 120
+    assert hist[0]["response_length/min"] > 12                                                # a tool turn was added
+    mask, lens = seen["mask"], seen["len"]
+    for row, n in zip(mask, lens.tolist()):
+        live = row[:n]
+        assert int(live.sum()) < n and int(live[:12].sum()) == 12 and int(live[12]) == 0   # first turn counts, tool turn does not
