@@ -146,3 +146,30 @@ def test_eplb_map_cli_from_dumped_counts(tmp_path):
         flat = [e for h in hosted for e in h]
         assert set(flat) == set(range(experts)) and flat.count(5) >= 2
         assert all(len(set(h)) == len(h) for h in hosted)
+
+
+def test_grpo_saves_and_resumes(tmp_path):
+    """Two iterations with a checkpoint after each; a second run that loads the checkpoint starts at iteration 2,
+    has the same weights, skips the prompts already used and trains one more iteration."""
+    import torch
+    from mindspeed_rl_b200.checkpoint.mcore import load_args_from_checkpoint
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.config.loader import apply_overrides
+    from mindspeed_rl_b200.runtime.launch import run_rl
+
+    save = str(tmp_path / "ckpt")
+    base = ["megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+            "generate_config.sampling_config.max_tokens=8", "megatron_training.seq_length=96",
+            f"actor_config.save={save}", "megatron_training.save_interval=1", "actor_config.lr=1e-3"]
+    hist = run_rl(apply_overrides(compose("grpo_tiny_cpu"), base + ["megatron_training.train_iters=2"]), "grpo")
+    assert len(hist) == 2
+    assert (tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text().strip() == "2"
+    assert (tmp_path / "ckpt" / "iter_0000001").is_dir() and (tmp_path / "ckpt" / "iter_0000002").is_dir()
+    args = load_args_from_checkpoint(save)
+    assert args is not None and int(getattr(args, "num_layers", args.get("num_layers") if isinstance(args, dict) else 0)) == 2
+    state = torch.load(tmp_path / "ckpt" / "iter_0000002" / "mp_rank_00" / "model_optim_rng.pt", weights_only=False)
+    assert state["iteration"] == 2 and "optimizer" in state and "opt_param_scheduler" in state
+    resumed = run_rl(apply_overrides(compose("grpo_tiny_cpu"),
+                                     base + ["megatron_training.train_iters=3", f"actor_config.load={save}"]), "grpo")
+    assert len(resumed) == 1                                   # iterations 1 and 2 are not repeated
+    assert (tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text().strip() == "3"

@@ -1,5 +1,6 @@
 """Packing helpers, context-parallel slicing, vocabulary-parallel log-probabilities and the samplers,
 each against a direct PyTorch formulation."""
+import os
 from types import SimpleNamespace
 
 import pytest
@@ -228,3 +229,70 @@ def test_host_resident_optimizer_state_steps_in_chunks():
     for a, b in zip(opt.state, opt2.state):
         for k in a:
             assert torch.equal(a[k], b[k]), k
+
+
+def test_store_hands_out_token_balanced_batches():
+    """With sequence-length balancing a consumer's draws are equal-sized parts of similar token count (rows, or
+    whole groups of samples), and every row is handed out exactly once."""
+    from mindspeed_rl_b200.data.transfer_dock import GRPOTransferDock, put_prompts_experience
+    lens = [10, 200, 30, 180, 50, 160, 70, 140]
+    td = GRPOTransferDock(8, 1)
+    data, idx = put_prompts_experience({"prompts": [torch.arange(n) for n in lens]}, 1)
+    td.put_experience(data, idx)
+    td.put_experience({"responses": [torch.ones(3, dtype=torch.int64)] * 8,
+                       "response_length": [torch.tensor([3], dtype=torch.int32)] * 8}, idx)
+    sums, seen = [], []
+    for _ in range(2):
+        _, got = td.get_experience("actor_train", ["prompts", "prompt_length", "responses", "response_length"], 4,
+                                   get_n_samples=False, use_batch_seqlen_balance=True)
+        sums.append(sum(lens[i] for i in got))
+        seen += got
+    assert sorted(seen) == list(range(8)) and abs(sums[0] - sums[1]) <= 40, sums       # total 840: about 420 each
+    assert td.all_consumed("actor_train")
+    # groups of two samples stay together
+    td = GRPOTransferDock(4, 2)
+    data, idx = put_prompts_experience({"prompts": [torch.arange(n) for n in (10, 200, 190, 20)]}, 2)
+    td.put_experience(data, idx)
+    td.put_experience({"responses": [torch.ones(2, dtype=torch.int64)] * 8,
+                       "response_length": [torch.tensor([2], dtype=torch.int32)] * 8}, idx)
+    _, got = td.get_experience("actor_train", ["prompts", "prompt_length", "responses", "response_length"], 4,
+                               get_n_samples=True, use_batch_seqlen_balance=True)
+    groups = sorted({i // 2 for i in got})
+    assert len(got) == 4 and got == [g * 2 + j for g in groups for j in range(2)]
+    assert sorted(groups) in ([0, 1], [2, 3], [0, 2], [1, 3])        # one short and one long prompt group
+
+
+def test_small_helpers_partition_filter_builder_and_tool_file(tmp_path):
+    import numpy as np
+    from mindspeed_rl_b200.datasets.indexed_dataset import (IndexedDataset, IndexedDatasetBuilder, get_bin_path,
+                                                            get_idx_path)
+    from mindspeed_rl_b200.tools.base import load_tool_map
+    from mindspeed_rl_b200.utils.seqlen_balancing import heapq_partition
+
+    parts = heapq_partition([9, 1, 8, 2, 7, 3], 2, equal_size=True)
+    assert sorted(map(len, parts)) == [3, 3] and sorted(i for p in parts for i in p) == list(range(6))
+    sums = [sum([9, 1, 8, 2, 7, 3][i] for i in p) for p in parts]
+    assert abs(sums[0] - sums[1]) <= 2
+    assert sorted(map(len, heapq_partition([5, 5, 5], 2, equal_size=False))) == [1, 2]
+    with pytest.raises(ValueError):
+        heapq_partition([1, 2, 3], 2, equal_size=True)
+
+    prefix = str(tmp_path / "docs")
+    b = IndexedDatasetBuilder(get_bin_path(prefix), dtype=np.int32)
+    b.add_document(torch.arange(7), [3, 4])                 # one document of two sequences
+    b.add_item(np.arange(10))
+    b.end_document()
+    b.finalize(get_idx_path(prefix))
+    ds = IndexedDataset(prefix)
+    assert len(ds) == 3 and ds[0].tolist() == [0, 1, 2] and ds[1].tolist() == [3, 4, 5, 6]
+    assert ds.document_indices.tolist() == [0, 2, 3] and ds.get_filter_mask().all()
+    short = IndexedDataset(prefix, max_len=4) if "max_len" in IndexedDataset.__init__.__code__.co_varnames else None
+    if short is not None:
+        mask = short.get_filter_mask()
+        assert mask.tolist() == [True, True, False]
+        short.do_filter(mask)
+        assert len(short) == 2 and short.sequence_lengths.tolist() == [3, 4]
+
+    tools = load_tool_map(os.path.join(os.path.dirname(__file__), "..", "configs", "tools", "retool.yaml"))
+    assert list(tools) == ["code_interpreter"] and type(tools["code_interpreter"]).__name__ == "ReTool"
+    assert tools["code_interpreter"].schema.to_openai()["function"]["parameters"]["required"] == ["code"]
