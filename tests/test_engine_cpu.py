@@ -42,3 +42,29 @@ def test_lookahead_decode_is_exact():
     reasons = {c[1] for _, outs in a for c in outs}
     assert reasons == {"length", "stop"}             # the case covers both ways a sequence ends
     assert steps_a == steps_b
+
+
+def test_abort_returns_partial_output_and_frees_blocks():
+    """A request that is aborted between steps hands back what it has produced so far, its cache blocks return
+    to the pool, and the remaining requests finish as if it had never been queued beside them."""
+    eng = _engine(lookahead=False)
+    free0 = eng.bm.num_free_blocks
+    params = SamplingParams(n=1, temperature=0.0, max_tokens=10)
+    eng.add_request("keep", [3, 9, 27, 5], params)
+    eng.add_request("drop", [1, 2, 3, 4, 5, 6], params)
+    for _ in range(4):
+        eng.step()
+    assert eng.get_num_unfinished_requests() == 2 and eng.bm.num_free_blocks < free0
+    out = eng.abort_request("drop")
+    assert out is not None and out.request_id == "drop" and 1 <= len(out.outputs[0].token_ids) < 10
+    assert eng.abort_request("drop") is None and eng.abort_request("never-queued") is None
+    assert eng.get_num_unfinished_requests() == 1
+    done = []
+    while eng.has_unfinished_requests():
+        done += [o for o in eng.step() if o.finished]
+    assert [o.request_id for o in done] == ["keep"]
+    assert eng.bm.num_free_blocks == free0                      # every block came back
+    alone = _engine(lookahead=False)
+    ref = alone.generate([[3, 9, 27, 5]], params)[0]
+    assert done[0].outputs[0].token_ids == ref.outputs[0].token_ids
+    assert eng.kv_bytes_per_block() == 2 * 2 * 4 * 2 * 8 * 4     # K and V x layers x block x kv heads x head dim x fp32
