@@ -127,6 +127,9 @@ def expert_map_from_counts(counts: torch.Tensor, num_gpus: int, num_redundancy_p
     num_phy = num_log + num_redundancy_per_gpu * num_gpus
     phy2log, _, _ = rebalance_experts(counts, num_phy, num_groups, num_nodes, num_gpus)
     per_gpu = num_phy // num_gpus
+    if per_gpu > num_log:
+        raise ValueError(f"{per_gpu} expert slots per device but only {num_log} experts: a device would have to "
+                         f"host the same expert twice; lower num_redundancy_per_gpu or use more devices")
     layer_list = []
     for l in range(layers):
         devices = []

@@ -7,6 +7,7 @@ import random
 import sys
 
 import numpy as np
+import pytest
 import yaml
 
 ROOT = os.path.join(os.path.dirname(__file__), "..")
@@ -173,3 +174,39 @@ def test_grpo_saves_and_resumes(tmp_path):
                                      base + ["megatron_training.train_iters=3", f"actor_config.load={save}"]), "grpo")
     assert len(resumed) == 1                                   # iterations 1 and 2 are not repeated
     assert (tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
+
+
+def test_expert_load_collection_to_placement_map_to_rollout(tmp_path):
+    """The load-balancing workflow end to end on one rank: a run of a small expert model records how many tokens
+    every expert received during rollout, the map generator turns the records into a placement with a redundant
+    slot, and a second run rolls out with that placement."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+
+    moe = ["+model.tiny_qwen2.num_experts=4", "+model.tiny_qwen2.moe_router_topk=2",
+           "+model.tiny_qwen2.moe_ffn_hidden_size=32", "+model.tiny_qwen2.norm_topk_prob=true",
+           "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+           "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=1"]
+    stats = tmp_path / "load"
+    hist = run_rl(compose("grpo_tiny_cpu", None, moe + ["generate_config.eplb_token_collects=true",
+                                                        f"generate_config.eplb_token_save_path={stats}"]), "grpo")
+    assert len(hist) == 1
+    record = json.loads((stats / "eplb_token_collects_0.json").read_text())
+    assert sorted(record, key=int) == ["0", "1"]                     # both layers are expert layers
+    for layer in record.values():
+        assert sorted(layer, key=int) == ["0", "1", "2", "3"] and sum(layer.values()) > 0
+    # prompts 4 x 2 samples, prefill + 8 decode steps, top-2 routing: every token is counted twice per layer
+    assert sum(record["0"].values()) == sum(record["1"].values()) and sum(record["0"].values()) % 2 == 0
+    out = tmp_path / "expert_map.json"
+    _cli("eplb_generate_map").main(["--json_folder", str(stats), "--num_gpus", "2", "--num_redundancy", "1",
+                                    "--output", str(out)])
+    emap = json.loads(out.read_text())
+    for li, layer in enumerate(emap["layer_list"]):
+        hosted = [d["device_expert"] for d in layer["device_list"]]
+        assert [len(h) for h in hosted] == [3, 3] and set(hosted[0]) | set(hosted[1]) == {0, 1, 2, 3}
+        hottest = max(record[str(li)], key=lambda e: record[str(li)][e])
+        assert sum(h.count(int(hottest)) for h in hosted) == 2          # the busiest expert got the spare slots
+    # one device cannot host five slots of four experts without a duplicate: refused with a clear message
+    with pytest.raises(ValueError, match="same expert twice"):
+        _cli("eplb_generate_map").main(["--json_folder", str(stats), "--num_gpus", "1", "--num_redundancy", "1",
+                                        "--output", str(out)])
