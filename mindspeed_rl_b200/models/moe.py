@@ -262,7 +262,9 @@ class MoELayer(nn.Module):
                 if (keep and cfg.moe_aux_loss_coeff) else None
         self.last_aux_loss = aux.detach() if aux is not None else None
         self.token_counts = torch.bincount(top_idx.reshape(-1), minlength=cfg.num_experts)
-        if cfg.moe_router_enable_expert_bias and torch.is_grad_enabled():
+        if cfg.moe_router_enable_expert_bias and keep:
+            # ``keep`` marks the one pass per training step whose intermediates feed the backward (the recompute
+            # pass under full recompute); forward-only passes (reference / old log-probs) do not count as load
             self._load_since_update += self.token_counts.float()
         if self.ep_size == 1:
             return self._forward_local(x, xr, top_p, top_idx, aux, comm, keep)

@@ -296,3 +296,62 @@ def test_small_helpers_partition_filter_builder_and_tool_file(tmp_path):
     tools = load_tool_map(os.path.join(os.path.dirname(__file__), "..", "configs", "tools", "retool.yaml"))
     assert list(tools) == ["code_interpreter"] and type(tools["code_interpreter"]).__name__ == "ReTool"
     assert tools["code_interpreter"].schema.to_openai()["function"]["parameters"]["required"] == ["code"]
+
+
+def test_expert_bias_follows_the_load():
+    """Auxiliary-loss-free balancing: experts that received fewer tokens than the mean since the last update get a
+    higher routing bias, the others a lower one, and the counters restart."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    cfg = TransformerConfig(num_layers=1, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+                            vocab_size=64, params_dtype=torch.float32, num_experts=4, moe_router_topk=2,
+                            moe_ffn_hidden_size=16, moe_router_enable_expert_bias=True, max_position_embeddings=64)
+    model = GPTModel(cfg, device="cpu", seed=1)
+    moe = model.decoder.layers[0].mlp
+    ids = torch.randint(0, 64, (24,), generator=torch.Generator().manual_seed(0))
+    lp, _ = model.forward_logprob(ids, ids, PackedMeta.from_lengths([24], "cpu"))
+    lp.sum().backward()
+    load = moe._load_since_update.clone()
+    assert float(load.sum()) == 24 * 2 and moe.router.expert_bias.abs().sum() == 0
+    moe.update_expert_bias(rate=0.01)
+    want = 0.01 * torch.sign(load.mean() - load)
+    assert torch.allclose(moe.router.expert_bias, want) and float(moe._load_since_update.sum()) == 0
+    with torch.no_grad():                                     # forward-only passes do not count as training load
+        model.forward_logprob(ids, ids, PackedMeta.from_lengths([24], "cpu"))
+    assert float(moe._load_since_update.sum()) == 0
+
+
+def test_metric_sinks_with_stand_in_packages(monkeypatch, tmp_path):
+    """The Weights & Biases and SwanLab sinks forward numeric metrics with the step; a missing package only
+    disables the sink."""
+    import sys
+    import types
+    from mindspeed_rl_b200.obs import loggers
+
+    calls = {}
+
+    def fake(name):
+        mod = types.ModuleType(name)
+        mod.init = lambda **kw: calls.setdefault(name + ".init", kw) or object()
+        mod.log = lambda data, step=None: calls.setdefault(name + ".log", []).append((data, step))
+        return mod
+
+    monkeypatch.setitem(sys.modules, "wandb", fake("wandb"))
+    monkeypatch.setitem(sys.modules, "swanlab", fake("swanlab"))
+    w = loggers.WandbLogger({"wandb_project": "p", "wandb_exp_name": "e", "wandb_save_dir": str(tmp_path / "w")})
+    s = loggers.SwanLabLogger({"swanlab_project": "p", "swanlab_exp_name": "e", "swanlab_save_dir": str(tmp_path / "s")})
+    for sink in (w, s):
+        sink.log_metrics({"a": 1.5, "b": 2, "text": "skip me"}, 7)
+    assert calls["wandb.init"]["project"] == "p" and calls["wandb.init"]["name"].startswith("e-")
+    assert calls["wandb.log"] == [({"a": 1.5, "b": 2}, 7)] and calls["swanlab.log"] == [({"a": 1.5, "b": 2}, 7)]
+    assert calls["swanlab.init"]["experiment_name"] == "e" and calls["swanlab.init"]["mode"] == "local"
+    monkeypatch.setitem(sys.modules, "wandb", None)            # import fails: the sink switches itself off
+    off = loggers.WandbLogger({})
+    off.log_metrics({"a": 1.0}, 1)
+    assert off.run is None
+
+
+def test_static_row_ranges_for_ordered_consumption():
+    from mindspeed_rl_b200.trainer.compute_utils import get_current_dp_range_indexes
+    assert get_current_dp_range_indexes(2, 6) == [[0, 1], [2, 3], [4, 5]]
+    assert get_current_dp_range_indexes(3, 6, current_dp_rank=1) == [[6, 7, 8], [9, 10, 11]]
