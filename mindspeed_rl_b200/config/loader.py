@@ -152,8 +152,10 @@ def parse_training_config(config: Dict[str, Any], with_critic: bool = False) -> 
     else:
         ref_for_validation = ref_config
     generate_config = GenerateConfig(config.get("generate_config"))
+    # vision-language runs: architecture (and optionally a rank range) of the vision tower
+    vit_config = _role(config, "vit_config") if "vit_config" in config else None
     validate_rl_args(actor_config, ref_for_validation, reward_config, rl_config, generate_config,
-                     critic_config=critic_config)
+                     critic_config=critic_config, vit_config=vit_config)
     prof = config.get("profiler_config") or {}
     profiler_config = {"integrated": ProfilerConfig(prof.get("integrated", {}), role="integrated")}
     msprobe_config = MsprobeConfig(config.get("msprobe_config") or {}, role="integrated")
@@ -162,4 +164,6 @@ def parse_training_config(config: Dict[str, Any], with_critic: bool = False) -> 
                profiler_config=profiler_config, msprobe_config=msprobe_config)
     if critic_config is not None:
         out["critic_config"] = critic_config
+    if vit_config is not None:
+        out["vit_config"] = vit_config
     return out

@@ -209,3 +209,29 @@ def test_expert_load_collection_to_placement_map_to_rollout(tmp_path):
     with pytest.raises(ValueError, match="same expert twice"):
         _cli("eplb_generate_map").main(["--json_folder", str(stats), "--num_gpus", "1", "--num_redundancy", "1",
                                         "--output", str(out)])
+
+
+def test_vision_language_run_through_the_launcher(tmp_path):
+    """JSON-lines rows with inline images -> multimodal dataset -> vision stage (architecture from the recipe's
+    ``vit_config`` section) -> rollout, reference and update of one GRPO iteration."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+
+    rng = np.random.default_rng(0)
+    with open(tmp_path / "rows.jsonl", "w") as f:
+        for i in range(8):
+            img = (rng.random((28, 42, 3)) * 255).astype(np.uint8).tolist()
+            f.write(json.dumps({"prompt": f"5 6 <image> 7 {8 + i}", "images": [img], "answer": str(i)}) + "\n")
+    cfg = compose("grpo_tiny_cpu", None, [
+        "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+        "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=1",
+        f"megatron_training.data_path={tmp_path / 'rows.jsonl'}", "+rl_config.is_multimodal=true",
+        "+rl_config.reuse_image_embeds=true", "generate_config.enable_prefix_caching=false",
+        "rl_config.use_remove_padding=false", "+megatron_training.image_token_id=1000",
+        "+megatron_training.vision_start_token_id=1001", "+megatron_training.vision_end_token_id=1002",
+        "+vit_config.hidden_size=32", "+vit_config.num_layers=1", "+vit_config.num_attention_heads=2",
+        "+vit_config.ffn_hidden_size=48", "+rl_config.max_prompt_length=96"])
+    hist = run_rl(cfg, "grpo")
+    assert len(hist) == 1 and hist[0]["timing/vit_image_emb"] > 0 and hist[0]["timing/rollout"] > 0
+    # 4 text tokens + start marker + 3 image placeholders (2 x 3 patches merged 2 x 2 -> ... ) + end marker
+    assert hist[0]["prompt_length/mean"] == hist[0]["prompt_length/max"] > 6
