@@ -235,3 +235,21 @@ def test_vision_language_run_through_the_launcher(tmp_path):
     assert len(hist) == 1 and hist[0]["timing/vit_image_emb"] > 0 and hist[0]["timing/rollout"] > 0
     # 4 text tokens + start marker + 3 image placeholders (2 x 3 patches merged 2 x 2 -> ... ) + end marker
     assert hist[0]["prompt_length/mean"] == hist[0]["prompt_length/max"] > 6
+
+
+def test_ppo_and_dapo_through_the_launcher():
+    """One iteration each of PPO (critic group built from the recipe's critic section) and DAPO (no reference
+    model) through the launcher that the command-line entry points call."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    small = ["megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+             "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=1"]
+    h = run_rl(compose("grpo_tiny_cpu", None, small + [
+        "megatron_training.stage=ray_ppo", "rl_config.adv_estimator=gae", "+critic_config.model=tiny_qwen2",
+        "+critic_config.micro_batch_size=4", "+critic_config.lr=1e-5", "+rl_config.critic_resource.num_gpus=1"]), "ppo")
+    assert len(h) == 1 and "critic/vf_loss" in h[0] and "critic/values/mean" in h[0] and h[0]["timing/update_critic"] > 0
+    h = run_rl(compose("grpo_tiny_cpu", None, small + [
+        "megatron_training.stage=ray_dapo", "+rl_config.clip_higher_enable=true", "+rl_config.clip_ratio_low=0.2",
+        "+rl_config.clip_ratio_high=0.28", "+rl_config.token_level_loss=true", "rl_config.init_kl_coef=0.0"]), "dapo")
+    assert len(h) == 1 and "dapo/score/mean" in h[0] and h[0]["actor/kl_loss"] == 0.0
+    assert "timing/reference_model" not in h[0] or h[0]["timing/reference_model"] == 0
