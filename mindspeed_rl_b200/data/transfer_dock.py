@@ -226,6 +226,8 @@ class GRPOTransferDock(TransferDock):
                 return None, None
         else:
             indexes = list(indexes)
+            if indexes and (max(indexes) >= self.max_len or min(indexes) < 0):
+                raise ValueError(f"indexes out of range for max_len {self.max_len}")
             self.experience_consumer_status[consumer][torch.as_tensor(indexes, dtype=torch.int64)] = 1
         rows = self._get(columns, indexes)
         if consumer == "actor_rollout" and self.enable_partial_rollout:

@@ -355,3 +355,35 @@ def test_static_row_ranges_for_ordered_consumption():
     from mindspeed_rl_b200.trainer.compute_utils import get_current_dp_range_indexes
     assert get_current_dp_range_indexes(2, 6) == [[0, 1], [2, 3], [4, 5]]
     assert get_current_dp_range_indexes(3, 6, current_dp_rank=1) == [[6, 7, 8], [9, 10, 11]]
+
+
+def test_store_waits_for_late_cells_and_gives_up_on_missing_ones(capsys):
+    """A read of explicitly named rows waits for cells that a slow producer fills later, reports that it is
+    waiting once the first limit has passed, and raises after ten times the limit when a cell never arrives."""
+    import threading
+    import time
+    from mindspeed_rl_b200.data.transfer_dock import GRPOTransferDock, put_prompts_experience
+    td = GRPOTransferDock(2, 1, timeout=0.05, timeout_interval=0.05)
+    data, idx = put_prompts_experience({"prompts": [torch.arange(3), torch.arange(5)]}, 1)
+    td.put_experience(data, idx)
+
+    def late():
+        time.sleep(0.2)
+        td.put_experience({"responses": [torch.tensor([7]), torch.tensor([8, 9])]}, [0, 1])
+
+    t = threading.Thread(target=late)
+    t.start()
+    batch, got = td.get_experience("actor_train", ["responses"], 2, indexes=[0, 1], get_n_samples=False)
+    t.join()
+    assert got == [0, 1] and batch["responses"].tolist() == [[7, 0], [8, 9]]
+    assert "waiting" in capsys.readouterr().out                     # the wait was reported while it lasted
+    t0 = time.time()
+    with pytest.raises(TimeoutError):
+        td.get_experience("actor_train", ["old_log_prob"], 2, indexes=[0, 1], get_n_samples=False)
+    assert 0.4 < time.time() - t0 < 5.0
+    with pytest.raises(ValueError):
+        td.get_experience("actor_train", ["responses"], 2, indexes=[0, 5], get_n_samples=False)
+    with pytest.raises(ValueError):
+        td.put_experience({"responses": [torch.tensor([1])]}, [0, 1])          # one row for two indexes
+    with pytest.raises(ValueError):
+        td.put_experience({"responses": [torch.tensor([1])]}, [9])
