@@ -1,5 +1,6 @@
 """Packing helpers, context-parallel slicing, vocabulary-parallel log-probabilities and the samplers,
 each against a direct PyTorch formulation."""
+import math
 import os
 from types import SimpleNamespace
 
@@ -387,3 +388,51 @@ def test_store_waits_for_late_cells_and_gives_up_on_missing_ones(capsys):
         td.put_experience({"responses": [torch.tensor([1])]}, [0, 1])          # one row for two indexes
     with pytest.raises(ValueError):
         td.put_experience({"responses": [torch.tensor([1])]}, [9])
+
+
+def test_yarn_frequencies_match_the_transformers_formula():
+    """Rotary frequencies under YaRN scaling (DeepSeek-style long context) against the implementation in
+    the transformers package, and the scaled table's amplitude."""
+    from mindspeed_rl_b200.ops.elementwise import _yarn_inv_freq, rope_table
+    hd, theta = 64, 10000.0
+    sc = dict(factor=40.0, original_max_position_embeddings=4096, beta_fast=32, beta_slow=1, mscale=1.0,
+              mscale_all_dim=1.0)
+    inv = 1.0 / (theta ** (torch.arange(0, hd // 2, dtype=torch.float64) * 2.0 / hd))
+    new, mscale = _yarn_inv_freq(inv, hd, theta, sc)
+    assert mscale == 1.0                                              # equal mscale factors cancel
+    assert torch.allclose(new[:4], inv[:4]) and torch.allclose(new[-4:], inv[-4:] / 40.0)   # fast dims kept, slow ones stretched
+    assert bool((new[1:] <= new[:-1]).all())
+    _, only_m = _yarn_inv_freq(inv, hd, theta, dict(sc, mscale_all_dim=0.0))
+    assert only_m == pytest.approx(0.1 * math.log(40.0) + 1.0)
+    try:
+        from transformers import PretrainedConfig
+        from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+        cfg = PretrainedConfig()
+        cfg.rope_theta, cfg.hidden_size, cfg.num_attention_heads, cfg.head_dim = theta, hd * 4, 4, hd
+        cfg.max_position_embeddings = 4096 * 40
+        cfg.rope_scaling = dict(sc, rope_type="yarn")
+        cfg.rope_parameters = dict(cfg.rope_scaling, rope_theta=theta)
+        inv_hf, att = ROPE_INIT_FUNCTIONS["yarn"](cfg, "cpu")
+    except Exception as e:                                            # another transformers API: nothing to compare with
+        pytest.skip(f"transformers rope helpers not usable here: {e!r}")
+    assert float((inv_hf.double() - new).abs().max()) < 1e-7 and att == pytest.approx(mscale)
+    tab = rope_table(32, hd, theta, "cpu", dict(sc, mscale_all_dim=0.0))
+    assert tab.shape == (32, hd) and float(tab[0, 0]) == pytest.approx(only_m, rel=1e-6)   # cos(0) x amplitude
+
+
+def test_decode_groups_for_the_shared_prefix_path():
+    from mindspeed_rl_b200.ops.decode import build_decode_groups, decode_group_max
+    # rows 0-2 and 4 sample prompt "a" (prefix 37 keys), row 3 is alone, rows 5-6 sample prompt "b"
+    ids = ["a", "a", "a", "c", "a", "b", "b"]
+    plen = [37, 37, 37, 50, 37, 20, 21]
+    key_start, rows, prefix, shared = build_decode_groups(ids, plen, group_max=3, multiple=16)
+    assert shared and len(rows) == len(prefix) == 7 and all(len(r) == 8 for r in rows)
+    assert rows[0][:3] == [0, 1, 2] and rows[0][3:] == [-1] * 5 and prefix[0] == 32       # 37 rounded down to the tile
+    assert rows[1][:1] == [4] and prefix[1] == 0                                         # overflow of the group: alone
+    assert rows[2][:1] == [3] and prefix[2] == 0
+    assert rows[3][:2] == [5, 6] and prefix[3] == 16                                     # min(20, 21) rounded down
+    assert rows[4:] == [[-1] * 8] * 3 and prefix[4:] == [0, 0, 0]
+    assert key_start == [32, 32, 32, 0, 0, 16, 16]
+    _, _, p1, s1 = build_decode_groups(ids, [5] * 7, group_max=8, multiple=16)
+    assert not s1 and set(p1) == {0}                                                     # prefixes shorter than a tile
+    assert decode_group_max(28, 4) == 8 and decode_group_max(32, 2) == 4 and decode_group_max(64, 1, 64) == 2
