@@ -325,10 +325,17 @@ def fix_model_tokenizer(tokenizer, name: str, prompt_type_path: str, enable_thin
     """Apply a template's special-token requirements (stop words become EOS / extra specials)."""
     tpl = get_model_template(name, prompt_type_path, enable_thinking)
     stops = list(tpl.stop_words)
+    def set_eos(token: str) -> None:
+        # registering it as a special token also adds it to the vocabulary when the model file lacks it
+        try:
+            tokenizer.add_special_tokens({"eos_token": token})
+        except Exception:
+            tokenizer.eos_token = token
+
     if tpl.replace_eos and stops:
-        tokenizer.eos_token = stops.pop(0)
+        set_eos(stops.pop(0))
     if tokenizer.eos_token_id is None:
-        tokenizer.eos_token = "<|endoftext|>"
+        set_eos("<|endoftext|>")
     if tokenizer.pad_token_id is None:
         tokenizer.pad_token = tokenizer.eos_token
     if stops:

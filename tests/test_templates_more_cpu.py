@@ -40,6 +40,10 @@ class CharTok:
         return self._id(tok)
 
     def add_special_tokens(self, d, replace_additional_special_tokens=True):
+        for name in ("eos_token", "pad_token"):                  # as the Hugging Face classes do: set and register
+            if name in d:
+                setattr(self, name, d[name])
+                self._id(d[name])
         for t in d.get("additional_special_tokens", []):
             self._id(t)
 
@@ -179,3 +183,34 @@ def test_padding_helpers():
     x3 = x.unsqueeze(-1).float().expand(2, 6, 2)
     got = truncate_middle_and_pad(torch.zeros(2, 4), x3, win, pad_value=0.0)
     assert got.shape == (2, 4, 2) and got[0, :, 0].tolist() == [2.0, 3.0, 0.0, 0.0]
+
+
+def test_hugging_face_tokenizer_wrapper_with_a_local_vocabulary(tmp_path):
+    """A word-level tokenizer saved in the Hugging Face layout, loaded through the wrapper with a chat template:
+    the template's stop word becomes EOS, pad falls back to EOS, and the rule reward decodes with it."""
+    from types import SimpleNamespace as NS
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    from mindspeed_rl_b200.rewards.registry import compute_verifier_score
+    from mindspeed_rl_b200.utils.tokenizer import get_tokenizer
+
+    vocab = {"<unk>": 0, "<eos>": 1}
+    for w in "user assistant add and the answer is \\boxed{3} \\boxed{4} 1 2 3 4 <|im_start|>".split(" "):
+        vocab.setdefault(w, len(vocab))
+    raw = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    raw.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    PreTrainedTokenizerFast(tokenizer_object=raw, unk_token="<unk>", eos_token="<eos>").save_pretrained(str(tmp_path))
+    tok = get_tokenizer(str(tmp_path), "HuggingFaceTokenizer", "qwen", TEMPLATES)
+    assert tok.tokenizer.eos_token == "<|im_end|>" and tok.eod == tok.pad == len(vocab)     # added as a special token
+    assert tok.vocab_size == len(vocab) + 1 and tok.vocab["add"] == vocab["add"]
+    ids = tok.tokenize("add 1 and 2")
+    assert ids == [vocab[w] for w in ("add", "1", "and", "2")] and tok.detokenize(ids) == "add 1 and 2"
+    assert tok.template is not None and tok.template.stop_words == ["<|im_end|>"]
+    # rule reward over token rows: -100 in the labels is mapped to EOS and dropped with the special tokens
+    resp = [torch.tensor(tok.tokenize("the answer is \\boxed{3}") + [tok.eod]),
+            torch.tensor(tok.tokenize("the answer is \\boxed{4}"))]
+    labels = [torch.tensor(tok.tokenize("3") + [-100]), torch.tensor(tok.tokenize("3"))]
+    cfg = NS(verifier_function=["math_17k_acc"], verifier_weight=[2.0], verifier_parallel=1)
+    scores, metrics, _ = compute_verifier_score({"responses": resp, "labels": labels,
+                                                 "response_length": [torch.tensor([6]), torch.tensor([5])]}, cfg, tok)
+    assert scores.tolist() == [2.0, 0.0] and metrics["math_17k_acc_rewards/mean"] == [1.0, 0.0]
