@@ -143,6 +143,9 @@ def _int_list(value, key: str):
         value = [v for v in value.replace(" ", "").split(",") if v]
     elif isinstance(value, int):
         value = [value]
+    if any(isinstance(v, (list, tuple)) for v in value):
+        # vision-language models: [layers of the vision tower per stage, layers of the decoder per stage]
+        return [_int_list(v, key) if isinstance(v, (list, tuple)) else [int(v)] for v in value]
     try:
         return [int(v) for v in value]
     except (TypeError, ValueError):

@@ -81,3 +81,20 @@ def test_layer_lists_are_read_from_comma_separated_text():
     assert MegatronConfig({"num_layers": 4}).num_layer_list is None
     with pytest.raises(ValueError):
         MegatronConfig({"num_layers": 4, "num_layer_list": "2,x"})
+
+
+def test_vision_language_model_file_sets_the_stage_layout(tmp_path):
+    import json
+    from mindspeed_rl_b200.config.training_config import MegatronConfig
+    path = tmp_path / "model.json"
+    path.write_text(json.dumps({"image_encoder": {"vision_encoder": {"pipeline_num_layers": [32, 0]}},
+                                "text_decoder": {"pipeline_num_layers": [12, 16]}}))
+    c = MegatronConfig({"num_layers": 28})
+    c.update({"model": "qwen25vl"}, str(path))
+    c._finalize()
+    assert c.num_layer_list == [[32, 0], [12, 16]] and c.mm_model == str(path)
+    path.write_text(json.dumps({"text_decoder": {}}))
+    with pytest.raises(ValueError):
+        MegatronConfig({"num_layers": 28}).update({"model": "x"}, str(path))
+    with pytest.raises(FileNotFoundError):
+        MegatronConfig({"num_layers": 28}).update({"model": "x"}, str(tmp_path / "missing.json"))
