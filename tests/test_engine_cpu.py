@@ -68,3 +68,14 @@ def test_abort_returns_partial_output_and_frees_blocks():
     ref = alone.generate([[3, 9, 27, 5]], params)[0]
     assert done[0].outputs[0].token_ids == ref.outputs[0].token_ids
     assert eng.kv_bytes_per_block() == 2 * 2 * 4 * 2 * 8 * 4     # K and V x layers x block x kv heads x head dim x fp32
+
+
+def test_prompt_at_the_length_limit_finishes_without_tokens():
+    """A prompt that already fills ``max_model_len`` is answered at once with finish reason "length" and no
+    tokens; the requests queued behind it are served normally."""
+    eng = _engine(lookahead=False)
+    params = SamplingParams(n=1, temperature=0.0, max_tokens=4)
+    outs = eng.generate([list(range(1, 41)), [3, 9, 27, 5]], params)       # max_model_len is 40
+    assert outs[0].outputs[0].token_ids == [] and outs[0].outputs[0].finish_reason == "length"
+    assert len(outs[1].outputs[0].token_ids) >= 1 and outs[1].finished
+    assert not eng.has_unfinished_requests()
