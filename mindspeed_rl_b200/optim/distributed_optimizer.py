@@ -345,14 +345,17 @@ class DistributedOptimizer:
         """Move device-resident optimizer state to pinned host memory (rollout phase)."""
         if self.offload_to_host:
             return
+        moved = False
         for st in self.state:
             for k, v in list(st.items()):
                 if v.is_cuda:
                     host = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
                     host.copy_(v, non_blocking=True)
                     st[k] = host
-        torch.cuda.synchronize()
-        self._state_offloaded = True
+                    moved = True
+        if moved:
+            torch.cuda.synchronize()
+        self._state_offloaded = moved or getattr(self, "_state_offloaded", False)
 
     def onload_state(self) -> None:
         if not getattr(self, "_state_offloaded", False):

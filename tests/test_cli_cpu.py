@@ -248,6 +248,13 @@ def test_ppo_and_dapo_through_the_launcher():
         "megatron_training.stage=ray_ppo", "rl_config.adv_estimator=gae", "+critic_config.model=tiny_qwen2",
         "+critic_config.micro_batch_size=4", "+critic_config.lr=1e-5", "+rl_config.critic_resource.num_gpus=1"]), "ppo")
     assert len(h) == 1 and "critic/vf_loss" in h[0] and "critic/values/mean" in h[0] and h[0]["timing/update_critic"] > 0
+    # the same with every training-state offload switched on: the critic parks its state between its stages
+    h = run_rl(compose("grpo_tiny_cpu", None, small + [
+        "megatron_training.stage=ray_ppo", "rl_config.adv_estimator=gae", "+critic_config.model=tiny_qwen2",
+        "+critic_config.micro_batch_size=4", "+critic_config.lr=1e-5", "+rl_config.critic_resource.num_gpus=1",
+        "megatron_training.train_iters=2", "+generate_config.offload_train_param=true",
+        "+generate_config.offload_train_grad=true", "+generate_config.offload_train_optimizer=true"]), "ppo")
+    assert len(h) == 2 and all(m["critic/vf_loss"] >= 0 and m["actor/grad_norm"] >= 0 for m in h)
     h = run_rl(compose("grpo_tiny_cpu", None, small + [
         "megatron_training.stage=ray_dapo", "+rl_config.clip_higher_enable=true", "+rl_config.clip_ratio_low=0.2",
         "+rl_config.clip_ratio_high=0.28", "+rl_config.token_level_loss=true", "rl_config.init_kl_coef=0.0"]), "dapo")
