@@ -1031,3 +1031,34 @@ def test_launch_grpo_context_parallel_ring():
 
 def test_launch_grpo_context_parallel_all_to_all():
     run_distributed(_launch_cp_worker, 2, "ulysses_cp_algo")
+
+
+def _launch_overlap_worker(rank, world, want):
+    """Two data-parallel replicas with bucketed gradient reduction behind the backward and the parameter gather
+    pipelined behind the optimizer's chunks: same numbers as the plain schedule."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"rl_config.actor_resource.num_gpus={world}", "megatron_training.global_batch_size=4",
+        "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=4", "actor_config.lr=1e-3",
+        "generate_config.sampling_config.max_tokens=48", "megatron_training.train_iters=2"] +
+        (["actor_config.overlap_grad_reduce=true", "actor_config.overlap_param_gather=true"] if want is not None else []))
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        got = [(m["actor/grad_norm"], m["actor/entropy"], m["response_length/mean"]) for m in hist]
+        if want is None:
+            import json, os
+            with open(os.environ["MSRL_TEST_OUT"], "w") as fh:
+                json.dump(got, fh)
+        else:
+            for a, b in zip(got, want):
+                assert all(abs(x - y) <= 1e-5 * max(1.0, abs(y)) for x, y in zip(a, b)), (got, want)
+
+
+def test_launch_grpo_dp2_with_overlapped_collectives(tmp_path, monkeypatch):
+    import json
+    monkeypatch.setenv("MSRL_TEST_OUT", str(tmp_path / "plain.json"))
+    run_distributed(_launch_overlap_worker, 2, None)
+    want = json.loads((tmp_path / "plain.json").read_text())
+    assert len(want) == 2 and want[0][0] > 0
+    run_distributed(_launch_overlap_worker, 2, want)
