@@ -91,3 +91,65 @@ def test_change_gate_chooses_the_tier_from_the_changed_files():
     assert len(cmds) == 3 and cmds[-1][-1] == "gpu" and "build()" in cmds[0][-1]
     assert len(gate.commands_for("build", gpu=False)) == 2
     assert gate.main(["--files-from", os.devnull, "--dry-run"]) == 0
+
+
+def test_rpc_errors_timeouts_and_concurrent_callers():
+    """Remote calls: an exception on the serving side arrives as RemoteError with its traceback text, a server
+    that does not answer in time gives TimeoutError (and the proxy is usable again afterwards), and calls from
+    several threads are served side by side."""
+    import threading
+    import time
+    import pytest
+    from mindspeed_rl_b200.runtime.rpc import ActorProxy, RemoteError, serve
+
+    class Target:
+        def __init__(self):
+            self.live, self.peak, self.lock = 0, 0, threading.Lock()
+
+        def add(self, a, b=0):
+            return a + b
+
+        def boom(self):
+            raise KeyError("no such row")
+
+        def slow(self, seconds):
+            with self.lock:
+                self.live += 1
+                self.peak = max(self.peak, self.live)
+            time.sleep(seconds)
+            with self.lock:
+                self.live -= 1
+            return seconds
+
+    target = Target()
+    server = serve(target, num_threads=4)
+    try:
+        proxy = ActorProxy(server.address, timeout_s=2.0)
+        assert proxy._call("__ping__") == "pong" and proxy.add(2, b=3) == 5
+        with pytest.raises(RemoteError) as err:
+            proxy.boom()
+        assert "KeyError" in str(err.value) and "no such row" in str(err.value) and "boom" in str(err.value)
+        with pytest.raises(RemoteError):
+            proxy.no_such_method()
+        assert proxy.add(1, 1) == 2                                   # the connection survives remote errors
+        results = []
+        threads = [threading.Thread(target=lambda: results.append(proxy.slow(0.2))) for _ in range(4)]
+        t0 = time.time()
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        assert results == [0.2] * 4 and target.peak >= 2 and time.time() - t0 < 0.75
+        quick = ActorProxy(server.address, timeout_s=0.1)
+        with pytest.raises(TimeoutError):
+            quick.slow(0.5)
+        time.sleep(0.5)
+        assert quick.add(4, 4) == 8                                   # a fresh socket after the timeout
+        with pytest.raises(AttributeError):
+            proxy._private
+    finally:
+        server.shutdown()
+    gone = ActorProxy(server.address, timeout_s=0.3)
+    time.sleep(0.3)
+    with pytest.raises(TimeoutError):
+        gone.add(1, 2)
