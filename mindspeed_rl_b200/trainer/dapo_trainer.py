@@ -119,6 +119,9 @@ class RayDAPOTrainer(RayBaseTrainer):
                 self.actor_worker.enter_infer_mode(blocking=self.blocking)
             self.actor_worker.generate_sequences(blocking=self.blocking)
             again = False
+            for reward in self.reward_list:          # model-based reward scorers: a stage every rank calls
+                if hasattr(reward, "worker"):
+                    reward.compute_rm_score(blocking=True)
             if self.is_driver:
                 for reward in self.reward_list:
                     if not hasattr(reward, "worker"):

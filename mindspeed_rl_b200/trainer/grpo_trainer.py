@@ -93,11 +93,16 @@ class RayGRPOTrainer(RayBaseTrainer):
                 self._driver_section_done()
             # rollout
             self.actor_worker.generate_sequences(blocking=self.blocking)
-            # rewards + advantages (driver-side CPU stages)
+            # model-based reward scorers are stages of a worker group: every rank of the job makes the call
+            for reward in self.reward_list:
+                if hasattr(reward, "worker"):
+                    reward.compute_rm_score(blocking=True)
+            # rule rewards + advantages (driver-side CPU stages)
             if self.is_driver:
                 t_r = time.time()
                 for reward in self.reward_list:
-                    reward.compute_rm_score()
+                    if not hasattr(reward, "worker"):
+                        reward.compute_rm_score()
                 t_a = time.time()
                 compute_advantage(td, self.gamma, self.lam, self.adv_estimator, rl.adv_dispatch_size,
                                   self.pad_token_id, self.global_batch_size, self.guarantee_order,

@@ -1062,3 +1062,27 @@ def test_launch_grpo_dp2_with_overlapped_collectives(tmp_path, monkeypatch):
     want = json.loads((tmp_path / "plain.json").read_text())
     assert len(want) == 2 and want[0][0] > 0
     run_distributed(_launch_overlap_worker, 2, want)
+
+
+def _launch_reward_model_worker(rank, world):
+    """Actor on rank 0, reference model on rank 1, a model-based reward scorer (decoder + scalar head) on rank 2:
+    the scores column is written by the scorer's group and consumed by the advantage stage."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        "rl_config.use_integrated_worker=false", "rl_config.actor_resource.num_gpus=1",
+        "+rl_config.reference_resource.num_gpus=1", "+rl_config.reward_resource.num_gpus=1", "+reward_config.model=tiny_qwen2", "+reward_config.micro_batch_size=4",
+        "+ref_config.model=tiny_qwen2", "+ref_config.micro_batch_size=4", "+rl_config.rule_reward=false",
+        "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+        "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=2"])
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == 2
+        for m in hist:
+            assert m["timing/reward_model"] > 0 and "actor/pg_loss" in m
+            assert m["grpo/score/max"] != m["grpo/score/min"]            # a random scalar head: scores differ
+            assert m["actor/grad_norm"] > 0
+
+
+def test_launch_grpo_reward_model_on_its_own_rank():
+    run_distributed(_launch_reward_model_worker, 3)
