@@ -1086,3 +1086,26 @@ def _launch_reward_model_worker(rank, world):
 
 def test_launch_grpo_reward_model_on_its_own_rank():
     run_distributed(_launch_reward_model_worker, 3)
+
+
+def _launch_critic_rank_worker(rank, world, blocking):
+    """PPO with the actor (and its reference) on rank 0 and the critic on rank 1: value estimates, advantages and
+    both updates flow through the experience store served by the driver."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        "rl_config.actor_resource.num_gpus=1", "megatron_training.stage=ray_ppo", "rl_config.adv_estimator=gae",
+        "+critic_config.model=tiny_qwen2", "+critic_config.micro_batch_size=4", "+critic_config.lr=1e-5",
+        "+rl_config.critic_resource.num_gpus=1", "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4",
+        "rl_config.n_samples_per_prompt=2", "generate_config.sampling_config.max_tokens=8",
+        "megatron_training.train_iters=2", f"rl_config.blocking={'true' if blocking else 'false'}"])
+    hist = run_rl(cfg, "ppo")
+    if rank == 0:
+        assert len(hist) == 2
+        assert all(m["critic/vf_loss"] >= 0 and m["timing/update_critic"] > 0 and m["timing/critic_model"] > 0
+                   and "actor/pg_loss" in m for m in hist)
+
+
+def test_launch_ppo_critic_on_its_own_rank():
+    run_distributed(_launch_critic_rank_worker, 2, True, timeout=240)
+    run_distributed(_launch_critic_rank_worker, 2, False, timeout=240)
