@@ -290,20 +290,31 @@ class GRPOTransferDock(TransferDock):
             ready &= self.experience_data_status[c] == 1
         return ready
 
+    def _training_window(self) -> torch.Tensor:
+        """Partial rollout: rows of the first ``GBS_train`` completed prompt groups.  More groups than one
+        training batch may have completed when the rollout stops; every downstream stage (rewards, log-probs,
+        advantages, update) must work on the same ones, so the choice is by position, not by chance."""
+        n = self.n_samples_per_prompt
+        done = (self.global_ready_mask.view(self.prompts_num, n).sum(dim=1) == n).nonzero(as_tuple=True)[0]
+        rows = torch.zeros(self.max_len, dtype=torch.bool)
+        for g in done[:self.GBS_train].tolist():
+            rows[g * n:(g + 1) * n] = True
+        return rows
+
     def _sample_ready_index(self, consumer: str, experience_count: int, columns: Sequence[str],
                             use_batch_seqlen_balance: bool = False) -> Optional[List[int]]:
         with self.consumer_sampling_lock[consumer]:
             usable = (self.experience_consumer_status[consumer] == 0) & self._ready_mask(columns)
             rollout_pr = self.enable_partial_rollout and consumer == "actor_rollout"
             if self.enable_partial_rollout and not rollout_pr:
-                usable &= self.global_ready_mask == 1
+                usable &= self._training_window()
             usable_idx = usable.nonzero(as_tuple=True)[0]
             if len(usable_idx) < experience_count:
                 if rollout_pr and len(usable_idx) > 0:
                     experience_count = len(usable_idx)
                 else:
                     return None
-            if rollout_pr:
+            if rollout_pr or self.enable_partial_rollout:
                 picked = usable_idx[:experience_count].tolist()
             elif (use_batch_seqlen_balance and consumer in _BALANCED_CONSUMERS
                   and len(usable_idx) % experience_count == 0):
@@ -327,7 +338,7 @@ class GRPOTransferDock(TransferDock):
             ready = self._ready_mask(columns).view(self.prompts_num, n).all(dim=1)
             usable = free & ready
             if self.enable_partial_rollout:
-                usable &= self.global_ready_mask.view(self.prompts_num, n).sum(dim=1) == n
+                usable &= self._training_window().view(self.prompts_num, n).all(dim=1)
             usable_idx = usable.nonzero(as_tuple=True)[0]
             if len(usable_idx) < groups_wanted:
                 return None

@@ -1109,3 +1109,23 @@ def _launch_critic_rank_worker(rank, world, blocking):
 def test_launch_ppo_critic_on_its_own_rank():
     run_distributed(_launch_critic_rank_worker, 2, True, timeout=240)
     run_distributed(_launch_critic_rank_worker, 2, False, timeout=240)
+
+
+def _launch_partial_rollout_worker(rank, world):
+    """Partial rollout over two data-parallel replicas: when more prompt groups than one training batch have
+    completed, every stage (rewards, log-probs, advantages, update) works on the same first groups, so the two
+    replicas get equal shares and the update's collectives line up."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"rl_config.actor_resource.num_gpus={world}", "megatron_training.global_batch_size=4",
+        "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2", "rl_config.partial_rollout_max_split=2",
+        "generate_config.sampling_config.max_tokens=16", "megatron_training.train_iters=3"])
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == 3
+        assert all(m["response_length/max"] <= 16 and "actor/pg_loss" in m for m in hist)
+
+
+def test_launch_grpo_partial_rollout_dp2():
+    run_distributed(_launch_partial_rollout_worker, 2, timeout=240)
