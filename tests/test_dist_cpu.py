@@ -1129,3 +1129,45 @@ def _launch_partial_rollout_worker(rank, world):
 
 def test_launch_grpo_partial_rollout_dp2():
     run_distributed(_launch_partial_rollout_worker, 2, timeout=240)
+
+
+def _launch_misc_worker(rank, world, overrides, expect_key):
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"rl_config.actor_resource.num_gpus={world}", "megatron_training.global_batch_size=4",
+        "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+        "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=2"] + list(overrides))
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == 2 and all(expect_key in m and "actor/pg_loss" in m for m in hist)
+
+
+def test_launch_grpo_multi_turn_with_tensor_parallel_rollout():
+    """The multi-turn loop with the tool file of the shipped recipe on a TP2 rollout group (the ranks of the
+    group step the loop together); the whitespace tokenizer never produces a call, so no tool runs."""
+    run_distributed(_launch_misc_worker, 2, [
+        "rl_config.multi_turn_enable=true", "rl_config.async_engine=true",
+        "rl_config.tool_config_path=configs/tools/retool.yaml", "rl_config.max_tool_calls=1",
+        "rl_config.max_parallel_calls=1", "rl_config.max_total_response_length=64",
+        "rl_config.max_tool_response_length=16", "rl_config.tool_parser_format=hermes",
+        "actor_config.tensor_model_parallel_size=2", "generate_config.infer_tensor_parallel_size=2"],
+        "tool_call_num/mean", timeout=240)
+
+
+def test_launch_grpo_vision_stage_on_its_own_rank(tmp_path):
+    import json
+    import numpy as np
+    rng = np.random.default_rng(0)
+    with open(tmp_path / "rows.jsonl", "w") as f:
+        for i in range(8):
+            img = (rng.random((28, 42, 3)) * 255).astype(np.uint8).tolist()
+            f.write(json.dumps({"prompt": f"5 6 <image> 7 {8 + i}", "images": [img], "answer": str(i)}) + "\n")
+    run_distributed(_launch_misc_worker, 2, [
+        "rl_config.actor_resource.num_gpus=1", "+rl_config.vit_resource.num_gpus=1",
+        f"megatron_training.data_path={tmp_path / 'rows.jsonl'}", "+rl_config.is_multimodal=true",
+        "+rl_config.reuse_image_embeds=true", "generate_config.enable_prefix_caching=false",
+        "rl_config.use_remove_padding=false", "+megatron_training.image_token_id=1000",
+        "+megatron_training.vision_start_token_id=1001", "+megatron_training.vision_end_token_id=1002",
+        "+vit_config.hidden_size=32", "+vit_config.num_layers=1", "+vit_config.num_attention_heads=2",
+        "+vit_config.ffn_hidden_size=48", "+rl_config.max_prompt_length=96"], "timing/vit_image_emb", timeout=240)
