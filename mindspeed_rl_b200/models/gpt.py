@@ -235,8 +235,10 @@ def layer_forward(layer: TransformerLayer, h: torch.Tensor, meta: PackedMeta, ke
         # activation-function recompute: drop silu(g)*u and rebuild it from gu in the backward
         mlp_ctx = (gu, None if cfg.recompute_activation_function else y) if keep else None
     else:
-        x2g = comm.gather_seq(x2)
-        mlp_out, mlp_ctx = layer.mlp.forward_tokens(x2g, comm, keep)
+        # expert layers work on the tokens this rank owns (under sequence parallelism every TP rank routes its
+        # own shard); their shared experts gather / reduce inside
+        x2g = x2
+        mlp_out, mlp_ctx = layer.mlp.forward_tokens(x2, comm, keep)
     h2 = ops.add(h1, mlp_out)
     if not keep:
         return h2, None
@@ -266,8 +268,7 @@ def layer_backward(layer: TransformerLayer, ctx: Dict[str, Any], meta: PackedMet
         if "fc1" in lo:
             dx2 = dx2 + lora.column_bwd(layer.mlp.linear_fc1, ctx["x2g"], lo["fc1"], dgu, comm)
     else:
-        d_out = comm.reduce_out_bwd(dh2)
-        dx2 = comm.gather_seq_bwd(layer.mlp.backward_tokens(ctx["mlp_ctx"], ctx["x2g"], d_out, comm))
+        dx2 = layer.mlp.backward_tokens(ctx["mlp_ctx"], ctx["x2g"], dh2, comm)
     dh1 = ops.rmsnorm_bwd(dx2, ctx["h1"], layer.pre_mlp_layernorm.weight, ctx["rstd2"],
                           grad_buffer(layer.pre_mlp_layernorm.weight), dres=dh2)
     # ---- attention ----

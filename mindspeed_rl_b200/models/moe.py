@@ -106,6 +106,19 @@ class MoELayer(nn.Module):
         if e % self.ep_size:
             raise ValueError("num_experts must be divisible by the expert-parallel size")
         self.num_local = e // self.ep_size
+        layout = getattr(ps, "layout", None)
+        tp = int(getattr(layout, "tp", 1) or 1)
+        extend = bool(getattr(layout, "moe_tp_extend_ep", False))
+        if tp > 1 and int(getattr(layout, "ep", 1) or 1) > 1 and not extend:
+            raise ValueError("experts are never cut by tensor parallelism here: with tensor_model_parallel_size > 1 "
+                             "and expert_model_parallel_size > 1 set moe_tp_extend_ep (experts spread over TP x EP)")
+        if tp > 1 and extend and not cfg.sequence_parallel:
+            raise ValueError("moe_tp_extend_ep with tensor parallelism needs sequence_parallel: every TP rank must "
+                             "route its own tokens, or the experts would see every token tp times")
+        # experts replicated over the TP group see only the local token shard under sequence parallelism:
+        # their gradients are partial sums that the gradient sync adds up over TP (and counts once in the norm)
+        self._experts_tp_partial = tp > 1 and not extend and bool(cfg.sequence_parallel)
+        self._experts_tp_replicated = tp > 1 and not extend
         dt, std = cfg.params_dtype, cfg.init_method_std
         out_std = std / math.sqrt(2.0 * cfg.num_layers)
         self.router = _W(_normal((e, h), std, torch.float32, device, gen))
@@ -115,6 +128,9 @@ class MoELayer(nn.Module):
             self._load_since_update = torch.zeros(e, dtype=torch.float32, device=device)
         self.experts = _Experts(_normal((h, self.num_local * 2 * f), std, dt, device, gen),
                                 _normal((self.num_local * f, h), out_std, dt, device, gen))
+        for w in (self.experts.weight1, self.experts.weight2):
+            w.tp_reduce_grad = self._experts_tp_partial
+            w.tp_replicated = self._experts_tp_replicated
         self.shared_experts = None
         if cfg.n_shared_experts:
             from .gpt import MLP
@@ -251,7 +267,9 @@ class MoELayer(nn.Module):
 
     # ------------------------------------------------------------------------------------------
     def forward_tokens(self, x: torch.Tensor, comm, keep: bool):
-        """``x [T, H]`` (full sequence on this rank) -> ``(out [T, H], ctx)``."""
+        """``x [T, H]``: the tokens this rank owns (its sequence shard under sequence parallelism, all tokens
+        otherwise) -> ``(out [T, H], ctx)``.  Routed experts are never cut by TP, so routing, dispatch and combine
+        need no TP collective; only the shared experts (a tensor-parallel MLP) talk to the TP group."""
         cfg = self.cfg
         t = x.shape[0]
         with torch.enable_grad():
@@ -285,10 +303,8 @@ class MoELayer(nn.Module):
         out = out.to(x.dtype)
         shared_ctx = None
         if self.shared_experts is not None:
-            gu = _gemm.linear_fwd(x, self.shared_experts.linear_fc1.weight)
-            act = ops.swiglu_fwd(gu)
-            out = out + comm.reduce_out(_gemm.linear_fwd(act, self.shared_experts.linear_fc2.weight))
-            shared_ctx = (gu, act) if keep else None
+            sh, shared_ctx = self._shared_fwd(x, comm, keep)
+            out = out + sh
         if not keep:
             return out, None
         ctx = dict(xr=xr, top_p=top_p, aux=aux, plan=plan, ectx=ectx, y_sorted=y_sorted,
@@ -297,10 +313,26 @@ class MoELayer(nn.Module):
 
     # ---- all experts on this rank: dispatch plan + grouped GEMMs, no host round trip in the forward ----
     def _shared_fwd(self, x, comm, keep):
-        gu = _gemm.linear_fwd(x, self.shared_experts.linear_fc1.weight)
+        """Shared experts are an ordinary tensor-parallel MLP over the tokens of this rank: tokens are gathered
+        over TP under sequence parallelism (identity otherwise), the row-parallel output is reduce-scattered
+        (all-reduced) back."""
+        xg = comm.gather_seq(x)
+        gu = _gemm.linear_fwd(xg, self.shared_experts.linear_fc1.weight)
         act = ops.swiglu_fwd(gu)
         y = comm.reduce_out(_gemm.linear_fwd(act, self.shared_experts.linear_fc2.weight))
-        return y, ((gu, act) if keep else None)
+        return y, ((xg, gu, act) if keep else None)
+
+    def _shared_bwd(self, shared_ctx, dout, comm) -> torch.Tensor:
+        from .gpt import accum_wgrad
+
+        xg, gu, act = shared_ctx
+        fc1, fc2 = self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight
+        d_sh = comm.reduce_out_bwd(dout)
+        dact = _gemm.linear_dgrad(d_sh, fc2)
+        accum_wgrad(fc2, d_sh, act)
+        dgu = ops.swiglu_bwd(gu, dact)
+        accum_wgrad(fc1, dgu, xg)
+        return comm.gather_seq_bwd(_gemm.linear_dgrad(dgu, fc1))
 
     def _forward_local(self, x, xr, top_p, top_idx, aux, comm, keep):
         from ..ops import moe as K
@@ -433,14 +465,7 @@ class MoELayer(nn.Module):
         if len(got) > 1 and got[1] is not None:
             grad_buffer(self.router.weight).add_(got[1].to(grad_buffer(self.router.weight).dtype))
         if self.shared_experts is not None:
-            gu, act = ctx["shared"]
-            fc1, fc2 = self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight
-            d_sh = comm.reduce_out_bwd(dout)
-            dact = _gemm.linear_dgrad(d_sh, fc2)
-            accum_wgrad(fc2, d_sh, act)
-            dgu = ops.swiglu_bwd(gu, dact)
-            dx += _gemm.linear_dgrad(dgu, fc1).float()
-            accum_wgrad(fc1, dgu, x)
+            dx += self._shared_bwd(ctx["shared"], dout, comm).float()
         return dx.to(x.dtype)
 
     def backward_tokens(self, ctx, x: torch.Tensor, dout: torch.Tensor, comm) -> torch.Tensor:
@@ -473,14 +498,7 @@ class MoELayer(nn.Module):
         if len(got) > 1 and got[1] is not None:
             grad_buffer(self.router.weight).add_(got[1].to(grad_buffer(self.router.weight).dtype))
         if self.shared_experts is not None:
-            gu, act = ctx["shared"]
-            fc1, fc2 = self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight
-            d_sh = comm.reduce_out_bwd(dout)
-            dact = _gemm.linear_dgrad(d_sh, fc2)
-            accum_wgrad(fc2, d_sh, act)
-            dgu = ops.swiglu_bwd(gu, dact)
-            dx += _gemm.linear_dgrad(dgu, fc1).float()
-            accum_wgrad(fc1, dgu, x)
+            dx += self._shared_bwd(ctx["shared"], dout, comm).float()
         return dx.to(x.dtype)
 
     # ------------------------------------------------------------------------------------------

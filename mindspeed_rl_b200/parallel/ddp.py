@@ -438,8 +438,9 @@ class DistributedDataParallel(nn.Module):
 
     # names of replicated parameters whose gradient is a partial sum over the TP ranks
     _TP_PARTIAL_ALWAYS = ("q_layernorm.weight", "k_layernorm.weight")          # each rank sees its own heads
-    # norms run on the local token shard (routers and the value head run on gathered tokens)
-    _TP_PARTIAL_WITH_SP = ("input_layernorm.weight", "pre_mlp_layernorm.weight", "final_layernorm.weight")
+    # norms and expert routers run on the local token shard (the value head runs on gathered tokens)
+    _TP_PARTIAL_WITH_SP = ("input_layernorm.weight", "pre_mlp_layernorm.weight", "final_layernorm.weight",
+                           "router.weight")
 
     def attach_tensor_parallel(self, tp_group, tp_size: int, sequence_parallel: bool) -> None:
         """Register the TP group so that ``finish_grad_sync`` can sum the gradients of replicated

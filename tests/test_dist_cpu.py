@@ -1171,3 +1171,91 @@ def test_launch_grpo_vision_stage_on_its_own_rank(tmp_path):
         "+megatron_training.vision_start_token_id=1001", "+megatron_training.vision_end_token_id=1002",
         "+vit_config.hidden_size=32", "+vit_config.num_layers=1", "+vit_config.num_attention_heads=2",
         "+vit_config.ffn_hidden_size=48", "+rl_config.max_prompt_length=96"], "timing/vit_image_emb", timeout=240)
+
+
+def _moe_tp_worker(rank, world, sp, extend):
+    """Expert layers under tensor parallelism against the single-rank model: experts replicated over the TP ranks
+    (with and without sequence parallelism) or spread over them (``moe_tp_extend_ep``); one shared expert."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel, set_parallel_state
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, add_qkv_bias=True, params_dtype=torch.float32, max_position_embeddings=128,
+              num_experts=4, moe_router_topk=2, moe_ffn_hidden_size=16, n_shared_experts=1, moe_aux_loss_coeff=0.01)
+    if sp:
+        # under sequence parallelism the balancing loss is computed per token shard (every TP rank balances its own
+        # tokens), which is not the single-rank loss over all tokens: it stays out of the strict comparison
+        kw["moe_aux_loss_coeff"] = 0.0
+    set_parallel_state(None)
+    initialize_model_parallel(world_size=1, rank=0)          # the reference model holds every expert
+    torch.manual_seed(0)
+    full = GPTModel(TransformerConfig(**kw), device="cpu", seed=5)
+    set_parallel_state(None)
+    ps = initialize_model_parallel(tensor_model_parallel_size=world, moe_tp_extend_ep=extend)
+    cfg = TransformerConfig(tensor_model_parallel_size=world, sequence_parallel=sp, **kw)
+    comm = TPComm(ps.group("tp"), sp, world_size=world, rank=rank)
+    model = GPTModel(cfg, comm, device="cpu")
+    ep = ps.size("ep")
+    assert ep == (world if extend else 1)
+    h, f, e = 32, 16, 4
+    per = e // ep
+    er = ps.rank_in("ep")
+
+    def shard(state):
+        out = _shard_state(state, cfg, world, rank)
+        for k, v in state.items():
+            if k.endswith("experts.weight1"):
+                out[k] = v.view(h, e, 2 * f)[:, er * per:(er + 1) * per].reshape(h, -1).contiguous()
+            elif k.endswith("experts.weight2"):
+                out[k] = v.view(e, f, h)[er * per:(er + 1) * per].reshape(-1, h).contiguous()
+            elif "shared_experts.linear_fc1" in k or "shared_experts.linear_fc2" in k:
+                pass                                        # cut like the dense MLP by _shard_state
+            elif ".mlp.router." in k:
+                out[k] = v.clone()
+        return out
+
+    model.load_state_dict(shard(full.state_dict()))
+    lens = [6, 10]
+    meta = PackedMeta.from_lengths(lens, "cpu", align=world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator().manual_seed(1)
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    ref_lp, ref_ent = full.forward_logprob(ids, labels, meta, 0.9, True)
+    (ref_lp * w + 0.1 * ref_ent).sum().backward()
+    if sp:
+        model.embed = lambda x, _m=model: _seq_shard(_orig_embed(_m, x), world, rank)
+    lp, ent = model.forward_logprob(ids, labels, meta, 0.9, True)
+    (lp * w + 0.1 * ent).sum().backward()
+    assert torch.allclose(lp, ref_lp, atol=1e-4), (lp - ref_lp).abs().max()
+    assert torch.allclose(ent, ref_ent, atol=1e-4)
+    want = shard({n: p.grad for n, p in full.named_parameters()})
+    bad = []
+    for n, p in model.named_parameters():
+        g_ = p.grad
+        partial = sp and ((p.dim() == 1 and "linear_qkv" not in n) or n.endswith("router.weight")
+                          or (".experts." in n and not extend))
+        assert bool(getattr(p, "tp_reduce_grad", False)) == (sp and ".experts." in n and not extend), n
+        if partial:                                          # what the gradient sync adds up over TP
+            dist.all_reduce(g_)
+        if not torch.allclose(g_, want[n], atol=3e-4, rtol=2e-3):
+            bad.append((n, float((g_ - want[n]).abs().max()), float(want[n].abs().max())))
+    assert not bad, bad
+
+
+def test_expert_layers_under_tensor_parallelism_match_single_rank():
+    run_distributed(_moe_tp_worker, 2, False, False, timeout=240)     # experts replicated, tokens replicated
+    run_distributed(_moe_tp_worker, 2, True, False, timeout=240)      # experts replicated, tokens split over TP
+    run_distributed(_moe_tp_worker, 2, True, True, timeout=240)       # experts spread over the TP ranks
+
+
+def test_launch_grpo_expert_recipe_shape():
+    """The 30B-A3B recipe's layout scaled down to 4 ranks: training TP2 x EP2 with the experts spread over
+    TP x EP and sequence parallelism, rollout TP1 x EP4 (dense weights gathered over TP, experts re-homed)."""
+    run_distributed(_launch_misc_worker, 4, [
+        "actor_config.tensor_model_parallel_size=2", "actor_config.expert_model_parallel_size=2",
+        "+actor_config.moe_tp_extend_ep=true", "+actor_config.sequence_parallel=true",
+        "generate_config.infer_tensor_parallel_size=1", "generate_config.infer_expert_parallel_size=4",
+        "+model.tiny_qwen2.num_experts=4", "+model.tiny_qwen2.moe_router_topk=2",
+        "+model.tiny_qwen2.moe_ffn_hidden_size=32", "+model.tiny_qwen2.norm_topk_prob=true",
+        "generate_config.sampling_config.max_tokens=32"], "actor/grad_norm", timeout=280)
