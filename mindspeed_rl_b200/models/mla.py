@@ -135,6 +135,32 @@ class MLASelfAttention(nn.Module):
         self.softmax_scale = m * m / math.sqrt(self.qd)
         self._table = None
 
+    @classmethod
+    def from_tensors(cls, cfg, tp_size: int, tensors) -> "MLASelfAttention":
+        """Forward-only block over existing tensors (the rollout's resharded copy of the weights): ``tensors`` maps
+        the parameter names of this block (``linear_q_up_proj.weight`` ...) to tensors already cut for ``tp_size``
+        ranks.  Nothing is allocated or initialised."""
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        self.cfg = cfg
+        self.nh = cfg.num_attention_heads // tp_size
+        self.nope, self.rope, self.vd = cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim
+        self.qd = self.nope + self.rope
+
+        class _View:                       # what ``qkv`` reads: an object with a ``weight``
+            def __init__(self, w):
+                self.weight = w
+
+        for name in ("linear_q_down_proj", "q_layernorm", "linear_q_up_proj", "linear_q_proj",
+                     "linear_kv_down_proj", "kv_layernorm", "linear_kv_up_proj", "linear_proj"):
+            w = tensors.get(name + ".weight")
+            object.__setattr__(self, name, _View(w) if w is not None else None)
+        sc = cfg.rope_scaling or {}
+        m = yarn_mscale(float(sc.get("factor", 1.0)), float(sc.get("mscale_all_dim", 0.0) or 0.0)) if sc else 1.0
+        self.softmax_scale = m * m / math.sqrt(self.qd)
+        self._table = None
+        return self
+
     # ------------------------------------------------------------------------------------------
     def rope_table(self, device) -> torch.Tensor:
         if self._table is None or self._table.device != device:

@@ -70,7 +70,9 @@ class ExpertPlacement:
 def partition_kind(name: str) -> str:
     """How training tensor parallelism cuts a parameter."""
     if name.endswith(("linear_qkv.weight", "linear_qkv.bias", "word_embeddings.weight", "output_layer.weight",
-                      "linear_qkv.lora_B")):
+                      "linear_qkv.lora_B",
+                      # latent attention: the up-projections hold whole heads, head-major
+                      "linear_q_up_proj.weight", "linear_kv_up_proj.weight", "linear_q_proj.weight")):
         return "rows"
     if name.endswith(("linear_fc1.weight", "linear_fc1.lora_B")):
         return "glu"
@@ -352,10 +354,23 @@ def weights_from_buffer(cfg: TransformerConfig, infer_tp: int, tp_rank: int, pla
         if getattr(cfg, "lora_r", 0):
             for holder in ("self_attention.linear_qkv", "self_attention.linear_proj", "mlp.linear_fc1", "mlp.linear_fc2"):
                 fold(p + holder)
-        kw = dict(input_norm=t(p + "input_layernorm.weight"), qkv_w=t(p + "self_attention.linear_qkv.weight"),
-                  qkv_b=t(p + "self_attention.linear_qkv.bias"), o_w=t(p + "self_attention.linear_proj.weight"),
-                  post_norm=t(p + "pre_mlp_layernorm.weight"), q_norm=t(p + "self_attention.q_layernorm.weight"),
-                  k_norm=t(p + "self_attention.k_layernorm.weight"))
+        if getattr(cfg, "multi_latent_attention", False):
+            from ..models.mla import MLASelfAttention
+
+            sa = p + "self_attention."
+            names = [n[len(sa):] for n in plan.tensors if n.startswith(sa)]
+            block = MLASelfAttention.from_tensors(cfg, infer_tp, {n: t(sa + n) for n in names})
+            if not block.rollout_supported():
+                raise NotImplementedError(
+                    "rollout of latent attention needs query/key and value heads of one common size 64 or 128 "
+                    f"(got {block.qd} / {block.vd}): the paged KV cache stores full per-head keys and values")
+            kw = dict(input_norm=t(p + "input_layernorm.weight"), qkv_w=None, qkv_b=None, mla=block,
+                      o_w=t(sa + "linear_proj.weight"), post_norm=t(p + "pre_mlp_layernorm.weight"))
+        else:
+            kw = dict(input_norm=t(p + "input_layernorm.weight"), qkv_w=t(p + "self_attention.linear_qkv.weight"),
+                      qkv_b=t(p + "self_attention.linear_qkv.bias"), o_w=t(p + "self_attention.linear_proj.weight"),
+                      post_norm=t(p + "pre_mlp_layernorm.weight"), q_norm=t(p + "self_attention.q_layernorm.weight"),
+                      k_norm=t(p + "self_attention.k_layernorm.weight"))
         if p + "mlp.linear_fc1.weight" in plan.tensors:
             kw.update(gate_up_w=t(p + "mlp.linear_fc1.weight"), down_w=t(p + "mlp.linear_fc2.weight"))
         elif moe_builder is not None:
@@ -365,8 +380,12 @@ def weights_from_buffer(cfg: TransformerConfig, infer_tp: int, tp_rank: int, pla
         layers.append(LayerWeights(**kw))
     head = t("output_layer.weight")
     embed = t("embedding.word_embeddings.weight")
-    layout = QKVLayout(cfg.num_attention_heads // infer_tp, cfg.num_query_groups // infer_tp, cfg.head_dim,
-                       interleaved=True)
+    if getattr(cfg, "multi_latent_attention", False):
+        nh = cfg.num_attention_heads // infer_tp           # one key / value head per query head, full size
+        layout = QKVLayout(nh, nh, cfg.qk_head_dim + cfg.qk_pos_emb_head_dim, interleaved=True)
+    else:
+        layout = QKVLayout(cfg.num_attention_heads // infer_tp, cfg.num_query_groups // infer_tp, cfg.head_dim,
+                           interleaved=True)
     return RolloutWeights(embed=embed, layers=layers, final_norm=t("decoder.final_layernorm.weight"),
                           lm_head=head if head is not None else embed, qkv_layout=layout,
                           vocab_start=tp_rank * (cfg.vocab_size // infer_tp))

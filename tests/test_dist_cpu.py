@@ -1259,3 +1259,22 @@ def test_launch_grpo_expert_recipe_shape():
         "+model.tiny_qwen2.num_experts=4", "+model.tiny_qwen2.moe_router_topk=2",
         "+model.tiny_qwen2.moe_ffn_hidden_size=32", "+model.tiny_qwen2.norm_topk_prob=true",
         "generate_config.sampling_config.max_tokens=32"], "actor/grad_norm", timeout=280)
+
+
+def test_launch_grpo_latent_attention_expert_recipe_shape():
+    """The 671B recipe's structure scaled down to 4 ranks: latent attention, a dense first layer, sigmoid-routed
+    experts with a shared expert, training TP2 x PP2 with the experts spread over TP and sequence parallelism,
+    rollout TP2 x EP2 through the resharding plan."""
+    run_distributed(_launch_misc_worker, 4, [
+        "+model.tiny_qwen2.multi_latent_attention=true", "+model.tiny_qwen2.q_lora_rank=48",
+        "+model.tiny_qwen2.kv_lora_rank=32", "+model.tiny_qwen2.qk_head_dim=32",
+        "+model.tiny_qwen2.qk_pos_emb_head_dim=32", "+model.tiny_qwen2.v_head_dim=64",
+        "+model.tiny_qwen2.group_query_attention=false", "+model.tiny_qwen2.add_qkv_bias=false",
+        "+model.tiny_qwen2.num_experts=4", "+model.tiny_qwen2.moe_router_topk=2",
+        "+model.tiny_qwen2.moe_ffn_hidden_size=32", "+model.tiny_qwen2.n_shared_experts=1",
+        "+model.tiny_qwen2.first_k_dense_replace=1", "+model.tiny_qwen2.moe_router_score_function=sigmoid",
+        "+model.tiny_qwen2.norm_topk_prob=true", "actor_config.tensor_model_parallel_size=2",
+        "actor_config.pipeline_model_parallel_size=2", "+actor_config.moe_tp_extend_ep=true",
+        "+actor_config.sequence_parallel=true", "+actor_config.no_pad_to_seq_lengths=true",
+        "generate_config.infer_tensor_parallel_size=2", "generate_config.infer_expert_parallel_size=2",
+        "generate_config.sampling_config.max_tokens=16"], "actor/grad_norm", timeout=280)

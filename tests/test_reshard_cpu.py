@@ -30,6 +30,8 @@ def _shard(full, cfg, tp, r):
             out[k] = C.shard_cols(v, tp, r)
         elif k.endswith(("word_embeddings.weight", "output_layer.weight")):
             out[k] = C.shard_rows(v, tp, r)
+        elif k.endswith(("linear_q_up_proj.weight", "linear_kv_up_proj.weight", "linear_q_proj.weight")):
+            out[k] = C.shard_rows(v, tp, r)          # latent attention: whole heads, head-major
         else:
             out[k] = v.clone()
     return out
@@ -353,3 +355,47 @@ def test_plan_for_expert_recipe_layout_with_experts_spread_over_tp():
                 ref = want[name]
             got = dst[off:off + ref.numel() * 4].view(torch.float32).view(shape)
             assert torch.equal(got, ref), (r, name)
+
+
+
+@pytest.mark.parametrize("tp_t,pp_t,tp_i,world", [(2, 2, 1, 4), (4, 1, 2, 4), (1, 2, 2, 4)])
+def test_plan_for_latent_attention(tp_t, pp_t, tp_i, world):
+    """Latent attention (DeepSeek-style): down-projections and their norms are replicated, up-projections are cut
+    by heads, the output projection by columns; the rollout block built over the destination buffer computes
+    the same q / k / v as a model that was sharded directly for the rollout layout."""
+    from mindspeed_rl_b200.models.mla import MLASelfAttention
+    cfg = _cfg(num_attention_heads=4, num_query_groups=4, kv_channels=None, add_qkv_bias=False,
+               multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=32, qk_pos_emb_head_dim=32,
+               v_head_dim=64, max_position_embeddings=64)
+    full = GPTModel(cfg, seed=3).state_dict()
+    train = RankLayout(world, tp=tp_t, pp=pp_t)
+    layers = stage_layers(cfg.num_layers, pp_t)
+    buffers, tables = {}, [None] * pp_t
+    for r in range(world):
+        c = train.coords(r)
+        st = _stage_state(_shard(full, cfg, tp_t, c["tp"]), layers[c["pp"]], c["pp"] == 0, c["pp"] == pp_t - 1)
+        slots, flat = _flatten(st)
+        tables[c["pp"]] = slots
+        buffers[r] = flat.view(torch.uint8)
+    x = torch.randn(5, cfg.hidden_size, generator=torch.Generator().manual_seed(0))
+    pos = torch.arange(5)
+    for r in range(world):
+        plan = build_plan(cfg, train, tp_i, r, tables, layers, lambda rank: 0, esz=4)
+        dst = torch.zeros(plan.nbytes, dtype=torch.uint8)
+        execute_plan_torch(plan, buffers, dst)
+        j = r % tp_i
+        want = _shard(full, cfg, tp_i, j)
+        assert set(plan.tensors) == set(want)
+        for name, (off, shape) in plan.tensors.items():
+            got = dst[off:off + want[name].numel() * 4].view(torch.float32).view(shape)
+            assert torch.equal(got, want[name]), name
+        w = weights_from_buffer(cfg, tp_i, j, plan, dst, torch.float32)
+        assert w.layers[0].qkv_w is None and w.layers[0].mla is not None
+        assert w.qkv_layout.num_heads == w.qkv_layout.num_kv_heads == 4 // tp_i and w.qkv_layout.head_dim == 64
+        sa = "decoder.layers.1.self_attention."
+        direct = MLASelfAttention.from_tensors(cfg, tp_i, {k[len(sa):]: v for k, v in want.items() if k.startswith(sa)})
+        assert torch.equal(w.layers[1].mla.rollout_qkv(x, pos), direct.rollout_qkv(x, pos))
+        assert torch.equal(w.layers[1].o_w, want[sa + "linear_proj.weight"])
+        if tp_i == 1:                                     # and both equal the block of the unsharded model
+            ref = GPTModel(cfg, seed=3).decoder.layers[1].self_attention
+            assert torch.equal(w.layers[1].mla.rollout_qkv(x, pos), ref.rollout_qkv(x, pos))
