@@ -1278,3 +1278,39 @@ def test_launch_grpo_latent_attention_expert_recipe_shape():
         "+actor_config.sequence_parallel=true", "+actor_config.no_pad_to_seq_lengths=true",
         "generate_config.infer_tensor_parallel_size=2", "generate_config.infer_expert_parallel_size=2",
         "generate_config.sampling_config.max_tokens=16"], "actor/grad_norm", timeout=280)
+
+
+def test_launch_grpo_lora_recipe_shape():
+    """The LoRA recipe's layout scaled down to 4 ranks: training TP2 x PP2 with sequence parallelism, adapters on
+    all four linears, rollout TP2 with the adapters carried through the resharding plan and folded there."""
+    run_distributed(_launch_misc_worker, 4, [
+        "actor_config.tensor_model_parallel_size=2", "actor_config.pipeline_model_parallel_size=2",
+        "generate_config.infer_tensor_parallel_size=2", "+actor_config.no_pad_to_seq_lengths=true",
+        "+actor_config.sequence_parallel=true", "+actor_config.lora_r=4", "+actor_config.lora_alpha=8",
+        "+actor_config.lora_target_modules=[linear_qkv,linear_proj,linear_fc1,linear_fc2]",
+        "generate_config.sampling_config.max_tokens=32", "actor_config.lr=1e-3"], "actor/grad_norm", timeout=280)
+
+
+def _launch_dapo_long_context_worker(rank, world):
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"rl_config.actor_resource.num_gpus={world}", "megatron_training.stage=ray_dapo",
+        "actor_config.tensor_model_parallel_size=2", "actor_config.pipeline_model_parallel_size=2",
+        "actor_config.context_parallel_size=2", "actor_config.context_parallel_algo=megatron_cp_algo",
+        "generate_config.infer_tensor_parallel_size=1", "+actor_config.no_pad_to_seq_lengths=true",
+        "+actor_config.sequence_parallel=true", "+rl_config.use_dynamic_bsz=true",
+        "+rl_config.max_packing_token_size=256", "+rl_config.clip_higher_enable=true", "+rl_config.clip_ratio_low=0.2",
+        "+rl_config.clip_ratio_high=0.28", "+rl_config.token_level_loss=true", "rl_config.init_kl_coef=0.0",
+        "generate_config.sampling_config.max_tokens=32", "rl_config.n_samples_per_prompt=4",
+        "megatron_training.global_batch_size=8", "rl_config.mini_batch_size=8", "megatron_training.train_iters=2"])
+    hist = run_rl(cfg, "dapo")
+    if rank == 0:
+        assert len(hist) == 2 and all("actor/pg_loss" in m and m["timing/rollout"] > 0 for m in hist)
+        assert abs(hist[0]["actor/ppo_kl"]) < 1e-4        # first update: the policy has not moved yet
+
+
+def test_launch_dapo_long_context_recipe_shape():
+    """The long-context DAPO recipes' layout scaled down to 8 ranks: training TP2 x PP2 x CP2 (ring) with sequence
+    parallelism, packed sequences and token-budget micro-batches, rollout TP1 x DP8."""
+    run_distributed(_launch_dapo_long_context_worker, 8, timeout=280)
