@@ -1314,3 +1314,46 @@ def test_launch_dapo_long_context_recipe_shape():
     """The long-context DAPO recipes' layout scaled down to 8 ranks: training TP2 x PP2 x CP2 (ring) with sequence
     parallelism, packed sequences and token-budget micro-batches, rollout TP1 x DP8."""
     run_distributed(_launch_dapo_long_context_worker, 8, timeout=280)
+
+
+def test_launch_grpo_large_expert_recipe_shape():
+    """The 235B recipe's structure scaled down to 8 ranks: QK-norm attention, 2 real layers in 4 slots (two empty
+    slots) over PP2, training TP2 with the experts spread over TP x EP2, rollout TP4 (TP grows) x EP2."""
+    run_distributed(_launch_misc_worker, 8, [
+        "actor_config.tensor_model_parallel_size=2", "actor_config.pipeline_model_parallel_size=2",
+        "actor_config.expert_model_parallel_size=2", "+actor_config.moe_tp_extend_ep=true",
+        "+actor_config.sequence_parallel=true", "+actor_config.no_pad_to_seq_lengths=true",
+        "generate_config.infer_tensor_parallel_size=4", "generate_config.infer_expert_parallel_size=2",
+        "+model.tiny_qwen2.num_experts=8", "+model.tiny_qwen2.moe_router_topk=2",
+        "+model.tiny_qwen2.moe_ffn_hidden_size=32", "+model.tiny_qwen2.norm_topk_prob=true",
+        "+model.tiny_qwen2.qk_layernorm=true", "+model.tiny_qwen2.add_qkv_bias=false",
+        "+model.tiny_qwen2.num_attention_heads=8", "+model.tiny_qwen2.num_query_groups=4",
+        "+actor_config.num_layers=4", "+actor_config.noop_layers='1,3'",
+        "generate_config.sampling_config.max_tokens=16", "megatron_training.global_batch_size=8",
+        "rl_config.mini_batch_size=8"], "actor/grad_norm", timeout=280)
+
+
+def _launch_ppo_recipe_worker(rank, world):
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"rl_config.actor_resource.num_gpus={world}", "megatron_training.stage=ray_ppo", "rl_config.adv_estimator=gae",
+        "+critic_config.model=tiny_qwen2", "+critic_config.micro_batch_size=4", "+critic_config.lr=1e-5",
+        f"+rl_config.critic_resource.num_gpus={world}", "actor_config.tensor_model_parallel_size=4",
+        "+critic_config.tensor_model_parallel_size=4", "+actor_config.sequence_parallel=true",
+        "+critic_config.sequence_parallel=true", "generate_config.infer_tensor_parallel_size=2",
+        "+actor_config.swap_optimizer=true", "+critic_config.swap_optimizer=true",
+        "+model.tiny_qwen2.num_query_groups=4", "+generate_config.offload_train_optimizer=true",
+        "+generate_config.offload_train_grad=true", "+generate_config.offload_train_param=true",
+        "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+        "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=2"])
+    hist = run_rl(cfg, "ppo")
+    if rank == 0:
+        assert len(hist) == 2
+        assert all(m["critic/vf_loss"] >= 0 and m["actor/grad_norm"] > 0 and m["timing/update_critic"] > 0 for m in hist)
+
+
+def test_launch_ppo_recipe_shape():
+    """The PPO recipe's layout scaled down to 4 ranks: actor, reference and critic co-located, training TP4 with
+    sequence parallelism and host-resident optimizer state, every offload switch on, rollout TP2 x DP2."""
+    run_distributed(_launch_ppo_recipe_worker, 4, timeout=280)
