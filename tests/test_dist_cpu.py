@@ -1357,3 +1357,14 @@ def test_launch_ppo_recipe_shape():
     """The PPO recipe's layout scaled down to 4 ranks: actor, reference and critic co-located, training TP4 with
     sequence parallelism and host-resident optimizer state, every offload switch on, rollout TP2 x DP2."""
     run_distributed(_launch_ppo_recipe_worker, 4, timeout=280)
+
+
+def test_launch_grpo_dense_recipe_shape_with_uneven_stages():
+    """The dense recipes' layout scaled down to 4 ranks: training TP2 x PP2 with sequence parallelism, QK-norm
+    attention, 4 layers dealt 1 + 3 to the stages (``num_layer_list``), rollout TP1 x DP4."""
+    run_distributed(_launch_misc_worker, 4, [
+        "actor_config.tensor_model_parallel_size=2", "actor_config.pipeline_model_parallel_size=2",
+        "generate_config.infer_tensor_parallel_size=1", "+actor_config.no_pad_to_seq_lengths=true",
+        "+actor_config.sequence_parallel=true", "+actor_config.num_layers=4", "+actor_config.num_layer_list='1,3'",
+        "+model.tiny_qwen2.qk_layernorm=true", "generate_config.sampling_config.max_tokens=32"],
+        "actor/grad_norm", timeout=280)
