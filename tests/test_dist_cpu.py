@@ -1,6 +1,8 @@
 """Multi-rank behaviour on CPU (gloo): parallel-state rank maths, tensor/sequence-parallel model
 equivalence with the single-rank model, distributed optimizer vs single-rank Adam, expert
 parallel MoE, and the experience store served over RPC."""
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -1368,3 +1370,47 @@ def test_launch_grpo_dense_recipe_shape_with_uneven_stages():
         "+actor_config.sequence_parallel=true", "+actor_config.num_layers=4", "+actor_config.num_layer_list='1,3'",
         "+model.tiny_qwen2.qk_layernorm=true", "generate_config.sampling_config.max_tokens=32"],
         "actor/grad_norm", timeout=280)
+
+
+def _launch_ckpt_worker(rank, world, save, load, iters):
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"rl_config.actor_resource.num_gpus={world}", "actor_config.tensor_model_parallel_size=2",
+        "actor_config.pipeline_model_parallel_size=2", "generate_config.infer_tensor_parallel_size=1",
+        "+actor_config.no_pad_to_seq_lengths=true", "+actor_config.sequence_parallel=true",
+        "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+        "generate_config.sampling_config.max_tokens=8", f"megatron_training.train_iters={iters}",
+        f"actor_config.save={save}", "megatron_training.save_interval=1"] + ([f"actor_config.load={load}"] if load else []))
+    hist = run_rl(cfg, "grpo")
+    if rank == 0:
+        assert len(hist) == (iters if not load else iters - 2)
+
+
+def test_checkpoint_of_a_tp_pp_run_resumes_and_converts(tmp_path):
+    """A TP2 x PP2 run writes one directory per (TP, PP) rank; a second run resumes from it at the saved
+    iteration; the command-line converter turns the shards into Hugging Face tensors and back bit for bit."""
+    import importlib
+    import sys
+    from mindspeed_rl_b200.checkpoint import convert as C
+    from mindspeed_rl_b200.config import MegatronConfig
+    from mindspeed_rl_b200.config.loader import load_model_catalogue
+    save = str(tmp_path / "ckpt")
+    run_distributed(_launch_ckpt_worker, 4, save, None, 2, timeout=240)
+    it = tmp_path / "ckpt" / "iter_0000002"
+    assert sorted(p.name for p in it.iterdir()) == ["mp_rank_00_000", "mp_rank_00_001", "mp_rank_01_000", "mp_rank_01_001"]
+    run_distributed(_launch_ckpt_worker, 4, save, save, 3, timeout=240)
+    assert (tmp_path / "ckpt" / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
+    root = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    cli = importlib.import_module("cli.convert_ckpt")
+    cli.main(["mcore2hf", "--model", "tiny_qwen2", "--load", save, "--save", str(tmp_path / "hf"), "--tp", "2", "--pp", "2"])
+    hf = C.load_hf_state(str(tmp_path / "hf"))
+    assert hf["model.embed_tokens.weight"].shape == (1024, 256) and hf["model.layers.1.mlp.gate_proj.weight"].shape == (688, 256)
+    cfg = MegatronConfig({"model": "tiny_qwen2"}, load_model_catalogue(["tiny_qwen2"]))
+    again, orig = C.hf_to_mcore(hf, cfg, 2, 2), C.read_mcore(save, 2, 2)
+    assert sorted(orig) == [(0, 0, 0), (0, 1, 0), (1, 0, 0), (1, 1, 0)]
+    for key in orig:
+        for name, value in orig[key].items():
+            assert torch.equal(again[key][name], value), (key, name)
