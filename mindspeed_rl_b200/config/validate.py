@@ -135,6 +135,32 @@ def validate_rl_args(actor_config: MegatronConfig, ref_config: Optional[Megatron
         _require(rl.integrated_mode_config is None,
                  "integrated_mode_config must not be set when use_integrated_worker is off")
 
+    # -- what the parallel sizes have to divide ---------------------------------------------
+    a = actor_config
+    if getattr(a, "num_attention_heads", None):
+        kv_heads = a.num_query_groups if a.group_query_attention else a.num_attention_heads
+        for label, tp in (("tensor_model_parallel_size", a.tensor_model_parallel_size or 1),
+                          ("infer_tensor_parallel_size", gen.infer_tensor_parallel_size or 1)):
+            _require(a.num_attention_heads % tp == 0,
+                     f"{label} {tp} must divide the {a.num_attention_heads} attention heads")
+            _require(a.multi_latent_attention or kv_heads % tp == 0,
+                     f"{label} {tp} must divide the {kv_heads} key / value heads")
+            _require(not a.padded_vocab_size or a.padded_vocab_size % tp == 0,
+                     f"{label} {tp} must divide the padded vocabulary size {a.padded_vocab_size}")
+    if getattr(a, "num_experts", None):
+        tp, ep = a.tensor_model_parallel_size or 1, a.expert_model_parallel_size or 1
+        _require(not (tp > 1 and ep > 1) or a.moe_tp_extend_ep,
+                 "expert models with tensor_model_parallel_size > 1 and expert_model_parallel_size > 1 need "
+                 "moe_tp_extend_ep (experts are spread over TP x EP, never cut by TP)")
+        _require(not (tp > 1 and a.moe_tp_extend_ep) or a.sequence_parallel,
+                 "moe_tp_extend_ep with tensor parallelism needs sequence_parallel")
+        spread = ep * tp if a.moe_tp_extend_ep else ep
+        _require(a.num_experts % spread == 0,
+                 f"{a.num_experts} experts do not divide over {spread} training expert-parallel ranks")
+        infer_ep = gen.infer_expert_parallel_size or 1
+        _require(a.num_experts % infer_ep == 0 or bool(getattr(gen, "expert_map_path", None)),
+                 f"{a.num_experts} experts do not divide over infer_expert_parallel_size {infer_ep}")
+
     # -- lengths, CP, packing -------------------------------------------------------------
     _require(gen.max_model_len >= actor_config.seq_length,
              f"seq_length {actor_config.seq_length} exceeds generate_config.max_model_len "

@@ -98,3 +98,18 @@ def test_vision_language_model_file_sets_the_stage_layout(tmp_path):
         MegatronConfig({"num_layers": 28}).update({"model": "x"}, str(path))
     with pytest.raises(FileNotFoundError):
         MegatronConfig({"num_layers": 28}).update({"model": "x"}, str(tmp_path / "missing.json"))
+
+
+def test_layouts_that_do_not_divide_are_refused():
+    from mindspeed_rl_b200.config.loader import apply_overrides
+    base = compose("dapo_qwen3_30b_a3b_b200")
+    parse_training_config(base)                                             # the shipped recipe is fine
+    for bad in (["actor_config.moe_tp_extend_ep=false"],                     # experts would be cut by TP
+                ["megatron_training.sequence_parallel=false"],               # every TP rank would route every token
+                ["generate_config.infer_expert_parallel_size=48"],           # 128 experts over 48 ranks
+                ["actor_config.tensor_model_parallel_size=8", "rl_config.actor_resource.num_gpus=16"]):   # 4 KV heads over TP8
+        with pytest.raises(ValueError):
+            parse_training_config(apply_overrides(compose("dapo_qwen3_30b_a3b_b200"), bad))
+    with pytest.raises(ValueError):                                          # 28 heads over TP8
+        parse_training_config(apply_overrides(compose("grpo_qwen25_7b_b200"),
+                                              ["actor_config.tensor_model_parallel_size=8"]))
