@@ -1414,3 +1414,68 @@ def test_checkpoint_of_a_tp_pp_run_resumes_and_converts(tmp_path):
     for key in orig:
         for name, value in orig[key].items():
             assert torch.equal(again[key][name], value), (key, name)
+
+
+def _moe_tp_step_worker(rank, world, extend):
+    """One optimizer step of an expert model under TP2 with sequence parallelism (experts replicated over the TP
+    ranks, or spread over them) equals the step of the single-rank model: the gradient sync adds up the partial
+    gradients of routers, norms and replicated experts, and the global gradient norm counts every parameter once."""
+    from mindspeed_rl_b200.models.gpt import GPTModel, PackedMeta
+    from mindspeed_rl_b200.models.transformer_config import TransformerConfig
+    from mindspeed_rl_b200.optim.distributed_optimizer import DistributedOptimizer
+    from mindspeed_rl_b200.parallel.ddp import DistributedDataParallel, expert_replica_groups
+    from mindspeed_rl_b200.parallel.state import initialize_model_parallel, set_parallel_state
+    from mindspeed_rl_b200.parallel.tp_comm import TPComm
+    kw = dict(num_layers=2, hidden_size=32, ffn_hidden_size=64, num_attention_heads=4, num_query_groups=2,
+              vocab_size=64, add_qkv_bias=True, params_dtype=torch.float32, max_position_embeddings=128,
+              num_experts=4, moe_router_topk=2, moe_ffn_hidden_size=16, n_shared_experts=1, moe_aux_loss_coeff=0.0,
+              norm_topk_prob=True)
+    set_parallel_state(None)
+    initialize_model_parallel(world_size=1, rank=0)
+    full = DistributedDataParallel(GPTModel(TransformerConfig(**kw), device="cpu", seed=5))
+    full_opt = DistributedOptimizer(full.buffers, lr=1e-2, clip_grad=0.5, weight_decay=0.0)
+    set_parallel_state(None)
+    ps = initialize_model_parallel(tensor_model_parallel_size=world, moe_tp_extend_ep=extend)
+    cfg = TransformerConfig(tensor_model_parallel_size=world, sequence_parallel=True, **kw)
+    comm = TPComm(ps.group("tp"), True, world_size=world, rank=rank)
+    core = GPTModel(cfg, comm, device="cpu")
+    ep, er = ps.size("ep"), ps.rank_in("ep")
+    h, f, e = 32, 16, 4
+    per = e // ep
+
+    def shard(state):
+        out = _shard_state(state, cfg, world, rank)
+        for k, v in state.items():
+            if k.endswith("experts.weight1"):
+                out[k] = v.view(h, e, 2 * f)[:, er * per:(er + 1) * per].reshape(h, -1).contiguous()
+            elif k.endswith("experts.weight2"):
+                out[k] = v.view(e, f, h)[er * per:(er + 1) * per].reshape(-1, h).contiguous()
+        return out
+
+    core.load_state_dict(shard({k: v.clone() for k, v in full.module.state_dict().items()}))
+    model = DistributedDataParallel(core, ps.group("dp_cp"), 1, **expert_replica_groups(ps, cfg))
+    model.attach_tensor_parallel(ps.group("tp"), world, True)
+    opt = DistributedOptimizer(model.buffers, lr=1e-2, clip_grad=0.5, weight_decay=0.0, dp_group=ps.group("dp_cp"),
+                               dp_rank=0, model_parallel_group=ps.group("mp"), tp_rank=rank)
+    meta = PackedMeta.from_lengths([6, 10], "cpu", align=world)
+    t = int(meta.cu_seqlens[-1])
+    g = torch.Generator().manual_seed(1)
+    ids, labels, w = torch.randint(0, 64, (t,), generator=g), torch.randint(0, 64, (t,), generator=g), torch.randn(t, generator=g)
+    (full.module.forward_logprob(ids, labels, meta, 0.9, False)[0] * w).sum().backward()
+    core.embed = lambda x, _m=core: _seq_shard(_orig_embed(_m, x), world, rank)
+    (core.forward_logprob(ids, labels, meta, 0.9, False)[0] * w).sum().backward()
+    for p in list(full.module.parameters()) + list(core.parameters()):
+        if p.grad is not None:
+            p.main_grad.add_(p.grad)
+    model.finish_grad_sync(to_shards=True)
+    _, norm, _ = opt.step()
+    _, full_norm, _ = full_opt.step()
+    assert torch.allclose(norm, full_norm, rtol=2e-4), (float(norm), float(full_norm))
+    want = shard(full.module.state_dict())
+    for k, v in core.state_dict().items():
+        assert torch.allclose(v, want[k], atol=5e-5), (k, float((v - want[k]).abs().max()))
+
+
+def test_expert_layers_under_tensor_parallelism_take_the_single_rank_step():
+    run_distributed(_moe_tp_step_worker, 2, False, timeout=240)
+    run_distributed(_moe_tp_step_worker, 2, True, timeout=240)
