@@ -113,3 +113,16 @@ def test_layouts_that_do_not_divide_are_refused():
     with pytest.raises(ValueError):                                          # 28 heads over TP8
         parse_training_config(apply_overrides(compose("grpo_qwen25_7b_b200"),
                                               ["actor_config.tensor_model_parallel_size=8"]))
+
+
+def test_partial_rollout_combinations_that_are_not_served_are_refused():
+    from mindspeed_rl_b200.config.loader import apply_overrides
+    ok = apply_overrides(compose("grpo_tiny_cpu"), ["rl_config.partial_rollout_max_split=2"])
+    assert parse_training_config(ok)["rl_config"].partial_rollout_max_split == 2
+    for bad in (["rl_config.guarantee_order=true"],
+                ["+rl_config.filter_groups_enable=true", "+rl_config.filter_groups_metric=contains_token_7"],
+                ["rl_config.multi_turn_enable=true", "rl_config.async_engine=true",
+                 "rl_config.max_total_response_length=128"]):
+        with pytest.raises(ValueError):
+            parse_training_config(apply_overrides(compose("grpo_tiny_cpu"),
+                                                  ["rl_config.partial_rollout_max_split=2"] + bad))
