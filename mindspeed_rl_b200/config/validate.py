@@ -323,9 +323,6 @@ def validate_rl_args(actor_config: MegatronConfig, ref_config: Optional[Megatron
         rl.filter_groups_metric += "_rewards/mean"
     _require(not (rl.partial_rollout_max_split > 1 and rl.guarantee_order),
              "partial rollout cannot be combined with guarantee_order")
-    _require(not (rl.partial_rollout_max_split > 1 and rl.filter_groups_enable),
-             "partial rollout cannot be combined with dynamic sampling (filter_groups_enable): the sampling store "
-             "keeps no continuation state between iterations")
     _require(not (rl.partial_rollout_max_split > 1 and rl.multi_turn_enable),
              "partial rollout cannot be combined with the multi-turn tool loop")
     if rl.multi_turn_enable:

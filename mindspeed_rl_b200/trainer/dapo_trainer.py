@@ -47,16 +47,22 @@ class RayDAPOTrainer(RayBaseTrainer):
         cons = ["dynamic_sampling", "dapo_metrics"]
         # each store is shared right after it is built (the descriptor of the newest one travels)
         main = sampling = None
+        # partial rollout lives in the store that the rollout writes: the main store without dynamic sampling,
+        # the sampling store with it (the main store then only receives finished, informative groups)
+        partial_main = self.enable_partial_rollout and not self.should_filter
         if self.is_driver:
-            main = self._new_dock(self.max_num_prompt_in_batch * (2 if self.enable_partial_rollout else 1),
+            main = self._new_dock(self.max_num_prompt_in_batch * (2 if partial_main else 1),
                                   self.n_samples_per_prompt, self.metrics,
-                                  max_age=self.partial_rollout_max_split,
+                                  max_age=self.partial_rollout_max_split if partial_main else 1,
                                   GBS_train=self.max_num_prompt_in_batch, addition_columns=cols,
                                   addition_consumers=cons)
         self.transfer_dock = self._share_dock(main)
         if self.should_filter and self.is_driver:
-            sampling = self._new_dock(self.global_batch_size, self.n_samples_per_prompt,
-                                      self.sampling_metrics, addition_columns=cols,
+            two = 2 if self.enable_partial_rollout else 1
+            sampling = self._new_dock(self.global_batch_size * two, self.n_samples_per_prompt,
+                                      self.sampling_metrics,
+                                      max_age=self.partial_rollout_max_split if self.enable_partial_rollout else 1,
+                                      GBS_train=self.global_batch_size, addition_columns=cols,
                                       addition_consumers=cons)
         self.sampling_transfer_dock = self._share_dock(sampling) if self.should_filter else None
         self.actor_worker.sync_init_transfer_dock(self.transfer_dock, None, self.sampling_transfer_dock)
@@ -104,20 +110,33 @@ class RayDAPOTrainer(RayBaseTrainer):
         data_iters = iter(data_loader)
         history = []
         all_time = 0.0
+
+        def next_batch():
+            nonlocal data_iters
+            try:
+                return next(data_iters)
+            except StopIteration:
+                data_iters = iter(data_loader)
+                return next(data_iters)
+
+        if self.enable_partial_rollout and self.is_driver:
+            # two batches stay in flight: unfinished responses continue beside the fresh prompts
+            data, idx = put_prompts_experience(next_batch(), n, self.dataset_additional_keys)
+            gen_td.put_experience(padding_dict_to_tensor_dict(data), idx, is_prompt=True)
         while iteration < self.train_iters:
             t0 = time.time()
             if self.is_driver:
-                try:
-                    batch = next(data_iters)
-                except StopIteration:
-                    data_iters = iter(data_loader)
-                    batch = next(data_iters)
-                data, idx = put_prompts_experience(batch, n, self.dataset_additional_keys)
+                data, idx = put_prompts_experience(next_batch(), n, self.dataset_additional_keys,
+                                                   add_another_batch=self.enable_partial_rollout)
                 gen_td.put_experience(padding_dict_to_tensor_dict(data), idx, is_prompt=True)
             self._driver_section_done()
             if self.should_filter:
                 self.actor_worker.enter_infer_mode(blocking=self.blocking)
             self.actor_worker.generate_sequences(blocking=self.blocking)
+            if self.should_filter:
+                # the driver is about to judge and clear the sampling store: every rank must have left its
+                # rollout loop first (a rank still polling a cleared store would never see it finished)
+                self.actor_worker.barrier()
             again = False
             for reward in self.reward_list:          # model-based reward scorers: a stage every rank calls
                 if hasattr(reward, "worker"):
@@ -131,7 +150,9 @@ class RayDAPOTrainer(RayBaseTrainer):
                     # rollout / reward timings were recorded in the sampling dock: carry them over
                     for k, v in list(gen_td.get_metrics().metric.items()):
                         td.update_metrics(k, value=v, cumulate=isinstance(v, list))
-                    gen_td.clear()
+                    # under partial rollout only the groups that were judged leave the sampling store; the
+                    # unfinished ones stay and are continued beside the next batch of prompts
+                    gen_td.clear("dynamic_sampling") if self.enable_partial_rollout else gen_td.clear()
             if self.should_filter:
                 if self._decide(again):
                     all_time += time.time() - t0

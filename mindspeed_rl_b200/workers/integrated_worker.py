@@ -423,6 +423,7 @@ class IntegratedWorker(BaseWorker):
         import math
 
         rl, base = self.rl_config, self.sampling_params
+        self._partial_calls = getattr(self, "_partial_calls", 0) + 1
         max_tokens = base.max_tokens
         per_round = max(1, math.ceil(max_tokens / rl.partial_rollout_max_split))
         limit = self.engine.max_model_len
@@ -437,7 +438,14 @@ class IntegratedWorker(BaseWorker):
             budget = min(per_round, max_tokens - len(r), limit - len(p) - len(r))
             ctxs.append(p + r)
             partials.append((p, r))
-            params.append(dataclasses.replace(base, n=1, max_tokens=max(int(budget), 1)))
+            # every row is a request of its own here: with a fixed sampling seed all of them would draw the same
+            # random numbers (the samples of one prompt would come out identical, round after round), so the seed
+            # is spread over the row, the tokens it already has and the call
+            seed = base.seed
+            if seed is not None:
+                seed = (((int(seed) * 1000003 + int(idx[i])) * 1000003 + len(r)) * 1000003 + self._partial_calls) \
+                    & 0x7FFFFFFF
+            params.append(dataclasses.replace(base, n=1, max_tokens=max(int(budget), 1), seed=seed))
             rids.append(f"pr_{idx[i]}_{int(age[i])}_{self.iteration}")
         outs = self.engine.generate(ctxs, params, request_ids=rids) \
             if (ctxs or self.engine.lockstep_group is not None) else []

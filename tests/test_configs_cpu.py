@@ -120,7 +120,6 @@ def test_partial_rollout_combinations_that_are_not_served_are_refused():
     ok = apply_overrides(compose("grpo_tiny_cpu"), ["rl_config.partial_rollout_max_split=2"])
     assert parse_training_config(ok)["rl_config"].partial_rollout_max_split == 2
     for bad in (["rl_config.guarantee_order=true"],
-                ["+rl_config.filter_groups_enable=true", "+rl_config.filter_groups_metric=contains_token_7"],
                 ["rl_config.multi_turn_enable=true", "rl_config.async_engine=true",
                  "rl_config.max_total_response_length=128"]):
         with pytest.raises(ValueError):

@@ -183,3 +183,36 @@ def test_grpo_multi_turn_tool_loop_cpu():
     for row, n in zip(mask, lens.tolist()):
         live = row[:n]
         assert int(live.sum()) < n and int(live[:12].sum()) == 12 and int(live[12]) == 0   # first turn counts, tool turn does not
+
+
+def test_dapo_dynamic_sampling_with_partial_rollout_cpu():
+    """Dynamic sampling and partial rollout together (the combination of the DAPO benchmark configuration): the
+    rollout writes rounds of at most max_tokens / 2 new tokens into the sampling store, finished groups are
+    judged and the informative ones moved to the training store, unfinished ones continue beside the next
+    batch of prompts.  The samples of one prompt must differ although the sampling seed is fixed."""
+    torch.manual_seed(0)
+    actor, rl, gen = _configs("ray_dapo", clip_higher_enable=True, clip_ratio_low=0.2, clip_ratio_high=0.28,
+                              filter_groups_enable=True, filter_groups_metric="contains_token_7",
+                              filter_groups_max_batches=20, filter_groups_train_batch_size=2, token_level_loss=True,
+                              partial_rollout_max_split=2)
+    validate_rl_args(actor, None, actor, rl, gen)
+    worker = IntegratedWorker(actor, rl, gen, eos_token_id=63, pad_token_id=0, device="cpu", with_reference=False)
+    group = SPMDWorkerGroup(worker, 1).initialize()
+    trainer = RayDAPOTrainer(group, reward_list=[RuleReward(rl, None, actor)], train_iters=2, save_interval=0,
+                             global_batch_size=4, n_samples_per_prompt=4, pad_token_id=0,
+                             partial_rollout_max_split=2)
+    store = trainer.sampling_transfer_dock
+    assert store.enable_partial_rollout and store.max_len == 2 * 4 * 4 and not trainer.transfer_dock.enable_partial_rollout
+    groups_seen = []
+    judge = trainer.dynamic_sampling
+
+    def spy():
+        rows = [r.tolist() for r in store.experience_data["responses"][:16] if r is not None]
+        groups_seen.extend(rows[i:i + 4] for i in range(0, len(rows) - 3, 4))
+        return judge()
+
+    trainer.dynamic_sampling = spy
+    hist = trainer.fit(SyntheticPromptLoader(4, 12, 63, seed=0, num_batches=200))
+    assert len(hist) == 2 and all(m["train/num_gen_batches"] >= 1 and "actor/pg_loss" in m for m in hist)
+    assert all(-1.0 < m["dapo/score/mean"] < 1.0 and m["response_length/max"] <= 16 for m in hist)
+    assert groups_seen and all(len({tuple(r) for r in g}) > 1 for g in groups_seen), "identical samples in a group"
