@@ -1479,3 +1479,32 @@ def _moe_tp_step_worker(rank, world, extend):
 def test_expert_layers_under_tensor_parallelism_take_the_single_rank_step():
     run_distributed(_moe_tp_step_worker, 2, False, timeout=240)
     run_distributed(_moe_tp_step_worker, 2, True, timeout=240)
+
+
+def _launch_dapo_benchmark_shape_worker(rank, world):
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    cfg = compose("grpo_tiny_cpu", None, [
+        f"rl_config.actor_resource.num_gpus={world}", "megatron_training.stage=ray_dapo",
+        "actor_config.tensor_model_parallel_size=4", "actor_config.context_parallel_size=2",
+        "actor_config.context_parallel_algo=megatron_cp_algo", "+actor_config.sequence_parallel=true",
+        "generate_config.infer_tensor_parallel_size=1", "+model.tiny_qwen2.num_query_groups=4",
+        "+model.tiny_qwen2.qk_layernorm=true", "+model.tiny_qwen2.add_qkv_bias=false",
+        "rl_config.partial_rollout_max_split=2", "+rl_config.filter_groups_enable=true",
+        "+rl_config.filter_groups_metric=contains_token_7", "+rl_config.filter_groups_max_batches=60",
+        "+rl_config.filter_groups_train_batch_size=4", "+rl_config.clip_higher_enable=true",
+        "+rl_config.clip_ratio_low=0.2", "+rl_config.clip_ratio_high=0.28", "+rl_config.token_level_loss=true",
+        "rl_config.init_kl_coef=0.0", "generate_config.sampling_config.max_tokens=32",
+        "rl_config.n_samples_per_prompt=4", "megatron_training.global_batch_size=8", "rl_config.mini_batch_size=4",
+        "megatron_training.train_iters=2"])
+    hist = run_rl(cfg, "dapo")
+    if rank == 0:
+        assert len(hist) == 2
+        assert all(m["train/num_gen_batches"] >= 1 and -1.0 < m["dapo/score/mean"] < 1.0 and m["actor/grad_norm"] > 0
+                   for m in hist)
+
+
+def test_launch_dapo_benchmark_configuration_shape():
+    """The DAPO benchmark configuration's structure scaled down to 8 ranks: QK-norm attention, training TP4 x CP2
+    (ring) with sequence parallelism, rollout TP1 x DP8, clip-higher, dynamic sampling and partial rollout."""
+    run_distributed(_launch_dapo_benchmark_shape_worker, 8, timeout=280)
