@@ -325,6 +325,8 @@ def validate_rl_args(actor_config: MegatronConfig, ref_config: Optional[Megatron
              "partial rollout cannot be combined with guarantee_order")
     _require(not (rl.partial_rollout_max_split > 1 and rl.multi_turn_enable),
              "partial rollout cannot be combined with the multi-turn tool loop")
+    _require(not (rl.partial_rollout_max_split > 1 and (actor_config.stage or "") == "ray_ppo"),
+             "partial rollout is served by the GRPO and DAPO trainers only")
     if rl.multi_turn_enable:
         _require(rl.max_total_response_length >= max_tokens,
                  "max_total_response_length must be >= sampling max_tokens in multi-turn mode")
