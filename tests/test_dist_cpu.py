@@ -1508,3 +1508,11 @@ def test_launch_dapo_benchmark_configuration_shape():
     """The DAPO benchmark configuration's structure scaled down to 8 ranks: QK-norm attention, training TP4 x CP2
     (ring) with sequence parallelism, rollout TP1 x DP8, clip-higher, dynamic sampling and partial rollout."""
     run_distributed(_launch_dapo_benchmark_shape_worker, 8, timeout=280)
+
+
+def test_launch_grpo_with_the_sharded_store_and_the_side_channel():
+    """The sharded experience store (``data_strategy: tq``) with the ZeroMQ fan-out inside a TP2 replica."""
+    run_distributed(_launch_misc_worker, 2, [
+        "+rl_config.data_strategy=tq", "+rl_config.zmq_communication=true",
+        "actor_config.tensor_model_parallel_size=2", "generate_config.infer_tensor_parallel_size=2",
+        "generate_config.sampling_config.max_tokens=32"], "actor/grad_norm", timeout=240)
