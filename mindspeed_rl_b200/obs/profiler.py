@@ -134,6 +134,10 @@ class TensorDump:
         self.enabled = bool(getattr(cfg, "msprobe", False)) if enabled is None else enabled
         self.dump_path = dump_path or getattr(cfg, "dump_path", "./msprobe_dump") or "./msprobe_dump"
         self.key_data = bool(getattr(cfg, "key_data_dump", True)) if cfg is not None else True
+        # per-stage switches (``actor_train_dump`` ...): when none is set, ``key_data_dump`` covers every stage
+        names = ("actor_train_dump", "actor_infer_dump", "reference_dump", "critic_train_dump")
+        chosen = {n for n in names if bool(getattr(cfg, n, False))} if cfg is not None else set()
+        self.stages = chosen or set(names)
         self.lo = getattr(cfg, "step_start", 0) if cfg is not None else 0
         self.hi = getattr(cfg, "step_end", 1 << 30) if cfg is not None else 1 << 30
         self.save_values = save_values
@@ -152,6 +156,9 @@ class TensorDump:
         return {"shape": list(t.shape), "dtype": str(t.dtype), "numel": t.numel(), "mean": float(f.mean()),
                 "absmax": float(f.abs().max()), "min": float(f.min()), "max": float(f.max()),
                 "l2": float(f.norm()), "nan": int(torch.isnan(f).sum()), "inf": int(torch.isinf(f).sum())}
+
+    def wants(self, switch: str) -> bool:
+        return self.active() and self.key_data and switch in self.stages
 
     def save_data(self, stage: str, tensors: Dict[str, Any]) -> None:
         if not (self.active() and self.key_data):

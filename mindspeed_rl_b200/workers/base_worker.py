@@ -174,6 +174,20 @@ class BaseWorker:
                 out[k] = [row.reshape(-1) for row in v.detach().cpu()]
         self.td.put_experience(padding_dict_to_tensor_dict(out), indexes)
 
+    def dump_key_data(self, stage: str, switch: str, tensors: Dict[str, Any]) -> None:
+        """Statistics of a stage's key tensors for the accuracy-debugging dump (``msprobe_config``: prompts,
+        responses, log-probs, advantages, losses; reference call sites ``actor_hybrid_worker.py:315,349-350,573``,
+        ``grpo_actor_loss_func.py:81-89``).  Only the writer rank of a replica records."""
+        dump = getattr(self, "tensor_dump", None)
+        if dump is None or not dump.wants(switch) or not self.is_writer():
+            return
+        flat = {}
+        for k, v in tensors.items():
+            if isinstance(v, (list, tuple)) and v and torch.is_tensor(v[0]):
+                v = torch.cat([t.reshape(-1).float() for t in v])
+            flat[k] = v
+        dump.save_data(stage, flat)
+
     def update_metrics(self, key, value, cumulate=True) -> None:
         if self.is_writer():
             self.td.update_metrics(key, value=value, cumulate=cumulate)

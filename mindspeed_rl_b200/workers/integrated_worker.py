@@ -410,6 +410,9 @@ class IntegratedWorker(BaseWorker):
                 responses.append(torch.tensor(ids, dtype=torch.int64))
                 input_ids.append(torch.tensor(p + ids, dtype=torch.int64))
                 lengths.append(torch.tensor([len(ids)], dtype=torch.int32))
+        self.dump_key_data("actor_generate", "actor_infer_dump",
+                           {"prompts": prompts, "prompt_length": plen, "responses": responses,
+                            "response_length": lengths})
         self.collect_transfer_dock_data(
             {"responses": responses, "input_ids": input_ids, "response_length": lengths}, idx)
 
@@ -519,6 +522,9 @@ class IntegratedWorker(BaseWorker):
                 time.sleep(0.002)
                 continue
             lp = engine.forward(self._with_image_token(batch))
+            self.dump_key_data(consumer, "reference_dump" if out_column == "ref_log_prob" else "actor_train_dump",
+                               {"input_ids": batch["input_ids"], "response_length": batch["response_length"],
+                                out_column: lp})
             self.collect_transfer_dock_data({out_column: lp}, idx, lengths=batch["response_length"])
         self.update_metrics(timing_key, [round(_now(), 4), round(start, 4)])
 
@@ -564,6 +570,11 @@ class IntegratedWorker(BaseWorker):
                 time.sleep(0.002)
                 continue
             metrics = self.actor.update(self._with_image_token(batch), kl_ctrl)
+            self.dump_key_data("actor_update", "actor_train_dump",
+                               {**{k: batch[k] for k in ("responses", "advantages", "old_log_prob", "ref_log_prob")
+                                   if k in batch},
+                                **{k: (sum(v) / len(v) if isinstance(v, (list, tuple)) and v else v)
+                                   for k, v in metrics.items() if k.startswith("actor/")}})
             self.consumed_train_samples += len(idx) * self.parallel_state.size("dp_cp")
             if self.is_writer():
                 self.td.update_metrics("", value=metrics, cumulate=True)

@@ -260,3 +260,35 @@ def test_ppo_and_dapo_through_the_launcher():
         "+rl_config.clip_ratio_high=0.28", "+rl_config.token_level_loss=true", "rl_config.init_kl_coef=0.0"]), "dapo")
     assert len(h) == 1 and "dapo/score/mean" in h[0] and h[0]["actor/kl_loss"] == 0.0
     assert "timing/reference_model" not in h[0] or h[0]["timing/reference_model"] == 0
+
+
+def test_profiler_trace_and_key_data_dump_through_the_launcher(tmp_path):
+    """A run with the profiler on for the update stage and the accuracy-debugging dump on for the first iteration
+    leaves a trace file, the configurations and per-stage statistics of prompts, responses, log-probs, advantages
+    and losses (what the reference's system test checks after its PPO run)."""
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    prof, dump = tmp_path / "prof", tmp_path / "dump"
+    cfg = compose("grpo_tiny_cpu", None, [
+        "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+        "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=2",
+        "+profiler_config.integrated.profile=true", "+profiler_config.integrated.stage=actor_update",
+        f"+profiler_config.integrated.profile_save_path={prof}", "+profiler_config.integrated.profile_step_start=1",
+        "+profiler_config.integrated.profile_step_end=2", "+msprobe_config.msprobe=true",
+        f"+msprobe_config.dump_path={dump}", "+msprobe_config.key_data_dump=true",
+        "+msprobe_config.configurations_dump=true", "+msprobe_config.step_start=0", "+msprobe_config.step_end=0"])
+    assert len(run_rl(cfg, "grpo")) == 2
+    traces = [f for _, _, fs in os.walk(prof) for f in fs]
+    assert traces and any(f.endswith(".json") for f in traces)
+    assert (dump / "configurations.json").exists()
+    step0 = dump / "step0" / "rank0"
+    # one mini-batch per iteration: the old log-probs equal the current ones and that stage is skipped
+    assert sorted(p.name for p in step0.iterdir()) == ["actor_generate.json", "actor_update.json", "ref_log_prob.json"]
+    upd = json.loads((step0 / "actor_update.json").read_text())
+    assert {"responses", "advantages", "ref_log_prob", "actor/pg_loss", "actor/grad_norm"} <= set(upd)
+    assert upd["ref_log_prob"]["nan"] == 0 and upd["ref_log_prob"]["max"] <= 0.0
+    ref = json.loads((step0 / "ref_log_prob.json").read_text())
+    assert ref["ref_log_prob"]["numel"] > 0 and ref["ref_log_prob"]["inf"] == 0
+    gen = json.loads((step0 / "actor_generate.json").read_text())
+    assert gen["responses"]["numel"] == 4 * 2 * 8 and gen["prompt_length"]["mean"] == 64.0
+    assert not (dump / "step1").exists()                              # outside the requested step range
