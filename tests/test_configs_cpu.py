@@ -125,3 +125,32 @@ def test_partial_rollout_combinations_that_are_not_served_are_refused():
         with pytest.raises(ValueError):
             parse_training_config(apply_overrides(compose("grpo_tiny_cpu"),
                                                   ["rl_config.partial_rollout_max_split=2"] + bad))
+
+
+def test_example_scripts_point_at_existing_entry_points_and_recipes():
+    """Every launch script names a command-line entry point and a recipe that exist, and the recipe's algorithm
+    matches the entry point; the scripts parse as shell."""
+    import re
+    import subprocess
+    repo = os.path.dirname(ROOT)
+    scripts = sorted(glob.glob(os.path.join(repo, "examples", "*", "*.sh")))
+    assert len(scripts) >= 20
+    stages = {"train_grpo.py": "ray_grpo", "train_dapo.py": "ray_dapo", "train_ppo.py": "ray_ppo", "train_dpo.py": "dpo"}
+    launched = 0
+    for path in scripts + [os.path.join(repo, "examples", "common.sh")]:
+        assert subprocess.run(["bash", "-n", path]).returncode == 0, path
+        text = open(path).read()
+        for cli in re.findall(r"cli/([a-z_]+\.py)", text):
+            assert os.path.isfile(os.path.join(repo, "cli", cli)), (path, cli)
+        m = re.search(r"^launch_trainer (\S+) (\S+)", text, re.MULTILINE)
+        if m:
+            launched += 1
+            cli, recipe = m.groups()
+            assert os.path.isfile(os.path.join(repo, "cli", cli)), (path, cli)
+            assert os.path.isfile(os.path.join(ROOT, recipe + ".yaml")), (path, recipe)
+            assert compose(recipe)["megatron_training"]["stage"] == stages[cli], (path, recipe)
+    assert launched >= 19
+    # every shipped full-size recipe has a launch script
+    named = {re.search(r"^launch_trainer \S+ (\S+)", open(p).read(), re.MULTILINE) for p in scripts}
+    named = {m.group(1) for m in named if m}
+    assert {r for r in RECIPES if r.endswith("_b200")} <= named, sorted({r for r in RECIPES if r.endswith("_b200")} - named)
