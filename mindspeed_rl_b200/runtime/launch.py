@@ -177,6 +177,9 @@ def run_rl(config: Dict[str, Any], algorithm: str) -> Any:
         def factory():
             w = cls(mc, rl_config, generate_config, pad_token_id=pad, **kw)
             w._state = states.get(role, states["actor"])
+            w.profiler_config = prof_cfg
+            if cfg.get("msprobe_config") is not None and getattr(cfg["msprobe_config"], "msprobe", False):
+                w.tensor_dump = TensorDump(cfg["msprobe_config"])
             return w
         return SPMDWorkerGroup(factory=factory, ranks=placement.of(role), overlapping=disjoint).initialize()
 

@@ -200,6 +200,10 @@ class CriticWorker(_ModelWorker):
                 time.sleep(0.002)
                 continue
             metrics = self.engine.update(batch)
+            self.dump_key_data("critic_update", "critic_train_dump",
+                               {**{k: batch[k] for k in ("values", "returns", "advantages") if k in batch},
+                                **{k: (sum(v) / len(v) if isinstance(v, (list, tuple)) and v else v)
+                                   for k, v in metrics.items() if k.startswith("critic/")}})
             self.consumed_train_samples += len(idx) * self.parallel_state.size("dp_cp")
             if self.is_writer():
                 self.td.update_metrics("", value=metrics, cumulate=True)

@@ -255,6 +255,7 @@ def test_ppo_and_dapo_through_the_launcher():
         "megatron_training.train_iters=2", "+generate_config.offload_train_param=true",
         "+generate_config.offload_train_grad=true", "+generate_config.offload_train_optimizer=true"]), "ppo")
     assert len(h) == 2 and all(m["critic/vf_loss"] >= 0 and m["actor/grad_norm"] >= 0 for m in h)
+
     h = run_rl(compose("grpo_tiny_cpu", None, small + [
         "megatron_training.stage=ray_dapo", "+rl_config.clip_higher_enable=true", "+rl_config.clip_ratio_low=0.2",
         "+rl_config.clip_ratio_high=0.28", "+rl_config.token_level_loss=true", "rl_config.init_kl_coef=0.0"]), "dapo")
@@ -292,3 +293,21 @@ def test_profiler_trace_and_key_data_dump_through_the_launcher(tmp_path):
     gen = json.loads((step0 / "actor_generate.json").read_text())
     assert gen["responses"]["numel"] == 4 * 2 * 8 and gen["prompt_length"]["mean"] == 64.0
     assert not (dump / "step1").exists()                              # outside the requested step range
+
+
+def test_critic_statistics_in_the_dump(tmp_path):
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    dump = tmp_path / "dump"
+    h = run_rl(compose("grpo_tiny_cpu", None, [
+        "megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+        "generate_config.sampling_config.max_tokens=8", "megatron_training.train_iters=1",
+        "megatron_training.stage=ray_ppo", "rl_config.adv_estimator=gae", "+critic_config.model=tiny_qwen2",
+        "+critic_config.micro_batch_size=4", "+critic_config.lr=1e-5", "+rl_config.critic_resource.num_gpus=1",
+        "+msprobe_config.msprobe=true", f"+msprobe_config.dump_path={dump}", "+msprobe_config.key_data_dump=true",
+        "+msprobe_config.critic_train_dump=true", "+msprobe_config.step_start=0", "+msprobe_config.step_end=0"]), "ppo")
+    assert len(h) == 1
+    files = sorted(p.name for p in (dump / "step0" / "rank0").iterdir())
+    assert files == ["critic_update.json"]                      # only the chosen stage is recorded
+    rec = json.loads((dump / "step0" / "rank0" / "critic_update.json").read_text())
+    assert {"values", "returns", "critic/vf_loss"} <= set(rec) and rec["values"]["nan"] == 0
