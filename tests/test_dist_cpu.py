@@ -1150,7 +1150,8 @@ def test_launch_grpo_multi_turn_with_tensor_parallel_rollout():
     group step the loop together); the whitespace tokenizer never produces a call, so no tool runs."""
     run_distributed(_launch_misc_worker, 2, [
         "rl_config.multi_turn_enable=true", "rl_config.async_engine=true",
-        "rl_config.tool_config_path=configs/tools/retool.yaml", "rl_config.max_tool_calls=1",
+        "rl_config.tool_config_path=" + os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "configs",
+                                                      "tools", "retool.yaml"), "rl_config.max_tool_calls=1",
         "rl_config.max_parallel_calls=1", "rl_config.max_total_response_length=64",
         "rl_config.max_tool_response_length=16", "rl_config.tool_parser_format=hermes",
         "actor_config.tensor_model_parallel_size=2", "generate_config.infer_tensor_parallel_size=2"],
