@@ -133,9 +133,10 @@ class RayDAPOTrainer(RayBaseTrainer):
             if self.should_filter:
                 self.actor_worker.enter_infer_mode(blocking=self.blocking)
             self.actor_worker.generate_sequences(blocking=self.blocking)
-            if self.should_filter:
+            if self.should_filter or self.enable_partial_rollout:
                 # the driver is about to judge and clear the sampling store: every rank must have left its
-                # rollout loop first (a rank still polling a cleared store would never see it finished)
+                # rollout loop first (a rank still polling a cleared store would never see it finished); under
+                # partial rollout the set of completed groups must stand still before any stage picks its rows
                 self.actor_worker.barrier()
             again = False
             for reward in self.reward_list:          # model-based reward scorers: a stage every rank calls

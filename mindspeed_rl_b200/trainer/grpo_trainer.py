@@ -93,6 +93,10 @@ class RayGRPOTrainer(RayBaseTrainer):
                 self._driver_section_done()
             # rollout
             self.actor_worker.generate_sequences(blocking=self.blocking)
+            if self.enable_partial_rollout:
+                # the set of completed groups must stand still before any stage picks its rows: a replica that
+                # is still writing results would shift the window the other stages have already started on
+                self.actor_worker.barrier()
             # model-based reward scorers are stages of a worker group: every rank of the job makes the call
             for reward in self.reward_list:
                 if hasattr(reward, "worker"):
