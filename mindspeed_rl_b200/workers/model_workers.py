@@ -51,7 +51,7 @@ class _ModelWorker(BaseWorker):
         core = GPTModel(tcfg, self.comm, device=self.device, seed=self.seed)
         if self.init_from is not None:
             core.load_state_dict(self.init_from.state_dict(), strict=False)
-        if mc.load:
+        if mc.load and not self.trainable:
             from ..checkpoint.mcore import load_checkpoint
 
             load_checkpoint(mc.load, core, None, None, ps, mc, strict=not self.value_head)
@@ -72,6 +72,13 @@ class _ModelWorker(BaseWorker):
                 self.model.buffers, dp_group=ps.group("dp_cp"), dp_rank=ps.rank_in("dp_cp"),
                 model_parallel_group=ps.group("mp"), tp_rank=ps.rank_in("tp"),
                 total_steps=max(mc.train_iters or 1, 1), warmup_steps=0, default_lr=1e-6)
+            if mc.load:
+                # trainable roles (the critic) resume with their optimizer state, schedule and step count; a
+                # checkpoint without a value head (fine-tuning from a policy) loads loosely and starts at step 0
+                from ..checkpoint.mcore import load_checkpoint
+
+                self.iteration, self.consumed_train_samples = load_checkpoint(
+                    mc.load, core, self.optimizer, self.scheduler, ps, mc, strict=not self.value_head)
             self.engine = TrainingEngine(self.model, self.optimizer, self.scheduler, role=self.role,
                                          mini_batch_size_per_dp=max(rl.mini_batch_size // dp, 1),
                                          epochs=rl.epochs, shuffle_mini_batch=rl.shuffle_mini_batch,

@@ -311,3 +311,27 @@ def test_critic_statistics_in_the_dump(tmp_path):
     assert files == ["critic_update.json"]                      # only the chosen stage is recorded
     rec = json.loads((dump / "step0" / "rank0" / "critic_update.json").read_text())
     assert {"values", "returns", "critic/vf_loss"} <= set(rec) and rec["values"]["nan"] == 0
+
+
+def test_ppo_resumes_actor_and_critic(tmp_path):
+    """PPO writes a checkpoint per trainable role; a second run resumes both: one more iteration is trained and the
+    critic's optimizer carries on from its saved step count."""
+    import torch
+    from mindspeed_rl_b200.config import compose
+    from mindspeed_rl_b200.runtime.launch import run_rl
+    actor_dir, critic_dir = tmp_path / "actor", tmp_path / "critic"
+    base = ["megatron_training.global_batch_size=4", "rl_config.mini_batch_size=4", "rl_config.n_samples_per_prompt=2",
+            "generate_config.sampling_config.max_tokens=8", "megatron_training.stage=ray_ppo",
+            "rl_config.adv_estimator=gae", "+critic_config.model=tiny_qwen2", "+critic_config.micro_batch_size=4",
+            "+critic_config.lr=1e-3", "+rl_config.critic_resource.num_gpus=1", f"actor_config.save={actor_dir}",
+            f"+critic_config.save={critic_dir}", "megatron_training.save_interval=1"]
+    assert len(run_rl(compose("grpo_tiny_cpu", None, base + ["megatron_training.train_iters=2"]), "ppo")) == 2
+    resumed = run_rl(compose("grpo_tiny_cpu", None, base + [
+        "megatron_training.train_iters=3", f"actor_config.load={actor_dir}", f"+critic_config.load={critic_dir}"]), "ppo")
+    assert len(resumed) == 1
+    for d in (actor_dir, critic_dir):
+        assert (d / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
+    state = torch.load(critic_dir / "iter_0000003" / "mp_rank_00" / "model_optim_rng.pt", weights_only=False)
+    optim = torch.load(critic_dir / "iter_0000003" / "mp_rank_00" / "distrib_optim.pt", weights_only=False)
+    assert state["iteration"] == 3 and optim["step"] == 3
+    assert any(k.startswith("rm_head") for k in state["model"])
